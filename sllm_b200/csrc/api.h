@@ -1,0 +1,53 @@
+/* C ABI of the sm_100a kernel library (libsllm_b200_kernels.so).
+ *
+ * Conventions shared by every entry point:
+ *   - returns 0 when the kernel was launched, a small positive SllmStatus code otherwise; nothing is
+ *     launched when arguments are rejected;
+ *   - pointers are device pointers unless the name says otherwise; `stream` is a cudaStream_t;
+ *   - no entry point allocates device memory: workspaces and counters are supplied by the caller
+ *     (counters must be zero before the first launch; kernels leave them zero);
+ *   - kernels that wait on barriers write a non-zero code to `status` (device int) instead of hanging.
+ *
+ * The role of this header mirrors the reference's include/sllm/hip.h (status codes :27-85, one
+ * prepare/execute pair per op :1274-1692), collapsed to one validated launch call per op.
+ */
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* gemm_tcgen05.cu */
+long long sllm_gemm_workspace_floats(int a_rows, int b_rows, int bn, int splits);
+int sllm_gemm(const void* a, const void* b, void* y, const float* scale_a, const float* scale_b,
+              const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out, int ldy,
+              int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws, long long ws_floats, int* counters,
+              int n_counters, int* status, void* stream);
+
+/* elementwise.cu */
+int sllm_embedding(const void* table, const int* ids, void* out, int tokens, int d, int vocab, float scale,
+                   void* stream);
+int sllm_rmsnorm(const void* x, const void* w, void* y_bf16, void* y_fp8, float* y_scale, int ld_scale, int rows,
+                 int d, float eps, int offset_one, void* stream);
+int sllm_gated_act(const void* in, void* y_bf16, void* y_fp8, float* y_scale, int ld_scale, int rows, int inter,
+                   int act, void* stream);
+int sllm_quant_fp8_1x128(const void* x, void* y, float* scale, int ld_scale, int rows, int k, void* stream);
+int sllm_rope_kv_append(void* qkv, const int* positions, const int* seq_index, const int* block_table,
+                        int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale, int tokens,
+                        int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8, float theta,
+                        float k_static_scale, float v_static_scale, const float* inv_freq, void* stream);
+int sllm_elementwise(const void* a, const void* b, void* y, long long n, int d, int op, float s, void* stream);
+int sllm_argmax(const void* logits, int* out_idx, float* out_val, int rows, int n, int ld, int index_offset,
+                void* stream);
+
+/* attention.cu */
+long long sllm_paged_attention_workspace_floats(int rows, int hq, int hd, int hkv, int splits);
+int sllm_paged_attention(const void* q, int q_ld, const void* k_pages, const void* v_pages, const float* k_scale,
+                         const float* v_scale, float k_static_scale, float v_static_scale, const int* block_table,
+                         int max_blocks, const int* seq_index, const int* kv_lens, int rows, int hq, int hkv, int hd,
+                         int page_size, int window, float sm_scale, int kv_fp8, void* out_bf16, void* out_fp8,
+                         float* out_scale, int ld_scale, const float* sinks, int splits, float* ws,
+                         long long ws_floats, int* counters, int n_counters, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,393 @@
+// Paged attention over the quantised KV cache (CUDA-core path): one kernel serves batched decode,
+// speculative verification (k+1 query rows per sequence, each with its own causal limit) and short or
+// cache-continuing prefill chunks.  Long fresh prefills use the tensor-core kernel in
+// prefill_attention.cu.
+//
+// Work decomposition: grid = (query rows, kv heads, KV splits); a CTA of 4 warps owns the whole GQA
+// group of one kv head for one query row and one slice of the visible keys, so each K/V byte is read
+// once per group.  Inside a warp, keys are handled 32 at a time: lane <-> key for Q.K (no shuffles in
+// the inner product), then lane <-> channel for P.V.  Per-(token, head) FP8 scales are folded into
+// the score (K) and into the probability (V), so pages are consumed in their stored encoding.
+// Partial (max, sum, acc) triples of the splits are merged by the last CTA to arrive (counter per
+// (row, kv head)); nobody waits.
+//
+// KV page layout (per layer, K and V alike): values [num_pages, page, kv_heads, head_dim] in bf16 or
+// E4M3FN, scales [num_pages, page, kv_heads] fp32.
+//
+// Counterparts in the reference: causal_attention_kernel.hip.cpp:125-495 (online softmax, split-KV
+// decode, GQA sharing, direct low-bit KV reads) and gemma_attention_kernel.hip.cpp:40 (sliding window).
+#include "common.cuh"
+#include "api.h"
+
+namespace sllm {
+
+struct PagedAttnParams {
+  const __nv_bfloat16* q;  // [rows, hq * hd] (row stride q_ld)
+  int q_ld;
+  const void* k_pages;
+  const void* v_pages;
+  const float* k_scale;
+  const float* v_scale;
+  float k_static_scale, v_static_scale;  // used when the scale planes are null (fp8-static)
+  const int* block_table;  // [num_seqs, max_blocks]
+  int max_blocks;
+  const int* seq_index;    // [rows]
+  const int* kv_lens;      // [rows] keys visible to the row (its own position + 1)
+  int hkv, page_size, window;
+  float sm_scale;
+  __nv_bfloat16* out_bf16;  // [rows, hq * hd] or null
+  uint8_t* out_fp8;         // E4M3 [rows, hq * hd] (hd == 128 only) or null
+  float* out_scale;         // [hq, ld_scale] kb-major scales for out_fp8
+  int ld_scale;
+  float* ws_o;              // [rows * hkv * splits, G, HD]
+  float* ws_ml;             // [rows * hkv * splits, G, 2]
+  int* counters;            // [rows * hkv]
+  const float* sinks;       // optional [hq] attention-sink logits (added to the softmax denominator)
+};
+
+template <int HD, bool kFp8>
+__device__ __forceinline__ void load_row16(const void* base, size_t elem_off, float (&out)[16]) {
+  if (kFp8) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(base) + elem_off);
+    const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float2 f = e4m3x2_to_f32x2(h[j]);
+      out[2 * j] = f.x;
+      out[2 * j + 1] = f.y;
+    }
+  } else {
+    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + elem_off);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const uint4 raw = p[half];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        out[half * 8 + 2 * j] = __bfloat162float(h[j].x);
+        out[half * 8 + 2 * j + 1] = __bfloat162float(h[j].y);
+      }
+    }
+  }
+}
+
+template <int HD, int G, bool kFp8>
+__global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnParams p) {
+  constexpr int EPL = HD / 32;  // channels per lane in the P.V phase
+  extern __shared__ float smem[];
+  float* q_s = smem;                       // [G][HD]
+  float* p_s = q_s + G * HD;               // [4 warps][32][G]
+  float* m_s = p_s + 4 * 32 * G;           // [4][G]
+  float* l_s = m_s + 4 * G;                // [4][G]
+  float* o_s = l_s + 4 * G;                // [4][G][HD]
+  __shared__ int s_is_last;
+  __shared__ float s_red[4];
+
+  const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hq = p.hkv * G;
+  const int seq = p.seq_index[r];
+  const int kv_len = p.kv_lens[r];
+  int first = 0;
+  if (p.window > 0 && kv_len > p.window) first = kv_len - p.window;
+  const int n = kv_len - first;
+  int chunk = (n + splits - 1) / splits;
+  chunk = (chunk + 31) & ~31;
+  const int begin = first + split * chunk;
+  int end = begin + chunk;
+  if (end > kv_len) end = kv_len;
+
+  for (int e = threadIdx.x; e < G * HD; e += blockDim.x) {
+    const int g = e / HD, d = e % HD;
+    q_s[e] = __bfloat162float(p.q[static_cast<size_t>(r) * p.q_ld + (kvh * G + g) * HD + d]) * p.sm_scale;
+  }
+  __syncthreads();
+
+  float m[G], l[G], o[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) o[g][e] = 0.f;
+  }
+  const int* bt = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
+  float* my_p = p_s + warp * 32 * G;
+
+  for (int base = begin + warp * 32; base < end; base += 4 * 32) {
+    const int tok = base + lane;
+    const bool valid = tok < end;
+    size_t slot = 0;
+    float s[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) s[g] = 0.f;
+    float vsc = 0.f;
+    if (valid) {
+      const int blk = bt[tok / p.page_size];
+      slot = (static_cast<size_t>(blk) * p.page_size + tok % p.page_size) * p.hkv + kvh;
+      const size_t off = slot * HD;
+#pragma unroll 2
+      for (int d = 0; d < HD; d += 16) {
+        float kf[16];
+        load_row16<HD, kFp8>(p.k_pages, off + d, kf);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float a = 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) a = fmaf(q_s[g * HD + d + j], kf[j], a);
+          s[g] += a;
+        }
+      }
+      if (kFp8) {
+        const float ksc = p.k_scale ? p.k_scale[slot] : p.k_static_scale;
+        vsc = p.v_scale ? p.v_scale[slot] : p.v_static_scale;
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[g] *= ksc;
+      } else {
+        vsc = 1.f;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float sv = valid ? s[g] : -INFINITY;
+      const float mx = warp_max(sv);
+      const float m_new = fmaxf(m[g], mx);
+      const float pr = valid ? __expf(sv - m_new) : 0.f;
+      const float sum = warp_sum(pr);
+      const float alpha = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - m_new);
+      l[g] = l[g] * alpha + sum;
+      m[g] = m_new;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) o[g][e] *= alpha;
+      my_p[lane * G + g] = pr * vsc;
+    }
+    __syncwarp();
+    const int cnt = min(32, end - base);
+    for (int j = 0; j < cnt; ++j) {
+      const size_t vslot = __shfl_sync(0xffffffffu, slot, j);
+      float vf[EPL];
+      if (kFp8) {
+        const uint8_t* vp = static_cast<const uint8_t*>(p.v_pages) + vslot * HD + lane * EPL;
+        if (EPL == 4) {
+          const uint32_t raw = *reinterpret_cast<const uint32_t*>(vp);
+          const float2 a = e4m3x2_to_f32x2(static_cast<uint16_t>(raw & 0xffff));
+          const float2 b = e4m3x2_to_f32x2(static_cast<uint16_t>(raw >> 16));
+          vf[0] = a.x; vf[1] = a.y; vf[2 % EPL] = b.x; vf[3 % EPL] = b.y;
+        } else if (EPL == 2) {
+          const float2 a = e4m3x2_to_f32x2(*reinterpret_cast<const uint16_t*>(vp));
+          vf[0] = a.x; vf[1 % EPL] = a.y;
+        } else {
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) vf[e] = e4m3_to_f32(vp[e]);
+        }
+      } else {
+        const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(p.v_pages) + vslot * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) vf[e] = __bfloat162float(vp[e]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float pj = my_p[j * G + g];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[g][e] = fmaf(pj, vf[e], o[g][e]);
+      }
+    }
+    __syncwarp();
+  }
+
+  // ---- merge the 4 warps
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      m_s[warp * G + g] = m[g];
+      l_s[warp * G + g] = l[g];
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) o_s[(warp * G + g) * HD + lane * EPL + e] = o[g][e];
+  }
+  __syncthreads();
+
+  const size_t unit = static_cast<size_t>(r) * p.hkv + kvh;
+  bool finalize = true;
+  if (splits > 1) {
+    float* wo = p.ws_o + (unit * splits + split) * (G * HD);
+    float* wml = p.ws_ml + (unit * splits + split) * (G * 2);
+    for (int e = threadIdx.x; e < G * HD; e += blockDim.x) {
+      const int g = e / HD, d = e % HD;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, m_s[w * G + g]);
+      float L = 0.f, O = 0.f;
+      if (M != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float f = __expf(m_s[w * G + g] - M);
+          L += l_s[w * G + g] * f;
+          O += o_s[(w * G + g) * HD + d] * f;
+        }
+      }
+      wo[e] = O;
+      if (d == 0) {
+        wml[g * 2] = M;
+        wml[g * 2 + 1] = L;
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int old = atomicAdd(&p.counters[unit], 1);
+      const int last = old == splits - 1;
+      if (last) p.counters[unit] = 0;
+      s_is_last = last;
+      __threadfence();
+    }
+    __syncthreads();
+    finalize = s_is_last != 0;
+  }
+  if (!finalize) return;
+
+  // ---- final normalisation (+ optional FP8 1x128 quantisation: one block per head when HD == 128)
+  for (int e0 = 0; e0 < G * HD; e0 += blockDim.x) {
+    const int e = e0 + threadIdx.x;
+    const bool in = e < G * HD;
+    const int g = in ? e / HD : 0, d = in ? e % HD : 0;
+    float M = -INFINITY, L = 0.f, O = 0.f;
+    if (in) {
+      if (splits > 1) {
+        const float* wo = p.ws_o + unit * splits * (G * HD);
+        const float* wml = p.ws_ml + unit * splits * (G * 2);
+        for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, __ldcg(wml + (s2 * G + g) * 2));
+        if (M != -INFINITY) {
+          for (int s2 = 0; s2 < splits; ++s2) {
+            const float ms = __ldcg(wml + (s2 * G + g) * 2);
+            const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
+            L += __ldcg(wml + (s2 * G + g) * 2 + 1) * f;
+            O += __ldcg(wo + static_cast<size_t>(s2) * G * HD + e) * f;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, m_s[w * G + g]);
+        if (M != -INFINITY) {
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float f = __expf(m_s[w * G + g] - M);
+            L += l_s[w * G + g] * f;
+            O += o_s[(w * G + g) * HD + d] * f;
+          }
+        }
+      }
+      if (p.sinks && M != -INFINITY) {
+        // A per-head sink logit joins the denominator only.
+        const float sk = p.sinks[kvh * G + g];
+        const float M2 = fmaxf(M, sk);
+        const float f = __expf(M - M2);
+        L = L * f + __expf(sk - M2);
+        O *= f;
+      }
+    }
+    float val = (L > 0.f) ? O / L : 0.f;
+    val = __bfloat162float(__float2bfloat16_rn(val));
+    const size_t oidx = static_cast<size_t>(r) * hq * HD + (kvh * G + g) * HD + d;
+    if (p.out_fp8) {
+      // HD == 128 == blockDim: this iteration is exactly head g.
+      float a = fabsf(val);
+      if (!(a == a) || a > 3.0e38f) a = 0.f;
+      a = warp_max(a);
+      if (lane == 0) s_red[warp] = a;
+      __syncthreads();
+      const float amax = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+      const float scale = amax > 0.f ? amax / 448.f : 1.f;
+      if (in) {
+        p.out_fp8[oidx] = f32_to_e4m3(val / scale);
+        if (d == 0) p.out_scale[static_cast<size_t>(kvh * G + g) * p.ld_scale + r] = scale;
+      }
+      __syncthreads();
+    } else if (in) {
+      p.out_bf16[oidx] = __float2bfloat16_rn(val);
+    }
+  }
+}
+
+template <int HD, int G, bool kFp8>
+static int launch_paged(const PagedAttnParams& p, int rows, int splits, cudaStream_t st) {
+  const size_t smem = sizeof(float) * (G * HD + 4 * 32 * G + 8 * G + 4 * G * HD);
+  static bool cfg = false;
+  if (!cfg) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(paged_attention_kernel<HD, G, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem));
+    cfg = true;
+  }
+  dim3 grid(rows, p.hkv, splits);
+  paged_attention_kernel<HD, G, kFp8><<<grid, 128, smem, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+template <int HD, bool kFp8>
+static int dispatch_g(const PagedAttnParams& p, int rows, int g, int splits, cudaStream_t st) {
+  switch (g) {
+    case 1: return launch_paged<HD, 1, kFp8>(p, rows, splits, st);
+    case 2: return launch_paged<HD, 2, kFp8>(p, rows, splits, st);
+    case 4: return launch_paged<HD, 4, kFp8>(p, rows, splits, st);
+    case 8: return launch_paged<HD, 8, kFp8>(p, rows, splits, st);
+    default: return SLLM_ERR_UNSUPPORTED_SHAPE;
+  }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT long long sllm_paged_attention_workspace_floats(int rows, int hq, int hd, int hkv, int splits) {
+  if (splits <= 1) return 0;
+  const long long g = hq / hkv;
+  return static_cast<long long>(rows) * hkv * splits * (g * hd + g * 2);
+}
+
+SLLM_EXPORT int sllm_paged_attention(const void* q, int q_ld, const void* k_pages, const void* v_pages,
+                                     const float* k_scale, const float* v_scale, float k_static_scale,
+                                     float v_static_scale, const int* block_table, int max_blocks,
+                                     const int* seq_index, const int* kv_lens, int rows, int hq, int hkv, int hd,
+                                     int page_size, int window, float sm_scale, int kv_fp8, void* out_bf16,
+                                     void* out_fp8, float* out_scale, int ld_scale, const float* sinks, int splits,
+                                     float* ws, long long ws_floats, int* counters, int n_counters, void* stream) {
+  if (!q || !k_pages || !v_pages || !block_table || !seq_index || !kv_lens || rows <= 0 || hkv <= 0 || hq % hkv)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  if (!out_bf16 && !out_fp8) return SLLM_ERR_INVALID_ARGUMENT;
+  if (out_fp8 && (hd != 128 || !out_scale)) return SLLM_ERR_UNSUPPORTED_SHAPE;
+  if (kv_fp8 && !k_scale && !(k_static_scale > 0.f && v_static_scale > 0.f)) return SLLM_ERR_INVALID_ARGUMENT;
+  if (splits < 1 || splits > 65535 || hkv > 65535) return SLLM_ERR_INVALID_ARGUMENT;
+  const int g = hq / hkv;
+  PagedAttnParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.q_ld = q_ld;
+  p.k_pages = k_pages; p.v_pages = v_pages; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.k_static_scale = k_static_scale; p.v_static_scale = v_static_scale;
+  p.block_table = block_table; p.max_blocks = max_blocks; p.seq_index = seq_index; p.kv_lens = kv_lens;
+  p.hkv = hkv; p.page_size = page_size; p.window = window; p.sm_scale = sm_scale;
+  p.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16); p.out_fp8 = static_cast<uint8_t*>(out_fp8);
+  p.out_scale = out_scale; p.ld_scale = ld_scale; p.sinks = sinks;
+  p.ws_o = nullptr; p.ws_ml = nullptr; p.counters = counters;
+  if (splits > 1) {
+    const long long units = static_cast<long long>(rows) * hkv;
+    const long long need = units * splits * (static_cast<long long>(g) * hd + g * 2);
+    if (!ws || !counters || ws_floats < need || n_counters < units) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+    p.ws_o = ws;
+    p.ws_ml = ws + units * splits * g * hd;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kv_fp8) {
+    switch (hd) {
+      case 64: return dispatch_g<64, true>(p, rows, g, splits, st);
+      case 128: return dispatch_g<128, true>(p, rows, g, splits, st);
+      case 256: return dispatch_g<256, true>(p, rows, g, splits, st);
+    }
+  } else {
+    switch (hd) {
+      case 64: return dispatch_g<64, false>(p, rows, g, splits, st);
+      case 128: return dispatch_g<128, false>(p, rows, g, splits, st);
+      case 256: return dispatch_g<256, false>(p, rows, g, splits, st);
+    }
+  }
+  return SLLM_ERR_UNSUPPORTED_SHAPE;
+}

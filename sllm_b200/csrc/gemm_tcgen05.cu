@@ -1,0 +1,465 @@
+// tcgen05 / TMEM / TMA GEMM for sm_100a:  D[a, b] = sum_k A[a, k] * B[b, k]
+//
+// Both operands are K-major (row-major with K contiguous), which is how activations [M, K] and
+// weights [N, K] are stored, so no transpose is ever materialised.  The 128-row operand A fills the
+// tensor-core M dimension; B supplies BN in {16, 32, 64, 128} columns.  Callers pick which tensor
+// plays which role:
+//   * prefill (many tokens): A = activations, B = weights, Y[a, b]            (transpose_out = 0)
+//   * decode  (few tokens) : A = weights, B = activations, Y[b, a] ("swap-AB", transpose_out = 1)
+//     so a batch of 1..128 tokens still drives full 128-row MMAs and the kernel streams the weight
+//     matrix once at HBM rate.
+// Two numeric modes:
+//   * bf16 x bf16 -> fp32 accumulate in TMEM over the whole K range (kind::f16)
+//   * E4M3 x E4M3 with fp32 scales per 128-element K block on both operands (the 1x128 block-scaled
+//     FP8 format).  Each K block is accumulated in its own TMEM buffer (double buffered) and promoted
+//     into fp32 registers with scaleA[kb, a] * scaleB[kb, b] by the epilogue warps while the tensor
+//     core works on the next block.
+// Split-K: gridDim.z CTAs share one output tile; each writes its fp32 partial to a workspace, bumps
+// a per-tile counter, and the CTA that arrives last sums the partials in split order (deterministic)
+// and writes the tile.  No CTA ever waits for another one.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 =
+// epilogue (TMEM lane quarter = warp index % 4).
+//
+// Replaces the reference's scalar-FMA matmul family and its library GEMM calls
+// (native/hip/src/matmul_kernel.hip.cpp:586-830, native/hip/src/matmul_runtime.inc:690).
+#include "common.cuh"
+#include "api.h"
+#include <cudaTypedefs.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace sllm {
+
+constexpr int kTileA = 128;        // rows of the A operand per CTA (tensor-core M)
+constexpr int kBoxBytes = 128;     // K bytes per pipeline stage row (one 128-byte swizzle row)
+constexpr int kMaxStages = 8;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int a_rows, b_rows;
+  int num_kb;          // K blocks (of kBoxBytes) over the whole K range
+  int kb_per_split;    // K blocks handled by one blockIdx.z
+  int stages;
+  int transpose_out;   // 0: Y[a, b]; 1: Y[b, a]
+  int ldy;
+  int ld_sa, ld_sb;    // leading dimensions of the kb-major scale arrays
+  int epilogue;        // 0 = store, 1 = add residual
+  const float* scale_a;  // [num_kb, ld_sa]
+  const float* scale_b;  // [num_kb, ld_sb]
+  __nv_bfloat16* y;
+  const __nv_bfloat16* residual;
+  float* ws;           // split-K partials
+  int* counters;       // one per output tile, zero between launches
+  int* status;         // device status word (0 = ok)
+};
+
+template <int BN>
+struct __align__(8) GemmBarriers {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+  float sb[2][BN];
+};
+
+template <int BN, bool kScaled>
+__global__ void __launch_bounds__(kGemmThreads, (BN <= 64 ? 2 : 1))
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // Tiles need 1024-byte alignment for the 128-byte swizzle atom.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kABytes = kTileA * kBoxBytes;
+  constexpr int kBBytes = BN * kBoxBytes;
+  constexpr int kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  constexpr int kElemsPerBox = kScaled ? 128 : 64;
+  GemmBarriers<BN>* bars = reinterpret_cast<GemmBarriers<BN>*>(smem + p.stages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int a_tile = blockIdx.x, b_tile = blockIdx.y, split = blockIdx.z;
+  const int kb0 = split * p.kb_per_split;
+  int nkb = p.num_kb - kb0;
+  if (nkb > p.kb_per_split) nkb = p.kb_per_split;
+  if (nkb < 0) nkb = 0;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->tmem_full[b], 1);
+      mbar_init(&bars->tmem_empty[b], 128);
+    }
+    bars->abort_flag = 0;
+    bars->is_last = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % p.stages;
+        const uint32_t ph = (i / p.stages) & 1;
+        if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY)) break;
+        mbar_expect_tx(&bars->full[s], kStageBytes);
+        uint8_t* sa = smem + s * kStageBytes;
+        const int x = (kb0 + i) * kElemsPerBox;
+        tma_load_2d(sa, &tm_a, &bars->full[s], x, a_tile * kTileA);
+        tma_load_2d(sa + kABytes, &tm_b, &bars->full[s], x, b_tile * BN);
+        issued = i + 1;
+      }
+      // Drain: every copy this thread started must have landed before the CTA may exit.  On the
+      // normal path these phases are already complete and the waits return at once.
+      for (int s = 0; s < p.stages; ++s) {
+        const int fills = (issued > s) ? (issued - s + p.stages - 1) / p.stages : 0;
+        if (fills > 0) {
+          int dummy_abort = 0;
+          mbar_wait(&bars->full[s], (fills - 1) & 1, &dummy_abort, p.status, SLLM_DEV_TIMEOUT_DRAIN, 200000000LL);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(kScaled ? kFmtE4M3 : kFmtBf16, kTileA, BN);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % p.stages;
+        const uint32_t ph = (i / p.stages) & 1;
+        if (!mbar_wait(&bars->full[s], ph, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL)) break;
+        const int buf = kScaled ? (i & 1) : 0;
+        if (kScaled) {
+          if (!mbar_wait(&bars->tmem_empty[buf], ((i >> 1) & 1) ^ 1, abort_flag, p.status,
+                         SLLM_DEV_TIMEOUT_TMEM_EMPTY))
+            break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + s * kStageBytes);
+        const uint64_t adesc = make_smem_desc_sw128(sa);
+        const uint64_t bdesc = make_smem_desc_sw128(sa + kABytes);
+        const uint32_t d = tmem_base + buf * BN;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per stage row
+          const uint32_t acc = kScaled ? (k > 0) : ((i > 0) || (k > 0));
+          if (kScaled)
+            umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+          else
+            umma_f16(d, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+        }
+        tc_commit(&bars->empty[s]);  // stage reusable once these MMAs have read it
+        if (kScaled) tc_commit(&bars->tmem_full[buf]);
+      }
+      if (!kScaled) tc_commit(&bars->tmem_full[0]);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (128 threads)
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;       // row of the A tile
+    const int et = threadIdx.x - 64;     // 0..127
+    const int a_row = a_tile * kTileA + row;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    float acc[BN];
+#pragma unroll
+    for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+    bool ok = true;
+
+    if (kScaled) {
+      const int b_row0 = b_tile * BN;
+      if (nkb > 0 && et < BN) {
+        const int br = b_row0 + et;
+        bars->sb[0][et] = (br < p.b_rows) ? p.scale_b[static_cast<size_t>(kb0) * p.ld_sb + br] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int i = 0; i < nkb; ++i) {
+        const int buf = i & 1;
+        float next_sb = 0.f;
+        if (i + 1 < nkb && et < BN) {
+          const int br = b_row0 + et;
+          if (br < p.b_rows) next_sb = p.scale_b[static_cast<size_t>(kb0 + i + 1) * p.ld_sb + br];
+        }
+        const float sa = (a_row < p.a_rows) ? p.scale_a[static_cast<size_t>(kb0 + i) * p.ld_sa + a_row] : 0.f;
+        if (ok) ok = mbar_wait(&bars->tmem_full[buf], (i >> 1) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < BN / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(lane_addr + buf * BN + c * 16, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              acc[c * 16 + j] = fmaf(__uint_as_float(r[j]), sa * bars->sb[buf][c * 16 + j], acc[c * 16 + j]);
+          }
+          tc_fence_before();
+          mbar_arrive(&bars->tmem_empty[buf]);
+        }
+        if (et < BN) bars->sb[buf ^ 1][et] = next_sb;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    } else {
+      if (nkb > 0) {
+        ok = mbar_wait(&bars->tmem_full[0], 0, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < BN / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(lane_addr + c * 16, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[c * 16 + j] = __uint_as_float(r[j]);
+          }
+          tc_fence_before();
+        }
+      }
+    }
+
+    // ---- split-K fix-up: last CTA to arrive for this tile reduces all partials in split order
+    bool writer = true;
+    if (gridDim.z > 1) {
+      const int tile_id = a_tile * gridDim.y + b_tile;
+      float* my = p.ws + (static_cast<size_t>(tile_id) * gridDim.z + split) * (BN * kTileA);
+#pragma unroll
+      for (int c = 0; c < BN; ++c) my[c * kTileA + row] = acc[c];
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) {
+        const int old = atomicAdd(&p.counters[tile_id], 1);
+        const int last = (old == static_cast<int>(gridDim.z) - 1);
+        if (last) p.counters[tile_id] = 0;  // ready for the next launch
+        bars->is_last = last;
+        __threadfence();
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      writer = bars->is_last != 0;
+      if (writer) {
+        const float* base = p.ws + static_cast<size_t>(tile_id) * gridDim.z * (BN * kTileA);
+#pragma unroll
+        for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+        for (int s = 0; s < static_cast<int>(gridDim.z); ++s) {
+          const float* src = base + static_cast<size_t>(s) * (BN * kTileA);
+#pragma unroll
+          for (int c = 0; c < BN; ++c) acc[c] += __ldcg(src + c * kTileA + row);
+        }
+      }
+    }
+
+    if (writer && ok && a_row < p.a_rows) {
+      if (p.transpose_out) {
+        // Y[b, a]: for a fixed column the 32 lanes of a warp write 32 consecutive bf16.
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
+          const int b_row = b_tile * BN + c;
+          if (b_row < p.b_rows) {
+            const size_t idx = static_cast<size_t>(b_row) * p.ldy + a_row;
+            float v = acc[c];
+            if (p.epilogue == 1) v += bf16_to_f32(p.residual[idx]);
+            p.y[idx] = f32_to_bf16(v);
+          }
+        }
+      } else {
+        // Y[a, b]: each thread owns BN consecutive outputs of its row; 16-byte stores.
+        const int b0 = b_tile * BN;
+        const size_t base = static_cast<size_t>(a_row) * p.ldy + b0;
+        if (b0 + BN <= p.b_rows && (p.ldy % 8) == 0) {
+#pragma unroll
+          for (int c = 0; c < BN; c += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = acc[c + j];
+            if (p.epilogue == 1) {
+              const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + base + c);
+              const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                v[2 * j] += __bfloat162float(r2[j].x);
+                v[2 * j + 1] += __bfloat162float(r2[j].y);
+              }
+            }
+            uint4 out;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            *reinterpret_cast<uint4*>(p.y + base + c) = out;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) {
+            if (b0 + c < p.b_rows) {
+              float v = acc[c];
+              if (p.epilogue == 1) v += bf16_to_f32(p.residual[base + c]);
+              p.y[base + c] = f32_to_bf16(v);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+// K-major 2-D tensor map: global [rows, k_elems], box = {128 bytes of K, box_rows}, 128-byte swizzle.
+int make_kmajor_tmap(CUtensorMap* out, const void* ptr, int elem_bytes, long long rows, long long k_elems,
+                     long long row_stride_bytes, int box_rows) {
+  auto fn = get_encode_fn();
+  if (!fn) return SLLM_ERR_DRIVER_ENTRY;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (row_stride_bytes & 15)) return SLLM_ERR_ALIGNMENT;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(k_elems), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_stride_bytes)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBoxBytes / elem_bytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = fn(out, dt, 2, const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+struct TmapKey {
+  const void* ptr;
+  long long rows, k, stride;
+  int elem, box;
+  bool operator<(const TmapKey& o) const {
+    return std::tie(ptr, rows, k, stride, elem, box) < std::tie(o.ptr, o.rows, o.k, o.stride, o.elem, o.box);
+  }
+};
+static std::map<TmapKey, CUtensorMap> g_tmap_cache;
+static std::mutex g_tmap_mutex;
+
+int cached_kmajor_tmap(CUtensorMap* out, const void* ptr, int elem_bytes, long long rows, long long k_elems,
+                       long long row_stride_bytes, int box_rows) {
+  TmapKey key{ptr, rows, k_elems, row_stride_bytes, elem_bytes, box_rows};
+  std::lock_guard<std::mutex> g(g_tmap_mutex);
+  auto it = g_tmap_cache.find(key);
+  if (it != g_tmap_cache.end()) {
+    *out = it->second;
+    return SLLM_OK;
+  }
+  int rc = make_kmajor_tmap(out, ptr, elem_bytes, rows, k_elems, row_stride_bytes, box_rows);
+  if (rc == SLLM_OK) {
+    if (g_tmap_cache.size() > 65536) g_tmap_cache.clear();
+    g_tmap_cache[key] = *out;
+  }
+  return rc;
+}
+
+template <int BN, bool kScaled>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, dim3 grid,
+                       cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(p.stages) * (kTileA + BN) * kBoxBytes + sizeof(GemmBarriers<BN>) + 1024;
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, kScaled>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return SLLM_ERR_CUDA;
+    configured = smem;
+  }
+  gemm_tcgen05_kernel<BN, kScaled><<<grid, kGemmThreads, smem, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT long long sllm_gemm_workspace_floats(int a_rows, int b_rows, int bn, int splits) {
+  if (splits <= 1) return 0;
+  const long long tiles = static_cast<long long>((a_rows + kTileA - 1) / kTileA) * ((b_rows + bn - 1) / bn);
+  return tiles * splits * bn * kTileA;
+}
+
+SLLM_EXPORT int sllm_gemm(const void* a, const void* b, void* y, const float* scale_a, const float* scale_b,
+                          const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out,
+                          int ldy, int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws,
+                          long long ws_floats, int* counters, int n_counters, int* status, void* stream) {
+  if (!a || !b || !y || a_rows <= 0 || b_rows <= 0 || k <= 0 || splits < 1) return SLLM_ERR_INVALID_ARGUMENT;
+  if (bn != 16 && bn != 32 && bn != 64 && bn != 128) return SLLM_ERR_UNSUPPORTED_SHAPE;
+  const int elem = scaled ? 1 : 2;
+  if ((static_cast<long long>(k) * elem) % 16) return SLLM_ERR_ALIGNMENT;
+  if (scaled && (!scale_a || !scale_b)) return SLLM_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(y) & 15) return SLLM_ERR_ALIGNMENT;
+  const int elems_per_box = kBoxBytes / elem;
+  const int num_kb = (k + elems_per_box - 1) / elems_per_box;
+  if (splits > num_kb) splits = num_kb;
+  const int kb_per_split = (num_kb + splits - 1) / splits;
+  splits = (num_kb + kb_per_split - 1) / kb_per_split;
+  const int a_tiles = (a_rows + kTileA - 1) / kTileA, b_tiles = (b_rows + bn - 1) / bn;
+  if (b_tiles > 65535 || splits > 65535) return SLLM_ERR_UNSUPPORTED_SHAPE;
+  if (splits > 1) {
+    if (!ws || !counters) return SLLM_ERR_INVALID_ARGUMENT;
+    if (ws_floats < static_cast<long long>(a_tiles) * b_tiles * splits * bn * kTileA || n_counters < a_tiles * b_tiles)
+      return SLLM_ERR_WORKSPACE_TOO_SMALL;
+  }
+  const int max_stages_smem = (227 * 1024 - 2048 - static_cast<int>(sizeof(GemmBarriers<128>))) / ((kTileA + bn) * kBoxBytes);
+  if (stages < 2) stages = 2;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > max_stages_smem) stages = max_stages_smem;
+
+  CUtensorMap ta, tb;
+  int rc = cached_kmajor_tmap(&ta, a, elem, a_rows, k, static_cast<long long>(k) * elem, kTileA);
+  if (rc != SLLM_OK) return rc;
+  rc = cached_kmajor_tmap(&tb, b, elem, b_rows, k, static_cast<long long>(k) * elem, bn);
+  if (rc != SLLM_OK) return rc;
+
+  GemmParams p;
+  p.a_rows = a_rows; p.b_rows = b_rows; p.num_kb = num_kb; p.kb_per_split = kb_per_split; p.stages = stages;
+  p.transpose_out = transpose_out; p.ldy = ldy; p.ld_sa = ld_sa; p.ld_sb = ld_sb;
+  p.epilogue = residual ? 1 : 0;
+  p.scale_a = scale_a; p.scale_b = scale_b;
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ws = ws; p.counters = counters; p.status = status;
+  dim3 grid(a_tiles, b_tiles, splits);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define SLLM_GEMM_CASE(BN_)                                                            \
+  case BN_:                                                                            \
+    return scaled ? launch_gemm<BN_, true>(ta, tb, p, grid, st) : launch_gemm<BN_, false>(ta, tb, p, grid, st);
+  switch (bn) {
+    SLLM_GEMM_CASE(16)
+    SLLM_GEMM_CASE(32)
+    SLLM_GEMM_CASE(64)
+    SLLM_GEMM_CASE(128)
+  }
+#undef SLLM_GEMM_CASE
+  return SLLM_ERR_UNSUPPORTED_SHAPE;
+}

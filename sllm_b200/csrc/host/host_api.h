@@ -1,0 +1,35 @@
+/* C ABI of the host runtime library (libsllm_b200_host.so): no CUDA dependency.
+ * Handles are small positive integers; functions that return a handle or a count return a negated
+ * status code on failure, all others return a status code (0 = ok).
+ */
+#pragma once
+#include <stdint.h>
+
+#define SLLM_HOST_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum SllmHostStatus {
+  SLLM_HOST_OK = 0,
+  SLLM_HOST_INVALID = 1,
+  SLLM_HOST_NOT_FOUND = 2,
+  SLLM_HOST_OUT_OF_PAGES = 3,
+  SLLM_HOST_LIMIT = 4,
+  SLLM_HOST_PARSE_ERROR = 5,
+  SLLM_HOST_BUSY = 6,
+};
+
+/* page_pool.cpp */
+SLLM_HOST_EXPORT int sllm_kv_pool_create(int num_pages, int page_size);
+SLLM_HOST_EXPORT int sllm_kv_pool_destroy(int h);
+SLLM_HOST_EXPORT int sllm_kv_pool_stats(int h, long long* out4);
+SLLM_HOST_EXPORT int sllm_kv_pool_inject_alloc_failure(int h, int fail_after_calls);
+SLLM_HOST_EXPORT int sllm_kv_page_refcount(int h, int page);
+SLLM_HOST_EXPORT int sllm_kv_seq_new(int h);
+SLLM_HOST_EXPORT int sllm_kv_seq_free(int h, int seq);
+SLLM_HOST_EXPORT int sllm_kv_seq_reserve(int h, int seq, long long new_len);
+SLLM_HOST_EXPORT int sllm_kv_seq_commit(int h, int seq, long long new_len);
+SLLM_HOST_EXPORT int sllm_kv_seq_truncate(int h, int seq, long long len);
+SLLM_HOST_EXPORT long long sllm_kv_seq_length(int h, int seq);
+SLLM_HOST_EXPORT int sllm_kv_seq_pages(int h, int seq, int* out, int cap);
+SLLM_HOST_EXPORT int sllm_kv_seq_fork(int h, int seq, long long prefix_len, int* copy_pair);
+SLLM_HOST_EXPORT int sllm_kv_seq_make_tail_private(int h, int seq, int* copy_pair);
+SLLM_HOST_EXPORT int sllm_kv_fill_block_table(int h, const int* seqs, int n, int* table, int max_blocks);

@@ -1,0 +1,282 @@
+"""Model executor: owns the weights, the paged KV cache and the CUDA-graph-captured decode step.
+
+The public calls are ``prefill`` / ``decode`` on lists of ``Sequence`` objects (used by the
+continuous-batching scheduler) and ``generate`` (batch convenience, used by the CLI and benchmarks).
+A step is transactional in the reference's sense (crates/sllm-core/src/prepared_execution.rs:25,
+docs/architecture/runtime.md:145-149): page storage is reserved before launch, and a sequence's
+published length moves only after the step's results have been read back; any exception leaves the
+published state untouched and marks only the affected sequences as failed.
+
+Decode steps run from CUDA graphs, one per padded batch size, over static input buffers (tokens,
+positions, key counts, block table); the host copies each step's inputs from pinned memory and
+reads the sampled tokens back, which is the only per-step host/device traffic
+(reference: 2 small H2D + 1 tiny D2H per step, docs/plans/main-plan.md:1297-1300).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from .. import ops
+from ..cache.paged import OutOfPages, PagedKVCache
+from ..models.config import ModelConfig
+from .batch import ForwardBatch, make_prefill_batch
+
+
+@dataclass
+class Sequence:
+    prompt: list
+    seq_id: int = -1           # handle in the page pool
+    tokens: list = field(default_factory=list)  # prompt + generated
+    num_computed: int = 0      # tokens whose KV is published
+    failed: Optional[str] = None
+    user: object = None
+
+    def __post_init__(self):
+        if not self.tokens:
+            self.tokens = list(self.prompt)
+
+    @property
+    def num_generated(self) -> int:
+        return len(self.tokens) - len(self.prompt)
+
+
+class Engine:
+    GRAPH_BATCHES = (1, 2, 4, 8, 16, 32, 64, 128)
+
+    def __init__(self, cfg: ModelConfig, model, cache: PagedKVCache, device, max_batch: int = 64,
+                 use_cuda_graphs: bool = True, tp=None):
+        self.cfg = cfg
+        self.model = model
+        self.cache = cache
+        self.device = torch.device(device)
+        self.is_cuda = self.device.type == "cuda"
+        self.max_batch = max_batch
+        self.max_blocks = (cfg.max_context + cfg.page_size - 1) // cfg.page_size
+        self.use_graphs = use_cuda_graphs and self.is_cuda
+        self.tp = tp
+        self._graphs: dict = {}
+        self._graph_launches: dict = {}
+        pin = self.is_cuda
+        # host staging (pinned) and device-side static inputs
+        self.h_tokens = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
+        self.h_positions = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
+        self.h_table = torch.zeros((max_batch, self.max_blocks), dtype=torch.int32, pin_memory=pin)
+        self.h_out = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
+        self.d_tokens = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
+        self.d_positions = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
+        self.d_kv_lens = torch.ones(max_batch, dtype=torch.int32, device=self.device)
+        self.d_seq_index = torch.arange(max_batch, dtype=torch.int32, device=self.device)
+        self.d_table = torch.zeros((max_batch, self.max_blocks), dtype=torch.int32, device=self.device)
+        self.d_out = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
+        self.d_logits = None
+        self.np_tokens = self.h_tokens.numpy()
+        self.np_positions = self.h_positions.numpy()
+        self._steps = 0
+        self._table_key = None
+        self.kernel_launches = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ------------------------------------------------------------------ sequences
+    def new_sequence(self, prompt: list, user=None) -> Sequence:
+        s = Sequence(prompt=list(prompt), user=user)
+        s.seq_id = self.cache.pool.new_seq()
+        return s
+
+    def free_sequence(self, s: Sequence) -> None:
+        if s.seq_id > 0:
+            self.cache.pool.free_seq(s.seq_id)
+            s.seq_id = -1
+
+    def rollback(self, s: Sequence, length: int) -> None:
+        """Speculative rollback / cancelled append: forget KV and tokens beyond ``length``."""
+        self.cache.pool.truncate(s.seq_id, length)
+        s.num_computed = min(s.num_computed, length)
+        del s.tokens[length:]
+
+    # ------------------------------------------------------------------ prefill
+    def prefill(self, seqs: list, chunk_tokens: int = 0, sample: bool = True):
+        """Runs the not-yet-computed prompt tokens of ``seqs``; returns greedy next tokens (list[int])
+        or, with sample=False, the last-row logits [len(seqs), vocab]."""
+        pool = self.cache.pool
+        for s in seqs:
+            pool.reserve(s.seq_id, len(s.tokens))
+        table = torch.zeros((len(seqs), self.max_blocks), dtype=torch.int32)
+        pool.fill_block_table([s.seq_id for s in seqs], table)
+        d_table = table.to(self.device, non_blocking=True) if self.is_cuda else table
+        self.h2d_bytes += table.numel() * 4
+        starts = [s.num_computed for s in seqs]
+        budget = chunk_tokens if chunk_tokens > 0 else max(len(s.tokens) for s in seqs)
+        out = None
+        while True:
+            parts, part_starts, rows = [], [], []
+            for i, s in enumerate(seqs):
+                n = min(budget, len(s.tokens) - starts[i])
+                if n > 0:
+                    parts.append(s.tokens[starts[i]:starts[i] + n])
+                    part_starts.append(starts[i])
+                    rows.append(i)
+            if not parts:
+                break
+            sub_table = d_table if len(rows) == len(seqs) else d_table[torch.tensor(rows, device=d_table.device)]
+            b = make_prefill_batch(parts, sub_table, self.device, part_starts)
+            self.h2d_bytes += b.num_tokens * 12
+            res = self.model.greedy(b, self.cache) if sample else self.model.forward(b, self.cache)
+            if out is None:
+                out = torch.zeros((len(seqs),) + tuple(res.shape[1:]), dtype=res.dtype, device=res.device)
+            out[torch.tensor(rows, device=res.device)] = res
+            for j, i in enumerate(rows):
+                starts[i] += len(parts[j])
+        if sample:
+            toks = out.tolist()
+            self.d2h_bytes += 4 * len(seqs)
+        self._table_key = None
+        self._check_status(every=1)
+        for i, s in enumerate(seqs):
+            pool.commit(s.seq_id, len(s.tokens))
+            s.num_computed = len(s.tokens)
+        return toks if sample else out
+
+    # ------------------------------------------------------------------ decode
+    def _decode_body(self, n: int, greedy: bool):
+        b = ForwardBatch(self.d_tokens[:n], self.d_positions[:n], self.d_seq_index[:n], self.d_kv_lens[:n],
+                         self.d_table[:n], None, self._max_kv)
+        if greedy:
+            self.d_out[:n] = self.model.greedy(b, self.cache)
+        else:
+            lg = self.model.forward(b, self.cache)
+            if self.d_logits is None or self.d_logits.shape[0] < self.max_batch:
+                self.d_logits = torch.empty((self.max_batch, lg.shape[1]), dtype=lg.dtype, device=lg.device)
+            self.d_logits[:n] = lg
+
+    def _padded(self, n: int) -> int:
+        for g in self.GRAPH_BATCHES:
+            if g >= n and g <= self.max_batch:
+                return g
+        return n
+
+    def _run_decode(self, n: int, greedy: bool):
+        if not self.use_graphs:
+            self._decode_body(n, greedy)
+            return
+        key = (n, greedy)
+        g = self._graphs.get(key)
+        if g is None:
+            # warm up outside capture (module init, workspace allocation), then capture
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._decode_body(n, greedy)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            from ..ops import _lib
+            before = _lib.LAUNCH_COUNT[0]
+            with torch.cuda.graph(g):
+                self._decode_body(n, greedy)
+            self._graph_launches[key] = _lib.LAUNCH_COUNT[0] - before
+            self._graphs[key] = g
+        g.replay()
+        self.kernel_launches += self._graph_launches[key]
+
+    def decode(self, seqs: list, sample: bool = True):
+        """One token for every sequence (the last token of each is the input).  Returns greedy next
+        tokens, or logits [len(seqs), vocab] with sample=False."""
+        n = len(seqs)
+        if n > self.max_batch:
+            raise ValueError("decode batch larger than max_batch")
+        pool = self.cache.pool
+        ps = self.cfg.page_size
+        for s in seqs:
+            pool.reserve(s.seq_id, len(s.tokens))
+        np_ = self._padded(n)
+        self.np_tokens[:n] = [s.tokens[-1] for s in seqs]
+        self.np_positions[:n] = [len(s.tokens) - 1 for s in seqs]
+        if np_ > n:  # padding rows replay row 0 (same token, same slot, same values: a harmless rewrite)
+            self.np_tokens[n:np_] = self.np_tokens[0]
+            self.np_positions[n:np_] = self.np_positions[0]
+        # The block table changes only when a sequence crosses a page boundary or the batch changes.
+        key = (tuple(s.seq_id for s in seqs), tuple((len(s.tokens) + ps - 1) // ps for s in seqs))
+        if key != self._table_key:
+            pool.fill_block_table([s.seq_id for s in seqs], self.h_table)
+            if np_ > n:
+                self.h_table[n:np_] = self.h_table[0]
+            self.d_table[:np_].copy_(self.h_table[:np_], non_blocking=True)
+            self.h2d_bytes += np_ * self.max_blocks * 4
+            self._table_key = key
+        self._max_kv = self.cfg.max_context
+        self.d_tokens[:np_].copy_(self.h_tokens[:np_], non_blocking=True)
+        self.d_positions[:np_].copy_(self.h_positions[:np_], non_blocking=True)
+        torch.add(self.d_positions[:np_], 1, out=self.d_kv_lens[:np_])
+        self.h2d_bytes += np_ * 8
+        self._run_decode(np_, sample)
+        if sample:
+            self.h_out[:np_].copy_(self.d_out[:np_], non_blocking=True)
+            if self.is_cuda:
+                torch.cuda.current_stream().synchronize()
+            self.d2h_bytes += np_ * 4
+            toks = self.h_out[:n].tolist()
+        self._check_status()
+        for s in seqs:
+            pool.commit(s.seq_id, len(s.tokens))
+            s.num_computed = len(s.tokens)
+        return toks if sample else self.d_logits[:n]
+
+    def _check_status(self, every: int = 64) -> None:
+        self._steps += 1
+        if self.is_cuda and (self._steps % every == 0 or every == 1):
+            ws = ops.workspace(self.device)
+            if int(ws.status.item()):
+                code = ops.device_status(self.device)
+                raise RuntimeError(f"device wait gave up (status {code}); engine must be drained")
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: list, max_new_tokens: int, eos: Optional[int] = None,
+                 on_token: Optional[Callable] = None) -> list:
+        """Greedy generation for a batch of prompts; returns the generated token lists."""
+        seqs = [self.new_sequence(p) for p in prompts]
+        try:
+            first = self.prefill(seqs)
+            done = [False] * len(seqs)
+            for i, s in enumerate(seqs):
+                s.tokens.append(first[i])
+                if on_token:
+                    on_token(i, first[i])
+                if eos is not None and first[i] == eos:
+                    done[i] = True
+            for _ in range(max_new_tokens - 1):
+                live = [s for i, s in enumerate(seqs) if not done[i]]
+                if not live:
+                    break
+                toks = self.decode(live)
+                k = 0
+                for i, s in enumerate(seqs):
+                    if done[i]:
+                        continue
+                    s.tokens.append(toks[k])
+                    if on_token:
+                        on_token(i, toks[k])
+                    if eos is not None and toks[k] == eos:
+                        done[i] = True
+                    k += 1
+            return [s.tokens[len(s.prompt):] for s in seqs]
+        finally:
+            for s in seqs:
+                self.free_sequence(s)
+
+
+def build_engine(cfg: ModelConfig, device="cuda", seed: int = 0, num_pages: Optional[int] = None,
+                 max_batch: int = 64, use_cuda_graphs: bool = True, tp=None) -> Engine:
+    """Random-init engine for a named shape (benchmarks, tests, smoke)."""
+    from ..models.llama import LlamaModel, init_random_weights
+    device = torch.device(device)
+    tp_size, tp_rank = (tp.size, tp.rank) if tp is not None else (1, 0)
+    weights = init_random_weights(cfg, device, seed, tp_size, tp_rank)
+    model = LlamaModel(cfg, weights, tp)
+    if num_pages is None:
+        num_pages = max_batch * ((cfg.max_context + cfg.page_size - 1) // cfg.page_size) + 8
+    cache = PagedKVCache(cfg, num_pages, device, kv_heads=model.local_kv_heads)
+    return Engine(cfg, model, cache, device, max_batch=max_batch, use_cuda_graphs=use_cuda_graphs, tp=tp)

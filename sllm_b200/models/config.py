@@ -1,0 +1,112 @@
+"""Model configuration shared by every decoder family, plus the named shapes used by the benchmarks.
+
+The reference hard-codes its model shapes in per-family graph builders
+(crates/sllm-core/src/qwen_graph.rs:44-110, gemma4_graph.rs:27-31, native/hip/src/moe_expert_kernel_internal.hpp:10-13);
+here one dataclass describes all of them and the graph code branches on its fields.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field, asdict
+from typing import Optional
+
+
+@dataclass
+class ModelConfig:
+    name: str = "tiny-llama"
+    family: str = "llama"            # llama | moe | qwen35 | gemma4
+    n_layers: int = 2
+    d_model: int = 256
+    n_heads: int = 4
+    n_kv_heads: int = 2
+    head_dim: int = 64
+    ffn: int = 688
+    vocab: int = 1024
+    rope_theta: float = 10000.0
+    rotary_dim: Optional[int] = None  # None = head_dim
+    rms_eps: float = 1e-5
+    norm_offset_one: bool = False     # scale = 1 + w (Qwen3.5) instead of w
+    act: str = "silu"                 # silu | gelu_tanh
+    tie_embeddings: bool = False
+    embedding_scale: float = 1.0
+    logit_softcap: float = 0.0
+    weight_format: str = "bf16"       # fp32 | bf16 | fp8 | nvfp4 | mxfp4
+    kv_format: str = "bf16"           # fp32 | bf16 | fp8 | fp8-static
+    page_size: int = 16
+    max_context: int = 8192
+    # sliding-window attention: window size and per-layer flags (True = windowed layer)
+    sliding_window: int = 0
+    window_layers: Optional[list] = None
+    attention_sinks: bool = False
+    qk_norm: bool = False
+    # mixture of experts
+    n_experts: int = 0
+    top_k: int = 0
+    expert_ffn: int = 0
+    shared_expert_ffn: int = 0
+    expert_format: str = "mxfp4"
+    # linear-attention (gated delta net) hybrid: every `full_attention_interval`-th layer is full attention
+    full_attention_interval: int = 0
+    gdn_heads: int = 0
+    gdn_head_dim: int = 0
+    gdn_conv_kernel: int = 4
+    attn_output_gate: bool = False
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+    def layer_window(self, layer: int) -> int:
+        if self.sliding_window <= 0:
+            return 0
+        if self.window_layers is None:
+            return self.sliding_window
+        return self.sliding_window if self.window_layers[layer] else 0
+
+    @property
+    def q_size(self) -> int:
+        return self.n_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+
+def tiny_llama() -> ModelConfig:
+    """2-layer CPU check model: fp32 weights, exact greedy comparison."""
+    return ModelConfig(name="tiny-llama", n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=688,
+                       vocab=1024, rope_theta=10000.0, rms_eps=1e-5, weight_format="fp32", kv_format="fp32")
+
+
+def llama3_8b(weight_format: str = "fp8", kv_format: str = "fp8") -> ModelConfig:
+    return ModelConfig(name="llama3-8b", n_layers=32, d_model=4096, n_heads=32, n_kv_heads=8, head_dim=128,
+                       ffn=14336, vocab=128256, rope_theta=500000.0, weight_format=weight_format,
+                       kv_format=kv_format)
+
+
+def llama3_70b(weight_format: str = "nvfp4", kv_format: str = "fp8") -> ModelConfig:
+    return ModelConfig(name="llama3-70b", n_layers=80, d_model=8192, n_heads=64, n_kv_heads=8, head_dim=128,
+                       ffn=28672, vocab=128256, rope_theta=500000.0, weight_format=weight_format,
+                       kv_format=kv_format)
+
+
+def llama_draft_1b() -> ModelConfig:
+    """Speculative-decoding draft: 16 layers, d=2048, 32/8 heads (head_dim 64), ffn 8192, shared vocab."""
+    return ModelConfig(name="llama-draft", n_layers=16, d_model=2048, n_heads=32, n_kv_heads=8, head_dim=64,
+                       ffn=8192, vocab=128256, rope_theta=500000.0, weight_format="bf16", kv_format="bf16")
+
+
+def gpt_oss_120b_shape() -> ModelConfig:
+    """36-layer MoE: d=2880, 64/8 heads of 64, alternating 128-token window / full attention,
+    128 experts top-4 (expert ffn 2880) in MXFP4; router and attention in bf16."""
+    return ModelConfig(name="moe-120b", family="moe", n_layers=36, d_model=2880, n_heads=64, n_kv_heads=8,
+                       head_dim=64, ffn=2880, vocab=201088, rope_theta=150000.0, weight_format="bf16",
+                       kv_format="bf16", sliding_window=128, window_layers=[i % 2 == 0 for i in range(36)],
+                       attention_sinks=True, n_experts=128, top_k=4, expert_ffn=2880, expert_format="mxfp4")
+
+
+NAMED = {
+    "tiny-llama": tiny_llama,
+    "llama3-8b": llama3_8b,
+    "llama3-70b": llama3_70b,
+    "llama-draft": llama_draft_1b,
+    "moe-120b": gpt_oss_120b_shape,
+}

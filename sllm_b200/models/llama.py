@@ -1,0 +1,206 @@
+"""Llama-style dense decoder (RMSNorm, split-half RoPE, GQA, SwiGLU) on the op layer.
+
+Per-layer op order follows the reference's dense full-attention layer
+(crates/sllm-core/src/qwen_graph.rs:2524-3501: input norm -> q/k/v matmul -> rotary + KV append ->
+causal attention -> o matmul -> residual -> post-attention norm -> gate/up matmul -> silu-mul ->
+down matmul -> residual; final norm -> lm head -> argmax), with these fusions: q/k/v and gate/up are
+single GEMMs, the norms and the activation emit the FP8 operand of the following GEMM, attention
+emits the FP8 operand of the o projection, and residual adds live in the GEMM epilogues.
+
+Tensor parallelism (absent from the reference) shards heads and the FFN dimension; the row-parallel
+projections (o, down) go through ``tp.row_linear`` which is either the fused GEMM+all-reduce kernel
+or the unfused NCCL baseline.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..engine.batch import ForwardBatch
+from ..ops.core import LinearWeight, QTensor
+from .config import ModelConfig
+
+
+class NoTP:
+    """Single-GPU stand-in for the tensor-parallel context."""
+    size = 1
+    rank = 0
+
+    def row_linear(self, x, w: LinearWeight, residual):
+        return ops.linear(x, w, residual)
+
+    def gather_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        return logits
+
+    def argmax(self, logits: torch.Tensor, vocab_offset: int) -> torch.Tensor:
+        return ops.argmax(logits)
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    qkv: LinearWeight
+    o: LinearWeight
+    mlp_norm: torch.Tensor
+    gate_up: LinearWeight
+    down: LinearWeight
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+
+
+@dataclass
+class LlamaWeights:
+    embed: torch.Tensor
+    layers: list
+    final_norm: torch.Tensor
+    lm_head: LinearWeight
+    vocab_offset: int = 0
+
+
+def _randn(shape, std, gen, device, dtype):
+    return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
+
+
+def _shard_rows(w: torch.Tensor, parts: list, tp_size: int, tp_rank: int) -> torch.Tensor:
+    """Row-shard a [sum(parts), K] weight whose row blocks (e.g. q | k | v) are each split across ranks."""
+    if tp_size == 1:
+        return w
+    out, r0 = [], 0
+    for p in parts:
+        blk = w[r0:r0 + p]
+        sz = p // tp_size
+        out.append(blk[tp_rank * sz:(tp_rank + 1) * sz])
+        r0 += p
+    return torch.cat(out, dim=0).contiguous()
+
+
+def init_random_weights(cfg: ModelConfig, device, seed: int = 0, tp_size: int = 1, tp_rank: int = 0,
+                        std: float = 0.02) -> LlamaWeights:
+    """Seeded ~N(0, std) weights of the configured shape, quantised to the resident format.
+
+    Every rank draws the full tensor from the same generator and keeps its shard, so a TP run holds
+    exactly the weights of the single-GPU run.
+    """
+    device = torch.device(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    wf = cfg.weight_format
+    dense_dtype = torch.float32 if wf == "fp32" else torch.bfloat16
+    kind = "fp8" if wf == "fp8" else "dense"
+    d, hd = cfg.d_model, cfg.head_dim
+    if cfg.n_kv_heads % tp_size and tp_size % cfg.n_kv_heads:
+        raise ValueError("kv heads and tensor-parallel size must divide one another")
+    if cfg.n_heads % tp_size or cfg.ffn % tp_size:
+        raise ValueError("heads and ffn must be divisible by the tensor-parallel size")
+
+    def lin(w: torch.Tensor) -> LinearWeight:
+        if kind == "fp8":
+            q = ops.quant_fp8(w.contiguous())
+            return LinearWeight("fp8", q.data, q.scale)
+        return LinearWeight("dense", w.contiguous())
+
+    def kv_shard(w_kv: torch.Tensor) -> torch.Tensor:
+        # fewer kv heads than ranks: each rank keeps the head its query group uses
+        if tp_size <= cfg.n_kv_heads:
+            sz = cfg.kv_size // tp_size
+            return w_kv[tp_rank * sz:(tp_rank + 1) * sz]
+        head = tp_rank * cfg.n_kv_heads // tp_size
+        return w_kv[head * hd:(head + 1) * hd]
+
+    embed = _randn((cfg.vocab, d), std, gen, device, dense_dtype)
+    layers = []
+    for _ in range(cfg.n_layers):
+        wq = _randn((cfg.q_size, d), std, gen, device, dense_dtype)
+        wk = _randn((cfg.kv_size, d), std, gen, device, dense_dtype)
+        wv = _randn((cfg.kv_size, d), std, gen, device, dense_dtype)
+        wo = _randn((d, cfg.q_size), std, gen, device, dense_dtype)
+        wg = _randn((cfg.ffn, d), std, gen, device, dense_dtype)
+        wu = _randn((cfg.ffn, d), std, gen, device, dense_dtype)
+        wd = _randn((d, cfg.ffn), std, gen, device, dense_dtype)
+        if tp_size > 1:
+            qs, fs = cfg.q_size // tp_size, cfg.ffn // tp_size
+            wq = wq[tp_rank * qs:(tp_rank + 1) * qs]
+            wk, wv = kv_shard(wk), kv_shard(wv)
+            wo = wo[:, tp_rank * qs:(tp_rank + 1) * qs]
+            wg, wu = wg[tp_rank * fs:(tp_rank + 1) * fs], wu[tp_rank * fs:(tp_rank + 1) * fs]
+            wd = wd[:, tp_rank * fs:(tp_rank + 1) * fs]
+        layers.append(LayerWeights(
+            attn_norm=torch.ones(d, device=device, dtype=dense_dtype),
+            qkv=lin(torch.cat([wq, wk, wv], dim=0)),
+            o=lin(wo),
+            mlp_norm=torch.ones(d, device=device, dtype=dense_dtype),
+            gate_up=lin(torch.cat([wg, wu], dim=0)),
+            down=lin(wd)))
+        del wq, wk, wv, wo, wg, wu, wd
+    final_norm = torch.ones(d, device=device, dtype=dense_dtype)
+    if cfg.tie_embeddings:
+        head = embed
+    else:
+        head = _randn((cfg.vocab, d), std, gen, device, dense_dtype)
+    vocab_offset = 0
+    if tp_size > 1:
+        vs = (cfg.vocab + tp_size - 1) // tp_size
+        vocab_offset = tp_rank * vs
+        head = head[vocab_offset:min(cfg.vocab, vocab_offset + vs)]
+    return LlamaWeights(embed, layers, final_norm, lin(head), vocab_offset)
+
+
+class LlamaModel:
+    """Stateless forward over a ForwardBatch; KV state lives in the PagedKVCache passed in."""
+
+    def __init__(self, cfg: ModelConfig, weights: LlamaWeights, tp=None):
+        self.cfg = cfg
+        self.w = weights
+        self.tp = tp or NoTP()
+        t = self.tp.size
+        self.hq = cfg.n_heads // t
+        self.hkv = max(1, cfg.n_kv_heads // t)
+        self.quant = cfg.weight_format == "fp8"
+
+    @property
+    def local_kv_heads(self) -> int:
+        return self.hkv
+
+    def hidden(self, b: ForwardBatch, cache) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        hd = cfg.head_dim
+        h = b.embeds if b.embeds is not None else ops.embedding(w.embed, b.tokens, cfg.embedding_scale)
+        qo = self.quant and hd == 128 and h.is_cuda
+        for li, lw in enumerate(w.layers):
+            kv = cache.layer(li)
+            x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
+            qkv = ops.linear(x, lw.qkv)
+            q = ops.rope_kv_append(qkv, b.positions, b.seq_index, b.block_table, kv, self.hq, self.hkv, hd,
+                                   cfg.rope_theta, cfg.rotary_dim)
+            a = ops.attention(q, kv, b, self.hq, self.hkv, hd, window=cfg.layer_window(li), quant_out=qo,
+                              qkv=qkv)
+            if self.quant and not qo:
+                a = ops.quant_fp8(a)
+            h = self.tp.row_linear(a, lw.o, h)
+            x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
+            gu = ops.linear(x, lw.gate_up)
+            act = ops.gated_act(gu, cfg.act, quant=self.quant)
+            h = self.tp.row_linear(act, lw.down, h)
+        return h
+
+    def logits(self, h: torch.Tensor, b: ForwardBatch) -> torch.Tensor:
+        """Local (vocab-shard) logits of the requested rows."""
+        cfg, w = self.cfg, self.w
+        if b.logit_rows is not None:
+            h = h.index_select(0, b.logit_rows)
+        x = ops.rmsnorm(h, w.final_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
+        lg = ops.linear(x, w.lm_head)
+        if cfg.logit_softcap > 0:
+            lg = ops.elementwise("tanh_softcap", lg, s=cfg.logit_softcap)
+        return lg
+
+    def forward(self, b: ForwardBatch, cache) -> torch.Tensor:
+        """Full-vocabulary logits [rows, vocab]."""
+        return self.tp.gather_logits(self.logits(self.hidden(b, cache), b))
+
+    def greedy(self, b: ForwardBatch, cache) -> torch.Tensor:
+        """Greedy next tokens (int32 [rows]) without materialising gathered logits."""
+        return self.tp.argmax(self.logits(self.hidden(b, cache), b), self.w.vocab_offset)

@@ -1,0 +1,102 @@
+"""ctypes bindings for the two native libraries.
+
+``kernels()`` loads ``libsllm_b200_kernels.so`` (CUDA, sm_100a) and raises if it is missing: there is
+no silent fallback to PyTorch on a GPU.  ``host()`` loads ``libsllm_b200_host.so`` (pure C++).
+Signatures are declared once here from ``csrc/api.h`` / ``csrc/host/host_api.h``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent.parent
+_KERNEL_PATH = _PKG / "libsllm_b200_kernels.so"
+_HOST_PATH = _PKG / "libsllm_b200_host.so"
+_lock = threading.Lock()
+_kernels = None
+_host = None
+
+P = C.c_void_p
+I = C.c_int
+L = C.c_longlong
+F = C.c_float
+
+STATUS_NAMES = {
+    0: "ok", 1: "invalid argument", 2: "unsupported shape", 3: "alignment", 4: "workspace too small",
+    5: "cuda error", 6: "driver entry point unavailable", 7: "limit exceeded",
+}
+DEVICE_STATUS_NAMES = {
+    0: "ok", 101: "timeout waiting for TMA data", 102: "timeout waiting for a free smem stage",
+    103: "timeout waiting for the accumulator", 104: "timeout waiting for a free accumulator",
+    105: "timeout waiting for a peer flag", 106: "timeout draining copies",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+LAUNCH_COUNT = [0]  # kernels launched through this library (graph capture counts once per capture)
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what}: launch rejected ({STATUS_NAMES.get(rc, rc)})")
+    LAUNCH_COUNT[0] += 1
+
+
+_KERNEL_SIGNATURES = {
+    "sllm_gemm_workspace_floats": (L, [I, I, I, I]),
+    "sllm_gemm": (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, L, P, I, P, P]),
+    "sllm_embedding": (I, [P, P, P, I, I, I, F, P]),
+    "sllm_rmsnorm": (I, [P, P, P, P, P, I, I, I, F, I, P]),
+    "sllm_gated_act": (I, [P, P, P, P, I, I, I, I, P]),
+    "sllm_quant_fp8_1x128": (I, [P, P, P, I, I, I, P]),
+    "sllm_rope_kv_append": (I, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, F, F, P, P]),
+    "sllm_elementwise": (I, [P, P, P, L, I, I, F, P]),
+    "sllm_argmax": (I, [P, P, P, I, I, I, I, P]),
+    "sllm_paged_attention_workspace_floats": (L, [I, I, I, I, I]),
+    "sllm_paged_attention": (I, [P, I, P, P, P, P, F, F, P, I, P, P, I, I, I, I, I, I, F, I, P, P, P, I, P, I, P, L,
+                                  P, I, P]),
+}
+
+# Entry points added by later translation units register themselves here (name -> (restype, argtypes)).
+EXTRA_KERNEL_SIGNATURES: dict = {}
+
+
+def kernels_available() -> bool:
+    return _KERNEL_PATH.exists()
+
+
+def kernels():
+    """The CUDA kernel library.  Raises when it has not been built."""
+    global _kernels
+    if _kernels is None:
+        with _lock:
+            if _kernels is None:
+                if not _KERNEL_PATH.exists():
+                    raise KernelError(
+                        f"{_KERNEL_PATH.name} is missing: run `python -m sllm_b200.build` (nvcc, sm_100a); "
+                        "CUDA tensors are never routed to a PyTorch fallback")
+                lib = C.CDLL(str(_KERNEL_PATH))
+                for name, (res, args) in {**_KERNEL_SIGNATURES, **EXTRA_KERNEL_SIGNATURES}.items():
+                    if hasattr(lib, name):
+                        fn = getattr(lib, name)
+                        fn.restype = res
+                        fn.argtypes = args
+                _kernels = lib
+    return _kernels
+
+
+def host():
+    """The host runtime library (page pool, grammar, sampler chain, batch planner)."""
+    global _host
+    if _host is None:
+        with _lock:
+            if _host is None:
+                if not _HOST_PATH.exists():
+                    from .. import build
+                    build.build_host()
+                _host = C.CDLL(str(_HOST_PATH))
+    return _host

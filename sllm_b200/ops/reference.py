@@ -1,0 +1,139 @@
+"""Plain PyTorch restatements of every op, computed in fp32 (or the input dtype on CPU).
+
+They serve two purposes: the numerics oracle for the CUDA kernels in the tests, and the execution
+path for CPU tensors (the tiny fp32 decoder used for token-for-token checks).  They mirror the
+kernels' rounding points (bf16 round after norm / activation, E4M3 saturation, scale = amax / 448)
+so that results are comparable within the stated tolerances.
+
+Oracle lineage: tests/reference/oracles.py:22-142 (bf16 RNE, RMSNorm), ci/tools/verify_kv_lowbit_oracle.py
+(low-bit KV) of the reference, restated from their documented maths.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+E4M3_MAX = 448.0
+
+
+def round_bf16(x: torch.Tensor) -> torch.Tensor:
+    return x.to(torch.bfloat16).to(torch.float32) if x.dtype != torch.bfloat16 else x.to(torch.float32)
+
+
+def to_e4m3(x: torch.Tensor) -> torch.Tensor:
+    """fp32 -> E4M3FN bytes (uint8): RNE, saturate to +-448, NaN -> 0x7f."""
+    xf = x.to(torch.float32)
+    nan = torch.isnan(xf)
+    q = xf.clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
+    return torch.where(nan, torch.full_like(q, 0x7F), q)
+
+
+def from_e4m3(b: torch.Tensor) -> torch.Tensor:
+    return b.view(torch.float8_e4m3fn).to(torch.float32)
+
+
+def quant_fp8_1x128(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """[M, K] -> (E4M3 bytes [M, K], scales [ceil(K/128), M] fp32)."""
+    m, k = x.shape
+    nkb = (k + 127) // 128
+    xf = x.to(torch.float32)
+    pad = nkb * 128 - k
+    if pad:
+        xf = torch.nn.functional.pad(xf, (0, pad))
+    blk = xf.view(m, nkb, 128)
+    finite = torch.where(torch.isfinite(blk), blk.abs(), torch.zeros_like(blk))
+    amax = finite.amax(dim=-1)
+    scale = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    q = to_e4m3(blk / scale.unsqueeze(-1)).view(m, nkb * 128)[:, :k].contiguous()
+    return q, scale.t().contiguous()
+
+
+def dequant_fp8_1x128(q: torch.Tensor, scale_t: torch.Tensor) -> torch.Tensor:
+    m, k = q.shape
+    s = scale_t.t().repeat_interleave(128, dim=1)[:, :k]
+    return from_e4m3(q) * s
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, offset_one: bool = False) -> torch.Tensor:
+    xf = x.to(torch.float32)
+    inv = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    g = w.to(torch.float32)
+    if offset_one:
+        g = 1.0 + g
+    return xf * inv * g
+
+
+def silu(x: torch.Tensor) -> torch.Tensor:
+    return x * torch.sigmoid(x)
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
+def gated_act(x: torch.Tensor, act: str = "silu", round_intermediate: bool = True) -> torch.Tensor:
+    inter = x.shape[-1] // 2
+    g, u = x[..., :inter].to(torch.float32), x[..., inter:].to(torch.float32)
+    a = silu(g) if act == "silu" else gelu_tanh(g)
+    if round_intermediate:
+        a = round_bf16(a)
+    return a * u
+
+
+def rope_split_half(x: torch.Tensor, positions: torch.Tensor, theta: float, rotary_dim: Optional[int] = None,
+                    inv_freq: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x: [T, H, D]; rotates the first rotary_dim channels, pairing channel i with i + rotary_dim/2."""
+    t, h, d = x.shape
+    r = rotary_dim or d
+    half = r // 2
+    xf = x.to(torch.float32)
+    if inv_freq is None:
+        inv_freq = theta ** (-2.0 * torch.arange(half, dtype=torch.float32, device=x.device) / r)
+    ang = positions.to(torch.float32).unsqueeze(-1) * inv_freq.to(torch.float32).unsqueeze(0)  # [T, half]
+    cs, sn = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
+    a, b = xf[..., :half], xf[..., half:r]
+    out = xf.clone()
+    out[..., :half] = a * cs - b * sn
+    out[..., half:r] = b * cs + a * sn
+    return out
+
+
+def quant_kv_token_head(x: torch.Tensor, static_scale: float = 0.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """x: [T, H, D] -> (E4M3 bytes, scale [T, H]) with scale = amax / 448 per (token, head)."""
+    xf = x.to(torch.float32)
+    if static_scale > 0:
+        scale = torch.full(xf.shape[:-1], static_scale, dtype=torch.float32, device=x.device)
+    else:
+        finite = torch.where(torch.isfinite(xf), xf.abs(), torch.zeros_like(xf))
+        amax = finite.amax(dim=-1)
+        scale = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    return to_e4m3(xf / scale.unsqueeze(-1)), scale
+
+
+def attention_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_len: int, window: int, sm_scale: float,
+                   sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One query row. q: [Hq, D]; k, v: [S, Hkv, D] (fp32, already dequantised); keys [first, kv_len)."""
+    hq, d = q.shape
+    hkv = k.shape[1]
+    g = hq // hkv
+    first = max(0, kv_len - window) if window > 0 else 0
+    ks = k[first:kv_len].to(torch.float32).repeat_interleave(g, dim=1)  # [S', Hq, D]
+    vs = v[first:kv_len].to(torch.float32).repeat_interleave(g, dim=1)
+    s = torch.einsum("hd,shd->hs", q.to(torch.float32) * sm_scale, ks)
+    if sink is not None:
+        s = torch.cat([s, sink.to(torch.float32).view(hq, 1)], dim=1)
+        p = torch.softmax(s, dim=-1)[:, :-1]
+    else:
+        p = torch.softmax(s, dim=-1)
+    return torch.einsum("hs,shd->hd", p, vs)
+
+
+def linear_fp8(xq: torch.Tensor, xs_t: torch.Tensor, wq: torch.Tensor, ws_t: torch.Tensor) -> torch.Tensor:
+    """Block-scaled FP8 GEMM oracle: dequantise both sides, fp32 matmul. Returns fp32 [M, N]."""
+    return dequant_fp8_1x128(xq, xs_t) @ dequant_fp8_1x128(wq, ws_t).t()
+
+
+def sm_scale_default(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)

@@ -1,0 +1,223 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+from sllm_b200 import ops
+from sllm_b200.ops import reference as ref
+from sllm_b200.ops.core import KVLayer, LinearWeight
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _status_ok():
+    assert ops.device_status(torch.device(DEV)) == 0
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (16, 384, 1024), (17, 128, 448), (32, 4096, 4096), (64, 512, 256),
+                                   (100, 640, 1024), (128, 256, 2048), (129, 512, 512), (300, 384, 1088),
+                                   (512, 1024, 4096)])
+def test_gemm_bf16(m, n, k):
+    torch.manual_seed(m * 7 + n)
+    x = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
+    r = (torch.randn(m, n, device=DEV)).bfloat16()
+    y = ops.linear(x, LinearWeight("dense", w))
+    want = x.float() @ w.float().t()
+    assert rel_err(y, want) < 6e-3
+    y2 = ops.linear(x, LinearWeight("dense", w), residual=r)
+    assert rel_err(y2, want + r.float()) < 6e-3
+    _status_ok()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (8, 6144, 4096), (32, 4096, 4096), (33, 512, 1024), (64, 384, 2048),
+                                   (128, 256, 14336), (200, 512, 1024), (1024, 1024, 4096)])
+def test_gemm_fp8_blockscaled(m, n, k):
+    torch.manual_seed(m + n + k)
+    x = (torch.randn(m, k, device=DEV) * 2).bfloat16()
+    x[:, :128] *= 30  # blocks with very different scales
+    w = (torch.randn(n, k, device=DEV) * 0.02).bfloat16()
+    lw = LinearWeight.from_dense(w.cpu(), "fp8").to(DEV)
+    xq = ops.quant_fp8(x)
+    xq_ref = ref.quant_fp8_1x128(x.cpu())
+    assert torch.equal(xq.data.cpu(), xq_ref[0])
+    assert torch.allclose(xq.scale.cpu(), xq_ref[1], rtol=1e-6, atol=0)
+    y = ops.linear(xq, lw)
+    want = ref.linear_fp8(xq_ref[0], xq_ref[1], lw.w.cpu(), lw.scale_t.cpu())
+    assert rel_err(y.cpu(), want) < 6e-3
+    # and close to the unquantised product
+    assert rel_err(y.cpu(), x.float().cpu() @ w.float().cpu().t()) < 8e-2
+    _status_ok()
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4, 7])
+def test_gemm_split_k_deterministic(splits):
+    torch.manual_seed(0)
+    m, n, k = 8, 512, 4096
+    x = torch.randn(m, k, device=DEV).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.03).bfloat16()
+    outs = []
+    for _ in range(2):
+        y = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_raw(w, x, y, transpose_out=True, bn=16, splits=splits, stages=4)
+        outs.append(y.clone())
+    assert torch.equal(outs[0], outs[1])
+    assert rel_err(outs[0], x.float() @ w.float().t()) < 6e-3
+    _status_ok()
+
+
+@pytest.mark.parametrize("rows,d", [(1, 256), (5, 4096), (33, 2048), (3, 8192), (2, 2880)])
+def test_rmsnorm(rows, d):
+    torch.manual_seed(d)
+    x = torch.randn(rows, d, device=DEV).bfloat16()
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).bfloat16()
+    for off in (False, True):
+        y = ops.rmsnorm(x, w, 1e-5, offset_one=off)
+        want = ref.rmsnorm(x.cpu(), w.cpu(), 1e-5, off)
+        assert rel_err(y.cpu(), want) < 5e-3
+    if d % 128 == 0:
+        q = ops.rmsnorm(x, w, 1e-5, quant=True)
+        want = ref.round_bf16(ref.rmsnorm(x.cpu(), w.cpu(), 1e-5))
+        deq = ref.dequant_fp8_1x128(q.data.cpu(), q.scale.cpu())
+        assert rel_err(deq, want) < 4e-2
+        assert (deq - want).abs().max() <= want.abs().max() * 0.07
+
+
+@pytest.mark.parametrize("rows,inter", [(1, 128), (7, 14336), (3, 688), (2, 1024)])
+def test_gated_act(rows, inter):
+    torch.manual_seed(inter)
+    x = torch.randn(rows, 2 * inter, device=DEV).bfloat16()
+    for act in ("silu", "gelu_tanh"):
+        y = ops.gated_act(x, act)
+        want = ref.gated_act(x.cpu(), act)
+        assert rel_err(y.cpu(), want) < 6e-3
+    if inter % 128 == 0:
+        q = ops.gated_act(x, "silu", quant=True)
+        deq = ref.dequant_fp8_1x128(q.data.cpu(), q.scale.cpu())
+        assert rel_err(deq, ref.gated_act(x.cpu(), "silu")) < 4e-2
+
+
+def test_quant_special_values():
+    x = torch.zeros(2, 256, device=DEV, dtype=torch.bfloat16)
+    x[0, 0] = float("nan")
+    x[0, 1] = float("inf")
+    x[0, 2] = 3.0
+    x[1, 130] = -5.0
+    q = ops.quant_fp8(x)
+    qr = ref.quant_fp8_1x128(x.cpu())
+    assert torch.equal(q.data.cpu(), qr[0])
+    assert torch.allclose(q.scale.cpu(), qr[1])
+    assert q.data[0, 0].item() == 0x7F and q.data[0, 1].item() == 0x7E
+    assert q.scale[1, 0].item() == 1.0  # all-zero block
+
+
+def _make_kv(num_pages, page, hkv, hd, fp8):
+    if fp8:
+        return KVLayer(torch.zeros(num_pages, page, hkv, hd, dtype=torch.uint8, device=DEV),
+                       torch.zeros(num_pages, page, hkv, hd, dtype=torch.uint8, device=DEV),
+                       torch.ones(num_pages, page, hkv, device=DEV), torch.ones(num_pages, page, hkv, device=DEV),
+                       True, page)
+    return KVLayer(torch.zeros(num_pages, page, hkv, hd, dtype=torch.bfloat16, device=DEV),
+                   torch.zeros(num_pages, page, hkv, hd, dtype=torch.bfloat16, device=DEV), None, None, False, page)
+
+
+def _cpu_kv(kv):
+    c = lambda t: None if t is None else t.cpu().clone()
+    return KVLayer(c(kv.k), c(kv.v), c(kv.k_scale), c(kv.v_scale), kv.fp8, kv.page_size)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("hq,hkv,hd,rd", [(4, 2, 64, 64), (32, 8, 128, 128), (8, 1, 128, 64), (16, 4, 256, 64)])
+def test_rope_kv_append(fp8, hq, hkv, hd, rd):
+    torch.manual_seed(hq)
+    t, page, pages = 37, 16, 12
+    qkv = torch.randn(t, (hq + 2 * hkv) * hd, device=DEV).bfloat16()
+    pos = torch.randint(0, 4 * page, (t,), device=DEV, dtype=torch.int32)
+    # distinct (seq, pos) pairs so no two tokens land on the same slot
+    seq = (torch.arange(t, device=DEV) % 3).int()
+    pos = (torch.arange(t, device=DEV) // 3 + 5).int()
+    table = torch.randperm(pages, device=DEV).int().view(3, 4)
+    kv = _make_kv(pages, page, hkv, hd, fp8)
+    kvc = _cpu_kv(kv)
+    q_ref = ops.rope_kv_append(qkv.cpu().clone(), pos.cpu(), seq.cpu(), table.cpu(), kvc, hq, hkv, hd, 10000.0, rd)
+    q = ops.rope_kv_append(qkv.clone(), pos, seq, table, kv, hq, hkv, hd, 10000.0, rd)
+    assert rel_err(q.cpu(), q_ref) < 5e-3
+    if fp8:
+        kd = ref.from_e4m3(kv.k.cpu()) * kv.k_scale.cpu().unsqueeze(-1)
+        kr = ref.from_e4m3(kvc.k) * kvc.k_scale.unsqueeze(-1)
+        vd = ref.from_e4m3(kv.v.cpu()) * kv.v_scale.cpu().unsqueeze(-1)
+        vr = ref.from_e4m3(kvc.v) * kvc.v_scale.unsqueeze(-1)
+        assert rel_err(kd, kr) < 3e-2 and rel_err(vd, vr) < 1e-6 + 3e-2
+        assert torch.equal(kv.v.cpu(), kvc.v)  # V is not rotated: bit-exact
+    else:
+        assert rel_err(kv.k.cpu(), kvc.k) < 5e-3
+        assert torch.equal(kv.v.cpu(), kvc.v)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 64), (32, 8, 128), (64, 8, 64), (8, 8, 128), (16, 4, 256)])
+@pytest.mark.parametrize("window", [0, 40])
+def test_paged_attention(fp8, hq, hkv, hd, window):
+    torch.manual_seed(hq + hd)
+    page, nseq, max_blocks = 16, 3, 40
+    lens = [1, 333, 600]
+    pages = nseq * max_blocks
+    table = torch.randperm(pages, device=DEV).int().view(nseq, max_blocks)
+    kv = _make_kv(pages, page, hkv, hd, fp8)
+    if fp8:
+        kv.k.copy_(torch.randint(0, 0x78, kv.k.shape, device=DEV, dtype=torch.uint8) |
+                   (torch.randint(0, 2, kv.k.shape, device=DEV, dtype=torch.uint8) << 7))
+        kv.v.copy_(torch.randint(0, 0x78, kv.v.shape, device=DEV, dtype=torch.uint8) |
+                   (torch.randint(0, 2, kv.v.shape, device=DEV, dtype=torch.uint8) << 7))
+        kv.k_scale.copy_(torch.rand_like(kv.k_scale) * 0.01 + 0.001)
+        kv.v_scale.copy_(torch.rand_like(kv.v_scale) * 0.01 + 0.001)
+    else:
+        kv.k.copy_(torch.randn(kv.k.shape, device=DEV))
+        kv.v.copy_(torch.randn(kv.v.shape, device=DEV))
+    # rows: one decode row per sequence + a 4-row verify block on the last sequence
+    seq_index = torch.tensor([0, 1, 2, 2, 2, 2, 2], device=DEV, dtype=torch.int32)
+    kv_lens = torch.tensor([lens[0], lens[1], lens[2], lens[2] - 1, lens[2] - 2, lens[2] - 3, 17], device=DEV,
+                           dtype=torch.int32)
+    q = torch.randn(len(seq_index), hq * hd, device=DEV).bfloat16()
+    want = ops.paged_attention(q.cpu(), _cpu_kv(kv), table.cpu(), seq_index.cpu(), kv_lens.cpu(), hq, hkv, hd,
+                               window=window)
+    for max_kv in (64, 640, 8192):  # exercises 1, few and many KV splits
+        got = ops.paged_attention(q, kv, table, seq_index, kv_lens, hq, hkv, hd, window=window, max_kv=max_kv)
+        assert rel_err(got.cpu(), want) < 8e-3, (max_kv, rel_err(got.cpu(), want))
+    if hd == 128:
+        gq = ops.paged_attention(q, kv, table, seq_index, kv_lens, hq, hkv, hd, window=window, max_kv=640,
+                                 quant_out=True)
+        deq = ref.dequant_fp8_1x128(gq.data.cpu(), gq.scale.cpu())
+        assert rel_err(deq, want) < 4e-2
+
+
+def test_argmax():
+    torch.manual_seed(3)
+    lg = torch.randn(5, 128256, device=DEV).bfloat16()
+    lg[1, 777] = 50
+    lg[1, 90000] = 50  # tie -> lowest index
+    lg[2, 5] = float("nan")
+    idx = ops.argmax(lg)
+    assert idx[1].item() == 777 and idx[2].item() == -1
+    want = lg.float().cpu().argmax(-1)
+    assert idx[0].item() == want[0].item() and idx[3].item() == want[3].item()
+
+
+def test_embedding_and_elementwise():
+    torch.manual_seed(0)
+    tab = torch.randn(1000, 256, device=DEV).bfloat16()
+    ids = torch.tensor([0, 999, 5, 5], device=DEV, dtype=torch.int32)
+    assert torch.equal(ops.embedding(tab, ids), tab[ids.long()])
+    a = torch.randn(4, 256, device=DEV).bfloat16()
+    b = torch.randn(4, 256, device=DEV).bfloat16()
+    for op, s in (("add", 0.0), ("scalar_mul", 1.7), ("sigmoid_mul", 0.0), ("tanh_softcap", 30.0)):
+        got = ops.elementwise(op, a, b, s)
+        want = ops.elementwise(op, a.cpu(), b.cpu(), s)
+        assert rel_err(got.cpu(), want) < 6e-3
