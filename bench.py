@@ -1,0 +1,274 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode throughput of the Llama-3-8B-shape model (block-scaled FP8 weights,
+FP8 paged KV cache, page 16), batch 32, 2048-token prompts, on N B200s of one node (TP = N).
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...             # the reference (unavailable: HIP/Rust only)
+
+One "step" is one decode step of the whole batch (batch output tokens).  `value` is device-timed
+(CUDA events around K graph-replayed steps with on-device token feedback); `e2e` times K calls of the
+public `Engine.decode` API, each copying that step's input tokens/positions from pinned host memory
+and reading the sampled tokens back.  Synthetic data: seeded uniform-random prompts, seeded ~N(0, 0.02)
+weights.  Each decode step streams the whole weight set (8 GB >> 126 MB L2), so no L2 flush is needed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+# Published decode rate of the reference used as the `vs_baseline` denominator: Qwen3.5-4B FP8 W8A8 on
+# MI300X, 17-in/17-out, batch 1 (ci/matrix/phase36-mi300x-session-d-summary-v1.json, row phase36-d-fp8-*).
+# The reference serialises concurrent requests, so its aggregate rate at any batch equals this number.
+REFERENCE_PUBLISHED_TOK_S = 56.62
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--model", default="llama3-8b")
+    ap.add_argument("--weights", default="fp8")
+    ap.add_argument("--kv", default="fp8")
+    ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--layers", type=int, default=0, help="profiling only: override the layer count")
+    ap.add_argument("--no-batch1", action="store_true", help="skip the extra batch-1 measurement")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        try:
+            for line in open(self.path):
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1])); smax.append(float(p[2])); power.append(float(p[3]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_reference(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference is Rust + HIP for AMD gfx1030/gfx1201/gfx942 only (no CUDA path, no cargo/hipcc "
+                       "here); `pip install /root/reference` fails at metadata generation (test-contract package "
+                       "with no importable modules)"}))
+    return 0
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    from sllm_b200 import build
+    build.build_all()
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.models import config as mc
+    from sllm_b200.ops import _lib
+
+    cfg = mc.NAMED[args.model]()
+    cfg.weight_format, cfg.kv_format = args.weights, args.kv
+    if args.layers > 0:
+        cfg.n_layers = args.layers
+        cfg.name += f"-{args.layers}layers-PROFILING-ONLY"
+    total_ctx = args.prompt + args.warmup + 2 * args.steps + 64
+    cfg.max_context = ((total_ctx + 255) // 256) * 256
+    tp = None
+    if world > 1:
+        from sllm_b200.parallel.tp import make_tp
+        tp = make_tp(world, rank, device, impl=args.tp_impl, max_tokens=max(args.batch, 128), d_model=cfg.d_model)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def measure(batch: int, steps: int, warmup: int, sample_clocks: bool):
+        eng = build_engine(cfg, device, seed=0, max_batch=batch, tp=tp)
+        g = torch.Generator().manual_seed(1234)
+        prompts = torch.randint(0, cfg.vocab, (batch, args.prompt), generator=g).tolist()
+        seqs = [eng.new_sequence(p) for p in prompts]
+        # ---- prefill (TTFT), in groups of 8 sequences to bound activation memory
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(0, batch, 8):
+            grp = seqs[i:i + 8]
+            first = eng.prefill(grp)
+            for s, t in zip(grp, first):
+                s.tokens.append(t)
+        e1.record()
+        barrier()
+        prefill_ms = max_over_ranks(e0.elapsed_time(e1))
+        # ---- warm-up through the public API (captures the CUDA graph)
+        for _ in range(warmup):
+            toks = eng.decode(seqs)
+            for s, t in zip(seqs, toks):
+                s.tokens.append(t)
+        clocks = ClockSampler(local_rank)
+        if sample_clocks and rank == 0:
+            clocks.start()
+        # ---- end-to-end: K calls of Engine.decode (pinned H2D of inputs + D2H of tokens every step)
+        h2d0, d2h0, l0 = eng.h2d_bytes, eng.d2h_bytes, eng.kernel_launches
+        barrier()
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            toks = eng.decode(seqs)
+            for s, t in zip(seqs, toks):
+                s.tokens.append(t)
+        e1.record()
+        barrier()
+        e2e_wall_ms = (time.perf_counter() - t0) * 1e3
+        e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), e2e_wall_ms))
+        h2d = (eng.h2d_bytes - h2d0) / steps
+        d2h = (eng.d2h_bytes - d2h0) / steps
+        launches_per_step = (eng.kernel_launches - l0) // steps
+        # ---- device-only: K graph replays with on-device token feedback
+        n = eng._padded(batch)
+        pool = eng.cache.pool
+        for s in seqs:
+            pool.reserve(s.seq_id, len(s.tokens) + steps + 1)
+        pool.fill_block_table([s.seq_id for s in seqs], eng.h_table)
+        eng.d_table[:batch].copy_(eng.h_table[:batch])
+        eng._table_key = None
+        graph = eng._graphs[(n, True)]
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            eng.d_tokens[:n].copy_(eng.d_out[:n])
+            eng.d_positions[:n].add_(1)
+            eng.d_kv_lens[:n].add_(1)
+            graph.replay()
+        e1.record()
+        barrier()
+        dev_ms = max_over_ranks(e0.elapsed_time(e1))
+        clk = clocks.stop() if (sample_clocks and rank == 0) else None
+        status = int(__import__("sllm_b200").ops.device_status(device))
+        for s in seqs:
+            eng.free_sequence(s)
+        res = dict(batch=batch, prefill_ms=prefill_ms, e2e_ms=e2e_ms, dev_ms=dev_ms, h2d=h2d, d2h=d2h,
+                   launches_per_step=launches_per_step, clocks=clk, status=status)
+        del eng
+        torch.cuda.empty_cache()
+        return res
+
+    main_res = measure(args.batch, args.steps, args.warmup, True)
+    extra = None
+    if not args.no_batch1 and args.batch != 1:
+        extra = measure(1, min(args.steps, 64), max(3, min(args.warmup, 4)), False)
+
+    if rank == 0:
+        k = args.steps
+        value = args.batch * k / (main_res["dev_ms"] / 1e3)
+        e2e_value = args.batch * k / (main_res["e2e_ms"] / 1e3)
+        out = {
+            "metric": "decode_output_tokens_per_s",
+            "value": round(value, 2),
+            "unit": "tok/s",
+            "n_gpus": args.gpus,
+            "steps": k,
+            "warmup": args.warmup,
+            "ms_per_step": round(main_res["dev_ms"] / k, 4),
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": round(value / REFERENCE_PUBLISHED_TOK_S, 2),
+            "dtype": "fp8_e4m3_block128_weights+fp8_kv (bf16 activations, fp32 accumulate)",
+            "data": "synthetic: seeded uniform-random prompts, seeded N(0,0.02) random-init weights",
+            "config": {"model": f"{cfg.name}-{args.weights}", "global_batch": args.batch,
+                       "seq_len": args.prompt, "output_tokens": k, "kv_cache": f"{args.kv}-paged-16",
+                       "parallelism": f"tp{args.gpus}" + (f"-{args.tp_impl}" if args.gpus > 1 else ""),
+                       "l2": "each step streams the full weight set (>> 126 MB L2); no flush needed"},
+            "clocks": main_res["clocks"],
+            "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "ms_per_step": round(main_res["e2e_ms"] / k, 4),
+                    "h2d_bytes_per_step": int(main_res["h2d"]), "d2h_bytes_per_step": int(main_res["d2h"]),
+                    "api": "sllm_b200.engine.Engine.decode"},
+            "gpu_launches": int(main_res["launches_per_step"] * k),
+            "ttft_ms_batch_prefill": round(main_res["prefill_ms"], 2),
+            "itl_ms": round(main_res["e2e_ms"] / k, 4),
+            "device_status": main_res["status"],
+            "impl": "own",
+        }
+        if extra:
+            ks = min(args.steps, 64)
+            out["batch1"] = {"tok_s_device": round(ks / (extra["dev_ms"] / 1e3), 2),
+                             "tok_s_e2e": round(ks / (extra["e2e_ms"] / 1e3), 2),
+                             "ttft_ms": round(extra["prefill_ms"], 2)}
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

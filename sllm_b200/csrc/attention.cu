@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
       const float amax = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
       const float scale = amax > 0.f ? amax / 448.f : 1.f;
       if (in) {
-        p.out_fp8[oidx] = f32_to_e4m3(val / scale);
+        p.out_fp8[oidx] = f32_to_e4m3(__fdiv_rn(val, scale));
         if (d == 0) p.out_scale[static_cast<size_t>(kvh * G + g) * p.ld_scale + r] = scale;
       }
       __syncthreads();

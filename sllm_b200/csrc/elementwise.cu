@@ -23,8 +23,10 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 }
 
 // Quantise 8 values held by each of 16 consecutive lanes (one 128-element block) and store them.
+// `store` = false for lanes that only take part in the shuffle (pointers are then never dereferenced;
+// no pointer to a local dummy is ever formed, which the compiler would fold into a dead store).
 __device__ __forceinline__ void quant_block128_store(const float (&v)[8], uint8_t* dst8, float* scale_dst,
-                                                     bool lane_writes_scale) {
+                                                     bool store, bool lane_writes_scale) {
   float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -34,13 +36,16 @@ __device__ __forceinline__ void quant_block128_store(const float (&v)[8], uint8_
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   const float scale = amax > 0.f ? amax / kE4M3Max : 1.f;
-  const float inv = 1.f / scale;
-  uint2 packed;
-  uint8_t* pb = reinterpret_cast<uint8_t*>(&packed);
+  uint32_t lo = 0, hi = 0;  // true division keeps the bytes identical to the host quantiser
 #pragma unroll
-  for (int j = 0; j < 8; ++j) pb[j] = f32_to_e4m3(v[j] * inv);
-  *reinterpret_cast<uint2*>(dst8) = packed;
-  if (lane_writes_scale) *scale_dst = scale;
+  for (int j = 0; j < 4; ++j) {
+    lo |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
+    hi |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j + 4], scale))) << (8 * j);
+  }
+  if (store) {
+    *reinterpret_cast<uint2*>(dst8) = make_uint2(lo, hi);
+    if (lane_writes_scale) *scale_dst = scale;
+  }
 }
 
 __device__ __forceinline__ void load8_bf16(const __nv_bfloat16* p, float (&v)[8]) {
@@ -128,11 +133,8 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
       for (int j = 0; j < 8; ++j) v[j] = 0.f;
     }
     if (kQuant) {
-      __align__(8) uint8_t scratch[8];
-      float sdummy;
-      uint8_t* dst = in_range ? y_fp8 + static_cast<size_t>(r) * d + i : scratch;
-      float* sdst = in_range ? y_scale + static_cast<size_t>(i >> 7) * ld_scale + r : &sdummy;
-      quant_block128_store(v, dst, sdst, in_range && (threadIdx.x & 15) == 0);
+      quant_block128_store(v, y_fp8 + static_cast<size_t>(r) * d + i,
+                           y_scale + static_cast<size_t>(i >> 7) * ld_scale + r, in_range, (threadIdx.x & 15) == 0);
     } else if (in_range) {
       store8_bf16(y_bf16 + static_cast<size_t>(r) * d + i, v);
     }
@@ -145,8 +147,8 @@ template <bool kQuant>
 __global__ void __launch_bounds__(256)
 gated_act_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ y_bf16,
                  uint8_t* __restrict__ y_fp8, float* __restrict__ y_scale, int ld_scale, int inter, int act) {
-  const int r = blockIdx.y;
-  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int r = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   // All lanes of a 16-lane group run the quantisation shuffle; out-of-range lanes contribute zeros.
   float g[8], u[8], v[8];
   const bool in_range = i < inter;
@@ -163,11 +165,8 @@ gated_act_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict
     for (int j = 0; j < 8; ++j) v[j] = 0.f;
   }
   if (kQuant) {
-    __align__(8) uint8_t scratch[8];
-    float sdummy;
-    uint8_t* dst = in_range ? y_fp8 + static_cast<size_t>(r) * inter + i : scratch;
-    float* sdst = in_range ? y_scale + static_cast<size_t>(i >> 7) * ld_scale + r : &sdummy;
-    quant_block128_store(v, dst, sdst, in_range && (threadIdx.x & 15) == 0);
+    quant_block128_store(v, y_fp8 + static_cast<size_t>(r) * inter + i,
+                         y_scale + static_cast<size_t>(i >> 7) * ld_scale + r, in_range, (threadIdx.x & 15) == 0);
   } else if (in_range) {
     store8_bf16(y_bf16 + static_cast<size_t>(r) * inter + i, v);
   }
@@ -177,8 +176,8 @@ gated_act_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict
 __global__ void __launch_bounds__(256)
 quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, float* __restrict__ scale,
                  int ld_scale, int k) {
-  const int r = blockIdx.y;
-  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int r = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   float v[8];
   const bool in_range = i < k;
   if (in_range) {
@@ -187,11 +186,8 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, f
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = 0.f;
   }
-  __align__(8) uint8_t scratch[8];
-  float sdummy;
-  uint8_t* dst = in_range ? y + static_cast<size_t>(r) * k + i : scratch;
-  float* sdst = in_range ? scale + static_cast<size_t>(i >> 7) * ld_scale + r : &sdummy;
-  quant_block128_store(v, dst, sdst, in_range && (threadIdx.x & 15) == 0);
+  quant_block128_store(v, y + static_cast<size_t>(r) * k + i, scale + static_cast<size_t>(i >> 7) * ld_scale + r,
+                       in_range, (threadIdx.x & 15) == 0);
 }
 
 // ---------------------------------------------------------------- RoPE + KV page append
@@ -262,9 +258,8 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
   amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
   const float st = is_v ? p.v_static_scale : p.k_static_scale;
   const float scale = st > 0.f ? st : (amax > 0.f ? amax / kE4M3Max : 1.f);
-  const float inv = 1.f / scale;
   uint8_t* dst = static_cast<uint8_t*>(is_v ? p.v_pages : p.k_pages) + (slot * p.hkv + kvh) * hd;
-  for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = f32_to_e4m3(rot[i] * inv);
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = f32_to_e4m3(__fdiv_rn(rot[i], scale));
   if (threadIdx.x == 0 && st <= 0.f) {
     float* sd = (is_v ? p.v_scale : p.k_scale) + slot * p.hkv + kvh;
     *sd = scale;
@@ -407,7 +402,7 @@ SLLM_EXPORT int sllm_rmsnorm(const void* x, const void* w, void* y_bf16, void* y
 SLLM_EXPORT int sllm_gated_act(const void* in, void* y_bf16, void* y_fp8, float* y_scale, int ld_scale, int rows,
                                int inter, int act, void* stream) {
   if (!in || rows <= 0 || inter <= 0 || (inter % 8)) return SLLM_ERR_INVALID_ARGUMENT;
-  dim3 grid((inter / 8 + 255) / 256, rows);
+  dim3 grid(rows, (inter / 8 + 255) / 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (y_fp8) {
     if (!y_scale) return SLLM_ERR_INVALID_ARGUMENT;
@@ -424,7 +419,7 @@ SLLM_EXPORT int sllm_gated_act(const void* in, void* y_bf16, void* y_fp8, float*
 SLLM_EXPORT int sllm_quant_fp8_1x128(const void* x, void* y, float* scale, int ld_scale, int rows, int k,
                                      void* stream) {
   if (!x || !y || !scale || rows <= 0 || k <= 0 || (k % 8)) return SLLM_ERR_INVALID_ARGUMENT;
-  dim3 grid((k / 8 + 255) / 256, rows);
+  dim3 grid(rows, (k / 8 + 255) / 256);
   quant_fp8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(y), scale, ld_scale, k);
   return check_launch();

@@ -18,6 +18,14 @@
 // a per-tile counter, and the CTA that arrives last sums the partials in split order (deterministic)
 // and writes the tile.  No CTA ever waits for another one.
 //
+// Fused all-reduce (tensor-parallel row-parallel projections): with a communicator attached, the CTA
+// that holds a finished tile of this rank's partial product pushes it (bf16) straight into every
+// peer's receive buffer with plain NVLink stores, raises a per-(tile, source) flag on the peer,
+// waits (bounded) for the peers' flags for the same tile, and sums the world's partials in rank order
+// before the usual residual/store epilogue - one kernel, tile-granular overlap of transfer and MMA,
+// bit-identical results on every rank.  Receive buffers are double-buffered by call parity; epochs
+// are per-tile device counters so CUDA-graph replays need no host-side argument changes.
+//
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 =
 // epilogue (TMEM lane quarter = warp index % 4).
 //
@@ -26,6 +34,7 @@
 #include "common.cuh"
 #include "api.h"
 #include <cudaTypedefs.h>
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -36,6 +45,16 @@ constexpr int kTileA = 128;        // rows of the A operand per CTA (tensor-core
 constexpr int kBoxBytes = 128;     // K bytes per pipeline stage row (one 128-byte swizzle row)
 constexpr int kMaxStages = 8;
 constexpr int kGemmThreads = 192;
+
+constexpr int kMaxWorld = 8;
+
+struct CommParams {
+  int world, rank;
+  long long cap_elems;                 // bf16 elements per (buffer, source) region
+  __nv_bfloat16* recv[kMaxWorld];      // recv[p]: base of rank p's receive buffer [2][world][cap_elems]
+  uint32_t* flags[kMaxWorld];          // flags[p]: base of rank p's flag array [max_tiles][world]
+  uint32_t* epoch;                     // local per-tile call counters [max_tiles]
+};
 
 struct GemmParams {
   int a_rows, b_rows;
@@ -53,6 +72,7 @@ struct GemmParams {
   float* ws;           // split-K partials
   int* counters;       // one per output tile, zero between launches
   int* status;         // device status word (0 = ok)
+  CommParams comm;     // used by the kComm instantiation only
 };
 
 template <int BN>
@@ -64,10 +84,20 @@ struct __align__(8) GemmBarriers {
   uint32_t tmem_base;
   int abort_flag;
   int is_last;
+  uint32_t epoch;
   float sb[2][BN];
 };
 
-template <int BN, bool kScaled>
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <int BN, bool kScaled, bool kComm>
 __global__ void __launch_bounds__(kGemmThreads, (BN <= 64 ? 2 : 1))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const GemmParams p) {
@@ -264,6 +294,74 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
     }
 
+    if (kComm && writer) {
+      // ---- fused all-reduce of this tile across ranks (all 128 epilogue threads take part)
+      const CommParams& cm = p.comm;
+      const int tile_id = a_tile * gridDim.y + b_tile;
+      if (et == 0) {
+        const uint32_t e = cm.epoch[tile_id] + 1;
+        cm.epoch[tile_id] = e;
+        bars->epoch = e;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const uint32_t e = bars->epoch;
+      const long long region = static_cast<long long>(e & 1) * cm.world;
+      const long long tile_off = static_cast<long long>(tile_id) * (kTileA * BN) + row * BN;
+      // Every rank (this one included) receives the bf16-rounded partial, so all ranks sum the
+      // same values in the same order.
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) {
+        uint4 v;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[8 * c + 2 * j], acc[8 * c + 2 * j + 1]);
+        for (int peer = 0; peer < cm.world; ++peer) {
+          uint4* dst = reinterpret_cast<uint4*>(cm.recv[peer] + (region + cm.rank) * cm.cap_elems + tile_off);
+          dst[c] = v;
+        }
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et < cm.world && et != cm.rank) {
+        st_release_sys(cm.flags[et] + static_cast<size_t>(tile_id) * cm.world + cm.rank, e);
+        const uint32_t* f = cm.flags[cm.rank] + static_cast<size_t>(tile_id) * cm.world + et;
+        uint32_t spins = 0;
+        long long t0 = 0;
+        while (static_cast<int32_t>(ld_acquire_sys(f) - e) < 0) {
+          ++spins;
+          if (spins == 1024) t0 = clock64();
+          if (spins > 1024 && (spins & 63) == 0) {
+            if (*abort_flag) break;
+            if (clock64() - t0 > kWaitLimitCycles) {
+              *abort_flag = 1;
+              if (p.status) atomicCAS(p.status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
+              break;
+            }
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abort_flag) ok = false;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+      if (ok) {
+        for (int src = 0; src < cm.world; ++src) {
+          const uint4* srcp =
+              reinterpret_cast<const uint4*>(cm.recv[cm.rank] + (region + src) * cm.cap_elems + tile_off);
+#pragma unroll
+          for (int c = 0; c < BN / 8; ++c) {
+            const uint4 v = __ldcg(srcp + c);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              acc[8 * c + 2 * j] += __bfloat162float(h[j].x);
+              acc[8 * c + 2 * j + 1] += __bfloat162float(h[j].y);
+            }
+          }
+        }
+      }
+    }
+
     if (writer && ok && a_row < p.a_rows) {
       if (p.transpose_out) {
         // Y[b, a]: for a fixed column the 32 lanes of a warp write 32 consecutive bf16.
@@ -383,18 +481,18 @@ int cached_kmajor_tmap(CUtensorMap* out, const void* ptr, int elem_bytes, long l
   return rc;
 }
 
-template <int BN, bool kScaled>
+template <int BN, bool kScaled, bool kComm>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, dim3 grid,
                        cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(p.stages) * (kTileA + BN) * kBoxBytes + sizeof(GemmBarriers<BN>) + 1024;
   static size_t configured = 0;
   if (smem > configured) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, kScaled>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, kScaled, kComm>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return SLLM_ERR_CUDA;
     configured = smem;
   }
-  gemm_tcgen05_kernel<BN, kScaled><<<grid, kGemmThreads, smem, stream>>>(ta, tb, p);
+  gemm_tcgen05_kernel<BN, kScaled, kComm><<<grid, kGemmThreads, smem, stream>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 
@@ -408,10 +506,20 @@ SLLM_EXPORT long long sllm_gemm_workspace_floats(int a_rows, int b_rows, int bn,
   return tiles * splits * bn * kTileA;
 }
 
-SLLM_EXPORT int sllm_gemm(const void* a, const void* b, void* y, const float* scale_a, const float* scale_b,
-                          const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out,
-                          int ldy, int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws,
-                          long long ws_floats, int* counters, int n_counters, int* status, void* stream) {
+struct SllmCommDesc {   // host-side mirror passed by the Python layer (ctypes.Structure)
+  int world, rank;
+  long long cap_elems;
+  int max_tiles;
+  int reserved;
+  void* recv[kMaxWorld];
+  void* flags[kMaxWorld];
+  void* epoch;
+};
+
+static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a, const float* scale_b,
+                     const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out, int ldy,
+                     int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws, long long ws_floats,
+                     int* counters, int n_counters, int* status, void* stream, const SllmCommDesc* comm) {
   if (!a || !b || !y || a_rows <= 0 || b_rows <= 0 || k <= 0 || splits < 1) return SLLM_ERR_INVALID_ARGUMENT;
   if (bn != 16 && bn != 32 && bn != 64 && bn != 128) return SLLM_ERR_UNSUPPORTED_SHAPE;
   const int elem = scaled ? 1 : 2;
@@ -435,13 +543,28 @@ SLLM_EXPORT int sllm_gemm(const void* a, const void* b, void* y, const float* sc
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages > max_stages_smem) stages = max_stages_smem;
 
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  if (comm) {
+    if (comm->world < 2 || comm->world > kMaxWorld || comm->rank < 0 || comm->rank >= comm->world || !comm->epoch)
+      return SLLM_ERR_INVALID_ARGUMENT;
+    const long long tiles = static_cast<long long>(a_tiles) * b_tiles;
+    if (tiles > comm->max_tiles || tiles * kTileA * bn > comm->cap_elems) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+    p.comm.world = comm->world; p.comm.rank = comm->rank; p.comm.cap_elems = comm->cap_elems;
+    for (int i = 0; i < comm->world; ++i) {
+      if (!comm->recv[i] || !comm->flags[i]) return SLLM_ERR_INVALID_ARGUMENT;
+      p.comm.recv[i] = static_cast<__nv_bfloat16*>(comm->recv[i]);
+      p.comm.flags[i] = static_cast<uint32_t*>(comm->flags[i]);
+    }
+    p.comm.epoch = static_cast<uint32_t*>(comm->epoch);
+  }
+
   CUtensorMap ta, tb;
   int rc = cached_kmajor_tmap(&ta, a, elem, a_rows, k, static_cast<long long>(k) * elem, kTileA);
   if (rc != SLLM_OK) return rc;
   rc = cached_kmajor_tmap(&tb, b, elem, b_rows, k, static_cast<long long>(k) * elem, bn);
   if (rc != SLLM_OK) return rc;
 
-  GemmParams p;
   p.a_rows = a_rows; p.b_rows = b_rows; p.num_kb = num_kb; p.kb_per_split = kb_per_split; p.stages = stages;
   p.transpose_out = transpose_out; p.ldy = ldy; p.ld_sa = ld_sa; p.ld_sb = ld_sb;
   p.epilogue = residual ? 1 : 0;
@@ -451,9 +574,13 @@ SLLM_EXPORT int sllm_gemm(const void* a, const void* b, void* y, const float* sc
   p.ws = ws; p.counters = counters; p.status = status;
   dim3 grid(a_tiles, b_tiles, splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define SLLM_GEMM_CASE(BN_)                                                            \
-  case BN_:                                                                            \
-    return scaled ? launch_gemm<BN_, true>(ta, tb, p, grid, st) : launch_gemm<BN_, false>(ta, tb, p, grid, st);
+#define SLLM_GEMM_CASE(BN_)                                                                                 \
+  case BN_:                                                                                                 \
+    if (comm)                                                                                               \
+      return scaled ? launch_gemm<BN_, true, true>(ta, tb, p, grid, st)                                     \
+                    : launch_gemm<BN_, false, true>(ta, tb, p, grid, st);                                   \
+    return scaled ? launch_gemm<BN_, true, false>(ta, tb, p, grid, st)                                      \
+                  : launch_gemm<BN_, false, false>(ta, tb, p, grid, st);
   switch (bn) {
     SLLM_GEMM_CASE(16)
     SLLM_GEMM_CASE(32)
@@ -462,4 +589,25 @@ SLLM_EXPORT int sllm_gemm(const void* a, const void* b, void* y, const float* sc
   }
 #undef SLLM_GEMM_CASE
   return SLLM_ERR_UNSUPPORTED_SHAPE;
+}
+
+SLLM_EXPORT int sllm_gemm(const void* a, const void* b, void* y, const float* scale_a, const float* scale_b,
+                          const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out,
+                          int ldy, int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws,
+                          long long ws_floats, int* counters, int n_counters, int* status, void* stream) {
+  return gemm_impl(a, b, y, scale_a, scale_b, residual, a_rows, b_rows, k, scaled, transpose_out, ldy, ld_sa, ld_sb,
+                   bn, splits, stages, ws, ws_floats, counters, n_counters, status, stream, nullptr);
+}
+
+// Same GEMM with the cross-rank sum of the partial products fused into the epilogue (see the file
+// comment).  `comm` points to a host SllmCommDesc whose device pointers come from sllm_symm_open.
+SLLM_EXPORT int sllm_gemm_allreduce(const void* a, const void* b, void* y, const float* scale_a,
+                                    const float* scale_b, const void* residual, int a_rows, int b_rows, int k,
+                                    int scaled, int transpose_out, int ldy, int ld_sa, int ld_sb, int bn, int splits,
+                                    int stages, float* ws, long long ws_floats, int* counters, int n_counters,
+                                    int* status, void* stream, const void* comm) {
+  if (!comm) return SLLM_ERR_INVALID_ARGUMENT;
+  return gemm_impl(a, b, y, scale_a, scale_b, residual, a_rows, b_rows, k, scaled, transpose_out, ldy, ld_sa, ld_sb,
+                   bn, splits, stages, ws, ws_floats, counters, n_counters, status, stream,
+                   static_cast<const SllmCommDesc*>(comm));
 }
