@@ -264,9 +264,14 @@ def main():
                              "tok_s_e2e": round(ks / (extra["e2e_ms"] / 1e3), 2),
                              "ttft_ms": round(extra["prefill_ms"], 2)}
         print(json.dumps(out))
+    sys.stdout.flush()
     if world > 1:
+        torch.cuda.synchronize()
+        if tp is not None:
+            tp.close()
         dist.barrier()
         dist.destroy_process_group()
+        os._exit(0)
     return 0
 
 

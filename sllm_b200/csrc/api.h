@@ -4,8 +4,9 @@
  *   - returns 0 when the kernel was launched, a small positive SllmStatus code otherwise; nothing is
  *     launched when arguments are rejected;
  *   - pointers are device pointers unless the name says otherwise; `stream` is a cudaStream_t;
- *   - no entry point allocates device memory: workspaces and counters are supplied by the caller
- *     (counters must be zero before the first launch; kernels leave them zero);
+ *   - no compute entry point allocates device memory: workspaces and counters are supplied by the
+ *     caller (counters must be zero before the first launch; kernels leave them zero); only
+ *     sllm_symm_alloc / sllm_symm_open create or map device memory;
  *   - kernels that wait on barriers write a non-zero code to `status` (device int) instead of hanging.
  *
  * The role of this header mirrors the reference's include/sllm/hip.h (status codes :27-85, one
@@ -23,6 +24,12 @@ int sllm_gemm(const void* a, const void* b, void* y, const float* scale_a, const
               int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws, long long ws_floats, int* counters,
               int n_counters, int* status, void* stream);
 
+void sllm_gemm_set_cluster_split(int enabled);
+int sllm_gemm_allreduce(const void* a, const void* b, void* y, const float* scale_a, const float* scale_b,
+                        const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out, int ldy,
+                        int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws, long long ws_floats,
+                        int* counters, int n_counters, int* status, void* stream, const void* comm);
+
 /* elementwise.cu */
 int sllm_embedding(const void* table, const int* ids, void* out, int tokens, int d, int vocab, float scale,
                    void* stream);
@@ -37,7 +44,7 @@ int sllm_rope_kv_append(void* qkv, const int* positions, const int* seq_index, c
                         float k_static_scale, float v_static_scale, const float* inv_freq, void* stream);
 int sllm_elementwise(const void* a, const void* b, void* y, long long n, int d, int op, float s, void* stream);
 int sllm_argmax(const void* logits, int* out_idx, float* out_val, int rows, int n, int ld, int index_offset,
-                void* stream);
+                void* ws, long long ws_bytes, int* counters, int n_counters, void* stream);
 
 /* attention.cu */
 long long sllm_paged_attention_workspace_floats(int rows, int hq, int hd, int hkv, int splits);
@@ -47,6 +54,20 @@ int sllm_paged_attention(const void* q, int q_ld, const void* k_pages, const voi
                          int page_size, int window, float sm_scale, int kv_fp8, void* out_bf16, void* out_fp8,
                          float* out_scale, int ld_scale, const float* sinks, int splits, float* ws,
                          long long ws_floats, int* counters, int n_counters, void* stream);
+
+/* prefill_attention.cu */
+int sllm_prefill_attention(const void* qkv, int total_tokens, int qkv_ld, const int* tiles, int num_tiles, int hq,
+                           int hkv, int hd, float sm_scale, void* out_bf16, void* out_fp8, float* out_scale,
+                           int ld_scale, int* status, void* stream);
+
+/* comm.cu */
+int sllm_symm_alloc(long long bytes, void** dev_ptr, unsigned char* handle64);
+int sllm_symm_open(const unsigned char* handle64, void** dev_ptr);
+int sllm_symm_close(void* peer_ptr);
+int sllm_symm_free(void* dev_ptr);
+int sllm_allgather_small(const void* const* bases, int world, int rank, long long offset, long long flag_offset,
+                         int slot_bytes, const void* src, void* dst, void* epoch, int* status, void* stream);
+int sllm_argmax_merge(const float* vals, const int* idx, int* out, int rows, int world, void* stream);
 
 #ifdef __cplusplus
 }

@@ -191,8 +191,8 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, f
 }
 
 // ---------------------------------------------------------------- RoPE + KV page append
-// qkv: [T, (hq + 2*hkv) * hd] bf16.  One CTA per (token, head): q heads are rotated in place, k heads
-// are rotated and written to the K pages, v heads are copied to the V pages; pages are bf16 or E4M3
+// qkv: [T, (hq + 2*hkv) * hd] bf16.  One CTA per (token, head): q and k heads are rotated in place, k heads
+// are also written to the K pages, v heads are copied to the V pages; pages are bf16 or E4M3
 // with one fp32 scale per (token, head) = amax / 448.
 // Split-half ("NeoX") rotation over the first rotary_dim channels:
 //   out[i] = x[i] cos - x[i + r/2] sin,  out[i + r/2] = x[i + r/2] cos + x[i] sin,  angle = pos * theta^(-2i/r)
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
     rot[i] = o;
     const float ao = fabsf(o);
     if (ao == ao && ao <= 3.0e38f) amax = fmaxf(amax, ao);
-    if (is_q) src[i] = __float2bfloat16_rn(o);
+    if (!is_v) src[i] = __float2bfloat16_rn(o);  // q and k are rotated in place as well
   }
   if (is_q) return;  // uniform per CTA
   const int kvh = is_v ? h - p.hq - p.hkv : h - p.hq;
@@ -291,27 +291,67 @@ __global__ void elementwise_kernel(const __nv_bfloat16* __restrict__ a, const __
 }
 
 // ---------------------------------------------------------------- row argmax
-// NaN anywhere in the row -> -1; ties -> lowest index.  Optional (offset, stride) let vocabulary
-// shards report global ids.  out_val (optional) receives the winning value for cross-rank merges.
-__global__ void __launch_bounds__(1024)
+// NaN anywhere in the row -> -1; ties -> lowest index.  index_offset lets vocabulary shards report
+// global ids; out_val (optional) receives the winning value for cross-rank merges.
+// grid = (rows, chunks): every CTA scans one slice with 16-byte loads and publishes a partial
+// (value, index, nan) record; the CTA that arrives last for a row (counter) merges the records.
+struct ArgmaxPartial {
+  float val;
+  int idx;
+  int nan;
+  int pad;
+};
+
+__device__ __forceinline__ void argmax_take(float& best, int& bi, float v, int i) {
+  if (v > best || (v == best && i < bi)) {
+    best = v;
+    bi = i;
+  }
+}
+
+__global__ void __launch_bounds__(256)
 argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out_idx, float* __restrict__ out_val,
-              int n, int ld, int index_offset) {
+              int n, int ld, int index_offset, int chunk, ArgmaxPartial* partials, int* counters) {
   const int r = blockIdx.x;
+  const int c0 = blockIdx.y * chunk;
+  int c1 = c0 + chunk;
+  if (c1 > n) c1 = n;
   const __nv_bfloat16* row = logits + static_cast<size_t>(r) * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  bool nan = false;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = __bfloat162float(row[i]);
-    if (v != v) nan = true;
-    if (v > best || (v == best && i < bi)) {
-      best = v;
-      bi = i;
+  int nan = 0;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15) == 0) && ((c0 & 7) == 0);
+  int i = c0 + threadIdx.x * 8;
+  if (vec_ok) {
+    for (; i + 8 <= c1; i += blockDim.x * 8) {
+      float v[8];
+      load8_bf16(row + i, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (v[j] != v[j]) nan = 1;
+        argmax_take(best, bi, v[j], i + j);
+      }
+    }
+    // ragged tail of the slice (fewer than 8 elements), handled by one thread
+    const int tail0 = c0 + ((c1 - c0) & ~7);
+    if (threadIdx.x == 0) {
+      for (int t = tail0; t < c1; ++t) {
+        const float v = __bfloat162float(row[t]);
+        if (v != v) nan = 1;
+        argmax_take(best, bi, v, t);
+      }
+    }
+  } else {
+    for (int t = c0 + threadIdx.x; t < c1; t += blockDim.x) {
+      const float v = __bfloat162float(row[t]);
+      if (v != v) nan = 1;
+      argmax_take(best, bi, v, t);
     }
   }
-  __shared__ float sv[32];
-  __shared__ int si[32];
+  __shared__ float sv[8];
+  __shared__ int si[8];
   __shared__ int snan;
+  __shared__ int s_last;
   if (threadIdx.x == 0) snan = 0;
   __syncthreads();
   if (nan) snan = 1;
@@ -319,30 +359,38 @@ argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out_id
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) {
-      best = ov;
-      bi = oi;
-    }
+    argmax_take(best, bi, ov, oi);
   }
   if ((threadIdx.x & 31) == 0) {
     sv[threadIdx.x >> 5] = best;
     si[threadIdx.x >> 5] = bi;
   }
   __syncthreads();
-  if (threadIdx.x < 32) {
-    const int nw = blockDim.x >> 5;
-    best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
-    bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) {
-        best = ov;
-        bi = oi;
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (blockDim.x >> 5); ++w) argmax_take(best, bi, sv[w], si[w]);
+    const int chunks = gridDim.y;
+    ArgmaxPartial rec;
+    rec.val = best; rec.idx = bi; rec.nan = snan; rec.pad = 0;
+    int last = 1;
+    if (chunks > 1) {
+      partials[static_cast<size_t>(r) * chunks + blockIdx.y] = rec;
+      __threadfence();
+      const int old = atomicAdd(&counters[r], 1);
+      last = old == chunks - 1;
+      if (last) {
+        counters[r] = 0;
+        __threadfence();
+        best = -INFINITY; bi = 0x7fffffff; snan = 0;
+        for (int c = 0; c < chunks; ++c) {
+          const ArgmaxPartial* pr = partials + static_cast<size_t>(r) * chunks + c;
+          const float v = __ldcg(&pr->val);
+          const int ix = __ldcg(&pr->idx);
+          if (__ldcg(&pr->nan)) snan = 1;
+          argmax_take(best, bi, v, ix);
+        }
       }
     }
-    if (threadIdx.x == 0) {
+    if (last) {
       if (snan) {
         out_idx[r] = -1;
         if (out_val) out_val[r] = NAN;
@@ -457,9 +505,22 @@ SLLM_EXPORT int sllm_elementwise(const void* a, const void* b, void* y, long lon
 }
 
 SLLM_EXPORT int sllm_argmax(const void* logits, int* out_idx, float* out_val, int rows, int n, int ld,
-                            int index_offset, void* stream) {
+                            int index_offset, void* ws, long long ws_bytes, int* counters, int n_counters,
+                            void* stream) {
   if (!logits || !out_idx || rows <= 0 || n <= 0) return SLLM_ERR_INVALID_ARGUMENT;
-  argmax_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(logits),
-                                                                      out_idx, out_val, n, ld, index_offset);
+  // Enough CTAs to cover the machine, slices a multiple of 8 elements and at least 2048 long.
+  int chunks = (2 * 148 + rows - 1) / rows;
+  const int max_chunks = (n + 2047) / 2048;
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks < 1) chunks = 1;
+  if (chunks > 1 && (!ws || !counters || ws_bytes < static_cast<long long>(rows) * chunks * 16 || n_counters < rows))
+    chunks = 1;
+  int chunk = (n + chunks - 1) / chunks;
+  chunk = (chunk + 7) & ~7;
+  chunks = (n + chunk - 1) / chunk;
+  dim3 grid(rows, chunks);
+  argmax_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), out_idx, out_val, n, ld, index_offset, chunk,
+      static_cast<ArgmaxPartial*>(ws), counters);
   return check_launch();
 }

@@ -65,6 +65,7 @@ struct GemmParams {
   int ldy;
   int ld_sa, ld_sb;    // leading dimensions of the kb-major scale arrays
   int epilogue;        // 0 = store, 1 = add residual
+  int cluster_split;   // 1: gridDim.z CTAs form one cluster and reduce split-K partials over DSMEM
   const float* scale_a;  // [num_kb, ld_sa]
   const float* scale_b;  // [num_kb, ld_sb]
   __nv_bfloat16* y;
@@ -75,8 +76,25 @@ struct GemmParams {
   CommParams comm;     // used by the kComm instantiation only
 };
 
+#ifdef SLLM_TRACE
+// Development-only phase timestamps of CTA (0,0,0) (globaltimer ns); never compiled into the product.
+__device__ unsigned long long g_trace[32];
+__device__ __forceinline__ void trace_mark(int slot) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_trace[slot] = t;
+  }
+}
+#define TRACE(slot) trace_mark(slot)
+#else
+#define TRACE(slot)
+#endif
+
+constexpr int kScaleChunk = 16;  // K blocks of scales staged in shared memory at a time
+
 template <int BN>
-struct __align__(8) GemmBarriers {
+struct __align__(16) GemmBarriers {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
@@ -85,7 +103,12 @@ struct __align__(8) GemmBarriers {
   int abort_flag;
   int is_last;
   uint32_t epoch;
-  float sb[2][BN];
+};
+
+template <int BN>
+struct __align__(16) GemmScales {
+  float sa[2][kScaleChunk][kTileA];
+  float sb[2][kScaleChunk][BN];
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -94,6 +117,22 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// 4-byte async copy global -> shared; src_bytes == 0 writes zero instead of reading.
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(const float* local_ptr, uint32_t cta_rank) {
+  uint32_t ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local_ptr)), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
   return v;
 }
 
@@ -110,6 +149,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
   constexpr int kElemsPerBox = kScaled ? 128 : 64;
   GemmBarriers<BN>* bars = reinterpret_cast<GemmBarriers<BN>*>(smem + p.stages * kStageBytes);
+  GemmScales<BN>* sc = reinterpret_cast<GemmScales<BN>*>(bars + 1);
+  float* red = reinterpret_cast<float*>(smem);  // [BN][128] cluster split-K partial (pipeline memory, reused)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -119,6 +160,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (nkb > p.kb_per_split) nkb = p.kb_per_split;
   if (nkb < 0) nkb = 0;
   volatile int* abort_flag = &bars->abort_flag;
+  const bool cluster_split = p.cluster_split != 0;
+  if (threadIdx.x == 0) TRACE(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -143,6 +186,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  if (threadIdx.x == 0) TRACE(1);
+
+  // Epilogue-thread coordinates (meaningful for warps 2..5 only).
+  const int q = warp & 3;              // TMEM lane quarter this warp may read
+  const int row = q * 32 + lane;       // row of the A tile
+  const int et = threadIdx.x - 64;     // 0..127
+  const int a_row = a_tile * kTileA + row;
+  float acc[BN];
+  bool ok = true;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -177,6 +229,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int s = i % p.stages;
         const uint32_t ph = (i / p.stages) & 1;
         if (!mbar_wait(&bars->full[s], ph, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL)) break;
+        if (i == 0) TRACE(2);
+        if (i == nkb - 1) TRACE(3);
         const int buf = kScaled ? (i & 1) : 0;
         if (kScaled) {
           if (!mbar_wait(&bars->tmem_empty[buf], ((i >> 1) & 1) ^ 1, abort_flag, p.status,
@@ -190,11 +244,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const uint32_t d = tmem_base + buf * BN;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per stage row
-          const uint32_t acc = kScaled ? (k > 0) : ((i > 0) || (k > 0));
+          const uint32_t accum = kScaled ? (k > 0) : ((i > 0) || (k > 0));
           if (kScaled)
-            umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+            umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
           else
-            umma_f16(d, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+            umma_f16(d, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
         }
         tc_commit(&bars->empty[s]);  // stage reusable once these MMAs have read it
         if (kScaled) tc_commit(&bars->tmem_full[buf]);
@@ -202,48 +256,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (!kScaled) tc_commit(&bars->tmem_full[0]);
     }
   } else {
-    // ------------------------------------------------------------ epilogue (128 threads)
-    const int q = warp & 3;              // TMEM lane quarter this warp may read
-    const int row = q * 32 + lane;       // row of the A tile
-    const int et = threadIdx.x - 64;     // 0..127
-    const int a_row = a_tile * kTileA + row;
+    // ------------------------------------------------------------ epilogue main loop (128 threads)
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    float acc[BN];
 #pragma unroll
     for (int c = 0; c < BN; ++c) acc[c] = 0.f;
-    bool ok = true;
 
     if (kScaled) {
+      // Scales of 16 K blocks at a time are staged in shared memory with cp.async (double buffered),
+      // so no global-memory latency sits on the per-block critical path.
       const int b_row0 = b_tile * BN;
-      if (nkb > 0 && et < BN) {
-        const int br = b_row0 + et;
-        bars->sb[0][et] = (br < p.b_rows) ? p.scale_b[static_cast<size_t>(kb0) * p.ld_sb + br] : 0.f;
-      }
+      auto stage_scales = [&](int chunk, int buf) {
+        const int base_kb = kb0 + chunk * kScaleChunk;
+        int cnt = kb0 + nkb - base_kb;
+        if (cnt > kScaleChunk) cnt = kScaleChunk;
+        for (int j = 0; j < cnt; ++j) {
+          const bool in = a_row < p.a_rows;
+          cp_async4(&sc->sa[buf][j][row], p.scale_a + static_cast<size_t>(base_kb + j) * p.ld_sa + (in ? a_row : 0),
+                    in ? 4 : 0);
+        }
+        for (int idx = et; idx < cnt * BN; idx += 128) {
+          const int j = idx / BN, c = idx % BN;
+          const bool in = b_row0 + c < p.b_rows;
+          cp_async4(&sc->sb[buf][j][c], p.scale_b + static_cast<size_t>(base_kb + j) * p.ld_sb + (in ? b_row0 + c : 0),
+                    in ? 4 : 0);
+        }
+      };
+      const int nchunks = (nkb + kScaleChunk - 1) / kScaleChunk;
+      if (nchunks > 0) stage_scales(0, 0);
+      cp_async_wait_all();
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      for (int i = 0; i < nkb; ++i) {
-        const int buf = i & 1;
-        float next_sb = 0.f;
-        if (i + 1 < nkb && et < BN) {
-          const int br = b_row0 + et;
-          if (br < p.b_rows) next_sb = p.scale_b[static_cast<size_t>(kb0 + i + 1) * p.ld_sb + br];
-        }
-        const float sa = (a_row < p.a_rows) ? p.scale_a[static_cast<size_t>(kb0 + i) * p.ld_sa + a_row] : 0.f;
-        if (ok) ok = mbar_wait(&bars->tmem_full[buf], (i >> 1) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
-        if (ok) {
-          tc_fence_after();
+      for (int ci = 0; ci < nchunks; ++ci) {
+        const int sbuf = ci & 1;
+        if (ci + 1 < nchunks) stage_scales(ci + 1, sbuf ^ 1);
+        int cnt = nkb - ci * kScaleChunk;
+        if (cnt > kScaleChunk) cnt = kScaleChunk;
+        for (int j = 0; j < cnt; ++j) {
+          const int i = ci * kScaleChunk + j;
+          const int buf = i & 1;
+          const float sa = sc->sa[sbuf][j][row];
+          if (ok) ok = mbar_wait(&bars->tmem_full[buf], (i >> 1) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
+          if (et == 0 && i == 0) TRACE(4);
+          if (et == 0 && i == 1) TRACE(5);
+          if (et == 0 && i == nkb - 1) TRACE(6);
+          if (ok) {
+            tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < BN / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld16(lane_addr + buf * BN + c * 16, r);
-            tmem_wait_ld();
+            for (int c = 0; c < BN / 16; ++c) {
+              uint32_t r[16];
+              tmem_ld16(lane_addr + buf * BN + c * 16, r);
+              tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              acc[c * 16 + j] = fmaf(__uint_as_float(r[j]), sa * bars->sb[buf][c * 16 + j], acc[c * 16 + j]);
+              for (int jj = 0; jj < 16; ++jj)
+                acc[c * 16 + jj] = fmaf(__uint_as_float(r[jj]), sa * sc->sb[sbuf][j][c * 16 + jj], acc[c * 16 + jj]);
+            }
+            tc_fence_before();
+            mbar_arrive(&bars->tmem_empty[buf]);
           }
-          tc_fence_before();
-          mbar_arrive(&bars->tmem_empty[buf]);
         }
-        if (et < BN) bars->sb[buf ^ 1][et] = next_sb;
+        cp_async_wait_all();
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     } else {
@@ -263,10 +333,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       }
     }
+    // Cluster split-K: CTAs other than the cluster leader park their partial in their own shared
+    // memory (the pipeline stages are drained by now) for the leader to read over DSMEM.
+    if (cluster_split && split != 0) {
+#pragma unroll
+      for (int c = 0; c < BN; ++c) red[c * kTileA + row] = acc[c];
+    }
+  }
 
-    // ---- split-K fix-up: last CTA to arrive for this tile reduces all partials in split order
+  if (threadIdx.x == 64) TRACE(7);
+  if (cluster_split) cluster_sync_all();  // partials visible cluster-wide
+  if (threadIdx.x == 64) TRACE(8);
+
+  if (warp >= 2) {
     bool writer = true;
-    if (gridDim.z > 1) {
+    if (cluster_split) {
+      writer = split == 0;
+      if (writer) {
+        for (uint32_t s = 1; s < gridDim.z; ++s) {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) acc[c] += ld_dsmem_f32(red + c * kTileA + row, s);
+        }
+      }
+    } else if (gridDim.z > 1) {
+      // ---- global split-K fix-up: last CTA to arrive for this tile reduces all partials in order
       const int tile_id = a_tile * gridDim.y + b_tile;
       float* my = p.ws + (static_cast<size_t>(tile_id) * gridDim.z + split) * (BN * kTileA);
 #pragma unroll
@@ -294,6 +384,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
     }
 
+    if (et == 0) TRACE(9);
     if (kComm && writer) {
       // ---- fused all-reduce of this tile across ranks (all 128 epilogue threads take part)
       const CommParams& cm = p.comm;
@@ -414,6 +505,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
   }
 
+  if (threadIdx.x == 64) TRACE(10);
+  // Non-leader CTAs must stay resident until the leader has read their shared memory.
+  if (cluster_split) cluster_sync_all();
+  if (threadIdx.x == 64) TRACE(11);
+
   // ------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
@@ -481,10 +577,15 @@ int cached_kmajor_tmap(CUtensorMap* out, const void* ptr, int elem_bytes, long l
   return rc;
 }
 
+template <int BN, bool kScaled>
+constexpr size_t gemm_fixed_smem() {
+  return sizeof(GemmBarriers<BN>) + (kScaled ? sizeof(GemmScales<BN>) : 0) + 1024;
+}
+
 template <int BN, bool kScaled, bool kComm>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, dim3 grid,
                        cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(p.stages) * (kTileA + BN) * kBoxBytes + sizeof(GemmBarriers<BN>) + 1024;
+  const size_t smem = static_cast<size_t>(p.stages) * (kTileA + BN) * kBoxBytes + gemm_fixed_smem<BN, kScaled>();
   static size_t configured = 0;
   if (smem > configured) {
     if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, kScaled, kComm>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -492,8 +593,55 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       return SLLM_ERR_CUDA;
     configured = smem;
   }
-  gemm_tcgen05_kernel<BN, kScaled, kComm><<<grid, kGemmThreads, smem, stream>>>(ta, tb, p);
-  return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  GemmParams pp = p;
+  if (pp.cluster_split) {
+    // Validate this cluster shape once per (instantiation, size); fall back to the global fix-up
+    // when the device cannot co-schedule it.
+    static int cluster_ok[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};  // 0 unknown, 1 ok, -1 unusable
+    static size_t cluster_smem[9] = {0};
+    const int z = static_cast<int>(grid.z);
+    if (cluster_ok[z] == 0 || cluster_smem[z] < smem) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = grid;
+      probe.blockDim = dim3(kGemmThreads);
+      probe.dynamicSmemBytes = smem;
+      cudaLaunchAttribute pa[1];
+      pa[0].id = cudaLaunchAttributeClusterDimension;
+      pa[0].val.clusterDim.x = 1;
+      pa[0].val.clusterDim.y = 1;
+      pa[0].val.clusterDim.z = grid.z;
+      probe.attrs = pa;
+      probe.numAttrs = 1;
+      int n_clusters = 0;
+      const cudaError_t e = cudaOccupancyMaxActiveClusters(&n_clusters, gemm_tcgen05_kernel<BN, kScaled, kComm>, &probe);
+      if (e != cudaSuccess) cudaGetLastError();
+      cluster_ok[z] = (e == cudaSuccess && n_clusters > 0) ? 1 : -1;
+      cluster_smem[z] = smem;
+    }
+    if (cluster_ok[z] < 0) {
+      pp.cluster_split = 0;
+      if (!pp.ws || !pp.counters) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+    }
+  }
+  if (pp.cluster_split) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = grid.z;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, kScaled, kComm>, ta, tb, pp) != cudaSuccess) {
+    cudaGetLastError();
+    return SLLM_ERR_CUDA;
+  }
+  return SLLM_OK;
 }
 
 }  // namespace sllm
@@ -505,6 +653,8 @@ SLLM_EXPORT long long sllm_gemm_workspace_floats(int a_rows, int b_rows, int bn,
   const long long tiles = static_cast<long long>((a_rows + kTileA - 1) / kTileA) * ((b_rows + bn - 1) / bn);
   return tiles * splits * bn * kTileA;
 }
+
+static int g_disable_cluster_split = 0;
 
 struct SllmCommDesc {   // host-side mirror passed by the Python layer (ctypes.Structure)
   int world, rank;
@@ -538,7 +688,9 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
     if (ws_floats < static_cast<long long>(a_tiles) * b_tiles * splits * bn * kTileA || n_counters < a_tiles * b_tiles)
       return SLLM_ERR_WORKSPACE_TOO_SMALL;
   }
-  const int max_stages_smem = (227 * 1024 - 2048 - static_cast<int>(sizeof(GemmBarriers<128>))) / ((kTileA + bn) * kBoxBytes);
+  const int fixed_smem = 2048 + static_cast<int>(sizeof(GemmBarriers<128>)) +
+                         (scaled ? static_cast<int>(sizeof(float)) * 2 * kScaleChunk * (kTileA + bn) : 0);
+  const int max_stages_smem = (227 * 1024 - fixed_smem) / ((kTileA + bn) * kBoxBytes);
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages > max_stages_smem) stages = max_stages_smem;
@@ -568,6 +720,8 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
   p.a_rows = a_rows; p.b_rows = b_rows; p.num_kb = num_kb; p.kb_per_split = kb_per_split; p.stages = stages;
   p.transpose_out = transpose_out; p.ldy = ldy; p.ld_sa = ld_sa; p.ld_sb = ld_sb;
   p.epilogue = residual ? 1 : 0;
+  // 2..8 splits reduce inside one thread-block cluster over DSMEM; more use the global fix-up.
+  p.cluster_split = (splits >= 2 && splits <= 8 && !g_disable_cluster_split) ? 1 : 0;
   p.scale_a = scale_a; p.scale_b = scale_b;
   p.y = static_cast<__nv_bfloat16*>(y);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
@@ -590,6 +744,15 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
 #undef SLLM_GEMM_CASE
   return SLLM_ERR_UNSUPPORTED_SHAPE;
 }
+
+#ifdef SLLM_TRACE
+SLLM_EXPORT int sllm_gemm_read_trace(unsigned long long* out32) {
+  return cudaMemcpyFromSymbol(out32, g_trace, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : 5;
+}
+#endif
+
+// Test hook: force the global-memory split-K fix-up even when a cluster reduction is possible.
+SLLM_EXPORT void sllm_gemm_set_cluster_split(int enabled) { g_disable_cluster_split = enabled ? 0 : 1; }
 
 SLLM_EXPORT int sllm_gemm(const void* a, const void* b, void* y, const float* scale_a, const float* scale_b,
                           const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out,

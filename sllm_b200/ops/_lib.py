@@ -55,7 +55,9 @@ _KERNEL_SIGNATURES = {
     "sllm_quant_fp8_1x128": (I, [P, P, P, I, I, I, P]),
     "sllm_rope_kv_append": (I, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, F, F, P, P]),
     "sllm_elementwise": (I, [P, P, P, L, I, I, F, P]),
-    "sllm_argmax": (I, [P, P, P, I, I, I, I, P]),
+    "sllm_argmax": (I, [P, P, P, I, I, I, I, P, L, P, I, P]),
+    "sllm_gemm_set_cluster_split": (None, [I]),
+    "sllm_prefill_attention": (I, [P, I, I, P, I, I, I, I, F, P, P, P, I, P, P]),
     "sllm_paged_attention_workspace_floats": (L, [I, I, I, I, I]),
     "sllm_paged_attention": (I, [P, I, P, P, P, P, F, F, P, I, P, P, I, I, I, I, I, I, F, I, P, P, P, I, P, I, P, L,
                                   P, I, P]),
@@ -80,13 +82,23 @@ def kernels():
                         f"{_KERNEL_PATH.name} is missing: run `python -m sllm_b200.build` (nvcc, sm_100a); "
                         "CUDA tensors are never routed to a PyTorch fallback")
                 lib = C.CDLL(str(_KERNEL_PATH))
-                for name, (res, args) in {**_KERNEL_SIGNATURES, **EXTRA_KERNEL_SIGNATURES}.items():
-                    if hasattr(lib, name):
-                        fn = getattr(lib, name)
-                        fn.restype = res
-                        fn.argtypes = args
+                _apply(lib, _KERNEL_SIGNATURES)
                 _kernels = lib
+    if len(_applied) < len(_KERNEL_SIGNATURES) + len(EXTRA_KERNEL_SIGNATURES):
+        _apply(_kernels, EXTRA_KERNEL_SIGNATURES)
     return _kernels
+
+
+_applied: set = set()
+
+
+def _apply(lib, table: dict) -> None:
+    for name, (res, args) in table.items():
+        if name not in _applied and hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _applied.add(name)
 
 
 def host():

@@ -115,10 +115,10 @@ def _gemm_plan(m: int, n: int, k_blocks: int):
     if m <= 128:
         bn = 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
         tiles = (n + 127) // 128
-        splits = max(1, min((2 * _SM_COUNT) // max(tiles, 1), k_blocks // 4))
-        stages = {16: 6, 32: 5, 64: 4, 128: 6}[bn]
+        splits = max(1, min((2 * _SM_COUNT) // max(tiles, 1), k_blocks // 4, 8))
+        stages = {16: 5, 32: 4, 64: 3, 128: 5}[bn]
         return True, bn, splits, stages
-    return False, 128, 1, 6
+    return False, 128, 1, 5
 
 
 def gemm_raw(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, *, scale_a=None, scale_b=None, residual=None,
@@ -284,7 +284,9 @@ def argmax(logits: torch.Tensor, index_offset: int = 0, with_values: bool = Fals
     rows, n = logits.shape
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     val = torch.empty(rows, dtype=torch.float32, device=logits.device) if with_values else None
-    rc = _lib.kernels().sllm_argmax(_p(logits), _p(out), _p(val), rows, n, logits.stride(0), index_offset, _stream())
+    wsp = workspace(logits.device)
+    rc = _lib.kernels().sllm_argmax(_p(logits), _p(out), _p(val), rows, n, logits.stride(0), index_offset,
+                                    _p(wsp.ws), wsp.ws.numel() * 4, _p(wsp.counters), wsp.counters.numel(), _stream())
     _lib.check(rc, "argmax")
     return (out, val) if with_values else out
 
@@ -344,10 +346,13 @@ def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.
 
 
 def _attn_splits(rows: int, hkv: int, max_kv: int) -> int:
+    """KV splits so that about 8 CTAs (32 warps) per SM are in flight: the kernel hides its
+    load -> compute -> load chains with occupancy, and each split keeps >= 128 keys."""
     ctas = rows * hkv
-    if ctas >= 2 * _SM_COUNT or max_kv <= 256:
+    target = 8 * _SM_COUNT
+    if ctas >= target or max_kv <= 128:
         return 1
-    return max(1, min((2 * _SM_COUNT + ctas - 1) // ctas, (max_kv + 255) // 256, 32))
+    return max(1, min((target + ctas - 1) // ctas, (max_kv + 127) // 128, 64))
 
 
 def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq_index: torch.Tensor,

@@ -57,8 +57,19 @@ def test_gemm_fp8_blockscaled(m, n, k):
     _status_ok()
 
 
-@pytest.mark.parametrize("splits", [1, 2, 4, 7])
-def test_gemm_split_k_deterministic(splits):
+@pytest.mark.parametrize("cluster", [True, False])
+@pytest.mark.parametrize("splits", [1, 2, 4, 7, 8, 12])
+def test_gemm_split_k_deterministic(splits, cluster):
+    """Split-K through the cluster/DSMEM reduction (2..8 splits) and through the global fix-up."""
+    from sllm_b200.ops import _lib
+    _lib.kernels().sllm_gemm_set_cluster_split(int(cluster))
+    try:
+        _split_k_case(splits)
+    finally:
+        _lib.kernels().sllm_gemm_set_cluster_split(1)
+
+
+def _split_k_case(splits):
     torch.manual_seed(0)
     m, n, k = 8, 512, 4096
     x = torch.randn(m, k, device=DEV).bfloat16()
