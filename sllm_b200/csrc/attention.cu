@@ -125,17 +125,45 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
     if (valid) {
       const int blk = bt[tok / p.page_size];
       slot = (static_cast<size_t>(blk) * p.page_size + tok % p.page_size) * p.hkv + kvh;
-      const size_t off = slot * HD;
-#pragma unroll 2
-      for (int d = 0; d < HD; d += 16) {
-        float kf[16];
-        load_row16<HD, kFp8>(p.k_pages, off + d, kf);
+      // All 16-byte pieces of (up to) 128 bytes of the key row are requested before any is used, so one
+      // memory round trip covers the whole row.
+      constexpr int kVecs = HD * (kFp8 ? 1 : 2) / 16;
+      constexpr int kBatch = kVecs < 8 ? kVecs : 8;
+      constexpr int kElemsPerVec = kFp8 ? 16 : 8;
+      const uint4* krow = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.k_pages) +
+                                                         slot * HD * (kFp8 ? 1 : 2));
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          float a = 0.f;
+      for (int b0 = 0; b0 < kVecs; b0 += kBatch) {
+        uint4 raw[kBatch];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) a = fmaf(q_s[g * HD + d + j], kf[j], a);
-          s[g] += a;
+        for (int u = 0; u < kBatch; ++u) raw[u] = krow[b0 + u];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          float kf[kElemsPerVec];
+          if (kFp8) {
+            const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw[u]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float2 f = e4m3x2_to_f32x2(h[j]);
+              kf[(2 * j) % kElemsPerVec] = f.x;
+              kf[(2 * j + 1) % kElemsPerVec] = f.y;
+            }
+          } else {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              kf[2 * j] = __bfloat162float(h[j].x);
+              kf[2 * j + 1] = __bfloat162float(h[j].y);
+            }
+          }
+          const int d = (b0 + u) * kElemsPerVec;
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            float a = 0.f;
+#pragma unroll
+            for (int j = 0; j < kElemsPerVec; ++j) a = fmaf(q_s[g * HD + d + j], kf[j], a);
+            s[g] += a;
+          }
         }
       }
       if (kFp8) {
@@ -163,33 +191,54 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
     }
     __syncwarp();
     const int cnt = min(32, end - base);
-    for (int j = 0; j < cnt; ++j) {
-      const size_t vslot = __shfl_sync(0xffffffffu, slot, j);
-      float vf[EPL];
-      if (kFp8) {
-        const uint8_t* vp = static_cast<const uint8_t*>(p.v_pages) + vslot * HD + lane * EPL;
-        if (EPL == 4) {
-          const uint32_t raw = *reinterpret_cast<const uint32_t*>(vp);
-          const float2 a = e4m3x2_to_f32x2(static_cast<uint16_t>(raw & 0xffff));
-          const float2 b = e4m3x2_to_f32x2(static_cast<uint16_t>(raw >> 16));
-          vf[0] = a.x; vf[1] = a.y; vf[2 % EPL] = b.x; vf[3 % EPL] = b.y;
-        } else if (EPL == 2) {
-          const float2 a = e4m3x2_to_f32x2(*reinterpret_cast<const uint16_t*>(vp));
-          vf[0] = a.x; vf[1 % EPL] = a.y;
+    // Values of 8 keys are requested together (8 independent loads in flight per lane).
+    for (int j0 = 0; j0 < cnt; j0 += 8) {
+      float vf[8][EPL];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const size_t vslot = __shfl_sync(0xffffffffu, slot, (j0 + u) & 31);
+        const bool live = j0 + u < cnt;
+        if (kFp8) {
+          const uint8_t* vp = static_cast<const uint8_t*>(p.v_pages) + vslot * HD + lane * EPL;
+          if (EPL == 4) {
+            const uint32_t raw = live ? *reinterpret_cast<const uint32_t*>(vp) : 0u;
+            const float2 a = e4m3x2_to_f32x2(static_cast<uint16_t>(raw & 0xffff));
+            const float2 b = e4m3x2_to_f32x2(static_cast<uint16_t>(raw >> 16));
+            vf[u][0] = a.x; vf[u][1 % EPL] = a.y; vf[u][2 % EPL] = b.x; vf[u][3 % EPL] = b.y;
+          } else if (EPL == 2) {
+            const uint16_t raw = live ? *reinterpret_cast<const uint16_t*>(vp) : static_cast<uint16_t>(0);
+            const float2 a = e4m3x2_to_f32x2(raw);
+            vf[u][0] = a.x; vf[u][1 % EPL] = a.y;
+          } else {
+            const uint2 raw = live ? *reinterpret_cast<const uint2*>(vp) : make_uint2(0u, 0u);
+            const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = e4m3x2_to_f32x2(h[e]);
+              vf[u][(2 * e) % EPL] = f.x;
+              vf[u][(2 * e + 1) % EPL] = f.y;
+            }
+          }
         } else {
+          const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(p.v_pages) + vslot * HD + lane * EPL;
 #pragma unroll
-          for (int e = 0; e < EPL; ++e) vf[e] = e4m3_to_f32(vp[e]);
+          for (int e = 0; e < EPL; e += 2) {
+            const __nv_bfloat162 h = live ? *reinterpret_cast<const __nv_bfloat162*>(vp + e) : __nv_bfloat162();
+            vf[u][e] = live ? __bfloat162float(h.x) : 0.f;
+            vf[u][(e + 1) % EPL] = live ? __bfloat162float(h.y) : 0.f;
+          }
         }
-      } else {
-        const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(p.v_pages) + vslot * HD + lane * EPL;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) vf[e] = __bfloat162float(vp[e]);
       }
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pj = my_p[j * G + g];
+      for (int u = 0; u < 8; ++u) {
+        if (j0 + u < cnt) {
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) o[g][e] = fmaf(pj, vf[e], o[g][e]);
+          for (int g = 0; g < G; ++g) {
+            const float pj = my_p[(j0 + u) * G + g];
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) o[g][e] = fmaf(pj, vf[u][e], o[g][e]);
+          }
+        }
       }
     }
     __syncwarp();

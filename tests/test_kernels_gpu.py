@@ -232,3 +232,37 @@ def test_embedding_and_elementwise():
         got = ops.elementwise(op, a, b, s)
         want = ops.elementwise(op, a.cpu(), b.cpu(), s)
         assert rel_err(got.cpu(), want) < 6e-3
+
+
+@pytest.mark.parametrize("lens", [[128], [300, 128, 129], [1000, 257]])
+@pytest.mark.parametrize("hq,hkv", [(4, 2), (8, 8), (4, 1)])
+def test_prefill_attention_tcgen05(lens, hq, hkv):
+    """Tensor-core causal prefill vs an fp32 dense-attention restatement."""
+    from sllm_b200.engine.batch import make_prefill_batch
+    from sllm_b200.ops import prefill
+    torch.manual_seed(sum(lens) + hq)
+    hd = 128
+    t = sum(lens)
+    qkv = torch.randn(t, (hq + 2 * hkv) * hd, device=DEV).bfloat16()
+    table = torch.zeros((len(lens), 1), dtype=torch.int32, device=DEV)
+    b = make_prefill_batch([[0] * n for n in lens], table, DEV)
+    assert prefill.usable(qkv, b, hd, 0, None, qkv)
+    out = prefill.prefill_attention(qkv, b, hq, hkv, hd)
+    outq = prefill.prefill_attention(qkv, b, hq, hkv, hd, quant_out=True)
+    x = qkv.float().cpu().view(t, hq + 2 * hkv, hd)
+    g = hq // hkv
+    want = torch.empty(t, hq, hd)
+    t0 = 0
+    for n in lens:
+        q = x[t0:t0 + n, :hq]
+        k = x[t0:t0 + n, hq:hq + hkv].repeat_interleave(g, dim=1)
+        v = x[t0:t0 + n, hq + hkv:].repeat_interleave(g, dim=1)
+        s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(hd)
+        s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool), 1), float("-inf"))
+        want[t0:t0 + n] = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v)
+        t0 += n
+    want = want.view(t, hq * hd)
+    assert rel_err(out.cpu(), want) < 1e-2, rel_err(out.cpu(), want)
+    deq = ref.dequant_fp8_1x128(outq.data.cpu(), outq.scale.cpu())
+    assert rel_err(deq, want) < 4e-2
+    _status_ok()
