@@ -55,6 +55,15 @@ int sllm_paged_attention(const void* q, int q_ld, const void* k_pages, const voi
                          float* out_scale, int ld_scale, const float* sinks, int splits, float* ws,
                          long long ws_floats, int* counters, int n_counters, void* stream);
 
+/* decode_attention_tc.cu */
+int sllm_decode_attention_tc(const void* q, int q_ld, const void* k_pages, const void* v_pages, const float* k_scale,
+                             const float* v_scale, float k_static_scale, float v_static_scale,
+                             const int* block_table, int max_blocks, const int* seq_index, const int* kv_lens,
+                             int rows, int hq, int hkv, int num_pages, int page_size, int window, float sm_scale,
+                             void* out_bf16, void* out_fp8, float* out_scale, int ld_scale, const float* sinks,
+                             int splits, float* ws, long long ws_floats, int* counters, int n_counters, int* status,
+                             void* stream);
+
 /* prefill_attention.cu */
 int sllm_prefill_attention(const void* qkv, int total_tokens, int qkv_ld, const int* tiles, int num_tiles, int hq,
                            int hkv, int hd, float sm_scale, void* out_bf16, void* out_fp8, float* out_scale,

@@ -18,58 +18,9 @@
 // decode, GQA sharing, direct low-bit KV reads) and gemma_attention_kernel.hip.cpp:40 (sliding window).
 #include "common.cuh"
 #include "api.h"
+#include "attention_common.cuh"
 
 namespace sllm {
-
-struct PagedAttnParams {
-  const __nv_bfloat16* q;  // [rows, hq * hd] (row stride q_ld)
-  int q_ld;
-  const void* k_pages;
-  const void* v_pages;
-  const float* k_scale;
-  const float* v_scale;
-  float k_static_scale, v_static_scale;  // used when the scale planes are null (fp8-static)
-  const int* block_table;  // [num_seqs, max_blocks]
-  int max_blocks;
-  const int* seq_index;    // [rows]
-  const int* kv_lens;      // [rows] keys visible to the row (its own position + 1)
-  int hkv, page_size, window;
-  float sm_scale;
-  __nv_bfloat16* out_bf16;  // [rows, hq * hd] or null
-  uint8_t* out_fp8;         // E4M3 [rows, hq * hd] (hd == 128 only) or null
-  float* out_scale;         // [hq, ld_scale] kb-major scales for out_fp8
-  int ld_scale;
-  float* ws_o;              // [rows * hkv * splits, G, HD]
-  float* ws_ml;             // [rows * hkv * splits, G, 2]
-  int* counters;            // [rows * hkv]
-  const float* sinks;       // optional [hq] attention-sink logits (added to the softmax denominator)
-};
-
-template <int HD, bool kFp8>
-__device__ __forceinline__ void load_row16(const void* base, size_t elem_off, float (&out)[16]) {
-  if (kFp8) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(base) + elem_off);
-    const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float2 f = e4m3x2_to_f32x2(h[j]);
-      out[2 * j] = f.x;
-      out[2 * j + 1] = f.y;
-    }
-  } else {
-    const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + elem_off);
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const uint4 raw = p[half];
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        out[half * 8 + 2 * j] = __bfloat162float(h[j].x);
-        out[half * 8 + 2 * j + 1] = __bfloat162float(h[j].y);
-      }
-    }
-  }
-}
 
 template <int HD, int G, bool kFp8>
 __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnParams p) {
@@ -99,7 +50,9 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
 
   for (int e = threadIdx.x; e < G * HD; e += blockDim.x) {
     const int g = e / HD, d = e % HD;
-    q_s[e] = __bfloat162float(p.q[static_cast<size_t>(r) * p.q_ld + (kvh * G + g) * HD + d]) * p.sm_scale;
+    // FP8 pages decode to value * 2^-120; half of the compensation (2^60) rides on q, half on the scale.
+    q_s[e] = __bfloat162float(p.q[static_cast<size_t>(r) * p.q_ld + (kvh * G + g) * HD + d]) * p.sm_scale *
+             (kFp8 ? kPow60 : 1.f);
   }
   __syncthreads();
 
@@ -141,12 +94,13 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
         for (int u = 0; u < kBatch; ++u) {
           float kf[kElemsPerVec];
           if (kFp8) {
-            const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw[u]);
+            const uint32_t* w32 = reinterpret_cast<const uint32_t*>(&raw[u]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float2 f = e4m3x2_to_f32x2(h[j]);
-              kf[(2 * j) % kElemsPerVec] = f.x;
-              kf[(2 * j + 1) % kElemsPerVec] = f.y;
+            for (int j = 0; j < 4; ++j) {
+              float f4[4];
+              e4m3x4_to_f32x4_exp120(w32[j], f4);
+#pragma unroll
+              for (int b = 0; b < 4; ++b) kf[(4 * j + b) % kElemsPerVec] = f4[b];
             }
           } else {
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
@@ -167,8 +121,8 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
         }
       }
       if (kFp8) {
-        const float ksc = p.k_scale ? p.k_scale[slot] : p.k_static_scale;
-        vsc = p.v_scale ? p.v_scale[slot] : p.v_static_scale;
+        const float ksc = kPow60 * (p.k_scale ? p.k_scale[slot] : p.k_static_scale);
+        vsc = kPow60 * (p.v_scale ? p.v_scale[slot] : p.v_static_scale);  // second 2^60 applied to o at the end
 #pragma unroll
         for (int g = 0; g < G; ++g) s[g] *= ksc;
       } else {
@@ -200,24 +154,24 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
         const bool live = j0 + u < cnt;
         if (kFp8) {
           const uint8_t* vp = static_cast<const uint8_t*>(p.v_pages) + vslot * HD + lane * EPL;
+          float f4[4];
           if (EPL == 4) {
             const uint32_t raw = live ? *reinterpret_cast<const uint32_t*>(vp) : 0u;
-            const float2 a = e4m3x2_to_f32x2(static_cast<uint16_t>(raw & 0xffff));
-            const float2 b = e4m3x2_to_f32x2(static_cast<uint16_t>(raw >> 16));
-            vf[u][0] = a.x; vf[u][1 % EPL] = a.y; vf[u][2 % EPL] = b.x; vf[u][3 % EPL] = b.y;
+            e4m3x4_to_f32x4_exp120(raw, f4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) vf[u][e % EPL] = f4[e];
           } else if (EPL == 2) {
-            const uint16_t raw = live ? *reinterpret_cast<const uint16_t*>(vp) : static_cast<uint16_t>(0);
-            const float2 a = e4m3x2_to_f32x2(raw);
-            vf[u][0] = a.x; vf[u][1 % EPL] = a.y;
+            const uint32_t raw = live ? static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(vp)) : 0u;
+            e4m3x4_to_f32x4_exp120(raw, f4);
+            vf[u][0] = f4[0]; vf[u][1 % EPL] = f4[1];
           } else {
             const uint2 raw = live ? *reinterpret_cast<const uint2*>(vp) : make_uint2(0u, 0u);
-            const uint16_t* h = reinterpret_cast<const uint16_t*>(&raw);
+            e4m3x4_to_f32x4_exp120(raw.x, f4);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = e4m3x2_to_f32x2(h[e]);
-              vf[u][(2 * e) % EPL] = f.x;
-              vf[u][(2 * e + 1) % EPL] = f.y;
-            }
+            for (int e = 0; e < 4; ++e) vf[u][e % EPL] = f4[e];
+            e4m3x4_to_f32x4_exp120(raw.y, f4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) vf[u][(4 + e) % EPL] = f4[e];
           }
         } else {
           const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(p.v_pages) + vslot * HD + lane * EPL;
@@ -245,6 +199,12 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
   }
 
   // ---- merge the 4 warps
+  if (kFp8) {
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) o[g][e] *= kPow60;
+  }
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     if (lane == 0) {
@@ -256,106 +216,7 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
   }
   __syncthreads();
 
-  const size_t unit = static_cast<size_t>(r) * p.hkv + kvh;
-  bool finalize = true;
-  if (splits > 1) {
-    float* wo = p.ws_o + (unit * splits + split) * (G * HD);
-    float* wml = p.ws_ml + (unit * splits + split) * (G * 2);
-    for (int e = threadIdx.x; e < G * HD; e += blockDim.x) {
-      const int g = e / HD, d = e % HD;
-      float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) M = fmaxf(M, m_s[w * G + g]);
-      float L = 0.f, O = 0.f;
-      if (M != -INFINITY) {
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const float f = __expf(m_s[w * G + g] - M);
-          L += l_s[w * G + g] * f;
-          O += o_s[(w * G + g) * HD + d] * f;
-        }
-      }
-      wo[e] = O;
-      if (d == 0) {
-        wml[g * 2] = M;
-        wml[g * 2 + 1] = L;
-      }
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int old = atomicAdd(&p.counters[unit], 1);
-      const int last = old == splits - 1;
-      if (last) p.counters[unit] = 0;
-      s_is_last = last;
-      __threadfence();
-    }
-    __syncthreads();
-    finalize = s_is_last != 0;
-  }
-  if (!finalize) return;
-
-  // ---- final normalisation (+ optional FP8 1x128 quantisation: one block per head when HD == 128)
-  for (int e0 = 0; e0 < G * HD; e0 += blockDim.x) {
-    const int e = e0 + threadIdx.x;
-    const bool in = e < G * HD;
-    const int g = in ? e / HD : 0, d = in ? e % HD : 0;
-    float M = -INFINITY, L = 0.f, O = 0.f;
-    if (in) {
-      if (splits > 1) {
-        const float* wo = p.ws_o + unit * splits * (G * HD);
-        const float* wml = p.ws_ml + unit * splits * (G * 2);
-        for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, __ldcg(wml + (s2 * G + g) * 2));
-        if (M != -INFINITY) {
-          for (int s2 = 0; s2 < splits; ++s2) {
-            const float ms = __ldcg(wml + (s2 * G + g) * 2);
-            const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
-            L += __ldcg(wml + (s2 * G + g) * 2 + 1) * f;
-            O += __ldcg(wo + static_cast<size_t>(s2) * G * HD + e) * f;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, m_s[w * G + g]);
-        if (M != -INFINITY) {
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const float f = __expf(m_s[w * G + g] - M);
-            L += l_s[w * G + g] * f;
-            O += o_s[(w * G + g) * HD + d] * f;
-          }
-        }
-      }
-      if (p.sinks && M != -INFINITY) {
-        // A per-head sink logit joins the denominator only.
-        const float sk = p.sinks[kvh * G + g];
-        const float M2 = fmaxf(M, sk);
-        const float f = __expf(M - M2);
-        L = L * f + __expf(sk - M2);
-        O *= f;
-      }
-    }
-    float val = (L > 0.f) ? O / L : 0.f;
-    val = __bfloat162float(__float2bfloat16_rn(val));
-    const size_t oidx = static_cast<size_t>(r) * hq * HD + (kvh * G + g) * HD + d;
-    if (p.out_fp8) {
-      // HD == 128 == blockDim: this iteration is exactly head g.
-      float a = fabsf(val);
-      if (!(a == a) || a > 3.0e38f) a = 0.f;
-      a = warp_max(a);
-      if (lane == 0) s_red[warp] = a;
-      __syncthreads();
-      const float amax = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-      const float scale = amax > 0.f ? amax / 448.f : 1.f;
-      if (in) {
-        p.out_fp8[oidx] = f32_to_e4m3(__fdiv_rn(val, scale));
-        if (d == 0) p.out_scale[static_cast<size_t>(kvh * G + g) * p.ld_scale + r] = scale;
-      }
-      __syncthreads();
-    } else if (in) {
-      p.out_bf16[oidx] = __float2bfloat16_rn(val);
-    }
-  }
+  attention_tail<HD, G, 4, SyncCta>(p, r, kvh, split, splits, threadIdx.x, m_s, l_s, o_s, &s_is_last, s_red);
 }
 
 template <int HD, int G, bool kFp8>
@@ -416,7 +277,7 @@ SLLM_EXPORT int sllm_paged_attention(const void* q, int q_ld, const void* k_page
   p.hkv = hkv; p.page_size = page_size; p.window = window; p.sm_scale = sm_scale;
   p.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16); p.out_fp8 = static_cast<uint8_t*>(out_fp8);
   p.out_scale = out_scale; p.ld_scale = ld_scale; p.sinks = sinks;
-  p.ws_o = nullptr; p.ws_ml = nullptr; p.counters = counters;
+  p.ws_o = nullptr; p.ws_ml = nullptr; p.counters = counters; p.status_word = nullptr;
   if (splits > 1) {
     const long long units = static_cast<long long>(rows) * hkv;
     const long long need = units * splits * (static_cast<long long>(g) * hd + g * 2);

@@ -209,6 +209,23 @@ __device__ __forceinline__ float2 e4m3x2_to_f32x2(uint16_t b) {
   return __half22float2(*reinterpret_cast<__half2*>(&h));
 }
 
+// Four packed E4M3 bytes -> four floats, each multiplied by 2^-120, with integer instructions only.
+// The 7 exponent/mantissa bits of an E4M3 byte placed at bits [26:20] of an fp32 word (sign at 31) are
+// the fp32 encoding of value * 2^-120 (exponent bias 127 vs 7), subnormals included; no conversion
+// instruction is issued, which keeps the special-function pipe free.  Callers fold 2^120 into their
+// scales in two factors of 2^60 (see kPow60).  0x7f (NaN) decodes as a finite number.
+constexpr float kPow60 = 1152921504606846976.f;  // 2^60
+__device__ __forceinline__ void e4m3x4_to_f32x4_exp120(uint32_t x, float (&o)[4]) {
+  const uint32_t t0 = __byte_perm(x, 0u, 0x1404);  // bytes 0, 1 in the upper byte of each 16-bit lane
+  const uint32_t t1 = __byte_perm(x, 0u, 0x3424);  // bytes 2, 3
+  const uint32_t h0 = ((t0 & 0x7f007f00u) >> 4) | (t0 & 0x80008000u);  // two bf16 words
+  const uint32_t h1 = ((t1 & 0x7f007f00u) >> 4) | (t1 & 0x80008000u);
+  o[0] = __uint_as_float(h0 << 16);
+  o[1] = __uint_as_float(h0 & 0xffff0000u);
+  o[2] = __uint_as_float(h1 << 16);
+  o[3] = __uint_as_float(h1 & 0xffff0000u);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

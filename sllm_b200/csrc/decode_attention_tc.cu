@@ -1,0 +1,440 @@
+// Paged decode / verify attention over FP8 KV pages on the tensor cores (tcgen05 + TMEM + TMA),
+// head_dim 128, GQA group <= 16.
+//
+// A CTA owns (query row, kv head, KV split) and walks its keys 128 at a time:
+//   * the page table is walked by one producer thread which issues one TMA box per 16-token page
+//     ({128 B of channels, 1 head, 16 tokens} out of the [pages*16, kv_heads, 128] E4M3 plane), eight
+//     boxes assembling a 128-key swizzled tile each for K and V; 3-stage ring;
+//   * S^T = K Q^T     : M = 128 keys, N = 16 (the group's heads, zero padded), K = 128 channels, E4M3
+//     inputs (Q is quantised to E4M3 per head once per CTA), result in TMEM [key lane, head column];
+//   * softmax        : thread t owns key t of the tile; per-head maxima cross the 128 threads by
+//     shuffle + shared memory; probabilities are folded with the per-token V scale, scaled into the
+//     E4M3 range and written as the K-major B operand P^T [head, key];
+//   * O^T = V^T P    : M = 128 channels (V consumed MN-major, exactly as stored), N = 16 heads,
+//     K = 128 keys; the running output is 16 fp32 registers per thread (thread = channel).
+// Per-token K scales multiply the scores; KV splits are merged by attention_tail (shared with the
+// CUDA-core kernel), which also applies sinks and the optional FP8 output quantisation.
+//
+// The CUDA-core kernel in attention.cu stays the path for bf16 pages and other head sizes.  Counterpart
+// in the reference: causal_attention_decode_wave_split_kernel (causal_attention_kernel.hip.cpp:264).
+#include "common.cuh"
+#include "api.h"
+#include "attention_common.cuh"
+#include <cudaTypedefs.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace sllm {
+
+constexpr int kDaThreads = 192;
+constexpr int kDaTile = 128;
+constexpr int kDaStages = 3;
+constexpr int kDaTileBytes = kDaTile * 128;  // 16 KB per K or V tile
+constexpr int kDaHeadsPad = 16;
+
+struct __align__(8) DecodeTcBarriers {
+  uint64_t kv_full[kDaStages];
+  uint64_t kv_empty[kDaStages];
+  uint64_t s_full[2];
+  uint64_t p_ready;
+  uint64_t o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+  float red[4][kDaHeadsPad + 1];   // per-warp maxima (heads + V scale)
+  float qscale[kDaHeadsPad];
+  float s_red[4];
+};
+
+// MN-major 8-bit operand: rows = K index (tokens), each row = 128 contiguous bytes of M (channels).
+__device__ __forceinline__ uint64_t make_smem_desc_sw128_mn8(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Decode an E4M3 byte exactly (integer path, see e4m3x4_to_f32x4_exp120).
+__device__ __forceinline__ float e4m3_to_f32_int(uint32_t b) {
+  const uint32_t bits = ((b & 0x80u) << 24) | ((b & 0x7fu) << 20);
+  return __uint_as_float(bits) * kPow60 * kPow60;
+}
+
+template <int G>
+__global__ void __launch_bounds__(kDaThreads, 2)
+decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                           const PagedAttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // layout: stages x {K tile, V tile} | Q (16 x 128 B) | P^T (16 x 128 B) | barriers | tail scratch
+  uint8_t* kv_s = smem;
+  uint8_t* q_s = smem + kDaStages * 2 * kDaTileBytes;
+  uint8_t* p_s = q_s + 2048;
+  DecodeTcBarriers* bars = reinterpret_cast<DecodeTcBarriers*>(p_s + 2048);
+  float* m_s = reinterpret_cast<float*>(bars + 1);  // [G]
+  float* l_s = m_s + kDaHeadsPad;                   // [G]
+  float* o_s = l_s + kDaHeadsPad;                   // [G][128]
+  constexpr uint32_t kTmemCols = 64;  // S buffers at columns 0 and 16, PV at column 32
+
+  const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = p.seq_index[r];
+  const int kv_len = p.kv_lens[r];
+  int first = 0;
+  if (p.window > 0 && kv_len > p.window) first = kv_len - p.window;
+  // Splits cover 128-aligned key ranges starting at the page-aligned beginning of the visible window.
+  const int base0 = first & ~(p.page_size - 1);
+  const int n = kv_len - base0;
+  int chunk = (n + splits - 1) / splits;
+  chunk = (chunk + kDaTile - 1) & ~(kDaTile - 1);
+  const int begin = base0 + split * chunk;
+  int end = begin + chunk;
+  if (end > kv_len) end = kv_len;
+  const int nt = end > begin ? (end - begin + kDaTile - 1) / kDaTile : 0;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDaStages; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    mbar_init(&bars->s_full[0], 1);
+    mbar_init(&bars->s_full[1], 1);
+    mbar_init(&bars->p_ready, 128);
+    mbar_init(&bars->o_full, 1);
+    bars->abort_flag = 0;
+    bars->is_last = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  // Zero Q and P^T (rows >= G stay zero for the whole kernel).
+  for (int i = threadIdx.x; i < 4096 / 16; i += blockDim.x) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ page-walking TMA producer
+    if (lane == 0) {
+      const int* bt = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
+      const int pages_per_tile = kDaTile / p.page_size;
+      const int box_bytes = p.page_size * 128;
+      int issued = 0;
+      for (int j = 0; j < nt; ++j) {
+        const int st = j % kDaStages;
+        if (!mbar_wait(&bars->kv_empty[st], ((j / kDaStages) & 1) ^ 1, abort_flag, nullptr, 0)) break;
+        uint8_t* kd = kv_s + st * 2 * kDaTileBytes;
+        uint8_t* vd = kd + kDaTileBytes;
+        mbar_expect_tx(&bars->kv_full[st], 2 * kDaTileBytes);
+        const int page0 = (begin + j * kDaTile) / p.page_size;
+        for (int i = 0; i < pages_per_tile; ++i) {
+          int pi = page0 + i;
+          if (pi >= p.max_blocks) pi = p.max_blocks - 1;   // beyond the table: any valid page, keys are masked
+          const int tok_row = bt[pi] * p.page_size;
+          tma_load_3d(kd + i * box_bytes, &tm_k, &bars->kv_full[st], 0, kvh, tok_row);
+          tma_load_3d(vd + i * box_bytes, &tm_v, &bars->kv_full[st], 0, kvh, tok_row);
+        }
+        issued = j + 1;
+      }
+      int dummy = 0;
+      for (int st = 0; st < kDaStages; ++st) {
+        const int fills = (issued > st) ? (issued - st + kDaStages - 1) / kDaStages : 0;
+        if (fills > 0) mbar_wait(&bars->kv_full[st], (fills - 1) & 1, &dummy, nullptr, 0, 200000000LL);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    // The softmax warps quantise Q into shared memory first; barrier 2 joins them with this warp.
+    if (nt > 0) asm volatile("bar.sync 2, 160;" ::: "memory");
+    if (lane == 0 && nt > 0) {
+      constexpr uint32_t idesc_s = make_idesc(kFmtE4M3, 128, kDaHeadsPad, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(kFmtE4M3, 128, kDaHeadsPad, 1, 0);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      auto issue_s = [&](int j) {
+        const uint32_t k_addr = smem_u32(kv_s + (j % kDaStages) * 2 * kDaTileBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // 32 channels per MMA
+          umma_f8(tmem_base + (j & 1) * 16, make_smem_desc_sw128(k_addr) + 2 * k, make_smem_desc_sw128(q_addr) + 2 * k,
+                  idesc_s, k != 0);
+        tc_commit(&bars->s_full[j & 1]);
+      };
+      bool ok = mbar_wait(&bars->kv_full[0], 0, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMA_FULL);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; ok && j < nt; ++j) {
+        if (j + 1 < nt) {
+          const int st1 = (j + 1) % kDaStages;
+          if (!mbar_wait(&bars->kv_full[st1], ((j + 1) / kDaStages) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMA_FULL))
+            break;
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        if (!mbar_wait(&bars->p_ready, j & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(kv_s + (j % kDaStages) * 2 * kDaTileBytes + kDaTileBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // 32 keys per MMA
+          umma_f8(tmem_base + 32, make_smem_desc_sw128_mn8(v_addr + k * 4096), make_smem_desc_sw128(p_addr) + 2 * k,
+                  idesc_pv, k != 0);
+        tc_commit(&bars->o_full);
+        tc_commit(&bars->kv_empty[j % kDaStages]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax / output (128 threads)
+    const int qd = warp & 3;
+    const int t = qd * 32 + lane;   // key index inside a tile, and channel index for the output phase
+    const int tid = t;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+    const float log2e = 1.4426950408889634f;
+
+    // ---- quantise Q: one head per iteration, thread t holds channel t
+    for (int g = 0; g < G; ++g) {
+      const float qv = __bfloat162float(p.q[static_cast<size_t>(r) * p.q_ld + (kvh * G + g) * 128 + t]);
+      float a = fabsf(qv);
+      if (!(a == a) || a > 3.0e38f) a = 0.f;
+      a = warp_max(a);
+      if (lane == 0) bars->s_red[qd] = a;
+      SyncBar1x128::sync();
+      const float amax = fmaxf(fmaxf(bars->s_red[0], bars->s_red[1]), fmaxf(bars->s_red[2], bars->s_red[3]));
+      const float qs = amax > 0.f ? amax / 448.f : 1.f;
+      // row g of the K-major tile: 16-byte unit (t / 16) lands at unit index ((t / 16) ^ (g % 8))
+      q_s[g * 128 + ((((t >> 4) ^ (g & 7))) << 4) + (t & 15)] = f32_to_e4m3(__fdiv_rn(qv, qs));
+      if (t == 0) bars->qscale[g] = qs * p.sm_scale * log2e;   // scores leave the MMA in log2 units after this factor
+      SyncBar1x128::sync();
+    }
+    fence_proxy_async_smem();
+    if (nt > 0) asm volatile("bar.sync 2, 160;" ::: "memory");
+
+    float m[G], l[G], o[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m[g] = -INFINITY;
+      l[g] = 0.f;
+      o[g] = 0.f;
+    }
+    const int* bt = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
+    bool ok = true;
+    for (int j = 0; j < nt && ok; ++j) {
+      // per-token scales of this tile (thread = key)
+      const int tok = begin + j * kDaTile + t;
+      const bool valid = tok < end && tok >= first;
+      float ksc = 0.f, vsc = 0.f;
+      if (tok < end) {
+        int pi = tok / p.page_size;
+        if (pi >= p.max_blocks) pi = p.max_blocks - 1;
+        const size_t slot = (static_cast<size_t>(bt[pi]) * p.page_size + tok % p.page_size) * p.hkv + kvh;
+        ksc = p.k_scale ? p.k_scale[slot] : p.k_static_scale;
+        vsc = p.v_scale ? p.v_scale[slot] : p.v_static_scale;
+      }
+      ok = mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t raw[16];
+      tmem_ld16(lane_addr + (j & 1) * 16, raw);
+      tmem_wait_ld();
+      float s[G];
+      float red_v[G + 1];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        s[g] = valid ? __uint_as_float(raw[g]) * ksc * bars->qscale[g] : -INFINITY;
+        red_v[g] = s[g];
+      }
+      red_v[G] = valid ? vsc : 0.f;
+#pragma unroll
+      for (int g = 0; g <= G; ++g) {
+        red_v[g] = warp_max(red_v[g]);
+        if (lane == 0) bars->red[qd][g] = red_v[g];
+      }
+      SyncBar1x128::sync();
+      float tmax[G + 1];
+#pragma unroll
+      for (int g = 0; g <= G; ++g)
+        tmax[g] = fmaxf(fmaxf(bars->red[0][g], bars->red[1][g]), fmaxf(bars->red[2][g], bars->red[3][g]));
+      const float vmax = tmax[G] > 0.f ? tmax[G] : 1.f;
+      const float vfold = valid ? vsc / vmax * 256.f : 0.f;   // probabilities enter the MMA as p * vsc/vmax * 256
+      float alpha[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float m_new = fmaxf(m[g], tmax[g]);
+        alpha[g] = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - m_new);
+        const float pr = (valid && m_new != -INFINITY) ? exp2f(s[g] - m_new) : 0.f;
+        const uint8_t p8 = f32_to_e4m3(pr * vfold);
+        p_s[g * 128 + ((((t >> 4) ^ (g & 7))) << 4) + (t & 15)] = p8;
+        // the normaliser uses the value the tensor core will actually multiply
+        const float p_eff = (vfold > 0.f) ? e4m3_to_f32_int(p8) / vfold : 0.f;
+        l[g] = l[g] * alpha[g] + p_eff;
+        m[g] = m_new;
+      }
+      // m[], alpha[] and vmax are identical in all 128 threads (they come from the shared reduction),
+      // so the output phase below needs no further exchange.
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready);
+      // ---- fold P.V of this tile into the output (thread = channel)
+      ok = mbar_wait(&bars->o_full, j & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld16(lane_addr + 32, raw);
+      tmem_wait_ld();
+      const float of = vmax / 256.f;
+#pragma unroll
+      for (int g = 0; g < G; ++g) o[g] = fmaf(o[g], alpha[g], __uint_as_float(raw[g]) * of);
+      tc_fence_before();
+      // red[] is rewritten by the next tile only after all 128 threads arrived on p_ready, i.e. after
+      // every read of this tile's maxima.
+    }
+
+    // ---- hand the split's state to the common tail: l is a per-thread partial over keys -> reduce
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float lg = warp_sum(l[g]);
+      if (lane == 0) bars->red[qd][g] = lg;
+    }
+    SyncBar1x128::sync();
+    if (t == 0) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        m_s[g] = (m[g] == -INFINITY) ? -INFINITY : m[g] * 0.6931471805599453f;  // back to natural-log units
+        l_s[g] = bars->red[0][g] + bars->red[1][g] + bars->red[2][g] + bars->red[3][g];
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) o_s[g * 128 + t] = ok ? o[g] : 0.f;
+    SyncBar1x128::sync();
+    attention_tail<128, G, 1, SyncBar1x128>(p, r, kvh, split, splits, tid, m_s, l_s, o_s, &bars->is_last, bars->s_red);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// [pages*page_size tokens, kv_heads, 128] E4M3 plane; box = {128 channels, 1 head, page_size tokens}.
+static int make_page_tmap(CUtensorMap* out, const void* pages, long long total_tokens, int hkv, int page_size) {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  if (!fn) return SLLM_ERR_DRIVER_ENTRY;
+  if (reinterpret_cast<uintptr_t>(pages) & 15) return SLLM_ERR_ALIGNMENT;
+  cuuint64_t gdim[3] = {128, static_cast<cuuint64_t>(hkv), static_cast<cuuint64_t>(total_tokens)};
+  cuuint64_t gstride[2] = {128, static_cast<cuuint64_t>(hkv) * 128};
+  cuuint32_t box[3] = {128, 1, static_cast<cuuint32_t>(page_size)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(pages), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> g_page_tmaps;
+static std::mutex g_page_mu;
+
+static int cached_page_tmap(CUtensorMap* out, const void* pages, long long total_tokens, int hkv, int page_size) {
+  auto key = std::make_tuple(pages, total_tokens, hkv, page_size);
+  std::lock_guard<std::mutex> g(g_page_mu);
+  auto it = g_page_tmaps.find(key);
+  if (it != g_page_tmaps.end()) {
+    *out = it->second;
+    return SLLM_OK;
+  }
+  int rc = make_page_tmap(out, pages, total_tokens, hkv, page_size);
+  if (rc == SLLM_OK) {
+    if (g_page_tmaps.size() > 4096) g_page_tmaps.clear();
+    g_page_tmaps[key] = *out;
+  }
+  return rc;
+}
+
+template <int G>
+static int launch_da(const CUtensorMap& tk, const CUtensorMap& tv, const PagedAttnParams& p, int rows, int splits,
+                     cudaStream_t st) {
+  const size_t smem = kDaStages * 2 * kDaTileBytes + 4096 + sizeof(DecodeTcBarriers) +
+                      sizeof(float) * (2 * kDaHeadsPad + kDaHeadsPad * 128) + 1024;
+  static bool cfg = false;
+  if (!cfg) {
+    if (cudaFuncSetAttribute(decode_attention_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return SLLM_ERR_CUDA;
+    cfg = true;
+  }
+  dim3 grid(rows, p.hkv, splits);
+  decode_attention_tc_kernel<G><<<grid, kDaThreads, smem, st>>>(tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+// Same contract as sllm_paged_attention, restricted to E4M3 pages with per-token scale planes or static
+// scales, head_dim 128, page sizes dividing 128 and a GQA group of 1, 2, 4, 8 or 16.
+SLLM_EXPORT int sllm_decode_attention_tc(const void* q, int q_ld, const void* k_pages, const void* v_pages,
+                                         const float* k_scale, const float* v_scale, float k_static_scale,
+                                         float v_static_scale, const int* block_table, int max_blocks,
+                                         const int* seq_index, const int* kv_lens, int rows, int hq, int hkv,
+                                         int num_pages, int page_size, int window, float sm_scale, void* out_bf16,
+                                         void* out_fp8, float* out_scale, int ld_scale, const float* sinks,
+                                         int splits, float* ws, long long ws_floats, int* counters, int n_counters,
+                                         int* status, void* stream) {
+  if (!q || !k_pages || !v_pages || !block_table || !seq_index || !kv_lens || rows <= 0 || hkv <= 0 || hq % hkv)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  if (!out_bf16 && !(out_fp8 && out_scale)) return SLLM_ERR_INVALID_ARGUMENT;
+  if (!k_scale && !(k_static_scale > 0.f && v_static_scale > 0.f)) return SLLM_ERR_INVALID_ARGUMENT;
+  if (page_size <= 0 || (kDaTile % page_size) || (page_size & (page_size - 1)) || page_size < 8)
+    return SLLM_ERR_UNSUPPORTED_SHAPE;
+  if (splits < 1 || splits > 65535 || hkv > 65535 || max_blocks <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  const int g = hq / hkv;
+  PagedAttnParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.q_ld = q_ld;
+  p.k_pages = k_pages; p.v_pages = v_pages; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.k_static_scale = k_static_scale; p.v_static_scale = v_static_scale;
+  p.block_table = block_table; p.max_blocks = max_blocks; p.seq_index = seq_index; p.kv_lens = kv_lens;
+  p.hkv = hkv; p.page_size = page_size; p.window = window; p.sm_scale = sm_scale;
+  p.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16); p.out_fp8 = static_cast<uint8_t*>(out_fp8);
+  p.out_scale = out_scale; p.ld_scale = ld_scale; p.sinks = sinks;
+  p.ws_o = nullptr; p.ws_ml = nullptr; p.counters = counters; p.status_word = status;
+  if (splits > 1) {
+    const long long units = static_cast<long long>(rows) * hkv;
+    const long long need = units * splits * (static_cast<long long>(g) * 128 + g * 2);
+    if (!ws || !counters || ws_floats < need || n_counters < units) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+    p.ws_o = ws;
+    p.ws_ml = ws + units * splits * g * 128;
+  }
+  CUtensorMap tk, tv;
+  const long long total_tokens = static_cast<long long>(num_pages) * page_size;
+  int rc = cached_page_tmap(&tk, k_pages, total_tokens, hkv, page_size);
+  if (rc != SLLM_OK) return rc;
+  rc = cached_page_tmap(&tv, v_pages, total_tokens, hkv, page_size);
+  if (rc != SLLM_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (g) {
+    case 1: return launch_da<1>(tk, tv, p, rows, splits, st);
+    case 2: return launch_da<2>(tk, tv, p, rows, splits, st);
+    case 4: return launch_da<4>(tk, tv, p, rows, splits, st);
+    case 8: return launch_da<8>(tk, tv, p, rows, splits, st);
+    case 16: return launch_da<16>(tk, tv, p, rows, splits, st);
+    default: return SLLM_ERR_UNSUPPORTED_SHAPE;
+  }
+}

@@ -57,6 +57,8 @@ _KERNEL_SIGNATURES = {
     "sllm_elementwise": (I, [P, P, P, L, I, I, F, P]),
     "sllm_argmax": (I, [P, P, P, I, I, I, I, P, L, P, I, P]),
     "sllm_gemm_set_cluster_split": (None, [I]),
+    "sllm_decode_attention_tc": (I, [P, I, P, P, P, P, F, F, P, I, P, P, I, I, I, I, I, I, F, P, P, P, I, P, I, P, L,
+                                      P, I, P, P]),
     "sllm_prefill_attention": (I, [P, I, I, P, I, I, I, I, F, P, P, P, I, P, P]),
     "sllm_paged_attention_workspace_floats": (L, [I, I, I, I, I]),
     "sllm_paged_attention": (I, [P, I, P, P, P, P, F, F, P, I, P, P, I, I, I, I, I, I, F, I, P, P, P, I, P, I, P, L,

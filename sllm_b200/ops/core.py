@@ -358,7 +358,7 @@ def _attn_splits(rows: int, hkv: int, max_kv: int) -> int:
 def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq_index: torch.Tensor,
                     kv_lens: torch.Tensor, hq: int, hkv: int, hd: int, *, window: int = 0,
                     sm_scale: Optional[float] = None, max_kv: int = 0, quant_out: bool = False,
-                    sinks: Optional[torch.Tensor] = None):
+                    sinks: Optional[torch.Tensor] = None, impl: Optional[str] = None):
     """Attention of each query row over its sequence's pages. q: [R, hq*hd] (row stride allowed).
     Returns [R, hq*hd] (bf16) or a QTensor when quant_out (head_dim 128)."""
     scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(hd)
@@ -398,6 +398,21 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
     else:
         ob = torch.empty((r, hq * hd), dtype=torch.bfloat16, device=q.device)
         out_b, out_q, out_s, ld = ob, None, None, 0
+    use_tc = (kv.fp8 and hd == 128 and (hq // hkv) in (1, 2, 4, 8, 16) and 128 % kv.page_size == 0
+              and kv.page_size >= 8 and impl != "cuda_core")
+    if impl == "tensor_core" and not use_tc:
+        raise ValueError("tensor-core decode attention needs FP8 pages, head_dim 128 and a GQA group <= 16")
+    if use_tc:
+        mk = max_kv if max_kv > 0 else block_table.shape[1] * kv.page_size
+        ctas = r * hkv
+        splits = max(1, min((3 * _SM_COUNT + ctas - 1) // ctas, (mk + 255) // 256, 64)) if ctas < 3 * _SM_COUNT else 1
+        rc = lib.sllm_decode_attention_tc(
+            _p(q), q.stride(0), _p(kv.k), _p(kv.v), _p(kv.k_scale), _p(kv.v_scale), kv.k_static, kv.v_static,
+            _p(block_table), block_table.stride(0), _p(seq_index), _p(kv_lens), r, hq, hkv, kv.k.shape[0],
+            kv.page_size, window, scale, _p(out_b), _p(out_q), _p(out_s), ld, _p(sinks), splits, _p(wsp.ws),
+            wsp.ws.numel(), _p(wsp.counters), wsp.counters.numel(), _p(wsp.status), _stream())
+        _lib.check(rc, "decode_attention_tc")
+        return oq if quant_out else ob
     rc = lib.sllm_paged_attention(
         _p(q), q.stride(0), _p(kv.k), _p(kv.v), _p(kv.k_scale), _p(kv.v_scale), kv.k_static, kv.v_static,
         _p(block_table), block_table.stride(0), _p(seq_index), _p(kv_lens), r, hq, hkv, hd, kv.page_size, window,

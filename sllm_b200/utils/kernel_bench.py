@@ -1,0 +1,157 @@
+"""Per-kernel micro-benchmarks with roofline fractions.
+
+    python -m sllm_b200.utils.kernel_bench --op gemm --m 32 --n 4096 --k 4096 [--fp8]
+    python -m sllm_b200.utils.kernel_bench --op attention --batch 32 --ctx 2048
+    python -m sllm_b200.utils.kernel_bench --op prefill --seqs 4 --len 2048
+    python -m sllm_b200.utils.kernel_bench --op decode-layer --batch 32 --ctx 2048
+
+Timing follows the usual hygiene: warm-up, an L2 flush (a 256 MB write) before each timed launch, CUDA
+events on the launching stream, median of the repetitions.  Fractions are reported against the
+measured peaks in MEASURED_PEAKS.json at the repository root when present ("of measured"), else
+against 6.65 TB/s and 1.59 PFLOP/s ("of fallback").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import statistics
+from pathlib import Path
+
+import torch
+
+from .. import ops
+from ..ops import reference as ref
+from ..ops.core import KVLayer, LinearWeight
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "of measured"
+    return 6.65e12, 1.59e15, "of fallback"
+
+
+_flush = None
+
+
+def timed(fn, reps: int = 10, warmup: int = 3, flush: bool = True) -> float:
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        if flush:
+            _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    return statistics.median(ts)
+
+
+def bench_gemm(m, n, k, fp8, reps):
+    dev = "cuda"
+    x = torch.randn(m, k, device=dev).bfloat16()
+    w = (torch.randn(n, k, device=dev) * 0.02).bfloat16()
+    if fp8:
+        wq = ops.quant_fp8(w)
+        lw = LinearWeight("fp8", wq.data, wq.scale)
+        xin = ops.quant_fp8(x)
+        wbytes = n * k
+    else:
+        lw = LinearWeight("dense", w)
+        xin = x
+        wbytes = 2 * n * k
+    t = timed(lambda: ops.linear(xin, lw), reps)
+    bw, fl, tag = peaks()
+    bytes_ = wbytes + m * k * (1 if fp8 else 2) + 2 * m * n
+    flops = 2.0 * m * n * k
+    peak_fl = fl * (2 if fp8 else 1)
+    roof = max(bytes_ / bw, flops / peak_fl)
+    return {"op": "gemm", "m": m, "n": n, "k": k, "fp8": fp8, "us": t * 1e6, "GBps": bytes_ / t / 1e9,
+            "TFLOPs": flops / t / 1e12, "roofline_us": roof * 1e6, "fraction": roof / t, "fraction_basis": tag}
+
+
+def _kv(batch, ctx, hkv, hd, fp8, page=16):
+    dev = "cuda"
+    blocks = (ctx + page - 1) // page + 1
+    pages = batch * blocks
+    table = torch.arange(pages, device=dev, dtype=torch.int32).view(batch, blocks)
+    if fp8:
+        kv = KVLayer(torch.randint(0, 0x70, (pages, page, hkv, hd), device=dev, dtype=torch.uint8),
+                     torch.randint(0, 0x70, (pages, page, hkv, hd), device=dev, dtype=torch.uint8),
+                     torch.full((pages, page, hkv), 0.01, device=dev), torch.full((pages, page, hkv), 0.01, device=dev),
+                     True, page)
+    else:
+        kv = KVLayer(torch.randn(pages, page, hkv, hd, device=dev).bfloat16(),
+                     torch.randn(pages, page, hkv, hd, device=dev).bfloat16(), None, None, False, page)
+    return kv, table
+
+
+def bench_attention(batch, ctx, hq, hkv, hd, fp8, reps):
+    dev = "cuda"
+    kv, table = _kv(batch, ctx, hkv, hd, fp8)
+    q = torch.randn(batch, hq * hd, device=dev).bfloat16()
+    seq = torch.arange(batch, device=dev, dtype=torch.int32)
+    lens = torch.full((batch,), ctx, device=dev, dtype=torch.int32)
+    t = timed(lambda: ops.paged_attention(q, kv, table, seq, lens, hq, hkv, hd, max_kv=ctx, quant_out=fp8 and hd == 128),
+              reps)
+    bw, _, tag = peaks()
+    bytes_ = 2 * batch * ctx * hkv * hd * (1 if fp8 else 2) + (2 * batch * ctx * hkv * 4 if fp8 else 0)
+    return {"op": "paged_attention", "batch": batch, "ctx": ctx, "hq": hq, "hkv": hkv, "hd": hd, "fp8": fp8,
+            "us": t * 1e6, "GBps": bytes_ / t / 1e9, "roofline_us": bytes_ / bw * 1e6, "fraction": bytes_ / bw / t,
+            "fraction_basis": tag}
+
+
+def bench_prefill(seqs, length, hq, hkv, reps):
+    from ..engine.batch import make_prefill_batch
+    from ..ops import prefill
+    dev = "cuda"
+    hd = 128
+    t_tok = seqs * length
+    qkv = torch.randn(t_tok, (hq + 2 * hkv) * hd, device=dev).bfloat16()
+    table = torch.zeros((seqs, 1), dtype=torch.int32, device=dev)
+    b = make_prefill_batch([[0] * length] * seqs, table, dev)
+    t = timed(lambda: prefill.prefill_attention(qkv, b, hq, hkv, hd), reps)
+    _, fl, tag = peaks()
+    flops = 4.0 * seqs * hq * hd * length * (length + 1) / 2
+    return {"op": "prefill_attention", "seqs": seqs, "len": length, "hq": hq, "hkv": hkv, "us": t * 1e6,
+            "TFLOPs": flops / t / 1e12, "fraction": flops / fl / t, "fraction_basis": tag}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True, choices=["gemm", "attention", "prefill", "decode-gemms"])
+    ap.add_argument("--m", type=int, default=32)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--fp8", action="store_true")
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--hd", type=int, default=128)
+    ap.add_argument("--seqs", type=int, default=4)
+    ap.add_argument("--len", type=int, default=2048)
+    ap.add_argument("--reps", type=int, default=10)
+    a = ap.parse_args()
+    if a.op == "gemm":
+        print(json.dumps(bench_gemm(a.m, a.n, a.k, a.fp8, a.reps)))
+    elif a.op == "attention":
+        print(json.dumps(bench_attention(a.batch, a.ctx, a.hq, a.hkv, a.hd, a.fp8, a.reps)))
+    elif a.op == "prefill":
+        print(json.dumps(bench_prefill(a.seqs, a.len, a.hq, a.hkv, a.reps)))
+    else:
+        for (n, k) in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096)):
+            print(json.dumps(bench_gemm(a.m, n, k, True, a.reps)))
+
+
+if __name__ == "__main__":
+    main()
