@@ -47,13 +47,14 @@ constexpr int kMaxStages = 8;
 constexpr int kGemmThreads = 192;
 
 constexpr int kMaxWorld = 8;
+constexpr int kMaxSlices = 8;   // cluster split-K slices per tile (flag / epoch slots per tile)
 
 struct CommParams {
   int world, rank;
   long long cap_elems;                 // bf16 elements per (buffer, source) region
   __nv_bfloat16* recv[kMaxWorld];      // recv[p]: base of rank p's receive buffer [2][world][cap_elems]
-  uint32_t* flags[kMaxWorld];          // flags[p]: base of rank p's flag array [max_tiles][world]
-  uint32_t* epoch;                     // local per-tile call counters [max_tiles]
+  uint32_t* flags[kMaxWorld];          // flags[p]: base of rank p's flag array [max_tiles * kMaxSlices][world]
+  uint32_t* epoch;                     // local call counters [max_tiles * kMaxSlices]
 };
 
 struct GemmParams {
@@ -128,6 +129,16 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ float4 ld_dsmem_f32x4(const float* local_ptr, uint32_t cta_rank) {
+  uint32_t ra;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local_ptr)), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(ra)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ float ld_dsmem_f32(const float* local_ptr, uint32_t cta_rank) {
   uint32_t ra;
   float v;
@@ -195,6 +206,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int a_row = a_tile * kTileA + row;
   float acc[BN];
   bool ok = true;
+  bool active = true;   // this CTA takes part in the output phase (false for non-final global split-K CTAs)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -333,30 +345,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       }
     }
-    // Cluster split-K: CTAs other than the cluster leader park their partial in their own shared
-    // memory (the pipeline stages are drained by now) for the leader to read over DSMEM.
-    if (cluster_split && split != 0) {
-#pragma unroll
-      for (int c = 0; c < BN; ++c) red[c * kTileA + row] = acc[c];
-    }
-  }
-
-  if (threadIdx.x == 64) TRACE(7);
-  if (cluster_split) cluster_sync_all();  // partials visible cluster-wide
-  if (threadIdx.x == 64) TRACE(8);
-
-  if (warp >= 2) {
-    bool writer = true;
-    if (cluster_split) {
-      writer = split == 0;
-      if (writer) {
-        for (uint32_t s = 1; s < gridDim.z; ++s) {
-#pragma unroll
-          for (int c = 0; c < BN; ++c) acc[c] += ld_dsmem_f32(red + c * kTileA + row, s);
-        }
-      }
-    } else if (gridDim.z > 1) {
-      // ---- global split-K fix-up: last CTA to arrive for this tile reduces all partials in order
+    // ---- global split-K fix-up (more than 8 splits, or clusters unavailable): the CTA that arrives
+    // last for this tile sums all partials in split order; nobody waits.
+    if (!cluster_split && gridDim.z > 1) {
       const int tile_id = a_tile * gridDim.y + b_tile;
       float* my = p.ws + (static_cast<size_t>(tile_id) * gridDim.z + split) * (BN * kTileA);
 #pragma unroll
@@ -371,8 +362,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         __threadfence();
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      writer = bars->is_last != 0;
-      if (writer) {
+      active = bars->is_last != 0;
+      if (active) {
         const float* base = p.ws + static_cast<size_t>(tile_id) * gridDim.z * (BN * kTileA);
 #pragma unroll
         for (int c = 0; c < BN; ++c) acc[c] = 0.f;
@@ -383,39 +374,158 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       }
     }
+    // Park the fp32 tile in shared memory as red[column][row] (the pipeline stages are drained by
+    // now).  The output phase below works on 16-byte units out of this buffer, and with a cluster
+    // split every CTA reduces and writes its own column slice of the tile over DSMEM.
+    if (active) {
+#pragma unroll
+      for (int c = 0; c < BN; ++c) red[c * kTileA + row] = acc[c];
+    }
+    if (!cluster_split) asm volatile("bar.sync 1, 128;" ::: "memory");
+  }
 
-    if (et == 0) TRACE(9);
-    if (kComm && writer) {
-      // ---- fused all-reduce of this tile across ranks (all 128 epilogue threads take part)
+  if (threadIdx.x == 64) TRACE(7);
+  if (cluster_split) cluster_sync_all();  // partials visible cluster-wide
+  if (threadIdx.x == 64) TRACE(8);
+
+  if (warp >= 2 && active && ok) {
+    const int nslice = cluster_split ? static_cast<int>(gridDim.z) : 1;
+    const int cw = BN / nslice;            // columns of the tile this CTA finishes
+    const int c0 = (cluster_split ? split : 0) * cw;
+    const int tile_id = a_tile * gridDim.y + b_tile;
+    const bool tr = p.transpose_out != 0;
+    // unit u -> (column, first row) of 8 consecutive outputs along the contiguous axis of Y
+    const int units = tr ? cw * (kTileA / 8) : kTileA * (cw / 8);
+    auto unit_pos = [&](int u, int& col, int& r0) {
+      if (tr) { col = c0 + u / (kTileA / 8); r0 = (u % (kTileA / 8)) * 8; }   // 8 rows of one column
+      else    { r0 = u % kTileA; col = c0 + (u / kTileA) * 8; }                // 8 columns of one row
+    };
+    auto load_unit = [&](int col, int r0, float (&v)[8]) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      for (int s = 0; s < nslice; ++s) {
+        if (tr) {
+          const float* src = red + col * kTileA + r0;
+          float4 x0, x1;
+          if (nslice == 1) {
+            x0 = *reinterpret_cast<const float4*>(src);
+            x1 = *reinterpret_cast<const float4*>(src + 4);
+          } else {
+            x0 = ld_dsmem_f32x4(src, s);
+            x1 = ld_dsmem_f32x4(src + 4, s);
+          }
+          v[0] += x0.x; v[1] += x0.y; v[2] += x0.z; v[3] += x0.w;
+          v[4] += x1.x; v[5] += x1.y; v[6] += x1.z; v[7] += x1.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float* src = red + (col + j) * kTileA + r0;
+            v[j] += (nslice == 1) ? *src : ld_dsmem_f32(src, s);
+          }
+        }
+      }
+    };
+    // offset of a unit inside a tile-sized bf16 exchange region ([column][row] or [row][column])
+    auto unit_off = [&](int col, int r0) -> long long {
+      return static_cast<long long>(tile_id) * (kTileA * BN) + (tr ? col * kTileA + r0 : r0 * BN + col);
+    };
+    auto store_unit = [&](int col, int r0, float (&v)[8]) {
+      if (tr) {
+        const int b_row = b_tile * BN + col;
+        const int a0 = a_tile * kTileA + r0;
+        if (b_row >= p.b_rows || a0 >= p.a_rows) return;
+        const size_t idx = static_cast<size_t>(b_row) * p.ldy + a0;
+        if (a0 + 8 <= p.a_rows && (p.ldy & 7) == 0) {
+          if (p.epilogue == 1) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + idx);
+            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { v[2 * j] += __bfloat162float(r2[j].x); v[2 * j + 1] += __bfloat162float(r2[j].y); }
+          }
+          uint4 out;
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+          *reinterpret_cast<uint4*>(p.y + idx) = out;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (a0 + j < p.a_rows) {
+              float x = v[j];
+              if (p.epilogue == 1) x += bf16_to_f32(p.residual[idx + j]);
+              p.y[idx + j] = f32_to_bf16(x);
+            }
+          }
+        }
+      } else {
+        const int a_row = a_tile * kTileA + r0;
+        const int b0 = b_tile * BN + col;
+        if (a_row >= p.a_rows || b0 >= p.b_rows) return;
+        const size_t idx = static_cast<size_t>(a_row) * p.ldy + b0;
+        if (b0 + 8 <= p.b_rows && (p.ldy & 7) == 0) {
+          if (p.epilogue == 1) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + idx);
+            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { v[2 * j] += __bfloat162float(r2[j].x); v[2 * j + 1] += __bfloat162float(r2[j].y); }
+          }
+          uint4 out;
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+          *reinterpret_cast<uint4*>(p.y + idx) = out;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (b0 + j < p.b_rows) {
+              float x = v[j];
+              if (p.epilogue == 1) x += bf16_to_f32(p.residual[idx + j]);
+              p.y[idx + j] = f32_to_bf16(x);
+            }
+          }
+        }
+      }
+    };
+
+    if (threadIdx.x == 64) TRACE(9);
+    if (!kComm) {
+      for (int u = et; u < units; u += 128) {
+        int col, r0;
+        unit_pos(u, col, r0);
+        float v[8];
+        load_unit(col, r0, v);
+        store_unit(col, r0, v);
+      }
+    } else {
+      // ---- fused all-reduce: push this CTA's slice (bf16) to every rank, flag, wait, sum in rank order
       const CommParams& cm = p.comm;
-      const int tile_id = a_tile * gridDim.y + b_tile;
+      const int slot = tile_id * kMaxSlices + (cluster_split ? split : 0);
       if (et == 0) {
-        const uint32_t e = cm.epoch[tile_id] + 1;
-        cm.epoch[tile_id] = e;
-        bars->epoch = e;
+        const uint32_t e1 = cm.epoch[slot] + 1;
+        cm.epoch[slot] = e1;
+        bars->epoch = e1;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const uint32_t e = bars->epoch;
       const long long region = static_cast<long long>(e & 1) * cm.world;
-      const long long tile_off = static_cast<long long>(tile_id) * (kTileA * BN) + row * BN;
-      // Every rank (this one included) receives the bf16-rounded partial, so all ranks sum the
-      // same values in the same order.
+      for (int u = et; u < units; u += 128) {
+        int col, r0;
+        unit_pos(u, col, r0);
+        float v[8];
+        load_unit(col, r0, v);
+        uint4 w;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
-        uint4 v;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[8 * c + 2 * j], acc[8 * c + 2 * j + 1]);
-        for (int peer = 0; peer < cm.world; ++peer) {
-          uint4* dst = reinterpret_cast<uint4*>(cm.recv[peer] + (region + cm.rank) * cm.cap_elems + tile_off);
-          dst[c] = v;
-        }
+        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        const long long off = (region + cm.rank) * cm.cap_elems + unit_off(col, r0);
+        for (int peer = 0; peer < cm.world; ++peer) *reinterpret_cast<uint4*>(cm.recv[peer] + off) = w;
       }
       __threadfence_system();
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      bool comm_ok = true;
       if (et < cm.world && et != cm.rank) {
-        st_release_sys(cm.flags[et] + static_cast<size_t>(tile_id) * cm.world + cm.rank, e);
-        const uint32_t* f = cm.flags[cm.rank] + static_cast<size_t>(tile_id) * cm.world + et;
+        st_release_sys(cm.flags[et] + static_cast<size_t>(slot) * cm.world + cm.rank, e);
+        const uint32_t* f = cm.flags[cm.rank] + static_cast<size_t>(slot) * cm.world + et;
         uint32_t spins = 0;
         long long t0 = 0;
         while (static_cast<int32_t>(ld_acquire_sys(f) - e) < 0) {
@@ -432,74 +542,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*abort_flag) ok = false;
+      if (*abort_flag) comm_ok = false;
+      if (comm_ok) {
+        for (int u = et; u < units; u += 128) {
+          int col, r0;
+          unit_pos(u, col, r0);
+          float v[8];
 #pragma unroll
-      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
-      if (ok) {
-        for (int src = 0; src < cm.world; ++src) {
-          const uint4* srcp =
-              reinterpret_cast<const uint4*>(cm.recv[cm.rank] + (region + src) * cm.cap_elems + tile_off);
+          for (int j = 0; j < 8; ++j) v[j] = 0.f;
+          const long long uo = unit_off(col, r0);
+          for (int src = 0; src < cm.world; ++src) {
+            const uint4 w = __ldcg(reinterpret_cast<const uint4*>(cm.recv[cm.rank] + (region + src) * cm.cap_elems + uo));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
 #pragma unroll
-          for (int c = 0; c < BN / 8; ++c) {
-            const uint4 v = __ldcg(srcp + c);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              acc[8 * c + 2 * j] += __bfloat162float(h[j].x);
-              acc[8 * c + 2 * j + 1] += __bfloat162float(h[j].y);
-            }
+            for (int j = 0; j < 4; ++j) { v[2 * j] += __bfloat162float(h[j].x); v[2 * j + 1] += __bfloat162float(h[j].y); }
           }
-        }
-      }
-    }
-
-    if (writer && ok && a_row < p.a_rows) {
-      if (p.transpose_out) {
-        // Y[b, a]: for a fixed column the 32 lanes of a warp write 32 consecutive bf16.
-#pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          const int b_row = b_tile * BN + c;
-          if (b_row < p.b_rows) {
-            const size_t idx = static_cast<size_t>(b_row) * p.ldy + a_row;
-            float v = acc[c];
-            if (p.epilogue == 1) v += bf16_to_f32(p.residual[idx]);
-            p.y[idx] = f32_to_bf16(v);
-          }
-        }
-      } else {
-        // Y[a, b]: each thread owns BN consecutive outputs of its row; 16-byte stores.
-        const int b0 = b_tile * BN;
-        const size_t base = static_cast<size_t>(a_row) * p.ldy + b0;
-        if (b0 + BN <= p.b_rows && (p.ldy % 8) == 0) {
-#pragma unroll
-          for (int c = 0; c < BN; c += 8) {
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = acc[c + j];
-            if (p.epilogue == 1) {
-              const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + base + c);
-              const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                v[2 * j] += __bfloat162float(r2[j].x);
-                v[2 * j + 1] += __bfloat162float(r2[j].y);
-              }
-            }
-            uint4 out;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-            *reinterpret_cast<uint4*>(p.y + base + c) = out;
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < BN; ++c) {
-            if (b0 + c < p.b_rows) {
-              float v = acc[c];
-              if (p.epilogue == 1) v += bf16_to_f32(p.residual[base + c]);
-              p.y[base + c] = f32_to_bf16(v);
-            }
-          }
+          store_unit(col, r0, v);
         }
       }
     }
@@ -701,6 +759,7 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
     if (comm->world < 2 || comm->world > kMaxWorld || comm->rank < 0 || comm->rank >= comm->world || !comm->epoch)
       return SLLM_ERR_INVALID_ARGUMENT;
     const long long tiles = static_cast<long long>(a_tiles) * b_tiles;
+    // flags and epochs hold kMaxSlices slots per tile
     if (tiles > comm->max_tiles || tiles * kTileA * bn > comm->cap_elems) return SLLM_ERR_WORKSPACE_TOO_SMALL;
     p.comm.world = comm->world; p.comm.rank = comm->rank; p.comm.cap_elems = comm->cap_elems;
     for (int i = 0; i < comm->world; ++i) {
@@ -721,7 +780,10 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
   p.transpose_out = transpose_out; p.ldy = ldy; p.ld_sa = ld_sa; p.ld_sb = ld_sb;
   p.epilogue = residual ? 1 : 0;
   // 2..8 splits reduce inside one thread-block cluster over DSMEM; more use the global fix-up.
-  p.cluster_split = (splits >= 2 && splits <= 8 && !g_disable_cluster_split) ? 1 : 0;
+  // (the output phase needs whole 16-byte units per slice: any slice width when Y is written
+  // transposed, at least 8 columns otherwise)
+  const bool pow2 = splits == 2 || splits == 4 || splits == 8;
+  p.cluster_split = (pow2 && bn % splits == 0 && (transpose_out || bn / splits >= 8) && !g_disable_cluster_split) ? 1 : 0;
   p.scale_a = scale_a; p.scale_b = scale_b;
   p.y = static_cast<__nv_bfloat16*>(y);
   p.residual = static_cast<const __nv_bfloat16*>(residual);

@@ -115,7 +115,8 @@ def _gemm_plan(m: int, n: int, k_blocks: int):
     if m <= 128:
         bn = 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
         tiles = (n + 127) // 128
-        splits = max(1, min((2 * _SM_COUNT) // max(tiles, 1), k_blocks // 4, 8))
+        want = max(1, min((2 * _SM_COUNT) // max(tiles, 1), k_blocks // 4, 8))
+        splits = 8 if want >= 8 else 4 if want >= 4 else 2 if want >= 2 else 1   # cluster sizes
         stages = {16: 5, 32: 4, 64: 3, 128: 5}[bn]
         return True, bn, splits, stages
     return False, 128, 1, 5

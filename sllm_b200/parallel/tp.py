@@ -93,7 +93,7 @@ class FusedTP(NcclTP):
         self.cap_elems = pad_tokens * n_pad
         self.max_tiles = max(n_pad // 128, (pad_tokens + 127) // 128 * (n_pad // 16))
         recv_bytes = 2 * size * self.cap_elems * 2
-        flag_bytes = self.max_tiles * size * 4
+        flag_bytes = self.max_tiles * 8 * size * 4   # 8 cluster slices per tile
         small_slot = max_rows_small * 8
         small_bytes = 2 * size * small_slot
         total = recv_bytes + flag_bytes + small_bytes + 4096
@@ -103,7 +103,7 @@ class FusedTP(NcclTP):
         self.off_small = self.region.carve(small_bytes)
         self.off_small_flags = self.region.carve(64)
         self.small_slot = small_slot
-        self.epoch = torch.zeros(self.max_tiles + 1, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(self.max_tiles * 8 + 8, dtype=torch.int32, device=device)
         self.small_epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self.desc = CommDesc()
         self.desc.world, self.desc.rank = size, rank
