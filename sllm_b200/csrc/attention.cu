@@ -24,6 +24,8 @@ namespace sllm {
 
 template <int HD, int G, bool kFp8>
 __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int EPL = HD / 32;  // channels per lane in the P.V phase
   extern __shared__ float smem[];
   float* q_s = smem;                       // [G][HD]
@@ -230,7 +232,7 @@ static int launch_paged(const PagedAttnParams& p, int rows, int splits, cudaStre
     cfg = true;
   }
   dim3 grid(rows, p.hkv, splits);
-  paged_attention_kernel<HD, G, kFp8><<<grid, 128, smem, st>>>(p);
+  launch_kernel(paged_attention_kernel<HD, G, kFp8>, dim3(grid), dim3(128), smem, st, 1u, p);
   return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 

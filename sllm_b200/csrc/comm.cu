@@ -96,6 +96,8 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t target,
 // (independent of the record size of a call); `epoch` is a local counter.
 __global__ void allgather_small_kernel(PeerTable pt, long long offset, long long flag_offset, int slot_bytes,
                                        const uint8_t* src, uint8_t* dst, uint32_t* epoch, int* status) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ uint32_t s_e;
   if (threadIdx.x == 0) {
     s_e = *epoch + 1;
@@ -124,6 +126,8 @@ __global__ void allgather_small_kernel(PeerTable pt, long long offset, long long
 // Merge per-shard argmax records: rows x world (value fp32, index int32) -> best index per row
 // (largest value, ties to the lowest index, any -1 (NaN shard) wins).
 __global__ void argmax_merge_kernel(const float* vals, const int* idx, int* out, int rows, int world) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float best = -INFINITY;
@@ -152,7 +156,7 @@ SLLM_EXPORT int sllm_allgather_small(const void* const* bases, int world, int ra
   pt.world = world;
   pt.rank = rank;
   for (int i = 0; i < world; ++i) pt.base[i] = const_cast<void*>(bases[i]);
-  allgather_small_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(allgather_small_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), 1u, 
       pt, offset, flag_offset, slot_bytes, static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst),
       static_cast<uint32_t*>(epoch), status);
   return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
@@ -160,6 +164,6 @@ SLLM_EXPORT int sllm_allgather_small(const void* const* bases, int world, int ra
 
 SLLM_EXPORT int sllm_argmax_merge(const float* vals, const int* idx, int* out, int rows, int world, void* stream) {
   if (!vals || !idx || !out || rows <= 0 || world <= 0) return SLLM_ERR_INVALID_ARGUMENT;
-  argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(vals, idx, out, rows, world);
+  launch_kernel(argmax_merge_kernel, dim3((rows + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u, vals, idx, out, rows, world);
   return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }

@@ -68,6 +68,8 @@ template <int G>
 __global__ void __launch_bounds__(kDaThreads, 2)
 decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            const PagedAttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // layout: stages x {K tile, V tile} | Q (16 x 128 B) | P^T (16 x 128 B) | barriers | tail scratch
@@ -380,7 +382,7 @@ static int launch_da(const CUtensorMap& tk, const CUtensorMap& tv, const PagedAt
     cfg = true;
   }
   dim3 grid(rows, p.hkv, splits);
-  decode_attention_tc_kernel<G><<<grid, kDaThreads, smem, st>>>(tk, tv, p);
+  launch_kernel(decode_attention_tc_kernel<G>, dim3(grid), dim3(kDaThreads), smem, st, 1u, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 

@@ -68,6 +68,8 @@ __device__ __forceinline__ void store8_bf16(__nv_bfloat16* p, const float (&v)[8
 // ---------------------------------------------------------------- embedding
 __global__ void embedding_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids,
                                  __nv_bfloat16* __restrict__ out, int d, int vocab, float scale) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -93,6 +95,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                __nv_bfloat16* __restrict__ y_bf16, uint8_t* __restrict__ y_fp8, float* __restrict__ y_scale,
                int ld_scale, int d, float eps, int offset_one) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float row[];  // d floats
   __shared__ float red[8];
   const int r = blockIdx.x;
@@ -147,6 +151,8 @@ template <bool kQuant>
 __global__ void __launch_bounds__(256)
 gated_act_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ y_bf16,
                  uint8_t* __restrict__ y_fp8, float* __restrict__ y_scale, int ld_scale, int inter, int act) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   // All lanes of a 16-lane group run the quantisation shuffle; out-of-range lanes contribute zeros.
@@ -176,6 +182,8 @@ gated_act_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict
 __global__ void __launch_bounds__(256)
 quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, float* __restrict__ scale,
                  int ld_scale, int k) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   float v[8];
@@ -213,6 +221,8 @@ struct RopeKvParams {
 };
 
 __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams p) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int h = blockIdx.y;  // 0..hq-1 q, hq..hq+hkv-1 k, then v
   const int hd = p.hd;
@@ -271,6 +281,8 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
 //     4 broadcast_add (a[r, :] + b[:]), 5 copy
 __global__ void elementwise_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                                    __nv_bfloat16* __restrict__ y, long long n, int d, int op, float s) {
+  pdl_wait();
+  pdl_trigger();
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float av = __bfloat162float(a[i]);
@@ -312,6 +324,8 @@ __device__ __forceinline__ void argmax_take(float& best, int& bi, float v, int i
 __global__ void __launch_bounds__(256)
 argmax_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out_idx, float* __restrict__ out_val,
               int n, int ld, int index_offset, int chunk, ArgmaxPartial* partials, int* counters) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int c0 = blockIdx.y * chunk;
   int c1 = c0 + chunk;
@@ -411,7 +425,7 @@ static inline int check_launch() { return cudaGetLastError() == cudaSuccess ? SL
 SLLM_EXPORT int sllm_embedding(const void* table, const int* ids, void* out, int tokens, int d, int vocab,
                                float scale, void* stream) {
   if (!table || !ids || !out || tokens <= 0 || d <= 0 || (d % 8)) return SLLM_ERR_INVALID_ARGUMENT;
-  embedding_kernel<<<tokens, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(embedding_kernel, dim3(tokens), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u, 
       static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), d, vocab, scale);
   return check_launch();
 }
@@ -429,7 +443,7 @@ SLLM_EXPORT int sllm_rmsnorm(const void* x, const void* w, void* y_bf16, void* y
       cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
       cfg = true;
     }
-    rmsnorm_kernel<true><<<rows, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
+    launch_kernel(rmsnorm_kernel<true>, dim3(rows), dim3(256), smem, st, 1u, static_cast<const __nv_bfloat16*>(x),
                                                   static_cast<const __nv_bfloat16*>(w), nullptr,
                                                   static_cast<uint8_t*>(y_fp8), y_scale, ld_scale, d, eps, offset_one);
   } else {
@@ -439,7 +453,7 @@ SLLM_EXPORT int sllm_rmsnorm(const void* x, const void* w, void* y_bf16, void* y
       cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
       cfg = true;
     }
-    rmsnorm_kernel<false><<<rows, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x),
+    launch_kernel(rmsnorm_kernel<false>, dim3(rows), dim3(256), smem, st, 1u, static_cast<const __nv_bfloat16*>(x),
                                                    static_cast<const __nv_bfloat16*>(w),
                                                    static_cast<__nv_bfloat16*>(y_bf16), nullptr, nullptr, 0, d, eps,
                                                    offset_one);
@@ -454,11 +468,11 @@ SLLM_EXPORT int sllm_gated_act(const void* in, void* y_bf16, void* y_fp8, float*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (y_fp8) {
     if (!y_scale) return SLLM_ERR_INVALID_ARGUMENT;
-    gated_act_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), nullptr,
+    launch_kernel(gated_act_kernel<true>, dim3(grid), dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(in), nullptr,
                                                  static_cast<uint8_t*>(y_fp8), y_scale, ld_scale, inter, act);
   } else {
     if (!y_bf16) return SLLM_ERR_INVALID_ARGUMENT;
-    gated_act_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in),
+    launch_kernel(gated_act_kernel<false>, dim3(grid), dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(in),
                                                   static_cast<__nv_bfloat16*>(y_bf16), nullptr, nullptr, 0, inter, act);
   }
   return check_launch();
@@ -468,7 +482,7 @@ SLLM_EXPORT int sllm_quant_fp8_1x128(const void* x, void* y, float* scale, int l
                                      void* stream) {
   if (!x || !y || !scale || rows <= 0 || k <= 0 || (k % 8)) return SLLM_ERR_INVALID_ARGUMENT;
   dim3 grid(rows, (k / 8 + 255) / 256);
-  quant_fp8_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(quant_fp8_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), 1u, 
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(y), scale, ld_scale, k);
   return check_launch();
 }
@@ -489,7 +503,7 @@ SLLM_EXPORT int sllm_rope_kv_append(void* qkv, const int* positions, const int* 
   p.hq = hq; p.hkv = hkv; p.hd = hd; p.rotary_dim = rotary_dim; p.page_size = page_size; p.kv_fp8 = kv_fp8;
   p.theta = theta; p.k_static_scale = k_static_scale; p.v_static_scale = v_static_scale; p.inv_freq = inv_freq;
   dim3 grid(tokens, hq + 2 * hkv);
-  rope_kv_append_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  launch_kernel(rope_kv_append_kernel, dim3(grid), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u, p);
   return check_launch();
 }
 
@@ -498,7 +512,7 @@ SLLM_EXPORT int sllm_elementwise(const void* a, const void* b, void* y, long lon
   if (!a || !y || n <= 0) return SLLM_ERR_INVALID_ARGUMENT;
   if ((op == 0 || op == 2 || op == 4) && !b) return SLLM_ERR_INVALID_ARGUMENT;
   const int blocks = static_cast<int>((n + 255) / 256);
-  elementwise_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(elementwise_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), 1u, 
       static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(y), n,
       d > 0 ? d : 1, op, s);
   return check_launch();
@@ -519,7 +533,7 @@ SLLM_EXPORT int sllm_argmax(const void* logits, int* out_idx, float* out_val, in
   chunk = (chunk + 7) & ~7;
   chunks = (n + chunk - 1) / chunk;
   dim3 grid(rows, chunks);
-  argmax_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_kernel(argmax_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), 1u, 
       static_cast<const __nv_bfloat16*>(logits), out_idx, out_val, n, ld, index_offset, chunk,
       static_cast<ArgmaxPartial*>(ws), counters);
   return check_launch();

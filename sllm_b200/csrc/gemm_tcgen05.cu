@@ -67,6 +67,7 @@ struct GemmParams {
   int ld_sa, ld_sb;    // leading dimensions of the kb-major scale arrays
   int epilogue;        // 0 = store, 1 = add residual
   int cluster_split;   // 1: gridDim.z CTAs form one cluster and reduce split-K partials over DSMEM
+  int const_operand;   // operand that no kernel writes (weights): 0 none, 1 A, 2 B; loaded before the PDL wait
   const float* scale_a;  // [num_kb, ld_sa]
   const float* scale_b;  // [num_kb, ld_sb]
   __nv_bfloat16* y;
@@ -212,17 +213,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int issued = 0;
-      for (int i = 0; i < nkb; ++i) {
+      // The constant operand (the weights) of the first ring of stages is requested before waiting for
+      // the previous kernel, so its HBM latency overlaps that kernel's tail; the dependent operand
+      // (activations) follows after the wait.
+      const int pre = nkb < p.stages ? nkb : p.stages;
+      auto load_a = [&](int i, int s) {
+        tma_load_2d(smem + s * kStageBytes, &tm_a, &bars->full[s], (kb0 + i) * kElemsPerBox, a_tile * kTileA);
+      };
+      auto load_b = [&](int i, int s) {
+        tma_load_2d(smem + s * kStageBytes + kABytes, &tm_b, &bars->full[s], (kb0 + i) * kElemsPerBox, b_tile * BN);
+      };
+      if (p.const_operand != 0) {
+        for (int i = 0; i < pre; ++i) {
+          mbar_expect_tx(&bars->full[i], kStageBytes);
+          if (p.const_operand == 1) load_a(i, i); else load_b(i, i);
+        }
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+        if (p.const_operand == 0) {
+          mbar_expect_tx(&bars->full[i], kStageBytes);
+          load_a(i, i);
+          load_b(i, i);
+        } else if (p.const_operand == 1) {
+          load_b(i, i);
+        } else {
+          load_a(i, i);
+        }
+        issued = i + 1;
+      }
+      for (int i = pre; i < nkb; ++i) {
         const int s = i % p.stages;
         const uint32_t ph = (i / p.stages) & 1;
         if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY)) break;
         mbar_expect_tx(&bars->full[s], kStageBytes);
-        uint8_t* sa = smem + s * kStageBytes;
-        const int x = (kb0 + i) * kElemsPerBox;
-        tma_load_2d(sa, &tm_a, &bars->full[s], x, a_tile * kTileA);
-        tma_load_2d(sa + kABytes, &tm_b, &bars->full[s], x, b_tile * BN);
+        load_a(i, s);
+        load_b(i, s);
         issued = i + 1;
       }
+      pdl_trigger();
       // Drain: every copy this thread started must have landed before the CTA may exit.  On the
       // normal path these phases are already complete and the waits return at once.
       for (int s = 0; s < p.stages; ++s) {
@@ -269,6 +298,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
   } else {
     // ------------------------------------------------------------ epilogue main loop (128 threads)
+    pdl_wait();
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
     for (int c = 0; c < BN; ++c) acc[c] = 0.f;
@@ -651,12 +681,6 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       return SLLM_ERR_CUDA;
     configured = smem;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
   GemmParams pp = p;
   if (pp.cluster_split) {
     // Validate this cluster shape once per (instantiation, size); fall back to the global fix-up
@@ -687,15 +711,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       if (!pp.ws || !pp.counters) return SLLM_ERR_WORKSPACE_TOO_SMALL;
     }
   }
-  if (pp.cluster_split) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = grid.z;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-  }
-  if (cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, kScaled, kComm>, ta, tb, pp) != cudaSuccess) {
+  if (launch_kernel(gemm_tcgen05_kernel<BN, kScaled, kComm>, grid, dim3(kGemmThreads), smem, stream,
+                    pp.cluster_split ? grid.z : 1u, ta, tb, pp) != cudaSuccess) {
     cudaGetLastError();
     return SLLM_ERR_CUDA;
   }
@@ -784,6 +801,7 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
   // transposed, at least 8 columns otherwise)
   const bool pow2 = splits == 2 || splits == 4 || splits == 8;
   p.cluster_split = (pow2 && bn % splits == 0 && (transpose_out || bn / splits >= 8) && !g_disable_cluster_split) ? 1 : 0;
+  p.const_operand = transpose_out ? 1 : 2;   // swap-AB: A is the weight matrix, else B is
   p.scale_a = scale_a; p.scale_b = scale_b;
   p.y = static_cast<__nv_bfloat16*>(y);
   p.residual = static_cast<const __nv_bfloat16*>(residual);

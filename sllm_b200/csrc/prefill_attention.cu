@@ -64,6 +64,8 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128_mn(uint32_t smem_addr, 
 
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const PrefillParams p) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // layout: Q (2 chunks) | P (2 chunks) | 2 stages x { K (2 chunks) | V (2 chunks) } | barriers
@@ -332,6 +334,6 @@ SLLM_EXPORT int sllm_prefill_attention(const void* qkv, int total_tokens, int qk
     cfg = true;
   }
   dim3 grid(num_tiles, hq);
-  prefill_attention_kernel<<<grid, kPfThreads, smem, static_cast<cudaStream_t>(stream)>>>(tm, p);
+  launch_kernel(prefill_attention_kernel, dim3(grid), dim3(kPfThreads), smem, static_cast<cudaStream_t>(stream), 1u, tm, p);
   return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
