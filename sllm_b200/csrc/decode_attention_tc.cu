@@ -38,7 +38,7 @@ struct __align__(8) DecodeTcBarriers {
   uint64_t kv_empty[kDaStages];
   uint64_t s_full[2];
   uint64_t p_ready;
-  uint64_t o_full;
+  uint64_t o_full[2];
   uint32_t tmem_base;
   int abort_flag;
   int is_last;
@@ -80,7 +80,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
   float* m_s = reinterpret_cast<float*>(bars + 1);  // [G]
   float* l_s = m_s + kDaHeadsPad;                   // [G]
   float* o_s = l_s + kDaHeadsPad;                   // [G][128]
-  constexpr uint32_t kTmemCols = 64;  // S buffers at columns 0 and 16, PV at column 32
+  constexpr uint32_t kTmemCols = 64;  // S buffers at columns 0 and 16, PV buffers at columns 32 and 48
 
   const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -107,7 +107,8 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->p_ready, 128);
-    mbar_init(&bars->o_full, 1);
+    mbar_init(&bars->o_full[0], 1);
+    mbar_init(&bars->o_full[1], 1);
     bars->abort_flag = 0;
     bars->is_last = 0;
     mbar_fence_init();
@@ -188,9 +189,9 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         const uint32_t v_addr = smem_u32(kv_s + (j % kDaStages) * 2 * kDaTileBytes + kDaTileBytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // 32 keys per MMA
-          umma_f8(tmem_base + 32, make_smem_desc_sw128_mn8(v_addr + k * 4096), make_smem_desc_sw128(p_addr) + 2 * k,
-                  idesc_pv, k != 0);
-        tc_commit(&bars->o_full);
+          umma_f8(tmem_base + 32 + (j & 1) * 16, make_smem_desc_sw128_mn8(v_addr + k * 4096),
+                  make_smem_desc_sw128(p_addr) + 2 * k, idesc_pv, k != 0);
+        tc_commit(&bars->o_full[j & 1]);
         tc_commit(&bars->kv_empty[j % kDaStages]);
       }
     }
@@ -220,12 +221,14 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     fence_proxy_async_smem();
     if (nt > 0) asm volatile("bar.sync 2, 160;" ::: "memory");
 
-    float m[G], l[G], o[G];
+    float m[G], l[G], o[G], alpha_prev[G];
+    float of_prev = 0.f;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       m[g] = -INFINITY;
       l[g] = 0.f;
       o[g] = 0.f;
+      alpha_prev[g] = 0.f;
     }
     const int* bt = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
     bool ok = true;
@@ -285,18 +288,36 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars->p_ready);
-      // ---- fold P.V of this tile into the output (thread = channel)
-      ok = mbar_wait(&bars->o_full, j & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
-      if (!ok) break;
-      tc_fence_after();
-      tmem_ld16(lane_addr + 32, raw);
-      tmem_wait_ld();
-      const float of = vmax / 256.f;
+      // ---- fold P.V of the PREVIOUS tile into the output (thread = channel) while the tensor core
+      // works on this tile: O <- O * alpha_{j-1} + PV_{j-1} * factor_{j-1}
+      if (j > 0) {
+        ok = mbar_wait(&bars->o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld16(lane_addr + 32 + ((j - 1) & 1) * 16, raw);
+        tmem_wait_ld();
 #pragma unroll
-      for (int g = 0; g < G; ++g) o[g] = fmaf(o[g], alpha[g], __uint_as_float(raw[g]) * of);
-      tc_fence_before();
+        for (int g = 0; g < G; ++g) o[g] = fmaf(o[g], alpha_prev[g], __uint_as_float(raw[g]) * of_prev);
+        tc_fence_before();
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) alpha_prev[g] = alpha[g];
+      of_prev = vmax / 256.f;
       // red[] is rewritten by the next tile only after all 128 threads arrived on p_ready, i.e. after
       // every read of this tile's maxima.
+    }
+    if (ok && nt > 0) {
+      const int j = nt - 1;
+      ok = mbar_wait(&bars->o_full[j & 1], (j >> 1) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
+      if (ok) {
+        uint32_t raw[16];
+        tc_fence_after();
+        tmem_ld16(lane_addr + 32 + (j & 1) * 16, raw);
+        tmem_wait_ld();
+#pragma unroll
+        for (int g = 0; g < G; ++g) o[g] = fmaf(o[g], alpha_prev[g], __uint_as_float(raw[g]) * of_prev);
+        tc_fence_before();
+      }
     }
 
     // ---- hand the split's state to the common tail: l is a per-thread partial over keys -> reduce

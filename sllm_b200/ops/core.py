@@ -406,7 +406,8 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
     if use_tc:
         mk = max_kv if max_kv > 0 else block_table.shape[1] * kv.page_size
         ctas = r * hkv
-        splits = max(1, min((3 * _SM_COUNT + ctas - 1) // ctas, (mk + 255) // 256, 64)) if ctas < 3 * _SM_COUNT else 1
+        # one wave of 2 CTAs per SM; a split keeps at least one 128-key tile
+        splits = max(1, min((2 * _SM_COUNT) // ctas, (mk + 127) // 128, 64)) if ctas < 2 * _SM_COUNT else 1
         rc = lib.sllm_decode_attention_tc(
             _p(q), q.stride(0), _p(kv.k), _p(kv.v), _p(kv.k_scale), _p(kv.v_scale), kv.k_static, kv.v_static,
             _p(block_table), block_table.stride(0), _p(seq_index), _p(kv_lens), r, hq, hkv, kv.k.shape[0],
