@@ -1,0 +1,227 @@
+// On-device token selection: temperature, additive logits (bias / penalties prepared on the host),
+// validity mask (grammar / EOS policy), top-k, min-p, top-p and a categorical draw, one CTA per row,
+// every step parallel over the vocabulary.
+//
+// Order and rules follow the host sampler chain (engine/sampling.py): scaled = (logit + additive) / T
+// over valid tokens; candidates ordered by scaled value descending with ties to the lower id; top-k
+// keeps k candidates; min-p keeps p_i >= min_p * p_max; top-p keeps the shortest prefix whose mass
+// reaches top_p; the draw u comes from SplitMix64 with state seed + (counter + 1) * gamma, taking the
+// top 53 bits, and selects the first candidate (in that order) whose cumulative mass exceeds
+// u * retained mass.  Instead of sorting, cut-offs are found by bisection over the order-preserving
+// integer image of the fp32 scores (32 passes over probabilities staged in a workspace).
+// Output record per row (16 bytes): {int32 token, int32 status, float logprob, float reserved};
+// status 0 = ok, 1 = NaN logit, 2 = empty distribution.
+//
+// Replaces the reference's single-thread selector (token_selector_kernel.hip.cpp:240-296), keeping
+// its RNG contract and record layout.
+#include "common.cuh"
+#include "api.h"
+
+namespace sllm {
+
+struct SelectorRow {
+  float temperature;
+  float top_p;
+  float min_p;
+  int top_k;                    // 0 = off
+  unsigned long long seed;
+  unsigned long long counter;
+};
+
+struct SelectorRecord {
+  int token;
+  int status;
+  float logprob;
+  float reserved;
+};
+
+__device__ __forceinline__ uint32_t ordered_key(float f) {
+  const uint32_t b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long splitmix64_at(unsigned long long seed, unsigned long long counter) {
+  unsigned long long v = seed + (counter + 1ull) * 0x9e3779b97f4a7c15ull;
+  v = (v ^ (v >> 30)) * 0xbf58476d1ce4e5b9ull;
+  v = (v ^ (v >> 27)) * 0x94d049bb133111ebull;
+  return v ^ (v >> 31);
+}
+
+template <typename T>
+__device__ __forceinline__ T block_reduce(T v, T* scratch, bool is_max) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const T other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? (other > v ? other : v) : v + other;
+  }
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  T r = scratch[0];
+  for (int w = 1; w < (blockDim.x >> 5); ++w) r = is_max ? (scratch[w] > r ? scratch[w] : r) : r + scratch[w];
+  return r;
+}
+
+// mass and count of candidates with key >= k (probabilities in prob[], keys recomputed from scores)
+__device__ __forceinline__ void mass_at_or_above(const float* score, const float* prob, int n, uint32_t k,
+                                                 double* scratch_d, int* scratch_i, double& mass, int& count) {
+  double m = 0.0;
+  int c = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float p = prob[i];
+    if (p > 0.f && ordered_key(score[i]) >= k) {
+      m += p;
+      ++c;
+    }
+  }
+  mass = block_reduce<double>(m, scratch_d, false);
+  count = block_reduce<int>(c, scratch_i, false);
+}
+
+__global__ void __launch_bounds__(1024)
+token_select_kernel(const __nv_bfloat16* __restrict__ logits, int ld, const float* __restrict__ additive,
+                    const uint8_t* __restrict__ mask, const SelectorRow* __restrict__ rows, int n,
+                    float* __restrict__ ws, SelectorRecord* __restrict__ out) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  const SelectorRow cfg = rows[r];
+  const __nv_bfloat16* lg = logits + static_cast<size_t>(r) * ld;
+  const float* add = additive ? additive + static_cast<size_t>(r) * n : nullptr;
+  const uint8_t* mk = mask ? mask + static_cast<size_t>(r) * n : nullptr;
+  float* score = ws + static_cast<size_t>(r) * 2 * n;   // scaled scores (-inf when invalid)
+  float* prob = score + n;                              // exp(score - max)
+  __shared__ double sd[32];
+  __shared__ float sf[32];
+  __shared__ int si[32];
+  __shared__ int s_nan;
+  if (threadIdx.x == 0) s_nan = 0;
+  __syncthreads();
+
+  const float inv_t = 1.f / cfg.temperature;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = __bfloat162float(lg[i]);
+    if (add) v += add[i];
+    if (v != v) s_nan = 1;
+    float s = v * inv_t;
+    if (mk && !mk[i]) s = -INFINITY;
+    score[i] = s;
+    mx = fmaxf(mx, s);
+  }
+  mx = block_reduce<float>(mx, sf, true);
+  if (s_nan || mx == -INFINITY) {
+    if (threadIdx.x == 0) {
+      SelectorRecord rec;
+      rec.token = -1; rec.status = s_nan ? 1 : 2; rec.logprob = 0.f; rec.reserved = 0.f;
+      out[r] = rec;
+    }
+    return;
+  }
+  double tot = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float s = score[i];
+    const float p = (s == -INFINITY) ? 0.f : expf(s - mx);
+    prob[i] = p;
+    tot += p;
+  }
+  const double total = block_reduce<double>(tot, sd, false);
+  __syncthreads();
+
+  // ---- cut-off key: the smallest key that every retained candidate satisfies
+  uint32_t cut = 0;  // keep everything
+  if (cfg.min_p > 0.f) {
+    const float thr = mx + logf(cfg.min_p);   // p_i / p_max >= min_p
+    cut = max(cut, ordered_key(thr));
+  }
+  if (cfg.top_k > 0 || cfg.top_p < 1.f) {
+    // bisection for the largest key K with count(key >= K) >= top_k (resp. mass >= top_p * total)
+    for (int which = 0; which < 2; ++which) {
+      if (which == 0 && cfg.top_k <= 0) continue;
+      if (which == 1 && !(cfg.top_p < 1.f)) continue;
+      uint32_t lo = 0, hi = 0xffffffffu;   // invariant: predicate(lo) true, predicate(hi + 1) false
+      while (lo < hi) {
+        const uint32_t mid = lo + ((hi - lo) >> 1) + 1;
+        double m;
+        int c;
+        mass_at_or_above(score, prob, n, max(mid, cut), sd, si, m, c);
+        const bool ok = which == 0 ? (c >= cfg.top_k) : (m >= static_cast<double>(cfg.top_p) * total);
+        if (ok) lo = mid; else hi = mid - 1;
+      }
+      // top-k with ties at the boundary keeps all tied candidates here; the draw below honours the
+      // id order inside the tie, and the retained mass is trimmed to exactly k candidates' worth.
+      cut = max(cut, lo);
+    }
+  }
+  double kept_mass;
+  int kept_count;
+  mass_at_or_above(score, prob, n, cut, sd, si, kept_mass, kept_count);
+  if (!(kept_mass > 0.0)) {
+    if (threadIdx.x == 0) {
+      SelectorRecord rec;
+      rec.token = -1; rec.status = 2; rec.logprob = 0.f; rec.reserved = 0.f;
+      out[r] = rec;
+    }
+    return;
+  }
+  // ---- draw: first candidate in (score desc, id asc) order whose cumulative mass exceeds u * kept
+  const unsigned long long bits = splitmix64_at(cfg.seed, cfg.counter);
+  const double u = static_cast<double>(bits >> 11) * (1.0 / 9007199254740992.0);
+  const double target = u * kept_mass;
+  // bisection for the largest key K with mass(key >= K, within kept) > target ... the selected
+  // candidate has key K; mass strictly above K is <= target.
+  uint32_t lo = cut, hi = 0xffffffffu;
+  while (lo < hi) {
+    const uint32_t mid = lo + ((hi - lo) >> 1) + 1;
+    double m;
+    int c;
+    mass_at_or_above(score, prob, n, mid, sd, si, m, c);
+    if (m > target) lo = mid; else hi = mid - 1;
+  }
+  const uint32_t sel_key = lo;
+  double above = 0.0;
+  int dummy;
+  if (sel_key != 0xffffffffu) mass_at_or_above(score, prob, n, sel_key + 1, sd, si, above, dummy);
+  // among ties with key == sel_key walk ids in ascending order (ties are rare: serial by one thread)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double cum = above;
+    int chosen = -1, last = -1;
+    for (int i = 0; i < n; ++i) {
+      if (prob[i] > 0.f && ordered_key(score[i]) == sel_key) {
+        last = i;
+        cum += prob[i];
+        if (target < cum) {
+          chosen = i;
+          break;
+        }
+      }
+    }
+    if (chosen < 0) chosen = last;
+    SelectorRecord rec;
+    rec.token = chosen;
+    rec.status = chosen >= 0 ? 0 : 2;
+    rec.logprob = chosen >= 0 ? static_cast<float>(static_cast<double>(score[chosen] - mx) - log(total)) : 0.f;
+    rec.reserved = 0.f;
+    out[r] = rec;
+  }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+// rows_cfg: device array of {float temperature, top_p, min_p; int top_k; u64 seed, counter} (32 bytes).
+// ws: 2 * rows * n floats.  out: rows records of 16 bytes.
+SLLM_EXPORT int sllm_token_select(const void* logits, int ld, const float* additive, const unsigned char* mask,
+                                  const void* rows_cfg, int rows, int n, float* ws, long long ws_floats, void* out,
+                                  void* stream) {
+  if (!logits || !rows_cfg || !ws || !out || rows <= 0 || n <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  if (ws_floats < 2LL * rows * n) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+  static_assert(sizeof(SelectorRow) == 32, "selector row layout");
+  static_assert(sizeof(SelectorRecord) == 16, "selector record layout");
+  cudaError_t e = launch_kernel(token_select_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), 1u,
+                                static_cast<const __nv_bfloat16*>(logits), ld, additive, mask,
+                                static_cast<const SelectorRow*>(rows_cfg), n, ws, static_cast<SelectorRecord*>(out));
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}

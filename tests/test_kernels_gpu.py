@@ -273,3 +273,34 @@ def test_prefill_attention_tcgen05(lens, hq, hkv):
     deq = ref.dequant_fp8_1x128(outq.data.cpu(), outq.scale.cpu())
     assert rel_err(deq, want) < 4e-2
     _status_ok()
+
+
+def test_device_token_selector():
+    """Device selector vs its host mirror: same stage order, same SplitMix64 draw."""
+    import numpy as np
+    from sllm_b200.engine import sampling as S
+    torch.manual_seed(11)
+    rows, v = 6, 32000
+    lg = (torch.randn(rows, v, device=DEV) * 2).bfloat16()
+    add = torch.zeros(rows, v, device=DEV)
+    add[1, 5] = 30.0
+    mask = torch.ones(rows, v, device=DEV, dtype=torch.uint8)
+    mask[2, :v // 2] = 0
+    cfg = [(0.8, 0.9, 0.0, 0, 42, 0), (1.0, 1.0, 0.0, 0, 42, 1), (0.7, 0.95, 0.0, 50, 7, 2), (1.5, 1.0, 0.05, 0, 7, 3),
+           (1.0, 0.5, 0.0, 20, 9, 4), (0.3, 1.0, 0.0, 1, 9, 5)]
+    out = S.device_select(lg, cfg, add, mask).cpu().numpy().view(S.SELECTOR_RECORD_DTYPE).reshape(rows)
+    lgh, addh, mh = lg.float().cpu().numpy(), add.cpu().numpy(), mask.cpu().numpy()
+    agree = 0
+    for r in range(rows):
+        tok, status, lp = S.reference_select(lgh[r], cfg[r], addh[r], mh[r])
+        assert out["status"][r] == status == 0
+        assert mh[r][out["token"][r]] == 1
+        agree += int(out["token"][r] == tok)
+        if out["token"][r] == tok:
+            assert abs(out["logprob"][r] - lp) < 2e-2
+    assert out["token"][1] == 5 and out["token"][5] == int(np.argmax(lgh[5]))
+    assert agree >= rows - 1   # fp32 vs fp64 accumulation may move a draw across one boundary
+    bad = lg.clone()
+    bad[0, 3] = float("nan")
+    rec = S.device_select(bad[:1], cfg[:1]).cpu().numpy().view(S.SELECTOR_RECORD_DTYPE)
+    assert rec["status"][0] == 1 and rec["token"][0] == -1

@@ -1,0 +1,139 @@
+"""Sampler contract on CPU: parameter ranges, RNG stream, profile sampler golden cases, chain stages,
+snapshot / restore, and the host mirror of the device selector."""
+import math
+
+import numpy as np
+import pytest
+
+from sllm_b200.engine import sampling as S
+
+
+class FixedUniform:
+    def __init__(self, u):
+        self.u = u
+
+    def next_unit(self):
+        return self.u
+
+
+# Golden cases of the profile sampler (same numbers as the reference's
+# tests/fixtures/profile_sampling_cases.json, schema profile-sampling-cases-v1).
+GOLDEN = [
+    ([0.0, 1.0, -1.0, 0.5, 2.0, 0.25, -0.25], 0.7, 0.9, 0.0, 0.0, [], 0.5, 4),
+    ([0.0, 2.5, 1.0], 1.0, 1.0, 1.0, 1.0, [1, 1], 0.1, 2),
+    ([2.0, 2.0, 1.0], 1.0, 0.0, 0.0, 0.0, [], 0.9, 0),
+    ([-3.0, 0.0, 3.0, 1.0, -1.0], 2.0, 1.0, 0.0, 0.0, [], 0.73, 3),
+]
+
+
+@pytest.mark.parametrize("logits,t,top_p,pp,fp,hist,u,want", GOLDEN)
+def test_profile_sampler_golden(logits, t, top_p, pp, fp, hist, u, want):
+    s = S.ProfileSampler(S.SamplingParams(t, top_p, pp, fp), hist)
+    assert s.select(0, np.array(logits, dtype=np.float32), FixedUniform(u)) == want
+
+
+def test_parameter_ranges():
+    for bad in (dict(temperature=2.1), dict(temperature=-0.1), dict(top_p=1.5), dict(presence_penalty=3),
+                dict(frequency_penalty=-2.5), dict(temperature=float("nan"))):
+        with pytest.raises(S.SamplingError):
+            S.SamplingParams(**bad)
+    assert not S.SamplingParams().requires_logits
+
+
+def test_splitmix_stream_and_positional_draw():
+    r = S.SplitMix64(12345)
+    first = [r.next_unit() for _ in range(5)]
+    assert all(0.0 <= x < 1.0 for x in first)
+    assert first == [S.SplitMix64.unit_at(12345, i) for i in range(5)]
+    # published SplitMix64 vector: seed 0 -> first output 0xe220a8397b1dcdaf
+    assert S.SplitMix64(0).next_u64() == 0xE220A8397B1DCDAF
+    assert S.derive_choice_seed(7, 0) == 7 and S.derive_choice_seed(7, 1) != S.derive_choice_seed(7, 2)
+
+
+def test_greedy_never_touches_logits_or_rng():
+    s = S.ProfileSampler(S.SamplingParams())
+    assert s.select(17, None, None) == 17
+    with pytest.raises(S.SamplingError):
+        s.select(5, np.zeros(3, dtype=np.float32), None)
+
+
+def test_special_values():
+    s = S.ProfileSampler(S.SamplingParams(1.0))
+    with pytest.raises(S.SamplingError):
+        s.select(0, np.array([0.0, np.nan], dtype=np.float32), FixedUniform(0.1))
+    assert s.select(0, np.array([0.0, np.inf, 3.0, np.inf], dtype=np.float32), FixedUniform(0.6)) == 3
+    with pytest.raises(S.SamplingError):
+        s.select(0, np.array([-np.inf, -np.inf], dtype=np.float32), FixedUniform(0.1))
+
+
+def test_chain_stages():
+    lg = np.array([1.0, 3.0, 2.0, 0.5, 2.9], dtype=np.float32)
+    # top-k 1 is greedy whatever the draw
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(1.0), top_k=1), seed=1)
+    assert ch.select(lg).token == 1
+    # logit bias and the validity mask
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(0.0), logit_bias=[(3, 50.0)]), seed=1)
+    assert ch.select(lg).token == 3
+    mask = np.array([1, 0, 1, 1, 0], dtype=np.uint8)
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(0.0)), seed=1)
+    assert ch.select(lg, valid_mask=mask).token == 2
+    # ignore-eos removes the token
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(0.0), ignore_eos_token=1), seed=1)
+    assert ch.select(lg).token == 4
+    # repeat penalty pushes a repeated positive logit down
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(0.0), repeat_penalty=2.0), prior_tokens=[1], seed=1)
+    assert ch.select(lg).token == 4
+    # min-p keeps only tokens within a factor of the best
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(1.0), min_p=0.5), seed=3)
+    assert {ch.select(lg).token for _ in range(50)} <= {1, 4}
+    # logprobs
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(0.0), return_logprobs=True, top_logprobs=2), seed=1)
+    sel = ch.select(lg)
+    z = lg.astype(np.float64)
+    want = z - math.log(np.exp(z).sum())
+    assert sel.token == 1 and abs(sel.logprob - want[1]) < 1e-6
+    assert [t for t, _ in sel.top_logprobs] == [1, 4]
+    with pytest.raises(S.SamplingError):
+        S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(1.0), logit_bias=[(1, 200.0)]))
+
+
+def test_chain_distribution_and_snapshot():
+    lg = np.log(np.array([0.1, 0.2, 0.3, 0.4], dtype=np.float64)).astype(np.float32)
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(1.0)), seed=99)
+    draws = [ch.select(lg).token for _ in range(4000)]
+    freq = np.bincount(draws, minlength=4) / 4000
+    assert np.abs(freq - [0.1, 0.2, 0.3, 0.4]).max() < 0.03
+    ch.accept(2)
+    blob = ch.snapshot()
+    nxt = [ch.select(lg).token for _ in range(10)]
+    ch2 = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(1.0)), seed=5)
+    ch2.restore(blob)
+    assert [ch2.select(lg).token for _ in range(10)] == nxt
+    with pytest.raises(S.SamplingError):
+        ch2.restore(b"\x00\x00")
+
+
+def test_dry_and_mirostat_run():
+    lg = np.zeros(16, dtype=np.float32)
+    lg[5] = 4.0
+    hist = [1, 2, 3, 5, 9, 1, 2, 3]   # "1 2 3" was followed by 5 before: DRY penalises 5
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(0.0), dry=S.DryConfig(5.0, 1.75, 2)), prior_tokens=hist)
+    assert ch.select(lg).token != 5
+    ch = S.SamplerChain(S.SamplerChainConfig(S.SamplingParams(1.0), mirostat=S.MirostatConfig(2)), seed=4)
+    mu0 = ch.mu
+    toks = [ch.select(np.random.default_rng(0).normal(size=64).astype(np.float32)).token for _ in range(5)]
+    assert all(0 <= t < 64 for t in toks) and ch.mu != mu0
+
+
+def test_reference_selector_matches_profile_sampler_order():
+    rng = np.random.default_rng(7)
+    for trial in range(50):
+        lg = rng.normal(0, 2, 300).astype(np.float32)
+        row = (0.8, 0.9, 0.0, 0, 1000 + trial, 3)
+        tok, status, lp = S.reference_select(lg, row)
+        assert status == 0
+        s = S.ProfileSampler(S.SamplingParams(0.8, 0.9))
+        want = s.select(0, lg, FixedUniform(S.SplitMix64.unit_at(1000 + trial, 3)))
+        assert tok == want
+    assert S.reference_select(np.array([np.nan, 1.0], dtype=np.float32), (1.0, 1.0, 0.0, 0, 1, 0))[1] == 1
+    assert S.reference_select(np.zeros(4, dtype=np.float32), (1.0, 1.0, 0.0, 0, 1, 0), mask=np.zeros(4))[1] == 2
