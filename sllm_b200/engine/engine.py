@@ -86,6 +86,22 @@ class Engine:
         s.seq_id = self.cache.pool.new_seq()
         return s
 
+    def fork_sequence(self, src: Sequence, prompt: list, user=None) -> Sequence:
+        """New sequence for `prompt` that reuses the KV of the longest common computed prefix of `src`
+        (full pages shared by reference count, a partial last page copied).  At least one prompt token
+        is left to compute so that the prefill produces logits."""
+        limit = min(src.num_computed, len(prompt) - 1)
+        common = 0
+        while common < limit and src.tokens[common] == prompt[common]:
+            common += 1
+        s = Sequence(prompt=list(prompt), user=user)
+        if common == 0:
+            s.seq_id = self.cache.pool.new_seq()
+        else:
+            s.seq_id = self.cache.fork(src.seq_id, common)
+            s.num_computed = common
+        return s
+
     def free_sequence(self, s: Sequence) -> None:
         if s.seq_id > 0:
             self.cache.pool.free_seq(s.seq_id)

@@ -370,6 +370,11 @@ class SamplerChain:
         return (c.params.requires_logits and c.typical_p >= 1.0 and c.dynamic_temperature is None and c.dry is None
                 and c.xtc is None and c.mirostat is None and c.repeat_penalty == 1.0 and c.top_logprobs == 0)
 
+    def counts_matter(self) -> bool:
+        """True when token counts change the logits (legacy penalties configured)."""
+        p = self.cfg.params
+        return p.frequency_penalty != 0.0 or p.presence_penalty != 0.0
+
     def device_row(self) -> tuple:
         """(temperature, top_p, min_p, top_k, seed, counter) for the next draw; advances the counter."""
         c = self.cfg
