@@ -33,3 +33,16 @@ SLLM_HOST_EXPORT int sllm_kv_seq_pages(int h, int seq, int* out, int cap);
 SLLM_HOST_EXPORT int sllm_kv_seq_fork(int h, int seq, long long prefix_len, int* copy_pair);
 SLLM_HOST_EXPORT int sllm_kv_seq_make_tail_private(int h, int seq, int* copy_pair);
 SLLM_HOST_EXPORT int sllm_kv_fill_block_table(int h, const int* seqs, int n, int* table, int max_blocks);
+
+/* grammar.cpp */
+SLLM_HOST_EXPORT int sllm_grammar_create(const char* gbnf, const char* root, char* err, int err_cap);
+SLLM_HOST_EXPORT int sllm_grammar_destroy(int h);
+SLLM_HOST_EXPORT int sllm_grammar_set_vocab(int h, int n_tokens, const unsigned char* blob, const unsigned int* offsets);
+SLLM_HOST_EXPORT int sllm_grammar_state_new(int h);
+SLLM_HOST_EXPORT int sllm_grammar_state_clone(int s);
+SLLM_HOST_EXPORT int sllm_grammar_state_free(int s);
+SLLM_HOST_EXPORT int sllm_grammar_mask(int s, unsigned char* out_mask, int n);
+SLLM_HOST_EXPORT int sllm_grammar_accept(int s, int token);
+SLLM_HOST_EXPORT int sllm_grammar_accept_bytes(int s, const unsigned char* bytes, int n);
+SLLM_HOST_EXPORT int sllm_grammar_is_complete(int s);
+SLLM_HOST_EXPORT int sllm_grammar_stats(int h, long long* out3);
