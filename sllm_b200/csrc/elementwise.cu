@@ -11,6 +11,8 @@
 // matmul_kernel.hip.cpp:210-247 (activation quantisation), argmax_kernel.hip.cpp:37.
 #include "common.cuh"
 #include "api.h"
+#include "noalloc.h"
+#include <mutex>
 
 namespace sllm {
 
@@ -537,4 +539,65 @@ SLLM_EXPORT int sllm_argmax(const void* logits, int* out_idx, float* out_val, in
       static_cast<const __nv_bfloat16*>(logits), out_idx, out_val, n, ld, index_offset, chunk,
       static_cast<ArgmaxPartial*>(ws), counters);
   return check_launch();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Row argmax for callers that must not allocate (declared in noalloc.h).
+//
+// Same kernel and same results as sllm_argmax, but the partial records and the per-row arrival
+// counters live in a fixed array that is part of the loaded library image instead of a caller
+// workspace.  Capacity: kNoAllocMaxRows rows; the array occupies kNoAllocScratchBytes on every GPU
+// that loads the library, until the process exits.
+namespace sllm {
+constexpr int kNoAllocMaxRows = 256;
+constexpr int kNoAllocMaxChunks = 64;
+constexpr size_t kNoAllocPartialBytes = static_cast<size_t>(kNoAllocMaxRows) * kNoAllocMaxChunks * sizeof(ArgmaxPartial);
+constexpr size_t kNoAllocScratchBytes = kNoAllocPartialBytes + kNoAllocMaxRows * sizeof(int);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+}  // namespace sllm
+
+SLLM_EXPORT int sllm_argmax_noalloc_max_rows(void) { return kNoAllocMaxRows; }
+
+SLLM_EXPORT int sllm_argmax_noalloc(const void* logits, int* out_idx, float* out_val, int rows, int n, int ld,
+                                    int index_offset, void* stream) {
+  if (!logits || !out_idx || rows <= 0 || n <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  if (rows > kNoAllocMaxRows) return SLLM_ERR_LIMIT;   // larger batches must use sllm_argmax with a workspace
+  // The array's name is only a host-side handle; the kernel needs its device address, which is looked
+  // up once per device (with that device current) and remembered.
+  constexpr int kMaxDevices = 64;
+  static void* scratch_ptr[kMaxDevices] = {nullptr};
+  static std::mutex setup_mutex;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SLLM_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(setup_mutex);
+    if (!scratch_ptr[dev]) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) {
+        cudaGetLastError();
+        return SLLM_ERR_CUDA;
+      }
+      // counters must start at zero; the kernel leaves them zero after every launch
+      if (cudaMemsetAsync(static_cast<unsigned char*>(p) + kNoAllocPartialBytes, 0, kNoAllocMaxRows * sizeof(int), st) !=
+          cudaSuccess)
+        return SLLM_ERR_CUDA;
+      scratch_ptr[dev] = p;
+    }
+    base = scratch_ptr[dev];
+  }
+  int chunks = (2 * 148 + rows - 1) / rows;
+  const int max_chunks = (n + 2047) / 2048;
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks > kNoAllocMaxChunks) chunks = kNoAllocMaxChunks;
+  if (chunks < 1) chunks = 1;
+  int chunk = (n + chunks - 1) / chunks;
+  chunk = (chunk + 7) & ~7;
+  chunks = (n + chunk - 1) / chunk;
+  dim3 grid(rows, chunks);
+  cudaError_t e = launch_kernel(argmax_kernel, grid, dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(logits),
+                                out_idx, out_val, n, ld, index_offset, chunk, static_cast<ArgmaxPartial*>(base),
+                                reinterpret_cast<int*>(static_cast<unsigned char*>(base) + kNoAllocPartialBytes));
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
