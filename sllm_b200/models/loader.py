@@ -1,0 +1,187 @@
+"""GGUF <-> resident weights for the dense decoder family.
+
+Export writes one GGUF with llama.cpp-style tensor names (`token_embd.weight`, `blk.N.attn_q.weight`, ...),
+the model configuration, tokenizer and chat template in metadata, FP8 planes as I8 carriers bound to their
+FP32 1x128 scale tensors through the tensor recipe, and returns the derived lock.  Load verifies the file
+against the lock, uploads each tensor through the pinned staging chunk, shards it for this tensor-parallel
+rank, concatenates q|k|v and gate|up, and transposes FP8 scales once into the layout the GEMM epilogue reads.
+(Reference: QwenResidentModel::new_gguf, crates/sllm-core/src/qwen_execution.rs:960-1194, resident upload
+crates/sllm-core/src/weights.rs:21; converter crates/sllm-core/src/gguf_convert.rs.)
+"""
+from __future__ import annotations
+
+import json
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..formats import gguf as G
+from ..ops.core import LinearWeight
+from .config import ModelConfig
+from .llama import LayerWeights, LlamaWeights
+
+CONVERTER_ID = "sllm-b200-convert-gguf-v1"
+FP8_ENCODING = "fp8-e4m3fn-kblock128-f32-scale"
+
+
+def _bf16_bytes(t: torch.Tensor) -> bytes:
+    return t.detach().to(torch.bfloat16).contiguous().cpu().view(torch.int16).numpy().tobytes()
+
+
+def _f32_bytes(t: torch.Tensor) -> bytes:
+    return t.detach().to(torch.float32).contiguous().cpu().numpy().tobytes()
+
+
+def _u8_bytes(t: torch.Tensor) -> bytes:
+    return t.detach().contiguous().cpu().view(torch.uint8).numpy().tobytes()
+
+
+def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_json: Optional[str] = None,
+                      chat_template: Optional[str] = None, source_fingerprints: tuple = (),
+                      converter_args: Optional[dict] = None) -> dict:
+    """Writes unsharded (tensor-parallel size 1) weights; returns the derived lock document."""
+    tensors, bindings = [], []
+    dense_t = G.T_F32 if cfg.weight_format == "fp32" else G.T_BF16
+    dense_b = _f32_bytes if cfg.weight_format == "fp32" else _bf16_bytes
+
+    def add_dense(name, t):
+        tensors.append((name, tuple(t.shape), dense_t, dense_b(t)))
+
+    def add_linear(name, lw: LinearWeight, r0: int, r1: int):
+        if lw.kind == "fp8":
+            val = lw.w[r0:r1]
+            sc = lw.scale_t[:, r0:r1].t().contiguous()          # file layout [N, ceil(K/128)]
+            tensors.append((name, tuple(val.shape), G.T_I8, _u8_bytes(val)))
+            tensors.append((name + ".scale", tuple(sc.shape), G.T_F32, _f32_bytes(sc)))
+            bindings.append({"logical_tensor": name, "value_tensor": name, "encoding": FP8_ENCODING, "role": "weight",
+                             "logical_shape": list(val.shape), "scope": "consumed",
+                             "scales": [{"role": "block", "tensor": name + ".scale"}]})
+        else:
+            add_dense(name, lw.w[r0:r1])
+
+    add_dense("token_embd.weight", w.embed)
+    q, kv, f = cfg.q_size, cfg.kv_size, cfg.ffn
+    for i, l in enumerate(w.layers):
+        p = f"blk.{i}."
+        add_dense(p + "attn_norm.weight", l.attn_norm)
+        add_linear(p + "attn_q.weight", l.qkv, 0, q)
+        add_linear(p + "attn_k.weight", l.qkv, q, q + kv)
+        add_linear(p + "attn_v.weight", l.qkv, q + kv, q + 2 * kv)
+        add_linear(p + "attn_output.weight", l.o, 0, cfg.d_model)
+        add_dense(p + "ffn_norm.weight", l.mlp_norm)
+        add_linear(p + "ffn_gate.weight", l.gate_up, 0, f)
+        add_linear(p + "ffn_up.weight", l.gate_up, f, 2 * f)
+        add_linear(p + "ffn_down.weight", l.down, 0, cfg.d_model)
+    add_dense("output_norm.weight", w.final_norm)
+    if not cfg.tie_embeddings:
+        add_linear("output.weight", w.lm_head, 0, cfg.vocab)
+    md = {"general.architecture": "llama", "general.name": cfg.name,
+          "llama.block_count": cfg.n_layers, "llama.embedding_length": cfg.d_model,
+          "llama.attention.head_count": cfg.n_heads, "llama.attention.head_count_kv": cfg.n_kv_heads,
+          "llama.feed_forward_length": cfg.ffn, "llama.context_length": cfg.max_context,
+          "llama.rope.freq_base": float(cfg.rope_theta), "llama.attention.layer_norm_rms_epsilon": float(cfg.rms_eps),
+          G.FRONTEND_CONFIG_KEY: json.dumps(cfg.to_dict(), sort_keys=True)}
+    if tokenizer_json is not None:
+        md[G.FRONTEND_TOKENIZER_KEY] = tokenizer_json
+    if chat_template is not None:
+        md["tokenizer.chat_template"] = chat_template
+    md.update(G.recipe_metadata(bindings))
+    digests = G.write_gguf(path, md, tensors)
+    return G.make_derived_lock(path, digests, f"{cfg.name}:{cfg.weight_format}", list(source_fingerprints),
+                               {"id": CONVERTER_ID, "args": converter_args or {}})
+
+
+def config_from_gguf(g: G.GgufFile) -> ModelConfig:
+    raw = g.metadata.get(G.FRONTEND_CONFIG_KEY)
+    if raw is None:
+        raise G.GgufError("the GGUF file carries no model configuration")
+    d = json.loads(raw)
+    known = set(ModelConfig.__dataclass_fields__)
+    if set(d) - known:
+        raise G.GgufError(f"unknown configuration fields: {sorted(set(d) - known)}")
+    return ModelConfig(**d)
+
+
+def load_llama_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, kv_format: Optional[str] = None):
+    """Returns (cfg, LlamaWeights) for this rank from a verified open GGUF file."""
+    cfg = config_from_gguf(g)
+    if kv_format:
+        cfg.kv_format = kv_format
+    rec = g.recipe() or {"bindings": []}
+    bound = {b["logical_tensor"]: b for b in rec["bindings"]}
+    device = torch.device(device)
+    hd = cfg.head_dim
+    dense_dtype = torch.float32 if cfg.weight_format == "fp32" else torch.bfloat16
+
+    def dense(name):
+        t = g.tensors[name]
+        want = G.T_F32 if dense_dtype == torch.float32 else G.T_BF16
+        if t.ttype != want:
+            raise G.GgufError(f"{name}: unexpected tensor type {t.ttype}")
+        return g.upload(name, device, dense_dtype).view(t.shape)
+
+    def rows(name, lo: int, hi: int, cols=None):
+        """(values[lo:hi, cols], scales[lo:hi, cols/128] or None)."""
+        t = g.tensors[name]
+        b = bound.get(name)
+        if b is None:
+            v = dense(name)
+            v = v[lo:hi] if cols is None else v[lo:hi, cols[0]:cols[1]]
+            return v, None
+        if b["encoding"] != FP8_ENCODING or t.ttype != G.T_I8:
+            raise G.GgufError(f"{name}: unsupported encoding {b['encoding']}")
+        v = g.upload(name, device, torch.uint8).view(t.shape)
+        sname = b["scales"][0]["tensor"]
+        s = g.upload(sname, device, torch.float32).view(g.tensors[sname].shape)
+        if cols is None:
+            return v[lo:hi], s[lo:hi]
+        if cols[0] % 128 or cols[1] % 128:
+            raise G.GgufError("tensor-parallel column shards of FP8 weights must align to 128")
+        return v[lo:hi, cols[0]:cols[1]], s[lo:hi, cols[0] // 128:cols[1] // 128]
+
+    def lin(parts) -> LinearWeight:
+        vals = torch.cat([p[0] for p in parts], dim=0).contiguous()
+        if parts[0][1] is None:
+            return LinearWeight("dense", vals)
+        sc = torch.cat([p[1] for p in parts], dim=0)
+        return LinearWeight("fp8", vals, sc.t().contiguous())
+
+    qs, fs = cfg.q_size // tp_size, cfg.ffn // tp_size
+    if tp_size <= cfg.n_kv_heads:
+        ks = cfg.kv_size // tp_size
+        kv_lo, kv_hi = tp_rank * ks, (tp_rank + 1) * ks
+    else:
+        head = tp_rank * cfg.n_kv_heads // tp_size
+        kv_lo, kv_hi = head * hd, (head + 1) * hd
+    embed = dense("token_embd.weight")
+    layers = []
+    for i in range(cfg.n_layers):
+        p = f"blk.{i}."
+        layers.append(LayerWeights(
+            attn_norm=dense(p + "attn_norm.weight"),
+            qkv=lin([rows(p + "attn_q.weight", tp_rank * qs, (tp_rank + 1) * qs),
+                     rows(p + "attn_k.weight", kv_lo, kv_hi), rows(p + "attn_v.weight", kv_lo, kv_hi)]),
+            o=lin([rows(p + "attn_output.weight", 0, cfg.d_model, (tp_rank * qs, (tp_rank + 1) * qs))]),
+            mlp_norm=dense(p + "ffn_norm.weight"),
+            gate_up=lin([rows(p + "ffn_gate.weight", tp_rank * fs, (tp_rank + 1) * fs),
+                         rows(p + "ffn_up.weight", tp_rank * fs, (tp_rank + 1) * fs)]),
+            down=lin([rows(p + "ffn_down.weight", 0, cfg.d_model, (tp_rank * fs, (tp_rank + 1) * fs))])))
+    final_norm = dense("output_norm.weight")
+    vs = (cfg.vocab + tp_size - 1) // tp_size
+    vo = tp_rank * vs if tp_size > 1 else 0
+    v_hi = min(cfg.vocab, vo + vs) if tp_size > 1 else cfg.vocab
+    if cfg.tie_embeddings:
+        head = LinearWeight("dense", embed[vo:v_hi].contiguous())
+    else:
+        head = lin([rows("output.weight", vo, v_hi)])
+    return cfg, LlamaWeights(embed, layers, final_norm, head, vo)
+
+
+def tokenizer_from_gguf(g: G.GgufFile):
+    """HF `tokenizers` JSON embedded in the file, or the byte tokenizer when absent."""
+    from ..frontend.text import ByteTokenizer, HFTokenizer
+    raw = g.metadata.get(G.FRONTEND_TOKENIZER_KEY)
+    if raw is None:
+        return ByteTokenizer()
+    return HFTokenizer(raw)
