@@ -206,15 +206,20 @@ class GenRequest:
     submitted_at: float = field(default_factory=time.monotonic)
     first_token_at: Optional[float] = None
     finish_reason: Optional[str] = None
-    prefix_seq: object = None            # optional engine Sequence whose KV prefix is forked
+    prefix_seq: object = None            # optional engine Sequence (or prefix-cache lease) whose KV prefix is forked
+    prefix_hit_tokens: int = 0
+    shifted_tokens: int = 0              # tokens dropped by context shifts so far
+    shift_count: int = 0
 
 
 class EngineLoop:
     """Single worker thread that owns the engine and runs planner rounds."""
 
     def __init__(self, engine, model_id: str = "model", max_batch: Optional[int] = None, queue_capacity: int = 64,
-                 prefill_interval: int = 4, prefill_chunk_tokens: int = 0):
+                 prefill_interval: int = 4, prefill_chunk_tokens: int = 0, prefix_cache=None, context_policy=None):
         self.engine = engine
+        self.prefix_cache = prefix_cache
+        self.context_policy = context_policy
         self.model_id = model_id
         self.planner = BatchPlanner(max_batch or engine.max_batch, prefill_interval,
                                     max_prefill_batch=min(8, max_batch or engine.max_batch))
@@ -302,6 +307,8 @@ class EngineLoop:
             return
         req.state = "done"
         req.finish_reason = reason
+        if req.prefix_seq is not None:
+            self._release_prefix(req)
         if req.seq is not None:
             try:
                 self.engine.free_sequence(req.seq)
@@ -364,7 +371,11 @@ class EngineLoop:
                 for r in reqs:
                     try:
                         if r.prefix_seq is not None:
-                            r.seq = eng.fork_sequence(r.prefix_seq, r.prompt)
+                            try:
+                                r.seq = eng.fork_sequence(r.prefix_seq, r.prompt)
+                                r.prefix_hit_tokens = r.seq.num_computed
+                            finally:
+                                self._release_prefix(r)
                         else:
                             r.seq = eng.new_sequence(r.prompt)
                         live.append(r)
@@ -373,8 +384,13 @@ class EngineLoop:
                         outcomes[r.rid] = "failed"
                 if live:
                     logits = eng.prefill([r.seq for r in live], self.prefill_chunk_tokens, sample=False)
+                    if self.prefix_cache is not None:
+                        for r in live:
+                            self.prefix_cache.publish(r.seq, len(r.prompt))
                     self._select_and_publish(live, logits, outcomes)
             else:
+                if self.context_policy is not None and not self.context_policy.is_disabled:
+                    self._shift_full_windows(reqs)
                 logits = eng.decode([r.seq for r in reqs], sample=False)
                 self._select_and_publish(reqs, logits, outcomes)
         except Exception as exc:
@@ -383,6 +399,27 @@ class EngineLoop:
                     r.finish_reason = f"error:{type(exc).__name__}:{exc}"
                     outcomes[r.rid] = "failed"
         return outcomes
+
+    def _release_prefix(self, r: GenRequest) -> None:
+        rel = getattr(r.prefix_seq, "release", None)
+        r.prefix_seq = None
+        if rel is not None:
+            rel()
+
+    def _shift_full_windows(self, reqs: list) -> None:
+        """Compacts every sequence whose next token would fill the context (keep-prefix/keep-recent policy)."""
+        from ..cache.context_shift import WindowState, apply_shift
+        cap = self.engine.cfg.max_context
+        for r in reqs:
+            n = len(r.seq.tokens) - 1          # tokens held by the KV state; the last one is the decode input
+            st = WindowState(n, n + r.shifted_tokens, r.shift_count)
+            d = self.context_policy.plan(st, cap, 1)
+            if d.shift:
+                last = r.seq.tokens.pop()
+                r.seq = apply_shift(self.engine, r.seq, d)
+                r.seq.tokens.append(last)
+                r.shifted_tokens += d.old_state.logical_length - d.new_state.logical_length
+                r.shift_count += 1
 
     def _select_and_publish(self, reqs: list, logits, outcomes: dict) -> None:
         from .. import ops
@@ -442,7 +479,8 @@ class EngineLoop:
                 elif r.generated >= r.max_new_tokens:
                     r.finish_reason = "length"
                     outcomes[r.rid] = "finished"
-                elif len(r.seq.tokens) >= self.engine.cfg.max_context:
+                elif len(r.seq.tokens) >= self.engine.cfg.max_context and (
+                        self.context_policy is None or self.context_policy.is_disabled):
                     r.finish_reason = "length"
                     outcomes[r.rid] = "finished"
                 else:

@@ -183,15 +183,24 @@ class EngineBackend:
     """Engine + continuous-batching loop + generation service for one resident model."""
 
     def __init__(self, engine, tokenizer, aliases=("model",), queue_capacity: int = 64, event_capacity: int = 256,
-                 prefill_chunk_tokens: int = 0, prefix_cache=None, kv_cache_encoding: str = "bf16"):
+                 prefill_chunk_tokens: int = 0, prefix_cache=None, kv_cache_encoding: str = "bf16",
+                 context_policy=None, checkpoint_store=None):
         from ..engine.scheduler import EngineLoop
         self.engine = engine
         self.tokenizer = tokenizer
         self.aliases = list(aliases)
+        if prefix_cache is True:
+            from ..cache.prefix import PrefixCache, PrefixIdentity
+            prefix_cache = PrefixCache(engine, PrefixIdentity(
+                model=engine.cfg.name, tokenizer=getattr(tokenizer, "identity", type(tokenizer).__name__),
+                kv_layout=engine.cfg.kv_format, context_policy=context_policy.identity() if context_policy else ""))
+        self.prefix_cache = prefix_cache or None
+        self.context_policy = context_policy
+        self.checkpoint_store = checkpoint_store
         self.loop = EngineLoop(engine, self.aliases[0], queue_capacity=queue_capacity,
-                               prefill_chunk_tokens=prefill_chunk_tokens)
+                               prefill_chunk_tokens=prefill_chunk_tokens, prefix_cache=self.prefix_cache,
+                               context_policy=context_policy)
         self.service = GenerationService(self.loop, tokenizer, engine.cfg.vocab, self.aliases[0], event_capacity)
-        self.prefix_cache = prefix_cache
         self.kv_cache_encoding = kv_cache_encoding
         self._embed_lock = threading.Lock()
 
