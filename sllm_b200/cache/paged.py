@@ -1,11 +1,13 @@
 """Paged KV-cache manager: device page tensors + the native page pool.
 
-Layout per layer (K and V alike): values ``[num_pages, page, kv_heads, head_dim]`` and, for dynamic
-FP8, fp32 scales ``[num_pages, page, kv_heads]`` (one scale per token and head, ``amax / 448``).  The
+Layout per layer (K and V alike): values ``[num_pages, kv_heads, page, head_dim]`` and, for dynamic
+FP8, fp32 scales ``[num_pages, kv_heads, page]`` (one scale per token and head, ``amax / 448``).  The
 byte offset of (sequence token t, head h, channel c) inside a sequence's page list is
-``page_list[t // page] * page_bytes + ((t % page) * kv_heads + h) * head_dim + c`` — the block-16
-address arithmetic of the reference's layout oracle (tests/reference/oracles.py:209-239,
-tests/fixtures/kv_layout.json).
+``page_list[t // page] * page_bytes + ((h * page) + t % page) * head_dim + c``: block-16 paging as in
+the reference's layout oracle (tests/reference/oracles.py:209-239, tests/fixtures/kv_layout.json), but
+head-major inside a page, so that the 16 tokens of one head are one contiguous 2 KB run in HBM - the
+unit one attention CTA fetches with a single TMA box (token-major pages gave 128-byte pieces at a 1 KB
+stride and held the decode attention kernel near half of the DRAM bandwidth).
 
 Sequences are handles into the native pool (csrc/host/page_pool.cpp): reserve -> run step -> commit
 gives the reference's transactional length publication (docs/architecture/runtime.md:145-149); fork
@@ -32,7 +34,7 @@ def paged_kv_offset(page_list, token: int, head: int, channel: int, page_size: i
                     elem_bytes: int = 1) -> int:
     """Byte offset of one element inside the value plane of a layer."""
     page = page_list[token // page_size]
-    return ((page * page_size + token % page_size) * kv_heads + head) * head_dim * elem_bytes + channel * elem_bytes
+    return ((page * kv_heads + head) * page_size + token % page_size) * head_dim * elem_bytes + channel * elem_bytes
 
 
 class PagePool:
@@ -154,11 +156,11 @@ class PagedKVCache:
         fmt = cfg.kv_format
         self.fp8 = fmt in ("fp8", "fp8-static")
         vdtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}.get(fmt, torch.uint8)
-        shape = (cfg.n_layers, 2, num_pages, cfg.page_size, hkv, cfg.head_dim)
+        shape = (cfg.n_layers, 2, num_pages, hkv, cfg.page_size, cfg.head_dim)
         self.values = torch.zeros(shape, dtype=vdtype, device=device)
         self.scales = None
         if fmt == "fp8":
-            self.scales = torch.ones((cfg.n_layers, 2, num_pages, cfg.page_size, hkv), dtype=torch.float32,
+            self.scales = torch.ones((cfg.n_layers, 2, num_pages, hkv, cfg.page_size), dtype=torch.float32,
                                      device=device)
         self.k_static, self.v_static = (k_static or 1.0, v_static or 1.0) if fmt == "fp8-static" else (0.0, 0.0)
         self._layers = [

@@ -11,8 +11,8 @@
 // Partial (max, sum, acc) triples of the splits are merged by the last CTA to arrive (counter per
 // (row, kv head)); nobody waits.
 //
-// KV page layout (per layer, K and V alike): values [num_pages, page, kv_heads, head_dim] in bf16 or
-// E4M3FN, scales [num_pages, page, kv_heads] fp32.
+// KV page layout (per layer, K and V alike): values [num_pages, kv_heads, page, head_dim] in bf16 or
+// E4M3FN, scales [num_pages, kv_heads, page] fp32 (head-major pages).
 //
 // Counterparts in the reference: causal_attention_kernel.hip.cpp:125-495 (online softmax, split-KV
 // decode, GQA sharing, direct low-bit KV reads) and gemma_attention_kernel.hip.cpp:40 (sliding window).
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
     float vsc = 0.f;
     if (valid) {
       const int blk = bt[tok / p.page_size];
-      slot = (static_cast<size_t>(blk) * p.page_size + tok % p.page_size) * p.hkv + kvh;
+      slot = (static_cast<size_t>(blk) * p.hkv + kvh) * p.page_size + tok % p.page_size;   // head-major pages
       // All 16-byte pieces of (up to) 128 bytes of the key row are requested before any is used, so one
       // memory round trip covers the whole row.
       constexpr int kVecs = HD * (kFp8 ? 1 : 2) / 16;

@@ -2,9 +2,10 @@
 // head_dim 128, GQA group <= 16.
 //
 // A CTA owns (query row, kv head, KV split) and walks its keys 128 at a time:
-//   * the page table is walked by one producer thread which issues one TMA box per 16-token page
-//     ({128 B of channels, 1 head, 16 tokens} out of the [pages*16, kv_heads, 128] E4M3 plane), eight
-//     boxes assembling a 128-key swizzled tile each for K and V; 3-stage ring;
+//   * the page table is walked by the producer warp: lane i issues the TMA box of page i of each tile
+//     ({128 B of channels, 16 tokens} = 2 KB contiguous out of the head-major [pages, kv_heads, 16, 128]
+//     E4M3 plane), eight boxes assembling a 128-key swizzled tile each for K and V, and stages the
+//     tile's per-token scales with cp.async under the same barrier; 3-stage ring;
 //   * S^T = K Q^T     : M = 128 keys, N = 16 (the group's heads, zero padded), K = 128 channels, E4M3
 //     inputs (Q is quantised to E4M3 per head once per CTA), result in TMEM [key lane, head column];
 //   * softmax        : thread t owns key t of the tile; per-head maxima cross the 128 threads by
@@ -21,6 +22,7 @@
 #include "api.h"
 #include "attention_common.cuh"
 #include <cudaTypedefs.h>
+#include <cstddef>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -33,7 +35,7 @@ constexpr int kDaStages = 3;
 constexpr int kDaTileBytes = kDaTile * 128;  // 16 KB per K or V tile
 constexpr int kDaHeadsPad = 16;
 
-struct __align__(8) DecodeTcBarriers {
+struct __align__(16) DecodeTcBarriers {
   uint64_t kv_full[kDaStages];
   uint64_t kv_empty[kDaStages];
   uint64_t s_full[2];
@@ -43,7 +45,7 @@ struct __align__(8) DecodeTcBarriers {
   int abort_flag;
   int is_last;
   float red[4][kDaHeadsPad + 1];   // per-warp maxima (heads + V scale)
-  float qscale[kDaHeadsPad];
+  alignas(16) float sc[kDaStages][2][kDaTile];  // per-token K and V scales of each staged tile (16-byte cp.async)
   float s_red[4];
 };
 
@@ -59,10 +61,31 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128_mn8(uint32_t smem_addr)
 }
 
 // Decode an E4M3 byte exactly (integer path, see e4m3x4_to_f32x4_exp120).
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+// Makes the barrier track this thread's earlier cp.async copies: the (pre-counted) arrival fires when they land.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ float e4m3_to_f32_int(uint32_t b) {
   const uint32_t bits = ((b & 0x80u) << 24) | ((b & 0x7fu) << 20);
   return __uint_as_float(bits) * kPow60 * kPow60;
 }
+
+#ifdef SLLM_TRACE
+// Development-only per-tile cycle stamps of CTA (0,0,0); never compiled into the product.
+__device__ long long g_da_trace[256];
+__device__ __forceinline__ void da_mark(int j, int slot) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 24) g_da_trace[j * 10 + slot] = clock64();
+}
+#define DA_TRACE(j, slot) da_mark(j, slot)
+#else
+#define DA_TRACE(j, slot)
+#endif
+
+static_assert(offsetof(DecodeTcBarriers, sc) % 16 == 0, "cp.async 16-byte destinations");
 
 template <int G>
 __global__ void __launch_bounds__(kDaThreads, 2)
@@ -101,7 +124,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kDaStages; ++s) {
-      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_full[s], p.k_scale ? 33 : 1);   // TMA issuer + 32 lanes' scale copies
       mbar_init(&bars->kv_empty[s], 1);
     }
     mbar_init(&bars->s_full[0], 1);
@@ -128,27 +151,56 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
 
   if (warp == 0) {
     // ------------------------------------------------------------ page-walking TMA producer
-    if (lane == 0) {
-      const int* bt = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
-      const int pages_per_tile = kDaTile / p.page_size;
-      const int box_bytes = p.page_size * 128;
-      int issued = 0;
-      for (int j = 0; j < nt; ++j) {
-        const int st = j % kDaStages;
-        if (!mbar_wait(&bars->kv_empty[st], ((j / kDaStages) & 1) ^ 1, abort_flag, nullptr, 0)) break;
-        uint8_t* kd = kv_s + st * 2 * kDaTileBytes;
-        uint8_t* vd = kd + kDaTileBytes;
-        mbar_expect_tx(&bars->kv_full[st], 2 * kDaTileBytes);
-        const int page0 = (begin + j * kDaTile) / p.page_size;
-        for (int i = 0; i < pages_per_tile; ++i) {
-          int pi = page0 + i;
-          if (pi >= p.max_blocks) pi = p.max_blocks - 1;   // beyond the table: any valid page, keys are masked
-          const int tok_row = bt[pi] * p.page_size;
-          tma_load_3d(kd + i * box_bytes, &tm_k, &bars->kv_full[st], 0, kvh, tok_row);
-          tma_load_3d(vd + i * box_bytes, &tm_v, &bars->kv_full[st], 0, kvh, tok_row);
-        }
-        issued = j + 1;
+    // The warp reads 32 block-table entries at a time (one coalesced load, issued a whole batch of
+    // tiles ahead of its first use, so a table row that misses the L2 costs no stall); lane i then
+    // issues the TMA boxes of page i of the tile with its entry taken from the holder by shuffle.
+    const int* bt = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
+    const int pages_per_tile = kDaTile / p.page_size;
+    const int tiles_per_batch = 32 / pages_per_tile;
+    const int box_bytes = p.page_size * 128;
+    auto load_batch = [&](int b) -> int {
+      int pi = begin / p.page_size + b * 32 + lane;
+      if (pi >= p.max_blocks) pi = p.max_blocks - 1;   // beyond the table: any valid page, keys are masked
+      return __ldg(bt + pi) * p.hkv + kvh;             // (page, head) row of the head-major plane
+    };
+    int rows_cur = nt > 0 ? load_batch(0) : 0;
+    int rows_next = nt > tiles_per_batch ? load_batch(1) : 0;
+    int issued = 0;
+    for (int j = 0; j < nt; ++j) {
+      const int within = j % tiles_per_batch;
+      if (within == 0 && j > 0) {
+        rows_cur = rows_next;
+        if (j + tiles_per_batch < nt) rows_next = load_batch(j / tiles_per_batch + 1);
       }
+      const int tok_row = __shfl_sync(0xffffffffu, rows_cur, within * pages_per_tile + (lane < pages_per_tile ? lane : 0));
+      const int st = j % kDaStages;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(&bars->kv_empty[st], ((j / kDaStages) & 1) ^ 1, abort_flag, nullptr, 0) ? 1 : 0;
+        if (ok) mbar_expect_tx(&bars->kv_full[st], 2 * kDaTileBytes);
+        DA_TRACE(j, 8);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        uint8_t* kd = kv_s + st * 2 * kDaTileBytes + lane * box_bytes;
+        tma_load_3d(kd, &tm_k, &bars->kv_full[st], 0, 0, tok_row);
+        tma_load_3d(kd + kDaTileBytes, &tm_v, &bars->kv_full[st], 0, 0, tok_row);
+      }
+      if (p.k_scale) {
+        // lane l stages the scales of keys 4l .. 4l+3 (one page: page sizes are multiples of 8)
+        const int key0 = lane * 4;
+        const size_t slot = static_cast<size_t>(__shfl_sync(0xffffffffu, rows_cur,
+                                                            within * pages_per_tile + key0 / p.page_size)) * p.page_size +
+                            key0 % p.page_size;
+        cp_async_16(&bars->sc[st][0][key0], p.k_scale + slot);
+        cp_async_16(&bars->sc[st][1][key0], p.v_scale + slot);
+      }
+      if (p.k_scale) cp_async_mbar_arrive_noinc(&bars->kv_full[st]);
+      if (lane == 0) DA_TRACE(j, 9);
+      issued = j + 1;
+    }
+    if (lane == 0) {
       int dummy = 0;
       for (int st = 0; st < kDaStages; ++st) {
         const int fills = (issued > st) ? (issued - st + kDaStages - 1) / kDaStages : 0;
@@ -182,10 +234,12 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
           if (!mbar_wait(&bars->kv_full[st1], ((j + 1) / kDaStages) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMA_FULL))
             break;
           tc_fence_after();
+          DA_TRACE(j, 6);
           issue_s(j + 1);
         }
         if (!mbar_wait(&bars->p_ready, j & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
+        DA_TRACE(j, 7);
         const uint32_t v_addr = smem_u32(kv_s + (j % kDaStages) * 2 * kDaTileBytes + kDaTileBytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // 32 keys per MMA
@@ -203,21 +257,28 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
     const float log2e = 1.4426950408889634f;
 
-    // ---- quantise Q: one head per iteration, thread t holds channel t
+    // ---- quantise Q: thread t holds channel t of every head of the group
+    float qv[G], qsc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+      qv[g] = __bfloat162float(p.q[static_cast<size_t>(r) * p.q_ld + (kvh * G + g) * 128 + t]);
+#pragma unroll
     for (int g = 0; g < G; ++g) {
-      const float qv = __bfloat162float(p.q[static_cast<size_t>(r) * p.q_ld + (kvh * G + g) * 128 + t]);
-      float a = fabsf(qv);
+      float a = fabsf(qv[g]);
       if (!(a == a) || a > 3.0e38f) a = 0.f;
-      a = warp_max(a);
-      if (lane == 0) bars->s_red[qd] = a;
-      SyncBar1x128::sync();
-      const float amax = fmaxf(fmaxf(bars->s_red[0], bars->s_red[1]), fmaxf(bars->s_red[2], bars->s_red[3]));
+      a = warp_max_redux(a);
+      if (lane == 0) bars->red[qd][g] = a;
+    }
+    SyncBar1x128::sync();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float amax = fmaxf(fmaxf(bars->red[0][g], bars->red[1][g]), fmaxf(bars->red[2][g], bars->red[3][g]));
       const float qs = amax > 0.f ? amax / 448.f : 1.f;
       // row g of the K-major tile: 16-byte unit (t / 16) lands at unit index ((t / 16) ^ (g % 8))
-      q_s[g * 128 + ((((t >> 4) ^ (g & 7))) << 4) + (t & 15)] = f32_to_e4m3(__fdiv_rn(qv, qs));
-      if (t == 0) bars->qscale[g] = qs * p.sm_scale * log2e;   // scores leave the MMA in log2 units after this factor
-      SyncBar1x128::sync();
+      q_s[g * 128 + ((((t >> 4) ^ (g & 7))) << 4) + (t & 15)] = f32_to_e4m3(__fdiv_rn(qv[g], qs));
+      qsc[g] = qs * p.sm_scale * log2e;   // scores leave the MMA in log2 units after this factor
     }
+    SyncBar1x128::sync();   // red[] is rewritten by the first tile
     fence_proxy_async_smem();
     if (nt > 0) asm volatile("bar.sync 2, 160;" ::: "memory");
 
@@ -230,46 +291,51 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       o[g] = 0.f;
       alpha_prev[g] = 0.f;
     }
-    const int* bt = p.block_table + static_cast<size_t>(seq) * p.max_blocks;
     bool ok = true;
     for (int j = 0; j < nt && ok; ++j) {
-      // per-token scales of this tile (thread = key)
       const int tok = begin + j * kDaTile + t;
       const bool valid = tok < end && tok >= first;
-      float ksc = 0.f, vsc = 0.f;
-      if (tok < end) {
-        int pi = tok / p.page_size;
-        if (pi >= p.max_blocks) pi = p.max_blocks - 1;
-        const size_t slot = (static_cast<size_t>(bt[pi]) * p.page_size + tok % p.page_size) * p.hkv + kvh;
-        ksc = p.k_scale ? p.k_scale[slot] : p.k_static_scale;
-        vsc = p.v_scale ? p.v_scale[slot] : p.v_static_scale;
-      }
+      if (t == 0) DA_TRACE(j, 0);
       ok = mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
+      // The tile's scales were staged by the producer warp under kv_full, which completed before the
+      // S MMA was issued; observing it here (it returns at once) orders the reads below after the copies.
+      float ksc = p.k_static_scale, vsc = p.v_static_scale;
+      if (p.k_scale) {
+        const int st = j % kDaStages;
+        ok = mbar_wait(&bars->kv_full[st], (j / kDaStages) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMA_FULL);
+        if (!ok) break;
+        ksc = bars->sc[st][0][t];
+        vsc = bars->sc[st][1][t];
+      }
       uint32_t raw[16];
+      if (t == 0) DA_TRACE(j, 1);
       tmem_ld16(lane_addr + (j & 1) * 16, raw);
       tmem_wait_ld();
+      if (t == 0) DA_TRACE(j, 2);
       float s[G];
       float red_v[G + 1];
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        s[g] = valid ? __uint_as_float(raw[g]) * ksc * bars->qscale[g] : -INFINITY;
+        s[g] = valid ? __uint_as_float(raw[g]) * ksc * qsc[g] : -INFINITY;
         red_v[g] = s[g];
       }
       red_v[G] = valid ? vsc : 0.f;
 #pragma unroll
       for (int g = 0; g <= G; ++g) {
-        red_v[g] = warp_max(red_v[g]);
+        red_v[g] = warp_max_redux(red_v[g]);
         if (lane == 0) bars->red[qd][g] = red_v[g];
       }
       SyncBar1x128::sync();
+      if (t == 0) DA_TRACE(j, 3);
       float tmax[G + 1];
 #pragma unroll
       for (int g = 0; g <= G; ++g)
         tmax[g] = fmaxf(fmaxf(bars->red[0][g], bars->red[1][g]), fmaxf(bars->red[2][g], bars->red[3][g]));
       const float vmax = tmax[G] > 0.f ? tmax[G] : 1.f;
       const float vfold = valid ? vsc / vmax * 256.f : 0.f;   // probabilities enter the MMA as p * vsc/vmax * 256
+      const float inv_vfold = vfold > 0.f ? __fdividef(1.f, vfold) : 0.f;
       float alpha[G];
 #pragma unroll
       for (int g = 0; g < G; ++g) {
@@ -279,7 +345,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         const uint8_t p8 = f32_to_e4m3(pr * vfold);
         p_s[g * 128 + ((((t >> 4) ^ (g & 7))) << 4) + (t & 15)] = p8;
         // the normaliser uses the value the tensor core will actually multiply
-        const float p_eff = (vfold > 0.f) ? e4m3_to_f32_int(p8) / vfold : 0.f;
+        const float p_eff = e4m3_to_f32_int(p8) * inv_vfold;
         l[g] = l[g] * alpha[g] + p_eff;
         m[g] = m_new;
       }
@@ -288,6 +354,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars->p_ready);
+      if (t == 0) DA_TRACE(j, 4);
       // ---- fold P.V of the PREVIOUS tile into the output (thread = channel) while the tensor core
       // works on this tile: O <- O * alpha_{j-1} + PV_{j-1} * factor_{j-1}
       if (j > 0) {
@@ -300,6 +367,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         for (int g = 0; g < G; ++g) o[g] = fmaf(o[g], alpha_prev[g], __uint_as_float(raw[g]) * of_prev);
         tc_fence_before();
       }
+      if (t == 0) DA_TRACE(j, 5);
 #pragma unroll
       for (int g = 0; g < G; ++g) alpha_prev[g] = alpha[g];
       of_prev = vmax / 256.f;
@@ -348,7 +416,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
   }
 }
 
-// [pages*page_size tokens, kv_heads, 128] E4M3 plane; box = {128 channels, 1 head, page_size tokens}.
+// [pages*kv_heads, page_size tokens, 128] E4M3 plane (head-major pages); box = {128 channels, page_size tokens, 1}.
 static int make_page_tmap(CUtensorMap* out, const void* pages, long long total_tokens, int hkv, int page_size) {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
   static std::once_flag once;
@@ -361,9 +429,10 @@ static int make_page_tmap(CUtensorMap* out, const void* pages, long long total_t
   });
   if (!fn) return SLLM_ERR_DRIVER_ENTRY;
   if (reinterpret_cast<uintptr_t>(pages) & 15) return SLLM_ERR_ALIGNMENT;
-  cuuint64_t gdim[3] = {128, static_cast<cuuint64_t>(hkv), static_cast<cuuint64_t>(total_tokens)};
-  cuuint64_t gstride[2] = {128, static_cast<cuuint64_t>(hkv) * 128};
-  cuuint32_t box[3] = {128, 1, static_cast<cuuint32_t>(page_size)};
+  cuuint64_t gdim[3] = {128, static_cast<cuuint64_t>(page_size),
+                        static_cast<cuuint64_t>(total_tokens / page_size) * static_cast<cuuint64_t>(hkv)};
+  cuuint64_t gstride[2] = {128, static_cast<cuuint64_t>(page_size) * 128};
+  cuuint32_t box[3] = {128, static_cast<cuuint32_t>(page_size), 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(pages), gdim, gstride, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -411,6 +480,12 @@ static int launch_da(const CUtensorMap& tk, const CUtensorMap& tv, const PagedAt
 
 using namespace sllm;
 
+#ifdef SLLM_TRACE
+SLLM_EXPORT int sllm_decode_attention_read_trace(long long* out256) {
+  return cudaMemcpyFromSymbol(out256, g_da_trace, sizeof(long long) * 256) == cudaSuccess ? 0 : 5;
+}
+#endif
+
 // Same contract as sllm_paged_attention, restricted to E4M3 pages with per-token scale planes or static
 // scales, head_dim 128, page sizes dividing 128 and a GQA group of 1, 2, 4, 8 or 16.
 SLLM_EXPORT int sllm_decode_attention_tc(const void* q, int q_ld, const void* k_pages, const void* v_pages,
@@ -428,6 +503,9 @@ SLLM_EXPORT int sllm_decode_attention_tc(const void* q, int q_ld, const void* k_
   if (page_size <= 0 || (kDaTile % page_size) || (page_size & (page_size - 1)) || page_size < 8)
     return SLLM_ERR_UNSUPPORTED_SHAPE;
   if (splits < 1 || splits > 65535 || hkv > 65535 || max_blocks <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  // the scale planes are staged with 16-byte copies
+  if (k_scale && ((reinterpret_cast<uintptr_t>(k_scale) | reinterpret_cast<uintptr_t>(v_scale)) & 15)) return SLLM_ERR_ALIGNMENT;
+  if (k_scale && !v_scale) return SLLM_ERR_INVALID_ARGUMENT;
   const int g = hq / hkv;
   PagedAttnParams p;
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_ld = q_ld;

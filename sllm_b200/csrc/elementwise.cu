@@ -212,9 +212,9 @@ struct RopeKvParams {
   const int* seq_index;    // [T] row of block_table owning each token
   const int* block_table;  // [num_seqs, max_blocks]
   int max_blocks;
-  void* k_pages;           // [num_pages, page, hkv, hd]
+  void* k_pages;           // [num_pages, hkv, page, hd]
   void* v_pages;
-  float* k_scale;          // [num_pages, page, hkv] (fp8 only)
+  float* k_scale;          // [num_pages, hkv, page] (fp8 only)
   float* v_scale;
   int hq, hkv, hd, rotary_dim, page_size, kv_fp8;
   float theta;
@@ -258,9 +258,9 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
   if (is_q) return;  // uniform per CTA
   const int kvh = is_v ? h - p.hq - p.hkv : h - p.hq;
   const int blk = p.block_table[static_cast<size_t>(p.seq_index[t]) * p.max_blocks + pos / p.page_size];
-  const size_t slot = static_cast<size_t>(blk) * p.page_size + pos % p.page_size;
+  const size_t slot = (static_cast<size_t>(blk) * p.hkv + kvh) * p.page_size + pos % p.page_size;   // head-major pages
   if (!p.kv_fp8) {
-    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_v ? p.v_pages : p.k_pages) + (slot * p.hkv + kvh) * hd;
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_v ? p.v_pages : p.k_pages) + slot * hd;
     for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = __float2bfloat16_rn(rot[i]);
     return;
   }
@@ -270,10 +270,10 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
   amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
   const float st = is_v ? p.v_static_scale : p.k_static_scale;
   const float scale = st > 0.f ? st : (amax > 0.f ? amax / kE4M3Max : 1.f);
-  uint8_t* dst = static_cast<uint8_t*>(is_v ? p.v_pages : p.k_pages) + (slot * p.hkv + kvh) * hd;
+  uint8_t* dst = static_cast<uint8_t*>(is_v ? p.v_pages : p.k_pages) + slot * hd;
   for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = f32_to_e4m3(__fdiv_rn(rot[i], scale));
   if (threadIdx.x == 0 && st <= 0.f) {
-    float* sd = (is_v ? p.v_scale : p.k_scale) + slot * p.hkv + kvh;
+    float* sd = (is_v ? p.v_scale : p.k_scale) + slot;
     *sd = scale;
   }
 }

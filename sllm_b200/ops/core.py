@@ -297,8 +297,9 @@ def argmax(logits: torch.Tensor, index_offset: int = 0, with_values: bool = Fals
 # ------------------------------------------------------------------------------------------------
 @dataclass
 class KVLayer:
-    """One layer's K/V pages.  values: [num_pages, page, hkv, hd] (uint8 E4M3 or bf16/fp32);
-    scales: [num_pages, page, hkv] fp32 for dynamic FP8, None otherwise."""
+    """One layer's K/V pages.  values: [num_pages, hkv, page, hd] (uint8 E4M3 or bf16/fp32);
+    scales: [num_pages, hkv, page] fp32 for dynamic FP8, None otherwise.  Head-major pages keep the
+    page_size x head_dim bytes one attention CTA streams contiguous in HBM (2 KB for FP8, page 16)."""
     k: torch.Tensor
     v: torch.Tensor
     k_scale: Optional[torch.Tensor]
@@ -329,14 +330,14 @@ def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.
         if kv.fp8:
             kq, ks = ref.quant_kv_token_head(k, kv.k_static)
             vq, vs = ref.quant_kv_token_head(v, kv.v_static)
-            kv.k[blk, off] = kq
-            kv.v[blk, off] = vq
+            kv.k[blk, :, off] = kq
+            kv.v[blk, :, off] = vq
             if kv.k_scale is not None:
-                kv.k_scale[blk, off] = ks
-                kv.v_scale[blk, off] = vs
+                kv.k_scale[blk, :, off] = ks
+                kv.v_scale[blk, :, off] = vs
         else:
-            kv.k[blk, off] = k.to(kv.k.dtype)
-            kv.v[blk, off] = v.to(kv.v.dtype)
+            kv.k[blk, :, off] = k.to(kv.k.dtype)
+            kv.v[blk, :, off] = v.to(kv.v.dtype)
         return q.reshape(t, hq * hd).to(qkv.dtype)
     rc = _lib.kernels().sllm_rope_kv_append(
         _p(qkv), _p(positions), _p(seq_index), _p(block_table), block_table.stride(0), _p(kv.k), _p(kv.v),
@@ -372,16 +373,16 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
             nblk = (n + kv.page_size - 1) // kv.page_size
             blks = block_table[s, :nblk].long()
             if kv.fp8:
-                kk = ref.from_e4m3(kv.k[blks]).view(-1, hkv, hd)
-                vv = ref.from_e4m3(kv.v[blks]).view(-1, hkv, hd)
+                kk = ref.from_e4m3(kv.k[blks]).transpose(1, 2).reshape(-1, hkv, hd)
+                vv = ref.from_e4m3(kv.v[blks]).transpose(1, 2).reshape(-1, hkv, hd)
                 if kv.k_scale is not None:
-                    kk = kk * kv.k_scale[blks].view(-1, hkv, 1)
-                    vv = vv * kv.v_scale[blks].view(-1, hkv, 1)
+                    kk = kk * kv.k_scale[blks].transpose(1, 2).reshape(-1, hkv, 1)
+                    vv = vv * kv.v_scale[blks].transpose(1, 2).reshape(-1, hkv, 1)
                 else:
                     kk, vv = kk * kv.k_static, vv * kv.v_static
             else:
-                kk = kv.k[blks].view(-1, hkv, hd).to(torch.float32)
-                vv = kv.v[blks].view(-1, hkv, hd).to(torch.float32)
+                kk = kv.k[blks].transpose(1, 2).reshape(-1, hkv, hd).to(torch.float32)
+                vv = kv.v[blks].transpose(1, 2).reshape(-1, hkv, hd).to(torch.float32)
             out[i] = ref.attention_rows(q[i].view(hq, hd), kk, vv, n, window, scale, sinks)
         out = out.view(r, hq * hd)
         if q.dtype == torch.float32 and not quant_out:

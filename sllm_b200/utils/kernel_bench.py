@@ -3,7 +3,7 @@
     python -m sllm_b200.utils.kernel_bench --op gemm --m 32 --n 4096 --k 4096 [--fp8]
     python -m sllm_b200.utils.kernel_bench --op attention --batch 32 --ctx 2048
     python -m sllm_b200.utils.kernel_bench --op prefill --seqs 4 --len 2048
-    python -m sllm_b200.utils.kernel_bench --op decode-layer --batch 32 --ctx 2048
+    python -m sllm_b200.utils.kernel_bench --op decode-gemms --m 32 --graph
 
 Timing follows the usual hygiene: warm-up, an L2 flush (a 256 MB write) before each timed launch, CUDA
 events on the launching stream, median of the repetitions.  Fractions are reported against the
@@ -56,7 +56,40 @@ def timed(fn, reps: int = 10, warmup: int = 3, flush: bool = True) -> float:
     return statistics.median(ts)
 
 
-def bench_gemm(m, n, k, fp8, reps):
+def timed_graph(fns, reps: int = 5) -> float:
+    """Steady-state time per launch: the callables (same op over distinct buffers that together exceed the
+    L2 several times over) are captured back to back in one CUDA graph, as a decode step launches them, and
+    the replay is timed with events.  Launch latency and L2 reuse are both out of the picture."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for f in fns:
+            f()
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3 / len(fns))
+    return statistics.median(ts)
+
+
+def _copies(nbytes: int) -> int:
+    return max(4, min(64, (3 * 126 * 1024 * 1024) // max(nbytes, 1) + 1))
+
+
+def bench_gemm(m, n, k, fp8, reps, graph=False):
     dev = "cuda"
     x = torch.randn(m, k, device=dev).bfloat16()
     w = (torch.randn(n, k, device=dev) * 0.02).bfloat16()
@@ -69,7 +102,12 @@ def bench_gemm(m, n, k, fp8, reps):
         lw = LinearWeight("dense", w)
         xin = x
         wbytes = 2 * n * k
-    t = timed(lambda: ops.linear(xin, lw), reps)
+    if graph:
+        lws = [lw] + [LinearWeight(lw.kind, lw.w.clone(), None if lw.scale_t is None else lw.scale_t.clone())
+                      for _ in range(_copies(wbytes) - 1)]
+        t = timed_graph([(lambda w_=w_: ops.linear(xin, w_)) for w_ in lws], reps)
+    else:
+        t = timed(lambda: ops.linear(xin, lw), reps)
     bw, fl, tag = peaks()
     bytes_ = wbytes + m * k * (1 if fp8 else 2) + 2 * m * n
     flops = 2.0 * m * n * k
@@ -85,26 +123,30 @@ def _kv(batch, ctx, hkv, hd, fp8, page=16):
     pages = batch * blocks
     table = torch.arange(pages, device=dev, dtype=torch.int32).view(batch, blocks)
     if fp8:
-        kv = KVLayer(torch.randint(0, 0x70, (pages, page, hkv, hd), device=dev, dtype=torch.uint8),
-                     torch.randint(0, 0x70, (pages, page, hkv, hd), device=dev, dtype=torch.uint8),
-                     torch.full((pages, page, hkv), 0.01, device=dev), torch.full((pages, page, hkv), 0.01, device=dev),
+        kv = KVLayer(torch.randint(0, 0x70, (pages, hkv, page, hd), device=dev, dtype=torch.uint8),
+                     torch.randint(0, 0x70, (pages, hkv, page, hd), device=dev, dtype=torch.uint8),
+                     torch.full((pages, hkv, page), 0.01, device=dev), torch.full((pages, hkv, page), 0.01, device=dev),
                      True, page)
     else:
-        kv = KVLayer(torch.randn(pages, page, hkv, hd, device=dev).bfloat16(),
-                     torch.randn(pages, page, hkv, hd, device=dev).bfloat16(), None, None, False, page)
+        kv = KVLayer(torch.randn(pages, hkv, page, hd, device=dev).bfloat16(),
+                     torch.randn(pages, hkv, page, hd, device=dev).bfloat16(), None, None, False, page)
     return kv, table
 
 
-def bench_attention(batch, ctx, hq, hkv, hd, fp8, reps):
+def bench_attention(batch, ctx, hq, hkv, hd, fp8, reps, graph=False):
     dev = "cuda"
     kv, table = _kv(batch, ctx, hkv, hd, fp8)
     q = torch.randn(batch, hq * hd, device=dev).bfloat16()
     seq = torch.arange(batch, device=dev, dtype=torch.int32)
     lens = torch.full((batch,), ctx, device=dev, dtype=torch.int32)
-    t = timed(lambda: ops.paged_attention(q, kv, table, seq, lens, hq, hkv, hd, max_kv=ctx, quant_out=fp8 and hd == 128),
-              reps)
-    bw, _, tag = peaks()
     bytes_ = 2 * batch * ctx * hkv * hd * (1 if fp8 else 2) + (2 * batch * ctx * hkv * 4 if fp8 else 0)
+    call = lambda kv_: ops.paged_attention(q, kv_, table, seq, lens, hq, hkv, hd, max_kv=ctx, quant_out=fp8 and hd == 128)
+    if graph:
+        kvs = [kv] + [_kv(batch, ctx, hkv, hd, fp8)[0] for _ in range(_copies(bytes_) - 1)]
+        t = timed_graph([(lambda kv_=kv_: call(kv_)) for kv_ in kvs], reps)
+    else:
+        t = timed(lambda: call(kv), reps)
+    bw, _, tag = peaks()
     return {"op": "paged_attention", "batch": batch, "ctx": ctx, "hq": hq, "hkv": hkv, "hd": hd, "fp8": fp8,
             "us": t * 1e6, "GBps": bytes_ / t / 1e9, "roofline_us": bytes_ / bw * 1e6, "fraction": bytes_ / bw / t,
             "fraction_basis": tag}
@@ -141,16 +183,18 @@ def main():
     ap.add_argument("--seqs", type=int, default=4)
     ap.add_argument("--len", type=int, default=2048)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--graph", action="store_true",
+                    help="time back-to-back launches over distinct buffers inside one CUDA graph (steady state)")
     a = ap.parse_args()
     if a.op == "gemm":
-        print(json.dumps(bench_gemm(a.m, a.n, a.k, a.fp8, a.reps)))
+        print(json.dumps(bench_gemm(a.m, a.n, a.k, a.fp8, a.reps, a.graph)))
     elif a.op == "attention":
-        print(json.dumps(bench_attention(a.batch, a.ctx, a.hq, a.hkv, a.hd, a.fp8, a.reps)))
+        print(json.dumps(bench_attention(a.batch, a.ctx, a.hq, a.hkv, a.hd, a.fp8, a.reps, a.graph)))
     elif a.op == "prefill":
         print(json.dumps(bench_prefill(a.seqs, a.len, a.hq, a.hkv, a.reps)))
     else:
         for (n, k) in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096)):
-            print(json.dumps(bench_gemm(a.m, n, k, True, a.reps)))
+            print(json.dumps(bench_gemm(a.m, n, k, True, a.reps, a.graph)))
 
 
 if __name__ == "__main__":

@@ -189,3 +189,18 @@ def test_checkpoint_roundtrip_and_tamper(tmp_path):
     with pytest.raises(CK.CheckpointError, match="quota"):
         small.save("a", ck)
     assert store.delete("sess-1") and not store.delete("sess-1")
+
+
+def test_paged_kv_offset_matches_tensor_layout():
+    from sllm_b200.cache.paged import paged_kv_offset
+    eng = _engine()
+    c = eng.cache
+    L, two, pages, hkv, page, hd = c.values.shape
+    assert (hkv, page, hd) == (c.spec.kv_heads, c.spec.page_size, c.spec.head_dim)
+    plane = c.values[0, 0]
+    flat = plane.reshape(-1)
+    page_list = [5, 2, 9]
+    for tok, head, ch in [(0, 0, 0), (17, 1, 3), (40, 1, 63), (33, 0, 7)]:
+        off = paged_kv_offset(page_list, tok, head, ch, page, hkv, hd, elem_bytes=1)
+        want = plane[page_list[tok // page], head, tok % page, ch].data_ptr() - plane.data_ptr()
+        assert off * plane.element_size() == want

@@ -131,12 +131,12 @@ def test_quant_special_values():
 
 def _make_kv(num_pages, page, hkv, hd, fp8):
     if fp8:
-        return KVLayer(torch.zeros(num_pages, page, hkv, hd, dtype=torch.uint8, device=DEV),
-                       torch.zeros(num_pages, page, hkv, hd, dtype=torch.uint8, device=DEV),
-                       torch.ones(num_pages, page, hkv, device=DEV), torch.ones(num_pages, page, hkv, device=DEV),
+        return KVLayer(torch.zeros(num_pages, hkv, page, hd, dtype=torch.uint8, device=DEV),
+                       torch.zeros(num_pages, hkv, page, hd, dtype=torch.uint8, device=DEV),
+                       torch.ones(num_pages, hkv, page, device=DEV), torch.ones(num_pages, hkv, page, device=DEV),
                        True, page)
-    return KVLayer(torch.zeros(num_pages, page, hkv, hd, dtype=torch.bfloat16, device=DEV),
-                   torch.zeros(num_pages, page, hkv, hd, dtype=torch.bfloat16, device=DEV), None, None, False, page)
+    return KVLayer(torch.zeros(num_pages, hkv, page, hd, dtype=torch.bfloat16, device=DEV),
+                   torch.zeros(num_pages, hkv, page, hd, dtype=torch.bfloat16, device=DEV), None, None, False, page)
 
 
 def _cpu_kv(kv):
