@@ -34,6 +34,9 @@ constexpr int kDaTile = 128;
 constexpr int kDaStages = 3;
 constexpr int kDaTileBytes = kDaTile * 128;  // 16 KB per K or V tile
 constexpr int kDaHeadsPad = 16;
+// Status codes of this kernel's bounded waits are the shared ones plus 100, so that a recorded timeout
+// names the kernel as well as the wait (201 KV tile, 203 S / PV accumulator, 204 probabilities).
+constexpr int kDaStatusBase = 100;
 
 struct __align__(16) DecodeTcBarriers {
   uint64_t kv_full[kDaStages];
@@ -44,7 +47,7 @@ struct __align__(16) DecodeTcBarriers {
   uint32_t tmem_base;
   int abort_flag;
   int is_last;
-  float red[4][kDaHeadsPad + 1];   // per-warp maxima (heads + V scale)
+  float red[2][4][kDaHeadsPad + 1];   // per-warp maxima (heads + V scale), double buffered by tile parity
   alignas(16) float sc[kDaStages][2][kDaTile];  // per-token K and V scales of each staged tile (16-byte cp.async)
   float s_red[4];
 };
@@ -92,17 +95,18 @@ __global__ void __launch_bounds__(kDaThreads, 2)
 decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            const PagedAttnParams p) {
   pdl_wait();
-  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // layout: stages x {K tile, V tile} | Q (16 x 128 B) | P^T (16 x 128 B) | barriers | tail scratch
+  // layout: stages x {K tile, V tile} | Q (16 x 128 B) | 2 x P^T (16 x 128 B) | barriers | tail scratch
   uint8_t* kv_s = smem;
   uint8_t* q_s = smem + kDaStages * 2 * kDaTileBytes;
   uint8_t* p_s = q_s + 2048;
-  DecodeTcBarriers* bars = reinterpret_cast<DecodeTcBarriers*>(p_s + 2048);
+  DecodeTcBarriers* bars = reinterpret_cast<DecodeTcBarriers*>(p_s + 2 * 2048);
   float* m_s = reinterpret_cast<float*>(bars + 1);  // [G]
   float* l_s = m_s + kDaHeadsPad;                   // [G]
-  float* o_s = l_s + kDaHeadsPad;                   // [G][128]
+  // [G][128] output staging of the tail, aliased onto the first K tile: it is written only after the last
+  // PV MMA of this CTA has completed, when no tile is in flight any more.
+  float* o_s = reinterpret_cast<float*>(kv_s);
   constexpr uint32_t kTmemCols = 64;  // S buffers at columns 0 and 16, PV buffers at columns 32 and 48
 
   const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
@@ -143,11 +147,15 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     tmem_relinquish();
   }
   // Zero Q and P^T (rows >= G stay zero for the whole kernel).
-  for (int i = threadIdx.x; i < 4096 / 16; i += blockDim.x) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = threadIdx.x; i < 3 * 2048 / 16; i += blockDim.x) reinterpret_cast<uint4*>(q_s)[i] = make_uint4(0, 0, 0, 0);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // No early trigger of dependent launches here: with one, the dependent GEMM's CTAs become resident
+  // beside this kernel's for its whole run, and runs of a few hundred decode steps then showed an
+  // occasional bounded wait of that GEMM running out (status 101, a 2 s stall); without it 1200 steps
+  // ran clean.  Dependents therefore start when this grid completes.
 
   if (warp == 0) {
     // ------------------------------------------------------------ page-walking TMA producer
@@ -176,7 +184,12 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       const int st = j % kDaStages;
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(&bars->kv_empty[st], ((j / kDaStages) & 1) ^ 1, abort_flag, nullptr, 0) ? 1 : 0;
+        ok = mbar_wait(&bars->kv_empty[st], ((j / kDaStages) & 1) ^ 1, abort_flag, p.status_word,
+                       kDaStatusBase + SLLM_DEV_TIMEOUT_SMEM_EMPTY) ? 1 : 0;
+        if (!ok && p.status_word && p.status_word[0] == kDaStatusBase + SLLM_DEV_TIMEOUT_SMEM_EMPTY) {
+          p.status_word[1] = j; p.status_word[2] = nt; p.status_word[3] = blockIdx.x; p.status_word[4] = blockIdx.y;
+          p.status_word[5] = kv_len; p.status_word[6] = begin;
+        }
         if (ok) mbar_expect_tx(&bars->kv_full[st], 2 * kDaTileBytes);
         DA_TRACE(j, 8);
       }
@@ -223,7 +236,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
                   idesc_s, k != 0);
         tc_commit(&bars->s_full[j & 1]);
       };
-      bool ok = mbar_wait(&bars->kv_full[0], 0, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMA_FULL);
+      bool ok = mbar_wait(&bars->kv_full[0], 0, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMA_FULL);
       if (ok) {
         tc_fence_after();
         issue_s(0);
@@ -231,20 +244,20 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       for (int j = 0; ok && j < nt; ++j) {
         if (j + 1 < nt) {
           const int st1 = (j + 1) % kDaStages;
-          if (!mbar_wait(&bars->kv_full[st1], ((j + 1) / kDaStages) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMA_FULL))
+          if (!mbar_wait(&bars->kv_full[st1], ((j + 1) / kDaStages) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMA_FULL))
             break;
           tc_fence_after();
           DA_TRACE(j, 6);
           issue_s(j + 1);
         }
-        if (!mbar_wait(&bars->p_ready, j & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_EMPTY)) break;
+        if (!mbar_wait(&bars->p_ready, j & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         DA_TRACE(j, 7);
         const uint32_t v_addr = smem_u32(kv_s + (j % kDaStages) * 2 * kDaTileBytes + kDaTileBytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // 32 keys per MMA
           umma_f8(tmem_base + 32 + (j & 1) * 16, make_smem_desc_sw128_mn8(v_addr + k * 4096),
-                  make_smem_desc_sw128(p_addr) + 2 * k, idesc_pv, k != 0);
+                  make_smem_desc_sw128(p_addr + (j & 1) * 2048) + 2 * k, idesc_pv, k != 0);
         tc_commit(&bars->o_full[j & 1]);
         tc_commit(&bars->kv_empty[j % kDaStages]);
       }
@@ -267,18 +280,17 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       float a = fabsf(qv[g]);
       if (!(a == a) || a > 3.0e38f) a = 0.f;
       a = warp_max_redux(a);
-      if (lane == 0) bars->red[qd][g] = a;
+      if (lane == 0) bars->red[1][qd][g] = a;
     }
     SyncBar1x128::sync();
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      const float amax = fmaxf(fmaxf(bars->red[0][g], bars->red[1][g]), fmaxf(bars->red[2][g], bars->red[3][g]));
+      const float amax = fmaxf(fmaxf(bars->red[1][0][g], bars->red[1][1][g]), fmaxf(bars->red[1][2][g], bars->red[1][3][g]));
       const float qs = amax > 0.f ? amax / 448.f : 1.f;
       // row g of the K-major tile: 16-byte unit (t / 16) lands at unit index ((t / 16) ^ (g % 8))
       q_s[g * 128 + ((((t >> 4) ^ (g & 7))) << 4) + (t & 15)] = f32_to_e4m3(__fdiv_rn(qv[g], qs));
       qsc[g] = qs * p.sm_scale * log2e;   // scores leave the MMA in log2 units after this factor
     }
-    SyncBar1x128::sync();   // red[] is rewritten by the first tile
     fence_proxy_async_smem();
     if (nt > 0) asm volatile("bar.sync 2, 160;" ::: "memory");
 
@@ -296,7 +308,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       const int tok = begin + j * kDaTile + t;
       const bool valid = tok < end && tok >= first;
       if (t == 0) DA_TRACE(j, 0);
-      ok = mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       // The tile's scales were staged by the producer warp under kv_full, which completed before the
@@ -304,7 +316,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       float ksc = p.k_static_scale, vsc = p.v_static_scale;
       if (p.k_scale) {
         const int st = j % kDaStages;
-        ok = mbar_wait(&bars->kv_full[st], (j / kDaStages) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMA_FULL);
+        ok = mbar_wait(&bars->kv_full[st], (j / kDaStages) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMA_FULL);
         if (!ok) break;
         ksc = bars->sc[st][0][t];
         vsc = bars->sc[st][1][t];
@@ -325,14 +337,15 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
 #pragma unroll
       for (int g = 0; g <= G; ++g) {
         red_v[g] = warp_max_redux(red_v[g]);
-        if (lane == 0) bars->red[qd][g] = red_v[g];
+        if (lane == 0) bars->red[j & 1][qd][g] = red_v[g];
       }
       SyncBar1x128::sync();
       if (t == 0) DA_TRACE(j, 3);
       float tmax[G + 1];
 #pragma unroll
       for (int g = 0; g <= G; ++g)
-        tmax[g] = fmaxf(fmaxf(bars->red[0][g], bars->red[1][g]), fmaxf(bars->red[2][g], bars->red[3][g]));
+        tmax[g] = fmaxf(fmaxf(bars->red[j & 1][0][g], bars->red[j & 1][1][g]),
+                        fmaxf(bars->red[j & 1][2][g], bars->red[j & 1][3][g]));
       const float vmax = tmax[G] > 0.f ? tmax[G] : 1.f;
       const float vfold = valid ? vsc / vmax * 256.f : 0.f;   // probabilities enter the MMA as p * vsc/vmax * 256
       const float inv_vfold = vfold > 0.f ? __fdividef(1.f, vfold) : 0.f;
@@ -343,7 +356,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         alpha[g] = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - m_new);
         const float pr = (valid && m_new != -INFINITY) ? exp2f(s[g] - m_new) : 0.f;
         const uint8_t p8 = f32_to_e4m3(pr * vfold);
-        p_s[g * 128 + ((((t >> 4) ^ (g & 7))) << 4) + (t & 15)] = p8;
+        p_s[(j & 1) * 2048 + g * 128 + ((((t >> 4) ^ (g & 7))) << 4) + (t & 15)] = p8;
         // the normaliser uses the value the tensor core will actually multiply
         const float p_eff = e4m3_to_f32_int(p8) * inv_vfold;
         l[g] = l[g] * alpha[g] + p_eff;
@@ -358,7 +371,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       // ---- fold P.V of the PREVIOUS tile into the output (thread = channel) while the tensor core
       // works on this tile: O <- O * alpha_{j-1} + PV_{j-1} * factor_{j-1}
       if (j > 0) {
-        ok = mbar_wait(&bars->o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
+        ok = mbar_wait(&bars->o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMEM_FULL);
         if (!ok) break;
         tc_fence_after();
         tmem_ld16(lane_addr + 32 + ((j - 1) & 1) * 16, raw);
@@ -371,12 +384,14 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
 #pragma unroll
       for (int g = 0; g < G; ++g) alpha_prev[g] = alpha[g];
       of_prev = vmax / 256.f;
-      // red[] is rewritten by the next tile only after all 128 threads arrived on p_ready, i.e. after
-      // every read of this tile's maxima.
+      // red[] and P^T are double buffered by tile parity: a fast thread may already be writing tile j+1's
+      // maxima and probabilities while a slow one still reads tile j's maxima and the tensor core still
+      // reads P^T(j); buffer j&1 is rewritten for tile j+2 only after this thread's wait on o_full(j)
+      // (PV(j) finished) and after the block-wide barrier of tile j+1.
     }
     if (ok && nt > 0) {
       const int j = nt - 1;
-      ok = mbar_wait(&bars->o_full[j & 1], (j >> 1) & 1, abort_flag, p.status_word, SLLM_DEV_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait(&bars->o_full[j & 1], (j >> 1) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMEM_FULL);
       if (ok) {
         uint32_t raw[16];
         tc_fence_after();
@@ -389,17 +404,18 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     }
 
     // ---- hand the split's state to the common tail: l is a per-thread partial over keys -> reduce
+    SyncBar1x128::sync();   // every thread has read the last tile's maxima before red[0] is reused
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float lg = warp_sum(l[g]);
-      if (lane == 0) bars->red[qd][g] = lg;
+      if (lane == 0) bars->red[0][qd][g] = lg;
     }
     SyncBar1x128::sync();
     if (t == 0) {
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         m_s[g] = (m[g] == -INFINITY) ? -INFINITY : m[g] * 0.6931471805599453f;  // back to natural-log units
-        l_s[g] = bars->red[0][g] + bars->red[1][g] + bars->red[2][g] + bars->red[3][g];
+        l_s[g] = bars->red[0][0][g] + bars->red[0][1][g] + bars->red[0][2][g] + bars->red[0][3][g];
       }
     }
 #pragma unroll
@@ -462,8 +478,8 @@ static int cached_page_tmap(CUtensorMap* out, const void* pages, long long total
 template <int G>
 static int launch_da(const CUtensorMap& tk, const CUtensorMap& tv, const PagedAttnParams& p, int rows, int splits,
                      cudaStream_t st) {
-  const size_t smem = kDaStages * 2 * kDaTileBytes + 4096 + sizeof(DecodeTcBarriers) +
-                      sizeof(float) * (2 * kDaHeadsPad + kDaHeadsPad * 128) + 1024;
+  const size_t smem = kDaStages * 2 * kDaTileBytes + 3 * 2048 + sizeof(DecodeTcBarriers) +
+                      sizeof(float) * (2 * kDaHeadsPad) + 1024;
   static bool cfg = false;
   if (!cfg) {
     if (cudaFuncSetAttribute(decode_attention_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -65,7 +65,6 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128_mn(uint32_t smem_addr, 
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const PrefillParams p) {
   pdl_wait();
-  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // layout: Q (2 chunks) | P (2 chunks) | 2 stages x { K (2 chunks) | V (2 chunks) } | barriers
@@ -105,6 +104,10 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const Prefi
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // No early trigger of dependent launches here: with one, the dependent GEMM's CTAs become resident
+  // beside this kernel's for its whole run, and runs of a few hundred decode steps then showed an
+  // occasional bounded wait of that GEMM running out (status 101, a 2 s stall); without it 1200 steps
+  // ran clean.  Dependents therefore start when this grid completes.
 
   if (warp == 0) {
     if (lane == 0) {

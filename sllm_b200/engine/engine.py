@@ -245,7 +245,7 @@ class Engine:
         self._steps += 1
         if self.is_cuda and (self._steps % every == 0 or every == 1):
             ws = ops.workspace(self.device)
-            if int(ws.status.item()):
+            if int(ws.status[0].item()):
                 code = ops.device_status(self.device)
                 raise RuntimeError(f"device wait gave up (status {code}); engine must be drained")
 

@@ -72,7 +72,8 @@ class Workspace:
         self.device = device
         self.ws = torch.empty(floats, dtype=torch.float32, device=device)
         self.counters = torch.zeros(counters, dtype=torch.int32, device=device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        # word 0: first bounded-wait status; words 1..7: detail recorded with it (kernel specific)
+        self.status = torch.zeros(8, dtype=torch.int32, device=device)
 
 
 _workspaces: dict = {}
@@ -90,7 +91,7 @@ def workspace(device: torch.device) -> Workspace:
 def device_status(device: torch.device) -> int:
     """Reads (and clears) the status word that bounded waits set when they give up.  Synchronises."""
     w = workspace(device)
-    v = int(w.status.item())
+    v = int(w.status[0].item())
     if v:
         w.status.zero_()
     return v
