@@ -1,0 +1,165 @@
+"""`sllm-convert-gguf`: writes a GGUF file plus its derived lock.
+
+Kinds:
+  random-llama   seeded random-init weights of a named shape (`--artifact llama3-8b`), for benchmarks and tests
+  hf-llama       a Llama-style Hugging Face checkpoint (config.json + safetensors) from a directory that is first
+                 verified against its model lock (`--lock lock.json --cache DIR`)
+`--weight-format bf16|fp8` selects the resident encoding (fp8 = E4M3FN with FP32 scales per 1x128 block).
+`--dry-run` validates inputs and prints the plan without writing.  (Reference: crates/sllm-server/src/bin/
+sllm-convert-gguf.rs flags --kind --lock --cache --artifact --manifest --output --derived-lock
+--converter-commit --dry-run; crates/sllm-core/src/gguf_convert.rs.)
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+from .common import CliError, StrictParser, emit, run_main
+
+KINDS = ("random-llama", "hf-llama")
+
+
+def _hf_config(raw: dict, weight_format: str):
+    from ..models.config import ModelConfig
+    if raw.get("model_type") not in ("llama", "mistral", "qwen2", "qwen3"):
+        raise CliError(f"unsupported model_type {raw.get('model_type')!r} for kind hf-llama")
+    heads = raw["num_attention_heads"]
+    hd = raw.get("head_dim") or raw["hidden_size"] // heads
+    return ModelConfig(name=raw.get("_name_or_path") or raw["model_type"], family="llama", n_layers=raw["num_hidden_layers"],
+                       d_model=raw["hidden_size"], n_heads=heads, n_kv_heads=raw.get("num_key_value_heads", heads),
+                       head_dim=hd, ffn=raw["intermediate_size"], vocab=raw["vocab_size"],
+                       rope_theta=float(raw.get("rope_theta", 10000.0)), rms_eps=float(raw.get("rms_norm_eps", 1e-5)),
+                       tie_embeddings=bool(raw.get("tie_word_embeddings", False)), weight_format=weight_format,
+                       kv_format="fp8" if weight_format == "fp8" else "bf16",
+                       max_context=min(int(raw.get("max_position_embeddings", 8192)), 131072))
+
+
+def _load_hf(cache, cfg):
+    """Reads the safetensors shards through the verified descriptors and assembles LlamaWeights on the CPU."""
+    import torch
+    from safetensors import safe_open
+    from ..models.llama import LayerWeights, LlamaWeights
+    from ..ops.core import LinearWeight
+    names = [p for p in cache.fds if p.endswith(".safetensors")]
+    tensors = {}
+    for n in sorted(names):
+        with safe_open(os.path.join(cache.root, n), framework="pt") as f:
+            for k in f.keys():
+                tensors[k] = f.get_tensor(k)
+    dt = torch.bfloat16
+
+    def get(name):
+        if name not in tensors:
+            raise CliError(f"checkpoint lacks tensor {name}")
+        return tensors.pop(name).to(dt)
+
+    def lin(w):
+        return LinearWeight.from_dense(w.float() if cfg.weight_format == "fp8" else w.contiguous(),
+                                       "fp8" if cfg.weight_format == "fp8" else "dense")
+
+    layers = []
+    for i in range(cfg.n_layers):
+        p = f"model.layers.{i}."
+        layers.append(LayerWeights(
+            attn_norm=get(p + "input_layernorm.weight"),
+            qkv=lin(torch.cat([get(p + "self_attn.q_proj.weight"), get(p + "self_attn.k_proj.weight"),
+                               get(p + "self_attn.v_proj.weight")], dim=0)),
+            o=lin(get(p + "self_attn.o_proj.weight")),
+            mlp_norm=get(p + "post_attention_layernorm.weight"),
+            gate_up=lin(torch.cat([get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")], dim=0)),
+            down=lin(get(p + "mlp.down_proj.weight"))))
+    embed = get("model.embed_tokens.weight")
+    head = embed if cfg.tie_embeddings else get("lm_head.weight")
+    leftover = [k for k in tensors if not k.endswith("rotary_emb.inv_freq")]
+    if leftover:
+        raise CliError(f"unconsumed tensors in the checkpoint (unknown policy is reject): {leftover[:4]}")
+    return LlamaWeights(embed, layers, get("model.norm.weight"), lin(head), 0)
+
+
+def main(argv=None) -> int:
+    def go():
+        p = StrictParser(prog="sllm-convert-gguf")
+        p.add_argument("--kind", required=True, choices=KINDS)
+        p.add_argument("--lock")
+        p.add_argument("--cache")
+        p.add_argument("--artifact", help="named shape for random-llama (tiny-llama, llama3-8b, llama-draft, ...)")
+        p.add_argument("--manifest", help="optional JSON overriding fields of the model configuration")
+        p.add_argument("--output", required=True)
+        p.add_argument("--derived-lock", required=True)
+        p.add_argument("--converter-commit", default="unknown")
+        p.add_argument("--weight-format", choices=("fp32", "bf16", "fp8"), default="bf16")
+        p.add_argument("--seed", type=int, default=0)
+        p.add_argument("--layers", type=int, default=None)
+        p.add_argument("--dry-run", action="store_true")
+        a = p.parse_args(sys.argv[1:] if argv is None else argv)
+        import torch
+        from ..formats import model_lock as ML
+        from ..models import config as MC
+        from ..models import loader
+        from ..models.llama import init_random_weights
+        overrides = {}
+        if a.manifest:
+            with open(a.manifest, "r", encoding="utf-8") as f:
+                overrides = json.load(f)
+            if not isinstance(overrides, dict):
+                raise CliError("--manifest must hold a JSON object")
+        fps, tokenizer_json, chat_template = [], None, None
+        if a.kind == "random-llama":
+            if a.artifact not in MC.NAMED:
+                raise CliError(f"--artifact must be one of {sorted(MC.NAMED)}")
+            cfg = MC.NAMED[a.artifact]()
+            cfg.weight_format = a.weight_format
+            if a.weight_format != "fp8" and cfg.kv_format == "fp8":
+                cfg.kv_format = "bf16"
+            if a.weight_format == "fp32":
+                cfg.kv_format = "fp32"
+        else:
+            if not (a.lock and a.cache):
+                raise CliError("kind hf-llama needs --lock and --cache")
+            try:
+                lock = ML.read_model_lock(a.lock)
+                cache = lock.verify_cache(a.cache)
+            except (OSError, ML.ModelLockError) as exc:
+                raise CliError(f"source verification failed: {exc}", 3) from None
+            fps = [lock.fingerprint]
+            cfg = _hf_config(json.loads(cache.read("config.json", 1 << 20)), a.weight_format)
+            if "tokenizer.json" in cache.fds:
+                tokenizer_json = cache.read("tokenizer.json").decode("utf-8")
+            if "chat_template.jinja" in cache.fds:
+                chat_template = cache.read("chat_template.jinja", 64 << 10).decode("utf-8")
+        if a.layers:
+            cfg.n_layers = a.layers
+        for k, v in overrides.items():
+            if k not in cfg.to_dict():
+                raise CliError(f"unknown configuration field {k!r} in --manifest")
+            setattr(cfg, k, v)
+        plan = {"kind": a.kind, "model": cfg.name, "layers": cfg.n_layers, "weight_format": cfg.weight_format,
+                "output": a.output, "derived_lock": a.derived_lock, "source_lock_fingerprints": fps}
+        if a.dry_run:
+            emit({"dry_run": True, **plan})
+            return 0
+        if a.kind == "random-llama":
+            dev = "cuda" if torch.cuda.is_available() else "cpu"
+            w = init_random_weights(cfg, dev, seed=a.seed)
+        else:
+            w = _load_hf(cache, cfg)
+            cache.close()
+        dl = loader.export_llama_gguf(cfg, w, a.output, tokenizer_json=tokenizer_json, chat_template=chat_template,
+                                      source_fingerprints=tuple(fps),
+                                      converter_args={"kind": a.kind, "commit": a.converter_commit, "seed": a.seed,
+                                                      "weight_format": a.weight_format})
+        tmp = a.derived_lock + ".tmp"
+        with open(tmp, "w", encoding="utf-8") as f:
+            json.dump(dl, f, sort_keys=True, indent=1)
+            f.flush()
+            os.fsync(f.fileno())
+        os.replace(tmp, a.derived_lock)
+        emit({"written": True, **plan, "size_bytes": dl["output"]["size_bytes"], "sha256": dl["output"]["sha256"],
+              "fingerprint": dl["fingerprint"]})
+        return 0
+    return run_main(go)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
