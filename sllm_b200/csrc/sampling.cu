@@ -207,9 +207,46 @@ token_select_kernel(const __nv_bfloat16* __restrict__ logits, int ld, const floa
   }
 }
 
+// ---------------------------------------------------------------- speculative verify (greedy)
+// One thread per sequence.  draft[b, 0..width) holds the drafted tokens (draft_len[b] of them are real),
+// target[b, 0..width] the target's selection after each row of the verify block.  accept[b] = length of the
+// longest prefix with draft == target (or, with `forced`, with forced[b, i] != 0: benchmark mode that keeps the
+// verify compute but fixes the acceptance pattern); next[b] = target[b, accept[b]].  The kernel also writes
+// the new published length new_len[b] = base_len[b] + accept[b] so that the KV truncation and the next step's
+// positions can be produced without a host round trip.
+__global__ void spec_verify_greedy_kernel(const int* __restrict__ draft, const int* __restrict__ draft_len,
+                                          const int* __restrict__ target, const unsigned char* __restrict__ forced,
+                                          const int* __restrict__ base_len, int width, int batch,
+                                          int* __restrict__ accept, int* __restrict__ next, int* __restrict__ new_len) {
+  pdl_wait();
+  pdl_trigger();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int n = min(draft_len[b], width);
+  int a = 0;
+  for (; a < n; ++a) {
+    const bool ok = forced ? forced[b * width + a] != 0 : draft[b * width + a] == target[b * (width + 1) + a];
+    if (!ok) break;
+  }
+  accept[b] = a;
+  next[b] = target[b * (width + 1) + a];
+  if (new_len) new_len[b] = (base_len ? base_len[b] : 0) + a;
+}
+
 }  // namespace sllm
 
 using namespace sllm;
+
+SLLM_EXPORT int sllm_spec_verify_greedy(const int* draft, const int* draft_len, const int* target,
+                                        const unsigned char* forced, const int* base_len, int width, int batch,
+                                        int* accept, int* next, int* new_len, void* stream) {
+  if (!draft || !draft_len || !target || !accept || !next || width < 1 || width > 8 || batch <= 0)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  cudaError_t e = launch_kernel(spec_verify_greedy_kernel, dim3((batch + 127) / 128), dim3(128), 0,
+                                static_cast<cudaStream_t>(stream), 1u, draft, draft_len, target, forced, base_len, width,
+                                batch, accept, next, new_len);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
 
 // rows_cfg: device array of {float temperature, top_p, min_p; int top_k; u64 seed, counter} (32 bytes).
 // ws: 2 * rows * n floats.  out: rows records of 16 bytes.

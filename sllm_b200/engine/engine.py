@@ -156,6 +156,35 @@ class Engine:
             s.num_computed = len(s.tokens)
         return toks if sample else out
 
+    def extend(self, seqs: list, sample: bool = True):
+        """Runs every not-yet-computed token of each sequence as its own row (a speculative verify block, or
+        any multi-token append) and returns, per sequence, the greedy token after each of those rows (or the
+        logits [rows, vocab] with sample=False).  The block-table rows of one sequence are shared by its rows."""
+        pool = self.cache.pool
+        for s in seqs:
+            pool.reserve(s.seq_id, len(s.tokens))
+        table = torch.zeros((len(seqs), self.max_blocks), dtype=torch.int32)
+        pool.fill_block_table([s.seq_id for s in seqs], table)
+        d_table = table.to(self.device, non_blocking=True) if self.is_cuda else table
+        parts = [s.tokens[s.num_computed:] for s in seqs]
+        if any(not p for p in parts):
+            raise ValueError("extend needs at least one uncomputed token per sequence")
+        b = make_prefill_batch(parts, d_table, self.device, [s.num_computed for s in seqs], last_only=False)
+        self.h2d_bytes += table.numel() * 4 + b.num_tokens * 12
+        res = self.model.greedy(b, self.cache) if sample else self.model.forward(b, self.cache)
+        self._table_key = None
+        self._check_status(every=1)
+        out, r0 = [], 0
+        flat = res.tolist() if sample else None
+        if sample:
+            self.d2h_bytes += 4 * b.num_tokens
+        for s, p in zip(seqs, parts):
+            out.append(flat[r0:r0 + len(p)] if sample else res[r0:r0 + len(p)])
+            r0 += len(p)
+            pool.commit(s.seq_id, len(s.tokens))
+            s.num_computed = len(s.tokens)
+        return out
+
     # ------------------------------------------------------------------ decode
     def _decode_body(self, n: int, greedy: bool):
         b = ForwardBatch(self.d_tokens[:n], self.d_positions[:n], self.d_seq_index[:n], self.d_kv_lens[:n],

@@ -220,6 +220,7 @@ class EngineLoop:
         self.engine = engine
         self.prefix_cache = prefix_cache
         self.context_policy = context_policy
+        self.speculative = None              # engine.speculative.SpeculativeDecoder for greedy requests
         self.model_id = model_id
         self.planner = BatchPlanner(max_batch or engine.max_batch, prefill_interval,
                                     max_prefill_batch=min(8, max_batch or engine.max_batch))
@@ -391,14 +392,61 @@ class EngineLoop:
             else:
                 if self.context_policy is not None and not self.context_policy.is_disabled:
                     self._shift_full_windows(reqs)
-                logits = eng.decode([r.seq for r in reqs], sample=False)
-                self._select_and_publish(reqs, logits, outcomes)
+                spec = [r for r in reqs if self.speculative is not None and r.chain is None and r.mask_fn is None]
+                rest = [r for r in reqs if r not in spec]
+                if spec:
+                    self._speculative_round(spec, outcomes)
+                if rest:
+                    logits = eng.decode([r.seq for r in rest], sample=False)
+                    self._select_and_publish(rest, logits, outcomes)
         except Exception as exc:
             for r in reqs:
                 if r.rid not in outcomes:
                     r.finish_reason = f"error:{type(exc).__name__}:{exc}"
                     outcomes[r.rid] = "failed"
         return outcomes
+
+    def _speculative_round(self, reqs: list, outcomes: dict) -> None:
+        """Draft + verify for greedy requests; every accepted token goes through the same publication path."""
+        budgets = [r.max_new_tokens - r.generated for r in reqs]
+        new = self.speculative.step([r.seq for r in reqs], budgets)
+        for r, toks in zip(reqs, new):
+            del r.seq.tokens[len(r.seq.tokens) - len(toks):]      # re-appended one by one below
+            for i, tok in enumerate(toks):
+                self._publish_token(r, tok, None, outcomes)
+                if outcomes[r.rid] != "continue":
+                    # the request ended inside the block: forget the KV of the unpublished tail
+                    if i + 1 < len(toks):
+                        self.engine.rollback(r.seq, len(r.seq.tokens))
+                    break
+            if outcomes[r.rid] != "continue":
+                self.speculative.release(r.seq)
+
+    def _publish_token(self, r: GenRequest, tok: int, selection, outcomes: dict) -> None:
+        if r.chain is not None:
+            r.chain.accept(tok)
+        r.seq.tokens.append(tok)
+        r.generated += 1
+        if r.first_token_at is None:
+            r.first_token_at = time.monotonic()
+        keep = True
+        if r.on_token:
+            keep = r.on_token(tok, selection) is not False
+        if tok in r.stop_tokens:
+            r.finish_reason = "stop"
+            outcomes[r.rid] = "finished"
+        elif not keep:
+            r.finish_reason = r.finish_reason or "stop"
+            outcomes[r.rid] = "finished"
+        elif r.generated >= r.max_new_tokens:
+            r.finish_reason = "length"
+            outcomes[r.rid] = "finished"
+        elif len(r.seq.tokens) >= self.engine.cfg.max_context and (
+                self.context_policy is None or self.context_policy.is_disabled):
+            r.finish_reason = "length"
+            outcomes[r.rid] = "finished"
+        else:
+            outcomes[r.rid] = "continue"
 
     def _release_prefix(self, r: GenRequest) -> None:
         rel = getattr(r.prefix_seq, "release", None)
@@ -461,30 +509,7 @@ class EngineLoop:
                     chain = r.chain or S.SamplerChain(S.SamplerChainConfig())
                     selection = chain.select(host_logits[i], device_argmax=greedy_tokens[i], valid_mask=mask)
                     tok = selection.token
-                if r.chain is not None:
-                    r.chain.accept(tok)
-                r.seq.tokens.append(tok)
-                r.generated += 1
-                if r.first_token_at is None:
-                    r.first_token_at = time.monotonic()
-                keep = True
-                if r.on_token:
-                    keep = r.on_token(tok, selection) is not False
-                if tok in r.stop_tokens:
-                    r.finish_reason = "stop"
-                    outcomes[r.rid] = "finished"
-                elif not keep:
-                    r.finish_reason = r.finish_reason or "stop"
-                    outcomes[r.rid] = "finished"
-                elif r.generated >= r.max_new_tokens:
-                    r.finish_reason = "length"
-                    outcomes[r.rid] = "finished"
-                elif len(r.seq.tokens) >= self.engine.cfg.max_context and (
-                        self.context_policy is None or self.context_policy.is_disabled):
-                    r.finish_reason = "length"
-                    outcomes[r.rid] = "finished"
-                else:
-                    outcomes[r.rid] = "continue"
+                self._publish_token(r, tok, selection, outcomes)
             except Exception as exc:
                 r.finish_reason = f"error:{type(exc).__name__}:{exc}"
                 outcomes[r.rid] = "failed"

@@ -304,3 +304,26 @@ def test_device_token_selector():
     bad[0, 3] = float("nan")
     rec = S.device_select(bad[:1], cfg[:1]).cpu().numpy().view(S.SELECTOR_RECORD_DTYPE)
     assert rec["status"][0] == 1 and rec["token"][0] == -1
+
+
+@pytest.mark.gpu
+def test_spec_verify_greedy_kernel():
+    from sllm_b200.engine import speculative as SP
+    torch.manual_seed(0)
+    b, w = 37, 4
+    target = torch.randint(0, 50, (b, w + 1), device=DEV, dtype=torch.int32)
+    draft = target[:, :w].clone()
+    flip = torch.rand(b, w, device=DEV) < 0.3
+    draft[flip] += 1
+    dlen = torch.randint(0, w + 1, (b,), device=DEV, dtype=torch.int32)
+    base = torch.randint(10, 100, (b,), device=DEV, dtype=torch.int32)
+    acc, nxt, new_len = SP.device_verify_greedy(draft, dlen, target, base)
+    forced = (torch.rand(b, w, device=DEV) < 0.7).to(torch.uint8)
+    acc_f, nxt_f, _ = SP.device_verify_greedy(draft, dlen, target, base, forced)
+    for i in range(b):
+        d = draft[i, :int(dlen[i])].tolist()
+        t = target[i, :len(d) + 1].tolist()
+        n, tok = SP.verify_greedy(d, t)
+        assert (int(acc[i]), int(nxt[i]), int(new_len[i])) == (n, tok, int(base[i]) + n)
+        n2, tok2 = SP.verify_greedy(d, t, forced[i, :len(d)].bool().tolist())
+        assert (int(acc_f[i]), int(nxt_f[i])) == (n2, tok2)
