@@ -1,0 +1,162 @@
+"""4-bit block-scaled weights (MXFP4 / NVFP4): resident layout, the tcgen05 W4A16 GEMM and its CPU oracle.
+
+File formats keep the layouts of the reference (codes: low nibble = even element; MXFP4 scales E8M0
+[N, K/32]; NVFP4 scales E4M3 [N, K/16] plus an FP32 tensor scale - docs/quantization/nvfp4.md:18-31,
+docs/formats/gguf.md:40-41).  `W4Weight.from_file_layout` repacks them once at load into what the kernel
+streams: rows padded to 128 and K to 128, nibbles of every eight elements reordered to
+(e0,e2,e4,e6,e1,e3,e5,e7), and codes and scales tiled together as
+[group][row tile][K chunk]{128 rows x 64 B codes | 128 rows x (4|8) B scales} so that one CTA reads one
+contiguous stretch of HBM with a single bulk copy per chunk.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..formats import codecs
+from . import _lib
+
+MAX_E8M0_CODE = 144
+
+
+@dataclass
+class W4Weight:
+    fmt: str                    # mxfp4 | nvfp4
+    groups: int
+    n: int                      # output features per group
+    k: int                      # input features
+    n_rows: int                 # n padded to 128
+    k_pad: int                  # k padded to 128
+    tiles: torch.Tensor         # uint8 [groups, n_rows / 128, k_pad / 128, 8192 + 128 * (4 | 8)]
+    tensor_scale: Optional[torch.Tensor]   # fp32 [groups] (nvfp4)
+    file_packed: Optional[np.ndarray] = None    # kept on CPU weights for the oracle
+    file_scales: Optional[np.ndarray] = None
+
+    @property
+    def block(self) -> int:
+        return 32 if self.fmt == "mxfp4" else 16
+
+    @staticmethod
+    def from_file_layout(fmt: str, packed: np.ndarray, scales: np.ndarray, k: int, tensor_scale=None,
+                         device="cpu", keep_file: bool = False) -> "W4Weight":
+        """packed: uint8 [G, N, ceil(K/2)] (or [N, ...]); scales: uint8 [G, N, ceil(K/block)]."""
+        if packed.ndim == 2:
+            packed, scales = packed[None], scales[None]
+        g, n, kb = packed.shape
+        block = 32 if fmt == "mxfp4" else 16
+        sb = 128 // block
+        if fmt == "mxfp4" and int(scales.max(initial=0)) > MAX_E8M0_CODE:
+            raise ValueError("MXFP4 block scale above 2^17 is outside the kernel's exact range")
+        n_rows, k_pad = (n + 127) // 128 * 128, (k + 127) // 128 * 128
+        codes = np.zeros((g, n_rows, k_pad), dtype=np.uint8)
+        codes[:, :n, :k] = codecs.unpack_nibbles(packed, k)
+        c8 = codes.reshape(g, n_rows, k_pad // 8, 8)
+        order = [0, 2, 4, 6, 1, 3, 5, 7]                 # nibble position p holds element order[p]
+        re = c8[..., order]
+        words = np.zeros(re.shape[:-1], dtype=np.uint32)
+        for pos in range(8):
+            words |= re[..., pos].astype(np.uint32) << (4 * pos)
+        rt, kc = n_rows // 128, k_pad // 128
+        res_packed = words.view(np.uint8).reshape(g, rt, 128, kc, 64).transpose(0, 1, 3, 2, 4).reshape(g, rt, kc, 8192)
+        sc = np.zeros((g, n_rows, k_pad // block), dtype=np.uint8)
+        sc[:, :n, :scales.shape[2]] = scales
+        sc_t = sc.reshape(g, rt, 128, kc, sb).transpose(0, 1, 3, 2, 4).reshape(g, rt, kc, 128 * sb)
+        tiled = np.concatenate([res_packed, sc_t], axis=3)
+        ts = None
+        if fmt == "nvfp4":
+            tsv = np.ones(g, dtype=np.float32) if tensor_scale is None else np.asarray(tensor_scale, dtype=np.float32).reshape(g)
+            ts = torch.from_numpy(tsv.copy()).to(device)
+        return W4Weight(fmt, g, n, k, n_rows, k_pad, torch.from_numpy(np.ascontiguousarray(tiled)).to(device), ts,
+                        packed.copy() if keep_file else None, scales.copy() if keep_file else None)
+
+    @staticmethod
+    def quantize(fmt: str, w: torch.Tensor, device="cpu", keep_file: bool = True) -> "W4Weight":
+        """w: float [G, N, K] or [N, K]."""
+        w3 = w.float().cpu().numpy()
+        if w3.ndim == 2:
+            w3 = w3[None]
+        pk, sc, ts = [], [], []
+        for gi in range(w3.shape[0]):
+            if fmt == "mxfp4":
+                p, s = codecs.quantize_mxfp4(w3[gi])
+            else:
+                p, s, t = codecs.quantize_nvfp4(w3[gi])
+                ts.append(t)
+            pk.append(p)
+            sc.append(s)
+        return W4Weight.from_file_layout(fmt, np.stack(pk), np.stack(sc), w3.shape[2], ts or None, device, keep_file)
+
+    def dequantized(self, group: int = 0) -> torch.Tensor:
+        """fp32 [n, k] of one group from the resident layout (exact)."""
+        rt, kc = self.n_rows // 128, self.k_pad // 128
+        t = self.tiles.cpu().numpy()[group]
+        pk = np.ascontiguousarray(t[:, :, :8192].reshape(rt, kc, 128, 64).transpose(0, 2, 1, 3)).reshape(self.n_rows, self.k_pad // 2)
+        words = pk.view(np.uint32).reshape(self.n_rows, self.k_pad // 8)
+        order = [0, 2, 4, 6, 1, 3, 5, 7]
+        codes = np.zeros((self.n_rows, self.k_pad // 8, 8), dtype=np.uint8)
+        for pos in range(8):
+            codes[..., order[pos]] = (words >> (4 * pos)) & 0xF
+        vals = codecs.decode_e2m1(codes.reshape(self.n_rows, self.k_pad))
+        sb = 128 // self.block
+        sc = t[:, :, 8192:].reshape(rt, kc, 128, sb).transpose(0, 2, 1, 3).reshape(self.n_rows, self.k_pad // self.block)
+        s = codecs.decode_e8m0(sc) if self.fmt == "mxfp4" else codecs.decode_e4m3fn(sc)
+        if self.tensor_scale is not None:
+            s = s * np.float32(float(self.tensor_scale[group].item()))
+        out = vals * np.repeat(s, self.block, axis=1)
+        return torch.from_numpy(out[:self.n, :self.k].astype(np.float32))
+
+    def nbytes(self) -> int:
+        return self.tiles.numel()
+
+
+def _bn_for(tokens: int) -> int:
+    return 16 if tokens <= 16 else 32 if tokens <= 32 else 64 if tokens <= 64 else 128
+
+
+def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = None, tok_off: Optional[torch.Tensor] = None,
+              tok_scale: Optional[torch.Tensor] = None, max_group_tokens: Optional[int] = None, splits: int = 0) -> torch.Tensor:
+    """y[t, :] = x[t, :] @ W_g(t)^T (* tok_scale[t]) (+ residual).  Dense when tok_off is None (groups must be 1);
+    grouped otherwise: tokens of group g are rows tok_off[g] .. tok_off[g + 1] of x."""
+    t, k = x.shape
+    if k != w.k:
+        raise ValueError("input width does not match the weight")
+    if not x.is_cuda:
+        out = torch.zeros((t, w.n), dtype=torch.float32)
+        offs = [0, t] if tok_off is None else tok_off.tolist()
+        xf = x.float()
+        for g in range(w.groups):
+            a, b = offs[g], offs[g + 1]
+            if b > a:
+                out[a:b] = xf[a:b] @ w.dequantized(g).t()
+        if tok_scale is not None:
+            out = out * tok_scale.float()[:, None]
+        if residual is not None:
+            out = out + residual.float()
+        return out if x.dtype == torch.float32 else out.to(torch.bfloat16)
+    from .core import _p, _stream, workspace
+    P, I, L, F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_gemm_w4", (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I,
+                                                               P, L, P, I, P, P]))
+    if w.groups > 1 and tok_off is None:
+        raise ValueError("grouped weights need token offsets")
+    x = x.contiguous() if x.stride(1) != 1 or x.stride(0) % 8 else x
+    y = torch.empty((t, w.n), dtype=torch.bfloat16, device=x.device)
+    mgt = max_group_tokens or t
+    bn = _bn_for(mgt if tok_off is None else min(mgt, 32))
+    k_chunks = w.k_pad // 128
+    if splits <= 0:
+        ctas = (w.n_rows // 128) * (w.groups if tok_off is None else max(1, min(w.groups, t))) * ((min(mgt, t) + bn - 1) // bn)
+        splits = 1
+        while ctas * splits < 148 and splits * 2 <= max(1, k_chunks // 4) and splits < 16:
+            splits *= 2
+    wsp = workspace(x.device)
+    rc = _lib.kernels().sllm_gemm_w4(_p(w.tiles), _p(w.tensor_scale), _p(x), _p(y), _p(residual), _p(tok_off),
+                                     _p(tok_scale), 0 if w.fmt == "mxfp4" else 1, w.groups, w.n_rows, w.n, w.k_pad, w.k,
+                                     x.stride(0), t, mgt, y.stride(0), bn, splits, 0, _p(wsp.ws), wsp.ws.numel(),
+                                     _p(wsp.counters), wsp.counters.numel(), _p(wsp.status), _stream())
+    _lib.check(rc, "gemm_w4")
+    return y

@@ -117,6 +117,39 @@ def bench_gemm(m, n, k, fp8, reps, graph=False):
             "TFLOPs": flops / t / 1e12, "roofline_us": roof * 1e6, "fraction": roof / t, "fraction_basis": tag}
 
 
+def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False):
+    """Dense (groups = 1) or grouped W4A16 GEMM; grouped: m tokens spread evenly over the groups."""
+    from ..ops.w4 import W4Weight, linear_w4
+    dev = "cuda"
+    g = max(1, groups)
+    import numpy as np
+    rng = np.random.default_rng(0)
+    blk = 32 if fmt == "mxfp4" else 16
+    packed = rng.integers(0, 256, (g, n, k // 2), dtype=np.uint8)
+    scales = rng.integers(118, 126, (g, n, k // blk), dtype=np.uint8) if fmt == "mxfp4" else \
+        rng.integers(0x30, 0x48, (g, n, k // blk), dtype=np.uint8)
+    w = W4Weight.from_file_layout(fmt, packed, scales, k, None, dev)
+    x = torch.randn(m, k, device=dev).bfloat16()
+    off = None
+    if g > 1:
+        per = [m // g + (1 if i < m % g else 0) for i in range(g)]
+        off = torch.tensor([0] + list(np.cumsum(per)), dtype=torch.int32, device=dev)
+    call = lambda w_: linear_w4(x, w_, tok_off=off, max_group_tokens=m)
+    wbytes = w.nbytes()
+    if graph:
+        ws = [w] + [W4Weight(w.fmt, w.groups, w.n, w.k, w.n_rows, w.k_pad, w.tiles.clone(), w.tensor_scale)
+                    for _ in range(_copies(wbytes) - 1)]
+        t = timed_graph([(lambda w_=w_: call(w_)) for w_ in ws], reps)
+    else:
+        t = timed(lambda: call(w), reps)
+    bw, fl, tag = peaks()
+    bytes_ = wbytes + 2 * m * k + 2 * m * n
+    flops = 2.0 * m * n * k
+    roof = max(bytes_ / bw, flops / fl)
+    return {"op": "gemm_w4", "fmt": fmt, "m": m, "n": n, "k": k, "groups": g, "us": t * 1e6, "GBps": bytes_ / t / 1e9,
+            "TFLOPs": flops / t / 1e12, "roofline_us": roof * 1e6, "fraction": roof / t, "fraction_basis": tag}
+
+
 def _kv(batch, ctx, hkv, hd, fp8, page=16):
     dev = "cuda"
     blocks = (ctx + page - 1) // page + 1
@@ -170,7 +203,9 @@ def bench_prefill(seqs, length, hq, hkv, reps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "attention", "prefill", "decode-gemms"])
+    ap.add_argument("--op", required=True, choices=["gemm", "gemm-w4", "attention", "prefill", "decode-gemms"])
+    ap.add_argument("--fmt", default="nvfp4", choices=["nvfp4", "mxfp4"])
+    ap.add_argument("--groups", type=int, default=1)
     ap.add_argument("--m", type=int, default=32)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -188,6 +223,8 @@ def main():
     a = ap.parse_args()
     if a.op == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.fp8, a.reps, a.graph)))
+    elif a.op == "gemm-w4":
+        print(json.dumps(bench_gemm_w4(a.m, a.n, a.k, a.fmt, a.groups, a.reps, a.graph)))
     elif a.op == "attention":
         print(json.dumps(bench_attention(a.batch, a.ctx, a.hq, a.hkv, a.hd, a.fp8, a.reps, a.graph)))
     elif a.op == "prefill":

@@ -1,6 +1,7 @@
 """Numerics of every CUDA kernel against a plain PyTorch fp32 restatement of the same op."""
 import math
 
+import numpy as np
 import pytest
 import torch
 
@@ -327,3 +328,41 @@ def test_spec_verify_greedy_kernel():
         assert (int(acc[i]), int(nxt[i]), int(new_len[i])) == (n, tok, int(base[i]) + n)
         n2, tok2 = SP.verify_greedy(d, t, forced[i, :len(d)].bool().tolist())
         assert (int(acc_f[i]), int(nxt_f[i])) == (n2, tok2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("t,n,k", [(5, 256, 256), (32, 384, 2880), (100, 200, 512), (1, 1024, 4096), (130, 128, 128)])
+def test_gemm_w4_dense(fmt, t, n, k):
+    from sllm_b200.ops.w4 import W4Weight, linear_w4
+    torch.manual_seed(t + n)
+    w = torch.randn(n, k) * 0.05
+    wq = W4Weight.quantize(fmt, w, device=DEV)
+    x = torch.randn(t, k, device=DEV).bfloat16()
+    res = torch.randn(t, n, device=DEV).bfloat16()
+    want = x.float().cpu() @ wq.dequantized(0).t()
+    for splits in (1, 0, 4):
+        got = linear_w4(x, wq, splits=splits).float().cpu()
+        assert rel_err(got, want) < 6e-3, (splits, rel_err(got, want))
+    got = linear_w4(x, wq, residual=res).float().cpu()
+    assert rel_err(got, want + res.float().cpu()) < 6e-3
+    assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+def test_gemm_w4_grouped(fmt):
+    from sllm_b200.ops.w4 import W4Weight, linear_w4
+    torch.manual_seed(7)
+    g, n, k = 6, 320, 384
+    w = torch.randn(g, n, k) * 0.05
+    wq = W4Weight.quantize(fmt, w, device=DEV)
+    counts = [3, 0, 17, 1, 40, 2]
+    t = sum(counts)
+    off = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32, device=DEV)
+    x = torch.randn(t, k, device=DEV).bfloat16()
+    sc = torch.rand(t, device=DEV)
+    want = linear_w4(x.cpu(), W4Weight.quantize(fmt, w), tok_off=off.cpu(), tok_scale=sc.cpu()).float()
+    got = linear_w4(x, wq, tok_off=off, tok_scale=sc, max_group_tokens=t).float().cpu()
+    assert rel_err(got, want) < 6e-3
+    assert ops.device_status(torch.device(DEV)) == 0
