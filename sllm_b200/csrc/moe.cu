@@ -1,0 +1,336 @@
+// Mixture-of-experts routing and token movement.
+//
+//   moe_route        router logits [T, E] -> top-k experts per token and their weights (softmax over the k
+//                    selected logits, or the selected entries of the softmax over all experts);
+//   moe_permute      groups the T x k assignments by expert: tok_off[E_local + 1], perm_src[P] (source token of
+//                    each permuted row), perm_dst[T, k] (row of each assignment, -1 when the expert is not local),
+//                    perm_w[P] (routing weight of each permuted row);
+//   moe_gather       X_perm[p, :] = X[perm_src[p], :];
+//   moe_combine      Y[t, :] = residual[t, :] + sum_j Y_perm[perm_dst[t, j], :]  (weights were applied by the
+//                    expert GEMM epilogue);
+//   moe_combine_allreduce   expert-parallel combine fused with the cross-rank reduction: every rank adds up its
+//                    local experts' rows for a token block, stores the partial block straight into every peer's
+//                    receive slot over NVLink, raises a flag per (block, source rank), waits (bounded) for the
+//                    peers' flags and sums the partials in rank order, so all ranks hold bit-identical results.
+//                    Activations are replicated across the expert-parallel ranks (they leave the attention
+//                    all-reduce that way), so dispatch moves no data: each rank gathers the tokens routed to its
+//                    own experts from its local copy.
+//
+// Reference counterparts: reference_sparse_moe_route (crates/sllm-core/src/moe.rs:229), the routing / expert
+// kernels of native/hip/src/moe_expert_kernel.hip.cpp (one request at a time, no expert parallelism).
+#include "common.cuh"
+#include "api.h"
+
+namespace sllm {
+
+constexpr int kMaxTopK = 8;
+constexpr int kMaxExperts = 256;
+
+// One warp per token.  Ties go to the lower expert index; NaN logits count as -inf.
+__global__ void moe_route_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int tokens, int experts, int top_k,
+                                 int softmax_all, int* __restrict__ out_idx, float* __restrict__ out_w) {
+  pdl_wait();
+  pdl_trigger();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= tokens) return;
+  float v[kMaxExperts / 32];
+#pragma unroll
+  for (int i = 0; i < kMaxExperts / 32; ++i) {
+    const int e = i * 32 + lane;
+    float x = e < experts ? __bfloat162float(logits[static_cast<size_t>(warp) * ld + e]) : -INFINITY;
+    v[i] = (x == x) ? x : -INFINITY;
+  }
+  float denom_all = 0.f, mx_all = -INFINITY;
+  if (softmax_all) {
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) mx_all = fmaxf(mx_all, v[i]);
+    mx_all = warp_max(mx_all);
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) denom_all += (v[i] == -INFINITY) ? 0.f : __expf(v[i] - mx_all);
+    denom_all = warp_sum(denom_all);
+  }
+  float sel_v[kMaxTopK];
+  int sel_i[kMaxTopK];
+  for (int j = 0; j < top_k; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i) {
+      const int e = i * 32 + lane;
+      if (v[i] > best || (v[i] == best && e < bi && v[i] != -INFINITY)) {
+        best = v[i];
+        bi = e;
+      }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ob > best || (ob == best && oi < bi)) {
+        best = ob;
+        bi = oi;
+      }
+    }
+    if (bi == 0x7fffffff) bi = j;     // fewer finite logits than k: fall back to distinct low indices
+    sel_v[j] = best;
+    sel_i[j] = bi;
+#pragma unroll
+    for (int i = 0; i < kMaxExperts / 32; ++i)
+      if (i * 32 + lane == bi) v[i] = -INFINITY;
+  }
+  if (lane == 0) {
+    float w[kMaxTopK];
+    float sum = 0.f;
+    const float m0 = softmax_all ? mx_all : sel_v[0];
+    for (int j = 0; j < top_k; ++j) {
+      w[j] = sel_v[j] == -INFINITY ? 0.f : __expf(sel_v[j] - m0);
+      sum += w[j];
+    }
+    // mode 0: softmax over the selected logits; mode 1: probabilities of the softmax over all experts
+    const float inv = softmax_all ? (denom_all > 0.f ? 1.f / denom_all : 0.f) : (sum > 0.f ? 1.f / sum : 0.f);
+    for (int j = 0; j < top_k; ++j) {
+      out_idx[warp * top_k + j] = sel_i[j];
+      out_w[warp * top_k + j] = sum > 0.f ? w[j] * inv : 1.f / top_k;
+    }
+  }
+}
+
+// Single CTA.  Counts per local expert in shared memory, exclusive scan, then placement; assignments keep token
+// order inside an expert (two passes over the assignments in index order, the second with a running cursor per
+// expert owned by one thread), so the layout is deterministic.
+__global__ void moe_permute_kernel(const int* __restrict__ idx, const float* __restrict__ w, int tokens, int top_k,
+                                   int e_lo, int e_hi, int* __restrict__ tok_off, int* __restrict__ perm_src,
+                                   int* __restrict__ perm_dst, float* __restrict__ perm_w) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int counts[kMaxExperts + 1];
+  const int n_local = e_hi - e_lo;
+  const int total = tokens * top_k;
+  for (int i = threadIdx.x; i <= n_local; i += blockDim.x) counts[i] = 0;
+  __syncthreads();
+  for (int a = threadIdx.x; a < total; a += blockDim.x) {
+    const int e = idx[a];
+    if (e >= e_lo && e < e_hi) atomicAdd(&counts[e - e_lo], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < n_local; ++e) {
+      const int c = counts[e];
+      counts[e] = run;
+      tok_off[e] = run;
+      run += c;
+    }
+    counts[n_local] = run;
+    tok_off[n_local] = run;
+  }
+  __syncthreads();
+  // thread e walks all assignments in order and places those of its expert: stable and race free
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) {
+    int cur = counts[e];
+    for (int a = 0; a < total; ++a) {
+      if (idx[a] == e + e_lo) {
+        perm_src[cur] = a / top_k;
+        perm_w[cur] = w[a];
+        perm_dst[a] = cur;
+        ++cur;
+      }
+    }
+  }
+  for (int a = threadIdx.x; a < total; a += blockDim.x) {
+    const int e = idx[a];
+    if (e < e_lo || e >= e_hi) perm_dst[a] = -1;
+  }
+}
+
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int* __restrict__ perm_src,
+                                  const int* __restrict__ tok_off, int n_local, __nv_bfloat16* __restrict__ xp, int d) {
+  pdl_wait();
+  pdl_trigger();
+  const int p = blockIdx.x;
+  if (p >= tok_off[n_local]) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(perm_src[p]) * ldx);
+  uint4* dst = reinterpret_cast<uint4*>(xp + static_cast<size_t>(p) * d);
+  for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+__device__ __forceinline__ void add8(float (&acc)[8], const uint4 v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
+  uint4 o;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  return o;
+}
+
+// One CTA per token: sum of the (local) expert rows in slot order, plus the residual.
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ yp, const int* __restrict__ perm_dst, int top_k,
+                                   const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ y, int d) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < d / 8; i += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const int p = perm_dst[t * top_k + j];
+      if (p >= 0) add8(acc, reinterpret_cast<const uint4*>(yp + static_cast<size_t>(p) * d)[i]);
+    }
+    if (residual) add8(acc, reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * d)[i]);
+    reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * d)[i] = pack8(acc);
+  }
+}
+
+struct EpPeers {
+  int world, rank;
+  __nv_bfloat16* recv[8];   // recv[p]: rank p's receive area [2 parities][world][max_tokens * d] as mapped here
+  uint32_t* flags[8];       // flags[p]: rank p's flags [world][max_blocks]
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// grid.x = token blocks of `rows_per_block` tokens.  cap = max_tokens * d elements per (parity, source) slot.
+__global__ void moe_combine_allreduce_kernel(EpPeers pe, const __nv_bfloat16* __restrict__ yp,
+                                             const int* __restrict__ perm_dst, int top_k,
+                                             const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ y,
+                                             int tokens, int d, int rows_per_block, long long cap, int max_blocks,
+                                             uint32_t* __restrict__ epoch, int* status) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ uint32_t s_e;
+  __shared__ int s_ok;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) {
+    s_e = epoch[b] + 1;
+    epoch[b] = s_e;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t e = s_e;
+  const long long par = static_cast<long long>(e & 1) * pe.world * cap;
+  const int t0 = b * rows_per_block;
+  const int t1 = min(tokens, t0 + rows_per_block);
+  const int vec = d / 8;
+  // 1. local partial rows -> every rank's slot [parity][my rank] (own slot included)
+  for (int i = threadIdx.x; i < (t1 - t0) * vec; i += blockDim.x) {
+    const int t = t0 + i / vec, c = i % vec;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const int p = perm_dst[t * top_k + j];
+      if (p >= 0) add8(acc, reinterpret_cast<const uint4*>(yp + static_cast<size_t>(p) * d)[c]);
+    }
+    const uint4 o = pack8(acc);
+    const long long off = par + static_cast<long long>(pe.rank) * cap + static_cast<long long>(t) * d + c * 8;
+    for (int p = 0; p < pe.world; ++p) *reinterpret_cast<uint4*>(pe.recv[p] + off) = o;
+  }
+  __threadfence_system();
+  __syncthreads();
+  // 2. flags: one per (block, source rank) at every destination; then wait for all sources (bounded)
+  if (threadIdx.x < pe.world) {
+    st_release_sys(pe.flags[threadIdx.x] + pe.rank * max_blocks + b, e);
+    const uint32_t* mine = pe.flags[pe.rank] + threadIdx.x * max_blocks + b;
+    uint32_t spins = 0;
+    long long tstart = 0;
+    while (static_cast<int32_t>(ld_acquire_sys_(mine) - e) < 0) {
+      ++spins;
+      if (spins == 1024) tstart = clock64();
+      if (spins > 1024 && (spins & 63) == 0 && clock64() - tstart > kWaitLimitCycles) {
+        if (status) atomicCAS(status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  // 3. sum the partials in rank order (+ residual)
+  const __nv_bfloat16* base = pe.recv[pe.rank] + par;
+  for (int i = threadIdx.x; i < (t1 - t0) * vec; i += blockDim.x) {
+    const int t = t0 + i / vec, c = i % vec;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < pe.world; ++r)
+      add8(acc, __ldcg(reinterpret_cast<const uint4*>(base + static_cast<long long>(r) * cap + static_cast<long long>(t) * d) + c));
+    if (residual) add8(acc, reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * d)[c]);
+    reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * d)[c] = pack8(acc);
+  }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_moe_route(const void* logits, int ld, int tokens, int experts, int top_k, int softmax_all,
+                               int* out_idx, float* out_w, void* stream) {
+  if (!logits || !out_idx || !out_w || tokens <= 0 || experts <= 0 || experts > kMaxExperts || top_k <= 0 ||
+      top_k > kMaxTopK || top_k > experts)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  cudaError_t e = launch_kernel(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                                1u, static_cast<const __nv_bfloat16*>(logits), ld, tokens, experts, top_k, softmax_all,
+                                out_idx, out_w);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+SLLM_EXPORT int sllm_moe_permute(const int* idx, const float* w, int tokens, int top_k, int e_lo, int e_hi, int* tok_off,
+                                 int* perm_src, int* perm_dst, float* perm_w, void* stream) {
+  if (!idx || !w || !tok_off || !perm_src || !perm_dst || !perm_w || tokens <= 0 || top_k <= 0 || e_lo < 0 ||
+      e_hi <= e_lo || e_hi - e_lo > kMaxExperts)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  cudaError_t e = launch_kernel(moe_permute_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), 1u, idx, w,
+                                tokens, top_k, e_lo, e_hi, tok_off, perm_src, perm_dst, perm_w);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+SLLM_EXPORT int sllm_moe_gather(const void* x, int ldx, const int* perm_src, const int* tok_off, int n_local, void* xp,
+                                int d, int max_rows, void* stream) {
+  if (!x || !perm_src || !tok_off || !xp || d <= 0 || (d % 8) || (ldx % 8) || max_rows <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  cudaError_t e = launch_kernel(moe_gather_kernel, dim3(max_rows), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u,
+                                static_cast<const __nv_bfloat16*>(x), ldx, perm_src, tok_off, n_local,
+                                static_cast<__nv_bfloat16*>(xp), d);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+SLLM_EXPORT int sllm_moe_combine(const void* yp, const int* perm_dst, int top_k, const void* residual, void* y, int tokens,
+                                 int d, void* stream) {
+  if (!yp || !perm_dst || !y || tokens <= 0 || d <= 0 || (d % 8) || top_k <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  cudaError_t e = launch_kernel(moe_combine_kernel, dim3(tokens), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u,
+                                static_cast<const __nv_bfloat16*>(yp), perm_dst, top_k,
+                                static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(y), d);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+// recv / flags: arrays of `world` peer pointers (this rank's own included); cap_elems = max_tokens * d.
+SLLM_EXPORT int sllm_moe_combine_allreduce(const void* const* recv, const void* const* flags, int world, int rank,
+                                           const void* yp, const int* perm_dst, int top_k, const void* residual, void* y,
+                                           int tokens, int d, int rows_per_block, long long cap_elems, int max_blocks,
+                                           void* epoch, int* status, void* stream) {
+  if (!recv || !flags || world < 2 || world > 8 || rank < 0 || rank >= world || !yp || !perm_dst || !y || !epoch ||
+      tokens <= 0 || d <= 0 || (d % 8) || rows_per_block <= 0)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  const int blocks = (tokens + rows_per_block - 1) / rows_per_block;
+  if (blocks > max_blocks || static_cast<long long>(tokens) * d > cap_elems) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+  EpPeers pe;
+  pe.world = world;
+  pe.rank = rank;
+  for (int i = 0; i < world; ++i) {
+    pe.recv[i] = static_cast<__nv_bfloat16*>(const_cast<void*>(recv[i]));
+    pe.flags[i] = static_cast<uint32_t*>(const_cast<void*>(flags[i]));
+  }
+  cudaError_t e = launch_kernel(moe_combine_allreduce_kernel, dim3(blocks), dim3(256), 0,
+                                static_cast<cudaStream_t>(stream), 1u, pe, static_cast<const __nv_bfloat16*>(yp), perm_dst,
+                                top_k, static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(y), tokens, d,
+                                rows_per_block, cap_elems, max_blocks, static_cast<uint32_t*>(epoch), status);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}

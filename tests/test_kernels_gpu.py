@@ -366,3 +366,52 @@ def test_gemm_w4_grouped(fmt):
     got = linear_w4(x, wq, tok_off=off, tok_scale=sc, max_group_tokens=t).float().cpu()
     assert rel_err(got, want) < 6e-3
     assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("t,e,k", [(1, 8, 2), (37, 128, 4), (64, 32, 8), (200, 128, 4)])
+def test_moe_route_permute_gather_combine(t, e, k):
+    from sllm_b200.ops import moe as M
+    torch.manual_seed(t)
+    logits = torch.randn(t, e, device=DEV).bfloat16()
+    idx, w = M.route(logits, k)
+    idx_c, w_c = M.route(logits.cpu(), k)
+    assert torch.equal(idx.cpu(), idx_c) and torch.allclose(w.cpu(), w_c, atol=2e-6)
+    idx_a, w_a = M.route(logits, k, softmax_all=True)
+    _, w_ac = M.route(logits.cpu(), k, softmax_all=True)
+    assert torch.allclose(w_a.cpu(), w_ac, atol=2e-6)
+    lo, hi = e // 4, e // 2 + 1
+    got = M.permute(idx, w, lo, hi)
+    want = M.permute(idx_c, w_c, lo, hi)
+    n = int(want[0][-1])
+    assert torch.equal(got[0].cpu(), want[0]) and torch.equal(got[2].cpu(), want[2])
+    assert torch.equal(got[1].cpu()[:n], want[1][:n]) and torch.allclose(got[3].cpu()[:n], want[3][:n], atol=2e-6)
+    x = torch.randn(t, 264, device=DEV).bfloat16()
+    xp = M.gather(x, got[1], got[0])
+    assert torch.equal(xp.cpu()[:n], x.cpu()[want[1][:n].long()])
+    res = torch.randn(t, 264, device=DEV).bfloat16()
+    y = M.combine(xp, got[2], res)
+    yc = M.combine(xp.cpu().float(), want[2], res.cpu().float())
+    assert rel_err(y.float().cpu(), yc) < 5e-3
+
+
+@pytest.mark.gpu
+def test_tiny_moe_gpu_matches_cpu():
+    from sllm_b200.cache.paged import PagedKVCache
+    from sllm_b200.engine.engine import Engine
+    from sllm_b200.models import moe as MOE
+    cfg = MOE.tiny_moe()
+
+    def engine(dev):
+        w = MOE.init_random_moe_weights(cfg, dev, seed=4)
+        m = MOE.MoeModel(cfg, w)
+        return Engine(cfg, m, PagedKVCache(cfg, 64, torch.device(dev), kv_heads=m.local_kv_heads), dev, max_batch=4)
+
+    prompts = [list(range(3, 40)), [9, 8, 7, 6]]
+    g, c = engine(DEV), engine("cpu")
+    lg = g.prefill([g.new_sequence(p) for p in prompts], sample=False).float().cpu()
+    lc = c.prefill([c.new_sequence(p) for p in prompts], sample=False).float()
+    assert rel_err(lg, lc) < 3e-2
+    out = g.generate(prompts, 12)
+    assert all(len(o) == 12 for o in out)
+    assert ops.device_status(torch.device(DEV)) == 0
