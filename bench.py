@@ -33,7 +33,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--impl", default="own", choices=["own", "reference", "torch"],
+                    help="own: this engine; reference: the unmodified reference (unavailable here); torch: the "
+                         "unfused plain-PyTorch + NCCL comparator under baseline/")
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--model", default="llama3-8b")
@@ -103,10 +105,108 @@ def run_reference(args):
     return 0
 
 
+def run_torch_baseline(args):
+    """Same model shape, prompt and step count through baseline/torch_llama.py (bf16 library GEMMs, SDPA, NCCL)."""
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from baseline.torch_llama import TorchLlama
+    from sllm_b200.models import config as mc
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    cfg = mc.NAMED[args.model]()
+    if args.layers > 0:
+        cfg.n_layers = args.layers
+    cfg.max_context = ((args.prompt + args.warmup + args.steps + 64 + 255) // 256) * 256
+    model = TorchLlama(cfg, device, seed=0, tp_size=world, tp_rank=rank, max_batch=args.batch)
+    g = torch.Generator().manual_seed(1234)
+    prompts = torch.randint(0, cfg.vocab, (args.batch, args.prompt), generator=g)
+    pinned = torch.empty((args.batch, 1), dtype=torch.int64, pin_memory=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sync()
+    e0.record()
+    nxt = None
+    for i in range(0, args.batch, 8):      # prefill in groups of 8 like the engine arm
+        part = model_forward_rows(model, prompts[i:i + 8].to(device), i, 0)
+        nxt = part if nxt is None else torch.cat([nxt, part])
+    e1.record()
+    sync()
+    prefill_ms = e0.elapsed_time(e1)
+    pos = args.prompt
+    for _ in range(args.warmup):
+        nxt = model.forward(nxt.view(-1, 1), pos)
+        pos += 1
+    clocks = ClockSampler(local_rank)
+    if rank == 0:
+        clocks.start()
+    sync()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        pinned.copy_(nxt.view(-1, 1))                     # D2H of the step's result
+        tok = pinned.to(device, non_blocking=True)        # H2D of the next step's input from pinned memory
+        nxt = model.forward(tok, pos)
+        pos += 1
+    e1.record()
+    sync()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    ms = max(e0.elapsed_time(e1), wall_ms)
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clk = clocks.stop() if rank == 0 else None
+    if rank == 0:
+        value = args.batch * args.steps / (ms / 1e3)
+        print(json.dumps({
+            "metric": "decode_output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": round(value / REFERENCE_PUBLISHED_TOK_S, 2), "dtype": "bf16",
+            "data": "synthetic: seeded uniform-random prompts, seeded N(0,0.02) random-init weights",
+            "config": {"model": f"{cfg.name}-bf16", "global_batch": args.batch, "seq_len": args.prompt,
+                       "output_tokens": args.steps, "kv_cache": "bf16-contiguous", "parallelism": f"tp{args.gpus}-nccl"},
+            "clocks": clk, "e2e": {"value": round(value, 2), "unit": "tok/s", "ms_per_step": round(ms / args.steps, 4),
+                                   "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": args.batch * 8,
+                                   "api": "baseline.torch_llama.TorchLlama.forward"},
+            "gpu_launches": 0, "ttft_ms_batch_prefill": round(prefill_ms, 2), "impl": "torch-unfused-baseline"}))
+    sys.stdout.flush()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+        os._exit(0)
+    return 0
+
+
+def model_forward_rows(model, tokens, row0: int, start: int):
+    """Prefill of a group of rows into their slice of the contiguous KV cache."""
+    k_full, v_full = model.k, model.v
+    n = tokens.shape[0]
+    model.k = [k[row0:row0 + n] for k in k_full]
+    model.v = [v[row0:row0 + n] for v in v_full]
+    try:
+        return model.forward(tokens, start)
+    finally:
+        model.k, model.v = k_full, v_full
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "torch":
+        return run_torch_baseline(args)
 
     import torch
     import torch.distributed as dist

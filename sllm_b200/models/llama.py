@@ -97,6 +97,9 @@ def init_random_weights(cfg: ModelConfig, device, seed: int = 0, tp_size: int = 
         raise ValueError("heads and ffn must be divisible by the tensor-parallel size")
 
     def lin(w: torch.Tensor) -> LinearWeight:
+        if wf in ("nvfp4", "mxfp4"):
+            from ..ops.w4 import W4Weight
+            return LinearWeight("w4", None, None, W4Weight.quantize_device(wf, w.contiguous()))
         if kind == "fp8":
             q = ops.quant_fp8(w.contiguous())
             return LinearWeight("fp8", q.data, q.scale)

@@ -37,18 +37,21 @@ class LinearWeight:
                   are contiguous for the GEMM epilogue).
     """
     kind: str
-    w: torch.Tensor
+    w: Optional[torch.Tensor]
     scale_t: Optional[torch.Tensor] = None
+    w4: object = None            # ops.w4.W4Weight for kind 'w4' (MXFP4 / NVFP4 codes, W4A16 GEMM)
 
     @property
     def out_features(self) -> int:
-        return self.w.shape[0]
+        return self.w4.n if self.kind == "w4" else self.w.shape[0]
 
     @property
     def in_features(self) -> int:
-        return self.w.shape[1]
+        return self.w4.k if self.kind == "w4" else self.w.shape[1]
 
     def dequantized(self) -> torch.Tensor:
+        if self.kind == "w4":
+            return self.w4.dequantized(0)
         if self.kind == "fp8":
             return ref.dequant_fp8_1x128(self.w, self.scale_t)
         return self.w.to(torch.float32)
@@ -61,6 +64,11 @@ class LinearWeight:
         return LinearWeight("dense", w)
 
     def to(self, device) -> "LinearWeight":
+        if self.kind == "w4":
+            import dataclasses
+            w4 = dataclasses.replace(self.w4, tiles=self.w4.tiles.to(device),
+                                     tensor_scale=None if self.w4.tensor_scale is None else self.w4.tensor_scale.to(device))
+            return LinearWeight("w4", None, None, w4)
         return LinearWeight(self.kind, self.w.to(device), None if self.scale_t is None else self.scale_t.to(device))
 
 
@@ -141,6 +149,9 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, *, scale_a=None,
 def linear(x, w: LinearWeight, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Y = X W^T (+ residual).  x: Tensor [M, K] (bf16 / fp32) or QTensor for FP8 weights."""
     xd = x.data if isinstance(x, QTensor) else x
+    if w.kind == "w4":
+        from .w4 import linear_w4
+        return linear_w4(xd, w.w4, residual=residual)
     if not xd.is_cuda:
         if isinstance(x, QTensor):
             xf = ref.dequant_fp8_1x128(x.data, x.scale)

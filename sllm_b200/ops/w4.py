@@ -90,6 +90,58 @@ class W4Weight:
             sc.append(s)
         return W4Weight.from_file_layout(fmt, np.stack(pk), np.stack(sc), w3.shape[2], ts or None, device, keep_file)
 
+    @staticmethod
+    def quantize_device(fmt: str, w: torch.Tensor) -> "W4Weight":
+        """Same quantiser as `quantize`, written in torch ops so that it runs on the GPU (benchmark-sized random
+        weights); w: float/bf16 [G, N, K] or [N, K] on any device.  Bit-identical to the NumPy codec."""
+        if w.dim() == 2:
+            w = w[None]
+        dev = w.device
+        g, n, k = w.shape
+        block = 32 if fmt == "mxfp4" else 16
+        sb = 128 // block
+        n_rows, k_pad = (n + 127) // 128 * 128, (k + 127) // 128 * 128
+        wf = torch.zeros((g, n_rows, k_pad), dtype=torch.float32, device=dev)
+        wf[:, :n, :k] = w.float()
+        blk = wf.view(g, n_rows, k_pad // block, block)
+        bamax = torch.where(torch.isfinite(blk), blk.abs(), torch.zeros_like(blk)).amax(dim=3)
+        ts = None
+        if fmt == "mxfp4":
+            bits = bamax.contiguous().view(torch.int32).to(torch.int64) + 0x00200000
+            code = (((bits & 0x7F800000) >> 23) - 2).clamp(0, 254)
+            code = torch.where(bamax == 0, torch.zeros_like(code), code)
+            if int(code.max()) > MAX_E8M0_CODE:
+                raise ValueError("MXFP4 block scale above 2^17 is outside the kernel's exact range")
+            scale = torch.ldexp(torch.ones_like(bamax), (code - 127).to(torch.int32))
+            sc_codes = code.to(torch.uint8)
+        else:
+            amax = bamax.view(g, -1).amax(dim=1)
+            ts = torch.where(amax > 0, amax / (448.0 * 6.0), torch.ones_like(amax)).float()
+            want = (bamax / 6.0) / ts.view(g, 1, 1)
+            sc_codes = want.clamp(max=448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+            scale = sc_codes.view(torch.float8_e4m3fn).float() * ts.view(g, 1, 1)
+        safe = torch.where(scale > 0, scale, torch.ones_like(scale))
+        a = (blk / safe.unsqueeze(-1)).abs().clamp(max=6.0)
+        vals = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], device=dev)
+        hi = torch.bucketize(a, vals).clamp(max=7)             # first index with vals[hi] >= a
+        lo = (hi - 1).clamp(min=0)
+        dlo, dhi = (a - vals[lo]).abs(), (vals[hi] - a).abs()
+        pick_hi = (dhi < dlo) | ((dhi == dlo) & ((hi & 1) == 0))
+        idx = torch.where(pick_hi, hi, lo)
+        sign = ((blk < 0) & (idx != 0)).to(torch.int64) << 3
+        codes = (idx | sign)
+        codes = torch.where((scale > 0).unsqueeze(-1), codes, torch.zeros_like(codes)).view(g, n_rows, k_pad // 8, 8)
+        order = [0, 2, 4, 6, 1, 3, 5, 7]
+        words = torch.zeros((g, n_rows, k_pad // 8), dtype=torch.int64, device=dev)
+        for pos in range(8):
+            words |= codes[..., order[pos]] << (4 * pos)
+        words = torch.where(words >= (1 << 31), words - (1 << 32), words).to(torch.int32)
+        rt, kc = n_rows // 128, k_pad // 128
+        pk = words.view(torch.uint8).view(g, rt, 128, kc, 64).permute(0, 1, 3, 2, 4).reshape(g, rt, kc, 8192)
+        sc_t = sc_codes.view(g, rt, 128, kc, sb).permute(0, 1, 3, 2, 4).reshape(g, rt, kc, 128 * sb)
+        tiles = torch.cat([pk, sc_t], dim=3).contiguous()
+        return W4Weight(fmt, g, n, k, n_rows, k_pad, tiles, ts)
+
     def dequantized(self, group: int = 0) -> torch.Tensor:
         """fp32 [n, k] of one group from the resident layout (exact)."""
         rt, kc = self.n_rows // 128, self.k_pad // 128

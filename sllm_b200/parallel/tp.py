@@ -86,6 +86,8 @@ class FusedTP(NcclTP):
         super().__init__(size, rank, device, group)
         from .symm import SymmetricRegion
         self.max_tokens = max_tokens
+        self._d_model = d_model
+        self._row_reduce = None
         # receive buffers: [2 parities][world][cap] bf16; cap covers a padded [tokens, d_model] tile grid
         pad_tokens = 16 if max_tokens <= 16 else 32 if max_tokens <= 32 else 64 if max_tokens <= 64 else \
             (max_tokens + 127) // 128 * 128
@@ -120,17 +122,35 @@ class FusedTP(NcclTP):
 
     def close(self) -> None:
         """Unmaps the peers' regions, then frees the local one (all ranks must call this together)."""
+        if self._row_reduce is not None:
+            self._row_reduce.close()
+            self._row_reduce = None
         if self.region is not None:
             torch.cuda.synchronize()
             dist.barrier(group=self.group)
             self.region.close()
             self.region = None
 
+    def _reduce_rows(self, part: torch.Tensor, residual):
+        """All-reduce of [m, n] partial rows (+ residual) in one kernel over peer memory: the expert-parallel
+        combine kernel with the identity permutation."""
+        if self._row_reduce is None:
+            from .ep import FusedEP
+            self._row_reduce = FusedEP(self.size, self.rank, self.device, self.max_tokens, self._d_model, self.group)
+            self._ident = torch.arange(self.max_tokens, dtype=torch.int32, device=self.device).view(-1, 1)
+        return self._row_reduce.combine(part, self._ident[:part.shape[0]], residual)
+
     def row_linear(self, x, w: LinearWeight, residual):
         xd = x.data if isinstance(x, QTensor) else x
         m, n = xd.shape[0], w.out_features
         if not xd.is_cuda or m > self.max_tokens:
             return super().row_linear(x, w, residual)
+        if w.kind == "w4":
+            # 4-bit weights: W4A16 GEMM, then the fused peer-memory reduction
+            part = ops.linear(x, w)
+            if n != self._d_model:
+                return super().row_linear(x, w, residual)
+            return self._reduce_rows(part, residual)
         lib = _lib.kernels()
         fp8 = w.kind == "fp8"
         if fp8 and not isinstance(x, QTensor):

@@ -415,3 +415,22 @@ def test_tiny_moe_gpu_matches_cpu():
     out = g.generate(prompts, 12)
     assert all(len(o) == 12 for o in out)
     assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_w4_llama_gpu_matches_cpu(fmt):
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.models import config as MC
+    cfg = MC.ModelConfig(name="w4-test", n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, vocab=2048,
+                         weight_format=fmt, kv_format="bf16", max_context=256)
+    g = build_engine(cfg, DEV, seed=3, num_pages=64, max_batch=4)
+    c = build_engine(cfg, "cpu", seed=3, num_pages=64, max_batch=4, use_cuda_graphs=False)
+    # both engines must hold the same codes: the device quantiser runs on different devices
+    assert torch.equal(g.model.w.layers[0].qkv.w4.tiles.cpu(), c.model.w.layers[0].qkv.w4.tiles)
+    prompts = [list(range(3, 40)), [9, 8, 7, 6]]
+    lg = g.prefill([g.new_sequence(p) for p in prompts], sample=False).float().cpu()
+    lc = c.prefill([c.new_sequence(p) for p in prompts], sample=False).float()
+    assert rel_err(lg, lc) < 3e-2
+    assert all(len(o) == 8 for o in g.generate(prompts, 8))
+    assert ops.device_status(torch.device(DEV)) == 0

@@ -58,6 +58,21 @@ def main():
             dist.all_gather(parts, y_f)
             for p in parts:
                 assert torch.equal(p, parts[0]), (kind, m, "ranks disagree")
+    # 4-bit weights: W4A16 GEMM + the fused peer-memory row reduction
+    from sllm_b200.ops.w4 import W4Weight
+    for m in (3, 40):
+        x = torch.randn(m, 1024, device=dev).bfloat16()
+        w = (torch.randn(d_model, 1024, device=dev) * 0.03)
+        r = torch.randn(m, d_model, device=dev).bfloat16()
+        dist.broadcast(x, 0); dist.broadcast(w, 0); dist.broadcast(r, 0)
+        ks = 1024 // world
+        lw = LinearWeight("w4", None, None, W4Weight.quantize_device("nvfp4", w[:, rank * ks:(rank + 1) * ks].contiguous()))
+        full = W4Weight.quantize_device("nvfp4", w)   # per-shard tensor scales differ slightly: compare loosely
+        want = x.float() @ full.dequantized(0).to(dev).t() + r.float()
+        xs = x[:, rank * ks:(rank + 1) * ks].contiguous()
+        y_f = fused.row_linear(xs, lw, r)
+        y_n = nccl.row_linear(xs, lw, r)
+        assert rel(y_f, want) < 0.15 and rel(y_f, y_n) < 1.5e-2, (m, rel(y_f, want), rel(y_f, y_n))
     mark("row_linear ok")
     # vocabulary-parallel argmax
     logits = torch.randn(5, 4096, device=dev).bfloat16()
