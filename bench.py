@@ -39,8 +39,14 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--model", default="llama3-8b")
-    ap.add_argument("--weights", default="fp8")
-    ap.add_argument("--kv", default="fp8")
+    ap.add_argument("--weights", default=None, help="weight format override (default: fp8 for the dense models)")
+    ap.add_argument("--kv", default=None, help="KV-cache format override")
+    ap.add_argument("--synthetic-kv", action="store_true",
+                    help="decode-only measurement: mark the prompt's KV pages as computed without running the prefill "
+                         "(used for shapes whose prefill is not the subject, e.g. the MoE decode config)")
+    ap.add_argument("--spec-width", type=int, default=0,
+                    help="speculative decoding: draft tokens per step from a llama-draft model (acceptance forced by a "
+                         "seeded Bernoulli(0.7) mask so that the full verify compute always runs)")
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--layers", type=int, default=0, help="profiling only: override the layer count")
     ap.add_argument("--no-batch1", action="store_true", help="skip the extra batch-1 measurement")
@@ -229,7 +235,11 @@ def main():
     from sllm_b200.ops import _lib
 
     cfg = mc.NAMED[args.model]()
-    cfg.weight_format, cfg.kv_format = args.weights, args.kv
+    if cfg.family != "moe":
+        cfg.weight_format, cfg.kv_format = args.weights or "fp8", args.kv or "fp8"
+    else:
+        cfg.weight_format, cfg.kv_format = args.weights or cfg.weight_format, args.kv or cfg.kv_format
+    args.weights, args.kv = cfg.weight_format, cfg.kv_format
     if args.layers > 0:
         cfg.n_layers = args.layers
         cfg.name += f"-{args.layers}layers-PROFILING-ONLY"
@@ -239,6 +249,11 @@ def main():
     if world > 1:
         from sllm_b200.parallel.tp import make_tp
         tp = make_tp(world, rank, device, impl=args.tp_impl, max_tokens=max(args.batch, 128), d_model=cfg.d_model)
+    ep = None
+    if world > 1 and cfg.family == "moe":
+        from sllm_b200.parallel.ep import FusedEP, NcclEP
+        ep = FusedEP(world, rank, device, max(args.batch, 128), cfg.d_model) if args.tp_impl == "fused" \
+            else NcclEP(world, rank, device)
 
     def barrier():
         if world > 1:
@@ -253,7 +268,7 @@ def main():
         return float(t.item())
 
     def measure(batch: int, steps: int, warmup: int, sample_clocks: bool):
-        eng = build_engine(cfg, device, seed=0, max_batch=batch, tp=tp)
+        eng = build_engine(cfg, device, seed=0, max_batch=batch, tp=tp, ep=ep)
         g = torch.Generator().manual_seed(1234)
         prompts = torch.randint(0, cfg.vocab, (batch, args.prompt), generator=g).tolist()
         seqs = [eng.new_sequence(p) for p in prompts]
@@ -261,11 +276,18 @@ def main():
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(0, batch, 8):
-            grp = seqs[i:i + 8]
-            first = eng.prefill(grp)
-            for s, t in zip(grp, first):
-                s.tokens.append(t)
+        if args.synthetic_kv:
+            for s in seqs:
+                eng.cache.pool.reserve(s.seq_id, len(s.tokens))
+                eng.cache.pool.commit(s.seq_id, len(s.tokens))
+                s.num_computed = len(s.tokens)
+                s.tokens.append(int(s.tokens[-1]))
+        else:
+            for i in range(0, batch, 8):
+                grp = seqs[i:i + 8]
+                first = eng.prefill(grp)
+                for s, t in zip(grp, first):
+                    s.tokens.append(t)
         e1.record()
         barrier()
         prefill_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -342,11 +364,16 @@ def main():
             "higher_is_better": True,
             "scaling": "strong",
             "vs_baseline": round(value / REFERENCE_PUBLISHED_TOK_S, 2),
-            "dtype": "fp8_e4m3_block128_weights+fp8_kv (bf16 activations, fp32 accumulate)",
-            "data": "synthetic: seeded uniform-random prompts, seeded N(0,0.02) random-init weights",
+            "dtype": ("fp8_e4m3_block128_weights+fp8_kv (bf16 activations, fp32 accumulate)" if args.weights == "fp8" else
+                      f"{args.weights} weights ({cfg.expert_format} experts) + {args.kv} kv, bf16 activations, fp32 accumulate"
+                      if cfg.family == "moe" else f"{args.weights} weights + {args.kv} kv, bf16 activations, fp32 accumulate"),
+            "data": "synthetic: seeded uniform-random prompts, seeded N(0,0.02) random-init weights" +
+                    ("; KV pages of the prompt marked computed without a prefill (decode-only measurement)"
+                     if args.synthetic_kv else ""),
             "config": {"model": f"{cfg.name}-{args.weights}", "global_batch": args.batch,
                        "seq_len": args.prompt, "output_tokens": k, "kv_cache": f"{args.kv}-paged-16",
-                       "parallelism": f"tp{args.gpus}" + (f"-{args.tp_impl}" if args.gpus > 1 else ""),
+                       "parallelism": (f"tp{args.gpus}+ep{args.gpus}" if cfg.family == "moe" else f"tp{args.gpus}") +
+                                      (f"-{args.tp_impl}" if args.gpus > 1 else ""),
                        "l2": "each step streams the full weight set (>> 126 MB L2); no flush needed"},
             "clocks": main_res["clocks"],
             "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "ms_per_step": round(main_res["e2e_ms"] / k, 4),
@@ -367,6 +394,8 @@ def main():
     sys.stdout.flush()
     if world > 1:
         torch.cuda.synchronize()
+        if ep is not None:
+            ep.close()
         if tp is not None:
             tp.close()
         dist.barrier()

@@ -314,13 +314,20 @@ class Engine:
 
 
 def build_engine(cfg: ModelConfig, device="cuda", seed: int = 0, num_pages: Optional[int] = None,
-                 max_batch: int = 64, use_cuda_graphs: bool = True, tp=None) -> Engine:
-    """Random-init engine for a named shape (benchmarks, tests, smoke)."""
-    from ..models.llama import LlamaModel, init_random_weights
+                 max_batch: int = 64, use_cuda_graphs: bool = True, tp=None, ep=None) -> Engine:
+    """Random-init engine for a named shape (benchmarks, tests, smoke).  `ep` (expert-parallel context) applies to
+    the mixture-of-experts family."""
     device = torch.device(device)
     tp_size, tp_rank = (tp.size, tp.rank) if tp is not None else (1, 0)
-    weights = init_random_weights(cfg, device, seed, tp_size, tp_rank)
-    model = LlamaModel(cfg, weights, tp)
+    if cfg.family == "moe":
+        from ..models.moe import MoeModel, init_random_moe_weights
+        ep_size, ep_rank = (ep.size, ep.rank) if ep is not None else (1, 0)
+        weights = init_random_moe_weights(cfg, device, seed, tp_size, tp_rank, ep_size, ep_rank)
+        model = MoeModel(cfg, weights, tp, ep)
+    else:
+        from ..models.llama import LlamaModel, init_random_weights
+        weights = init_random_weights(cfg, device, seed, tp_size, tp_rank)
+        model = LlamaModel(cfg, weights, tp)
     if num_pages is None:
         num_pages = max_batch * ((cfg.max_context + cfg.page_size - 1) // cfg.page_size) + 8
     cache = PagedKVCache(cfg, num_pages, device, kv_heads=model.local_kv_heads)

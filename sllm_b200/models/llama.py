@@ -162,6 +162,7 @@ class LlamaModel:
         self.hq = cfg.n_heads // t
         self.hkv = max(1, cfg.n_kv_heads // t)
         self.quant = cfg.weight_format == "fp8"
+        self.adapters = None      # models.adapters.AdapterSet applied to every forward while set
 
     @property
     def local_kv_heads(self) -> int:
@@ -174,6 +175,10 @@ class LlamaModel:
         qo = self.quant and hd == 128 and h.is_cuda
         for li, lw in enumerate(w.layers):
             kv = cache.layer(li)
+            ad = self.adapters
+            if ad is not None and (ad.loras or ad.cvs):
+                h = self._adapter_layer(li, lw, h, b, kv, ad)
+                continue
             x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
             qkv = ops.linear(x, lw.qkv)
             q = ops.rope_kv_append(qkv, b.positions, b.seq_index, b.block_table, kv, self.hq, self.hkv, hd,
@@ -188,6 +193,25 @@ class LlamaModel:
             act = ops.gated_act(gu, cfg.act, quant=self.quant)
             h = self.tp.row_linear(act, lw.down, h)
         return h
+
+    def _adapter_layer(self, li, lw, h, b, kv, ad):
+        """One layer with LoRA deltas on the projections and the control vector on the residual stream.  The
+        projections take bf16 inputs here (the delta needs the unquantised activation); single GPU only."""
+        cfg = self.cfg
+        hd = cfg.head_dim
+        if self.tp.size != 1:
+            raise ValueError("adapters are supported without tensor parallelism")
+        x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one)
+        qkv = ad.lora_delta(li, "qkv", x, ops.linear(x, lw.qkv))
+        q = ops.rope_kv_append(qkv, b.positions, b.seq_index, b.block_table, kv, self.hq, self.hkv, hd, cfg.rope_theta,
+                               cfg.rotary_dim)
+        a = ops.attention(q, kv, b, self.hq, self.hkv, hd, window=cfg.layer_window(li), qkv=qkv)
+        h = ad.lora_delta(li, "o", a, ops.linear(a, lw.o, h))
+        x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
+        gu = ad.lora_delta(li, "gate_up", x, ops.linear(x, lw.gate_up))
+        act = ops.gated_act(gu, cfg.act)
+        h = ad.lora_delta(li, "down", act, ops.linear(act, lw.down, h))
+        return ad.control(li, h)
 
     def logits(self, h: torch.Tensor, b: ForwardBatch) -> torch.Tensor:
         """Local (vocab-shard) logits of the requested rows."""

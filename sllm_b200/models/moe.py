@@ -49,7 +49,10 @@ def init_random_moe_weights(cfg: ModelConfig, device, seed: int = 0, tp_size: in
     """Seeded random weights; every rank draws the same tensors and keeps its shard (attention heads by
     tensor-parallel rank, experts by expert-parallel rank)."""
     device = torch.device(device)
-    gen = torch.Generator(device="cpu")
+    # small models draw on the CPU (identical weights on every device, used by the CPU-vs-GPU tests); benchmark
+    # shapes draw on the target device, where generating and quantising ~10^11 parameters takes seconds
+    big = cfg.n_layers * cfg.n_experts * cfg.expert_ffn * cfg.d_model * 3 > 2e9 and device.type == "cuda"
+    gen = torch.Generator(device=device if big else "cpu")
     gen.manual_seed(seed)
     cpu_fp32 = cfg.weight_format == "fp32"
     dt = torch.float32 if cpu_fp32 else torch.bfloat16
@@ -65,7 +68,9 @@ def init_random_moe_weights(cfg: ModelConfig, device, seed: int = 0, tp_size: in
         kv_lo, kv_hi = head * hd, (head + 1) * hd
 
     def rnd(shape):
-        return (torch.randn(shape, generator=gen, dtype=torch.float32) * std)
+        return (torch.randn(shape, generator=gen, dtype=torch.float32, device=device if big else "cpu") * std)
+
+    quant = W4Weight.quantize_device if big else (lambda f, w: W4Weight.quantize(f, w, device, keep_file=False))
 
     embed = rnd((cfg.vocab, d)).to(dt).to(device)
     layers = []
@@ -89,8 +94,9 @@ def init_random_moe_weights(cfg: ModelConfig, device, seed: int = 0, tp_size: in
             .float().contiguous().to(device),
             mlp_norm=torch.ones(d, dtype=dt, device=device),
             router=LinearWeight("dense", router.to(dt).contiguous().to(device)),
-            gate_up=W4Weight.quantize(cfg.expert_format, torch.stack(gu_local), device, keep_file=False),
-            down=W4Weight.quantize(cfg.expert_format, torch.stack(dn_local), device, keep_file=False)))
+            gate_up=quant(cfg.expert_format, torch.stack(gu_local)),
+            down=quant(cfg.expert_format, torch.stack(dn_local))))
+        del gu_local, dn_local
     final_norm = torch.ones(d, dtype=dt, device=device)
     head = rnd((cfg.vocab, d))
     vo = 0

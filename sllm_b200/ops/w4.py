@@ -96,6 +96,13 @@ class W4Weight:
         weights); w: float/bf16 [G, N, K] or [N, K] on any device.  Bit-identical to the NumPy codec."""
         if w.dim() == 2:
             w = w[None]
+        if w.shape[0] > 1 and w.numel() > (1 << 27):
+            # large expert stacks: quantise a few groups at a time to bound the temporaries
+            step = max(1, (1 << 27) // (w.shape[1] * w.shape[2]))
+            parts = [W4Weight.quantize_device(fmt, w[i:i + step]) for i in range(0, w.shape[0], step)]
+            p0 = parts[0]
+            ts = None if p0.tensor_scale is None else torch.cat([p.tensor_scale for p in parts])
+            return W4Weight(fmt, w.shape[0], p0.n, p0.k, p0.n_rows, p0.k_pad, torch.cat([p.tiles for p in parts]), ts)
         dev = w.device
         g, n, k = w.shape
         block = 32 if fmt == "mxfp4" else 16
