@@ -1,0 +1,196 @@
+// Gated delta net (linear attention) layers of the Qwen3.5 hybrid: depthwise causal convolution + SiLU with a
+// rolling convolution state, and the gated delta-rule recurrence fused with the output RMSNorm and the SiLU(z)
+// gate.  Both kernels work on a flat token batch in which the rows of one sequence are contiguous
+// (row_off[s] .. row_off[s + 1]) and every sequence owns a state slot (slots[s]), so a decode step of many
+// requests and a prefill of several prompts are the same launch.
+//
+// Recurrence per value head (state S[dv][dk], fp32), token by token:
+//   q, k    L2-normalised over the head (eps 1e-6), rounded to bf16; q additionally scaled by 1/sqrt(dk)
+//   beta    sigmoid(b) rounded to bf16;  decay = exp(-exp(A_log) * softplus(a + dt_bias))
+//   S      <- decay * S;  r = v - S k;  S <- S + beta * r k^T;  o = S q
+//   out     bf16(rmsnorm(bf16(o)) over dv, eps 1e-6) * norm_weight * silu(z)
+// One CTA per (sequence, value head), thread d owns row d of the state in registers for the whole sequence
+// (the reference re-reads the state from memory for every token: linear_attention_kernel.hip.cpp:128; same
+// operation order here so that results agree with its fp32 oracle).
+#include "common.cuh"
+#include "api.h"
+
+namespace sllm {
+
+constexpr int kGdnHeadDim = 128;
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// x: [T, width] bf16 (the q|k|v projection), w: [width, taps] bf16, state: [slots, taps - 1, width] bf16.
+// grid (ceil(width / 128), sequences).
+__global__ void gdn_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                     __nv_bfloat16* __restrict__ state, __nv_bfloat16* __restrict__ y,
+                                     const int* __restrict__ row_off, const int* __restrict__ slots, int width, int taps) {
+  pdl_wait();
+  pdl_trigger();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y;
+  if (c >= width) return;
+  const int r0 = row_off[s], r1 = row_off[s + 1];
+  const int hist = taps - 1;
+  __nv_bfloat16* st = state + static_cast<size_t>(slots[s]) * hist * width;
+  float win[8];       // sliding window of the last `taps` inputs (taps <= 8)
+  float wt[8];
+  for (int t = 0; t < taps; ++t) wt[t] = __bfloat162float(w[static_cast<size_t>(c) * taps + t]);
+  for (int t = 0; t < hist; ++t) win[t] = __bfloat162float(st[static_cast<size_t>(t) * width + c]);
+  for (int r = r0; r < r1; ++r) {
+    win[hist] = __bfloat162float(x[static_cast<size_t>(r) * width + c]);
+    float sum = 0.f;
+    for (int t = 0; t < taps; ++t) sum += win[t] * wt[t];
+    y[static_cast<size_t>(r) * width + c] = __float2bfloat16_rn(sum / (1.f + expf(-sum)));
+    for (int t = 0; t < hist; ++t) win[t] = win[t + 1];
+  }
+  for (int t = 0; t < hist; ++t) st[static_cast<size_t>(t) * width + c] = __float2bfloat16_rn(win[t]);
+}
+
+// qkv: [T, 2 * qk_heads * 128 + v_heads * 128] bf16 after the convolution; z: [T, v_heads * 128];
+// b, a: [T, v_heads]; a_log fp32 [v_heads]; dt_bias bf16 [v_heads]; norm_w fp32 [128];
+// state: [slots, v_heads, 128 (dv), 128 (dk)] fp32; out: [T, v_heads * 128] bf16.
+// grid (v_heads, sequences), 128 threads.
+__global__ void __launch_bounds__(kGdnHeadDim)
+gdn_recurrent_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ z,
+                     const __nv_bfloat16* __restrict__ b_in, const __nv_bfloat16* __restrict__ a_in,
+                     const float* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
+                     const float* __restrict__ norm_w, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
+                     const int* __restrict__ row_off, const int* __restrict__ slots, int qk_heads, int v_heads) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int HD = kGdnHeadDim;
+  const int vh = blockIdx.x, s = blockIdx.y, d = threadIdx.x;
+  const int qh = vh / (v_heads / qk_heads);
+  const int width = (2 * qk_heads + v_heads) * HD, ow = v_heads * HD;
+  const int r0 = row_off[s], r1 = row_off[s + 1];
+  if (r1 <= r0) return;
+  __shared__ float q_s[HD], k_s[HD];
+  __shared__ float red[3][4];
+  __shared__ float sc[2];
+  float* srow = state + ((static_cast<size_t>(slots[s]) * v_heads + vh) * HD + d) * HD;
+  float S[HD];
+#pragma unroll
+  for (int i = 0; i < HD; i += 4) {
+    const float4 v4 = *reinterpret_cast<const float4*>(srow + i);
+    S[i] = v4.x; S[i + 1] = v4.y; S[i + 2] = v4.z; S[i + 3] = v4.w;
+  }
+  const int lane = d & 31, warp = d >> 5;
+  const float a_neg = -expf(a_log[vh]);
+  const float dtb = __bfloat162float(dt_bias[vh]);
+  const float nw = norm_w[d];
+  for (int r = r0; r < r1; ++r) {
+    const size_t row = static_cast<size_t>(r) * width;
+    const float qv = __bfloat162float(qkv[row + qh * HD + d]);
+    const float kv = __bfloat162float(qkv[row + (qk_heads + qh) * HD + d]);
+    const float vv = __bfloat162float(qkv[row + (2 * qk_heads + vh) * HD + d]);
+    float qq = warp_sum(qv * qv), kk = warp_sum(kv * kv);
+    if (lane == 0) { red[0][warp] = qq; red[1][warp] = kk; }
+    __syncthreads();
+    if (d == 0) {
+      const float bq = __bfloat162float(b_in[static_cast<size_t>(r) * v_heads + vh]);
+      sc[0] = bf16_round(1.f / (1.f + expf(-bq)));
+      const float av = __bfloat162float(a_in[static_cast<size_t>(r) * v_heads + vh]) + dtb;
+      sc[1] = expf(a_neg * softplus_f(av));
+    }
+    qq = red[0][0] + red[0][1] + red[0][2] + red[0][3];
+    kk = red[1][0] + red[1][1] + red[1][2] + red[1][3];
+    q_s[d] = bf16_round(qv * (1.f / sqrtf(qq + 1e-6f))) * (1.f / sqrtf(static_cast<float>(HD)));
+    k_s[d] = bf16_round(kv * (1.f / sqrtf(kk + 1e-6f)));
+    __syncthreads();
+    const float beta = sc[0], decay = sc[1];
+    float prev = 0.f;
+#pragma unroll
+    for (int i = 0; i < HD; ++i) {
+      S[i] *= decay;
+      prev += S[i] * k_s[i];
+    }
+    const float resid = beta * (vv - prev);
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < HD; ++i) {
+      S[i] += resid * k_s[i];
+      o += S[i] * q_s[i];
+    }
+    o = bf16_round(o);
+    float oo = warp_sum(o * o);
+    if (lane == 0) red[2][warp] = oo;
+    __syncthreads();
+    oo = red[2][0] + red[2][1] + red[2][2] + red[2][3];
+    const float inv = 1.f / sqrtf(oo / static_cast<float>(HD) + 1e-6f);
+    const float zv = __bfloat162float(z[static_cast<size_t>(r) * ow + vh * HD + d]);
+    out[static_cast<size_t>(r) * ow + vh * HD + d] = __float2bfloat16_rn(bf16_round(o * inv) * nw * (zv / (1.f + expf(-zv))));
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < HD; i += 4) *reinterpret_cast<float4*>(srow + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+}
+
+// In place per-head RMSNorm of the q and k heads inside a fused qkv activation (query/key normalisation of
+// the Qwen3 / Gemma families): x [T, ld], heads 0 .. hq + hkv - 1 of width hd each; weight_q / weight_k fp32-exact
+// bf16 [hd]; offset_one: scale = 1 + w.  grid (T, hq + hkv), 128 threads.
+__global__ void qk_headnorm_kernel(__nv_bfloat16* __restrict__ x, int ld, int hq, int hkv, int hd,
+                                   const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk, float eps,
+                                   int offset_one) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x, h = blockIdx.y;
+  __nv_bfloat16* p = x + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * hd;
+  const __nv_bfloat16* w = h < hq ? wq : wk;
+  __shared__ float red[4];
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    const float v = __bfloat162float(p[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  ss = red[0] + red[1] + red[2] + red[3];
+  const float inv = rsqrtf(ss / static_cast<float>(hd) + eps);
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    const float g = __bfloat162float(w[i]) + (offset_one ? 1.f : 0.f);
+    p[i] = __float2bfloat16_rn(__bfloat162float(p[i]) * inv * g);
+  }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_gdn_conv_silu(const void* x, const void* w, void* state, void* y, const int* row_off, const int* slots,
+                                   int sequences, int width, int taps, void* stream) {
+  if (!x || !w || !state || !y || !row_off || !slots || sequences <= 0 || width <= 0 || taps < 2 || taps > 8)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  cudaError_t e = launch_kernel(gdn_conv_silu_kernel, dim3((width + 127) / 128, sequences), dim3(128), 0,
+                                static_cast<cudaStream_t>(stream), 1u, static_cast<const __nv_bfloat16*>(x),
+                                static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(state),
+                                static_cast<__nv_bfloat16*>(y), row_off, slots, width, taps);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+SLLM_EXPORT int sllm_gdn_recurrent(const void* qkv, const void* z, const void* b, const void* a, const float* a_log,
+                                   const void* dt_bias, const float* norm_w, float* state, void* out, const int* row_off,
+                                   const int* slots, int sequences, int qk_heads, int v_heads, int head_dim, void* stream) {
+  if (!qkv || !z || !b || !a || !a_log || !dt_bias || !norm_w || !state || !out || !row_off || !slots || sequences <= 0 ||
+      qk_heads <= 0 || v_heads <= 0 || (v_heads % qk_heads))
+    return SLLM_ERR_INVALID_ARGUMENT;
+  if (head_dim != kGdnHeadDim) return SLLM_ERR_UNSUPPORTED_SHAPE;
+  cudaError_t e = launch_kernel(gdn_recurrent_kernel, dim3(v_heads, sequences), dim3(kGdnHeadDim), 0,
+                                static_cast<cudaStream_t>(stream), 1u, static_cast<const __nv_bfloat16*>(qkv),
+                                static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(b),
+                                static_cast<const __nv_bfloat16*>(a), a_log, static_cast<const __nv_bfloat16*>(dt_bias), norm_w,
+                                state, static_cast<__nv_bfloat16*>(out), row_off, slots, qk_heads, v_heads);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+SLLM_EXPORT int sllm_qk_headnorm(void* x, int ld, int tokens, int hq, int hkv, int hd, const void* wq, const void* wk, float eps,
+                                 int offset_one, void* stream) {
+  if (!x || !wq || !wk || tokens <= 0 || hq <= 0 || hkv <= 0 || hd <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  cudaError_t e = launch_kernel(qk_headnorm_kernel, dim3(tokens, hq + hkv), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u,
+                                static_cast<__nv_bfloat16*>(x), ld, hq, hkv, hd, static_cast<const __nv_bfloat16*>(wq),
+                                static_cast<const __nv_bfloat16*>(wk), eps, offset_one);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}

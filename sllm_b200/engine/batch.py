@@ -28,6 +28,10 @@ class ForwardBatch:
     embeds: Optional[torch.Tensor] = None      # optional [T, d] input embeddings replacing the gather
     cu_seqlens_host: Optional[list] = None     # the same offsets as a Python list (tile scheduling)
     prefill_tiles: Optional[torch.Tensor] = None  # cached tile table of the tensor-core prefill kernel
+    # Recurrent-state (gated delta net) layers: rows of sequence s are row_off[s] .. row_off[s + 1], its state lives in
+    # slot slots[s] of the state cache.
+    row_off: Optional[torch.Tensor] = None     # int32 [S + 1]
+    slots: Optional[torch.Tensor] = None       # int32 [S]
 
     @property
     def num_tokens(self) -> int:
@@ -55,4 +59,5 @@ def make_prefill_batch(prompts: list, block_table: torch.Tensor, device, start_p
         tokens=t(toks), positions=positions, seq_index=t(sidx), kv_lens=positions + 1,
         block_table=block_table, logit_rows=t(rows, torch.int64) if last_only else None,
         max_kv=max(pos) + 1 if pos else 0, cu_seqlens=t(cu) if fresh else None,
-        max_seqlen=max(len(p) for p in prompts) if prompts else 0, cu_seqlens_host=cu if fresh else None)
+        max_seqlen=max(len(p) for p in prompts) if prompts else 0, cu_seqlens_host=cu if fresh else None,
+        row_off=t(cu))

@@ -57,6 +57,7 @@ class Engine:
         self.max_blocks = (cfg.max_context + cfg.page_size - 1) // cfg.page_size
         self.use_graphs = use_cuda_graphs and self.is_cuda
         self.tp = tp
+        self.has_state = hasattr(cache, "alloc_slot")     # recurrent-state (gated delta net) layers present
         self._graphs: dict = {}
         self._graph_launches: dict = {}
         pin = self.is_cuda
@@ -71,6 +72,9 @@ class Engine:
         self.d_seq_index = torch.arange(max_batch, dtype=torch.int32, device=self.device)
         self.d_table = torch.zeros((max_batch, self.max_blocks), dtype=torch.int32, device=self.device)
         self.d_out = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
+        self.h_slots = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
+        self.d_slots = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
+        self.d_row_off = torch.arange(max_batch + 1, dtype=torch.int32, device=self.device)
         self.d_logits = None
         self.np_tokens = self.h_tokens.numpy()
         self.np_positions = self.h_positions.numpy()
@@ -84,6 +88,8 @@ class Engine:
     def new_sequence(self, prompt: list, user=None) -> Sequence:
         s = Sequence(prompt=list(prompt), user=user)
         s.seq_id = self.cache.pool.new_seq()
+        if self.has_state:
+            self.cache.alloc_slot(s.seq_id)
         return s
 
     def fork_sequence(self, src: Sequence, prompt: list, user=None) -> Sequence:
@@ -94,21 +100,32 @@ class Engine:
         common = 0
         while common < limit and src.tokens[common] == prompt[common]:
             common += 1
+        if self.has_state and common != src.num_computed:
+            common = 0        # a recurrent state describes the end of the source's computed tokens only
         s = Sequence(prompt=list(prompt), user=user)
         if common == 0:
             s.seq_id = self.cache.pool.new_seq()
+            if self.has_state:
+                self.cache.alloc_slot(s.seq_id)
         else:
             s.seq_id = self.cache.fork(src.seq_id, common)
             s.num_computed = common
+            if self.has_state:
+                self.cache.alloc_slot(s.seq_id)
+                self.cache.copy_slot(src.seq_id, s.seq_id)
         return s
 
     def free_sequence(self, s: Sequence) -> None:
         if s.seq_id > 0:
+            if self.has_state:
+                self.cache.free_slot(s.seq_id)
             self.cache.pool.free_seq(s.seq_id)
             s.seq_id = -1
 
     def rollback(self, s: Sequence, length: int) -> None:
         """Speculative rollback / cancelled append: forget KV and tokens beyond ``length``."""
+        if self.has_state and length < s.num_computed:
+            raise ValueError("a recurrent-state model cannot rewind computed tokens without a state snapshot")
         self.cache.pool.truncate(s.seq_id, length)
         s.num_computed = min(s.num_computed, length)
         del s.tokens[length:]
@@ -139,6 +156,8 @@ class Engine:
                 break
             sub_table = d_table if len(rows) == len(seqs) else d_table[torch.tensor(rows, device=d_table.device)]
             b = make_prefill_batch(parts, sub_table, self.device, part_starts)
+            if self.has_state:
+                b.slots = torch.tensor([self.cache.slot_of[seqs[i].seq_id] for i in rows], dtype=torch.int32, device=self.device)
             self.h2d_bytes += b.num_tokens * 12
             res = self.model.greedy(b, self.cache) if sample else self.model.forward(b, self.cache)
             if out is None:
@@ -170,6 +189,8 @@ class Engine:
         if any(not p for p in parts):
             raise ValueError("extend needs at least one uncomputed token per sequence")
         b = make_prefill_batch(parts, d_table, self.device, [s.num_computed for s in seqs], last_only=False)
+        if self.has_state:
+            b.slots = torch.tensor([self.cache.slot_of[s.seq_id] for s in seqs], dtype=torch.int32, device=self.device)
         self.h2d_bytes += table.numel() * 4 + b.num_tokens * 12
         res = self.model.greedy(b, self.cache) if sample else self.model.forward(b, self.cache)
         self._table_key = None
@@ -189,6 +210,8 @@ class Engine:
     def _decode_body(self, n: int, greedy: bool):
         b = ForwardBatch(self.d_tokens[:n], self.d_positions[:n], self.d_seq_index[:n], self.d_kv_lens[:n],
                          self.d_table[:n], None, self._max_kv)
+        if self.has_state:
+            b.row_off, b.slots = self.d_row_off[:n + 1], self.d_slots[:n]
         if greedy:
             self.d_out[:n] = self.model.greedy(b, self.cache)
         else:
@@ -198,6 +221,8 @@ class Engine:
             self.d_logits[:n] = lg
 
     def _padded(self, n: int) -> int:
+        if self.has_state:
+            return n          # a padding row would advance row 0's recurrent state twice
         for g in self.GRAPH_BATCHES:
             if g >= n and g <= self.max_batch:
                 return g
@@ -253,6 +278,11 @@ class Engine:
             self.h2d_bytes += np_ * self.max_blocks * 4
             self._table_key = key
         self._max_kv = self.cfg.max_context
+        if self.has_state:
+            if np_ > n:
+                raise ValueError("recurrent-state models decode unpadded batches only")
+            self.h_slots[:n] = torch.tensor([self.cache.slot_of[s.seq_id] for s in seqs], dtype=torch.int32)
+            self.d_slots[:n].copy_(self.h_slots[:n], non_blocking=True)
         self.d_tokens[:np_].copy_(self.h_tokens[:np_], non_blocking=True)
         self.d_positions[:np_].copy_(self.h_positions[:np_], non_blocking=True)
         torch.add(self.d_positions[:np_], 1, out=self.d_kv_lens[:np_])
@@ -319,6 +349,14 @@ def build_engine(cfg: ModelConfig, device="cuda", seed: int = 0, num_pages: Opti
     the mixture-of-experts family."""
     device = torch.device(device)
     tp_size, tp_rank = (tp.size, tp.rank) if tp is not None else (1, 0)
+    if cfg.family == "qwen35":
+        from ..cache.hybrid import HybridCache
+        from ..models.qwen35 import Qwen35Model, init_random_qwen35_weights
+        model = Qwen35Model(cfg, init_random_qwen35_weights(cfg, device, seed), tp)
+        if num_pages is None:
+            num_pages = max_batch * ((cfg.max_context + cfg.page_size - 1) // cfg.page_size) + 8
+        cache = HybridCache(cfg, num_pages, device, max_seqs=2 * max_batch + 2, kv_heads=model.local_kv_heads)
+        return Engine(cfg, model, cache, device, max_batch=max_batch, use_cuda_graphs=use_cuda_graphs, tp=tp)
     if cfg.family == "moe":
         from ..models.moe import MoeModel, init_random_moe_weights
         ep_size, ep_rank = (ep.size, ep.rank) if ep is not None else (1, 0)

@@ -46,10 +46,12 @@ class ModelConfig:
     expert_format: str = "mxfp4"
     # linear-attention (gated delta net) hybrid: every `full_attention_interval`-th layer is full attention
     full_attention_interval: int = 0
-    gdn_heads: int = 0
+    gdn_heads: int = 0               # value heads of a gated-delta-net layer
+    gdn_qk_heads: int = 0            # query / key heads (value heads are a multiple)
     gdn_head_dim: int = 0
     gdn_conv_kernel: int = 4
     attn_output_gate: bool = False
+    post_norms: bool = False         # Gemma-style norms after attention and after the MLP (before the residual add)
 
     def to_dict(self) -> dict:
         return asdict(self)
@@ -103,10 +105,31 @@ def gpt_oss_120b_shape() -> ModelConfig:
                        attention_sinks=True, n_experts=128, top_k=4, expert_ffn=2880, expert_format="mxfp4")
 
 
+def qwen35_hybrid_shape(layers: int = 32) -> ModelConfig:
+    """Qwen3.5-class hybrid: three gated-delta-net layers then one full-attention layer, repeated; full layers use
+    q/k RMSNorm (1 + w), rotary on the first 64 of 256 channels (theta 1e7) and a sigmoid output gate."""
+    return ModelConfig(name="qwen35-hybrid", family="qwen35", n_layers=layers, d_model=2560, n_heads=16, n_kv_heads=4, head_dim=256,
+                       ffn=9216, vocab=151936, rope_theta=1e7, rotary_dim=64, rms_eps=1e-6, norm_offset_one=True,
+                       weight_format="bf16", kv_format="bf16", qk_norm=True, full_attention_interval=4, gdn_heads=32,
+                       gdn_qk_heads=16, gdn_head_dim=128, gdn_conv_kernel=4, attn_output_gate=True, max_context=8192)
+
+
+def gemma4_shape(layers: int = 48) -> ModelConfig:
+    """Gemma-4-class dense decoder: five 1024-token sliding-window layers per full layer, q/k norm, sandwich norms,
+    gelu-tanh gated MLP, embeddings scaled by sqrt(d), final logit soft-cap 30, tied embeddings."""
+    return ModelConfig(name="gemma4", family="gemma4", n_layers=layers, d_model=3840, n_heads=16, n_kv_heads=8, head_dim=256,
+                       ffn=15360, vocab=262144, rope_theta=1e6, rms_eps=1e-6, act="gelu_tanh", tie_embeddings=True,
+                       embedding_scale=3840 ** 0.5, logit_softcap=30.0, weight_format="bf16", kv_format="bf16",
+                       sliding_window=1024, window_layers=[(i + 1) % 6 != 0 for i in range(layers)], qk_norm=True,
+                       post_norms=True, max_context=8192)
+
+
 NAMED = {
     "tiny-llama": tiny_llama,
     "llama3-8b": llama3_8b,
     "llama3-70b": llama3_70b,
     "llama-draft": llama_draft_1b,
     "moe-120b": gpt_oss_120b_shape,
+    "qwen35-hybrid": qwen35_hybrid_shape,
+    "gemma4": gemma4_shape,
 }

@@ -49,6 +49,8 @@ class LayerWeights:
     down: LinearWeight
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
+    post_attn_norm: Optional[torch.Tensor] = None     # Gemma-style norms applied to the block output before the add
+    post_mlp_norm: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -136,7 +138,11 @@ def init_random_weights(cfg: ModelConfig, device, seed: int = 0, tp_size: int = 
             o=lin(wo),
             mlp_norm=torch.ones(d, device=device, dtype=dense_dtype),
             gate_up=lin(torch.cat([wg, wu], dim=0)),
-            down=lin(wd)))
+            down=lin(wd),
+            q_norm=torch.ones(hd, device=device, dtype=dense_dtype) if cfg.qk_norm else None,
+            k_norm=torch.ones(hd, device=device, dtype=dense_dtype) if cfg.qk_norm else None,
+            post_attn_norm=torch.ones(d, device=device, dtype=dense_dtype) if cfg.post_norms else None,
+            post_mlp_norm=torch.ones(d, device=device, dtype=dense_dtype) if cfg.post_norms else None))
         del wq, wk, wv, wo, wg, wu, wd
     final_norm = torch.ones(d, device=device, dtype=dense_dtype)
     if cfg.tie_embeddings:
@@ -181,17 +187,29 @@ class LlamaModel:
                 continue
             x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
             qkv = ops.linear(x, lw.qkv)
+            if cfg.qk_norm:
+                from ..ops import gdn as _g
+                qkv = _g.qk_headnorm(qkv, self.hq, self.hkv, hd, lw.q_norm, lw.k_norm, cfg.rms_eps, cfg.norm_offset_one)
             q = ops.rope_kv_append(qkv, b.positions, b.seq_index, b.block_table, kv, self.hq, self.hkv, hd,
                                    cfg.rope_theta, cfg.rotary_dim)
             a = ops.attention(q, kv, b, self.hq, self.hkv, hd, window=cfg.layer_window(li), quant_out=qo,
                               qkv=qkv)
             if self.quant and not qo:
                 a = ops.quant_fp8(a)
-            h = self.tp.row_linear(a, lw.o, h)
+            if cfg.post_norms:
+                # sandwich norms: the block output is normalised before it joins the residual stream
+                o = ops.rmsnorm(self.tp.row_linear(a, lw.o, None), lw.post_attn_norm, cfg.rms_eps, cfg.norm_offset_one)
+                h = ops.elementwise("add", h, o)
+            else:
+                h = self.tp.row_linear(a, lw.o, h)
             x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
             gu = ops.linear(x, lw.gate_up)
             act = ops.gated_act(gu, cfg.act, quant=self.quant)
-            h = self.tp.row_linear(act, lw.down, h)
+            if cfg.post_norms:
+                o = ops.rmsnorm(self.tp.row_linear(act, lw.down, None), lw.post_mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
+                h = ops.elementwise("add", h, o)
+            else:
+                h = self.tp.row_linear(act, lw.down, h)
         return h
 
     def _adapter_layer(self, li, lw, h, b, kv, ad):

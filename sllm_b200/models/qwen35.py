@@ -1,0 +1,164 @@
+"""Qwen3.5-class hybrid decoder: gated-delta-net (linear attention) layers with every N-th layer full attention.
+
+Full-attention layer: RMSNorm(1 + w) -> q | k | v (+ gate) projections -> per-head q/k RMSNorm(1 + w) -> rotary on
+the first `rotary_dim` channels -> paged causal attention -> sigmoid(gate) * attention -> o projection.
+GDN layer: RMSNorm -> in-projection to (q | k | v), z, b, a -> causal depthwise conv + SiLU on q|k|v with a rolling
+state -> gated delta-rule recurrence fused with the output RMSNorm and SiLU(z) -> out projection.  Both are
+followed by a SwiGLU MLP.  (Reference layer recipe: SURVEY call stack crates/sllm-core/src/qwen_graph.rs
+`linear.{qkv,z,b,a}_matmul -> linear_attention_state -> linear.out_matmul`; kernels K16, K27, K28.)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..engine.batch import ForwardBatch
+from ..ops import gdn as G
+from ..ops.core import LinearWeight
+from .config import ModelConfig
+from .llama import NoTP
+
+
+@dataclass
+class Qwen35Layer:
+    kind: str                       # full | gdn
+    in_norm: torch.Tensor
+    mlp_norm: torch.Tensor
+    gate_up: LinearWeight
+    down: LinearWeight
+    # full attention
+    qkv: Optional[LinearWeight] = None
+    gate: Optional[LinearWeight] = None
+    o: Optional[LinearWeight] = None
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    # gated delta net
+    in_proj: Optional[LinearWeight] = None      # -> [qkv width | z (v_heads * hd) | b (v_heads) | a (v_heads)] (padded to 8)
+    conv_w: Optional[torch.Tensor] = None       # [qkv width, taps]
+    a_log: Optional[torch.Tensor] = None        # fp32 [v_heads]
+    dt_bias: Optional[torch.Tensor] = None      # bf16 [v_heads]
+    out_norm: Optional[torch.Tensor] = None     # fp32 [hd]
+    out_proj: Optional[LinearWeight] = None
+
+
+@dataclass
+class Qwen35Weights:
+    embed: torch.Tensor
+    layers: list
+    final_norm: torch.Tensor
+    lm_head: LinearWeight
+    vocab_offset: int = 0
+
+
+def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: float = 0.02) -> Qwen35Weights:
+    device = torch.device(device)
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(seed)
+    dt = torch.float32 if cfg.weight_format == "fp32" else torch.bfloat16
+    d, hd = cfg.d_model, cfg.head_dim
+    ghd, vh, qh = cfg.gdn_head_dim, cfg.gdn_heads, cfg.gdn_qk_heads
+    width = (2 * qh + vh) * ghd
+
+    def rnd(shape, s=std):
+        return (torch.randn(shape, generator=gen, dtype=torch.float32) * s)
+
+    def lin(w):
+        return LinearWeight("dense", w.to(dt).contiguous().to(device))
+
+    def vec(v, dtype=None):
+        return v.to(dtype or dt).contiguous().to(device)
+
+    layers = []
+    for i in range(cfg.n_layers):
+        common = dict(in_norm=vec(rnd((d,), 0.05)), mlp_norm=vec(rnd((d,), 0.05)), gate_up=lin(rnd((2 * cfg.ffn, d))),
+                      down=lin(rnd((d, cfg.ffn))))
+        if (i + 1) % cfg.full_attention_interval == 0:
+            layers.append(Qwen35Layer("full", qkv=lin(rnd((cfg.q_size + 2 * cfg.kv_size, d))),
+                                      gate=lin(rnd((cfg.q_size, d))) if cfg.attn_output_gate else None,
+                                      o=lin(rnd((d, cfg.q_size))), q_norm=vec(rnd((hd,), 0.05), torch.bfloat16 if dt != torch.float32 else dt),
+                                      k_norm=vec(rnd((hd,), 0.05), torch.bfloat16 if dt != torch.float32 else dt), **common))
+        else:
+            n_in = width + vh * ghd + 2 * vh
+            n_in_pad = (n_in + 7) // 8 * 8
+            w_in = torch.zeros((n_in_pad, d))
+            w_in[:n_in] = rnd((n_in, d))
+            layers.append(Qwen35Layer("gdn", in_proj=lin(w_in), conv_w=vec(rnd((width, cfg.gdn_conv_kernel), 0.3)),
+                                      a_log=vec(rnd((vh,), 0.5), torch.float32), dt_bias=vec(rnd((vh,), 0.5)),
+                                      out_norm=vec(1.0 + rnd((ghd,), 0.05), torch.float32), out_proj=lin(rnd((d, vh * ghd))), **common))
+    embed = rnd((cfg.vocab, d)).to(dt).to(device)
+    head = embed if cfg.tie_embeddings else rnd((cfg.vocab, d)).to(dt).contiguous().to(device)
+    return Qwen35Weights(embed, layers, vec(rnd((d,), 0.05)), LinearWeight("dense", head), 0)
+
+
+class Qwen35Model:
+    def __init__(self, cfg: ModelConfig, weights: Qwen35Weights, tp=None):
+        self.cfg, self.w = cfg, weights
+        self.tp = tp or NoTP()
+        if self.tp.size != 1:
+            raise ValueError("the hybrid family runs without tensor parallelism in this build")
+        self.hq, self.hkv = cfg.n_heads, cfg.n_kv_heads
+
+    @property
+    def local_kv_heads(self) -> int:
+        return self.hkv
+
+    def _mlp(self, h, lw):
+        cfg = self.cfg
+        x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
+        return ops.linear(ops.gated_act(ops.linear(x, lw.gate_up), cfg.act), lw.down, h)
+
+    def hidden(self, b: ForwardBatch, cache) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        hd, ghd, vh, qh = cfg.head_dim, cfg.gdn_head_dim, cfg.gdn_heads, cfg.gdn_qk_heads
+        width = (2 * qh + vh) * ghd
+        if b.row_off is None or b.slots is None:
+            raise ValueError("the hybrid family needs row offsets and state slots in the batch")
+        h = ops.embedding(w.embed, b.tokens, cfg.embedding_scale)
+        for li, lw in enumerate(w.layers):
+            x = ops.rmsnorm(h, lw.in_norm, cfg.rms_eps, cfg.norm_offset_one)
+            if lw.kind == "full":
+                kv = cache.layer(li)
+                qkv = ops.linear(x, lw.qkv)
+                qkv = G.qk_headnorm(qkv, self.hq, self.hkv, hd, lw.q_norm, lw.k_norm, cfg.rms_eps, True)
+                q = ops.rope_kv_append(qkv, b.positions, b.seq_index, b.block_table, kv, self.hq, self.hkv, hd, cfg.rope_theta,
+                                       cfg.rotary_dim)
+                a = ops.paged_attention(q, kv, b.block_table, b.seq_index, b.kv_lens, self.hq, self.hkv, hd, max_kv=b.max_kv)
+                if lw.gate is not None:
+                    a = ops.elementwise("sigmoid_mul", a.contiguous(), ops.linear(x, lw.gate))
+                h = ops.linear(a, lw.o, h)
+            else:
+                conv_state, rec_state = cache.gdn(li)
+                p = ops.linear(x, lw.in_proj)
+                qkv = p[:, :width].contiguous()
+                z = p[:, width:width + vh * ghd].contiguous()
+                bb = p[:, width + vh * ghd:width + vh * ghd + vh].contiguous()
+                aa = p[:, width + vh * ghd + vh:width + vh * ghd + 2 * vh].contiguous()
+                qkv = G.conv_silu(qkv, lw.conv_w, conv_state, b.row_off, b.slots)
+                o = G.recurrent(qkv, z, bb, aa, lw.a_log, lw.dt_bias, lw.out_norm, rec_state, b.row_off, b.slots, qh, vh, ghd)
+                h = ops.linear(o, lw.out_proj, h)
+            h = self._mlp(h, lw)
+        return h
+
+    def logits(self, h, b):
+        cfg, w = self.cfg, self.w
+        if b.logit_rows is not None:
+            h = h.index_select(0, b.logit_rows)
+        x = ops.rmsnorm(h, w.final_norm, cfg.rms_eps, cfg.norm_offset_one)
+        return ops.linear(x, w.lm_head)
+
+    def forward(self, b, cache):
+        return self.logits(self.hidden(b, cache), b)
+
+    def greedy(self, b, cache):
+        return ops.argmax(self.logits(self.hidden(b, cache), b))
+
+
+def tiny_qwen35() -> ModelConfig:
+    """CPU-checkable hybrid: 4 layers (3 GDN + 1 full), 1 GDN q/k head and 2 value heads of 128."""
+    return ModelConfig(name="tiny-qwen35", family="qwen35", n_layers=4, d_model=128, n_heads=2, n_kv_heads=1, head_dim=64, ffn=256,
+                       vocab=512, rope_theta=1e7, rotary_dim=32, rms_eps=1e-6, norm_offset_one=True, weight_format="bf16",
+                       kv_format="bf16", qk_norm=True, full_attention_interval=4, gdn_heads=2, gdn_qk_heads=1, gdn_head_dim=128,
+                       gdn_conv_kernel=4, attn_output_gate=True, max_context=128)

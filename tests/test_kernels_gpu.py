@@ -434,3 +434,62 @@ def test_w4_llama_gpu_matches_cpu(fmt):
     assert rel_err(lg, lc) < 3e-2
     assert all(len(o) == 8 for o in g.generate(prompts, 8))
     assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+def test_gdn_kernels_match_oracle():
+    from sllm_b200.ops import gdn
+    torch.manual_seed(3)
+    qk_heads, v_heads, hd, taps = 2, 4, 128, 4
+    width = (2 * qk_heads + v_heads) * hd
+    counts = [5, 1, 9]
+    t = sum(counts)
+    row_off = torch.tensor([0, 5, 6, 15], dtype=torch.int32)
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32)
+    x = (torch.randn(t, width) * 0.5).bfloat16()
+    w = (torch.randn(width, taps) * 0.3).bfloat16()
+    cs = (torch.randn(4, taps - 1, width) * 0.5).bfloat16()
+    cs_d = cs.clone().to(DEV)
+    y_c = gdn.conv_silu(x, w, cs, row_off, slots)
+    y_g = gdn.conv_silu(x.to(DEV), w.to(DEV), cs_d, row_off.to(DEV), slots.to(DEV))
+    assert rel_err(y_g.float().cpu(), y_c.float()) < 1e-2
+    assert rel_err(cs_d.float().cpu(), cs.float()) < 1e-6
+    z = torch.randn(t, v_heads * hd).bfloat16()
+    b, a = torch.randn(t, v_heads).bfloat16(), torch.randn(t, v_heads).bfloat16()
+    a_log, dtb, nw = torch.randn(v_heads) * 0.5, torch.randn(v_heads).bfloat16(), torch.rand(hd) + 0.5
+    st = torch.randn(4, v_heads, hd, hd) * 0.1
+    st_d = st.clone().to(DEV)
+    o_c = gdn.recurrent(y_c, z, b, a, a_log, dtb, nw, st, row_off, slots, qk_heads, v_heads, hd)
+    o_g = gdn.recurrent(y_c.to(DEV), z.to(DEV), b.to(DEV), a.to(DEV), a_log.to(DEV), dtb.to(DEV), nw.to(DEV), st_d,
+                        row_off.to(DEV), slots.to(DEV), qk_heads, v_heads, hd)
+    assert rel_err(o_g.float().cpu(), o_c.float()) < 2e-2
+    assert rel_err(st_d.cpu(), st) < 1e-3
+    assert torch.equal(st_d.cpu()[1], st[1])                       # the unused slot is untouched
+    qkv = torch.randn(7, (4 + 2 * 2) * 64).bfloat16()
+    wq, wk = torch.randn(64).bfloat16(), torch.randn(64).bfloat16()
+    want = gdn.qk_headnorm(qkv.clone(), 4, 2, 64, wq, wk, 1e-6, True)
+    got = gdn.qk_headnorm(qkv.clone().to(DEV), 4, 2, 64, wq.to(DEV), wk.to(DEV), 1e-6, True)
+    assert rel_err(got.float().cpu(), want.float()) < 1e-2
+    assert torch.equal(got.cpu()[:, 6 * 64:], qkv[:, 6 * 64:])     # v heads untouched
+
+
+@pytest.mark.gpu
+def test_hybrid_and_gemma_models_gpu_match_cpu():
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.models import config as MC
+    from sllm_b200.models.qwen35 import tiny_qwen35
+    gem = MC.ModelConfig(name="tiny-gemma", family="gemma4", n_layers=3, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512,
+                         vocab=1024, act="gelu_tanh", tie_embeddings=True, embedding_scale=16.0, logit_softcap=30.0,
+                         weight_format="bf16", kv_format="bf16", sliding_window=16, window_layers=[True, True, False], qk_norm=True,
+                         post_norms=True, max_context=128)
+    for cfg in (tiny_qwen35(), gem):
+        g = build_engine(cfg, DEV, seed=1, num_pages=32, max_batch=2)
+        c = build_engine(cfg, "cpu", seed=1, num_pages=32, max_batch=2, use_cuda_graphs=False)
+        prompts = [list(range(3, 40)), [5, 6, 7, 8]]
+        lg = g.prefill([g.new_sequence(p) for p in prompts], sample=False).float().cpu()
+        lc = c.prefill([c.new_sequence(p) for p in prompts], sample=False).float()
+        assert rel_err(lg, lc) < 4e-2, (cfg.name, rel_err(lg, lc))
+        out = g.generate(prompts, 10)                      # graph-captured decode with state slots
+        assert out == g.generate(prompts, 10)
+        assert g.generate([prompts[0] + out[0][:5]], 5)[0] == out[0][5:]
+    assert ops.device_status(torch.device(DEV)) == 0

@@ -1,0 +1,63 @@
+"""Model families beyond the plain dense decoder, on the CPU oracle path: the gated-delta-net hybrid and the
+Gemma-style options (q/k norm, sandwich norms, gelu-tanh, soft-cap, scaled tied embeddings, window schedule)."""
+import pytest
+import torch
+
+from sllm_b200.engine.engine import build_engine
+from sllm_b200.models import config as MC
+from sllm_b200.models.qwen35 import tiny_qwen35
+
+
+def test_hybrid_decode_equals_prefill_and_state_slots_are_isolated():
+    cfg = tiny_qwen35()
+    cfg.weight_format, cfg.kv_format = "fp32", "fp32"
+    eng = build_engine(cfg, "cpu", seed=1, num_pages=32, max_batch=2, use_cuda_graphs=False)
+    p = [list(range(3, 20)), [5, 6, 7]]
+    both = eng.generate(p, 6)
+    alone = [eng.generate([x], 6)[0] for x in p]
+    assert both == alone                                     # batch rows do not leak state into one another
+    assert eng.generate([p[0] + both[0][:3]], 3)[0] == both[0][3:]
+    assert len(eng.cache.slot_of) == 0 and len(eng.cache._free) == eng.cache.max_seqs
+    # chunked prefill carries the conv window and the recurrent matrix across chunks
+    s = eng.new_sequence(p[0])
+    t_chunked = eng.prefill([s], chunk_tokens=5)[0]
+    eng.free_sequence(s)
+    assert t_chunked == both[0][0]
+    # a recurrent state can be shared only at the end of the source's computed tokens
+    src = eng.new_sequence(p[0])
+    eng.prefill([src])
+    f1 = eng.fork_sequence(src, p[0] + [9, 9])
+    assert f1.num_computed == len(p[0])
+    f2 = eng.fork_sequence(src, p[0][:10] + [1, 2])
+    assert f2.num_computed == 0
+    a = eng.prefill([f1])[0]
+    fresh = eng.new_sequence(p[0] + [9, 9])
+    assert eng.prefill([fresh])[0] == a
+    with pytest.raises(ValueError):
+        eng.rollback(src, 3)
+    for q in (src, f1, f2, fresh):
+        eng.free_sequence(q)
+
+
+def test_gemma_style_options():
+    cfg = MC.ModelConfig(name="tiny-gemma", family="gemma4", n_layers=3, d_model=128, n_heads=4, n_kv_heads=2, head_dim=32, ffn=256,
+                         vocab=512, act="gelu_tanh", tie_embeddings=True, embedding_scale=128 ** 0.5, logit_softcap=30.0,
+                         weight_format="fp32", kv_format="fp32", sliding_window=8, window_layers=[True, True, False], qk_norm=True,
+                         post_norms=True, max_context=128)
+    eng = build_engine(cfg, "cpu", seed=2, num_pages=32, max_batch=2, use_cuda_graphs=False)
+    assert eng.model.w.lm_head.w is eng.model.w.embed                       # tied
+    prompt = list(range(7, 40))
+    out = eng.generate([prompt], 8)[0]
+    assert eng.generate([prompt + out[:4]], 4)[0] == out[4:]                 # window + cache consistent across decode
+    s = eng.new_sequence(prompt)
+    lg = eng.prefill([s], sample=False)
+    eng.free_sequence(s)
+    assert lg.abs().max() <= 30.0 + 1e-4                                      # soft-capped
+    # the options matter: switching them off changes the logits
+    import dataclasses
+    plain = dataclasses.replace(cfg, post_norms=False, qk_norm=False, logit_softcap=0.0)
+    e2 = build_engine(plain, "cpu", seed=2, num_pages=32, max_batch=2, use_cuda_graphs=False)
+    s = e2.new_sequence(prompt)
+    assert not torch.allclose(e2.prefill([s], sample=False), lg, atol=1e-3)
+    assert MC.NAMED["gemma4"]().window_layers[:6] == [True] * 5 + [False]
+    assert MC.NAMED["qwen35-hybrid"]().full_attention_interval == 4
