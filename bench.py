@@ -195,6 +195,86 @@ def run_torch_baseline(args):
     return 0
 
 
+def run_speculative(args, cfg, device, tp, world, rank, barrier, max_over_ranks, clocks):
+    """Speculative decoding: the target (tensor parallel over all ranks) verifies `spec_width` tokens drafted by a
+    llama-draft model that runs on every rank (TP=1); acceptance is forced by a seeded Bernoulli(0.7) mask so that the
+    full verify compute always runs; the comparison is target-only decoding of the same batch on the same box."""
+    import torch
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.engine.speculative import ExternalDraftProvider, SpeculativeDecoder
+    from sllm_b200.models import config as mc
+    eng = build_engine(cfg, device, seed=0, max_batch=args.batch, tp=tp)
+    dcfg = mc.NAMED["llama-draft"]()
+    dcfg.max_context = cfg.max_context
+    deng = build_engine(dcfg, device, seed=7, max_batch=args.batch)
+    g = torch.Generator().manual_seed(1234)
+    prompts = torch.randint(0, cfg.vocab, (args.batch, args.prompt), generator=g).tolist()
+
+    def fresh():
+        seqs = [eng.new_sequence(p) for p in prompts]
+        for i in range(0, args.batch, 8):
+            for s, t in zip(seqs[i:i + 8], eng.prefill(seqs[i:i + 8])):
+                s.tokens.append(t)
+        return seqs
+
+    # target-only reference on the same box
+    seqs = fresh()
+    for _ in range(args.warmup):
+        for s, t in zip(seqs, eng.decode(seqs)):
+            s.tokens.append(t)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        for s, t in zip(seqs, eng.decode(seqs)):
+            s.tokens.append(t)
+    e1.record()
+    barrier()
+    base_ms = max_over_ranks(e0.elapsed_time(e1))
+    for s in seqs:
+        eng.free_sequence(s)
+    # speculative
+    dec = SpeculativeDecoder(eng, ExternalDraftProvider(deng, args.spec_width, cfg.vocab), args.spec_width, forced_accept_p=0.7,
+                             seed=99)
+    seqs = fresh()
+    for _ in range(args.warmup):
+        dec.step(seqs)
+    if rank == 0:
+        clocks.start()
+    emitted0 = dec.acct.emitted
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        dec.step(seqs)
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    clk = clocks.stop() if rank == 0 else None
+    tokens = dec.acct.emitted - emitted0
+    if rank == 0:
+        value = tokens / (ms / 1e3)
+        base = args.batch * args.steps / (base_ms / 1e3)
+        print(json.dumps({
+            "metric": "speculative_decode_output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": round(value / REFERENCE_PUBLISHED_TOK_S, 2), "dtype": f"{args.weights} target, bf16 draft",
+            "data": "synthetic: seeded uniform-random prompts, random-init weights; acceptance forced by a seeded Bernoulli(0.7) mask",
+            "config": {"model": f"{cfg.name}-{args.weights}", "draft": "llama-draft-bf16", "global_batch": args.batch,
+                       "seq_len": args.prompt, "draft_width": args.spec_width, "parallelism": f"target tp{args.gpus}, draft tp1"},
+            "clocks": clk, "target_only_tok_s": round(base, 2), "speedup_vs_target_only": round(value / base, 3),
+            "acceptance": dec.acct.to_dict(), "gpu_launches": int(eng.kernel_launches + deng.kernel_launches), "impl": "own"}))
+    sys.stdout.flush()
+    if world > 1:
+        torch.cuda.synchronize()
+        if tp is not None:
+            tp.close()
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+        os._exit(0)
+    return 0
+
+
 def model_forward_rows(model, tokens, row0: int, start: int):
     """Prefill of a group of rows into their slice of the contiguous KV cache."""
     k_full, v_full = model.k, model.v
@@ -344,6 +424,8 @@ def main():
         torch.cuda.empty_cache()
         return res
 
+    if args.spec_width > 0:
+        return run_speculative(args, cfg, device, tp, world, rank, barrier, max_over_ranks, ClockSampler(local_rank))
     main_res = measure(args.batch, args.steps, args.warmup, True)
     extra = None
     if not args.no_batch1 and args.batch != 1:

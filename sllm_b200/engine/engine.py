@@ -188,6 +188,10 @@ class Engine:
         parts = [s.tokens[s.num_computed:] for s in seqs]
         if any(not p for p in parts):
             raise ValueError("extend needs at least one uncomputed token per sequence")
+        r = len(parts[0])
+        if (sample and self.use_graphs and not self.has_state and r <= self.MAX_EXTEND_ROWS and len(seqs) <= self.max_batch
+                and all(len(p) == r for p in parts)):
+            return self._extend_graphed(seqs, parts, r, table)
         b = make_prefill_batch(parts, d_table, self.device, [s.num_computed for s in seqs], last_only=False)
         if self.has_state:
             b.slots = torch.tensor([self.cache.slot_of[s.seq_id] for s in seqs], dtype=torch.int32, device=self.device)
@@ -202,6 +206,72 @@ class Engine:
         for s, p in zip(seqs, parts):
             out.append(flat[r0:r0 + len(p)] if sample else res[r0:r0 + len(p)])
             r0 += len(p)
+            pool.commit(s.seq_id, len(s.tokens))
+            s.num_computed = len(s.tokens)
+        return out
+
+    MAX_EXTEND_ROWS = 9      # a verify block: the last committed token plus up to 8 drafts
+
+    def _extend_graphed(self, seqs: list, parts: list, r: int, table: torch.Tensor):
+        """`extend` for equally long blocks (speculative verify) replayed from a CUDA graph per (sequences, rows)."""
+        n = len(seqs)
+        t = n * r
+        if getattr(self, "_ext", None) is None:
+            cap = self.max_batch * self.MAX_EXTEND_ROWS
+            pin = self.is_cuda
+            self._ext = dict(
+                h_tok=torch.zeros(cap, dtype=torch.int32, pin_memory=pin), h_pos=torch.zeros(cap, dtype=torch.int32, pin_memory=pin),
+                d_tok=torch.zeros(cap, dtype=torch.int32, device=self.device), d_pos=torch.zeros(cap, dtype=torch.int32, device=self.device),
+                d_kv=torch.ones(cap, dtype=torch.int32, device=self.device), d_out=torch.zeros(cap, dtype=torch.int32, device=self.device),
+                h_out=torch.zeros(cap, dtype=torch.int32, pin_memory=pin), seq_index={}, graphs={}, launches={})
+        e = self._ext
+        flat_tok = [x for p in parts for x in p]
+        flat_pos = [s.num_computed + i for s in seqs for i in range(r)]
+        e["h_tok"][:t] = torch.tensor(flat_tok, dtype=torch.int32)
+        e["h_pos"][:t] = torch.tensor(flat_pos, dtype=torch.int32)
+        self.h_table[:n].copy_(table)
+        self.d_table[:n].copy_(self.h_table[:n], non_blocking=True)
+        self._table_key = None
+        e["d_tok"][:t].copy_(e["h_tok"][:t], non_blocking=True)
+        e["d_pos"][:t].copy_(e["h_pos"][:t], non_blocking=True)
+        torch.add(e["d_pos"][:t], 1, out=e["d_kv"][:t])
+        self.h2d_bytes += n * self.max_blocks * 4 + t * 8
+        key = (n, r)
+        si = e["seq_index"].get(key)
+        if si is None:
+            si = torch.arange(n, dtype=torch.int32, device=self.device).repeat_interleave(r).contiguous()
+            e["seq_index"][key] = si
+
+        def body():
+            b = ForwardBatch(e["d_tok"][:t], e["d_pos"][:t], si, e["d_kv"][:t], self.d_table[:n], None, self.cfg.max_context)
+            e["d_out"][:t] = self.model.greedy(b, self.cache)
+
+        g = e["graphs"].get(key)
+        if g is None:
+            st = torch.cuda.Stream(device=self.device)
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                body()
+            torch.cuda.current_stream().wait_stream(st)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            from ..ops import _lib
+            before = _lib.LAUNCH_COUNT[0]
+            with torch.cuda.graph(g):
+                body()
+            e["launches"][key] = _lib.LAUNCH_COUNT[0] - before
+            e["graphs"][key] = g
+        g.replay()
+        self.kernel_launches += e["launches"][key]
+        e["h_out"][:t].copy_(e["d_out"][:t], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += 4 * t
+        flat = e["h_out"][:t].tolist()
+        self._check_status()
+        pool = self.cache.pool
+        out = []
+        for i, s in enumerate(seqs):
+            out.append(flat[i * r:(i + 1) * r])
             pool.commit(s.seq_id, len(s.tokens))
             s.num_computed = len(s.tokens)
         return out

@@ -76,19 +76,28 @@ class ExternalDraftProvider:
         """Greedy drafts for a batch; the draft engine keeps one sequence per key and reuses its KV prefix."""
         w = min(width or self.width, self.width)
         eng = self.engine
-        seqs, fresh = [], []
+        seqs = []
         for key, toks in zip(keys, token_lists):
             s = self._seqs.get(key)
-            if s is None or s.tokens[:s.num_computed] != toks[:s.num_computed] or s.num_computed >= len(toks):
-                if s is not None:
-                    eng.free_sequence(s)
+            if s is None:
                 s = eng.new_sequence(toks)
                 self._seqs[key] = s
             else:
+                # keep the KV of the longest prefix the draft already computed (its own accepted drafts included)
+                limit = min(s.num_computed, len(toks) - 1)
+                c = 0
+                while c < limit and s.tokens[c] == toks[c]:
+                    c += 1
+                eng.rollback(s, c)
                 s.tokens = list(toks)
+                s.prompt = list(toks)
             seqs.append(s)
         drafts = [[] for _ in seqs]
-        first = eng.prefill(seqs)           # computes whatever suffix is new and samples greedily
+        # computes whatever suffix is new and samples greedily; equal suffix lengths replay a captured graph
+        if len({len(s.tokens) - s.num_computed for s in seqs}) == 1 and seqs[0].num_computed > 0:
+            first = [r[-1] for r in eng.extend(seqs)]
+        else:
+            first = eng.prefill(seqs)
         for i, s in enumerate(seqs):
             s.tokens.append(first[i])
             drafts[i].append(first[i])
