@@ -162,7 +162,7 @@ class PrefixCache:
                 self.counters["rejected"] += 1
                 return False
         try:
-            child = self.engine.cache.fork(seq.seq_id, n_tokens)
+            child = self.engine.fork_kv(seq, n_tokens)
         except Exception:
             self.counters["rejected"] += 1
             return False
@@ -205,7 +205,7 @@ class PrefixCache:
                     del self._index[h]
         self._entries.pop(e.eid, None)
         try:
-            self.engine.cache.pool.free_seq(e.seq_id)
+            self.engine.free_kv(e.seq_id)
         except Exception:
             pass
 

@@ -125,7 +125,14 @@ def make_backend(a, gguf: str, derived_lock: str, alias: str, overrides=None):
     src = argparse.Namespace(gguf=gguf, derived_lock=derived_lock, device_index=o.get("device_index", a.device_index),
                              target=a.target, kv_cache_encoding=o.get("kv_cache_encoding") or a.kv_cache_encoding,
                              context_length=o.get("context_length") or a.context_length, cpu=a.cpu)
-    eng, tok, g, lock = open_model(src, max_batch=o.get("max_batch") or a.max_batch)
+    tp, ctrl = getattr(a, "_tp", None), getattr(a, "_ctrl", None)
+    eng, tok, g, lock = open_model(src, max_batch=o.get("max_batch") or a.max_batch, tp=tp)
+    if tp is not None:
+        from ..engine.distributed import LeaderEngine, follow
+        if tp.rank != 0:
+            follow(eng, ctrl)          # returns when the leader shuts down
+            return None
+        eng = LeaderEngine(eng, ctrl)
     policy = None
     if a.context_policy == "keep-prefix-recent":
         policy = ContextPolicy.keep_prefix_recent(a.context_keep_prefix, a.context_keep_recent)
@@ -152,6 +159,35 @@ def serve(a) -> int:
     from ..server.model_lifecycle import ManifestError, ModelLifecycleRegistry, read_manifest
     life = ServerLifecycle()
     t0 = time.time()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        # one process per GPU: rank 0 serves HTTP and drives the others through the leader/follower protocol
+        import datetime
+        import torch
+        import torch.distributed as dist
+        from ..parallel.tp import make_tp
+        if a.models:
+            raise CliError("multi-rank serving takes one model (--gguf), not a manifest")
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        rank = int(os.environ.get("RANK", "0"))
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if a.cpu:
+            raise CliError("multi-rank serving needs GPUs")
+        torch.cuda.set_device(local)
+        a.device_index = local
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=600))
+        a._ctrl = dist.new_group(backend="gloo")
+        from ..formats import gguf as G
+        from ..models import loader
+        gfile = G.GgufFile(a.gguf)
+        d_model = loader.config_from_gguf(gfile).d_model
+        gfile.close()
+        a._tp = make_tp(world, rank, torch.device("cuda", local), impl="fused", max_tokens=max(a.max_batch, 128), d_model=d_model)
+        if rank != 0:
+            make_backend(a, a.gguf, a.derived_lock, a.model or "model")     # follows until the leader stops
+            a._tp.close()
+            dist.destroy_process_group()
+            os._exit(0)
     dyn = None
     backends, fps = {}, {}
     try:
@@ -220,6 +256,13 @@ def serve(a) -> int:
     life.to("shutdown")
     audit["uptime_seconds"] = round(time.time() - t0, 3)
     emit(audit)
+    if world > 1:
+        import torch.distributed as dist
+        for b in backends.values():
+            b.engine.stop_followers()
+        a._tp.close()
+        dist.destroy_process_group()
+        os._exit(0)
     return 0
 
 

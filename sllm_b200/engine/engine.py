@@ -115,6 +115,13 @@ class Engine:
                 self.cache.copy_slot(src.seq_id, s.seq_id)
         return s
 
+    def fork_kv(self, s: Sequence, n_tokens: int) -> int:
+        """Pool-level fork (used by the prefix cache): a new pool sequence sharing the first `n_tokens` of `s`."""
+        return self.cache.fork(s.seq_id, n_tokens)
+
+    def free_kv(self, pool_seq_id: int) -> None:
+        self.cache.pool.free_seq(pool_seq_id)
+
     def free_sequence(self, s: Sequence) -> None:
         if s.seq_id > 0:
             if self.has_state:

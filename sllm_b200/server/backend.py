@@ -249,6 +249,8 @@ class EngineBackend:
         (reference: crates/sllm-core/src/inference_embedding.rs)."""
         import torch
         from ..engine.batch import make_prefill_batch
+        if type(self.engine).__name__ == "LeaderEngine":
+            raise RuntimeError("embeddings are not available on a multi-rank engine")
         out = []
         with self._embed_lock:
             for ids in token_lists:

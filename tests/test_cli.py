@@ -287,3 +287,29 @@ def test_server_flag_validation(capsys):
         capsys.readouterr()
         assert server.main(argv) == 2
         assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["event"] == "error"
+
+
+@pytest.mark.timeout(180)
+def test_serve_bench_against_live_server(model):
+    from sllm_b200.utils import serve_bench
+    port = _free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "sllm-server"), "--gguf", model[0], "--derived-lock", model[1],
+                             "--model", "tiny", "--cpu", "--listen", f"127.0.0.1:{port}", "--max-batch", "4", "--queue-capacity", "16",
+                             "--shutdown-timeout-seconds", "5"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+    try:
+        assert json.loads(proc.stdout.readline())["event"] == "ready"
+        import asyncio
+        import argparse
+        a = argparse.Namespace(url=f"http://127.0.0.1:{port}", model="tiny", requests=6, rate=50.0, concurrency=4, prompt_min=20,
+                               prompt_max=60, output_min=4, output_max=8, tokens_per_word=1, byte_tokens=True, api_key_env=None,
+                               timeout=120.0, seed=1)
+        rep = asyncio.run(serve_bench.run(a))
+        assert rep["completed"] == 6 and rep["failed"] == 0 and rep["output_tokens"] >= 20
+        assert rep["ttft_ms"]["p50"] > 0 and rep["itl_ms"]["p50"] is not None
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        try:
+            proc.communicate(timeout=60)
+        except Exception:
+            proc.kill()
