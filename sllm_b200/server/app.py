@@ -448,7 +448,9 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
                             yield emit(err.body())      # terminal error envelope, then close without [DONE]
                             return
                         extra = {"logprobs": _logprobs_obj(backend, lps[i])} if (req.logprobs and backend) else None
-                        yield emit(chunk(i, {}, payload["finish_reason"], extra))
+                        fin = chunk(i, {}, payload["finish_reason"], extra)
+                        fin["usage"] = payload["usage"]        # per-choice usage rides on its finishing chunk
+                        yield emit(fin)
             ok = True
             if session is not None:
                 session.append(b"[DONE]")
