@@ -313,12 +313,18 @@ class Engine:
         g = self._graphs.get(key)
         if g is None:
             # warm up outside capture (module init, workspace allocation), then capture
+            # a recurrent state is advanced by every execution: keep it out of the warm-up run
+            snap = (self.cache.conv_state.clone(), self.cache.rec_state.clone()) if self.has_state else None
             s = torch.cuda.Stream(device=self.device)
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
                 self._decode_body(n, greedy)
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
+            if snap is not None:
+                self.cache.conv_state.copy_(snap[0])
+                self.cache.rec_state.copy_(snap[1])
+                torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             from ..ops import _lib
             before = _lib.LAUNCH_COUNT[0]
