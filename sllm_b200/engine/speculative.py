@@ -85,9 +85,16 @@ class ExternalDraftProvider:
             else:
                 # keep the KV of the longest prefix the draft already computed (its own accepted drafts included)
                 limit = min(s.num_computed, len(toks) - 1)
-                c = 0
-                while c < limit and s.tokens[c] == toks[c]:
-                    c += 1
+                if s.tokens[:limit] == toks[:limit]:      # the usual case, compared at C speed
+                    c = limit
+                else:
+                    c = 0
+                    while c < limit and s.tokens[c] == toks[c]:
+                        c += 1
+                # recompute exactly two rows whenever possible: every sequence then appends the same number of
+                # rows and the catch-up replays one captured graph instead of an eager ragged prefill
+                if c >= len(toks) - 2 >= 1:
+                    c = len(toks) - 2
                 eng.rollback(s, c)
                 s.tokens = list(toks)
                 s.prompt = list(toks)
