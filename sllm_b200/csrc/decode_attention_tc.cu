@@ -29,7 +29,7 @@
 
 namespace sllm {
 
-constexpr int kDaThreads = 192;
+constexpr int kDaThreads = 224;   // producer warp, S issuer, four softmax warps, PV issuer
 constexpr int kDaTile = 128;
 constexpr int kDaStages = 3;
 constexpr int kDaTileBytes = kDaTile * 128;  // 16 KB per K or V tile
@@ -42,7 +42,7 @@ struct __align__(16) DecodeTcBarriers {
   uint64_t kv_full[kDaStages];
   uint64_t kv_empty[kDaStages];
   uint64_t s_full[2];
-  uint64_t p_ready;
+  uint64_t p_ready[2];   // by tile parity: a waiter can then never fall a whole parity cycle behind
   uint64_t o_full[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -133,7 +133,8 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     }
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
-    mbar_init(&bars->p_ready, 128);
+    mbar_init(&bars->p_ready[0], 128);
+    mbar_init(&bars->p_ready[1], 128);
     mbar_init(&bars->o_full[0], 1);
     mbar_init(&bars->o_full[1], 1);
     bars->abort_flag = 0;
@@ -221,45 +222,53 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ S = K.Q^T issuer
+    // One thread spends about 160 cycles per tcgen05.mma, so the S and the P.V MMAs of a tile come from two
+    // threads in different warps, whose issue overlaps.  Each of them consumes every phase of the barriers
+    // it waits on, in order.
     // The softmax warps quantise Q into shared memory first; barrier 2 joins them with this warp.
     if (nt > 0) asm volatile("bar.sync 2, 160;" ::: "memory");
     if (lane == 0 && nt > 0) {
       constexpr uint32_t idesc_s = make_idesc(kFmtE4M3, 128, kDaHeadsPad, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc(kFmtE4M3, 128, kDaHeadsPad, 1, 0);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
-      auto issue_s = [&](int j) {
-        const uint32_t k_addr = smem_u32(kv_s + (j % kDaStages) * 2 * kDaTileBytes);
+      const uint32_t q_addr = smem_u32(q_s);
+      for (int j = 0; j < nt; ++j) {
+        const int st = j % kDaStages;
+        if (!mbar_wait(&bars->kv_full[st], (j / kDaStages) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMA_FULL))
+          break;
+        // S buffer j & 1 is free once the softmax warps have read S(j - 2), which they do before p_ready(j - 2)
+        if (j >= 2 && !mbar_wait(&bars->p_ready[j & 1], ((j - 2) >> 1) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMEM_EMPTY))
+          break;
+        tc_fence_after();
+        DA_TRACE(j, 6);
+        const uint32_t k_addr = smem_u32(kv_s + st * 2 * kDaTileBytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // 32 channels per MMA
           umma_f8(tmem_base + (j & 1) * 16, make_smem_desc_sw128(k_addr) + 2 * k, make_smem_desc_sw128(q_addr) + 2 * k,
                   idesc_s, k != 0);
         tc_commit(&bars->s_full[j & 1]);
-      };
-      bool ok = mbar_wait(&bars->kv_full[0], 0, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMA_FULL);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
       }
-      for (int j = 0; ok && j < nt; ++j) {
-        if (j + 1 < nt) {
-          const int st1 = (j + 1) % kDaStages;
-          if (!mbar_wait(&bars->kv_full[st1], ((j + 1) / kDaStages) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMA_FULL))
-            break;
-          tc_fence_after();
-          DA_TRACE(j, 6);
-          issue_s(j + 1);
-        }
-        if (!mbar_wait(&bars->p_ready, j & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMEM_EMPTY)) break;
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ O = P.V issuer
+    if (lane == 0 && nt > 0) {
+      constexpr uint32_t idesc_pv = make_idesc(kFmtE4M3, 128, kDaHeadsPad, 1, 0);
+      const uint32_t p_addr = smem_u32(p_s);
+      for (int j = 0; j < nt; ++j) {
+        const int st = j % kDaStages;
+        // this thread's own view of the tile's TMA writes; the phase completed before S(j) was issued
+        if (!mbar_wait(&bars->kv_full[st], (j / kDaStages) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMA_FULL))
+          break;
+        if (!mbar_wait(&bars->p_ready[j & 1], (j >> 1) & 1, abort_flag, p.status_word, kDaStatusBase + SLLM_DEV_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         DA_TRACE(j, 7);
-        const uint32_t v_addr = smem_u32(kv_s + (j % kDaStages) * 2 * kDaTileBytes + kDaTileBytes);
+        const uint32_t v_addr = smem_u32(kv_s + st * 2 * kDaTileBytes + kDaTileBytes);
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // 32 keys per MMA
           umma_f8(tmem_base + 32 + (j & 1) * 16, make_smem_desc_sw128_mn8(v_addr + k * 4096),
                   make_smem_desc_sw128(p_addr + (j & 1) * 2048) + 2 * k, idesc_pv, k != 0);
         tc_commit(&bars->o_full[j & 1]);
-        tc_commit(&bars->kv_empty[j % kDaStages]);
+        // the K half of the stage was last read by S(j), which completed before p_ready(j) could be reached
+        tc_commit(&bars->kv_empty[st]);
       }
     }
   } else {
@@ -366,7 +375,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       // so the output phase below needs no further exchange.
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&bars->p_ready);
+      mbar_arrive(&bars->p_ready[j & 1]);
       if (t == 0) DA_TRACE(j, 4);
       // ---- fold P.V of the PREVIOUS tile into the output (thread = channel) while the tensor core
       // works on this tile: O <- O * alpha_{j-1} + PV_{j-1} * factor_{j-1}

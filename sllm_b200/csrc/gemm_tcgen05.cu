@@ -26,8 +26,12 @@
 // bit-identical results on every rank.  Receive buffers are double-buffered by call parity; epochs
 // are per-tile device counters so CUDA-graph replays need no host-side argument changes.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 =
-// epilogue (TMEM lane quarter = warp index % 4).
+// Warp roles: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue (TMEM lane
+// quarter = warp index % 4), warps 6.. = further MMA issuers.  One thread spends about 160 cycles per
+// tcgen05.mma whatever its shape, which is more than the tensor core needs for a 128x128 tile and far more
+// than for a decode tile; issuers in different warps overlap, so K blocks are dealt round-robin to
+// gemm_issuers(BN) issuing threads, each K block (scaled) or each issuer (unscaled) with its own TMEM
+// accumulator out of four.
 //
 // Replaces the reference's scalar-FMA matmul family and its library GEMM calls
 // (native/hip/src/matmul_kernel.hip.cpp:586-830, native/hip/src/matmul_runtime.inc:690).
@@ -44,7 +48,13 @@ namespace sllm {
 constexpr int kTileA = 128;        // rows of the A operand per CTA (tensor-core M)
 constexpr int kBoxBytes = 128;     // K bytes per pipeline stage row (one 128-byte swizzle row)
 constexpr int kMaxStages = 8;
-constexpr int kGemmThreads = 192;
+constexpr int kAccBufs = 4;        // TMEM accumulators of BN columns each
+// MMA-issuing threads per CTA.  BN = 64 keeps one: its epilogue needs the registers that two CTAs per SM of
+// 192 threads leave.  The stage count and kAccBufs are multiples of the issuer count, so a pipeline stage and
+// a TMEM accumulator always belong to the same issuer: a parity wait is only sound when the waiter has
+// itself seen the barrier's previous phase complete, and TMA loads in flight together may land out of order.
+__host__ __device__ constexpr int gemm_issuers(int bn) { return bn == 64 ? 1 : 2; }
+__host__ __device__ constexpr int gemm_threads(int bn) { return 192 + 32 * (gemm_issuers(bn) - 1); }
 
 constexpr int kMaxWorld = 8;
 constexpr int kMaxSlices = 8;   // cluster split-K slices per tile (flag / epoch slots per tile)
@@ -99,8 +109,8 @@ template <int BN>
 struct __align__(16) GemmBarriers {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t tmem_full[kAccBufs];
+  uint64_t tmem_empty[kAccBufs];
   uint32_t tmem_base;
   int abort_flag;
   int is_last;
@@ -149,7 +159,7 @@ __device__ __forceinline__ float ld_dsmem_f32(const float* local_ptr, uint32_t c
 }
 
 template <int BN, bool kScaled, bool kComm>
-__global__ void __launch_bounds__(kGemmThreads, (BN <= 64 ? 2 : 1))
+__global__ void __launch_bounds__(gemm_threads(BN), (BN <= 64 ? 2 : 1))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -158,7 +168,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   constexpr int kABytes = kTileA * kBoxBytes;
   constexpr int kBBytes = BN * kBoxBytes;
   constexpr int kStageBytes = kABytes + kBBytes;
-  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  constexpr uint32_t kTmemCols = (kAccBufs * BN < 32) ? 32 : kAccBufs * BN;
+  constexpr int kIssuers = gemm_issuers(BN);
   constexpr int kElemsPerBox = kScaled ? 128 : 64;
   GemmBarriers<BN>* bars = reinterpret_cast<GemmBarriers<BN>*>(smem + p.stages * kStageBytes);
   GemmScales<BN>* sc = reinterpret_cast<GemmScales<BN>*>(bars + 1);
@@ -180,7 +191,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAccBufs; ++b) {
       mbar_init(&bars->tmem_full[b], 1);
       mbar_init(&bars->tmem_empty[b], 128);
     }
@@ -262,19 +273,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp >= 6) {
+    // ------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(kScaled ? kFmtE4M3 : kFmtBf16, kTileA, BN);
-      for (int i = 0; i < nkb; ++i) {
+      const int iw = warp == 1 ? 0 : warp - 5;
+      bool issued_any = false;
+      for (int i = iw; i < nkb; i += kIssuers) {
         const int s = i % p.stages;
         const uint32_t ph = (i / p.stages) & 1;
         if (!mbar_wait(&bars->full[s], ph, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL)) break;
         if (i == 0) TRACE(2);
         if (i == nkb - 1) TRACE(3);
-        const int buf = kScaled ? (i & 1) : 0;
+        // scaled: one accumulator per K block (the epilogue promotes it); unscaled: one per issuer
+        const int buf = kScaled ? (i % kAccBufs) : iw;
         if (kScaled) {
-          if (!mbar_wait(&bars->tmem_empty[buf], ((i >> 1) & 1) ^ 1, abort_flag, p.status,
+          if (!mbar_wait(&bars->tmem_empty[buf], ((i / kAccBufs) & 1) ^ 1, abort_flag, p.status,
                          SLLM_DEV_TIMEOUT_TMEM_EMPTY))
             break;
         }
@@ -285,7 +299,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const uint32_t d = tmem_base + buf * BN;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per stage row
-          const uint32_t accum = kScaled ? (k > 0) : ((i > 0) || (k > 0));
+          const uint32_t accum = kScaled ? (k > 0) : ((i > iw) || (k > 0));
           if (kScaled)
             umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
           else
@@ -293,8 +307,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         tc_commit(&bars->empty[s]);  // stage reusable once these MMAs have read it
         if (kScaled) tc_commit(&bars->tmem_full[buf]);
+        issued_any = true;
       }
-      if (!kScaled) tc_commit(&bars->tmem_full[0]);
+      if (!kScaled && issued_any) tc_commit(&bars->tmem_full[iw]);
     }
   } else {
     // ------------------------------------------------------------ epilogue main loop (128 threads)
@@ -334,9 +349,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (cnt > kScaleChunk) cnt = kScaleChunk;
         for (int j = 0; j < cnt; ++j) {
           const int i = ci * kScaleChunk + j;
-          const int buf = i & 1;
+          const int buf = i % kAccBufs;
           const float sa = sc->sa[sbuf][j][row];
-          if (ok) ok = mbar_wait(&bars->tmem_full[buf], (i >> 1) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
+          if (ok) ok = mbar_wait(&bars->tmem_full[buf], (i / kAccBufs) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
           if (et == 0 && i == 0) TRACE(4);
           if (et == 0 && i == 1) TRACE(5);
           if (et == 0 && i == nkb - 1) TRACE(6);
@@ -359,19 +374,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     } else {
-      if (nkb > 0) {
-        ok = mbar_wait(&bars->tmem_full[0], 0, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
-        if (ok) {
-          tc_fence_after();
+      // one partial accumulator per issuer that had at least one K block
 #pragma unroll
-          for (int c = 0; c < BN / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld16(lane_addr + c * 16, r);
-            tmem_wait_ld();
+      for (int a = 0; a < kIssuers; ++a) {
+        if (a < nkb && ok) {
+          ok = mbar_wait(&bars->tmem_full[a], 0, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
+          if (ok) {
+            tc_fence_after();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[c * 16 + j] = __uint_as_float(r[j]);
+            for (int c = 0; c < BN / 16; ++c) {
+              uint32_t r[16];
+              tmem_ld16(lane_addr + a * BN + c * 16, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[c * 16 + j] += __uint_as_float(r[j]);
+            }
+            tc_fence_before();
           }
-          tc_fence_before();
         }
       }
     }
@@ -418,7 +437,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (cluster_split) cluster_sync_all();  // partials visible cluster-wide
   if (threadIdx.x == 64) TRACE(8);
 
-  if (warp >= 2 && active && ok) {
+  if (warp >= 2 && warp < 6 && active && ok) {
     const int nslice = cluster_split ? static_cast<int>(gridDim.z) : 1;
     const int cw = BN / nslice;            // columns of the tile this CTA finishes
     const int c0 = (cluster_split ? split : 0) * cw;
@@ -691,7 +710,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (cluster_ok[z] == 0 || cluster_smem[z] < smem) {
       cudaLaunchConfig_t probe = {};
       probe.gridDim = grid;
-      probe.blockDim = dim3(kGemmThreads);
+      probe.blockDim = dim3(gemm_threads(BN));
       probe.dynamicSmemBytes = smem;
       cudaLaunchAttribute pa[1];
       pa[0].id = cudaLaunchAttributeClusterDimension;
@@ -711,7 +730,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       if (!pp.ws || !pp.counters) return SLLM_ERR_WORKSPACE_TOO_SMALL;
     }
   }
-  if (launch_kernel(gemm_tcgen05_kernel<BN, kScaled, kComm>, grid, dim3(kGemmThreads), smem, stream,
+  if (launch_kernel(gemm_tcgen05_kernel<BN, kScaled, kComm>, grid, dim3(gemm_threads(BN)), smem, stream,
                     pp.cluster_split ? grid.z : 1u, ta, tb, pp) != cudaSuccess) {
     cudaGetLastError();
     return SLLM_ERR_CUDA;
@@ -769,6 +788,8 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages > max_stages_smem) stages = max_stages_smem;
+  stages -= stages % gemm_issuers(bn);   // each stage stays with one issuer
+  if (stages < 2) return SLLM_ERR_UNSUPPORTED_SHAPE;
 
   GemmParams p;
   memset(&p, 0, sizeof(p));

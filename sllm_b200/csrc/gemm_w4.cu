@@ -14,8 +14,11 @@
 //               significant bits - and store the chunk's two 128-byte-swizzled K-major A tiles (128 rows x 64
 //               elements each) into the group's half of a four-slot ring; one generic->async proxy fence per
 //               chunk, and while one group sits in its fence the other converts;
-//   warp 1      MMA issuer: D[128 weight rows, BN tokens] += A * B^T, kind::f16, four K=16 steps per slot;
-//   epilogue    (the first converter group again) TMEM -> registers, times the tensor scale and 2^16 (the other half of
+//   warps 1, 18..20  MMA issuers, one per (converter group, half chunk): D[128 weight rows, BN tokens] += A * B^T,
+//               kind::f16, four K=16 steps per slot, each issuer into its own TMEM accumulator.  One thread
+//               spends about 160 cycles per tcgen05.mma whatever its shape, but issuers in different warps
+//               overlap, so four of them quadruple the rate at which small-N MMAs enter the tensor core;
+//   epilogue    (the first converter group again) sum of the accumulators TMEM -> registers, times the tensor scale and 2^16 (the other half of
 //               the exponent offset), optional per-token routing weight, optional residual, bf16 store
 //               Y[token, row]; with split-K the partials go through an fp32 workspace and the last CTA of a tile
 //               sums them.
@@ -38,7 +41,8 @@
 
 namespace sllm {
 
-constexpr int kW4Threads = 576;        // TMA warp, MMA warp, two groups of eight converter warps
+constexpr int kW4Issuers = 4;          // MMA-issuing threads: (converter group, half chunk)
+constexpr int kW4Threads = 576 + 32 * (kW4Issuers - 1);   // TMA warp, MMA warp, 16 converter warps, 3 more MMA warps
 constexpr int kW4Rows = 128;          // weight rows per CTA (MMA M)
 constexpr int kW4Chunk = 128;         // K elements per TMA stage
 constexpr int kW4PackedBytes = kW4Rows * (kW4Chunk / 2);   // 8 KB
@@ -70,9 +74,9 @@ struct W4Params {
 struct __align__(16) W4Barriers {
   uint64_t full[kW4MaxStages];
   uint64_t empty[kW4MaxStages];
-  uint64_t conv_done[2];      // per converter group: the chunk's two A tiles are written
-  uint64_t a_empty[2];        // per converter group: the MMAs that read them have completed
-  uint64_t acc_full;
+  uint64_t conv_done[2][2];   // per (converter group, half chunk): the A tile is written
+  uint64_t a_empty[2][2];     // per (converter group, half chunk): the MMAs that read it have completed
+  uint64_t acc_full;          // every issuer has committed its last MMA
   uint32_t tmem_base;
   int abort_flag;
   int is_last;
@@ -131,10 +135,8 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
   uint8_t* a_ring = smem;                                   // kW4ASlots x 16 KB
   uint8_t* stages = smem + kW4ASlots * kW4ASlotBytes;
   W4Barriers* bars = reinterpret_cast<W4Barriers*>(stages + p.stages * kStageBytes);
-  // kAcc independent accumulators (one per K=16 step of a 64-element tile): consecutive MMAs then do not
-  // wait for one another's result; the epilogue adds them up.
-  constexpr int kAcc = BN <= 64 ? 4 : (BN == 128 ? 2 : 1);
-  constexpr uint32_t kTmemCols = kAcc * BN < 32 ? 32 : kAcc * BN;
+  // one accumulator per issuer; the epilogue adds them up
+  constexpr uint32_t kTmemCols = kW4Issuers * BN < 32 ? 32 : kW4Issuers * BN;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row_tile = blockIdx.x, g = blockIdx.y;
@@ -152,13 +154,14 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->empty[s], 257);                      // 256 converter threads + the MMA commit
+      mbar_init(&bars->empty[s], 258);                      // 256 converter threads + the two issuers' commits
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&bars->conv_done[a], 256);
-      mbar_init(&bars->a_empty[a], 1);
-    }
-    mbar_init(&bars->acc_full, 1);
+    for (int a = 0; a < 2; ++a)
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&bars->conv_done[a][b], 128);
+        mbar_init(&bars->a_empty[a][b], 1);
+      }
+    mbar_init(&bars->acc_full, kW4Issuers);
     bars->abort_flag = 0;
     bars->is_last = 0;
     mbar_fence_init();
@@ -219,41 +222,39 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp >= 18) {
+    // ------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(kFmtBf16, kW4Rows, BN < 16 ? 16 : BN);
+      const int iw = warp == 1 ? 0 : warp - 17;   // 0..3
+      const int grp = iw >> 1, sub = iw & 1;
+      const uint32_t d = tmem_base + iw * BN;
       bool ok = true;
-      for (int i = 0; ok && i < nk; ++i) {
+      for (int i = grp; ok && i < nk; i += 2) {
         const int s = i % p.stages;
         ok = mbar_wait(&bars->full[s], (i / p.stages) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL);
         if (!ok) break;
         const uint32_t b_addr = smem_u32(stages + s * kStageBytes + kW4PackedBytes + kScaleTile);
-        const int grp = i & 1;
-        ok = mbar_wait(&bars->conv_done[grp], (i >> 1) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_EMPTY);
+        ok = mbar_wait(&bars->conv_done[grp][sub], (i >> 1) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
-        W4_TRACE(i, 2);
+        if (sub == 0) W4_TRACE(i, 2);
+        const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + (grp * 2 + sub) * kW4ASlotBytes));
+        const uint64_t bdesc = make_smem_desc_sw128(b_addr + sub * BN * 128);
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-          const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + (grp * 2 + sub) * kW4ASlotBytes));
-          const uint64_t bdesc = make_smem_desc_sw128(b_addr + sub * BN * 128);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + (k % kAcc) * BN, adesc + 2 * k, bdesc + 2 * k, idesc,
-                     (i > 0) || (sub > 0) || (k >= kAcc));
-        }
-        tc_commit(&bars->a_empty[grp]);
-        W4_TRACE(i, 3);
-        if (ok) tc_commit(&bars->empty[s]);
+        for (int k = 0; k < 4; ++k) umma_f16(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i > grp) || (k > 0));
+        tc_commit(&bars->a_empty[grp][sub]);
+        if (sub == 0) W4_TRACE(i, 3);
+        tc_commit(&bars->empty[s]);
       }
+      // an issuer without chunks (nk == 1) has nothing in flight: the commit arrives at once
       if (ok) tc_commit(&bars->acc_full);
     }
   } else {
     // ------------------------------------------------------------ converters, then epilogue (128 threads)
     const int q = warp & 3;
     const int r = q * 32 + lane;                 // weight row of the tile, TMEM lane
-    const int grp = (warp - 2) >> 3;             // converter group: chunks i with (i & 1) == grp
+    const int grp = (warp - 2) >> 3;             // converter group: chunks i with (i & 1) == grp (warps 2..17 only)
     const int sub = ((warp - 2) >> 2) & 1;       // which 64-element half of the chunk this thread converts
     bool ok = true;
     for (int i = grp; ok && i < nk; i += 2) {
@@ -275,7 +276,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
 #pragma unroll
       for (int j = 0; j < 2; ++j) pk[j] = *reinterpret_cast<const uint4*>(st + r * 64 + sub * 32 + j * 16);
       // the group's two ring slots are free once the MMAs of its previous chunk have completed
-      ok = mbar_wait(&bars->a_empty[grp], ((i >> 1) & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY);
+      ok = mbar_wait(&bars->a_empty[grp][sub], ((i >> 1) & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY);
       if (!ok) break;
       if (r == 0 && sub == 0) W4_TRACE(i, 5);
       {
@@ -304,44 +305,61 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
       }
       if (r == 0 && sub == 0) W4_TRACE(i, 6);
       fence_proxy_async_smem();
-      mbar_arrive(&bars->conv_done[grp]);
+      mbar_arrive(&bars->conv_done[grp][sub]);
       mbar_arrive(&bars->empty[s]);
       if (r == 0 && sub == 0) W4_TRACE(i, 7);
     }
     if (grp == 0 && sub == 0) {
-    // ---- epilogue
+    // ---- epilogue, 16 token columns at a time
     pdl_wait();
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    float acc[BN];
-#pragma unroll
-    for (int c = 0; c < BN; ++c) acc[c] = 0.f;
     if (ok && nk > 0) {
       ok = mbar_wait(&bars->acc_full, 0, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int a = 0; a < kAcc; ++a) {
-#pragma unroll
-          for (int c = 0; c < BN / 16; ++c) {
-            uint32_t v[16];
-            tmem_ld16(lane_addr + a * BN + c * 16, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[c * 16 + j] += __uint_as_float(v[j]);
-          }
-        }
-        tc_fence_before();
-      }
+      if (ok) tc_fence_after();
     }
     const int out_row = row_tile * kW4Rows + r;            // feature index inside the group
     const bool row_ok = out_row < p.n_valid;
     const float ts = (p.tensor_scale ? p.tensor_scale[g] : 1.f) * 65536.f;
-    bool finish = true;
+    auto finalize = [&](int c, float a) {
+      const int tok = t_begin + c;
+      float v = a * ts;
+      if (p.tok_scale) v *= p.tok_scale[tok];
+      if (p.residual) v += __bfloat162float(p.residual[static_cast<size_t>(tok) * p.ldy + out_row]);
+      p.y[static_cast<size_t>(tok) * p.ldy + out_row] = __float2bfloat16_rn(v);
+    };
+#pragma unroll 1
+    for (int cb = 0; cb < BN / 16; ++cb) {
+      if (cb * 16 >= count) break;
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = 0.f;
+      if (ok && nk > 0) {
+#pragma unroll
+        for (int a = 0; a < kW4Issuers; ++a) {
+          if ((a >> 1) >= nk) continue;          // that issuer had no chunk: its accumulator was never written
+          uint32_t t[16];
+          tmem_ld16(lane_addr + a * BN + cb * 16, t);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(t[j]);
+        }
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int c = cb * 16 + j;
+          if (c < count) {
+            // split-K partials are [split][token][feature]; the last CTA of the tile sums them in split order
+            if (p.splits > 1)
+              p.ws[(static_cast<size_t>(split) * p.total_tokens + t_begin + c) * p.n_valid + out_row] = v[j];
+            else
+              finalize(c, v[j]);
+          }
+        }
+      }
+    }
+    tc_fence_before();
     if (p.splits > 1) {
-      // partials [split][token][feature]; the last CTA of the tile sums them in split order
-      if (row_ok)
-        for (int c = 0; c < count; ++c)
-          p.ws[(static_cast<size_t>(split) * p.total_tokens + t_begin + c) * p.n_valid + out_row] = ok ? acc[c] : 0.f;
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const int tile_id = (g * gridDim.x + row_tile) * (gridDim.z / p.splits) + tt;
@@ -351,28 +369,15 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
         if (prev == p.splits - 1) p.counters[tile_id] = 0;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      finish = bars->is_last != 0;
-      if (finish) {
+      if (bars->is_last != 0) {
         __threadfence();
         if (row_ok)
           for (int c = 0; c < count; ++c) {
             float sum = 0.f;
             for (int sp = 0; sp < p.splits; ++sp)
               sum += __ldcg(&p.ws[(static_cast<size_t>(sp) * p.total_tokens + t_begin + c) * p.n_valid + out_row]);
-            acc[c] = sum;
+            finalize(c, sum);
           }
-      }
-    }
-    if (finish && row_ok) {
-#pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        if (c < count) {
-          const int tok = t_begin + c;
-          float v = acc[c] * ts;
-          if (p.tok_scale) v *= p.tok_scale[tok];
-          if (p.residual) v += __bfloat162float(p.residual[static_cast<size_t>(tok) * p.ldy + out_row]);
-          p.y[static_cast<size_t>(tok) * p.ldy + out_row] = __float2bfloat16_rn(v);
-        }
       }
     }
     }   // first 128 converter threads = epilogue
@@ -393,6 +398,9 @@ static int launch_w4(const CUtensorMap& tx, W4Params& p, dim3 grid, cudaStream_t
   int stages = (227 * 1024 - fixed) / kStageBytes;
   if (stages > kW4MaxStages) stages = kW4MaxStages;
   if (stages > p.stages && p.stages >= 2) stages = p.stages;
+  // an even ring keeps every stage with the same converter group and issuers: a parity wait is only sound
+  // when the waiter has itself seen the barrier's previous phase complete (loads may land out of order)
+  stages &= ~1;
   if (stages < 2) return SLLM_ERR_UNSUPPORTED_SHAPE;
   p.stages = stages;
   const size_t smem = static_cast<size_t>(fixed) + static_cast<size_t>(stages) * kStageBytes;
