@@ -192,7 +192,6 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
           p.status_word[5] = kv_len; p.status_word[6] = begin;
         }
         if (ok) mbar_expect_tx(&bars->kv_full[st], 2 * kDaTileBytes);
-        DA_TRACE(j, 8);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
@@ -211,7 +210,6 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         cp_async_16(&bars->sc[st][1][key0], p.v_scale + slot);
       }
       if (p.k_scale) cp_async_mbar_arrive_noinc(&bars->kv_full[st]);
-      if (lane == 0) DA_TRACE(j, 9);
       issued = j + 1;
     }
     if (lane == 0) {
@@ -246,6 +244,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
           umma_f8(tmem_base + (j & 1) * 16, make_smem_desc_sw128(k_addr) + 2 * k, make_smem_desc_sw128(q_addr) + 2 * k,
                   idesc_s, k != 0);
         tc_commit(&bars->s_full[j & 1]);
+        DA_TRACE(j, 8);
       }
     }
   } else if (warp == 6) {
@@ -269,6 +268,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
         tc_commit(&bars->o_full[j & 1]);
         // the K half of the stage was last read by S(j), which completed before p_ready(j) could be reached
         tc_commit(&bars->kv_empty[st]);
+        DA_TRACE(j, 9);
       }
     }
   } else {

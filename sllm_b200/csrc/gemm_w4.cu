@@ -12,7 +12,7 @@
 //               eight E2M1 codes per 32-bit word with mask/shift into bf16 pairs whose exponent field holds
 //               the code, multiply by (block scale * 2^110) in bf16x2 - exact, the product has at most six
 //               significant bits - and store the chunk's two 128-byte-swizzled K-major A tiles (128 rows x 64
-//               elements each) into the group's half of a four-slot ring; one generic->async proxy fence per
+//               elements each) into the group's own tile buffers (two per half chunk at decode tile sizes); one generic->async proxy fence per
 //               chunk, and while one group sits in its fence the other converts;
 //   warps 1, 18..20  MMA issuers, one per (converter group, half chunk): D[128 weight rows, BN tokens] += A * B^T,
 //               kind::f16, four K=16 steps per slot, each issuer into its own TMEM accumulator.  One thread
@@ -46,7 +46,9 @@ constexpr int kW4Threads = 576 + 32 * (kW4Issuers - 1);   // TMA warp, MMA warp,
 constexpr int kW4Rows = 128;          // weight rows per CTA (MMA M)
 constexpr int kW4Chunk = 128;         // K elements per TMA stage
 constexpr int kW4PackedBytes = kW4Rows * (kW4Chunk / 2);   // 8 KB
-constexpr int kW4ASlots = 4;          // ring of converted bf16 A tiles (128 rows x 64 elements = 16 KB each)
+// converted bf16 A tiles (128 rows x 64 elements = 16 KB each): one per (converter group, half chunk), doubled for
+// the decode tile sizes so that a group converts its next chunk while the MMAs of its previous one still read
+__host__ __device__ constexpr int w4_abufs(int bn) { return bn <= 32 ? 2 : 1; }
 constexpr int kW4ASlotBytes = kW4Rows * 128;
 constexpr int kW4MaxStages = 8;
 
@@ -74,8 +76,8 @@ struct W4Params {
 struct __align__(16) W4Barriers {
   uint64_t full[kW4MaxStages];
   uint64_t empty[kW4MaxStages];
-  uint64_t conv_done[2][2];   // per (converter group, half chunk): the A tile is written
-  uint64_t a_empty[2][2];     // per (converter group, half chunk): the MMAs that read it have completed
+  uint64_t conv_done[2][2][2];   // per (converter group, half chunk, buffer): the A tile is written
+  uint64_t a_empty[2][2][2];     // per (converter group, half chunk, buffer): the MMAs that read it have completed
   uint64_t acc_full;          // every issuer has committed its last MMA
   uint32_t tmem_base;
   int abort_flag;
@@ -132,8 +134,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
   constexpr int kScaleTile = kW4Rows * 8;                  // room for the larger (NVFP4) scale tile
   constexpr int kStageBytes = kW4PackedBytes + kScaleTile + kBBytes;
   static_assert(kStageBytes % 1024 == 0, "stage alignment");
-  uint8_t* a_ring = smem;                                   // kW4ASlots x 16 KB
-  uint8_t* stages = smem + kW4ASlots * kW4ASlotBytes;
+  constexpr int kABufs = w4_abufs(BN);
+  uint8_t* a_ring = smem;                                   // [group][half][buffer] x 16 KB
+  uint8_t* stages = smem + 4 * kABufs * kW4ASlotBytes;
   W4Barriers* bars = reinterpret_cast<W4Barriers*>(stages + p.stages * kStageBytes);
   // one accumulator per issuer; the epilogue adds them up
   constexpr uint32_t kTmemCols = kW4Issuers * BN < 32 ? 32 : kW4Issuers * BN;
@@ -157,10 +160,11 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
       mbar_init(&bars->empty[s], 258);                      // 256 converter threads + the two issuers' commits
     }
     for (int a = 0; a < 2; ++a)
-      for (int b = 0; b < 2; ++b) {
-        mbar_init(&bars->conv_done[a][b], 128);
-        mbar_init(&bars->a_empty[a][b], 1);
-      }
+      for (int b = 0; b < 2; ++b)
+        for (int c = 0; c < 2; ++c) {
+          mbar_init(&bars->conv_done[a][b][c], 128);
+          mbar_init(&bars->a_empty[a][b][c], 1);
+        }
     mbar_init(&bars->acc_full, kW4Issuers);
     bars->abort_flag = 0;
     bars->is_last = 0;
@@ -235,15 +239,17 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
         ok = mbar_wait(&bars->full[s], (i / p.stages) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL);
         if (!ok) break;
         const uint32_t b_addr = smem_u32(stages + s * kStageBytes + kW4PackedBytes + kScaleTile);
-        ok = mbar_wait(&bars->conv_done[grp][sub], (i >> 1) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_EMPTY);
+        const int t = i >> 1;                       // the group's chunk counter
+        const int ab = t % kABufs;
+        ok = mbar_wait(&bars->conv_done[grp][sub][ab], (t / kABufs) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
         if (sub == 0) W4_TRACE(i, 2);
-        const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + (grp * 2 + sub) * kW4ASlotBytes));
+        const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + ((grp * 2 + sub) * kABufs + ab) * kW4ASlotBytes));
         const uint64_t bdesc = make_smem_desc_sw128(b_addr + sub * BN * 128);
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma_f16(d, adesc + 2 * k, bdesc + 2 * k, idesc, (i > grp) || (k > 0));
-        tc_commit(&bars->a_empty[grp][sub]);
+        tc_commit(&bars->a_empty[grp][sub][ab]);
         if (sub == 0) W4_TRACE(i, 3);
         tc_commit(&bars->empty[s]);
       }
@@ -275,13 +281,14 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
       uint4 pk[2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) pk[j] = *reinterpret_cast<const uint4*>(st + r * 64 + sub * 32 + j * 16);
-      // the group's two ring slots are free once the MMAs of its previous chunk have completed
-      ok = mbar_wait(&bars->a_empty[grp][sub], ((i >> 1) & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY);
+      // the buffer is free once the MMAs of the chunk that used it last have completed
+      const int t = i >> 1, ab = t % kABufs;
+      ok = mbar_wait(&bars->a_empty[grp][sub][ab], ((t / kABufs) & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY);
       if (!ok) break;
       if (r == 0 && sub == 0) W4_TRACE(i, 5);
       {
         const uint32_t words[8] = {pk[0].x, pk[0].y, pk[0].z, pk[0].w, pk[1].x, pk[1].y, pk[1].z, pk[1].w};
-        uint8_t* dst_row = a_ring + (grp * 2 + sub) * kW4ASlotBytes + r * 128;
+        uint8_t* dst_row = a_ring + ((grp * 2 + sub) * kABufs + ab) * kW4ASlotBytes + r * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {            // word c = elements 8c .. 8c+7 of the 64-element sub-block
           uint32_t code;
@@ -305,7 +312,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
       }
       if (r == 0 && sub == 0) W4_TRACE(i, 6);
       fence_proxy_async_smem();
-      mbar_arrive(&bars->conv_done[grp][sub]);
+      mbar_arrive(&bars->conv_done[grp][sub][ab]);
       mbar_arrive(&bars->empty[s]);
       if (r == 0 && sub == 0) W4_TRACE(i, 7);
     }
@@ -394,7 +401,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
 template <int BN, int kFmt>
 static int launch_w4(const CUtensorMap& tx, W4Params& p, dim3 grid, cudaStream_t st) {
   constexpr int kStageBytes = kW4PackedBytes + kW4Rows * 8 + 2 * BN * 128;
-  const int fixed = kW4ASlots * kW4ASlotBytes + static_cast<int>(sizeof(W4Barriers)) + 1024;
+  const int fixed = 4 * w4_abufs(BN) * kW4ASlotBytes + static_cast<int>(sizeof(W4Barriers)) + 1024;
   int stages = (227 * 1024 - fixed) / kStageBytes;
   if (stages > kW4MaxStages) stages = kW4MaxStages;
   if (stages > p.stages && p.stages >= 2) stages = p.stages;
