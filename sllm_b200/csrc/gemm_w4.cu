@@ -4,7 +4,7 @@
 // each expert's rows are contiguous).
 //
 // The weights stay 4-bit in HBM and in the TMA ring; they become bf16 only inside the SM:
-//   warp 0      producer: per 128-element K chunk ONE bulk copy of the weight tile (128 rows x 64 B of codes
+//   warps 0, 21 producers (even / odd K chunks): per 128-element K chunk ONE bulk copy of the weight tile (128 rows x 64 B of codes
 //               followed by the 128 x 4 or 8 B of their scales, contiguous in HBM) and two TMA boxes of
 //               activations (BN tokens x 64 elements, 128-byte swizzle);
 //   warps 2..17 converters, two groups of 256 threads taking alternate K chunks (thread = weight row x half
@@ -42,7 +42,10 @@
 namespace sllm {
 
 constexpr int kW4Issuers = 4;          // MMA-issuing threads: (converter group, half chunk)
-constexpr int kW4Threads = 576 + 32 * (kW4Issuers - 1);   // TMA warp, MMA warp, 16 converter warps, 3 more MMA warps
+// warp 0 TMA producer of the even chunks, warp 1 MMA issuer, 16 converter warps, 3 more MMA issuers, warp 21
+// TMA producer of the odd chunks
+constexpr int kW4Threads = 576 + 32 * (kW4Issuers - 1) + 32;
+constexpr int kW4Producer1 = 21;
 constexpr int kW4Rows = 128;          // weight rows per CTA (MMA M)
 constexpr int kW4Chunk = 128;         // K elements per TMA stage
 constexpr int kW4PackedBytes = kW4Rows * (kW4Chunk / 2);   // 8 KB
@@ -182,10 +185,15 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
   const size_t tile0 = (static_cast<size_t>(g) * (p.n_rows / kW4Rows) + row_tile) * p.k_chunks;
   const uint32_t tile_bytes = kW4PackedBytes + kW4Rows * p.scale_bytes;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == kW4Producer1) {
+    // ------------------------------------------------------------ TMA producers
+    // The converters keep the instruction issue slots busy, and one producer thread competing with them needed
+    // about as long per chunk as the chunk takes to convert, so it never got ahead of the consumers; each
+    // converter group therefore has its own producer (the ring has an even number of stages, so a stage always
+    // carries chunks of one group).
     if (lane == 0) {
-      int issued = 0;
+      const int pg = warp == 0 ? 0 : 1;
+      int issued_end = 0;
       // the weights are constant: the first ring of weight tiles is requested before waiting for the
       // previous kernel, the activations after it
       const int pre = nk < p.stages ? nk : p.stages;
@@ -198,16 +206,16 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
         tma_load_2d(st + BN * 128, &tm_x, &bars->full[s], (c0 + i) * kW4Chunk + 64, t_begin);
       };
       const uint32_t tx = tile_bytes + kBBytes;
-      for (int i = 0; i < pre; ++i) {
+      for (int i = pg; i < pre; i += 2) {
         mbar_expect_tx(&bars->full[i], tx);
         load_w(i, i);
       }
       pdl_wait();
-      for (int i = 0; i < pre; ++i) {
+      for (int i = pg; i < pre; i += 2) {
         load_x(i, i);
-        issued = i + 1;
+        issued_end = i + 1;
       }
-      for (int i = pre; i < nk; ++i) {
+      for (int i = pre + ((pre & 1) != pg ? 1 : 0); i < nk; i += 2) {
         const int s = i % p.stages;
         if (!mbar_wait(&bars->empty[s], ((i / p.stages) & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY)) break;
         W4_TRACE(i, 0);
@@ -215,18 +223,19 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
         load_w(i, s);
         load_x(i, s);
         W4_TRACE(i, 1);
-        issued = i + 1;
+        issued_end = i + 1;
       }
-      pdl_trigger();
-      for (int s = 0; s < p.stages; ++s) {
-        const int fills = (issued > s) ? (issued - s + p.stages - 1) / p.stages : 0;
+      if (pg == 0) pdl_trigger();
+      // every copy this thread started must have landed before the CTA may exit
+      for (int s = pg; s < p.stages; s += 2) {
+        const int fills = (issued_end > s) ? (issued_end - s + p.stages - 1) / p.stages : 0;
         if (fills > 0) {
           int dummy = 0;
           mbar_wait(&bars->full[s], (fills - 1) & 1, &dummy, p.status, SLLM_DEV_TIMEOUT_DRAIN, 200000000LL);
         }
       }
     }
-  } else if (warp == 1 || warp >= 18) {
+  } else if (warp == 1 || warp >= 18) {   // (warp 21 took the producer branch above)
     // ------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(kFmtBf16, kW4Rows, BN < 16 ? 16 : BN);
@@ -263,9 +272,16 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
     const int grp = (warp - 2) >> 3;             // converter group: chunks i with (i & 1) == grp (warps 2..17 only)
     const int sub = ((warp - 2) >> 2) & 1;       // which 64-element half of the chunk this thread converts
     bool ok = true;
-    for (int i = grp; ok && i < nk; i += 2) {
-      const int s = i % p.stages;
-      ok = mbar_wait(&bars->full[s], (i / p.stages) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL);
+    // running stage index and phase (a division per chunk in 512 threads is worth avoiding: the converters are
+    // bound by instruction issue); grp < stages and the ring is even, so s keeps the group's parity
+    int s = grp;
+    uint32_t full_ph = 0;
+    for (int i = grp; ok && i < nk; i += 2, s += 2) {
+      if (s >= p.stages) {
+        s -= p.stages;
+        full_ph ^= 1;
+      }
+      ok = mbar_wait(&bars->full[s], full_ph, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL);
       if (!ok) break;
       if (r == 0 && sub == 0) W4_TRACE(i, 4);
       const uint8_t* st = stages + s * kStageBytes;
