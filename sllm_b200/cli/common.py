@@ -88,6 +88,7 @@ def open_model(args, max_batch: int = 8, tp=None):
     blocks = (cfg.max_context + cfg.page_size - 1) // cfg.page_size
     cache = PagedKVCache(cfg, max_batch * blocks + 8, device, kv_heads=model.local_kv_heads)
     eng = Engine(cfg, model, cache, device, max_batch=max_batch, use_cuda_graphs=not use_cpu, tp=tp)
+    eng.mtp_weights = loader.load_mtp_gguf(g, cfg, device) if tp_size == 1 else None
     tok = loader.tokenizer_from_gguf(g)
     return eng, tok, g, lock
 

@@ -91,6 +91,8 @@ def main(argv=None) -> int:
         p.add_argument("--weight-format", choices=("fp32", "bf16", "fp8"), default="bf16")
         p.add_argument("--seed", type=int, default=0)
         p.add_argument("--layers", type=int, default=None)
+        p.add_argument("--with-mtp", action="store_true",
+                       help="random-llama: add a seeded multi-token-prediction component (mtp.* tensors)")
         p.add_argument("--dry-run", action="store_true")
         a = p.parse_args(sys.argv[1:] if argv is None else argv)
         import torch
@@ -145,8 +147,14 @@ def main(argv=None) -> int:
         else:
             w = _load_hf(cache, cfg)
             cache.close()
+        mtp = None
+        if a.with_mtp:
+            if a.kind != "random-llama":
+                raise CliError("--with-mtp applies to kind random-llama")
+            from ..models.mtp import init_random_mtp_weights
+            mtp = init_random_mtp_weights(cfg, dev, seed=a.seed + 1)
         dl = loader.export_llama_gguf(cfg, w, a.output, tokenizer_json=tokenizer_json, chat_template=chat_template,
-                                      source_fingerprints=tuple(fps),
+                                      source_fingerprints=tuple(fps), mtp=mtp,
                                       converter_args={"kind": a.kind, "commit": a.converter_commit, "seed": a.seed,
                                                       "weight_format": a.weight_format})
         tmp = a.derived_lock + ".tmp"

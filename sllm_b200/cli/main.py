@@ -209,6 +209,16 @@ def _generate(eng, tok, ids, a, on_delta=None, timeline=None):
     from ..engine.scheduler import EngineLoop
     from ..frontend.generation import GenerationConfig, GenerationService
     loop = EngineLoop(eng, "cli", prefill_chunk_tokens=a.prefill_chunk_tokens)
+    if getattr(a, "mtp_draft_width", 0) > 0:
+        if getattr(eng, "mtp_weights", None) is None:
+            loop.shutdown(5.0)
+            raise CliError("--mtp-draft-width needs a model file with an MTP component (mtp.* tensors)")
+        from ..engine.speculative import SpeculativeDecoder
+        from ..models.mtp import MtpDraftProvider, MtpHead
+        head = getattr(eng, "_mtp_head", None)
+        if head is None:
+            head = eng._mtp_head = MtpHead(eng, eng.mtp_weights)
+        loop.speculative = SpeculativeDecoder(eng, MtpDraftProvider(head, a.mtp_draft_width), a.mtp_draft_width)
     try:
         svc = GenerationService(loop, tok, eng.cfg.vocab, "cli")
         cfg = GenerationConfig(max_new_tokens=a.max_new_tokens, chain=sampling_from_args(a), seed=a.seed,

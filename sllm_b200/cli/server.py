@@ -66,7 +66,7 @@ def build_parser() -> StrictParser:
     p.add_argument("--checkpoint-load")
     p.add_argument("--checkpoint-save")
     # speculative decoding
-    p.add_argument("--draft", choices=("none", "ngram", "external"), default="none")
+    p.add_argument("--draft", choices=("none", "ngram", "external", "mtp"), default="none")
     p.add_argument("--draft-ngram-order", type=int, default=3)
     p.add_argument("--draft-width", type=int, default=4)
     p.add_argument("--draft-model-identity")

@@ -83,6 +83,10 @@ class Engine:
         self.kernel_launches = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # with keep_hidden set, prefill / extend log the final residual-stream row of every computed position per
+        # sequence (consumed by a multi-token-prediction head through take_hidden)
+        self.keep_hidden = False
+        self._hidden_log: dict = {}
 
     # ------------------------------------------------------------------ sequences
     def new_sequence(self, prompt: list, user=None) -> Sequence:
@@ -127,6 +131,7 @@ class Engine:
             if self.has_state:
                 self.cache.free_slot(s.seq_id)
             self.cache.pool.free_seq(s.seq_id)
+            self._hidden_log.pop(s.seq_id, None)
             s.seq_id = -1
 
     def rollback(self, s: Sequence, length: int) -> None:
@@ -136,6 +141,41 @@ class Engine:
         self.cache.pool.truncate(s.seq_id, length)
         s.num_computed = min(s.num_computed, length)
         del s.tokens[length:]
+        log = self._hidden_log.get(s.seq_id)
+        if log:
+            kept = []
+            for start, rows in log:
+                if start < length:
+                    kept.append((start, rows[:length - start]))
+            self._hidden_log[s.seq_id] = kept
+
+    def _log_hidden(self, seqs: list, starts: list, counts: list, hidden: torch.Tensor) -> None:
+        r0 = 0
+        for s, st, n in zip(seqs, starts, counts):
+            self._hidden_log.setdefault(s.seq_id, []).append((st, hidden[r0:r0 + n].clone()))
+            r0 += n
+
+    def hidden_start(self, s: Sequence) -> Optional[int]:
+        """First position of ``s`` with a logged hidden row, or None."""
+        log = self._hidden_log.get(s.seq_id)
+        return log[0][0] if log else None
+
+    def take_hidden(self, s: Sequence, start: int, end: int) -> torch.Tensor:
+        """Logged hidden rows of positions [start, end) of ``s``; rows before ``end`` are dropped from the log."""
+        log = self._hidden_log.get(s.seq_id, [])
+        parts, rest, pos = [], [], start
+        for st, rows in log:
+            en = st + rows.shape[0]
+            if en > pos and st <= pos < end:
+                take = rows[pos - st:min(en, end) - st]
+                parts.append(take)
+                pos += take.shape[0]
+            if en > end:
+                rest.append((max(st, end), rows[max(st, end) - st:]))
+        if pos != end:
+            raise ValueError(f"hidden rows {pos}..{end} of sequence {s.seq_id} were not logged")
+        self._hidden_log[s.seq_id] = rest
+        return torch.cat(parts, 0) if len(parts) != 1 else parts[0]
 
     # ------------------------------------------------------------------ prefill
     def prefill(self, seqs: list, chunk_tokens: int = 0, sample: bool = True):
@@ -167,6 +207,8 @@ class Engine:
                 b.slots = torch.tensor([self.cache.slot_of[seqs[i].seq_id] for i in rows], dtype=torch.int32, device=self.device)
             self.h2d_bytes += b.num_tokens * 12
             res = self.model.greedy(b, self.cache) if sample else self.model.forward(b, self.cache)
+            if self.keep_hidden:
+                self._log_hidden([seqs[i] for i in rows], part_starts, [len(p) for p in parts], self.model.last_hidden)
             if out is None:
                 out = torch.zeros((len(seqs),) + tuple(res.shape[1:]), dtype=res.dtype, device=res.device)
             out[torch.tensor(rows, device=res.device)] = res
@@ -182,10 +224,11 @@ class Engine:
             s.num_computed = len(s.tokens)
         return toks if sample else out
 
-    def extend(self, seqs: list, sample: bool = True):
+    def extend(self, seqs: list, sample: bool = True, embeds: Optional[torch.Tensor] = None):
         """Runs every not-yet-computed token of each sequence as its own row (a speculative verify block, or
         any multi-token append) and returns, per sequence, the greedy token after each of those rows (or the
-        logits [rows, vocab] with sample=False).  The block-table rows of one sequence are shared by its rows."""
+        logits [rows, vocab] with sample=False).  The block-table rows of one sequence are shared by its rows.
+        ``embeds`` ([rows, d], in sequence order) replaces the embedding gather."""
         pool = self.cache.pool
         for s in seqs:
             pool.reserve(s.seq_id, len(s.tokens))
@@ -196,14 +239,17 @@ class Engine:
         if any(not p for p in parts):
             raise ValueError("extend needs at least one uncomputed token per sequence")
         r = len(parts[0])
-        if (sample and self.use_graphs and not self.has_state and r <= self.MAX_EXTEND_ROWS and len(seqs) <= self.max_batch
-                and all(len(p) == r for p in parts)):
+        if (sample and self.use_graphs and not self.has_state and embeds is None and r <= self.MAX_EXTEND_ROWS
+                and len(seqs) <= self.max_batch and all(len(p) == r for p in parts)):
             return self._extend_graphed(seqs, parts, r, table)
         b = make_prefill_batch(parts, d_table, self.device, [s.num_computed for s in seqs], last_only=False)
+        b.embeds = embeds
         if self.has_state:
             b.slots = torch.tensor([self.cache.slot_of[s.seq_id] for s in seqs], dtype=torch.int32, device=self.device)
         self.h2d_bytes += table.numel() * 4 + b.num_tokens * 12
         res = self.model.greedy(b, self.cache) if sample else self.model.forward(b, self.cache)
+        if self.keep_hidden:
+            self._log_hidden(seqs, [s.num_computed for s in seqs], [len(p) for p in parts], self.model.last_hidden)
         self._table_key = None
         self._check_status(every=1)
         out, r0 = [], 0
@@ -268,7 +314,10 @@ class Engine:
                 body()
             e["launches"][key] = _lib.LAUNCH_COUNT[0] - before
             e["graphs"][key] = g
+            e.setdefault("hidden", {})[key] = self.model.last_hidden      # the graph's own output buffer
         g.replay()
+        if self.keep_hidden:
+            self._log_hidden(seqs, [s.num_computed for s in seqs], [r] * n, e["hidden"][key])
         self.kernel_launches += e["launches"][key]
         e["h_out"][:t].copy_(e["d_out"][:t], non_blocking=True)
         torch.cuda.current_stream().synchronize()

@@ -246,7 +246,9 @@ class SpeculativeDecoder:
         eng = self.engine
         widths = [min(self.width, (b - 1) if b is not None else self.width,
                       eng.cfg.max_context - len(s.tokens) - 1) for s, b in zip(seqs, budgets or [None] * len(seqs))]
-        if hasattr(self.provider, "propose_batch"):
+        if hasattr(self.provider, "propose_seqs"):       # providers that read engine state (the MTP head)
+            drafts = self.provider.propose_seqs(seqs, max(1, max(widths)))
+        elif hasattr(self.provider, "propose_batch"):
             drafts = self.provider.propose_batch([id(s) for s in seqs], [s.tokens for s in seqs], max(1, max(widths)))
         else:
             drafts = [self.provider.propose(s.tokens, max(1, w)) for s, w in zip(seqs, widths)]
@@ -303,6 +305,11 @@ def configure_draft(backend, args) -> None:
                                          getattr(backend.tokenizer, "identity", "byte"),
                                          args.draft_tokenizer_identity or getattr(d_tok, "identity", "byte"),
                                          d_lock["semantic_model_id"])
+    elif args.draft == "mtp":
+        from ..models.mtp import MtpDraftProvider, MtpHead
+        if getattr(eng, "mtp_weights", None) is None:
+            raise SpeculativeError("--draft mtp needs a model file with an MTP component (mtp.* tensors)")
+        provider = MtpDraftProvider(MtpHead(eng, eng.mtp_weights), args.draft_width)
     else:
         return
     backend.loop.speculative = SpeculativeDecoder(eng, provider, args.draft_width)

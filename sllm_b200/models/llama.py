@@ -231,6 +231,12 @@ class LlamaModel:
         h = ad.lora_delta(li, "down", act, ops.linear(act, lw.down, h))
         return ad.control(li, h)
 
+    def _keep(self, h: torch.Tensor) -> torch.Tensor:
+        """Remembers the residual stream of the last forward (all rows, before the final norm) for consumers such
+        as a multi-token-prediction head; a reference, not a copy."""
+        self.last_hidden = h
+        return h
+
     def logits(self, h: torch.Tensor, b: ForwardBatch) -> torch.Tensor:
         """Local (vocab-shard) logits of the requested rows."""
         cfg, w = self.cfg, self.w
@@ -244,8 +250,8 @@ class LlamaModel:
 
     def forward(self, b: ForwardBatch, cache) -> torch.Tensor:
         """Full-vocabulary logits [rows, vocab]."""
-        return self.tp.gather_logits(self.logits(self.hidden(b, cache), b))
+        return self.tp.gather_logits(self.logits(self._keep(self.hidden(b, cache)), b))
 
     def greedy(self, b: ForwardBatch, cache) -> torch.Tensor:
         """Greedy next tokens (int32 [rows]) without materialising gathered logits."""
-        return self.tp.argmax(self.logits(self.hidden(b, cache), b), self.w.vocab_offset)
+        return self.tp.argmax(self.logits(self._keep(self.hidden(b, cache)), b), self.w.vocab_offset)

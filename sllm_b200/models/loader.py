@@ -39,8 +39,9 @@ def _u8_bytes(t: torch.Tensor) -> bytes:
 
 def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_json: Optional[str] = None,
                       chat_template: Optional[str] = None, source_fingerprints: tuple = (),
-                      converter_args: Optional[dict] = None) -> dict:
-    """Writes unsharded (tensor-parallel size 1) weights; returns the derived lock document."""
+                      converter_args: Optional[dict] = None, mtp=None) -> dict:
+    """Writes unsharded (tensor-parallel size 1) weights; returns the derived lock document.  ``mtp``
+    (models.mtp.MtpWeights, dense) adds the multi-token-prediction component as `mtp.*` tensors."""
     tensors, bindings = [], []
     dense_t = G.T_F32 if cfg.weight_format == "fp32" else G.T_BF16
     dense_b = _f32_bytes if cfg.weight_format == "fp32" else _bf16_bytes
@@ -76,6 +77,15 @@ def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_js
     add_dense("output_norm.weight", w.final_norm)
     if not cfg.tie_embeddings:
         add_linear("output.weight", w.lm_head, 0, cfg.vocab)
+    if mtp is not None:
+        l = mtp.layer
+        add_dense("mtp.fc.weight", mtp.fc.w)
+        add_dense("mtp.pre_fc_norm_embedding.weight", mtp.norm_embedding)
+        add_dense("mtp.pre_fc_norm_hidden.weight", mtp.norm_hidden)
+        add_dense("mtp.norm.weight", mtp.norm)
+        for name, t in (("attn_norm", l.attn_norm), ("attn_qkv", l.qkv.w), ("attn_output", l.o.w),
+                        ("ffn_norm", l.mlp_norm), ("ffn_gate_up", l.gate_up.w), ("ffn_down", l.down.w)):
+            add_dense(f"mtp.blk.0.{name}.weight", t)
     md = {"general.architecture": "llama", "general.name": cfg.name,
           "llama.block_count": cfg.n_layers, "llama.embedding_length": cfg.d_model,
           "llama.attention.head_count": cfg.n_heads, "llama.attention.head_count_kv": cfg.n_kv_heads,
@@ -176,6 +186,36 @@ def load_llama_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, k
     else:
         head = lin([rows("output.weight", vo, v_hi)])
     return cfg, LlamaWeights(embed, layers, final_norm, head, vo)
+
+
+def load_mtp_gguf(g: G.GgufFile, cfg: ModelConfig, device):
+    """The multi-token-prediction component of a verified open GGUF file (models.mtp.MtpWeights), or None when
+    the file carries none.  The component is dense (fp32 with an fp32 model, bf16 otherwise)."""
+    if "mtp.fc.weight" not in g.tensors:
+        return None
+    from .mtp import MtpWeights
+    dt = torch.float32 if cfg.weight_format == "fp32" else torch.bfloat16
+    want = G.T_F32 if dt == torch.float32 else G.T_BF16
+
+    def dense(name):
+        t = g.tensors.get(name)
+        if t is None:
+            raise G.GgufError(f"incomplete MTP component: {name} is missing")
+        if t.ttype != want:
+            raise G.GgufError(f"{name}: unexpected tensor type {t.ttype}")
+        return g.upload(name, torch.device(device), dt).view(t.shape)
+
+    d = cfg.d_model
+    fc = dense("mtp.fc.weight")
+    if tuple(fc.shape) != (d, 2 * d):
+        raise G.GgufError("mtp.fc.weight must be [d_model, 2 * d_model]")
+    p = "mtp.blk.0."
+    layer = LayerWeights(attn_norm=dense(p + "attn_norm.weight"), qkv=LinearWeight("dense", dense(p + "attn_qkv.weight")),
+                         o=LinearWeight("dense", dense(p + "attn_output.weight")), mlp_norm=dense(p + "ffn_norm.weight"),
+                         gate_up=LinearWeight("dense", dense(p + "ffn_gate_up.weight")),
+                         down=LinearWeight("dense", dense(p + "ffn_down.weight")))
+    return MtpWeights(LinearWeight("dense", fc), dense("mtp.pre_fc_norm_embedding.weight"),
+                      dense("mtp.pre_fc_norm_hidden.weight"), layer, dense("mtp.norm.weight"))
 
 
 def tokenizer_from_gguf(g: G.GgufFile):

@@ -140,6 +140,12 @@ class MoeModel:
             h = self.ep.combine(yp, perm_dst, h)
         return h
 
+    def _keep(self, h: torch.Tensor) -> torch.Tensor:
+        """Remembers the residual stream of the last forward (all rows, before the final norm) for consumers such
+        as a multi-token-prediction head; a reference, not a copy."""
+        self.last_hidden = h
+        return h
+
     def logits(self, h: torch.Tensor, b: ForwardBatch) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         if b.logit_rows is not None:
@@ -148,10 +154,10 @@ class MoeModel:
         return ops.linear(x, w.lm_head)
 
     def forward(self, b: ForwardBatch, cache) -> torch.Tensor:
-        return self.tp.gather_logits(self.logits(self.hidden(b, cache), b))
+        return self.tp.gather_logits(self.logits(self._keep(self.hidden(b, cache)), b))
 
     def greedy(self, b: ForwardBatch, cache) -> torch.Tensor:
-        return self.tp.argmax(self.logits(self.hidden(b, cache), b), self.w.vocab_offset)
+        return self.tp.argmax(self.logits(self._keep(self.hidden(b, cache)), b), self.w.vocab_offset)
 
 
 def tiny_moe() -> ModelConfig:

@@ -142,6 +142,12 @@ class Qwen35Model:
             h = self._mlp(h, lw)
         return h
 
+    def _keep(self, h: torch.Tensor) -> torch.Tensor:
+        """Remembers the residual stream of the last forward (all rows, before the final norm) for consumers such
+        as a multi-token-prediction head; a reference, not a copy."""
+        self.last_hidden = h
+        return h
+
     def logits(self, h, b):
         cfg, w = self.cfg, self.w
         if b.logit_rows is not None:
@@ -150,10 +156,10 @@ class Qwen35Model:
         return ops.linear(x, w.lm_head)
 
     def forward(self, b, cache):
-        return self.logits(self.hidden(b, cache), b)
+        return self.logits(self._keep(self.hidden(b, cache)), b)
 
     def greedy(self, b, cache):
-        return ops.argmax(self.logits(self.hidden(b, cache), b))
+        return ops.argmax(self.logits(self._keep(self.hidden(b, cache)), b))
 
 
 def tiny_qwen35() -> ModelConfig:
