@@ -30,6 +30,8 @@ def main():
     dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     cfg = MOE.tiny_moe()
     cfg.n_experts, cfg.top_k = 8, 2
+    if world > cfg.n_kv_heads:            # the attention of the end-to-end part is sharded by head over all ranks
+        cfg.n_heads, cfg.n_kv_heads = 2 * world, world
     d = cfg.d_model
     fused = FusedEP(world, rank, dev, max_tokens=64, d_model=d)
     nccl = NcclEP(world, rank, dev)
