@@ -35,6 +35,23 @@ def _hf_config(raw: dict, weight_format: str):
                        max_context=min(int(raw.get("max_position_embeddings", 8192)), 131072))
 
 
+BENCH_WORDS = ("alpha", "beta", "gamma", "delta", "omega", "sigma", "kappa", "theta", "lambda", "zeta")
+
+
+def _synthetic_tokenizer(vocab_size: int) -> str:
+    """`tokenizers` JSON of a whitespace word-level vocabulary: id i is the word `w<i>`, except that the first ids
+    after 0 are the words the serving load generator writes its prompts with; unknown text maps to id 0."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    vocab = {f"w{i}": i for i in range(vocab_size)}
+    for j, word in enumerate(BENCH_WORDS, start=1):
+        if j < vocab_size:
+            del vocab[f"w{j}"]
+            vocab[word] = j
+    tk = Tokenizer(models.WordLevel(vocab, unk_token="w0"))
+    tk.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    return tk.to_str()
+
+
 def _load_hf(cache, cfg):
     """Reads the safetensors shards through the verified descriptors and assembles LlamaWeights on the CPU."""
     import torch
@@ -91,6 +108,9 @@ def main(argv=None) -> int:
         p.add_argument("--weight-format", choices=("fp32", "bf16", "fp8"), default="bf16")
         p.add_argument("--seed", type=int, default=0)
         p.add_argument("--layers", type=int, default=None)
+        p.add_argument("--synthetic-tokenizer", action="store_true",
+                       help="random-llama: embed a word-level tokenizer in which every id decodes to a visible word "
+                            "(serving benchmarks of random weights then stream one text delta per token)")
         p.add_argument("--with-mtp", action="store_true",
                        help="random-llama: add a seeded multi-token-prediction component (mtp.* tensors)")
         p.add_argument("--dry-run", action="store_true")
@@ -147,6 +167,10 @@ def main(argv=None) -> int:
         else:
             w = _load_hf(cache, cfg)
             cache.close()
+        if a.synthetic_tokenizer:
+            if a.kind != "random-llama":
+                raise CliError("--synthetic-tokenizer applies to kind random-llama")
+            tokenizer_json = _synthetic_tokenizer(cfg.vocab)
         mtp = None
         if a.with_mtp:
             if a.kind != "random-llama":

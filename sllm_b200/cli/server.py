@@ -127,6 +127,8 @@ def make_backend(a, gguf: str, derived_lock: str, alias: str, overrides=None):
                              context_length=o.get("context_length") or a.context_length, cpu=a.cpu)
     tp, ctrl = getattr(a, "_tp", None), getattr(a, "_ctrl", None)
     eng, tok, g, lock = open_model(src, max_batch=o.get("max_batch") or a.max_batch, tp=tp)
+    if tp is None and not a.cpu:
+        eng.warm_up(greedy_modes=(False,))     # capture the decode graphs before the first request, not during it
     if tp is not None:
         from ..engine.distributed import LeaderEngine, follow
         if tp.rank != 0:

@@ -384,6 +384,24 @@ class Engine:
         g.replay()
         self.kernel_launches += self._graph_launches[key]
 
+    def warm_up(self, greedy_modes=(True, False)) -> int:
+        """Captures the decode graphs of every padded batch size up front (a server would otherwise pay a
+        capture, a few hundred milliseconds, the first time each batch size occurs).  Call while no sequence is
+        live: the capture runs on the static input buffers.  Returns the number of graphs captured."""
+        if not self.use_graphs or self.has_state:
+            return 0
+        made = 0
+        self._max_kv = self.cfg.max_context
+        for n in self.GRAPH_BATCHES:
+            if n > self.max_batch:
+                break
+            for greedy in greedy_modes:
+                if (n, greedy) not in self._graphs:
+                    self._run_decode(n, greedy)
+                    made += 1
+        torch.cuda.synchronize()
+        return made
+
     def decode(self, seqs: list, sample: bool = True):
         """One token for every sequence (the last token of each is the input).  Returns greedy next
         tokens, or logits [len(seqs), vocab] with sample=False."""
