@@ -182,18 +182,55 @@ token_select_kernel(const __nv_bfloat16* __restrict__ logits, int ld, const floa
   double above = 0.0;
   int dummy;
   if (sel_key != 0xffffffffu) mass_at_or_above(score, prob, n, sel_key + 1, sd, si, above, dummy);
-  // among ties with key == sel_key walk ids in ascending order (ties are rare: serial by one thread)
+  // among ties with key == sel_key walk ids in ascending order.  The candidates with that key are found by all
+  // threads (a serial scan of the vocabulary by one thread cost milliseconds at 128 K entries); they are few, so
+  // they are collected in shared memory and thread 0 walks them in id order.  More ties than the list holds fall
+  // back to the serial scan.
+  constexpr int kTieCap = 256;
+  __shared__ int tie_ids[kTieCap];
+  __shared__ int tie_count;
+  if (threadIdx.x == 0) tie_count = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    if (prob[i] > 0.f && ordered_key(score[i]) == sel_key) {
+      const int slot = atomicAdd(&tie_count, 1);
+      if (slot < kTieCap) tie_ids[slot] = i;
+    }
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     double cum = above;
     int chosen = -1, last = -1;
-    for (int i = 0; i < n; ++i) {
-      if (prob[i] > 0.f && ordered_key(score[i]) == sel_key) {
+    const int cnt = tie_count;
+    if (cnt <= kTieCap) {
+      // insertion sort by id (the atomics hand out slots in no particular order)
+      for (int a = 1; a < cnt; ++a) {
+        const int v = tie_ids[a];
+        int b = a - 1;
+        while (b >= 0 && tie_ids[b] > v) {
+          tie_ids[b + 1] = tie_ids[b];
+          --b;
+        }
+        tie_ids[b + 1] = v;
+      }
+      for (int a = 0; a < cnt; ++a) {
+        const int i = tie_ids[a];
         last = i;
         cum += prob[i];
         if (target < cum) {
           chosen = i;
           break;
+        }
+      }
+    } else {
+      for (int i = 0; i < n; ++i) {
+        if (prob[i] > 0.f && ordered_key(score[i]) == sel_key) {
+          last = i;
+          cum += prob[i];
+          if (target < cum) {
+            chosen = i;
+            break;
+          }
         }
       }
     }

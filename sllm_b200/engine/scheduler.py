@@ -18,6 +18,7 @@ from __future__ import annotations
 import collections
 import itertools
 import queue
+import os
 import threading
 import time
 from dataclasses import dataclass, field
@@ -323,6 +324,18 @@ class EngineLoop:
                 pass
 
     def _run(self) -> None:
+        # SLLM_PROFILE_ENGINE_LOOP=<file>: cProfile statistics of this thread, written when the loop stops
+        path = os.environ.get("SLLM_PROFILE_ENGINE_LOOP")
+        if not path:
+            return self._run_loop()
+        import cProfile
+        prof = cProfile.Profile()
+        try:
+            prof.runcall(self._run_loop)
+        finally:
+            prof.dump_stats(path)
+
+    def _run_loop(self) -> None:
         while True:
             with self._wake:
                 while not self._stop and self.planner.idle():
@@ -473,7 +486,6 @@ class EngineLoop:
         from .. import ops
         from . import sampling as S
         n = len(reqs)
-        greedy_tokens = ops.argmax(logits).tolist() if logits.shape[0] else []
         host_rows = [i for i, r in enumerate(reqs) if r.chain is not None or r.mask_fn is not None]
         host_logits = None
         device_rows = []
@@ -481,13 +493,18 @@ class EngineLoop:
             device_rows = [i for i in host_rows if reqs[i].chain is not None and reqs[i].mask_fn is None
                            and logits.is_cuda and reqs[i].chain.supports_device_selector()
                            and not reqs[i].chain.cfg.logit_bias and not reqs[i].chain.counts_matter()]
-            need_host = [i for i in host_rows if i not in device_rows]
+        # the device argmax (a kernel and a synchronising read) only when some row needs it
+        greedy_tokens = ops.argmax(logits).tolist() if logits.shape[0] and len(device_rows) < n else []
+        if host_rows:
+            dset = set(device_rows)
+            need_host = [i for i in host_rows if i not in dset]
             if need_host:
                 host_logits = {i: logits[i].float().cpu().numpy() for i in need_host}
         dev_tokens = {}
         if device_rows:
             import torch
-            sel = logits[torch.tensor(device_rows, device=logits.device)].contiguous()
+            sel = logits if len(device_rows) == n else \
+                logits[torch.tensor(device_rows, device=logits.device)].contiguous()
             recs = S.device_select(sel, [reqs[i].chain.device_row() for i in device_rows]).cpu().numpy() \
                 .view(S.SELECTOR_RECORD_DTYPE).reshape(len(device_rows))
             for j, i in enumerate(device_rows):

@@ -190,6 +190,22 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
     async def next_event(handle):
         return await asyncio.to_thread(handle.events.get)
 
+    def _drain_events(handle, limit: int = 64) -> list:
+        """Blocks for one event, then takes whatever else is already queued (up to `limit`, stopping after a
+        terminal event).  A stream whose consumer lags behind the engine then pays one thread hop, one JSON
+        document and one socket write for the whole backlog instead of one per token."""
+        import queue as _q
+        out = [handle.events.get()]
+        try:
+            while len(out) < limit and out[-1][0] == "delta":
+                out.append(handle.events.get_nowait())
+        except _q.Empty:
+            pass
+        return out
+
+    async def next_events(handle):
+        return await asyncio.to_thread(_drain_events, handle)
+
     def grammar_for(response_format: dict) -> Optional[str]:
         t = response_format.get("type")
         if t == "json_object":
@@ -417,7 +433,7 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
             backend = registry.backends.get(req.model)
             for i in range(len(handles)):
                 yield emit(chunk(i, {"role": "assistant", "content": ""}))
-            pending = {i: asyncio.ensure_future(next_event(h)) for i, h in enumerate(handles)}
+            pending = {i: asyncio.ensure_future(next_events(h)) for i, h in enumerate(handles)}
             first_at = None
             lps = {i: [] for i in pending}
             while pending:
@@ -426,17 +442,33 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
                 if not done_set:
                     raise asyncio.TimeoutError()
                 for i in [k for k, f in pending.items() if f in done_set]:
-                    kind, payload = pending[i].result()
-                    if kind == "delta":
-                        first_at = first_at or time.monotonic()
-                        lps[i].extend(payload.get("logprobs", []))
-                        if payload.get("reasoning"):
-                            yield emit(chunk(i, {"reasoning_content": payload["reasoning"]}))
-                        for piece in _split_utf8(payload.get("content", "")):
-                            if piece:
-                                yield emit(chunk(i, {"content": piece}))
-                        pending[i] = asyncio.ensure_future(next_event(handles[i]))
-                    else:
+                    events = pending[i].result()
+                    # consecutive content-only deltas of a backlog travel as one chunk
+                    merged, text = [], []
+                    for kind, payload in events:
+                        if kind == "delta" and not payload.get("reasoning"):
+                            lps[i].extend(payload.get("logprobs", []))
+                            text.append(payload.get("content", ""))
+                            continue
+                        if text:
+                            merged.append(("delta", {"content": "".join(text)}))
+                            text = []
+                        if kind == "delta":
+                            lps[i].extend(payload.get("logprobs", []))
+                        merged.append((kind, payload))
+                    if text:
+                        merged.append(("delta", {"content": "".join(text)}))
+                    finished = False
+                    for kind, payload in merged:
+                        if kind == "delta":
+                            first_at = first_at or time.monotonic()
+                            if payload.get("reasoning"):
+                                yield emit(chunk(i, {"reasoning_content": payload["reasoning"]}))
+                            for piece in _split_utf8(payload.get("content", "")):
+                                if piece:
+                                    yield emit(chunk(i, {"content": piece}))
+                            continue
+                        finished = True
                         del pending[i]
                         account(req.model, handles[i], payload, t0, first_at)
                         if payload["finish_reason"] in ("error", "cancelled", "timeout"):
@@ -451,6 +483,8 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
                         fin = chunk(i, {}, payload["finish_reason"], extra)
                         fin["usage"] = payload["usage"]        # per-choice usage rides on its finishing chunk
                         yield emit(fin)
+                    if not finished:
+                        pending[i] = asyncio.ensure_future(next_events(handles[i]))
             ok = True
             if session is not None:
                 session.append(b"[DONE]")
