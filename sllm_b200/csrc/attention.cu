@@ -280,6 +280,7 @@ SLLM_EXPORT int sllm_paged_attention(const void* q, int q_ld, const void* k_page
   p.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16); p.out_fp8 = static_cast<uint8_t*>(out_fp8);
   p.out_scale = out_scale; p.ld_scale = ld_scale; p.sinks = sinks;
   p.ws_o = nullptr; p.ws_ml = nullptr; p.counters = counters; p.status_word = nullptr;
+  p.early_trigger = 0;
   if (splits > 1) {
     const long long units = static_cast<long long>(rows) * hkv;
     const long long need = units * splits * (static_cast<long long>(g) * hd + g * 2);

@@ -23,6 +23,7 @@
 #include "attention_common.cuh"
 #include <cudaTypedefs.h>
 #include <cstddef>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -153,10 +154,9 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
-  // No early trigger of dependent launches here: with one, the dependent GEMM's CTAs become resident
-  // beside this kernel's for its whole run, and runs of a few hundred decode steps then showed an
-  // occasional bounded wait of that GEMM running out (status 101, a 2 s stall); without it 1200 steps
-  // ran clean.  Dependents therefore start when this grid completes.
+  // Dependents may start once this CTA holds its tensor memory: the next GEMM then requests its first weight
+  // tiles while this grid drains.
+  if (p.early_trigger) pdl_trigger();
 
   if (warp == 0) {
     // ------------------------------------------------------------ page-walking TMA producer
@@ -541,6 +541,9 @@ SLLM_EXPORT int sllm_decode_attention_tc(const void* q, int q_ld, const void* k_
   p.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16); p.out_fp8 = static_cast<uint8_t*>(out_fp8);
   p.out_scale = out_scale; p.ld_scale = ld_scale; p.sinks = sinks;
   p.ws_o = nullptr; p.ws_ml = nullptr; p.counters = counters; p.status_word = status;
+  // dependent kernels start while this grid drains; SLLM_ATTN_EARLY_TRIGGER=0 turns that off
+  static const int early = [] { const char* e = getenv("SLLM_ATTN_EARLY_TRIGGER"); return (e && e[0] == '0') ? 0 : 1; }();
+  p.early_trigger = early;
   if (splits > 1) {
     const long long units = static_cast<long long>(rows) * hkv;
     const long long need = units * splits * (static_cast<long long>(g) * 128 + g * 2);
