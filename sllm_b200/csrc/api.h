@@ -42,6 +42,13 @@ int sllm_rope_kv_append(void* qkv, const int* positions, const int* seq_index, c
                         int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale, int tokens,
                         int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8, float theta,
                         float k_static_scale, float v_static_scale, const float* inv_freq, void* stream);
+/* rope_pos3 [3, tokens]: temporal / height / width rotary index per token; rotary pair j uses axis 0 for
+   j < sec_t, axis 1 for j < sec_t + sec_h, axis 2 otherwise.  The page slot still comes from positions. */
+int sllm_rope_kv_append_mrope(void* qkv, const int* positions, const int* seq_index, const int* block_table,
+                              int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale, int tokens,
+                              int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8, float theta,
+                              float k_static_scale, float v_static_scale, const float* inv_freq,
+                              const int* rope_pos3, int sec_t, int sec_h, void* stream);
 int sllm_elementwise(const void* a, const void* b, void* y, long long n, int d, int op, float s, void* stream);
 int sllm_argmax(const void* logits, int* out_idx, float* out_val, int rows, int n, int ld, int index_offset,
                 void* ws, long long ws_bytes, int* counters, int n_counters, void* stream);

@@ -220,6 +220,11 @@ struct RopeKvParams {
   float theta;
   float k_static_scale, v_static_scale;  // > 0: static fp8 scales instead of per token-head amax
   const float* inv_freq;   // optional [rotary_dim / 2] precomputed frequencies (scaled RoPE variants)
+  // multi-axis rotary positions (vision-language prompts): [3, tokens] = temporal, height, width index of every
+  // token; rotary pair j turns with axis 0 for j < sec_t, axis 1 for j < sec_t + sec_h, axis 2 otherwise.
+  // Null: every pair turns with positions[t].  The page slot always comes from positions[t].
+  const int* rope_pos3;
+  int tokens, sec_t, sec_h;
 };
 
 __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams p) {
@@ -244,8 +249,13 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
     if (!is_v && i < p.rotary_dim) {
       const int fi = i < half ? i : i - half;
       const float freq = p.inv_freq ? p.inv_freq[fi] : powf(p.theta, -2.f * fi / p.rotary_dim);
+      int rp = pos;
+      if (p.rope_pos3) {
+        const int axis = fi < p.sec_t ? 0 : (fi < p.sec_t + p.sec_h ? 1 : 2);
+        rp = p.rope_pos3[static_cast<size_t>(axis) * p.tokens + t];
+      }
       float sn, cs;
-      sincosf(pos * freq, &sn, &cs);
+      sincosf(rp * freq, &sn, &cs);
       const float a = vals[fi], b = vals[fi + half];
       o = i < half ? a * cs - b * sn : b * cs + a * sn;
     }
@@ -489,24 +499,48 @@ SLLM_EXPORT int sllm_quant_fp8_1x128(const void* x, void* y, float* scale, int l
   return check_launch();
 }
 
-SLLM_EXPORT int sllm_rope_kv_append(void* qkv, const int* positions, const int* seq_index, const int* block_table,
-                                    int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale,
-                                    int tokens, int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8,
-                                    float theta, float k_static_scale, float v_static_scale, const float* inv_freq,
-                                    void* stream) {
+static int rope_kv_append_impl(void* qkv, const int* positions, const int* seq_index, const int* block_table,
+                               int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale,
+                               int tokens, int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8,
+                               float theta, float k_static_scale, float v_static_scale, const float* inv_freq,
+                               const int* rope_pos3, int sec_t, int sec_h, void* stream) {
   if (!qkv || !positions || !seq_index || !block_table || !k_pages || !v_pages || tokens <= 0)
     return SLLM_ERR_INVALID_ARGUMENT;
   if (hd > 512 || (rotary_dim & 1) || rotary_dim > hd || page_size <= 0) return SLLM_ERR_UNSUPPORTED_SHAPE;
   if (kv_fp8 && k_static_scale <= 0.f && (!k_scale || !v_scale)) return SLLM_ERR_INVALID_ARGUMENT;
+  if (rope_pos3 && (sec_t < 0 || sec_h < 0 || sec_t + sec_h > rotary_dim / 2)) return SLLM_ERR_INVALID_ARGUMENT;
   RopeKvParams p;
   p.qkv = static_cast<__nv_bfloat16*>(qkv);
   p.positions = positions; p.seq_index = seq_index; p.block_table = block_table; p.max_blocks = max_blocks;
   p.k_pages = k_pages; p.v_pages = v_pages; p.k_scale = k_scale; p.v_scale = v_scale;
   p.hq = hq; p.hkv = hkv; p.hd = hd; p.rotary_dim = rotary_dim; p.page_size = page_size; p.kv_fp8 = kv_fp8;
   p.theta = theta; p.k_static_scale = k_static_scale; p.v_static_scale = v_static_scale; p.inv_freq = inv_freq;
+  p.rope_pos3 = rope_pos3; p.tokens = tokens; p.sec_t = sec_t; p.sec_h = sec_h;
   dim3 grid(tokens, hq + 2 * hkv);
   launch_kernel(rope_kv_append_kernel, dim3(grid), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u, p);
   return check_launch();
+}
+
+SLLM_EXPORT int sllm_rope_kv_append(void* qkv, const int* positions, const int* seq_index, const int* block_table,
+                                    int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale,
+                                    int tokens, int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8,
+                                    float theta, float k_static_scale, float v_static_scale, const float* inv_freq,
+                                    void* stream) {
+  return rope_kv_append_impl(qkv, positions, seq_index, block_table, max_blocks, k_pages, v_pages, k_scale, v_scale,
+                             tokens, hq, hkv, hd, rotary_dim, page_size, kv_fp8, theta, k_static_scale, v_static_scale,
+                             inv_freq, nullptr, 0, 0, stream);
+}
+
+// The same with 3-axis rotary positions rope_pos3 [3, tokens] (see RopeKvParams).
+SLLM_EXPORT int sllm_rope_kv_append_mrope(void* qkv, const int* positions, const int* seq_index, const int* block_table,
+                                          int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale,
+                                          int tokens, int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8,
+                                          float theta, float k_static_scale, float v_static_scale, const float* inv_freq,
+                                          const int* rope_pos3, int sec_t, int sec_h, void* stream) {
+  if (!rope_pos3) return SLLM_ERR_INVALID_ARGUMENT;
+  return rope_kv_append_impl(qkv, positions, seq_index, block_table, max_blocks, k_pages, v_pages, k_scale, v_scale,
+                             tokens, hq, hkv, hd, rotary_dim, page_size, kv_fp8, theta, k_static_scale, v_static_scale,
+                             inv_freq, rope_pos3, sec_t, sec_h, stream);
 }
 
 SLLM_EXPORT int sllm_elementwise(const void* a, const void* b, void* y, long long n, int d, int op, float s,

@@ -26,6 +26,7 @@ class ForwardBatch:
     cu_seqlens: Optional[torch.Tensor] = None  # int32 [S + 1]
     max_seqlen: int = 0
     embeds: Optional[torch.Tensor] = None      # optional [T, d] input embeddings replacing the gather
+    rope_pos3: Optional[torch.Tensor] = None   # optional int32 [3, T] temporal / height / width rotary positions
     cu_seqlens_host: Optional[list] = None     # the same offsets as a Python list (tile scheduling)
     prefill_tiles: Optional[torch.Tensor] = None  # cached tile table of the tensor-core prefill kernel
     # Recurrent-state (gated delta net) layers: rows of sequence s are row_off[s] .. row_off[s + 1], its state lives in

@@ -33,6 +33,7 @@ class Sequence:
     num_computed: int = 0      # tokens whose KV is published
     failed: Optional[str] = None
     user: object = None
+    rope_delta: int = 0        # rotary position of token i = i + rope_delta once a multimodal prompt compressed it
 
     def __post_init__(self):
         if not self.tokens:
@@ -76,6 +77,11 @@ class Engine:
         self.d_slots = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
         self.d_row_off = torch.arange(max_batch + 1, dtype=torch.int32, device=self.device)
         self.d_logits = None
+        # text rows after a multimodal prompt: rotary position = index + per-sequence delta, on all three axes
+        self.h_rope_delta = torch.zeros(max_batch, dtype=torch.int32, pin_memory=pin)
+        self.d_rope_delta = torch.zeros(max_batch, dtype=torch.int32, device=self.device)
+        self.d_rope3 = torch.zeros(3 * max_batch, dtype=torch.int32, device=self.device)
+        self._rope3_on = False
         self.np_tokens = self.h_tokens.numpy()
         self.np_positions = self.h_positions.numpy()
         self._steps = 0
@@ -149,6 +155,12 @@ class Engine:
                     kept.append((start, rows[:length - start]))
             self._hidden_log[s.seq_id] = kept
 
+    def _rope3_rows(self, seqs: list, counts: list, positions: torch.Tensor) -> torch.Tensor:
+        """3-axis rotary positions of text rows that follow a multimodal prompt: index + the sequence's delta."""
+        delta = torch.tensor([s.rope_delta for s, c in zip(seqs, counts) for _ in range(c)], dtype=torch.int32,
+                             device=positions.device)
+        return (positions + delta).unsqueeze(0).expand(3, -1).contiguous()
+
     def _log_hidden(self, seqs: list, starts: list, counts: list, hidden: torch.Tensor) -> None:
         r0 = 0
         for s, st, n in zip(seqs, starts, counts):
@@ -178,9 +190,17 @@ class Engine:
         return torch.cat(parts, 0) if len(parts) != 1 else parts[0]
 
     # ------------------------------------------------------------------ prefill
-    def prefill(self, seqs: list, chunk_tokens: int = 0, sample: bool = True):
+    def prefill(self, seqs: list, chunk_tokens: int = 0, sample: bool = True, embeds: Optional[torch.Tensor] = None,
+                rope_pos3: Optional[torch.Tensor] = None):
         """Runs the not-yet-computed prompt tokens of ``seqs``; returns greedy next tokens (list[int])
-        or, with sample=False, the last-row logits [len(seqs), vocab]."""
+        or, with sample=False, the last-row logits [len(seqs), vocab].  A multimodal prompt passes ``embeds``
+        ([T, d], the uncomputed tokens of all sequences in order, visual rows spliced in) and ``rope_pos3`` (int32
+        [3, T]); it runs as one chunk and leaves each sequence's ``rope_delta`` for the decode steps."""
+        if embeds is not None or rope_pos3 is not None:
+            if chunk_tokens:
+                raise ValueError("a multimodal prefill runs as one chunk")
+            if rope_pos3 is not None and not self.cfg.mrope_sections:
+                raise ValueError("the model has no multi-axis rotary sections")
         pool = self.cache.pool
         for s in seqs:
             pool.reserve(s.seq_id, len(s.tokens))
@@ -203,6 +223,17 @@ class Engine:
                 break
             sub_table = d_table if len(rows) == len(seqs) else d_table[torch.tensor(rows, device=d_table.device)]
             b = make_prefill_batch(parts, sub_table, self.device, part_starts)
+            if embeds is not None:
+                b.embeds = embeds
+            if rope_pos3 is not None:
+                b.rope_pos3 = rope_pos3.to(self.device, torch.int32).contiguous()
+                r0 = 0
+                for j, i in enumerate(rows):
+                    n_i = len(parts[j])
+                    seqs[i].rope_delta = int(b.rope_pos3[:, r0:r0 + n_i].max().item()) + 1 - (part_starts[j] + n_i)
+                    r0 += n_i
+            elif self.cfg.mrope_sections and any(seqs[i].rope_delta for i in rows):
+                b.rope_pos3 = self._rope3_rows([seqs[i] for i in rows], [len(p) for p in parts], b.positions)
             if self.has_state:
                 b.slots = torch.tensor([self.cache.slot_of[seqs[i].seq_id] for i in rows], dtype=torch.int32, device=self.device)
             self.h2d_bytes += b.num_tokens * 12
@@ -240,10 +271,13 @@ class Engine:
             raise ValueError("extend needs at least one uncomputed token per sequence")
         r = len(parts[0])
         if (sample and self.use_graphs and not self.has_state and embeds is None and r <= self.MAX_EXTEND_ROWS
+                and not any(s.rope_delta for s in seqs)
                 and len(seqs) <= self.max_batch and all(len(p) == r for p in parts)):
             return self._extend_graphed(seqs, parts, r, table)
         b = make_prefill_batch(parts, d_table, self.device, [s.num_computed for s in seqs], last_only=False)
         b.embeds = embeds
+        if self.cfg.mrope_sections and any(s.rope_delta for s in seqs):
+            b.rope_pos3 = self._rope3_rows(seqs, [len(p) for p in parts], b.positions)
         if self.has_state:
             b.slots = torch.tensor([self.cache.slot_of[s.seq_id] for s in seqs], dtype=torch.int32, device=self.device)
         self.h2d_bytes += table.numel() * 4 + b.num_tokens * 12
@@ -338,6 +372,8 @@ class Engine:
                          self.d_table[:n], None, self._max_kv)
         if self.has_state:
             b.row_off, b.slots = self.d_row_off[:n + 1], self.d_slots[:n]
+        if self._rope3_on:
+            b.rope_pos3 = self.d_rope3[:3 * n].view(3, n)
         if greedy:
             self.d_out[:n] = self.model.greedy(b, self.cache)
         else:
@@ -358,7 +394,7 @@ class Engine:
         if not self.use_graphs:
             self._decode_body(n, greedy)
             return
-        key = (n, greedy)
+        key = (n, greedy, True) if self._rope3_on else (n, greedy)
         g = self._graphs.get(key)
         if g is None:
             # warm up outside capture (module init, workspace allocation), then capture
@@ -391,6 +427,7 @@ class Engine:
         if not self.use_graphs or self.has_state:
             return 0
         made = 0
+        self._rope3_on = False
         self._max_kv = self.cfg.max_context
         for n in self.GRAPH_BATCHES:
             if n > self.max_batch:
@@ -437,6 +474,16 @@ class Engine:
         self.d_positions[:np_].copy_(self.h_positions[:np_], non_blocking=True)
         torch.add(self.d_positions[:np_], 1, out=self.d_kv_lens[:np_])
         self.h2d_bytes += np_ * 8
+        self._rope3_on = bool(self.cfg.mrope_sections) and any(s.rope_delta for s in seqs)
+        if self._rope3_on:
+            self.h_rope_delta[:n] = torch.tensor([s.rope_delta for s in seqs], dtype=torch.int32)
+            if np_ > n:
+                self.h_rope_delta[n:np_] = self.h_rope_delta[0]
+            self.d_rope_delta[:np_].copy_(self.h_rope_delta[:np_], non_blocking=True)
+            r3 = self.d_rope3[:3 * np_].view(3, np_)
+            torch.add(self.d_positions[:np_], self.d_rope_delta[:np_], out=r3[0])
+            r3[1].copy_(r3[0])
+            r3[2].copy_(r3[0])
         self._run_decode(np_, sample)
         if sample:
             self.h_out[:np_].copy_(self.d_out[:np_], non_blocking=True)

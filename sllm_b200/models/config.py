@@ -52,6 +52,9 @@ class ModelConfig:
     gdn_conv_kernel: int = 4
     attn_output_gate: bool = False
     post_norms: bool = False         # Gemma-style norms after attention and after the MLP (before the residual add)
+    # vision-language models: rotary pairs [0, t) follow the temporal index, [t, t + h) the height index and the rest
+    # the width index of a token's 3-axis position (text tokens carry the same value on all three)
+    mrope_sections: Optional[list] = None
 
     def to_dict(self) -> dict:
         return asdict(self)

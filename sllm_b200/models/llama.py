@@ -191,7 +191,8 @@ class LlamaModel:
                 from ..ops import gdn as _g
                 qkv = _g.qk_headnorm(qkv, self.hq, self.hkv, hd, lw.q_norm, lw.k_norm, cfg.rms_eps, cfg.norm_offset_one)
             q = ops.rope_kv_append(qkv, b.positions, b.seq_index, b.block_table, kv, self.hq, self.hkv, hd,
-                                   cfg.rope_theta, cfg.rotary_dim)
+                                   cfg.rope_theta, cfg.rotary_dim, rope_pos3=b.rope_pos3,
+                                   mrope_sections=cfg.mrope_sections)
             a = ops.attention(q, kv, b, self.hq, self.hkv, hd, window=cfg.layer_window(li), quant_out=qo,
                               qkv=qkv)
             if self.quant and not qo:
@@ -222,7 +223,7 @@ class LlamaModel:
         x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one)
         qkv = ad.lora_delta(li, "qkv", x, ops.linear(x, lw.qkv))
         q = ops.rope_kv_append(qkv, b.positions, b.seq_index, b.block_table, kv, self.hq, self.hkv, hd, cfg.rope_theta,
-                               cfg.rotary_dim)
+                               cfg.rotary_dim, rope_pos3=b.rope_pos3, mrope_sections=cfg.mrope_sections)
         a = ops.attention(q, kv, b, self.hq, self.hkv, hd, window=cfg.layer_window(li), qkv=qkv)
         h = ad.lora_delta(li, "o", a, ops.linear(a, lw.o, h))
         x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)

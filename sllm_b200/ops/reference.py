@@ -83,15 +83,24 @@ def gated_act(x: torch.Tensor, act: str = "silu", round_intermediate: bool = Tru
 
 
 def rope_split_half(x: torch.Tensor, positions: torch.Tensor, theta: float, rotary_dim: Optional[int] = None,
-                    inv_freq: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x: [T, H, D]; rotates the first rotary_dim channels, pairing channel i with i + rotary_dim/2."""
+                    inv_freq: Optional[torch.Tensor] = None, rope_pos3: Optional[torch.Tensor] = None,
+                    sections: Optional[tuple] = None) -> torch.Tensor:
+    """x: [T, H, D]; rotates the first rotary_dim channels, pairing channel i with i + rotary_dim/2.  With
+    rope_pos3 [3, T] and sections (sec_t, sec_h), rotary pair j turns with the temporal index for j < sec_t, the
+    height index for j < sec_t + sec_h and the width index otherwise."""
     t, h, d = x.shape
     r = rotary_dim or d
     half = r // 2
     xf = x.to(torch.float32)
     if inv_freq is None:
         inv_freq = theta ** (-2.0 * torch.arange(half, dtype=torch.float32, device=x.device) / r)
-    ang = positions.to(torch.float32).unsqueeze(-1) * inv_freq.to(torch.float32).unsqueeze(0)  # [T, half]
+    if rope_pos3 is not None:
+        st, sh = sections
+        axis = torch.tensor([0 if j < st else (1 if j < st + sh else 2) for j in range(half)], device=x.device)
+        pos = rope_pos3.to(torch.float32).t()[:, axis]                                       # [T, half]
+        ang = pos * inv_freq.to(torch.float32).unsqueeze(0)
+    else:
+        ang = positions.to(torch.float32).unsqueeze(-1) * inv_freq.to(torch.float32).unsqueeze(0)  # [T, half]
     cs, sn = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
     a, b = xf[..., :half], xf[..., half:r]
     out = xf.clone()
