@@ -42,6 +42,7 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <vector>
 
 namespace sllm {
 
@@ -67,6 +68,19 @@ struct CommParams {
   uint32_t* epoch;                     // local call counters [max_tiles * kMaxSlices]
 };
 
+// All-gather fused into a column-parallel GEMM: the K range of the B operand (activations) is spread over the
+// ranks, K blocks [src * kb_per_rank, (src + 1) * kb_per_rank) live in rank src's symmetric buffer.  The producer
+// reads them straight out of peer memory with plain (non-multicast) TMA loads, own shard first, after a bounded
+// wait on the flag the owner raises when its shard is written; the MMAs of the shards that have arrived run while
+// the later ones cross NVLink.
+struct GatherParams {
+  int world, rank;
+  int kb_per_rank;
+  const CUtensorMap* maps;   // device array [world]: maps[src] covers rank src's shard [b_rows, K / world]
+  const uint32_t* flags;     // local [world]: flags[src] = last epoch rank src published
+  const uint32_t* epoch;     // local: the epoch this call consumes
+};
+
 struct GemmParams {
   int a_rows, b_rows;
   int num_kb;          // K blocks (of kBoxBytes) over the whole K range
@@ -86,6 +100,7 @@ struct GemmParams {
   int* counters;       // one per output tile, zero between launches
   int* status;         // device status word (0 = ok)
   CommParams comm;     // used by the kComm instantiation only
+  GatherParams gather; // world > 1: B operand gathered from the peers (unscaled GEMM only)
 };
 
 #ifdef SLLM_TRACE
@@ -228,10 +243,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       // the previous kernel, so its HBM latency overlaps that kernel's tail; the dependent operand
       // (activations) follows after the wait.
       const int pre = nkb < p.stages ? nkb : p.stages;
+      const bool gather = p.gather.world > 1;
+      // gathered K blocks are visited own shard first, then the peers in ring order
+      auto kmap = [&](int j) {
+        if (!gather) return j;
+        int kb = j + p.gather.rank * p.gather.kb_per_rank;
+        return kb >= p.num_kb ? kb - p.num_kb : kb;
+      };
+      int gather_ready = gather ? p.gather.rank : -1;      // the last source whose flag has been seen
+      // the epoch is written by the publishing kernel just before this one: it is read on the first gathered
+      // load, which comes after the wait for that kernel
+      uint32_t gather_epoch = 0u;
+      bool gather_have_epoch = false, gather_ok = true;
       auto load_a = [&](int i, int s) {
-        tma_load_2d(smem + s * kStageBytes, &tm_a, &bars->full[s], (kb0 + i) * kElemsPerBox, a_tile * kTileA);
+        tma_load_2d(smem + s * kStageBytes, &tm_a, &bars->full[s], kmap(kb0 + i) * kElemsPerBox, a_tile * kTileA);
       };
       auto load_b = [&](int i, int s) {
+        if (gather) {
+          const int kb = kmap(kb0 + i);
+          const int src = kb / p.gather.kb_per_rank;
+          if (!gather_have_epoch) {
+            gather_epoch = *reinterpret_cast<const volatile uint32_t*>(p.gather.epoch);
+            gather_have_epoch = true;
+          }
+          if (src != gather_ready) {
+            // bounded wait for the owner's flag, then order the TMA (async proxy) reads after it
+            uint32_t spins = 0;
+            long long t0 = 0;
+            while (gather_ok && static_cast<int32_t>(ld_acquire_sys(p.gather.flags + src) - gather_epoch) < 0) {
+              ++spins;
+              if (spins == 1024) t0 = clock64();
+              if (spins > 1024 && (spins & 63) == 0 && clock64() - t0 > kWaitLimitCycles) {
+                if (p.status) atomicCAS(p.status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
+                gather_ok = false;
+              }
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+            gather_ready = src;
+          }
+          // a shard that never arrived is replaced by this rank's own rows: the result is wrong, the status word
+          // says so, and every barrier still completes
+          const int from = gather_ok ? src : p.gather.rank;
+          // two buffers per rank, chosen by the parity of the epoch: maps[parity][source]
+          tma_load_2d(smem + s * kStageBytes + kABytes, p.gather.maps + (gather_epoch & 1u) * p.gather.world + from,
+                      &bars->full[s],
+                      (kb - src * p.gather.kb_per_rank) * kElemsPerBox, b_tile * BN);
+          return;
+        }
         tma_load_2d(smem + s * kStageBytes + kABytes, &tm_b, &bars->full[s], (kb0 + i) * kElemsPerBox, b_tile * BN);
       };
       if (p.const_operand != 0) {
@@ -760,10 +818,19 @@ struct SllmCommDesc {   // host-side mirror passed by the Python layer (ctypes.S
   void* epoch;
 };
 
+struct SllmGatherDesc {   // host-side mirror passed by the Python layer (ctypes.Structure)
+  int world, rank;
+  void* maps;      // device array [4 tile widths (16, 32, 64, 128)][2 parities][world] of CUtensorMap
+  void* flags;     // local flags [world]
+  void* epoch;     // local epoch counter
+};
+
 static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a, const float* scale_b,
                      const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out, int ldy,
                      int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws, long long ws_floats,
-                     int* counters, int n_counters, int* status, void* stream, const SllmCommDesc* comm) {
+                     int* counters, int n_counters, int* status, void* stream, const SllmCommDesc* comm,
+                     const SllmGatherDesc* gather = nullptr) {
+  if (gather) b = a;    // the B operand comes from the peers' buffers; keep the argument checks below simple
   if (!a || !b || !y || a_rows <= 0 || b_rows <= 0 || k <= 0 || splits < 1) return SLLM_ERR_INVALID_ARGUMENT;
   if (bn != 16 && bn != 32 && bn != 64 && bn != 128) return SLLM_ERR_UNSUPPORTED_SHAPE;
   const int elem = scaled ? 1 : 2;
@@ -827,6 +894,16 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
   p.y = static_cast<__nv_bfloat16*>(y);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ws = ws; p.counters = counters; p.status = status;
+  if (gather) {
+    if (scaled || !transpose_out || comm || gather->world < 2 || gather->world > kMaxWorld || gather->rank < 0 ||
+        gather->rank >= gather->world || !gather->maps || !gather->flags || !gather->epoch || num_kb % gather->world)
+      return SLLM_ERR_INVALID_ARGUMENT;
+    const int bi = bn == 16 ? 0 : bn == 32 ? 1 : bn == 64 ? 2 : 3;
+    p.gather.world = gather->world; p.gather.rank = gather->rank; p.gather.kb_per_rank = num_kb / gather->world;
+    p.gather.maps = static_cast<const CUtensorMap*>(gather->maps) + static_cast<size_t>(bi) * 2 * gather->world;
+    p.gather.flags = static_cast<const uint32_t*>(gather->flags);
+    p.gather.epoch = static_cast<const uint32_t*>(gather->epoch);
+  }
   dim3 grid(a_tiles, b_tiles, splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define SLLM_GEMM_CASE(BN_)                                                                                 \
@@ -874,4 +951,77 @@ SLLM_EXPORT int sllm_gemm_allreduce(const void* a, const void* b, void* y, const
   return gemm_impl(a, b, y, scale_a, scale_b, residual, a_rows, b_rows, k, scaled, transpose_out, ldy, ld_sa, ld_sb,
                    bn, splits, stages, ws, ws_floats, counters, n_counters, status, stream,
                    static_cast<const SllmCommDesc*>(comm));
+}
+
+// ---------------------------------------------------------------- all-gather -> column-parallel GEMM
+namespace sllm {
+// Copies this rank's activation shard [rows, ks] into its symmetric buffer of the next epoch's parity and raises
+// flag[rank] = epoch on every rank.  One CTA: the shard is small (decode / verify rows).
+__global__ void __launch_bounds__(1024)
+gather_publish_kernel(const __nv_bfloat16* __restrict__ x, int rows, int ks, int ldx, __nv_bfloat16* buf0,
+                      __nv_bfloat16* buf1, int cap_rows, uint32_t* epoch, CommParams peers) {
+  pdl_wait();
+  __shared__ uint32_t s_e;
+  if (threadIdx.x == 0) {
+    s_e = *epoch + 1;
+    *epoch = s_e;
+  }
+  __syncthreads();
+  const uint32_t e = s_e;
+  __nv_bfloat16* dst = (e & 1u) ? buf1 : buf0;
+  const int units = ks / 8;                      // 16-byte units per row
+  for (int i = threadIdx.x; i < rows * units; i += blockDim.x) {
+    const int r = i / units, u = i % units;
+    reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * ks)[u] =
+        *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * ldx + u * 8);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < peers.world) st_release_sys(peers.flags[threadIdx.x] + peers.rank, e);
+  pdl_trigger();
+}
+}  // namespace sllm
+
+// Builds the tensor maps of every rank's two shard buffers for the four token-tile widths and copies them to
+// `dev_maps` ([4][2][world] CUtensorMap).  bufs[p * 2 + parity]: rank p's buffer as mapped in this process.
+SLLM_EXPORT int sllm_gather_build_maps(void* dev_maps, const void* const* bufs, int world, int cap_rows, int k_shard) {
+  if (!dev_maps || !bufs || world < 2 || world > kMaxWorld || cap_rows <= 0 || k_shard <= 0 || (k_shard % 64))
+    return SLLM_ERR_INVALID_ARGUMENT;
+  static const int widths[4] = {16, 32, 64, 128};
+  std::vector<CUtensorMap> host(static_cast<size_t>(4) * 2 * world);
+  for (int bi = 0; bi < 4; ++bi)
+    for (int par = 0; par < 2; ++par)
+      for (int pr = 0; pr < world; ++pr) {
+        const int rc = make_kmajor_tmap(&host[(static_cast<size_t>(bi) * 2 + par) * world + pr], bufs[pr * 2 + par], 2,
+                                        cap_rows, k_shard, static_cast<long long>(k_shard) * 2, widths[bi]);
+        if (rc != SLLM_OK) return rc;
+      }
+  return cudaMemcpy(dev_maps, host.data(), host.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice) == cudaSuccess
+             ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+// flags_on_peers[p]: rank p's flag array as mapped in this process.
+SLLM_EXPORT int sllm_gather_publish(const void* x, int rows, int k_shard, int ldx, void* buf0, void* buf1, int cap_rows,
+                                    void* epoch, const void* const* flags_on_peers, int world, int rank, void* stream) {
+  if (!x || !buf0 || !buf1 || !epoch || !flags_on_peers || rows <= 0 || rows > cap_rows || (k_shard % 8) || (ldx % 8) ||
+      world < 2 || world > kMaxWorld || rank < 0 || rank >= world || (reinterpret_cast<uintptr_t>(x) & 15))
+    return SLLM_ERR_INVALID_ARGUMENT;
+  CommParams peers;
+  memset(&peers, 0, sizeof(peers));
+  peers.world = world; peers.rank = rank;
+  for (int i = 0; i < world; ++i) peers.flags[i] = static_cast<uint32_t*>(const_cast<void*>(flags_on_peers[i]));
+  launch_kernel(gather_publish_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), 1u,
+                static_cast<const __nv_bfloat16*>(x), rows, k_shard, ldx, static_cast<__nv_bfloat16*>(buf0),
+                static_cast<__nv_bfloat16*>(buf1), cap_rows, static_cast<uint32_t*>(epoch), peers);
+  return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+// Y[rows, n] = concat over ranks of X_r[rows, k / world] times W[n, k]^T, bf16, weights as the 128-row operand.
+// The shards must have been published with sllm_gather_publish on every rank (same stream order everywhere).
+SLLM_EXPORT int sllm_gemm_allgather(const void* w, void* y, const void* residual, int n, int rows, int k, int ldy, int bn,
+                                    int splits, int stages, float* ws, long long ws_floats, int* counters, int n_counters,
+                                    int* status, void* stream, const void* gather) {
+  if (!gather) return SLLM_ERR_INVALID_ARGUMENT;
+  return gemm_impl(w, nullptr, y, nullptr, nullptr, residual, n, rows, k, 0, 1, ldy, 0, 0, bn, splits, stages, ws,
+                   ws_floats, counters, n_counters, status, stream, nullptr, static_cast<const SllmGatherDesc*>(gather));
 }

@@ -111,6 +111,28 @@ def main():
     assert ops.device_status(dev) == 0
     del eng, ref_eng
     torch.cuda.synchronize()
+    # all-gather fused into a column-parallel GEMM: K shards pulled from the peers by the GEMM's own TMA producer
+    from sllm_b200.parallel.gather import GatherGemm, NcclGatherGemm
+    k, n_local = 512 * world, 384
+    gg = GatherGemm(world, rank, dev, max_rows=200, k=k)
+    ng = NcclGatherGemm(world, rank, dev)
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    w_local = LinearWeight("dense", (torch.randn(n_local, k, device=dev, generator=gen) * 0.05).bfloat16())
+    for m in (1, 5, 33, 128, 200):
+        for rep in range(3):                      # both buffer parities
+            x = (torch.randn(m, k, device=dev) * (rep + 1)).bfloat16()
+            dist.broadcast(x, 0)
+            res = torch.randn(m, n_local, device=dev).bfloat16()
+            shard = x[:, rank * (k // world):(rank + 1) * (k // world)]
+            want = x.float() @ w_local.w.float().t() + res.float()
+            got_f = gg.linear(shard, w_local, res)
+            got_n = ng.linear(shard, w_local, res)
+            assert rel(got_f, want) < 1e-2, ("gather fused", m, rep, rel(got_f, want))
+            assert rel(got_n, want) < 1e-2, ("gather nccl", m, rep, rel(got_n, want))
+    assert ops.device_status(dev) == 0
+    mark("gather gemm ok")
+    torch.cuda.synchronize()
+    gg.close()
     fused.close()
     dist.barrier()
     if rank == 0:
