@@ -89,6 +89,10 @@ def open_model(args, max_batch: int = 8, tp=None):
     cache = PagedKVCache(cfg, max_batch * blocks + 8, device, kv_heads=model.local_kv_heads)
     eng = Engine(cfg, model, cache, device, max_batch=max_batch, use_cuda_graphs=not use_cpu, tp=tp)
     eng.mtp_weights = loader.load_mtp_gguf(g, cfg, device) if tp_size == 1 else None
+    vis = loader.load_vision_gguf(g, cfg, device)
+    if vis is not None:
+        from ..models.vision_tower import VisionTower
+        eng.vision = VisionTower(*vis)
     tok = loader.tokenizer_from_gguf(g)
     return eng, tok, g, lock
 
@@ -121,7 +125,9 @@ def add_generation_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--no-generation-prompt", action="store_true")
 
 
-def prompt_ids_from_args(args, tok) -> list:
+def prompt_ids_from_args(args, tok, as_text: bool = False):
+    """Token ids of the request (or, with as_text, its rendered text; --image inputs put one vision marker each in
+    front of the first user message)."""
     from ..frontend.chat import ChatMessage, render_chatml
     given = [x for x in (args.prompt, args.message or None, args.input_token_ids) if x]
     if len(given) != 1:
@@ -139,6 +145,8 @@ def prompt_ids_from_args(args, tok) -> list:
             raise CliError("--input-token-ids must be integers") from None
         if not ids or any(i < 0 for i in ids):
             raise CliError("--input-token-ids must be non-negative and non-empty")
+        if as_text:
+            raise CliError("--image needs --prompt or --message")
         return ids
     if args.prompt is not None:
         msgs = [ChatMessage("user", args.prompt)]
@@ -149,9 +157,17 @@ def prompt_ids_from_args(args, tok) -> list:
             if not sep or role not in ("system", "user", "assistant", "tool"):
                 raise CliError("--message must look like ROLE:CONTENT with role system|user|assistant|tool")
             msgs.append(ChatMessage(role, content))
+    if args.image:
+        marks = "<|vision_start|><|image_pad|><|vision_end|>" * len(args.image)
+        for i, m in enumerate(msgs):
+            if m.role == "user":
+                msgs[i] = ChatMessage("user", marks + m.content)
+                break
+        else:
+            raise CliError("--image needs a user message")
     text = render_chatml(msgs, thinking="enabled" if args.thinking else "disabled",
                          add_generation_prompt=not args.no_generation_prompt)
-    return tok.encode(text)
+    return text if as_text else tok.encode(text)
 
 
 def run_main(fn) -> int:

@@ -111,6 +111,9 @@ def main(argv=None) -> int:
         p.add_argument("--synthetic-tokenizer", action="store_true",
                        help="random-llama: embed a word-level tokenizer in which every id decodes to a visible word "
                             "(serving benchmarks of random weights then stream one text delta per token)")
+        p.add_argument("--with-vision", choices=("tiny", "qwen"), default=None,
+                       help="random-llama: add a seeded vision tower (tiny: 2 blocks of width 64; qwen: 24 blocks of "
+                            "width 1024) whose merger projects to the model width, and 3-axis rotary sections")
         p.add_argument("--with-mtp", action="store_true",
                        help="random-llama: add a seeded multi-token-prediction component (mtp.* tensors)")
         p.add_argument("--dry-run", action="store_true")
@@ -171,6 +174,20 @@ def main(argv=None) -> int:
             if a.kind != "random-llama":
                 raise CliError("--synthetic-tokenizer applies to kind random-llama")
             tokenizer_json = _synthetic_tokenizer(cfg.vocab)
+        vision = None
+        if a.with_vision:
+            if a.kind != "random-llama":
+                raise CliError("--with-vision applies to kind random-llama")
+            from dataclasses import asdict
+            from ..models import vision_tower as VT
+            vc = VT.tiny_vision() if a.with_vision == "tiny" else VT.VisionConfig()
+            vc.out_hidden = cfg.d_model
+            pairs = (cfg.rotary_dim or cfg.head_dim) // 2
+            cfg.vision = asdict(vc)
+            cfg.mrope_sections = [pairs // 4, (pairs - pairs // 4) // 2]
+            cfg.image_token_id = cfg.vocab - 1
+            vision = VT.init_random_vision_weights(vc, dev, seed=a.seed + 2,
+                                                   dtype=torch.float32 if cfg.weight_format == "fp32" else torch.bfloat16)
         mtp = None
         if a.with_mtp:
             if a.kind != "random-llama":
@@ -178,7 +195,7 @@ def main(argv=None) -> int:
             from ..models.mtp import init_random_mtp_weights
             mtp = init_random_mtp_weights(cfg, dev, seed=a.seed + 1)
         dl = loader.export_llama_gguf(cfg, w, a.output, tokenizer_json=tokenizer_json, chat_template=chat_template,
-                                      source_fingerprints=tuple(fps), mtp=mtp,
+                                      source_fingerprints=tuple(fps), mtp=mtp, vision=vision,
                                       converter_args={"kind": a.kind, "commit": a.converter_commit, "seed": a.seed,
                                                       "weight_format": a.weight_format})
         tmp = a.derived_lock + ".tmp"

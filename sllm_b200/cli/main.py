@@ -204,7 +204,22 @@ def cmd_input_tokens(argv):
 
 
 # ------------------------------------------------------------------------------------------ model commands
-def _generate(eng, tok, ids, a, on_delta=None, timeline=None):
+def _multimodal_from_args(eng, tok, a):
+    """models.vision_tower.MultimodalPrompt for --image inputs."""
+    from ..frontend import vision as V
+    from ..models.vision_tower import MultimodalPrompt, encode_with_images
+    tower = getattr(eng, "vision", None)
+    if tower is None:
+        raise CliError("--image needs a model file with a vision tower (v.* tensors)")
+    tok_id = eng.cfg.image_token_id if eng.cfg.image_token_id is not None else eng.cfg.vocab - 1
+    try:
+        images = V.process_many([V.BoundedImage.from_local_path(p) for p in a.image])
+    except (OSError, V.VisionError) as exc:
+        raise CliError(f"image input rejected: {exc}") from None
+    return MultimodalPrompt(tower, images, encode_with_images(tok, prompt_ids_from_args(a, tok, as_text=True), tok_id), tok_id)
+
+
+def _generate(eng, tok, ids, a, on_delta=None, timeline=None, mm=None):
     """Runs one request through the generation service; returns (text, reasoning, done, handle)."""
     from ..engine.scheduler import EngineLoop
     from ..frontend.generation import GenerationConfig, GenerationService
@@ -225,7 +240,7 @@ def _generate(eng, tok, ids, a, on_delta=None, timeline=None):
                                stop=tuple(a.stop), thinking=a.thinking, separate_reasoning=a.thinking, echo_tokens=True)
         if timeline is not None:
             timeline("PrefillSubmit")
-        h = svc.submit(ids, cfg)
+        h = svc.submit(ids, cfg, mm=mm)
         content, reasoning, done, tokens, first = [], [], None, [], True
         for kind, payload in h:
             if kind == "delta":
@@ -262,9 +277,10 @@ def _gen_parser(name):
 def cmd_generate(argv, name="generate"):
     a = _gen_parser(name).parse_args(argv)
     eng, tok, g, lock = open_model(a)
-    ids = prompt_ids_from_args(a, tok)
+    mm = _multimodal_from_args(eng, tok, a) if a.image else None
+    ids = mm.tokens if mm is not None else prompt_ids_from_args(a, tok)
     t0 = time.perf_counter()
-    text, reasoning, done, tokens = _generate(eng, tok, ids, a)
+    text, reasoning, done, tokens = _generate(eng, tok, ids, a, mm=mm)
     out = {"text": text, "tokens": tokens, "finish_reason": done["finish_reason"], "usage": done["usage"],
            "model": lock["semantic_model_id"], "seconds": round(time.perf_counter() - t0, 4)}
     if reasoning:

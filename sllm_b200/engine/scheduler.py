@@ -211,6 +211,7 @@ class GenRequest:
     prefix_hit_tokens: int = 0
     shifted_tokens: int = 0              # tokens dropped by context shifts so far
     shift_count: int = 0
+    mm: object = None                    # multimodal prompt: mm(engine) -> (embeds [T, d], rope_pos3 [3, T])
 
 
 class EngineLoop:
@@ -396,12 +397,26 @@ class EngineLoop:
                     except Exception as exc:   # allocation failure poisons only this request
                         r.finish_reason = f"error:{type(exc).__name__}"
                         outcomes[r.rid] = "failed"
-                if live:
-                    logits = eng.prefill([r.seq for r in live], self.prefill_chunk_tokens, sample=False)
+                plain = [r for r in live if r.mm is None]
+                if plain:
+                    logits = eng.prefill([r.seq for r in plain], self.prefill_chunk_tokens, sample=False)
                     if self.prefix_cache is not None:
-                        for r in live:
+                        for r in plain:
                             self.prefix_cache.publish(r.seq, len(r.prompt))
-                    self._select_and_publish(live, logits, outcomes)
+                    self._select_and_publish(plain, logits, outcomes)
+                for r in live:
+                    if r.mm is None:
+                        continue
+                    # a multimodal prompt runs alone and in one chunk: visual rows replace the placeholder
+                    # embeddings and the rotary positions carry three axes
+                    try:
+                        embeds, pos3 = r.mm(eng)
+                        logits = eng.prefill([r.seq], sample=False, embeds=embeds, rope_pos3=pos3)
+                    except Exception as exc:
+                        r.finish_reason = f"error:{type(exc).__name__}:{exc}"
+                        outcomes[r.rid] = "failed"
+                        continue
+                    self._select_and_publish([r], logits, outcomes)
             else:
                 if self.context_policy is not None and not self.context_policy.is_disabled:
                     self._shift_full_windows(reqs)

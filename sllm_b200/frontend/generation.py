@@ -107,7 +107,9 @@ class GenerationService:
                 self._grammar_cache[gbnf] = g
         return g
 
-    def submit(self, prompt_ids: list, cfg: GenerationConfig, prefix_seq=None) -> GenerationHandle:
+    def submit(self, prompt_ids: list, cfg: GenerationConfig, prefix_seq=None, mm=None) -> GenerationHandle:
+        """``mm`` (models.vision_tower.MultimodalPrompt) marks a prompt with images: ``prompt_ids`` must then be
+        its expanded token list."""
         if not prompt_ids:
             raise ValueError("prompt must contain at least one token")
         if not 1 <= cfg.max_new_tokens <= MAX_COMPLETION_TOKENS:
@@ -219,7 +221,8 @@ class GenerationService:
         req = GenRequest(prompt=list(prompt_ids), max_new_tokens=cfg.max_new_tokens, chain=chain,
                          stop_tokens=() if cfg.ignore_eos else eos_ids, on_token=on_token, on_done=on_done,
                          mask_fn=mask_fn if (gstate is not None or rctl is not None) else None,
-                         deadline=(time.monotonic() + cfg.timeout_s) if cfg.timeout_s else None, prefix_seq=prefix_seq)
+                         deadline=(time.monotonic() + cfg.timeout_s) if cfg.timeout_s else None,
+                         prefix_seq=None if mm is not None else prefix_seq, mm=mm)
         h.rid = self.loop.submit(req)
         h.request = req
         return h

@@ -55,6 +55,8 @@ class ModelConfig:
     # vision-language models: rotary pairs [0, t) follow the temporal index, [t, t + h) the height index and the rest
     # the width index of a token's 3-axis position (text tokens carry the same value on all three)
     mrope_sections: Optional[list] = None
+    image_token_id: Optional[int] = None     # placeholder id of visual tokens (None: vocab - 1)
+    vision: Optional[dict] = None            # fields of models.vision_tower.VisionConfig when the file carries a tower
 
     def to_dict(self) -> dict:
         return asdict(self)

@@ -39,7 +39,7 @@ def _u8_bytes(t: torch.Tensor) -> bytes:
 
 def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_json: Optional[str] = None,
                       chat_template: Optional[str] = None, source_fingerprints: tuple = (),
-                      converter_args: Optional[dict] = None, mtp=None) -> dict:
+                      converter_args: Optional[dict] = None, mtp=None, vision=None) -> dict:
     """Writes unsharded (tensor-parallel size 1) weights; returns the derived lock document.  ``mtp``
     (models.mtp.MtpWeights, dense) adds the multi-token-prediction component as `mtp.*` tensors."""
     tensors, bindings = [], []
@@ -77,6 +77,9 @@ def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_js
     add_dense("output_norm.weight", w.final_norm)
     if not cfg.tie_embeddings:
         add_linear("output.weight", w.lm_head, 0, cfg.vocab)
+    if vision is not None:              # models.vision_tower.VisionWeights: the 297-tensor inventory as `v.*`
+        for name, t in vision_tensor_list(vision):
+            add_dense(name, t)
     if mtp is not None:
         l = mtp.layer
         add_dense("mtp.fc.weight", mtp.fc.w)
@@ -186,6 +189,55 @@ def load_llama_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, k
     else:
         head = lin([rows("output.weight", vo, v_hi)])
     return cfg, LlamaWeights(embed, layers, final_norm, head, vo)
+
+
+def vision_tensor_list(w) -> list:
+    """(name, tensor) of every tensor of a vision tower, in file order."""
+    out = [("v.patch_embd.weight", w.patch_w.w), ("v.patch_embd.bias", w.patch_b), ("v.position_embd.weight", w.pos_table)]
+    for i, b in enumerate(w.blocks):
+        p = f"v.blk.{i}."
+        out += [(p + "ln1.weight", b.norm1_w), (p + "ln1.bias", b.norm1_b), (p + "ln2.weight", b.norm2_w),
+                (p + "ln2.bias", b.norm2_b), (p + "attn_qkv.weight", b.qkv.w), (p + "attn_qkv.bias", b.qkv_b),
+                (p + "attn_out.weight", b.proj.w), (p + "attn_out.bias", b.proj_b), (p + "ffn_up.weight", b.fc1.w),
+                (p + "ffn_up.bias", b.fc1_b), (p + "ffn_down.weight", b.fc2.w), (p + "ffn_down.bias", b.fc2_b)]
+    out += [("v.merger.ln.weight", w.merger_norm_w), ("v.merger.ln.bias", w.merger_norm_b),
+            ("v.merger.fc1.weight", w.merger_fc1.w), ("v.merger.fc1.bias", w.merger_fc1_b),
+            ("v.merger.fc2.weight", w.merger_fc2.w), ("v.merger.fc2.bias", w.merger_fc2_b)]
+    return out
+
+
+def load_vision_gguf(g: G.GgufFile, cfg: ModelConfig, device):
+    """(VisionConfig, VisionWeights) of a verified open GGUF file, or None when it carries no tower."""
+    if not cfg.vision or "v.patch_embd.weight" not in g.tensors:
+        return None
+    from .vision_tower import VisionBlock, VisionConfig, VisionWeights
+    vc = VisionConfig(**cfg.vision)
+    if vc.out_hidden != cfg.d_model:
+        raise G.GgufError("the vision tower's output width differs from the language model's")
+    dt = torch.float32 if cfg.weight_format == "fp32" else torch.bfloat16
+    want = G.T_F32 if dt == torch.float32 else G.T_BF16
+
+    def t(name):
+        e = g.tensors.get(name)
+        if e is None:
+            raise G.GgufError(f"incomplete vision tower: {name} is missing")
+        if e.ttype != want:
+            raise G.GgufError(f"{name}: unexpected tensor type {e.ttype}")
+        return g.upload(name, torch.device(device), dt).view(e.shape)
+
+    def lw(name):
+        return LinearWeight("dense", t(name))
+    w = VisionWeights(lw("v.patch_embd.weight"), t("v.patch_embd.bias"), t("v.position_embd.weight"))
+    for i in range(vc.depth):
+        p = f"v.blk.{i}."
+        w.blocks.append(VisionBlock(t(p + "ln1.weight"), t(p + "ln1.bias"), t(p + "ln2.weight"), t(p + "ln2.bias"),
+                                    lw(p + "attn_qkv.weight"), t(p + "attn_qkv.bias"), lw(p + "attn_out.weight"),
+                                    t(p + "attn_out.bias"), lw(p + "ffn_up.weight"), t(p + "ffn_up.bias"),
+                                    lw(p + "ffn_down.weight"), t(p + "ffn_down.bias")))
+    w.merger_norm_w, w.merger_norm_b = t("v.merger.ln.weight"), t("v.merger.ln.bias")
+    w.merger_fc1, w.merger_fc1_b = lw("v.merger.fc1.weight"), t("v.merger.fc1.bias")
+    w.merger_fc2, w.merger_fc2_b = lw("v.merger.fc2.weight"), t("v.merger.fc2.bias")
+    return vc, w
 
 
 def load_mtp_gguf(g: G.GgufFile, cfg: ModelConfig, device):

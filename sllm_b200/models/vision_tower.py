@@ -272,3 +272,52 @@ def assemble_multimodal(tokens: list, image_token_id: int, token_embeds: torch.T
     if img != len(images):
         raise ValueError("fewer image placeholder runs than images")
     return out, pos
+
+
+IMAGE_MARKER = "<|image_pad|>"
+
+
+def encode_with_images(tokenizer, text: str, image_token_id: int) -> list:
+    """Token ids of `text` in which every IMAGE_MARKER becomes one `image_token_id` (tokenizers that do not know
+    the marker as a special token would otherwise spell it out)."""
+    parts = text.split(IMAGE_MARKER)
+    ids = []
+    for i, part in enumerate(parts):
+        if i:
+            ids.append(image_token_id)
+        if part:
+            ids.extend(tokenizer.encode(part))
+    return ids
+
+
+class MultimodalPrompt:
+    """A prompt with images, ready for the engine: `tokens` carries one placeholder run per image (as long as the
+    image's merged grid), and calling the object with the engine returns (embeds [T, d], rope_pos3 int32 [3, T])
+    for `Engine.prefill`.  The tower runs when the request is scheduled, on the engine's device."""
+
+    def __init__(self, tower: VisionTower, images: list, prompt_ids: list, image_token_id: int):
+        merge2 = tower.cfg.merge * tower.cfg.merge
+        if sum(1 for t in prompt_ids if t == image_token_id) != len(images):
+            raise ValueError("the prompt needs exactly one image placeholder per image")
+        self.tower, self.images, self.image_token_id = tower, images, image_token_id
+        self.tokens, k = [], 0
+        for t in prompt_ids:
+            if t == image_token_id:
+                g = images[k].grid_thw
+                self.tokens.extend([image_token_id] * (g[0] * g[1] * g[2] // merge2))
+                k += 1
+            else:
+                self.tokens.append(t)
+
+    def __call__(self, engine):
+        dev = engine.device
+        w = engine.model.w
+        rows = []
+        for img in self.images:
+            patches = torch.from_numpy(np.ascontiguousarray(img.patches)).to(dev)
+            rows.append((self.tower.forward(patches, img.grid_thw), img.grid_thw))
+        # the placeholder id may lie outside the embedding table: embed a harmless id there, the rows are overwritten
+        ids = [0 if t == self.image_token_id else t for t in self.tokens]
+        emb = ops.embedding(w.embed, torch.tensor(ids, dtype=torch.int32, device=dev), engine.cfg.embedding_scale)
+        embeds, pos3 = assemble_multimodal(self.tokens, self.image_token_id, emb, rows, self.tower.cfg.merge)
+        return embeds.contiguous(), torch.from_numpy(pos3).to(dev)

@@ -178,9 +178,9 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
         if n_prompt + max_new > backend.max_context():
             raise E.invalid_value("prompt tokens plus max tokens exceed the server context length", "max_completion_tokens")
 
-    def submit(backend, ids, gcfg, alias):
+    def submit(backend, ids, gcfg, alias, mm=None):
         try:
-            return backend.submit(ids, gcfg)
+            return backend.submit(ids, gcfg, mm=mm) if mm is not None else backend.submit(ids, gcfg)
         except QueueFull:
             metrics.request(alias, "rejected")
             raise E.rate_limited() from None
@@ -326,7 +326,19 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
                 prompt = render_chatml(req.messages, "enabled" if req.thinking else "disabled")
             except ChatRenderError as exc:
                 raise E.invalid_value(str(exc), "messages") from None
-            ids = backend.tokenizer.encode(prompt)
+            mm_prompt = None
+            if req.images:
+                from ..frontend import vision as V
+                try:
+                    mm_prompt = await asyncio.to_thread(
+                        backend.multimodal_prompt, prompt, [V.BoundedImage.from_bytes(i.data) for i in req.images])
+                except V.VisionError as exc:
+                    raise E.invalid_value(str(exc), "messages") from None
+                except ValueError as exc:
+                    raise E.unsupported(str(exc), "messages") from None
+                ids = mm_prompt.tokens
+            else:
+                ids = backend.tokenizer.encode(prompt)
             check_context(backend, len(ids), req.max_tokens)
             gbnf = grammar_for(req.response_format)
             if req.ignore_eos and getattr(backend.tokenizer, "eos_token_id", None) is not None:
@@ -347,7 +359,7 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
                                         reasoning_budget=req.reasoning_budget, grammar_gbnf=gbnf,
                                         timeout_s=cfg.completion_timeout_s, ignore_eos=req.ignore_eos)
                 try:
-                    handles.append(submit(backend, ids, gcfg, req.model))
+                    handles.append(submit(backend, ids, gcfg, req.model, mm_prompt))
                 except E.ApiError:
                     for h in handles:
                         h.cancel()

@@ -213,7 +213,7 @@ class EngineBackend:
         return {"backend": "sllm-b200", "model_family": c.family, "context_length": c.max_context, "vocab_size": c.vocab,
                 "kv_cache_encoding": c.kv_format, "weight_format": c.weight_format, "page_size": c.page_size,
                 "tensor_parallel": getattr(self.engine.tp, "size", 1) if self.engine.tp else 1,
-                "prefix_cache": self.prefix_cache is not None}
+                "prefix_cache": self.prefix_cache is not None, "vision": getattr(self.engine, "vision", None) is not None}
 
     def memory(self) -> dict:
         cache = self.engine.cache
@@ -239,10 +239,25 @@ class EngineBackend:
     def max_context(self) -> int:
         return self.engine.cfg.max_context
 
-    def submit(self, prompt_ids: list, cfg: GenerationConfig, prefix_seq=None) -> GenerationHandle:
+    def submit(self, prompt_ids: list, cfg: GenerationConfig, prefix_seq=None, mm=None) -> GenerationHandle:
+        if mm is not None:                       # prompts with images bypass the (token-keyed) prefix cache
+            return self.service.submit(prompt_ids, cfg, mm=mm)
         if prefix_seq is None and self.prefix_cache is not None:
             prefix_seq = self.prefix_cache.lookup(prompt_ids)
         return self.service.submit(prompt_ids, cfg, prefix_seq=prefix_seq)
+
+    def multimodal_prompt(self, text: str, images: list):
+        """Tokenises a rendered prompt whose image markers stand for `images` (frontend.vision.BoundedImage) and
+        returns the models.vision_tower.MultimodalPrompt for `submit`."""
+        from ..frontend import vision as V
+        from ..models.vision_tower import MultimodalPrompt, encode_with_images
+        tower = getattr(self.engine, "vision", None)
+        if tower is None:
+            raise ValueError("the model has no vision tower")
+        tok_id = self.engine.cfg.image_token_id
+        if tok_id is None:
+            tok_id = self.engine.cfg.vocab - 1
+        return MultimodalPrompt(tower, V.process_many(images), encode_with_images(self.tokenizer, text, tok_id), tok_id)
 
     def embed(self, token_lists: list) -> list:
         """Mean of the final hidden rows in float64, L2-normalised, finite float32
