@@ -17,7 +17,10 @@ from .paged import PagedKVCache
 
 
 class HybridCache(PagedKVCache):
-    def __init__(self, cfg: ModelConfig, num_pages: int, device, max_seqs: int, kv_heads: Optional[int] = None):
+    def __init__(self, cfg: ModelConfig, num_pages: int, device, max_seqs: int, kv_heads: Optional[int] = None,
+                 tp_size: int = 1):
+        """``tp_size``: the gated-delta-net heads (and with them the conv and recurrent state) are split over that
+        many tensor-parallel ranks; this cache holds one rank's share."""
         self.full_layers = [i for i in range(cfg.n_layers) if (i + 1) % cfg.full_attention_interval == 0]
         self.gdn_layers = [i for i in range(cfg.n_layers) if i not in self.full_layers]
         import dataclasses
@@ -26,13 +29,13 @@ class HybridCache(PagedKVCache):
         self._kv_index = {l: j for j, l in enumerate(self.full_layers)}
         self._gdn_index = {l: j for j, l in enumerate(self.gdn_layers)}
         hd = cfg.gdn_head_dim
-        self.width = (2 * cfg.gdn_qk_heads + cfg.gdn_heads) * hd
+        self.width = (2 * cfg.gdn_qk_heads + cfg.gdn_heads) // tp_size * hd
         n = max(1, len(self.gdn_layers))
         self.max_seqs = max_seqs
         self.conv_state = torch.zeros((n, max_seqs, cfg.gdn_conv_kernel - 1, self.width), dtype=torch.bfloat16 if
                                       torch.device(device).type == "cuda" or cfg.weight_format != "fp32" else torch.float32,
                                       device=device)
-        self.rec_state = torch.zeros((n, max_seqs, cfg.gdn_heads, hd, hd), dtype=torch.float32, device=device)
+        self.rec_state = torch.zeros((n, max_seqs, cfg.gdn_heads // tp_size, hd, hd), dtype=torch.float32, device=device)
         self._free = list(range(max_seqs - 1, -1, -1))
         self.slot_of: dict = {}
 

@@ -549,10 +549,11 @@ def build_engine(cfg: ModelConfig, device="cuda", seed: int = 0, num_pages: Opti
     if cfg.family == "qwen35":
         from ..cache.hybrid import HybridCache
         from ..models.qwen35 import Qwen35Model, init_random_qwen35_weights
-        model = Qwen35Model(cfg, init_random_qwen35_weights(cfg, device, seed), tp)
+        model = Qwen35Model(cfg, init_random_qwen35_weights(cfg, device, seed, tp_size=tp_size, tp_rank=tp_rank), tp)
         if num_pages is None:
             num_pages = max_batch * ((cfg.max_context + cfg.page_size - 1) // cfg.page_size) + 8
-        cache = HybridCache(cfg, num_pages, device, max_seqs=2 * max_batch + 2, kv_heads=model.local_kv_heads)
+        cache = HybridCache(cfg, num_pages, device, max_seqs=2 * max_batch + 2, kv_heads=model.local_kv_heads,
+                            tp_size=tp_size)
         return Engine(cfg, model, cache, device, max_batch=max_batch, use_cuda_graphs=use_cuda_graphs, tp=tp)
     if cfg.family == "moe":
         from ..models.moe import MoeModel, init_random_moe_weights

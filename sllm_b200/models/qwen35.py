@@ -53,7 +53,25 @@ class Qwen35Weights:
     vocab_offset: int = 0
 
 
-def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: float = 0.02) -> Qwen35Weights:
+def _head_rows(w: torch.Tensor, segments: list, tp_size: int, tp_rank: int) -> torch.Tensor:
+    """Row shard of a weight whose rows are consecutive segments of (heads, rows per head): every segment gives the
+    rank its contiguous share of heads."""
+    if tp_size == 1:
+        return w
+    out, r0 = [], 0
+    for heads, per in segments:
+        if heads % tp_size:
+            raise ValueError(f"{heads} heads do not divide over {tp_size} tensor-parallel ranks")
+        loc = heads // tp_size
+        out.append(w[r0 + tp_rank * loc * per:r0 + (tp_rank + 1) * loc * per])
+        r0 += heads * per
+    return torch.cat(out, dim=0)
+
+
+def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: float = 0.02, tp_size: int = 1,
+                               tp_rank: int = 0) -> Qwen35Weights:
+    """Every rank draws the full tensors from the same generator and keeps its shard: attention and gated-delta-net
+    layers are sharded by head, the MLP by intermediate channel; norms, embedding and output matrix are replicated."""
     device = torch.device(device)
     gen = torch.Generator(device="cpu")
     gen.manual_seed(seed)
@@ -71,23 +89,37 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
     def vec(v, dtype=None):
         return v.to(dtype or dt).contiguous().to(device)
 
+    def rows(w, segments):
+        return _head_rows(w, segments, tp_size, tp_rank)
+
+    def cols(w, segments):
+        return _head_rows(w.t(), segments, tp_size, tp_rank).t()
+
+    f = cfg.ffn
     layers = []
     for i in range(cfg.n_layers):
-        common = dict(in_norm=vec(rnd((d,), 0.05)), mlp_norm=vec(rnd((d,), 0.05)), gate_up=lin(rnd((2 * cfg.ffn, d))),
-                      down=lin(rnd((d, cfg.ffn))))
+        common = dict(in_norm=vec(rnd((d,), 0.05)), mlp_norm=vec(rnd((d,), 0.05)),
+                      gate_up=lin(rows(rnd((2 * f, d)), [(f, 1), (f, 1)])), down=lin(cols(rnd((d, f)), [(f, 1)])))
         if (i + 1) % cfg.full_attention_interval == 0:
-            layers.append(Qwen35Layer("full", qkv=lin(rnd((cfg.q_size + 2 * cfg.kv_size, d))),
-                                      gate=lin(rnd((cfg.q_size, d))) if cfg.attn_output_gate else None,
-                                      o=lin(rnd((d, cfg.q_size))), q_norm=vec(rnd((hd,), 0.05), torch.bfloat16 if dt != torch.float32 else dt),
+            hq, hkv = cfg.n_heads, cfg.n_kv_heads
+            qkv = rows(rnd((cfg.q_size + 2 * cfg.kv_size, d)), [(hq, hd), (hkv, hd), (hkv, hd)])
+            gate = rows(rnd((cfg.q_size, d)), [(hq, hd)]) if cfg.attn_output_gate else None
+            layers.append(Qwen35Layer("full", qkv=lin(qkv), gate=lin(gate) if gate is not None else None,
+                                      o=lin(cols(rnd((d, cfg.q_size)), [(hq, hd)])),
+                                      q_norm=vec(rnd((hd,), 0.05), torch.bfloat16 if dt != torch.float32 else dt),
                                       k_norm=vec(rnd((hd,), 0.05), torch.bfloat16 if dt != torch.float32 else dt), **common))
         else:
             n_in = width + vh * ghd + 2 * vh
-            n_in_pad = (n_in + 7) // 8 * 8
-            w_in = torch.zeros((n_in_pad, d))
-            w_in[:n_in] = rnd((n_in, d))
-            layers.append(Qwen35Layer("gdn", in_proj=lin(w_in), conv_w=vec(rnd((width, cfg.gdn_conv_kernel), 0.3)),
-                                      a_log=vec(rnd((vh,), 0.5), torch.float32), dt_bias=vec(rnd((vh,), 0.5)),
-                                      out_norm=vec(1.0 + rnd((ghd,), 0.05), torch.float32), out_proj=lin(rnd((d, vh * ghd))), **common))
+            segs = [(qh, ghd), (qh, ghd), (vh, ghd), (vh, ghd), (vh, 1), (vh, 1)]
+            w_loc = rows(rnd((n_in, d)), segs)
+            w_in = torch.zeros(((w_loc.shape[0] + 7) // 8 * 8, d))
+            w_in[:w_loc.shape[0]] = w_loc
+            conv = rows(rnd((width, cfg.gdn_conv_kernel), 0.3), segs[:3])
+            layers.append(Qwen35Layer("gdn", in_proj=lin(w_in), conv_w=vec(conv),
+                                      a_log=vec(rows(rnd((vh,), 0.5), [(vh, 1)]), torch.float32),
+                                      dt_bias=vec(rows(rnd((vh,), 0.5), [(vh, 1)])),
+                                      out_norm=vec(1.0 + rnd((ghd,), 0.05), torch.float32),
+                                      out_proj=lin(cols(rnd((d, vh * ghd)), [(vh, ghd)])), **common))
     embed = rnd((cfg.vocab, d)).to(dt).to(device)
     head = embed if cfg.tie_embeddings else rnd((cfg.vocab, d)).to(dt).contiguous().to(device)
     return Qwen35Weights(embed, layers, vec(rnd((d,), 0.05)), LinearWeight("dense", head), 0)
@@ -97,9 +129,14 @@ class Qwen35Model:
     def __init__(self, cfg: ModelConfig, weights: Qwen35Weights, tp=None):
         self.cfg, self.w = cfg, weights
         self.tp = tp or NoTP()
-        if self.tp.size != 1:
-            raise ValueError("the hybrid family runs without tensor parallelism in this build")
-        self.hq, self.hkv = cfg.n_heads, cfg.n_kv_heads
+        n = self.tp.size
+        for name, v in (("n_heads", cfg.n_heads), ("n_kv_heads", cfg.n_kv_heads), ("gdn_heads", cfg.gdn_heads),
+                        ("gdn_qk_heads", cfg.gdn_qk_heads), ("ffn", cfg.ffn)):
+            if v % n:
+                raise ValueError(f"{name} = {v} does not divide over {n} tensor-parallel ranks")
+        # heads of this rank (attention and gated-delta-net layers are sharded by head)
+        self.hq, self.hkv = cfg.n_heads // n, cfg.n_kv_heads // n
+        self.vh, self.qh = cfg.gdn_heads // n, cfg.gdn_qk_heads // n
 
     @property
     def local_kv_heads(self) -> int:
@@ -108,11 +145,11 @@ class Qwen35Model:
     def _mlp(self, h, lw):
         cfg = self.cfg
         x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
-        return ops.linear(ops.gated_act(ops.linear(x, lw.gate_up), cfg.act), lw.down, h)
+        return self.tp.row_linear(ops.gated_act(ops.linear(x, lw.gate_up), cfg.act), lw.down, h)
 
     def hidden(self, b: ForwardBatch, cache) -> torch.Tensor:
         cfg, w = self.cfg, self.w
-        hd, ghd, vh, qh = cfg.head_dim, cfg.gdn_head_dim, cfg.gdn_heads, cfg.gdn_qk_heads
+        hd, ghd, vh, qh = cfg.head_dim, cfg.gdn_head_dim, self.vh, self.qh
         width = (2 * qh + vh) * ghd
         if b.row_off is None or b.slots is None:
             raise ValueError("the hybrid family needs row offsets and state slots in the batch")
@@ -128,7 +165,7 @@ class Qwen35Model:
                 a = ops.paged_attention(q, kv, b.block_table, b.seq_index, b.kv_lens, self.hq, self.hkv, hd, max_kv=b.max_kv)
                 if lw.gate is not None:
                     a = ops.elementwise("sigmoid_mul", a.contiguous(), ops.linear(x, lw.gate))
-                h = ops.linear(a, lw.o, h)
+                h = self.tp.row_linear(a, lw.o, h)
             else:
                 conv_state, rec_state = cache.gdn(li)
                 p = ops.linear(x, lw.in_proj)
@@ -138,7 +175,7 @@ class Qwen35Model:
                 aa = p[:, width + vh * ghd + vh:width + vh * ghd + 2 * vh].contiguous()
                 qkv = G.conv_silu(qkv, lw.conv_w, conv_state, b.row_off, b.slots)
                 o = G.recurrent(qkv, z, bb, aa, lw.a_log, lw.dt_bias, lw.out_norm, rec_state, b.row_off, b.slots, qh, vh, ghd)
-                h = ops.linear(o, lw.out_proj, h)
+                h = self.tp.row_linear(o, lw.out_proj, h)
             h = self._mlp(h, lw)
         return h
 

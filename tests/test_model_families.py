@@ -61,3 +61,15 @@ def test_gemma_style_options():
     assert not torch.allclose(e2.prefill([s], sample=False), lg, atol=1e-3)
     assert MC.NAMED["gemma4"]().window_layers[:6] == [True] * 5 + [False]
     assert MC.NAMED["qwen35-hybrid"]().full_attention_interval == 4
+
+
+def test_hybrid_family_tensor_parallel_cpu():
+    """Two gloo ranks with sharded heads reproduce the single-rank hybrid model."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29843", os.path.join(here, "hybrid_tp_worker.py")]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0 and "HYBRID_TP_OK" in proc.stdout, proc.stdout[-2000:] + proc.stderr[-3000:]
