@@ -176,8 +176,6 @@ def test_text_only_through_the_multimodal_entry_is_unchanged():
 def test_multimodal_prefill_then_decode_matches_one_shot_gpu():
     a, b = _multimodal_logits("cuda")
     assert _rel(b, a) < 3e-2
-    cpu_a, _ = _multimodal_logits("cpu")
-    assert a.argmax(-1).tolist() == a.argmax(-1).tolist()
 
 
 @pytest.mark.gpu
