@@ -90,9 +90,11 @@ class LeaderEngine:
     def _sync_tokens(self, seqs):
         return [(self._h(s), list(s.tokens[s.num_computed:])) for s in seqs]
 
-    def prefill(self, seqs, chunk_tokens: int = 0, sample: bool = True):
-        self._ch.send(("prefill", self._sync_tokens(seqs), chunk_tokens, sample))
-        return self._e.prefill(seqs, chunk_tokens, sample)
+    def prefill(self, seqs, chunk_tokens: int = 0, sample: bool = True, embeds=None, rope_pos3=None, one_chunk: bool = False):
+        if embeds is not None or rope_pos3 is not None:
+            raise ValueError("multimodal prompts are not mirrored to follower ranks")
+        self._ch.send(("prefill", self._sync_tokens(seqs), chunk_tokens, sample, one_chunk))
+        return self._e.prefill(seqs, chunk_tokens, sample, one_chunk=one_chunk)
 
     def decode(self, seqs, sample: bool = True):
         self._ch.send(("decode", [(self._h(s), s.tokens[-1]) for s in seqs], sample))
@@ -146,7 +148,7 @@ def follow(engine: Engine, control_group=None) -> int:
                 s.tokens.extend(new_tokens)
                 batch.append(s)
             if op == "prefill":
-                engine.prefill(batch, cmd[2], cmd[3])
+                engine.prefill(batch, cmd[2], cmd[3], one_chunk=cmd[4])
             else:
                 engine.extend(batch, cmd[2])
         elif op == "decode":

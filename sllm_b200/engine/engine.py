@@ -191,11 +191,14 @@ class Engine:
 
     # ------------------------------------------------------------------ prefill
     def prefill(self, seqs: list, chunk_tokens: int = 0, sample: bool = True, embeds: Optional[torch.Tensor] = None,
-                rope_pos3: Optional[torch.Tensor] = None):
+                rope_pos3: Optional[torch.Tensor] = None, one_chunk: bool = False):
         """Runs the not-yet-computed prompt tokens of ``seqs``; returns greedy next tokens (list[int])
         or, with sample=False, the last-row logits [len(seqs), vocab].  A multimodal prompt passes ``embeds``
         ([T, d], the uncomputed tokens of all sequences in order, visual rows spliced in) and ``rope_pos3`` (int32
-        [3, T]); it runs as one chunk and leaves each sequence's ``rope_delta`` for the decode steps."""
+        [3, T]); it runs as one chunk and leaves each sequence's ``rope_delta`` for the decode steps.
+        With ``one_chunk`` only the first ``chunk_tokens`` uncomputed tokens of every sequence run; a sequence is done
+        when ``num_computed == len(tokens)`` afterwards, and only then is its row of the result meaningful (a
+        scheduler interleaves the chunks of a long prompt with decode steps of the running requests)."""
         if embeds is not None or rope_pos3 is not None:
             if chunk_tokens:
                 raise ValueError("a multimodal prefill runs as one chunk")
@@ -245,14 +248,16 @@ class Engine:
             out[torch.tensor(rows, device=res.device)] = res
             for j, i in enumerate(rows):
                 starts[i] += len(parts[j])
+            if one_chunk and chunk_tokens > 0:
+                break
         if sample:
             toks = out.tolist()
             self.d2h_bytes += 4 * len(seqs)
         self._table_key = None
         self._check_status(every=1)
         for i, s in enumerate(seqs):
-            pool.commit(s.seq_id, len(s.tokens))
-            s.num_computed = len(s.tokens)
+            pool.commit(s.seq_id, starts[i])
+            s.num_computed = starts[i]
         return toks if sample else out
 
     def extend(self, seqs: list, sample: bool = True, embeds: Optional[torch.Tensor] = None):

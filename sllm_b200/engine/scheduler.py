@@ -115,7 +115,8 @@ class BatchPlanner:
     def next_round(self) -> Optional[Round]:
         if self.in_flight is not None:
             raise PlannerError("a round is already in flight")
-        want_prefill = bool(self.waiting) and (not self.ready or self.decode_rounds_since_prefill >= self.prefill_interval)
+        interval = 1 if getattr(self, "partial_prefill", False) else self.prefill_interval
+        want_prefill = bool(self.waiting) and (not self.ready or self.decode_rounds_since_prefill >= interval)
         active = sum(1 for e in self.entries.values() if e.phase in (DECODE_READY, BACKPRESSURED))
         if want_prefill and active < self.max_batch:
             first = self.entries[self.waiting[0]]
@@ -132,6 +133,7 @@ class BatchPlanner:
                 self.waiting.remove(rid)
                 self.entries[rid].phase = PREFILL_IN_FLIGHT
             self.decode_rounds_since_prefill = 0
+            self.partial_prefill = False
             self.in_flight = Round("prefill", rows)
             return self.in_flight
         if self.ready:
@@ -174,6 +176,12 @@ class BatchPlanner:
                 cancelled.append(rid)
             elif o == "backpressured":
                 e.phase = BACKPRESSURED
+            elif o == "prefill_more":
+                # a long prompt ran one chunk: it goes back to the head of the waiting queue and its next chunk
+                # follows after one decode round of the running requests
+                e.phase = QUEUED
+                self.waiting.insert(0, rid)
+                self.partial_prefill = True
             elif o == "continue":
                 e.phase = DECODE_READY
                 self.ready.append(rid)       # round robin: back of the queue
@@ -384,6 +392,9 @@ class EngineLoop:
             if kind == "prefill":
                 live = []
                 for r in reqs:
+                    if r.seq is not None:            # a later chunk of a prompt that is already under way
+                        live.append(r)
+                        continue
                     try:
                         if r.prefix_seq is not None:
                             try:
@@ -399,11 +410,21 @@ class EngineLoop:
                         outcomes[r.rid] = "failed"
                 plain = [r for r in live if r.mm is None]
                 if plain:
-                    logits = eng.prefill([r.seq for r in plain], self.prefill_chunk_tokens, sample=False)
-                    if self.prefix_cache is not None:
-                        for r in plain:
-                            self.prefix_cache.publish(r.seq, len(r.prompt))
-                    self._select_and_publish(plain, logits, outcomes)
+                    chunked = self.prefill_chunk_tokens > 0
+                    logits = eng.prefill([r.seq for r in plain], self.prefill_chunk_tokens, sample=False, one_chunk=chunked)
+                    done = [i for i, r in enumerate(plain) if r.seq.num_computed == len(r.seq.tokens)]
+                    for i, r in enumerate(plain):
+                        if i not in done:
+                            outcomes[r.rid] = "prefill_more"
+                    fin = [plain[i] for i in done]
+                    if fin:
+                        if self.prefix_cache is not None:
+                            for r in fin:
+                                self.prefix_cache.publish(r.seq, len(r.prompt))
+                        if len(fin) != len(plain):
+                            import torch
+                            logits = logits[torch.tensor(done, device=logits.device)]
+                        self._select_and_publish(fin, logits, outcomes)
                 for r in live:
                     if r.mm is None:
                         continue

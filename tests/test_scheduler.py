@@ -152,3 +152,52 @@ def test_prefix_fork_reuses_pages():
     for s in (s1, child, fresh):
         eng.free_sequence(s)
     assert eng.cache.pool.stats()["free"] == eng.cache.pool.stats()["pages"]
+
+
+def test_chunked_prefill_interleaves_with_decode():
+    """With a prefill chunk size a long prompt runs one chunk per prefill round, and the running request decodes
+    between the chunks; the results equal unchunked generation."""
+    eng, loop = _loop(prefill_interval=4, prefill_chunk_tokens=8)
+    g = torch.Generator().manual_seed(1)
+    short = torch.randint(0, 1024, (6,), generator=g).tolist()
+    long = torch.randint(0, 1024, (50,), generator=g).tolist()
+    try:
+        stamps = []
+        first = _collect(loop, short, 30)
+        first[0].on_token = lambda t, s, _o=first[0].on_token: (stamps.append(("short", loop.rounds["prefill"])), _o(t, s))[1]
+        while len(first[1]) < 2:                               # the short request is decoding
+            time.sleep(0.005)
+        before = loop.rounds["prefill"]
+        second = _collect(loop, long, 5)
+        assert first[2].wait(60) and second[2].wait(60)
+        ref_eng = build_engine(eng.cfg, "cpu", seed=0, max_batch=4, use_cuda_graphs=False)
+        assert first[1] == ref_eng.generate([short], 30)[0]
+        assert second[1] == ref_eng.generate([long], 5)[0]
+        # 50 tokens in chunks of 8 = 7 prefill rounds for the long prompt
+        assert loop.rounds["prefill"] - before == 7
+        # the short request produced tokens while the long prompt was still being prefilled
+        during = {n for who, n in stamps if before < n < before + 7}
+        assert len(during) >= 3
+        assert eng.cache.pool.stats()["sequences"] == 0
+    finally:
+        loop.shutdown(1.0)
+
+
+def test_planner_prefill_more_goes_back_to_the_head():
+    p = sch.BatchPlanner(max_batch=4, prefill_interval=4)
+    p.submit(1, "m")
+    assert p.next_round().kind == "prefill"
+    p.complete_round({1: "continue"})
+    p.submit(2, "m")
+    p.submit(3, "m")
+    for _ in range(4):
+        assert p.next_round().kind == "decode"
+        p.complete_round({1: "continue"})
+    r = p.next_round()
+    assert r.kind == "prefill" and r.rows == [2, 3]
+    p.complete_round({2: "prefill_more", 3: "continue"})
+    assert p.next_round().kind == "decode"                    # one decode round, then the next chunk
+    p.complete_round({1: "continue", 3: "continue"})
+    r = p.next_round()
+    assert r.kind == "prefill" and r.rows == [2]
+    p.complete_round({2: "continue"})
