@@ -65,7 +65,6 @@ def main(argv=None) -> int:
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from .. import ops
-    from ..ops import moe as M
     from ..ops.core import LinearWeight
     from ..parallel.ep import FusedEP, NcclEP
     from ..parallel.gather import GatherGemm, NcclGatherGemm
