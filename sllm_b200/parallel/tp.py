@@ -197,6 +197,11 @@ def make_tp(size: int, rank: int, device, impl: str = "fused", max_tokens: int =
             group=None):
     if size == 1:
         return None
+    if torch.device(device).type == "cuda":
+        # the kernel after decode attention is a GEMM fused with a collective here: measured 10 % slower at two GPUs
+        # when its CTAs become resident while the attention grid still drains
+        _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_attention_set_early_trigger", (None, [C.c_int]))
+        _lib.kernels().sllm_attention_set_early_trigger(0)
     if impl == "fused":
         return FusedTP(size, rank, device, max_tokens, d_model, group)
     return NcclTP(size, rank, device, group)
