@@ -59,7 +59,7 @@ async def _one(session, url, model, prompt, max_tokens, headers, out):
     except Exception as exc:      # connection errors count as failed requests
         err = type(exc).__name__
     out.append({"ttft": None if first is None else first - t0, "gaps": gaps, "usage": usage, "error": err,
-                "total": time.perf_counter() - t0})
+                "total": time.perf_counter() - t0, "stream": None if first is None or last is None else last - first})
 
 
 async def run(a) -> dict:
@@ -91,6 +91,10 @@ async def run(a) -> dict:
     ok = [r for r in results if r["error"] is None]          # a reply without visible text still completed
     ttft = [r["ttft"] for r in ok if r["ttft"] is not None]
     gaps = [g for r in ok for g in r["gaps"]]
+    # time per output token of a request: its streaming time over its tokens after the first (a chunk may carry
+    # several tokens when the server coalesces a backlog, so this does not depend on chunking)
+    tpot = [r["stream"] / (r["usage"]["completion_tokens"] - 1) for r in ok
+            if r.get("stream") and r["usage"] and r["usage"].get("completion_tokens", 0) > 1]
     out_tokens = sum((r["usage"] or {}).get("completion_tokens", len(r["gaps"]) + 1) for r in ok)
     in_tokens = sum((r["usage"] or {}).get("prompt_tokens", 0) for r in ok)
     return {"requests": a.requests, "completed": len(ok), "failed": len(results) - len(ok), "wall_s": round(wall, 3),
@@ -98,6 +102,7 @@ async def run(a) -> dict:
             "output_tokens": out_tokens, "prompt_tokens": in_tokens, "output_tok_per_s": round(out_tokens / wall, 2) if wall > 0 else None,
             "ttft_ms": {"p50": None if not ttft else round(statistics.median(ttft) * 1e3, 2), "p99": None if not ttft else round(_pct(ttft, 99) * 1e3, 2)},
             "itl_ms": {"p50": None if not gaps else round(statistics.median(gaps) * 1e3, 3), "p99": None if not gaps else round(_pct(gaps, 99) * 1e3, 3)},
+            "tpot_ms": {"p50": None if not tpot else round(statistics.median(tpot) * 1e3, 3), "p99": None if not tpot else round(_pct(tpot, 99) * 1e3, 3)},
             "errors": sorted({r["error"] for r in results if r["error"]})}
 
 
