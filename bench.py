@@ -106,7 +106,7 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference",
         "unavailable": "reference is Rust + HIP for AMD gfx1030/gfx1201/gfx942 only (no CUDA path, no cargo/hipcc "
-                       "here); `pip install /root/reference` fails at metadata generation (test-contract package "
+                       "here); installing the reference with pip fails at metadata generation (test-contract package "
                        "with no importable modules)"}))
     return 0
 

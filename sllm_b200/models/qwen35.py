@@ -4,7 +4,7 @@ Full-attention layer: RMSNorm(1 + w) -> q | k | v (+ gate) projections -> per-he
 the first `rotary_dim` channels -> paged causal attention -> sigmoid(gate) * attention -> o projection.
 GDN layer: RMSNorm -> in-projection to (q | k | v), z, b, a -> causal depthwise conv + SiLU on q|k|v with a rolling
 state -> gated delta-rule recurrence fused with the output RMSNorm and SiLU(z) -> out projection.  Both are
-followed by a SwiGLU MLP.  (Reference layer recipe: SURVEY call stack crates/sllm-core/src/qwen_graph.rs
+followed by a SwiGLU MLP.  (Reference layer recipe: crates/sllm-core/src/qwen_graph.rs
 `linear.{qkv,z,b,a}_matmul -> linear_attention_state -> linear.out_matmul`; kernels K16, K27, K28.)
 """
 from __future__ import annotations
