@@ -43,9 +43,9 @@ class NcclGatherGemm:
 
     def linear(self, x_shard: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         rows, ks = x_shard.shape
-        parts = torch.empty((self.size, rows, ks), dtype=x_shard.dtype, device=x_shard.device)
-        dist.all_gather_into_tensor(parts, x_shard.contiguous(), group=self.group)
-        x = parts.permute(1, 0, 2).reshape(rows, self.size * ks).contiguous()
+        flat = torch.empty((self.size * rows, ks), dtype=x_shard.dtype, device=x_shard.device)
+        dist.all_gather_into_tensor(flat, x_shard.contiguous(), group=self.group)
+        x = flat.view(self.size, rows, ks).permute(1, 0, 2).reshape(rows, self.size * ks).contiguous()
         return ops.linear(x, w, residual)
 
     def close(self) -> None:

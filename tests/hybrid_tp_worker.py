@@ -34,6 +34,16 @@ def main():
     assert err < 2e-3, err      # partial products are rounded before the cross-rank sum
     got_tokens = build_engine(cfg, "cpu", seed=2, max_batch=4, use_cuda_graphs=False, tp=tp).generate(prompts, 8)
     assert got_tokens == want_tokens, (got_tokens, want_tokens)
+    # the all-gather + column-parallel GEMM op on its host path (tiny shapes, fp32): K shards of every rank times
+    # this rank's weight rows equal the full product
+    from sllm_b200.ops.core import LinearWeight
+    from sllm_b200.parallel.gather import NcclGatherGemm
+    gen = torch.Generator().manual_seed(11)
+    x = torch.randn(5, 64 * world, generator=gen)
+    w_loc = torch.randn(24, 64 * world, generator=torch.Generator().manual_seed(20 + rank))
+    res = torch.randn(5, 24, generator=gen)
+    got = NcclGatherGemm(world, rank, "cpu").linear(x[:, rank * 64:(rank + 1) * 64], LinearWeight("dense", w_loc), res)
+    assert torch.allclose(got, x @ w_loc.t() + res, atol=1e-4), (got - (x @ w_loc.t() + res)).abs().max()
     dist.barrier()
     if rank == 0:
         print("HYBRID_TP_OK", flush=True)
