@@ -36,6 +36,7 @@ enum SllmDeviceStatus : int {
   SLLM_DEV_TIMEOUT_TMEM_EMPTY = 104,
   SLLM_DEV_TIMEOUT_PEER_FLAG = 105,
   SLLM_DEV_TIMEOUT_DRAIN = 106,
+  SLLM_DEV_TIMEOUT_GRID_BARRIER = 107,
 };
 
 namespace sllm {

@@ -1,0 +1,915 @@
+// Fused decode kernel: the weight-streaming GEMMs of a decoder layer as phases of ONE persistent kernel.
+//
+// Decode at small batch is bound by streaming the weights once per step.  A chain of separate GEMM kernels
+// stalls HBM at every kernel boundary (prologue, first TMA round trip, epilogue, grid drain), which costs more
+// than the transfer itself for the smaller projections.  Here one CTA per SM stays resident across up to four
+// dependent GEMMs; because weights do not depend on activations, the TMA producer of every CTA keeps
+// streaming the NEXT phase's weight tiles into its shared-memory ring while the current phase finishes and the
+// grid barrier between phases resolves, so the HBM pipe never drains inside a launch.
+//
+// Work decomposition ("stream-K"): a phase is tiles x K-blocks units of 128 weight rows x 128 K bytes; CTA c
+// owns the contiguous unit range [c U / G, (c + 1) U / G), i.e. every SM streams the same number of bytes
+// whatever the shape.  A tile whose K range is split over several CTAs is finished by the CTA that arrives
+// last (partials in a workspace, summed in a fixed order, so results do not depend on arrival order).
+//
+// Roles (256 threads): warp 0 weight producer (TMA, never waits for a grid barrier), warp 1 activation producer
+// (TMA, waits for the barrier that publishes the phase's input), warps 2-3 MMA issuers (tcgen05.mma
+// kind::f8f6f4, one K block per TMEM accumulator; each issuer has its own rings and accumulators), warps 4-7
+// epilogue (promotion of every K block with scaleA * scaleB into fp32 registers, then the fused tile epilogue).
+//
+// Epilogues fold what used to be separate kernels into the GEMM that produces their input: residual add,
+// RMSNorm statistics, FP8 1x128 quantisation of the next operand, SiLU*up, RoPE and the quantising KV-page
+// append.  RMSNorm itself never runs: its weight vector is folded into the next weight matrix at load and
+// its per-row factor rsqrt(mean(h^2) + eps) is applied to the accumulators of the next phase.
+//
+// Waits (mbarrier, grid barrier, peer flag) are bounded; a wait that gives up records a status code, and the
+// CTA runs to its normal teardown.
+//
+// Replaces, for decode, the reference's per-op layer sequence (crates/sllm-core/src/qwen_graph.rs:2524-3501:
+// rmsnorm, matmul, rotary + KV append, silu-mul, residual add as separate kernels).
+#include "common.cuh"
+#include "api.h"
+#include "decode_fused.h"
+#include <cstddef>
+#include <cstring>
+
+namespace sllm {
+
+int cached_kmajor_tmap(CUtensorMap* out, const void* ptr, int elem_bytes, long long rows, long long k_elems,
+                       long long row_stride_bytes, int box_rows);
+
+constexpr int kFdThreads = 256;
+constexpr int kFdASlots = 5;                       // weight-ring slots per issuer
+constexpr int kFdBSlots = 3;                       // activation-ring slots per issuer
+constexpr int kFdATile = 128 * 128;                // 128 weight rows x 128 K bytes
+constexpr int kFdASlotBytes = kFdATile + 1024;     // + 128 fp32 row scales, padded to the swizzle alignment
+constexpr int kFdMaxWorld = 8;
+constexpr float kFdE4M3Max = 448.f;
+constexpr unsigned long long kFdSyncQuantum = 4096;   // grid-barrier arrivals per launch (>= phases x CTAs)
+
+template <int BN> constexpr int fd_b_tile() { return BN * 128; }
+template <int BN> constexpr int fd_b_slot() { return BN * 128 + 1024; }
+
+struct FdComm {
+  int world, rank;
+  long long cap_elems;
+  __nv_bfloat16* recv[kFdMaxWorld];
+  uint32_t* flags[kFdMaxWorld];
+  uint32_t* epoch;
+};
+
+struct FdMaps {
+  CUtensorMap a[SLLM_FD_MAX_PHASES];
+  CUtensorMap b[SLLM_FD_MAX_PHASES];
+};
+
+struct FdParams {
+  int n_phases, rows;
+  SllmFdPhase ph[SLLM_FD_MAX_PHASES];
+  SllmFdRope rope;
+  float* ws;
+  int* counters;
+  unsigned long long* sync;
+  int* status;
+  long long wait_limit;
+  FdComm comm;
+};
+
+struct __align__(16) FdShared {
+  uint64_t afull[2][kFdASlots], aempty[2][kFdASlots];
+  uint64_t bfull[2][kFdBSlots], bempty[2][kFdBSlots];
+  uint64_t tfull[4], tempty[4];
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+  uint32_t epoch;
+  float rnorm[32];
+  float inv_freq[64];
+};
+
+__device__ __forceinline__ float fd_silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float fd_gelu_tanh(float x) {
+  const float c = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tanhf(c * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float fd_bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ unsigned long long fd_ld_acquire_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fd_red_release_add_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void fd_st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t fd_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// 1-D bulk copy global -> shared completing on an mbarrier; both addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void fd_bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void fd_fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded wait until the grid-barrier counter reaches `target`.
+__device__ __forceinline__ bool fd_grid_wait(const unsigned long long* ctr, unsigned long long target,
+                                             volatile int* abort_flag, int* status, long long limit) {
+  uint32_t spins = 0;
+  long long t0 = 0;
+  while (fd_ld_acquire_u64(ctr) < target) {
+    ++spins;
+    if (spins == 64) t0 = clock64();
+    if (spins > 64 && (spins & 15) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > limit) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, SLLM_DEV_TIMEOUT_GRID_BARRIER);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Barrier 1 over the 128 epilogue threads that also ORs a predicate, so that every thread takes the same branch
+// on a flag another role may set at any moment.
+__device__ __forceinline__ bool fd_epi_any(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
+
+// CTA that owns unit u when U units are dealt to G CTAs as [c U / G, (c + 1) U / G).
+__device__ __forceinline__ int fd_cta_of_unit(long long u, long long U, int G) {
+  return static_cast<int>(((u + 1) * G - 1) / U);
+}
+
+struct FdPhaseGeom {
+  int tiles, nkb, dual;
+  long long U, u0, u1;
+};
+__device__ __forceinline__ FdPhaseGeom fd_geom(const SllmFdPhase& ph, int cta, int G) {
+  FdPhaseGeom g;
+  g.tiles = (ph.n + 127) >> 7;
+  g.nkb = ph.k >> 7;
+  g.dual = ph.dual_off > 0 ? 1 : 0;
+  g.U = static_cast<long long>(g.tiles) * g.nkb;
+  g.u0 = cta * g.U / G;
+  g.u1 = (cta + 1) * g.U / G;
+  return g;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kFdThreads, 1)
+fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__ FdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kBSlot = fd_b_slot<BN>();
+  constexpr int kBTile = fd_b_tile<BN>();
+  constexpr uint32_t kTmemCols = 8 * BN;            // 4 accumulators x (gate, up) x BN columns
+  uint8_t* a_ring = smem;                                         // [2][kFdASlots][kFdASlotBytes]
+  uint8_t* b_ring = a_ring + 2 * kFdASlots * kFdASlotBytes;       // [2][kFdBSlots][kBSlot]
+  float* stage = reinterpret_cast<float*>(b_ring + 2 * kFdBSlots * kBSlot);   // [BN][128]
+  FdShared* sh = reinterpret_cast<FdShared*>(stage + BN * 128);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int cta = blockIdx.x;
+  const int G = gridDim.x;
+  volatile int* abort_flag = &sh->abort_flag;
+  const long long limit = p.wait_limit;
+
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < 2; ++r) {
+      for (int s = 0; s < kFdASlots; ++s) { mbar_init(&sh->afull[r][s], 1); mbar_init(&sh->aempty[r][s], 4); }
+      for (int s = 0; s < kFdBSlots; ++s) { mbar_init(&sh->bfull[r][s], 1); mbar_init(&sh->bempty[r][s], 4); }
+    }
+    for (int a = 0; a < 4; ++a) { mbar_init(&sh->tfull[a], 1); mbar_init(&sh->tempty[a], 4); }
+    sh->abort_flag = 0;
+    sh->is_last = 0;
+    mbar_fence_init();
+    for (int i = 0; i < p.n_phases; ++i) { tma_prefetch_desc(&maps.a[i]); tma_prefetch_desc(&maps.b[i]); }
+  }
+  if (warp == 2) {
+    tmem_alloc(&sh->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  if (threadIdx.x >= 128 && threadIdx.x < 192) {
+    const int fi = threadIdx.x - 128;
+    const int rd = p.rope.rotary_dim > 0 ? p.rope.rotary_dim : 128;
+    sh->inv_freq[fi] = p.rope.inv_freq ? (fi < rd / 2 ? p.rope.inv_freq[fi] : 0.f)
+                                       : powf(p.rope.theta > 0.f ? p.rope.theta : 10000.f, -2.f * fi / rd);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ weight producer
+    if (lane == 0) {
+      uint32_t apos[2] = {0u, 0u};
+      uint32_t n = 0;
+      bool ok = true;
+      for (int pi = 0; pi < p.n_phases && ok; ++pi) {
+        const SllmFdPhase& ph = p.ph[pi];
+        const FdPhaseGeom g = fd_geom(ph, cta, G);
+        const int w_rows = ph.dual_off + ph.n;
+        int tile = static_cast<int>(g.u0 / g.nkb), kb = static_cast<int>(g.u0 % g.nkb);
+        for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
+          const int r = n & 1;
+          for (int half = 0; half <= g.dual; ++half) {
+            const uint32_t slot = apos[r] % kFdASlots, fill = apos[r] / kFdASlots;
+            if (!mbar_wait(&sh->aempty[r][slot], (fill & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY, limit)) {
+              ok = false;
+              break;
+            }
+            uint8_t* dst = a_ring + (r * kFdASlots + slot) * kFdASlotBytes;
+            const int row0 = tile * 128 + half * ph.dual_off;
+            int srows = w_rows - row0;
+            if (srows > 128) srows = 128;
+            mbar_expect_tx(&sh->afull[r][slot], kFdATile + srows * 4);
+            tma_load_2d(dst, &maps.a[pi], &sh->afull[r][slot], kb * 128, row0);
+            fd_bulk_load(dst + kFdATile, ph.w_scale + static_cast<size_t>(kb) * ph.ld_sa + row0, srows * 4,
+                         &sh->afull[r][slot]);
+            ++apos[r];
+          }
+          if (++kb == g.nkb) { kb = 0; ++tile; }
+        }
+      }
+      pdl_trigger();
+      // Drain: every copy this thread started must have landed before the CTA may exit (on the normal path
+      // all of them have been consumed already and the waits return at once).
+      for (int r = 0; r < 2; ++r)
+        for (int s = 0; s < kFdASlots; ++s) {
+          const uint32_t fills = apos[r] > static_cast<uint32_t>(s) ? (apos[r] - s + kFdASlots - 1) / kFdASlots : 0u;
+          if (fills > 0) {
+            int dummy = 0;
+            mbar_wait(&sh->afull[r][s], (fills - 1) & 1, &dummy, p.status, SLLM_DEV_TIMEOUT_DRAIN, 200000000LL);
+          }
+        }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ activation producer
+    if (lane == 0) {
+      uint32_t bpos[2] = {0u, 0u};
+      uint32_t n = 0;
+      bool ok = true;
+      unsigned long long base = 0;
+      for (int pi = 0; pi < p.n_phases && ok; ++pi) {
+        const SllmFdPhase& ph = p.ph[pi];
+        const FdPhaseGeom g = fd_geom(ph, cta, G);
+        if (pi == 0) {
+          pdl_wait();
+          base = fd_ld_acquire_u64(p.sync) / kFdSyncQuantum * kFdSyncQuantum;
+        } else if (!fd_grid_wait(p.sync, base + static_cast<unsigned long long>(pi) * G, abort_flag, p.status, limit)) {
+          ok = false;
+          break;
+        }
+        fd_fence_proxy_async();
+        int kb = static_cast<int>(g.u0 % g.nkb);
+        for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
+          const int r = n & 1;
+          const uint32_t slot = bpos[r] % kFdBSlots, fill = bpos[r] / kFdBSlots;
+          if (!mbar_wait(&sh->bempty[r][slot], (fill & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY, limit)) {
+            ok = false;
+            break;
+          }
+          uint8_t* dst = b_ring + (r * kFdBSlots + slot) * kBSlot;
+          mbar_expect_tx(&sh->bfull[r][slot], kBTile + BN * 4);
+          tma_load_2d(dst, &maps.b[pi], &sh->bfull[r][slot], kb * 128, 0);
+          fd_bulk_load(dst + kBTile, ph.x_scale + static_cast<size_t>(kb) * ph.ld_sb, BN * 4, &sh->bfull[r][slot]);
+          ++bpos[r];
+          if (++kb == g.nkb) kb = 0;
+        }
+      }
+      for (int r = 0; r < 2; ++r)
+        for (int s = 0; s < kFdBSlots; ++s) {
+          const uint32_t fills = bpos[r] > static_cast<uint32_t>(s) ? (bpos[r] - s + kFdBSlots - 1) / kFdBSlots : 0u;
+          if (fills > 0) {
+            int dummy = 0;
+            mbar_wait(&sh->bfull[r][s], (fills - 1) & 1, &dummy, p.status, SLLM_DEV_TIMEOUT_DRAIN, 200000000LL);
+          }
+        }
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ MMA issuers
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(kFmtE4M3, 128, BN);
+      const int iw = warp - 2;
+      uint32_t apos = 0, bpos = 0, mine = 0, n = 0;
+      bool ok = true;
+      for (int pi = 0; pi < p.n_phases && ok; ++pi) {
+        const FdPhaseGeom g = fd_geom(p.ph[pi], cta, G);
+        for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
+          if (static_cast<int>(n & 1) != iw) continue;
+          const int acc = iw * 2 + (mine & 1);
+          const uint32_t use = mine >> 1;
+          const uint32_t bslot = bpos % kFdBSlots, bfill = bpos / kFdBSlots;
+          uint32_t aslot[2];
+          for (int half = 0; half <= g.dual && ok; ++half) {
+            aslot[half] = (apos + half) % kFdASlots;
+            const uint32_t afill = (apos + half) / kFdASlots;
+            ok = mbar_wait(&sh->afull[iw][aslot[half]], afill & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL, limit);
+          }
+          if (ok) ok = mbar_wait(&sh->bfull[iw][bslot], bfill & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL, limit);
+          if (ok) ok = mbar_wait(&sh->tempty[acc], (use & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_EMPTY, limit);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(b_ring + (iw * kFdBSlots + bslot) * kBSlot));
+          for (int half = 0; half <= g.dual; ++half) {
+            const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + (iw * kFdASlots + aslot[half]) * kFdASlotBytes));
+            const uint32_t d = tmem_base + acc * (2 * BN) + half * BN;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0);
+          }
+          tc_commit(&sh->tfull[acc]);
+          apos += 1 + g.dual;
+          ++bpos;
+          ++mine;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (128 threads)
+    const int ew = warp - 4;                 // TMEM lane quarter
+    const int row = ew * 32 + lane;          // row of the weight tile
+    const int et = threadIdx.x - 128;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
+    const int T = p.rows;
+    uint32_t apos[2] = {0u, 0u}, bpos[2] = {0u, 0u};
+    uint32_t n = 0;
+    bool ok = true;
+    unsigned long long base = 0;
+    float acc[BN], acc2[BN];
+
+    for (int pi = 0; pi < p.n_phases; ++pi) {
+      const SllmFdPhase& ph = p.ph[pi];
+      const FdPhaseGeom g = fd_geom(ph, cta, G);
+      if (pi == 0) {
+        pdl_wait();
+        base = fd_ld_acquire_u64(p.sync) / kFdSyncQuantum * kFdSyncQuantum;
+      } else if (ok) {
+        if (et == 0) fd_grid_wait(p.sync, base + static_cast<unsigned long long>(pi) * G, abort_flag, p.status, limit);
+        if (fd_epi_any(*abort_flag != 0)) ok = false;
+      }
+      // RMSNorm factor of every token row from the per-block sums of squares of the phase's input
+      if (ph.norm_tiles > 0 && et < BN) {
+        float ss = 0.f;
+        if (et < T)
+          for (int i = 0; i < ph.norm_tiles; ++i) ss += __ldcg(ph.ssq_in + static_cast<size_t>(i) * ph.ld_s_out + et);
+        sh->rnorm[et] = rsqrtf(ss / static_cast<float>(ph.norm_dim) + ph.eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+
+      long long u = g.u0;
+      while (u < g.u1 && ok) {
+        const int tile = static_cast<int>(u / g.nkb);
+        const int kb0 = static_cast<int>(u - static_cast<long long>(tile) * g.nkb);
+        int kbe = g.nkb;
+        if (g.u1 - u < g.nkb - kb0) kbe = kb0 + static_cast<int>(g.u1 - u);
+        const bool full_tile = kb0 == 0 && kbe == g.nkb;
+        const bool seg_first = u == g.u0;
+#pragma unroll
+        for (int c = 0; c < BN; ++c) { acc[c] = 0.f; acc2[c] = 0.f; }
+        // ---- promotion: one K block per TMEM accumulator
+        for (int kb = kb0; kb < kbe; ++kb, ++n) {
+          const int iw = n & 1;
+          const uint32_t m = n >> 1;
+          const int a = iw * 2 + (m & 1);
+          const uint32_t use = m >> 1;
+          // a wait that gives up leaves the loop warp-uniformly; the CTA-wide decision follows the segment
+          if (!__all_sync(0xffffffffu, mbar_wait(&sh->tfull[a], use & 1, abort_flag, p.status,
+                                                  SLLM_DEV_TIMEOUT_TMEM_FULL, limit))) {
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t as0 = apos[iw] % kFdASlots;
+          const uint32_t bs = bpos[iw] % kFdBSlots;
+          const float* sa_p = reinterpret_cast<const float*>(a_ring + (iw * kFdASlots + as0) * kFdASlotBytes + kFdATile);
+          const float* sb_p = reinterpret_cast<const float*>(b_ring + (iw * kFdBSlots + bs) * kBSlot + kBTile);
+          const float sa = sa_p[row];
+          const uint32_t t0 = lane_addr + a * (2 * BN);
+#pragma unroll
+          for (int c = 0; c < BN / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(t0 + c * 16, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              acc[c * 16 + j] = fmaf(__uint_as_float(r[j]), sa * sb_p[c * 16 + j], acc[c * 16 + j]);
+          }
+          uint32_t as1 = 0;
+          if (g.dual) {
+            as1 = (apos[iw] + 1) % kFdASlots;
+            const float sa2 =
+                reinterpret_cast<const float*>(a_ring + (iw * kFdASlots + as1) * kFdASlotBytes + kFdATile)[row];
+#pragma unroll
+            for (int c = 0; c < BN / 16; ++c) {
+              uint32_t r[16];
+              tmem_ld16(t0 + BN + c * 16, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                acc2[c * 16 + j] = fmaf(__uint_as_float(r[j]), sa2 * sb_p[c * 16 + j], acc2[c * 16 + j]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(&sh->tempty[a]);
+            mbar_arrive(&sh->aempty[iw][as0]);
+            if (g.dual) mbar_arrive(&sh->aempty[iw][as1]);
+            mbar_arrive(&sh->bempty[iw][bs]);
+          }
+          apos[iw] += 1 + g.dual;
+          ++bpos[iw];
+        }
+        if (fd_epi_any(*abort_flag != 0)) {
+          ok = false;
+          break;
+        }
+        u += kbe - kb0;
+
+        // ---- a tile shared with other CTAs: publish the partial; the last arriver sums all parts in order
+        bool finish = true;
+        if (!full_tile) {
+          const int accs = 1 + g.dual;
+          const size_t part_floats = static_cast<size_t>(accs) * BN * 128;
+          float* my = p.ws + (static_cast<size_t>(2 * cta) + (seg_first ? 0 : 1)) * part_floats;
+#pragma unroll
+          for (int c = 0; c < BN; ++c) my[c * 128 + row] = acc[c];
+          if (g.dual) {
+#pragma unroll
+            for (int c = 0; c < BN; ++c) my[(BN + c) * 128 + row] = acc2[c];
+          }
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const long long tu0 = static_cast<long long>(tile) * g.nkb;
+          const int first_c = fd_cta_of_unit(tu0, g.U, G);
+          const int last_c = fd_cta_of_unit(tu0 + g.nkb - 1, g.U, G);
+          if (et == 0) {
+            // CTAs with an empty unit range (fewer units than CTAs) contribute no part
+            int nparts = 0;
+            for (int j = first_c; j <= last_c; ++j) nparts += ((j + 1) * g.U / G > j * g.U / G) ? 1 : 0;
+            const int old = atomicAdd(&p.counters[tile], 1);
+            const int last = old == nparts - 1;
+            if (last) p.counters[tile] = 0;
+            sh->is_last = last;
+            __threadfence();
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          finish = sh->is_last != 0;
+          if (finish) {
+#pragma unroll
+            for (int c = 0; c < BN; ++c) { acc[c] = 0.f; acc2[c] = 0.f; }
+            for (int j = first_c; j <= last_c; ++j) {
+              const long long sj = j * g.U / G;
+              if ((j + 1) * g.U / G == sj) continue;
+              const float* src = p.ws + (static_cast<size_t>(2 * j) + (sj >= tu0 ? 0 : 1)) * part_floats;
+#pragma unroll
+              for (int c = 0; c < BN; ++c) acc[c] += __ldcg(src + c * 128 + row);
+              if (g.dual) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) acc2[c] += __ldcg(src + (BN + c) * 128 + row);
+              }
+            }
+          }
+          // the flag in shared memory is rewritten by the next partial tile
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        if (!finish) continue;
+
+        // ---- tile epilogue: norm factor / activation, then staged as stage[token][row of the tile]
+        const bool has_norm = ph.norm_tiles > 0;
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
+          float v = acc[c];
+          if (has_norm) v *= sh->rnorm[c];
+          if (g.dual) {
+            const float up = acc2[c] * (has_norm ? sh->rnorm[c] : 1.f);
+            const float a = ph.act == 0 ? fd_silu(v) : fd_gelu_tanh(v);
+            v = fd_bf16r(a) * up;
+          }
+          stage[c * 128 + row] = v;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+
+        const int n0 = tile * 128 + lane * 4;     // first of this lane's four outputs of a token row
+        bool comm_ok = true;
+        if (ph.epilogue == SLLM_FD_RESID_QUANT && p.comm.world > 1) {
+          // ---- cross-rank sum of the tile: push the partial (bf16) to every rank, flag, wait, sum in rank order
+          const FdComm& cm = p.comm;
+          if (et == 0) {
+            const uint32_t e1 = cm.epoch[tile] + 1;
+            cm.epoch[tile] = e1;
+            sh->epoch = e1;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const uint32_t e = sh->epoch;
+          const long long region = static_cast<long long>(e & 1) * cm.world;
+          const long long toff = static_cast<long long>(tile) * (128 * BN);
+          for (int c = ew; c < T; c += 4) {
+            const float4 x = *reinterpret_cast<const float4*>(stage + c * 128 + lane * 4);
+            uint2 w;
+            *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(x.x, x.y);
+            *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(x.z, x.w);
+            const long long off = (region + cm.rank) * cm.cap_elems + toff + c * 128 + lane * 4;
+            for (int peer = 0; peer < cm.world; ++peer) *reinterpret_cast<uint2*>(cm.recv[peer] + off) = w;
+          }
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et < cm.world && et != cm.rank) {
+            fd_st_release_sys(cm.flags[et] + static_cast<size_t>(tile) * cm.world + cm.rank, e);
+            const uint32_t* f = cm.flags[cm.rank] + static_cast<size_t>(tile) * cm.world + et;
+            uint32_t spins = 0;
+            long long t0 = 0;
+            while (static_cast<int32_t>(fd_ld_acquire_sys(f) - e) < 0) {
+              ++spins;
+              if (spins == 1024) t0 = clock64();
+              if (spins > 1024 && (spins & 63) == 0) {
+                if (*abort_flag) break;
+                if (clock64() - t0 > limit) {
+                  *abort_flag = 1;
+                  if (p.status) atomicCAS(p.status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
+                  break;
+                }
+              }
+            }
+          }
+          if (fd_epi_any(*abort_flag != 0)) { comm_ok = false; ok = false; }
+          if (comm_ok) {
+            for (int c = ew; c < T; c += 4) {
+              float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int src = 0; src < cm.world; ++src) {
+                const uint2 w = __ldcg(reinterpret_cast<const uint2*>(
+                    cm.recv[cm.rank] + (region + src) * cm.cap_elems + toff + c * 128 + lane * 4));
+                const __nv_bfloat162 h0 = *reinterpret_cast<const __nv_bfloat162*>(&w.x);
+                const __nv_bfloat162 h1 = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
+                s.x += __bfloat162float(h0.x); s.y += __bfloat162float(h0.y);
+                s.z += __bfloat162float(h1.x); s.w += __bfloat162float(h1.y);
+              }
+              *reinterpret_cast<float4*>(stage + c * 128 + lane * 4) = s;   // same lane reads it back below
+            }
+          }
+        }
+
+        if (comm_ok) {
+          for (int c = ew; c < T; c += 4) {
+            const float4 x = *reinterpret_cast<const float4*>(stage + c * 128 + lane * 4);
+            float v[4] = {x.x, x.y, x.z, x.w};
+            if (ph.epilogue == SLLM_FD_PLAIN) {
+              __nv_bfloat16* y = static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0;
+              const __nv_bfloat16* res =
+                  ph.residual ? static_cast<const __nv_bfloat16*>(ph.residual) + static_cast<size_t>(c) * ph.ldy + n0 : nullptr;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (n0 + j < ph.n) {
+                  float o = v[j];
+                  if (res) o += __bfloat162float(res[j]);
+                  if (ph.softcap > 0.f) o = ph.softcap * tanhf(o / ph.softcap);
+                  y[j] = __float2bfloat16_rn(o);
+                }
+              }
+            } else if (ph.epilogue == SLLM_FD_RESID_QUANT || ph.epilogue == SLLM_FD_SILU_QUANT) {
+              if (ph.epilogue == SLLM_FD_RESID_QUANT) {
+                const uint2 rr = *reinterpret_cast<const uint2*>(
+                    static_cast<const __nv_bfloat16*>(ph.residual) + static_cast<size_t>(c) * ph.ldy + n0);
+                const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
+                const __nv_bfloat162 r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
+                v[0] += __bfloat162float(r0.x); v[1] += __bfloat162float(r0.y);
+                v[2] += __bfloat162float(r1.x); v[3] += __bfloat162float(r1.y);
+                uint2 hw;
+                *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
+                *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
+                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
+              }
+              float amax = 0.f, ss = 0.f;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                v[j] = fd_bf16r(v[j]);
+                ss += v[j] * v[j];
+                const float a = fabsf(v[j]);
+                if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
+              }
+              amax = warp_max(amax);
+              const float scale = amax > 0.f ? amax / kFdE4M3Max : 1.f;
+              uint32_t q = 0;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
+              *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ph.q_out) + static_cast<size_t>(c) * ph.n + n0) = q;
+              if (lane == 0) ph.s_out[static_cast<size_t>(tile) * ph.ld_s_out + c] = scale;
+              if (ph.ssq_out) {
+                ss = warp_sum(ss);
+                if (lane == 0) ph.ssq_out[static_cast<size_t>(tile) * ph.ld_s_out + c] = ss;
+              }
+            } else {
+              // ROPE_KV: tile = head index (q heads, then k heads, then v heads), lane holds dims 4 lane .. 4 lane + 3
+              const SllmFdRope& rp = p.rope;
+              const int head = tile;
+              const bool is_q = head < rp.hq;
+              const bool is_v = head >= rp.hq + rp.hkv;
+              const int pos = rp.positions[c];
+              if (!is_v) {
+                const int half = rp.rotary_dim >> 1;
+                const int lane_off = half >> 2;          // partner lane distance (half / 4), a power of two
+                float pv[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) pv[j] = __shfl_xor_sync(0xffffffffu, v[j], lane_off);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int i = lane * 4 + j;
+                  if (i < rp.rotary_dim) {
+                    const bool lo = i < half;
+                    const int fi = lo ? i : i - half;
+                    float sn, cs;
+                    sincosf(static_cast<float>(pos) * sh->inv_freq[fi], &sn, &cs);
+                    const float a = lo ? v[j] : pv[j], b = lo ? pv[j] : v[j];
+                    v[j] = lo ? a * cs - b * sn : b * cs + a * sn;
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] = fd_bf16r(v[j]);
+              if (is_q) {
+                uint2 hw;
+                *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
+                *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
+                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
+              } else {
+                const int kvh = is_v ? head - rp.hq - rp.hkv : head - rp.hq;
+                const int blk = rp.block_table[static_cast<size_t>(rp.seq_index[c]) * rp.max_blocks + pos / rp.page_size];
+                const size_t slot = (static_cast<size_t>(blk) * rp.hkv + kvh) * rp.page_size + pos % rp.page_size;
+                if (!rp.kv_fp8) {
+                  uint2 hw;
+                  *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
+                  *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
+                  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
+                  *reinterpret_cast<uint2*>(dst) = hw;
+                } else {
+                  float amax = 0.f;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float a = fabsf(v[j]);
+                    if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
+                  }
+                  amax = warp_max(amax);
+                  const float st = is_v ? rp.v_static : rp.k_static;
+                  const float scale = st > 0.f ? st : (amax > 0.f ? amax / kFdE4M3Max : 1.f);
+                  uint32_t q = 0;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
+                  uint8_t* dst = static_cast<uint8_t*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
+                  *reinterpret_cast<uint32_t*>(dst) = q;
+                  if (lane == 0 && st <= 0.f) (is_v ? rp.v_scale : rp.k_scale)[slot] = scale;
+                }
+              }
+            }
+          }
+        }
+        // the staging buffer is reused by the next tile
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+
+      // ---- publish the phase: every output of this CTA is written; arrive at the grid barrier
+      __threadfence();
+      fd_fence_proxy_async();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) {
+        // Barrier k of a launch completes at base + k G.  The arrivals of a whole launch add up to kFdSyncQuantum
+        // whatever the grid and the phase count (CTA 0 tops up its last arrival), so the counter is a multiple of the
+        // quantum between launches and a CTA that starts late still derives the same base from it.
+        unsigned long long add = 1ull;
+        if (pi == p.n_phases - 1 && cta == 0) add += kFdSyncQuantum - static_cast<unsigned long long>(p.n_phases) * G;
+        fd_red_release_add_u64(p.sync, add);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- embedding + quantisation
+// One CTA per token: h = table[id] * scale (bf16), E4M3 + scale per 128 columns, sum of squares per 128 columns.
+__global__ void __launch_bounds__(256)
+embed_quant_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids, __nv_bfloat16* __restrict__ h,
+                   uint8_t* __restrict__ q_out, float* __restrict__ s_out, float* __restrict__ ssq_out, int ld_s, int d,
+                   int vocab, float scale) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const __nv_bfloat16* src = table + static_cast<size_t>(id) * d;
+  for (int blk = warp; blk < d / 128; blk += 8) {
+    const int i0 = blk * 128 + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(src + i0);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    float v[4] = {__bfloat162float(a.x), __bfloat162float(a.y), __bfloat162float(b.x), __bfloat162float(b.y)};
+    float amax = 0.f, ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (scale != 1.f) v[j] = fd_bf16r(v[j] * scale);
+      ss += v[j] * v[j];
+      const float x = fabsf(v[j]);
+      if (x == x && x <= 3.0e38f) amax = fmaxf(amax, x);
+    }
+    uint2 hw;
+    *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(h + static_cast<size_t>(t) * d + i0) = hw;
+    amax = warp_max(amax);
+    ss = warp_sum(ss);
+    const float sc = amax > 0.f ? amax / kFdE4M3Max : 1.f;
+    uint32_t q = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], sc))) << (8 * j);
+    *reinterpret_cast<uint32_t*>(q_out + static_cast<size_t>(t) * d + i0) = q;
+    if (lane == 0) {
+      s_out[static_cast<size_t>(blk) * ld_s + t] = sc;
+      ssq_out[static_cast<size_t>(blk) * ld_s + t] = ss;
+    }
+  }
+}
+
+static int fd_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+      n = v;
+    else
+      n = 148;
+  }
+  return n;
+}
+
+template <int BN>
+constexpr size_t fd_smem_bytes() {
+  return 1024 + 2 * kFdASlots * kFdASlotBytes + 2 * kFdBSlots * fd_b_slot<BN>() + BN * 128 * 4 + sizeof(FdShared);
+}
+
+template <int BN>
+static int fd_launch(const FdMaps& maps, const FdParams& p, int grid, cudaStream_t stream) {
+  constexpr size_t smem = fd_smem_bytes<BN>();
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(fused_decode_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return SLLM_ERR_CUDA;
+    configured = true;
+  }
+  if (launch_kernel(fused_decode_kernel<BN>, dim3(grid), dim3(kFdThreads), smem, stream, 1u, maps, p) != cudaSuccess) {
+    cudaGetLastError();
+    return SLLM_ERR_CUDA;
+  }
+  return SLLM_OK;
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+struct SllmCommDescFd {   // same layout as the descriptor of sllm_gemm_allreduce
+  int world, rank;
+  long long cap_elems;
+  int max_tiles;
+  int reserved;
+  void* recv[kFdMaxWorld];
+  void* flags[kFdMaxWorld];
+  void* epoch;
+};
+
+SLLM_EXPORT long long sllm_fused_decode_ws_floats(int grid) {
+  if (grid <= 0) grid = fd_sm_count();
+  return static_cast<long long>(2) * grid * 2 * 32 * 128;
+}
+
+SLLM_EXPORT int sllm_fused_decode(const SllmFdDesc* d, void* stream) {
+  if (!d || d->n_phases < 1 || d->n_phases > SLLM_FD_MAX_PHASES || d->rows < 1 || d->rows > 32 || !d->ws ||
+      !d->counters || !d->sync)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  const int bn = d->rows <= 16 ? 16 : 32;
+  const int grid = d->grid > 0 ? d->grid : fd_sm_count();
+  if (static_cast<unsigned long long>(grid) * SLLM_FD_MAX_PHASES > kFdSyncQuantum) return SLLM_ERR_UNSUPPORTED_SHAPE;
+  if (d->ws_floats < sllm_fused_decode_ws_floats(grid)) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+  FdMaps maps;
+  FdParams p;
+  memset(&p, 0, sizeof(p));
+  p.n_phases = d->n_phases;
+  p.rows = d->rows;
+  p.rope = d->rope;
+  p.ws = d->ws; p.counters = d->counters; p.sync = d->sync; p.status = d->status;
+  p.wait_limit = d->wait_limit_cycles > 0 ? d->wait_limit_cycles : kWaitLimitCycles;
+  for (int i = 0; i < d->n_phases; ++i) {
+    const SllmFdPhase& ph = d->phase[i];
+    if (!ph.w || !ph.w_scale || !ph.x || !ph.x_scale || ph.n <= 0 || ph.k <= 0 || (ph.k & 127) || (ph.n & 3))
+      return SLLM_ERR_INVALID_ARGUMENT;
+    const int tiles = (ph.n + 127) / 128;
+    if (tiles > d->n_counters) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+    if (ph.ld_sb < bn || (ph.ld_sb & 3) || (ph.ld_sa & 3) || ph.ld_sa < ph.dual_off + ph.n) return SLLM_ERR_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(ph.w_scale) & 15) || (reinterpret_cast<uintptr_t>(ph.x_scale) & 15))
+      return SLLM_ERR_ALIGNMENT;
+    if (ph.norm_tiles > 0 && (!ph.ssq_in || ph.norm_dim <= 0)) return SLLM_ERR_INVALID_ARGUMENT;
+    switch (ph.epilogue) {
+      case SLLM_FD_PLAIN:
+        if (!ph.y || ph.dual_off || (ph.ldy & 3)) return SLLM_ERR_INVALID_ARGUMENT;
+        break;
+      case SLLM_FD_RESID_QUANT:
+        if (!ph.y || !ph.residual || !ph.q_out || !ph.s_out || ph.dual_off || (ph.n & 127) || (ph.ldy & 3) ||
+            ph.ld_s_out < d->rows)
+          return SLLM_ERR_INVALID_ARGUMENT;
+        break;
+      case SLLM_FD_SILU_QUANT:
+        if (!ph.q_out || !ph.s_out || ph.dual_off < ph.n || (ph.dual_off & 3) || (ph.n & 127) || ph.ld_s_out < d->rows)
+          return SLLM_ERR_INVALID_ARGUMENT;
+        break;
+      case SLLM_FD_ROPE_KV: {
+        const SllmFdRope& r = d->rope;
+        if (!ph.y || ph.dual_off || (ph.ldy & 3) || !r.positions || !r.seq_index || !r.block_table || !r.k_pages ||
+            !r.v_pages || r.hq <= 0 || r.hkv <= 0 || ph.n != (r.hq + 2 * r.hkv) * 128 || r.page_size <= 0)
+          return SLLM_ERR_INVALID_ARGUMENT;
+        if (r.rotary_dim != 32 && r.rotary_dim != 64 && r.rotary_dim != 128) return SLLM_ERR_UNSUPPORTED_SHAPE;
+        if (r.kv_fp8 && (r.k_static <= 0.f || r.v_static <= 0.f) && (!r.k_scale || !r.v_scale))
+          return SLLM_ERR_INVALID_ARGUMENT;
+        break;
+      }
+      default:
+        return SLLM_ERR_INVALID_ARGUMENT;
+    }
+    p.ph[i] = ph;
+    int rc = cached_kmajor_tmap(&maps.a[i], ph.w, 1, ph.dual_off + ph.n, ph.k, ph.k, 128);
+    if (rc != SLLM_OK) return rc;
+    rc = cached_kmajor_tmap(&maps.b[i], ph.x, 1, d->rows, ph.k, ph.k, bn);
+    if (rc != SLLM_OK) return rc;
+  }
+  for (int i = d->n_phases; i < SLLM_FD_MAX_PHASES; ++i) { maps.a[i] = maps.a[0]; maps.b[i] = maps.b[0]; }
+  if (d->comm) {
+    const SllmCommDescFd* c = static_cast<const SllmCommDescFd*>(d->comm);
+    if (c->world < 2 || c->world > kFdMaxWorld || c->rank < 0 || c->rank >= c->world || !c->epoch)
+      return SLLM_ERR_INVALID_ARGUMENT;
+    for (int i = 0; i < d->n_phases; ++i) {
+      if (d->phase[i].epilogue != SLLM_FD_RESID_QUANT) continue;
+      const long long tiles = (d->phase[i].n + 127) / 128;
+      if (tiles > c->max_tiles || tiles * 128 * bn > c->cap_elems) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+    }
+    p.comm.world = c->world; p.comm.rank = c->rank; p.comm.cap_elems = c->cap_elems;
+    for (int i = 0; i < c->world; ++i) {
+      if (!c->recv[i] || !c->flags[i]) return SLLM_ERR_INVALID_ARGUMENT;
+      p.comm.recv[i] = static_cast<__nv_bfloat16*>(c->recv[i]);
+      p.comm.flags[i] = static_cast<uint32_t*>(c->flags[i]);
+    }
+    p.comm.epoch = static_cast<uint32_t*>(c->epoch);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return bn == 16 ? fd_launch<16>(maps, p, grid, st) : fd_launch<32>(maps, p, grid, st);
+}
+
+SLLM_EXPORT int sllm_embed_quant(const void* table, const int* ids, void* h, void* q_out, float* s_out, float* ssq_out,
+                                 int ld_s, int rows, int d, int vocab, float scale, void* stream) {
+  if (!table || !ids || !h || !q_out || !s_out || !ssq_out || rows <= 0 || d <= 0 || (d & 127) || ld_s < rows || vocab <= 0)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  launch_kernel(embed_quant_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 1u,
+                static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(h),
+                static_cast<uint8_t*>(q_out), s_out, ssq_out, ld_s, d, vocab, scale);
+  return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+SLLM_EXPORT int sllm_fused_decode_abi(int* out, int n) {
+  const int rec[] = {
+      static_cast<int>(sizeof(SllmFdPhase)), static_cast<int>(offsetof(SllmFdPhase, eps)),
+      static_cast<int>(offsetof(SllmFdPhase, w)), static_cast<int>(offsetof(SllmFdPhase, ssq_out)),
+      static_cast<int>(sizeof(SllmFdRope)), static_cast<int>(offsetof(SllmFdRope, theta)),
+      static_cast<int>(offsetof(SllmFdRope, k_pages)), static_cast<int>(offsetof(SllmFdRope, inv_freq)),
+      static_cast<int>(sizeof(SllmFdDesc)), static_cast<int>(offsetof(SllmFdDesc, phase)),
+      static_cast<int>(offsetof(SllmFdDesc, rope)), static_cast<int>(offsetof(SllmFdDesc, ws)),
+      static_cast<int>(offsetof(SllmFdDesc, sync)), static_cast<int>(offsetof(SllmFdDesc, comm)),
+      static_cast<int>(offsetof(SllmFdDesc, wait_limit_cycles)),
+      static_cast<int>(sizeof(SllmCommDescFd)), static_cast<int>(offsetof(SllmCommDescFd, recv)),
+      static_cast<int>(offsetof(SllmCommDescFd, epoch)),
+  };
+  const int have = static_cast<int>(sizeof(rec) / sizeof(rec[0]));
+  for (int i = 0; i < n && i < have; ++i) out[i] = rec[i];
+  return have;
+}

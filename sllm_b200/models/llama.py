@@ -169,6 +169,34 @@ class LlamaModel:
         self.hkv = max(1, cfg.n_kv_heads // t)
         self.quant = cfg.weight_format == "fp8"
         self.adapters = None      # models.adapters.AdapterSet applied to every forward while set
+        self._fused: dict = {}    # row count -> FusedLlamaDecoder (decode steps of up to 32 rows)
+        self._fused_reason = None
+        self.fallbacks = 0        # forwards of a fused-eligible model that took the per-op path
+
+    def _fused_decoder(self, b: ForwardBatch):
+        """The fused decode chain for this batch, or None when the batch or the model is not covered (prefill rows,
+        input embeddings, multi-axis rotary positions, adapters, more than 32 rows)."""
+        if not b.tokens.is_cuda or b.logit_rows is not None or b.embeds is not None or b.rope_pos3 is not None:
+            return None
+        rows = b.num_tokens
+        if rows > 32 or (self.adapters is not None and (self.adapters.loras or self.adapters.cvs)):
+            return None
+        if self._fused_reason is None:
+            from . import fused_llama
+            self._fused_reason = fused_llama.eligible(self) or ""
+        if self._fused_reason:
+            return None
+        dec = self._fused.get(rows)
+        if dec is None:
+            from .fused_llama import FusedLlamaDecoder
+            dec = FusedLlamaDecoder(self, rows, b.tokens.device)
+            self._fused[rows] = dec
+        return dec
+
+    def _fused_logits(self, dec, b: ForwardBatch, cache) -> torch.Tensor:
+        lg = dec.run(b, cache)
+        self.last_hidden = dec.h
+        return lg
 
     @property
     def local_kv_heads(self) -> int:
@@ -251,8 +279,14 @@ class LlamaModel:
 
     def forward(self, b: ForwardBatch, cache) -> torch.Tensor:
         """Full-vocabulary logits [rows, vocab]."""
+        dec = self._fused_decoder(b)
+        if dec is not None:
+            return self.tp.gather_logits(self._fused_logits(dec, b, cache))
         return self.tp.gather_logits(self.logits(self._keep(self.hidden(b, cache)), b))
 
     def greedy(self, b: ForwardBatch, cache) -> torch.Tensor:
         """Greedy next tokens (int32 [rows]) without materialising gathered logits."""
+        dec = self._fused_decoder(b)
+        if dec is not None:
+            return self.tp.argmax(self._fused_logits(dec, b, cache), self.w.vocab_offset)
         return self.tp.argmax(self.logits(self._keep(self.hidden(b, cache)), b), self.w.vocab_offset)

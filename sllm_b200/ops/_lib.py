@@ -30,6 +30,7 @@ DEVICE_STATUS_NAMES = {
     0: "ok", 101: "timeout waiting for TMA data", 102: "timeout waiting for a free smem stage",
     103: "timeout waiting for the accumulator", 104: "timeout waiting for a free accumulator",
     105: "timeout waiting for a peer flag", 106: "timeout draining copies",
+    107: "timeout waiting at a grid barrier",
 }
 
 

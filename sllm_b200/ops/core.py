@@ -385,9 +385,10 @@ def _attn_splits(rows: int, hkv: int, max_kv: int) -> int:
 def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq_index: torch.Tensor,
                     kv_lens: torch.Tensor, hq: int, hkv: int, hd: int, *, window: int = 0,
                     sm_scale: Optional[float] = None, max_kv: int = 0, quant_out: bool = False,
-                    sinks: Optional[torch.Tensor] = None, impl: Optional[str] = None):
+                    sinks: Optional[torch.Tensor] = None, impl: Optional[str] = None, out: Optional[QTensor] = None):
     """Attention of each query row over its sequence's pages. q: [R, hq*hd] (row stride allowed).
-    Returns [R, hq*hd] (bf16) or a QTensor when quant_out (head_dim 128)."""
+    Returns [R, hq*hd] (bf16) or a QTensor when quant_out (head_dim 128); ``out`` supplies the QTensor to fill
+    (its scale plane may have a leading dimension larger than R)."""
     scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(hd)
     r = q.shape[0]
     if not q.is_cuda:
@@ -420,8 +421,8 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
     if quant_out:
         if hd != 128:
             raise ValueError("quantised attention output needs head_dim 128")
-        oq = _alloc_q(r, hq * hd, q.device)
-        out_b, out_q, out_s, ld = None, oq.data, oq.scale, r
+        oq = out if out is not None else _alloc_q(r, hq * hd, q.device)
+        out_b, out_q, out_s, ld = None, oq.data, oq.scale, max(oq.scale.stride(0), oq.scale.shape[1])
     else:
         ob = torch.empty((r, hq * hd), dtype=torch.bfloat16, device=q.device)
         out_b, out_q, out_s, ld = ob, None, None, 0
