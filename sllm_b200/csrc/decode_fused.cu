@@ -38,17 +38,18 @@ namespace sllm {
 int cached_kmajor_tmap(CUtensorMap* out, const void* ptr, int elem_bytes, long long rows, long long k_elems,
                        long long row_stride_bytes, int box_rows);
 
-constexpr int kFdThreads = 256;
-constexpr int kFdASlots = 5;                       // weight-ring slots per issuer
-constexpr int kFdBSlots = 3;                       // activation-ring slots per issuer
+constexpr int kFdThreads = 384;                    // 2 producer + 2 MMA warps, two epilogue groups of 4 warps
+constexpr int kFdASlots = 4;                       // weight-ring slots (16 KB) per issuer, released by the MMA commit
+constexpr int kFdBSlots = 6;                       // activation-ring slots per issuer, released by the epilogue
 constexpr int kFdATile = 128 * 128;                // 128 weight rows x 128 K bytes
-constexpr int kFdASlotBytes = kFdATile + 1024;     // + 128 fp32 row scales, padded to the swizzle alignment
+constexpr int kFdASlotBytes = kFdATile;
 constexpr int kFdMaxWorld = 8;
+constexpr int kFdLookaheadDefault = 12;            // weight tiles (16 KB each) prefetched into L2 ahead of the ring, per CTA
 constexpr float kFdE4M3Max = 448.f;
 constexpr unsigned long long kFdSyncQuantum = 4096;   // grid-barrier arrivals per launch (>= phases x CTAs)
 
 template <int BN> constexpr int fd_b_tile() { return BN * 128; }
-template <int BN> constexpr int fd_b_slot() { return BN * 128 + 1024; }
+template <int BN> constexpr int fd_b_slot() { return BN * 128; }
 
 struct FdComm {
   int world, rank;
@@ -72,6 +73,9 @@ struct FdParams {
   unsigned long long* sync;
   int* status;
   long long wait_limit;
+  int lookahead;               // L2 prefetch distance of the weight producer in tiles
+  int debug;                   // experiment switches (timing studies only; results are wrong when set)
+  unsigned long long* trace;   // optional [CTAs][MAX_PHASES][8] globaltimer stamps (profiling aid), null = off
   FdComm comm;
 };
 
@@ -117,6 +121,32 @@ __device__ __forceinline__ void fd_bulk_load(void* smem_dst, const void* gsrc, u
                : "memory");
 }
 __device__ __forceinline__ void fd_fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// TMA prefetch of a 2-D tile into L2 only (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void fd_tma_prefetch_l2(const CUtensorMap* m, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void fd_prefetch_l2(const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread, no wait.
+__device__ __forceinline__ void fd_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+template <int BN>
+__device__ __forceinline__ void fd_tmem_ld(uint32_t taddr, uint32_t (&r)[BN]) {
+  if constexpr (BN == 32) fd_tmem_ld32(taddr, r);
+  else tmem_ld16(taddr, r);
+}
 
 // Bounded wait until the grid-barrier counter reaches `target`.
 __device__ __forceinline__ bool fd_grid_wait(const unsigned long long* ctr, unsigned long long target,
@@ -150,6 +180,27 @@ __device__ __forceinline__ bool fd_epi_any(bool pred) {
   return r != 0;
 }
 
+__device__ __forceinline__ void fd_stamp(unsigned long long* trace, int cta, int pi, int slot) {
+  if (trace) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    trace[(static_cast<size_t>(cta) * SLLM_FD_MAX_PHASES + pi) * 8 + slot] = t;
+  }
+}
+
+#ifdef SLLM_FD_PROFILE
+// Cycle accounting of the pipeline roles (timing studies; never compiled into the product library).
+#define FD_PROF_DECL(n) long long prof_##n = 0
+#define FD_PROF_T0() const long long prof_t0 = clock64()
+#define FD_PROF_ADD(n) prof_##n += clock64() - prof_t0
+#define FD_PROF_OUT(slot, n) if (p.trace) p.trace[static_cast<size_t>(gridDim.x) * 32 + static_cast<size_t>(blockIdx.x) * 32 + (slot)] = prof_##n
+#else
+#define FD_PROF_DECL(n)
+#define FD_PROF_T0()
+#define FD_PROF_ADD(n)
+#define FD_PROF_OUT(slot, n)
+#endif
+
 // CTA that owns unit u when U units are dealt to G CTAs as [c U / G, (c + 1) U / G).
 __device__ __forceinline__ int fd_cta_of_unit(long long u, long long U, int G) {
   return static_cast<int>(((u + 1) * G - 1) / U);
@@ -170,6 +221,226 @@ __device__ __forceinline__ FdPhaseGeom fd_geom(const SllmFdPhase& ph, int cta, i
   return g;
 }
 
+// Barrier 2 over the 256 threads of both epilogue groups, ORing a predicate (see fd_epi_any).
+__device__ __forceinline__ bool fd_all_any(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 2, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void mbar_arrive_cnt(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+// Per-token-row part of a tile epilogue, run by the 128 threads of epilogue group 0 after the tile has been staged
+// as stage[token][row of the tile]: warp w takes tokens w, w + 4, ...; lane l owns outputs 4 l .. 4 l + 3 of the tile.
+// Kept out of line and rolled: it runs once per tile, so its size (instruction fetch), not its issue rate, matters.
+// Returns false when the cross-rank exchange gave up.
+template <int BN>
+__device__ __noinline__ bool fd_finish_columns(const FdParams& p, const SllmFdPhase& ph, FdShared* sh, float* stage,
+                                               int tile, int ew, int lane, int et, int T, volatile int* abort_flag,
+                                               long long limit) {
+  const int n0 = tile * 128 + lane * 4;     // first of this lane's four outputs of a token row
+  if (ph.epilogue == SLLM_FD_RESID_QUANT && p.comm.world > 1) {
+    // ---- cross-rank sum of the tile: push the partial (bf16) to every rank, flag, wait, sum in rank order
+    const FdComm& cm = p.comm;
+    if (et == 0) {
+      const uint32_t e1 = cm.epoch[tile] + 1;
+      cm.epoch[tile] = e1;
+      sh->epoch = e1;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const uint32_t e = sh->epoch;
+    const long long region = static_cast<long long>(e & 1) * cm.world;
+    const long long toff = static_cast<long long>(tile) * (128 * BN);
+#pragma unroll 1
+    for (int c = ew; c < T; c += 4) {
+      const float4 x = *reinterpret_cast<const float4*>(stage + c * 128 + lane * 4);
+      uint2 w;
+      *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(x.x, x.y);
+      *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(x.z, x.w);
+      const long long off = (region + cm.rank) * cm.cap_elems + toff + c * 128 + lane * 4;
+      for (int peer = 0; peer < cm.world; ++peer) *reinterpret_cast<uint2*>(cm.recv[peer] + off) = w;
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (et < cm.world && et != cm.rank) {
+      fd_st_release_sys(cm.flags[et] + static_cast<size_t>(tile) * cm.world + cm.rank, e);
+      const uint32_t* f = cm.flags[cm.rank] + static_cast<size_t>(tile) * cm.world + et;
+      uint32_t spins = 0;
+      long long t0 = 0;
+      while (static_cast<int32_t>(fd_ld_acquire_sys(f) - e) < 0) {
+        ++spins;
+        if (spins == 1024) t0 = clock64();
+        if (spins > 1024 && (spins & 63) == 0) {
+          if (*abort_flag) break;
+          if (clock64() - t0 > limit) {
+            *abort_flag = 1;
+            if (p.status) atomicCAS(p.status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
+            break;
+          }
+        }
+      }
+    }
+    if (fd_epi_any(*abort_flag != 0)) return false;
+#pragma unroll 1
+    for (int c = ew; c < T; c += 4) {
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int src = 0; src < cm.world; ++src) {
+        const uint2 w = __ldcg(reinterpret_cast<const uint2*>(cm.recv[cm.rank] + (region + src) * cm.cap_elems + toff +
+                                                              c * 128 + lane * 4));
+        const __nv_bfloat162 h0 = *reinterpret_cast<const __nv_bfloat162*>(&w.x);
+        const __nv_bfloat162 h1 = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
+        s.x += __bfloat162float(h0.x); s.y += __bfloat162float(h0.y);
+        s.z += __bfloat162float(h1.x); s.w += __bfloat162float(h1.y);
+      }
+      *reinterpret_cast<float4*>(stage + c * 128 + lane * 4) = s;   // the same lane reads it back below
+    }
+  }
+
+  const __nv_bfloat16* res_base = static_cast<const __nv_bfloat16*>(ph.residual);
+  const bool resid = ph.epilogue == SLLM_FD_RESID_QUANT;
+  // the residual of the next token row is requested while the current one is processed
+  uint2 res_next = make_uint2(0u, 0u);
+  if (resid && ew < T) res_next = *reinterpret_cast<const uint2*>(res_base + static_cast<size_t>(ew) * ph.ldy + n0);
+#pragma unroll 1
+  for (int c = ew; c < T; c += 4) {
+    const float4 x = *reinterpret_cast<const float4*>(stage + c * 128 + lane * 4);
+    float v[4] = {x.x, x.y, x.z, x.w};
+    const uint2 rr = res_next;
+    if (resid && c + 4 < T)
+      res_next = *reinterpret_cast<const uint2*>(res_base + static_cast<size_t>(c + 4) * ph.ldy + n0);
+    if (ph.epilogue == SLLM_FD_PLAIN) {
+      __nv_bfloat16* y = static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0;
+      const __nv_bfloat16* res = res_base ? res_base + static_cast<size_t>(c) * ph.ldy + n0 : nullptr;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (n0 + j < ph.n) {
+          float o = v[j];
+          if (res) o += __bfloat162float(res[j]);
+          if (ph.softcap > 0.f) o = ph.softcap * tanhf(o / ph.softcap);
+          y[j] = __float2bfloat16_rn(o);
+        }
+      }
+    } else if (ph.epilogue == SLLM_FD_RESID_QUANT || ph.epilogue == SLLM_FD_SILU_QUANT) {
+      if (resid) {
+        const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
+        const __nv_bfloat162 r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
+        v[0] += __bfloat162float(r0.x); v[1] += __bfloat162float(r0.y);
+        v[2] += __bfloat162float(r1.x); v[3] += __bfloat162float(r1.y);
+        uint2 hw;
+        *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
+      }
+      float amax = 0.f, ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[j] = fd_bf16r(v[j]);
+        ss += v[j] * v[j];
+        const float a = fabsf(v[j]);
+        if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
+      }
+      amax = warp_max(amax);
+      const float scale = amax > 0.f ? amax / kFdE4M3Max : 1.f;
+      uint32_t q = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
+      *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ph.q_out) + static_cast<size_t>(c) * ph.n + n0) = q;
+      if (lane == 0) ph.s_out[static_cast<size_t>(tile) * ph.ld_s_out + c] = scale;
+      if (ph.ssq_out) {
+        ss = warp_sum(ss);
+        if (lane == 0) ph.ssq_out[static_cast<size_t>(tile) * ph.ld_s_out + c] = ss;
+      }
+    } else {
+      // ROPE_KV: tile = head index (q heads, then k heads, then v heads), lane holds dims 4 lane .. 4 lane + 3
+      const SllmFdRope& rp = p.rope;
+      const int head = tile;
+      const bool is_q = head < rp.hq;
+      const bool is_v = head >= rp.hq + rp.hkv;
+      const int pos = rp.positions[c];
+      if (!is_v) {
+        const int half = rp.rotary_dim >> 1;
+        const int lane_off = half >> 2;          // partner lane distance (half / 4), a power of two
+        float pv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pv[j] = __shfl_xor_sync(0xffffffffu, v[j], lane_off);
+        const int i0 = lane * 4;
+        if (i0 < rp.rotary_dim) {
+          const bool lo = i0 < half;
+          const int f0 = lo ? i0 : i0 - half;
+#pragma unroll 1
+          for (int j = 0; j < 4; ++j) {
+            float sn, cs;
+            sincosf(static_cast<float>(pos) * sh->inv_freq[f0 + j], &sn, &cs);
+            const float a = lo ? v[j] : pv[j], b = lo ? pv[j] : v[j];
+            v[j] = lo ? a * cs - b * sn : b * cs + a * sn;
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = fd_bf16r(v[j]);
+      uint2 hw;
+      *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
+      if (is_q) {
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
+      } else {
+        const int kvh = is_v ? head - rp.hq - rp.hkv : head - rp.hq;
+        const int blk = rp.block_table[static_cast<size_t>(rp.seq_index[c]) * rp.max_blocks + pos / rp.page_size];
+        const size_t slot = (static_cast<size_t>(blk) * rp.hkv + kvh) * rp.page_size + pos % rp.page_size;
+        if (!rp.kv_fp8) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
+          *reinterpret_cast<uint2*>(dst) = hw;
+        } else {
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = fabsf(v[j]);
+            if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
+          }
+          amax = warp_max(amax);
+          const float st = is_v ? rp.v_static : rp.k_static;
+          const float scale = st > 0.f ? st : (amax > 0.f ? amax / kFdE4M3Max : 1.f);
+          uint32_t q = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
+          uint8_t* dst = static_cast<uint8_t*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
+          *reinterpret_cast<uint32_t*>(dst) = q;
+          if (lane == 0 && st <= 0.f) (is_v ? rp.v_scale : rp.k_scale)[slot] = scale;
+        }
+      }
+    }
+  }
+  return true;
+}
+
+constexpr int kFdFastParts = 6;   // parts of a split tile whose loads are kept in flight together
+// dst[(col0 + c) * 128] = sum over parts jj < np (in order) of base[offs[jj] + (col0 + c) * 128], c < 8: all loads are
+// issued before the first one is used, and the sums go to shared memory so that no accumulator array is live here.
+__device__ __forceinline__ void fd_sum_parts(const float* base, const uint32_t (&offs)[kFdFastParts], int np, int col0,
+                                             float* dst) {
+  float t[kFdFastParts][8];
+#pragma unroll
+  for (int jj = 0; jj < kFdFastParts; ++jj) {
+    if (jj < np) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) t[jj][c] = __ldcg(base + offs[jj] + static_cast<size_t>(col0 + c) * 128);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float sum = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < kFdFastParts; ++jj)
+      if (jj < np) sum += t[jj][c];
+    dst[(col0 + c) * 128] = sum;
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kFdThreads, 1)
 fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__ FdParams p) {
@@ -180,8 +451,10 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
   constexpr uint32_t kTmemCols = 8 * BN;            // 4 accumulators x (gate, up) x BN columns
   uint8_t* a_ring = smem;                                         // [2][kFdASlots][kFdASlotBytes]
   uint8_t* b_ring = a_ring + 2 * kFdASlots * kFdASlotBytes;       // [2][kFdBSlots][kBSlot]
-  float* stage = reinterpret_cast<float*>(b_ring + 2 * kFdBSlots * kBSlot);   // [BN][128]
-  FdShared* sh = reinterpret_cast<FdShared*>(stage + BN * 128);
+  float* b_scale = reinterpret_cast<float*>(b_ring + 2 * kFdBSlots * kBSlot);   // [2][kFdBSlots][BN] activation scales
+  float* stage = b_scale + 2 * kFdBSlots * BN;                                  // [BN][128] tile staged for the row epilogue
+  float* xchg = stage + BN * 128;                                             // [BN][128] group 1 -> group 0 hand-over
+  FdShared* sh = reinterpret_cast<FdShared*>(xchg + BN * 128);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -192,10 +465,10 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < 2; ++r) {
-      for (int s = 0; s < kFdASlots; ++s) { mbar_init(&sh->afull[r][s], 1); mbar_init(&sh->aempty[r][s], 4); }
-      for (int s = 0; s < kFdBSlots; ++s) { mbar_init(&sh->bfull[r][s], 1); mbar_init(&sh->bempty[r][s], 4); }
+      for (int s = 0; s < kFdASlots; ++s) { mbar_init(&sh->afull[r][s], 1); mbar_init(&sh->aempty[r][s], 1); }
+      for (int s = 0; s < kFdBSlots; ++s) { mbar_init(&sh->bfull[r][s], 1); mbar_init(&sh->bempty[r][s], 8); }
     }
-    for (int a = 0; a < 4; ++a) { mbar_init(&sh->tfull[a], 1); mbar_init(&sh->tempty[a], 4); }
+    for (int a = 0; a < 4; ++a) { mbar_init(&sh->tfull[a], 1); mbar_init(&sh->tempty[a], 8); }
     sh->abort_flag = 0;
     sh->is_last = 0;
     mbar_fence_init();
@@ -215,6 +488,7 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
+  if (threadIdx.x == 0) fd_stamp(p.trace, cta, 0, 0);       // CTA set up
 
   if (warp == 0) {
     // ------------------------------------------------------------------ weight producer
@@ -222,33 +496,61 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       uint32_t apos[2] = {0u, 0u};
       uint32_t n = 0;
       bool ok = true;
+      FD_PROF_DECL(pa);
+      // L2 prefetch cursor: runs kFdLookahead tile loads ahead of the shared-memory ring, across phase
+      // boundaries, so HBM keeps streaming while a phase's reduction / epilogue / grid barrier resolves.
+      int f_pi = 0, f_half = 0;
+      FdPhaseGeom fg = fd_geom(p.ph[0], cta, G);
+      long long f_u = fg.u0;
+      auto prefetch_next = [&]() {
+        while (f_pi < p.n_phases && f_u >= fg.u1) {
+          if (++f_pi < p.n_phases) { fg = fd_geom(p.ph[f_pi], cta, G); f_u = fg.u0; f_half = 0; }
+        }
+        if (f_pi >= p.n_phases) return;
+        const int ft = static_cast<int>(f_u / fg.nkb), fk = static_cast<int>(f_u % fg.nkb);
+        const SllmFdPhase& fp = p.ph[f_pi];
+        const int frow = ft * 128 + f_half * fp.dual_off;
+        fd_tma_prefetch_l2(&maps.a[f_pi], fk * 128, frow);
+        int fs = fp.dual_off + fp.n - frow;      // the row scales the epilogue will read from L2
+        if (fs > 128) fs = 128;
+        fd_prefetch_l2(fp.w_scale + static_cast<size_t>(fk) * fp.ld_sa + frow, fs * 4);
+        if (f_half < fg.dual) ++f_half; else { f_half = 0; ++f_u; }
+      };
+      for (int i = 0; i < p.lookahead; ++i) prefetch_next();
       for (int pi = 0; pi < p.n_phases && ok; ++pi) {
         const SllmFdPhase& ph = p.ph[pi];
         const FdPhaseGeom g = fd_geom(ph, cta, G);
-        const int w_rows = ph.dual_off + ph.n;
         int tile = static_cast<int>(g.u0 / g.nkb), kb = static_cast<int>(g.u0 % g.nkb);
         for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
           const int r = n & 1;
           for (int half = 0; half <= g.dual; ++half) {
             const uint32_t slot = apos[r] % kFdASlots, fill = apos[r] / kFdASlots;
+            { FD_PROF_T0();
             if (!mbar_wait(&sh->aempty[r][slot], (fill & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY, limit)) {
               ok = false;
               break;
             }
+            FD_PROF_ADD(pa); }
             uint8_t* dst = a_ring + (r * kFdASlots + slot) * kFdASlotBytes;
             const int row0 = tile * 128 + half * ph.dual_off;
-            int srows = w_rows - row0;
-            if (srows > 128) srows = 128;
-            mbar_expect_tx(&sh->afull[r][slot], kFdATile + srows * 4);
-            tma_load_2d(dst, &maps.a[pi], &sh->afull[r][slot], kb * 128, row0);
-            fd_bulk_load(dst + kFdATile, ph.w_scale + static_cast<size_t>(kb) * ph.ld_sa + row0, srows * 4,
-                         &sh->afull[r][slot]);
+            if (p.debug & 1) {
+              mbar_arrive(&sh->afull[r][slot]);                       // no weight traffic at all
+            } else if (p.debug & 4) {
+              mbar_expect_tx(&sh->afull[r][slot], kFdATile);          // one contiguous 16 KB copy instead of a tiled box
+              fd_bulk_load(dst, static_cast<const uint8_t*>(ph.w) + (static_cast<size_t>(tile) * g.nkb + kb) * kFdATile,
+                           kFdATile, &sh->afull[r][slot]);
+            } else {
+              mbar_expect_tx(&sh->afull[r][slot], kFdATile);
+              tma_load_2d(dst, &maps.a[pi], &sh->afull[r][slot], kb * 128, row0);
+            }
             ++apos[r];
+            if (p.lookahead > 0) prefetch_next();
           }
           if (++kb == g.nkb) { kb = 0; ++tile; }
         }
       }
       pdl_trigger();
+      FD_PROF_OUT(16, pa);
       // Drain: every copy this thread started must have landed before the CTA may exit (on the normal path
       // all of them have been consumed already and the waits return at once).
       for (int r = 0; r < 2; ++r)
@@ -267,9 +569,11 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       uint32_t n = 0;
       bool ok = true;
       unsigned long long base = 0;
+      FD_PROF_DECL(pb); FD_PROF_DECL(pg);
       for (int pi = 0; pi < p.n_phases && ok; ++pi) {
         const SllmFdPhase& ph = p.ph[pi];
         const FdPhaseGeom g = fd_geom(ph, cta, G);
+        FD_PROF_T0();
         if (pi == 0) {
           pdl_wait();
           base = fd_ld_acquire_u64(p.sync) / kFdSyncQuantum * kFdSyncQuantum;
@@ -278,22 +582,27 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
           break;
         }
         fd_fence_proxy_async();
+        FD_PROF_ADD(pg);
         int kb = static_cast<int>(g.u0 % g.nkb);
         for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
           const int r = n & 1;
           const uint32_t slot = bpos[r] % kFdBSlots, fill = bpos[r] / kFdBSlots;
+          { FD_PROF_T0();
           if (!mbar_wait(&sh->bempty[r][slot], (fill & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_SMEM_EMPTY, limit)) {
             ok = false;
             break;
           }
+          FD_PROF_ADD(pb); }
           uint8_t* dst = b_ring + (r * kFdBSlots + slot) * kBSlot;
           mbar_expect_tx(&sh->bfull[r][slot], kBTile + BN * 4);
           tma_load_2d(dst, &maps.b[pi], &sh->bfull[r][slot], kb * 128, 0);
-          fd_bulk_load(dst + kBTile, ph.x_scale + static_cast<size_t>(kb) * ph.ld_sb, BN * 4, &sh->bfull[r][slot]);
+          fd_bulk_load(b_scale + (r * kFdBSlots + slot) * BN, ph.x_scale + static_cast<size_t>(kb) * ph.ld_sb, BN * 4,
+                       &sh->bfull[r][slot]);
           ++bpos[r];
           if (++kb == g.nkb) kb = 0;
         }
       }
+      FD_PROF_OUT(17, pb); FD_PROF_OUT(18, pg);
       for (int r = 0; r < 2; ++r)
         for (int s = 0; s < kFdBSlots; ++s) {
           const uint32_t fills = bpos[r] > static_cast<uint32_t>(s) ? (bpos[r] - s + kFdBSlots - 1) / kFdBSlots : 0u;
@@ -310,6 +619,7 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       const int iw = warp - 2;
       uint32_t apos = 0, bpos = 0, mine = 0, n = 0;
       bool ok = true;
+      FD_PROF_DECL(wa); FD_PROF_DECL(wb); FD_PROF_DECL(wt); FD_PROF_DECL(is);
       for (int pi = 0; pi < p.n_phases && ok; ++pi) {
         const FdPhaseGeom g = fd_geom(p.ph[pi], cta, G);
         for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
@@ -318,60 +628,102 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
           const uint32_t use = mine >> 1;
           const uint32_t bslot = bpos % kFdBSlots, bfill = bpos / kFdBSlots;
           uint32_t aslot[2];
+          { FD_PROF_T0();
           for (int half = 0; half <= g.dual && ok; ++half) {
             aslot[half] = (apos + half) % kFdASlots;
             const uint32_t afill = (apos + half) / kFdASlots;
             ok = mbar_wait(&sh->afull[iw][aslot[half]], afill & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL, limit);
           }
+          FD_PROF_ADD(wa); }
+          { FD_PROF_T0();
           if (ok) ok = mbar_wait(&sh->bfull[iw][bslot], bfill & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL, limit);
+          FD_PROF_ADD(wb); }
+          { FD_PROF_T0();
           if (ok) ok = mbar_wait(&sh->tempty[acc], (use & 1) ^ 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_EMPTY, limit);
+          FD_PROF_ADD(wt); }
           if (!ok) break;
+          FD_PROF_T0();
           tc_fence_after();
           const uint64_t bdesc = make_smem_desc_sw128(smem_u32(b_ring + (iw * kFdBSlots + bslot) * kBSlot));
           for (int half = 0; half <= g.dual; ++half) {
             const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + (iw * kFdASlots + aslot[half]) * kFdASlotBytes));
             const uint32_t d = tmem_base + acc * (2 * BN) + half * BN;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0);
+            for (int k = 0; k < 4; ++k)
+              if (k == 0 || !(p.debug & 2)) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0);
           }
+          for (int half = 0; half <= g.dual; ++half) tc_commit(&sh->aempty[iw][aslot[half]]);   // slot reusable once read
           tc_commit(&sh->tfull[acc]);
+          FD_PROF_ADD(is);
           apos += 1 + g.dual;
           ++bpos;
           ++mine;
         }
       }
+      FD_PROF_OUT(iw * 4 + 0, wa); FD_PROF_OUT(iw * 4 + 1, wb); FD_PROF_OUT(iw * 4 + 2, wt); FD_PROF_OUT(iw * 4 + 3, is);
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (128 threads)
-    const int ew = warp - 4;                 // TMEM lane quarter
+    // ------------------------------------------------------------------ epilogue: two groups of 128 threads
+    // Promotion is a chain of long-latency steps per K block (barrier wait, TMEM load, release), so two groups
+    // work on different accumulators at the same time: in a plain phase group g promotes the K blocks of issuer
+    // g; in a gate/up phase group 0 promotes every gate accumulator and group 1 every up accumulator.  At the
+    // end of a tile segment group 1 hands its registers to group 0 through shared memory; group 0 finishes tiles.
+    const int grp = (warp - 4) >> 2;
+    const int ew = (warp - 4) & 3;           // TMEM lane quarter (= warp % 4)
     const int row = ew * 32 + lane;          // row of the weight tile
-    const int et = threadIdx.x - 128;
+    const int et = threadIdx.x - 128 - grp * 128;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
     const int T = p.rows;
-    uint32_t apos[2] = {0u, 0u}, bpos[2] = {0u, 0u};
+    uint32_t bpos[2] = {0u, 0u};
     uint32_t n = 0;
     bool ok = true;
     unsigned long long base = 0;
-    float acc[BN], acc2[BN];
+    float acc[BN];
+    FD_PROF_DECL(wf); FD_PROF_DECL(ld); FD_PROF_DECL(fm); FD_PROF_DECL(seg);
 
     for (int pi = 0; pi < p.n_phases; ++pi) {
       const SllmFdPhase& ph = p.ph[pi];
       const FdPhaseGeom g = fd_geom(ph, cta, G);
-      if (pi == 0) {
-        pdl_wait();
-        base = fd_ld_acquire_u64(p.sync) / kFdSyncQuantum * kFdSyncQuantum;
-      } else if (ok) {
-        if (et == 0) fd_grid_wait(p.sync, base + static_cast<unsigned long long>(pi) * G, abort_flag, p.status, limit);
-        if (fd_epi_any(*abort_flag != 0)) ok = false;
+      float norm_part = 0.f;
+      bool norm_ready = ph.norm_tiles == 0;
+      if (grp == 0) {
+        if (pi == 0) {
+          pdl_wait();
+          base = fd_ld_acquire_u64(p.sync) / kFdSyncQuantum * kFdSyncQuantum;
+        } else if (ok) {
+          if (et == 0) fd_grid_wait(p.sync, base + static_cast<unsigned long long>(pi) * G, abort_flag, p.status, limit);
+          fd_epi_any(false);                 // the group resumes together; a failed wait shows at the next segment end
+        }
+        if (et == 0) fd_stamp(p.trace, cta, pi, 1);         // phase input visible
+        // RMSNorm factor of every token row from the per-block sums of squares of the phase's input: the loads
+        // are issued here (token = et % BN, every (128 / BN)-th block) and first used when a tile is finished,
+        // so their latency hides under the promotion loop.
+        if (ph.norm_tiles > 0) {
+          constexpr int kParts = 128 / BN;
+          const int tok = et % BN, part = et / BN;
+          if (tok < T)
+            for (int i = part; i < ph.norm_tiles; i += kParts)
+              norm_part += __ldcg(ph.ssq_in + static_cast<size_t>(i) * ph.ld_s_out + tok);
+        }
       }
-      // RMSNorm factor of every token row from the per-block sums of squares of the phase's input
-      if (ph.norm_tiles > 0 && et < BN) {
-        float ss = 0.f;
-        if (et < T)
-          for (int i = 0; i < ph.norm_tiles; ++i) ss += __ldcg(ph.ssq_in + static_cast<size_t>(i) * ph.ld_s_out + et);
-        sh->rnorm[et] = rsqrtf(ss / static_cast<float>(ph.norm_dim) + ph.eps);
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      bool first_unit = true;
+      const size_t part_floats = static_cast<size_t>(1 + g.dual) * BN * 128;
+      // Weight scales (one fp32 per weight row and K block) come straight from L2, where the producer's prefetch
+      // cursor has put them: each thread keeps the scales of its next two K blocks in registers.
+      const uint32_t nkb_u = static_cast<uint32_t>(g.nkb);
+      const uint32_t u_end = static_cast<uint32_t>(g.u1);
+      const uint32_t s_stride = g.dual ? 1u : 2u;
+      const int s_rows = ph.dual_off + ph.n;
+      const int s_row_off = row + ((g.dual && grp == 1) ? ph.dual_off : 0);
+      auto load_sa = [&](uint32_t uu) -> float {
+        if (uu >= u_end) return 0.f;
+        const uint32_t t = uu / nkb_u, k = uu - t * nkb_u;
+        const int rg = static_cast<int>(t) * 128 + s_row_off;
+        return rg < s_rows ? __ldg(ph.w_scale + static_cast<size_t>(k) * ph.ld_sa + rg) : 0.f;
+      };
+      uint32_t s_next = static_cast<uint32_t>(g.u0) + (g.dual ? 0u : ((static_cast<uint32_t>(grp) - n) & 1u));
+      float sa_q0 = load_sa(s_next), sa_q1 = load_sa(s_next + s_stride);
+      s_next += 2 * s_stride;
 
       long long u = g.u0;
       while (u < g.u1 && ok) {
@@ -379,323 +731,221 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
         const int kb0 = static_cast<int>(u - static_cast<long long>(tile) * g.nkb);
         int kbe = g.nkb;
         if (g.u1 - u < g.nkb - kb0) kbe = kb0 + static_cast<int>(g.u1 - u);
-        const bool full_tile = kb0 == 0 && kbe == g.nkb;
+        const bool split = !(kb0 == 0 && kbe == g.nkb);
         const bool seg_first = u == g.u0;
 #pragma unroll
-        for (int c = 0; c < BN; ++c) { acc[c] = 0.f; acc2[c] = 0.f; }
+        for (int c = 0; c < BN; ++c) acc[c] = 0.f;
         // ---- promotion: one K block per TMEM accumulator
         for (int kb = kb0; kb < kbe; ++kb, ++n) {
           const int iw = n & 1;
+          const uint32_t bs = bpos[iw] % kFdBSlots;
+          ++bpos[iw];
+          if (!g.dual && iw != grp) continue;
           const uint32_t m = n >> 1;
           const int a = iw * 2 + (m & 1);
-          const uint32_t use = m >> 1;
           // a wait that gives up leaves the loop warp-uniformly; the CTA-wide decision follows the segment
-          if (!__all_sync(0xffffffffu, mbar_wait(&sh->tfull[a], use & 1, abort_flag, p.status,
+          { FD_PROF_T0();
+          if (!__all_sync(0xffffffffu, mbar_wait(&sh->tfull[a], (m >> 1) & 1, abort_flag, p.status,
                                                   SLLM_DEV_TIMEOUT_TMEM_FULL, limit))) {
             *abort_flag = 1;
             break;
           }
+          FD_PROF_ADD(wf); }
           tc_fence_after();
-          const uint32_t as0 = apos[iw] % kFdASlots;
-          const uint32_t bs = bpos[iw] % kFdBSlots;
-          const float* sa_p = reinterpret_cast<const float*>(a_ring + (iw * kFdASlots + as0) * kFdASlotBytes + kFdATile);
-          const float* sb_p = reinterpret_cast<const float*>(b_ring + (iw * kFdBSlots + bs) * kBSlot + kBTile);
-          const float sa = sa_p[row];
-          const uint32_t t0 = lane_addr + a * (2 * BN);
-#pragma unroll
-          for (int c = 0; c < BN / 16; ++c) {
-            uint32_t r[16];
-            tmem_ld16(t0 + c * 16, r);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              acc[c * 16 + j] = fmaf(__uint_as_float(r[j]), sa * sb_p[c * 16 + j], acc[c * 16 + j]);
+          if (first_unit) {
+            first_unit = false;
+            if (et == 0 && grp == 0) fd_stamp(p.trace, cta, pi, 2);       // first accumulator ready
           }
-          uint32_t as1 = 0;
-          if (g.dual) {
-            as1 = (apos[iw] + 1) % kFdASlots;
-            const float sa2 =
-                reinterpret_cast<const float*>(a_ring + (iw * kFdASlots + as1) * kFdASlotBytes + kFdATile)[row];
+          const float sa = sa_q0;
+          sa_q0 = sa_q1;
+          sa_q1 = load_sa(s_next);
+          s_next += s_stride;
+          const float* sb_p = b_scale + (iw * kFdBSlots + bs) * BN;
+          uint32_t r[BN];
+          { FD_PROF_T0();
+          fd_tmem_ld<BN>(lane_addr + a * (2 * BN) + ((g.dual && grp == 1) ? BN : 0), r);
+          tmem_wait_ld();
+          FD_PROF_ADD(ld); }
+          { FD_PROF_T0();
 #pragma unroll
-            for (int c = 0; c < BN / 16; ++c) {
-              uint32_t r[16];
-              tmem_ld16(t0 + BN + c * 16, r);
-              tmem_wait_ld();
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                acc2[c * 16 + j] = fmaf(__uint_as_float(r[j]), sa2 * sb_p[c * 16 + j], acc2[c * 16 + j]);
-            }
-          }
+          for (int c = 0; c < BN; ++c) acc[c] = fmaf(__uint_as_float(r[c]), sa * sb_p[c], acc[c]);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) {
-            mbar_arrive(&sh->tempty[a]);
-            mbar_arrive(&sh->aempty[iw][as0]);
-            if (g.dual) mbar_arrive(&sh->aempty[iw][as1]);
-            mbar_arrive(&sh->bempty[iw][bs]);
+            // either release barrier expects 8 arrivals: both groups' warps once each, or one group's warps twice
+            const uint32_t cnt = g.dual ? 1u : 2u;
+            mbar_arrive_cnt(&sh->tempty[a], cnt);
+            mbar_arrive_cnt(&sh->bempty[iw][bs], cnt);
           }
-          apos[iw] += 1 + g.dual;
-          ++bpos[iw];
-        }
-        if (fd_epi_any(*abort_flag != 0)) {
-          ok = false;
-          break;
+          FD_PROF_ADD(fm); }
         }
         u += kbe - kb0;
 
-        // ---- a tile shared with other CTAs: publish the partial; the last arriver sums all parts in order
-        bool finish = true;
-        if (!full_tile) {
-          const int accs = 1 + g.dual;
-          const size_t part_floats = static_cast<size_t>(accs) * BN * 128;
-          float* my = p.ws + (static_cast<size_t>(2 * cta) + (seg_first ? 0 : 1)) * part_floats;
+        // ---- hand-over: group 1's accumulators travel through shared memory, or, for a split gate/up tile,
+        // both halves go to the workspace
+        const bool both_to_ws = split && g.dual;
+        float* my_part = p.ws + (static_cast<size_t>(2 * cta) + (seg_first ? 0 : 1)) * part_floats;
+        if (both_to_ws) {
+          float* dst = my_part + grp * (BN * 128);
 #pragma unroll
-          for (int c = 0; c < BN; ++c) my[c * 128 + row] = acc[c];
+          for (int c = 0; c < BN; ++c) dst[c * 128 + row] = acc[c];
+          __threadfence();
+        } else if (grp == 1) {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) xchg[c * 128 + row] = acc[c];
+        }
+        if (fd_all_any(*abort_flag != 0)) {      // barrier 2 (256 threads)
+          ok = false;
+          break;
+        }
+        if (grp == 0 && et == 0) fd_stamp(p.trace, cta, pi, 3);         // segment promoted
+        float up[BN];
+        if (grp == 0 && !both_to_ws) {
           if (g.dual) {
 #pragma unroll
-            for (int c = 0; c < BN; ++c) my[(BN + c) * 128 + row] = acc2[c];
-          }
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          const long long tu0 = static_cast<long long>(tile) * g.nkb;
-          const int first_c = fd_cta_of_unit(tu0, g.U, G);
-          const int last_c = fd_cta_of_unit(tu0 + g.nkb - 1, g.U, G);
-          if (et == 0) {
-            // CTAs with an empty unit range (fewer units than CTAs) contribute no part
-            int nparts = 0;
-            for (int j = first_c; j <= last_c; ++j) nparts += ((j + 1) * g.U / G > j * g.U / G) ? 1 : 0;
-            const int old = atomicAdd(&p.counters[tile], 1);
-            const int last = old == nparts - 1;
-            if (last) p.counters[tile] = 0;
-            sh->is_last = last;
-            __threadfence();
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          finish = sh->is_last != 0;
-          if (finish) {
+            for (int c = 0; c < BN; ++c) up[c] = xchg[c * 128 + row];
+          } else {
 #pragma unroll
-            for (int c = 0; c < BN; ++c) { acc[c] = 0.f; acc2[c] = 0.f; }
+            for (int c = 0; c < BN; ++c) acc[c] += xchg[c * 128 + row];
+          }
+        }
+        // ---- a tile shared with other CTAs: publish the partial; the last arriver sums all parts in order
+        const long long tu0 = static_cast<long long>(tile) * g.nkb;
+        int first_c = 0, last_c = 0;
+        if (split) {
+          first_c = fd_cta_of_unit(tu0, g.U, G);
+          last_c = fd_cta_of_unit(tu0 + g.nkb - 1, g.U, G);
+          if (grp == 0) {
+            if (!g.dual) {
+#pragma unroll
+              for (int c = 0; c < BN; ++c) my_part[c * 128 + row] = acc[c];
+              __threadfence();
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            if (et == 0) {
+              // CTAs with an empty unit range (fewer units than CTAs) contribute no part
+              int nparts = 0;
+              for (int j = first_c; j <= last_c; ++j) nparts += ((j + 1) * g.U / G > j * g.U / G) ? 1 : 0;
+              const int old = atomicAdd(&p.counters[tile], 1);
+              const int last = old == nparts - 1;
+              if (last) p.counters[tile] = 0;
+              sh->is_last = last;
+              __threadfence();
+            }
+          }
+        }
+        asm volatile("bar.sync 3, 256;" ::: "memory");     // xchg consumed, is_last visible
+        if (split) {
+          if (sh->is_last == 0) continue;
+          // ---- last arriver: sum the parts in CTA order.  With up to 8 parts the loads of all parts of 8 token
+          // columns are in flight together (one L2 round trip per 8 columns); in a plain phase the two groups
+          // share the columns, in a gate/up phase each sums its own half of the accumulators.
+          const int np = last_c - first_c + 1;
+          const bool fast = np <= kFdFastParts && g.U >= G;   // every CTA of the range holds a part
+          const float* base0 = p.ws + (g.dual ? grp * (BN * 128) : 0) + row;
+          if (fast) {
+            uint32_t offs[kFdFastParts];
+#pragma unroll
+            for (int jj = 0; jj < kFdFastParts; ++jj) {
+              const long long j = first_c + jj;
+              const long long sj = j * g.U / G;
+              offs[jj] = static_cast<uint32_t>((static_cast<size_t>(2 * j) + (sj >= tu0 ? 0 : 1)) * part_floats);
+            }
+            // sums land in shared memory: plain phase -> stage (each group half of the columns); gate/up phase ->
+            // gate in stage (group 0), up in xchg (group 1)
+            float* dst = ((g.dual && grp == 1) ? xchg : stage) + row;
+            const int col0 = g.dual ? 0 : grp * (BN / 2);
+            const int ncol = g.dual ? BN : BN / 2;
+#pragma unroll 1
+            for (int cc = 0; cc < ncol; cc += 8) fd_sum_parts(base0, offs, np, col0 + cc, dst);
+          } else if (grp == 0 || g.dual) {
+#pragma unroll
+            for (int c = 0; c < BN; ++c) acc[c] = 0.f;
             for (int j = first_c; j <= last_c; ++j) {
               const long long sj = j * g.U / G;
               if ((j + 1) * g.U / G == sj) continue;
-              const float* src = p.ws + (static_cast<size_t>(2 * j) + (sj >= tu0 ? 0 : 1)) * part_floats;
+              const float* src = base0 + (static_cast<size_t>(2 * j) + (sj >= tu0 ? 0 : 1)) * part_floats;
 #pragma unroll
-              for (int c = 0; c < BN; ++c) acc[c] += __ldcg(src + c * 128 + row);
-              if (g.dual) {
-#pragma unroll
-                for (int c = 0; c < BN; ++c) acc2[c] += __ldcg(src + (BN + c) * 128 + row);
-              }
+              for (int c = 0; c < BN; ++c) acc[c] += __ldcg(src + c * 128);
             }
           }
-          // the flag in shared memory is rewritten by the next partial tile
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (fast) {
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+            if (grp == 0) {
+#pragma unroll
+              for (int c = 0; c < BN; ++c) acc[c] = stage[c * 128 + row];
+              if (g.dual) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) up[c] = xchg[c * 128 + row];
+              }
+            }
+            asm volatile("bar.sync 3, 256;" ::: "memory");
+          } else if (g.dual) {
+            if (grp == 1) {
+#pragma unroll
+              for (int c = 0; c < BN; ++c) xchg[c * 128 + row] = acc[c];
+            }
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+            if (grp == 0) {
+#pragma unroll
+              for (int c = 0; c < BN; ++c) up[c] = xchg[c * 128 + row];
+            }
+            asm volatile("bar.sync 3, 256;" ::: "memory");
+          }
         }
-        if (!finish) continue;
+        if (grp == 1) continue;              // group 1 goes on with the next segment
+        if (et == 0) fd_stamp(p.trace, cta, pi, 4);         // tile complete in registers
 
-        // ---- tile epilogue: norm factor / activation, then staged as stage[token][row of the tile]
+        // ---- tile epilogue (group 0): norm factor / activation, then staged as stage[token][row of the tile]
         const bool has_norm = ph.norm_tiles > 0;
+        if (!norm_ready) {
+          constexpr int kParts = 128 / BN;
+          stage[et] = norm_part;                 // [part][token]
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et < BN) {
+            float ss = 0.f;
+#pragma unroll
+            for (int q = 0; q < kParts; ++q) ss += stage[q * BN + et];
+            sh->rnorm[et] = rsqrtf(ss / static_cast<float>(ph.norm_dim) + ph.eps);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          norm_ready = true;
+        }
 #pragma unroll
         for (int c = 0; c < BN; ++c) {
           float v = acc[c];
-          if (has_norm) v *= sh->rnorm[c];
+          const float rn = has_norm ? sh->rnorm[c] : 1.f;
+          v *= rn;
           if (g.dual) {
-            const float up = acc2[c] * (has_norm ? sh->rnorm[c] : 1.f);
             const float a = ph.act == 0 ? fd_silu(v) : fd_gelu_tanh(v);
-            v = fd_bf16r(a) * up;
+            v = fd_bf16r(a) * (up[c] * rn);
           }
           stage[c * 128 + row] = v;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-
-        const int n0 = tile * 128 + lane * 4;     // first of this lane's four outputs of a token row
-        bool comm_ok = true;
-        if (ph.epilogue == SLLM_FD_RESID_QUANT && p.comm.world > 1) {
-          // ---- cross-rank sum of the tile: push the partial (bf16) to every rank, flag, wait, sum in rank order
-          const FdComm& cm = p.comm;
-          if (et == 0) {
-            const uint32_t e1 = cm.epoch[tile] + 1;
-            cm.epoch[tile] = e1;
-            sh->epoch = e1;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          const uint32_t e = sh->epoch;
-          const long long region = static_cast<long long>(e & 1) * cm.world;
-          const long long toff = static_cast<long long>(tile) * (128 * BN);
-          for (int c = ew; c < T; c += 4) {
-            const float4 x = *reinterpret_cast<const float4*>(stage + c * 128 + lane * 4);
-            uint2 w;
-            *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(x.x, x.y);
-            *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(x.z, x.w);
-            const long long off = (region + cm.rank) * cm.cap_elems + toff + c * 128 + lane * 4;
-            for (int peer = 0; peer < cm.world; ++peer) *reinterpret_cast<uint2*>(cm.recv[peer] + off) = w;
-          }
-          __threadfence_system();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et < cm.world && et != cm.rank) {
-            fd_st_release_sys(cm.flags[et] + static_cast<size_t>(tile) * cm.world + cm.rank, e);
-            const uint32_t* f = cm.flags[cm.rank] + static_cast<size_t>(tile) * cm.world + et;
-            uint32_t spins = 0;
-            long long t0 = 0;
-            while (static_cast<int32_t>(fd_ld_acquire_sys(f) - e) < 0) {
-              ++spins;
-              if (spins == 1024) t0 = clock64();
-              if (spins > 1024 && (spins & 63) == 0) {
-                if (*abort_flag) break;
-                if (clock64() - t0 > limit) {
-                  *abort_flag = 1;
-                  if (p.status) atomicCAS(p.status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
-                  break;
-                }
-              }
-            }
-          }
-          if (fd_epi_any(*abort_flag != 0)) { comm_ok = false; ok = false; }
-          if (comm_ok) {
-            for (int c = ew; c < T; c += 4) {
-              float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int src = 0; src < cm.world; ++src) {
-                const uint2 w = __ldcg(reinterpret_cast<const uint2*>(
-                    cm.recv[cm.rank] + (region + src) * cm.cap_elems + toff + c * 128 + lane * 4));
-                const __nv_bfloat162 h0 = *reinterpret_cast<const __nv_bfloat162*>(&w.x);
-                const __nv_bfloat162 h1 = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
-                s.x += __bfloat162float(h0.x); s.y += __bfloat162float(h0.y);
-                s.z += __bfloat162float(h1.x); s.w += __bfloat162float(h1.y);
-              }
-              *reinterpret_cast<float4*>(stage + c * 128 + lane * 4) = s;   // same lane reads it back below
-            }
-          }
-        }
-
-        if (comm_ok) {
-          for (int c = ew; c < T; c += 4) {
-            const float4 x = *reinterpret_cast<const float4*>(stage + c * 128 + lane * 4);
-            float v[4] = {x.x, x.y, x.z, x.w};
-            if (ph.epilogue == SLLM_FD_PLAIN) {
-              __nv_bfloat16* y = static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0;
-              const __nv_bfloat16* res =
-                  ph.residual ? static_cast<const __nv_bfloat16*>(ph.residual) + static_cast<size_t>(c) * ph.ldy + n0 : nullptr;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (n0 + j < ph.n) {
-                  float o = v[j];
-                  if (res) o += __bfloat162float(res[j]);
-                  if (ph.softcap > 0.f) o = ph.softcap * tanhf(o / ph.softcap);
-                  y[j] = __float2bfloat16_rn(o);
-                }
-              }
-            } else if (ph.epilogue == SLLM_FD_RESID_QUANT || ph.epilogue == SLLM_FD_SILU_QUANT) {
-              if (ph.epilogue == SLLM_FD_RESID_QUANT) {
-                const uint2 rr = *reinterpret_cast<const uint2*>(
-                    static_cast<const __nv_bfloat16*>(ph.residual) + static_cast<size_t>(c) * ph.ldy + n0);
-                const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
-                const __nv_bfloat162 r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
-                v[0] += __bfloat162float(r0.x); v[1] += __bfloat162float(r0.y);
-                v[2] += __bfloat162float(r1.x); v[3] += __bfloat162float(r1.y);
-                uint2 hw;
-                *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
-                *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
-                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
-              }
-              float amax = 0.f, ss = 0.f;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                v[j] = fd_bf16r(v[j]);
-                ss += v[j] * v[j];
-                const float a = fabsf(v[j]);
-                if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
-              }
-              amax = warp_max(amax);
-              const float scale = amax > 0.f ? amax / kFdE4M3Max : 1.f;
-              uint32_t q = 0;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
-              *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ph.q_out) + static_cast<size_t>(c) * ph.n + n0) = q;
-              if (lane == 0) ph.s_out[static_cast<size_t>(tile) * ph.ld_s_out + c] = scale;
-              if (ph.ssq_out) {
-                ss = warp_sum(ss);
-                if (lane == 0) ph.ssq_out[static_cast<size_t>(tile) * ph.ld_s_out + c] = ss;
-              }
-            } else {
-              // ROPE_KV: tile = head index (q heads, then k heads, then v heads), lane holds dims 4 lane .. 4 lane + 3
-              const SllmFdRope& rp = p.rope;
-              const int head = tile;
-              const bool is_q = head < rp.hq;
-              const bool is_v = head >= rp.hq + rp.hkv;
-              const int pos = rp.positions[c];
-              if (!is_v) {
-                const int half = rp.rotary_dim >> 1;
-                const int lane_off = half >> 2;          // partner lane distance (half / 4), a power of two
-                float pv[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) pv[j] = __shfl_xor_sync(0xffffffffu, v[j], lane_off);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const int i = lane * 4 + j;
-                  if (i < rp.rotary_dim) {
-                    const bool lo = i < half;
-                    const int fi = lo ? i : i - half;
-                    float sn, cs;
-                    sincosf(static_cast<float>(pos) * sh->inv_freq[fi], &sn, &cs);
-                    const float a = lo ? v[j] : pv[j], b = lo ? pv[j] : v[j];
-                    v[j] = lo ? a * cs - b * sn : b * cs + a * sn;
-                  }
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) v[j] = fd_bf16r(v[j]);
-              if (is_q) {
-                uint2 hw;
-                *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
-                *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
-                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
-              } else {
-                const int kvh = is_v ? head - rp.hq - rp.hkv : head - rp.hq;
-                const int blk = rp.block_table[static_cast<size_t>(rp.seq_index[c]) * rp.max_blocks + pos / rp.page_size];
-                const size_t slot = (static_cast<size_t>(blk) * rp.hkv + kvh) * rp.page_size + pos % rp.page_size;
-                if (!rp.kv_fp8) {
-                  uint2 hw;
-                  *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
-                  *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
-                  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
-                  *reinterpret_cast<uint2*>(dst) = hw;
-                } else {
-                  float amax = 0.f;
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float a = fabsf(v[j]);
-                    if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
-                  }
-                  amax = warp_max(amax);
-                  const float st = is_v ? rp.v_static : rp.k_static;
-                  const float scale = st > 0.f ? st : (amax > 0.f ? amax / kFdE4M3Max : 1.f);
-                  uint32_t q = 0;
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
-                  uint8_t* dst = static_cast<uint8_t*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
-                  *reinterpret_cast<uint32_t*>(dst) = q;
-                  if (lane == 0 && st <= 0.f) (is_v ? rp.v_scale : rp.k_scale)[slot] = scale;
-                }
-              }
-            }
-          }
-        }
+        if (!fd_finish_columns<BN>(p, ph, sh, stage, tile, ew, lane, et, T, abort_flag, limit)) ok = false;
         // the staging buffer is reused by the next tile
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
 
-      // ---- publish the phase: every output of this CTA is written; arrive at the grid barrier
-      __threadfence();
-      fd_fence_proxy_async();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) {
-        // Barrier k of a launch completes at base + k G.  The arrivals of a whole launch add up to kFdSyncQuantum
-        // whatever the grid and the phase count (CTA 0 tops up its last arrival), so the counter is a multiple of the
-        // quantum between launches and a CTA that starts late still derives the same base from it.
-        unsigned long long add = 1ull;
-        if (pi == p.n_phases - 1 && cta == 0) add += kFdSyncQuantum - static_cast<unsigned long long>(p.n_phases) * G;
-        fd_red_release_add_u64(p.sync, add);
+      if (grp == 0) {
+        // ---- publish the phase: every output of this CTA is written; arrive at the grid barrier
+        if (et == 0) fd_stamp(p.trace, cta, pi, 5);           // all tiles of this CTA written
+        __threadfence();
+        fd_fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          // Barrier k of a launch completes at base + k G.  The arrivals of a whole launch add up to kFdSyncQuantum
+          // whatever the grid and the phase count (CTA 0 tops up its last arrival), so the counter is a multiple of
+          // the quantum between launches and a CTA that starts late still derives the same base from it.
+          unsigned long long add = 1ull;
+          if (pi == p.n_phases - 1 && cta == 0) add += kFdSyncQuantum - static_cast<unsigned long long>(p.n_phases) * G;
+          fd_red_release_add_u64(p.sync, add);
+          fd_stamp(p.trace, cta, pi, 6);
+        }
       }
     }
+    if (et == 0) { FD_PROF_OUT(8 + grp * 4 + 0, wf); FD_PROF_OUT(8 + grp * 4 + 1, ld); FD_PROF_OUT(8 + grp * 4 + 2, fm); }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -767,7 +1017,8 @@ static int fd_sm_count() {
 
 template <int BN>
 constexpr size_t fd_smem_bytes() {
-  return 1024 + 2 * kFdASlots * kFdASlotBytes + 2 * kFdBSlots * fd_b_slot<BN>() + BN * 128 * 4 + sizeof(FdShared);
+  return 1024 + 2 * kFdASlots * kFdASlotBytes + 2 * kFdBSlots * (fd_b_slot<BN>() + BN * 4) + 2 * BN * 128 * 4 +
+         sizeof(FdShared);
 }
 
 template <int BN>
@@ -801,6 +1052,17 @@ struct SllmCommDescFd {   // same layout as the descriptor of sllm_gemm_allreduc
   void* epoch;
 };
 
+static unsigned long long* g_fd_trace = nullptr;
+static int g_fd_lookahead = kFdLookaheadDefault;
+static int g_fd_debug = 0;
+SLLM_EXPORT void sllm_fused_decode_set_debug(int bits) { g_fd_debug = bits; }
+// Tuning knob: L2 prefetch distance of the weight producer in 16 KB tiles per CTA (0 = no prefetch).
+SLLM_EXPORT void sllm_fused_decode_set_lookahead(int tiles) { g_fd_lookahead = tiles < 0 ? 0 : (tiles > 256 ? 256 : tiles); }
+// Profiling aid: device buffer of [CTAs][4][8] u64 that subsequent launches fill with globaltimer stamps
+// (0 set-up done, 1 phase input visible, 2 first accumulator ready, 3 last segment promoted, 4 last tile complete,
+// 5 outputs written, 6 arrived at the barrier); null switches it off.
+SLLM_EXPORT void sllm_fused_decode_set_trace(void* dev_buf) { g_fd_trace = static_cast<unsigned long long*>(dev_buf); }
+
 SLLM_EXPORT long long sllm_fused_decode_ws_floats(int grid) {
   if (grid <= 0) grid = fd_sm_count();
   return static_cast<long long>(2) * grid * 2 * 32 * 128;
@@ -822,6 +1084,9 @@ SLLM_EXPORT int sllm_fused_decode(const SllmFdDesc* d, void* stream) {
   p.rope = d->rope;
   p.ws = d->ws; p.counters = d->counters; p.sync = d->sync; p.status = d->status;
   p.wait_limit = d->wait_limit_cycles > 0 ? d->wait_limit_cycles : kWaitLimitCycles;
+  p.trace = g_fd_trace;
+  p.lookahead = g_fd_lookahead;
+  p.debug = g_fd_debug;
   for (int i = 0; i < d->n_phases; ++i) {
     const SllmFdPhase& ph = d->phase[i];
     if (!ph.w || !ph.w_scale || !ph.x || !ph.x_scale || ph.n <= 0 || ph.k <= 0 || (ph.k & 127) || (ph.n & 3))

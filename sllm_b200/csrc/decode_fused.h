@@ -96,6 +96,12 @@ long long sllm_fused_decode_ws_floats(int grid);
    per-block sums of squares.  d must be a multiple of 128. */
 int sllm_embed_quant(const void* table, const int* ids, void* h, void* q_out, float* s_out, float* ssq_out, int ld_s,
                      int rows, int d, int vocab, float scale, void* stream);
+/* Profiling aid: device buffer of [CTAs][4][8] 64-bit words that later launches fill with globaltimer stamps per phase
+   (0 set-up done, 1 phase input visible, 2 first accumulator ready, 3 last segment promoted, 4 last tile complete,
+   5 outputs written, 6 arrived at the grid barrier); null switches it off. */
+void sllm_fused_decode_set_trace(void* dev_buf);
+/* Tuning knob: L2 prefetch distance of the weight producer, in 16 KB tiles per CTA (0 = none). */
+void sllm_fused_decode_set_lookahead(int tiles);
 /* sizeof / offsetof records of the descriptor structs for a layout check by foreign-language bindings:
    writes up to n ints, returns how many the library has. */
 int sllm_fused_decode_abi(int* out, int n);

@@ -53,6 +53,8 @@ _lib.EXTRA_KERNEL_SIGNATURES.update({
     "sllm_fused_decode_ws_floats": (C.c_longlong, [C.c_int]),
     "sllm_embed_quant": (C.c_int, [C.c_void_p] * 6 + [C.c_int] * 4 + [C.c_float, C.c_void_p]),
     "sllm_fused_decode_abi": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
+    "sllm_fused_decode_set_trace": (None, [C.c_void_p]),
+    "sllm_fused_decode_set_lookahead": (None, [C.c_int]),
 })
 
 _abi_checked = False
@@ -116,6 +118,17 @@ def reset_state(device: torch.device) -> None:
 def _ld(t: torch.Tensor) -> int:
     """Leading dimension of a 2-D plane; a single-row tensor may report any stride for dimension 0."""
     return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def set_trace(buf: Optional[torch.Tensor]) -> None:
+    """Profiling aid: later launches write per-CTA, per-phase globaltimer stamps into ``buf`` (int64 [CTAs, 4, 8]);
+    None switches it off."""
+    _lib.kernels().sllm_fused_decode_set_trace(None if buf is None else buf.data_ptr())
+
+
+def set_lookahead(tiles: int) -> None:
+    """Tuning knob: how many 16 KB weight tiles per CTA the producer prefetches into L2 ahead of its ring."""
+    _lib.kernels().sllm_fused_decode_set_lookahead(int(tiles))
 
 
 def phase(epilogue: int, w, w_scale, x, x_scale, *, n: int, k: int, dual_off: int = 0, ssq_in=None, norm_dim: int = 0,

@@ -45,7 +45,9 @@ def parse_key_file(text: str) -> list:
 
 
 class CredentialStore:
-    """open() = no authentication; from_user_key / from_key_file = protected."""
+    """open() = no authentication for the user surface and NO admin access; from_user_key = one user-role key (the
+    legacy ``--api-key-env`` configuration, which never administers models); from_key_file = explicit user / admin keys.
+    Same separation as the reference (crates/sllm-server/src/security.rs:118-132 and its test at :406)."""
 
     def __init__(self, entries: Optional[list], path: Optional[str] = None):
         self._entries = entries
@@ -60,7 +62,7 @@ class CredentialStore:
     def from_user_key(cls, token: str):
         if not MIN_TOKEN_BYTES <= len(token.encode()) <= MAX_TOKEN_BYTES:
             raise CredentialError("token length out of range")
-        return cls([("admin", _digest(token))])
+        return cls([("user", _digest(token))])
 
     @classmethod
     def from_key_file(cls, path: str):
@@ -76,9 +78,10 @@ class CredentialStore:
         return self._entries is not None
 
     def role_for(self, authorization_header: Optional[str]) -> Optional[str]:
-        """Returns 'admin', 'user' or None (rejected).  An open store grants admin to everyone."""
+        """Returns 'admin', 'user' or None (rejected).  An open store makes every caller a user; admin always needs an
+        explicit ``admin:`` key from a key file."""
         if self._entries is None:
-            return "admin"
+            return "user"
         if not authorization_header or not authorization_header.startswith("Bearer "):
             return None
         d = _digest(authorization_header[7:])

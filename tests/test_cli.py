@@ -245,9 +245,11 @@ def test_server_binary_ready_serve_and_shutdown_audit(model, tmp_path):
     manifest = tmp_path / "models.json"
     manifest.write_text(json.dumps({"schema_version": "sllm-model-manifest-v1", "models": [
         {"alias": "tiny", "gguf": model[0], "derived_lock": model[1], "preload": False, "max_batch": 4}]}))
-    env = dict(os.environ, SLLM_TEST_KEY="k" * 32, PYTHONPATH=ROOT)
+    keys = tmp_path / "keys"
+    keys.write_text("user:" + "k" * 32 + "\nadmin:" + "a" * 32 + "\n")
+    env = dict(os.environ, SLLM_TEST_KEY="k" * 32, SLLM_TEST_ADMIN_KEY="a" * 32, PYTHONPATH=ROOT)
     proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "sllm-server"), "--models", str(manifest), "--cpu",
-                             "--listen", f"127.0.0.1:{port}", "--api-key-env", "SLLM_TEST_KEY", "--metrics", "--prefix-cache",
+                             "--listen", f"127.0.0.1:{port}", "--api-key-file", str(keys), "--metrics", "--prefix-cache",
                              "--max-batch", "4", "--shutdown-timeout-seconds", "5"],
                             stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
     try:
@@ -263,8 +265,12 @@ def test_server_binary_ready_serve_and_shutdown_audit(model, tmp_path):
         rc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "sllm"), "models", "list", "--server", base,
                              "--api-key-env", "SLLM_TEST_KEY"], capture_output=True, text=True, env=env)
         assert rc.returncode == 0 and "tiny" in rc.stdout
+        # a user key cannot administer models; the admin key can
         rc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "sllm"), "models", "unload", "tiny", "--server", base,
                              "--api-key-env", "SLLM_TEST_KEY"], capture_output=True, text=True, env=env)
+        assert rc.returncode == 1
+        rc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "sllm"), "models", "unload", "tiny", "--server", base,
+                             "--api-key-env", "SLLM_TEST_ADMIN_KEY"], capture_output=True, text=True, env=env)
         assert rc.returncode == 0 and json.loads(rc.stdout)["state"] == "unloaded"
         rc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "sllm"), "models", "list", "--server",
                              "http://example.com:80"], capture_output=True, text=True, env=env)

@@ -166,7 +166,9 @@ def test_auth_roles_keys_reload_and_anthropic_header(tmp_path):
     assert c.get("/v1/models", headers={"authorization": "Bearer nope-nope"}).json()["error"]["code"] == "invalid_api_key"
     uh, ah = {"authorization": "Bearer user-token-1"}, {"authorization": "Bearer admin-token-1"}
     assert c.get("/v1/models", headers=uh).json()["data"][0]["id"] == MODEL
-    assert c.get("/slots", headers=uh).status_code == 403 and c.get("/slots", headers=ah).status_code == 200
+    assert c.get("/slots", headers=uh).status_code == 403 and c.get("/slots", headers=ah).json() == {"slots": []}
+    assert c.post("/admin/slots/12345/cancel", headers=uh).status_code == 403
+    assert c.post("/admin/slots/12345/cancel", headers=ah).status_code == 404
     assert c.get("/metrics", headers=uh).status_code == 200
     kf.write_text("user:user-token-2\nadmin:admin-token-1\n")
     assert c.post("/admin/keys/reload", headers=ah).json()["keys"] == 2
@@ -178,6 +180,23 @@ def test_auth_roles_keys_reload_and_anthropic_header(tmp_path):
     r = c.post("/v1/messages", json={"model": MODEL, "max_tokens": 5, "messages": [{"role": "user", "content": "hi"}]},
                headers={"anthropic-version": "2023-06-01"})
     assert r.status_code == 401 and r.json()["type"] == "error" and r.json()["error"]["type"] == "authentication_error"
+
+
+def test_open_and_legacy_user_key_roles_are_separated():
+    """An open store and the single legacy key grant the user surface only; admin needs an explicit admin key."""
+    open_store = CredentialStore.open()
+    assert open_store.role_for(None) == "user" and not open_store.protected
+    legacy = CredentialStore.from_user_key("user-secret")
+    assert legacy.role_for("Bearer user-secret") == "user"
+    assert legacy.role_for("Bearer other-secret") is None and legacy.role_for("Basic user-secret") is None
+    c, _ = client(credentials=legacy)
+    h = {"authorization": "Bearer user-secret"}
+    assert c.get("/v1/models", headers=h).status_code == 200
+    for path in ("/admin/slots/1/cancel", "/admin/keys/reload", f"/admin/models/{MODEL}/unload", "/admin/models/evict-idle"):
+        assert c.post(path, headers=h).status_code == 403, path
+    c_open, _ = client()
+    for path in ("/admin/slots/1/cancel", f"/admin/models/{MODEL}/load", "/admin/models/evict-idle"):
+        assert c_open.post(path).status_code == 403, path
 
 
 def test_metrics_props_slots_and_lifecycle():
@@ -193,8 +212,8 @@ def test_metrics_props_slots_and_lifecycle():
     assert "hello" not in text
     p = c.get("/props").json()
     assert p["lifecycle"] == "ready" and p["models"][0]["id"] == MODEL and "features" in p
-    assert c.get("/slots").json() == {"slots": []}
-    assert c.post("/admin/slots/12345/cancel").status_code == 404
+    assert c.get("/slots").status_code == 403                             # admin surface: closed without an admin key
+    assert c.post("/admin/slots/12345/cancel").status_code == 403      # an open store never grants admin
     c2, _ = client()
     assert c2.get("/metrics").status_code == 404          # opt-in
     life = ServerLifecycle()
