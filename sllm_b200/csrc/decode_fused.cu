@@ -88,7 +88,15 @@ struct __align__(16) FdShared {
   int is_last;
   uint32_t epoch;
   float rnorm[32];
+  float norm_scratch[128];
   float inv_freq[64];
+  int rope_pos[32];            // position and KV page of every token row (ROPE_KV launches)
+  int rope_page[32];
+  // the launch descriptors, copied from kernel-parameter space once: a run-time phase index (and the out-of-line
+  // tile epilogue) would otherwise read them through generic loads of the parameter window on every use
+  SllmFdPhase ph[SLLM_FD_MAX_PHASES];
+  SllmFdRope rope;
+  FdComm comm;
 };
 
 __device__ __forceinline__ float fd_silu(float x) { return x / (1.f + __expf(-x)); }
@@ -202,22 +210,23 @@ __device__ __forceinline__ void fd_stamp(unsigned long long* trace, int cta, int
 #endif
 
 // CTA that owns unit u when U units are dealt to G CTAs as [c U / G, (c + 1) U / G).
-__device__ __forceinline__ int fd_cta_of_unit(long long u, long long U, int G) {
-  return static_cast<int>(((u + 1) * G - 1) / U);
+// (all unit arithmetic is 32-bit: the launcher checks that units x (CTAs + 1) stays below 2^31)
+__device__ __forceinline__ int fd_cta_of_unit(uint32_t u, uint32_t U, int G) {
+  return static_cast<int>(((u + 1u) * static_cast<uint32_t>(G) - 1u) / U);
 }
 
 struct FdPhaseGeom {
   int tiles, nkb, dual;
-  long long U, u0, u1;
+  uint32_t U, u0, u1;
 };
 __device__ __forceinline__ FdPhaseGeom fd_geom(const SllmFdPhase& ph, int cta, int G) {
   FdPhaseGeom g;
   g.tiles = (ph.n + 127) >> 7;
   g.nkb = ph.k >> 7;
   g.dual = ph.dual_off > 0 ? 1 : 0;
-  g.U = static_cast<long long>(g.tiles) * g.nkb;
-  g.u0 = cta * g.U / G;
-  g.u1 = (cta + 1) * g.U / G;
+  g.U = static_cast<uint32_t>(g.tiles) * static_cast<uint32_t>(g.nkb);
+  g.u0 = static_cast<uint32_t>(cta) * g.U / static_cast<uint32_t>(G);
+  g.u1 = static_cast<uint32_t>(cta + 1) * g.U / static_cast<uint32_t>(G);
   return g;
 }
 
@@ -235,18 +244,14 @@ __device__ __forceinline__ void mbar_arrive_cnt(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
 
-// Per-token-row part of a tile epilogue, run by the 128 threads of epilogue group 0 after the tile has been staged
-// as stage[token][row of the tile]: warp w takes tokens w, w + 4, ...; lane l owns outputs 4 l .. 4 l + 3 of the tile.
-// Kept out of line and rolled: it runs once per tile, so its size (instruction fetch), not its issue rate, matters.
-// Returns false when the cross-rank exchange gave up.
+// Cross-rank sum of a staged tile (tensor parallelism), run by the 128 threads of epilogue group 0: push the partial
+// (bf16) to every rank, flag, wait (bounded), sum in rank order back into the staging buffer.
 template <int BN>
-__device__ __noinline__ bool fd_finish_columns(const FdParams& p, const SllmFdPhase& ph, FdShared* sh, float* stage,
-                                               int tile, int ew, int lane, int et, int T, volatile int* abort_flag,
-                                               long long limit) {
-  const int n0 = tile * 128 + lane * 4;     // first of this lane's four outputs of a token row
-  if (ph.epilogue == SLLM_FD_RESID_QUANT && p.comm.world > 1) {
+__device__ __noinline__ bool fd_comm_sum_tile(int* status, FdShared* sh, float* stage, int tile, int ew, int lane, int et,
+                                              int T, volatile int* abort_flag, long long limit) {
+  {
     // ---- cross-rank sum of the tile: push the partial (bf16) to every rank, flag, wait, sum in rank order
-    const FdComm& cm = p.comm;
+    const FdComm& cm = sh->comm;
     if (et == 0) {
       const uint32_t e1 = cm.epoch[tile] + 1;
       cm.epoch[tile] = e1;
@@ -279,7 +284,7 @@ __device__ __noinline__ bool fd_finish_columns(const FdParams& p, const SllmFdPh
           if (*abort_flag) break;
           if (clock64() - t0 > limit) {
             *abort_flag = 1;
-            if (p.status) atomicCAS(p.status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
+            if (status) atomicCAS(status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
             break;
           }
         }
@@ -297,22 +302,79 @@ __device__ __noinline__ bool fd_finish_columns(const FdParams& p, const SllmFdPh
         s.x += __bfloat162float(h0.x); s.y += __bfloat162float(h0.y);
         s.z += __bfloat162float(h1.x); s.w += __bfloat162float(h1.y);
       }
-      *reinterpret_cast<float4*>(stage + c * 128 + lane * 4) = s;   // the same lane reads it back below
+      *reinterpret_cast<float4*>(stage + c * 128 + lane * 4) = s;
     }
   }
 
-  const __nv_bfloat16* res_base = static_cast<const __nv_bfloat16*>(ph.residual);
-  const bool resid = ph.epilogue == SLLM_FD_RESID_QUANT;
-  // the residual of the next token row is requested while the current one is processed
-  uint2 res_next = make_uint2(0u, 0u);
-  if (resid && ew < T) res_next = *reinterpret_cast<const uint2*>(res_base + static_cast<size_t>(ew) * ph.ldy + n0);
+  return true;
+}
+
+// Tile epilogue, run by all 256 epilogue threads.  On entry the raw sums of the tile are in stage[token][row]
+// (group 1's share of a plain tile, or the up sums of a gate/up tile, in xchg).  Step 1: every thread rewrites half of
+// the token columns of its row in place (residual, norm factor, activation).  Step 2 (tensor-parallel launches): the
+// tile is summed across ranks.  Step 3: warp w of 8 takes token rows w, w + 8, ...; lane l owns outputs 4 l .. 4 l + 3
+// and writes / quantises them.  Kept out of line and rolled: it runs once per tile.
+// Returns false when the cross-rank exchange gave up.
+template <int BN>
+__device__ __noinline__ bool fd_finish_tile(int* status, const SllmFdPhase& ph, FdShared* sh, float* stage,
+                                            const float* xchg, int tile, int grp, int ew, int lane, int et, int T,
+                                            int dual, int add_xchg, float norm_part, bool& norm_ready,
+                                            volatile int* abort_flag, long long limit) {
+  const int row = ew * 32 + lane;
+  const bool has_norm = ph.norm_tiles > 0;
+  if (!norm_ready) {
+    // the norm factors of the phase are reduced the first time a tile needs them
+    constexpr int kParts = 128 / BN;
+    if (grp == 0) sh->norm_scratch[et] = norm_part;      // [part][token]
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    if (grp == 0 && et < BN) {
+      float ss = 0.f;
+#pragma unroll
+      for (int q = 0; q < kParts; ++q) ss += sh->norm_scratch[q * BN + et];
+      sh->rnorm[et] = rsqrtf(ss / static_cast<float>(ph.norm_dim) + ph.eps);
+    }
+    norm_ready = true;
+  }
+  asm volatile("bar.sync 2, 256;" ::: "memory");          // sums and norm factors visible
+  {
+    // tensor-parallel launches sum the tile across ranks afterwards: the residual then joins on rank 0 only
+    const bool resid = ph.epilogue == SLLM_FD_RESID_QUANT && (sh->comm.world <= 1 || sh->comm.rank == 0);
+    const int act = ph.act;
+    // residual stream: this thread owns feature tile * 128 + row; the loads of its token columns are in flight together
+    const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(ph.residual) + static_cast<size_t>(tile) * 128 + row;
+    float rv[BN / 2];
+#pragma unroll
+    for (int i = 0; i < BN / 2; ++i) {
+      const int c = grp + 2 * i;
+      rv[i] = (resid && c < T) ? __bfloat162float(res[static_cast<size_t>(c) * ph.ldy]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < BN / 2; ++i) {
+      const int c = grp + 2 * i;
+      const float rn = has_norm ? sh->rnorm[c] : 1.f;
+      float v = stage[c * 128 + row];
+      if (add_xchg) v += xchg[c * 128 + row];
+      v = (v + rv[i]) * rn;
+      if (dual) {
+        const float a = act == 0 ? fd_silu(v) : fd_gelu_tanh(v);
+        v = fd_bf16r(a) * (xchg[c * 128 + row] * rn);
+      }
+      stage[c * 128 + row] = v;
+    }
+  }
+  asm volatile("bar.sync 2, 256;" ::: "memory");
+  bool comm_ok = true;
+  if (ph.epilogue == SLLM_FD_RESID_QUANT && sh->comm.world > 1) {
+    if (grp == 0) comm_ok = fd_comm_sum_tile<BN>(status, sh, stage, tile, ew, lane, et, T, abort_flag, limit);
+    if (fd_all_any(!comm_ok)) return false;
+  }
+  const int n0 = tile * 128 + lane * 4;     // first of this lane's four outputs of a token row
+  const bool resid = ph.epilogue == SLLM_FD_RESID_QUANT;    // the residual is already part of the staged values
+  const __nv_bfloat16* res_base = static_cast<const __nv_bfloat16*>(ph.residual);     // PLAIN: optional residual
 #pragma unroll 1
-  for (int c = ew; c < T; c += 4) {
+  for (int c = grp * 4 + ew; c < T; c += 8) {
     const float4 x = *reinterpret_cast<const float4*>(stage + c * 128 + lane * 4);
     float v[4] = {x.x, x.y, x.z, x.w};
-    const uint2 rr = res_next;
-    if (resid && c + 4 < T)
-      res_next = *reinterpret_cast<const uint2*>(res_base + static_cast<size_t>(c + 4) * ph.ldy + n0);
     if (ph.epilogue == SLLM_FD_PLAIN) {
       __nv_bfloat16* y = static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0;
       const __nv_bfloat16* res = res_base ? res_base + static_cast<size_t>(c) * ph.ldy + n0 : nullptr;
@@ -327,10 +389,6 @@ __device__ __noinline__ bool fd_finish_columns(const FdParams& p, const SllmFdPh
       }
     } else if (ph.epilogue == SLLM_FD_RESID_QUANT || ph.epilogue == SLLM_FD_SILU_QUANT) {
       if (resid) {
-        const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
-        const __nv_bfloat162 r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
-        v[0] += __bfloat162float(r0.x); v[1] += __bfloat162float(r0.y);
-        v[2] += __bfloat162float(r1.x); v[3] += __bfloat162float(r1.y);
         uint2 hw;
         *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
         *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
@@ -357,11 +415,11 @@ __device__ __noinline__ bool fd_finish_columns(const FdParams& p, const SllmFdPh
       }
     } else {
       // ROPE_KV: tile = head index (q heads, then k heads, then v heads), lane holds dims 4 lane .. 4 lane + 3
-      const SllmFdRope& rp = p.rope;
+      const SllmFdRope& rp = sh->rope;
       const int head = tile;
       const bool is_q = head < rp.hq;
       const bool is_v = head >= rp.hq + rp.hkv;
-      const int pos = rp.positions[c];
+      const int pos = sh->rope_pos[c];
       if (!is_v) {
         const int half = rp.rotary_dim >> 1;
         const int lane_off = half >> 2;          // partner lane distance (half / 4), a power of two
@@ -390,7 +448,7 @@ __device__ __noinline__ bool fd_finish_columns(const FdParams& p, const SllmFdPh
         *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
       } else {
         const int kvh = is_v ? head - rp.hq - rp.hkv : head - rp.hq;
-        const int blk = rp.block_table[static_cast<size_t>(rp.seq_index[c]) * rp.max_blocks + pos / rp.page_size];
+        const int blk = sh->rope_page[c];
         const size_t slot = (static_cast<size_t>(blk) * rp.hkv + kvh) * rp.page_size + pos % rp.page_size;
         if (!rp.kv_fp8) {
           __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
@@ -415,27 +473,29 @@ __device__ __noinline__ bool fd_finish_columns(const FdParams& p, const SllmFdPh
       }
     }
   }
+  asm volatile("bar.sync 2, 256;" ::: "memory");          // the staging buffers are free again
   return true;
 }
 
 constexpr int kFdFastParts = 6;   // parts of a split tile whose loads are kept in flight together
-// dst[(col0 + c) * 128] = sum over parts jj < np (in order) of base[offs[jj] + (col0 + c) * 128], c < 8: all loads are
+// dst[(col0 + c) * 128] = sum over parts jj < np (in order) of base[offs[jj] + (col0 + c) * 128], c < CH: all loads are
 // issued before the first one is used, and the sums go to shared memory so that no accumulator array is live here.
+template <int NP, int CH>
 __device__ __forceinline__ void fd_sum_parts(const float* base, const uint32_t (&offs)[kFdFastParts], int np, int col0,
                                              float* dst) {
-  float t[kFdFastParts][8];
+  float t[NP][CH];
 #pragma unroll
-  for (int jj = 0; jj < kFdFastParts; ++jj) {
+  for (int jj = 0; jj < NP; ++jj) {
     if (jj < np) {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) t[jj][c] = __ldcg(base + offs[jj] + static_cast<size_t>(col0 + c) * 128);
+      for (int c = 0; c < CH; ++c) t[jj][c] = __ldcg(base + offs[jj] + static_cast<size_t>(col0 + c) * 128);
     }
   }
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
+  for (int c = 0; c < CH; ++c) {
     float sum = 0.f;
 #pragma unroll
-    for (int jj = 0; jj < kFdFastParts; ++jj)
+    for (int jj = 0; jj < NP; ++jj)
       if (jj < np) sum += t[jj][c];
     dst[(col0 + c) * 128] = sum;
   }
@@ -463,6 +523,16 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
   volatile int* abort_flag = &sh->abort_flag;
   const long long limit = p.wait_limit;
 
+  {
+    constexpr int kPhWords = sizeof(SllmFdPhase) * SLLM_FD_MAX_PHASES / 4, kRopeWords = sizeof(SllmFdRope) / 4,
+                  kCommWords = sizeof(FdComm) / 4;
+    const uint32_t* src_ph = reinterpret_cast<const uint32_t*>(&p.ph[0]);
+    const uint32_t* src_rope = reinterpret_cast<const uint32_t*>(&p.rope);
+    const uint32_t* src_comm = reinterpret_cast<const uint32_t*>(&p.comm);
+    for (int i = threadIdx.x; i < kPhWords; i += kFdThreads) reinterpret_cast<uint32_t*>(&sh->ph[0])[i] = src_ph[i];
+    for (int i = threadIdx.x; i < kRopeWords; i += kFdThreads) reinterpret_cast<uint32_t*>(&sh->rope)[i] = src_rope[i];
+    for (int i = threadIdx.x; i < kCommWords; i += kFdThreads) reinterpret_cast<uint32_t*>(&sh->comm)[i] = src_comm[i];
+  }
   if (threadIdx.x == 0) {
     for (int r = 0; r < 2; ++r) {
       for (int s = 0; s < kFdASlots; ++s) { mbar_init(&sh->afull[r][s], 1); mbar_init(&sh->aempty[r][s], 1); }
@@ -481,8 +551,7 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
   if (threadIdx.x >= 128 && threadIdx.x < 192) {
     const int fi = threadIdx.x - 128;
     const int rd = p.rope.rotary_dim > 0 ? p.rope.rotary_dim : 128;
-    sh->inv_freq[fi] = p.rope.inv_freq ? (fi < rd / 2 ? p.rope.inv_freq[fi] : 0.f)
-                                       : powf(p.rope.theta > 0.f ? p.rope.theta : 10000.f, -2.f * fi / rd);
+    sh->inv_freq[fi] = (p.rope.inv_freq && fi < rd / 2) ? p.rope.inv_freq[fi] : 0.f;
   }
   tc_fence_before();
   __syncthreads();
@@ -500,15 +569,15 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       // L2 prefetch cursor: runs kFdLookahead tile loads ahead of the shared-memory ring, across phase
       // boundaries, so HBM keeps streaming while a phase's reduction / epilogue / grid barrier resolves.
       int f_pi = 0, f_half = 0;
-      FdPhaseGeom fg = fd_geom(p.ph[0], cta, G);
-      long long f_u = fg.u0;
+      FdPhaseGeom fg = fd_geom(sh->ph[0], cta, G);
+      uint32_t f_u = fg.u0;
       auto prefetch_next = [&]() {
         while (f_pi < p.n_phases && f_u >= fg.u1) {
-          if (++f_pi < p.n_phases) { fg = fd_geom(p.ph[f_pi], cta, G); f_u = fg.u0; f_half = 0; }
+          if (++f_pi < p.n_phases) { fg = fd_geom(sh->ph[f_pi], cta, G); f_u = fg.u0; f_half = 0; }
         }
         if (f_pi >= p.n_phases) return;
         const int ft = static_cast<int>(f_u / fg.nkb), fk = static_cast<int>(f_u % fg.nkb);
-        const SllmFdPhase& fp = p.ph[f_pi];
+        const SllmFdPhase& fp = sh->ph[f_pi];
         const int frow = ft * 128 + f_half * fp.dual_off;
         fd_tma_prefetch_l2(&maps.a[f_pi], fk * 128, frow);
         int fs = fp.dual_off + fp.n - frow;      // the row scales the epilogue will read from L2
@@ -518,10 +587,10 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       };
       for (int i = 0; i < p.lookahead; ++i) prefetch_next();
       for (int pi = 0; pi < p.n_phases && ok; ++pi) {
-        const SllmFdPhase& ph = p.ph[pi];
+        const SllmFdPhase& ph = sh->ph[pi];
         const FdPhaseGeom g = fd_geom(ph, cta, G);
         int tile = static_cast<int>(g.u0 / g.nkb), kb = static_cast<int>(g.u0 % g.nkb);
-        for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
+        for (uint32_t u = g.u0; u < g.u1 && ok; ++u, ++n) {
           const int r = n & 1;
           for (int half = 0; half <= g.dual; ++half) {
             const uint32_t slot = apos[r] % kFdASlots, fill = apos[r] / kFdASlots;
@@ -571,7 +640,7 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       unsigned long long base = 0;
       FD_PROF_DECL(pb); FD_PROF_DECL(pg);
       for (int pi = 0; pi < p.n_phases && ok; ++pi) {
-        const SllmFdPhase& ph = p.ph[pi];
+        const SllmFdPhase& ph = sh->ph[pi];
         const FdPhaseGeom g = fd_geom(ph, cta, G);
         FD_PROF_T0();
         if (pi == 0) {
@@ -584,7 +653,7 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
         fd_fence_proxy_async();
         FD_PROF_ADD(pg);
         int kb = static_cast<int>(g.u0 % g.nkb);
-        for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
+        for (uint32_t u = g.u0; u < g.u1 && ok; ++u, ++n) {
           const int r = n & 1;
           const uint32_t slot = bpos[r] % kFdBSlots, fill = bpos[r] / kFdBSlots;
           { FD_PROF_T0();
@@ -621,8 +690,8 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       bool ok = true;
       FD_PROF_DECL(wa); FD_PROF_DECL(wb); FD_PROF_DECL(wt); FD_PROF_DECL(is);
       for (int pi = 0; pi < p.n_phases && ok; ++pi) {
-        const FdPhaseGeom g = fd_geom(p.ph[pi], cta, G);
-        for (long long u = g.u0; u < g.u1 && ok; ++u, ++n) {
+        const FdPhaseGeom g = fd_geom(sh->ph[pi], cta, G);
+        for (uint32_t u = g.u0; u < g.u1 && ok; ++u, ++n) {
           if (static_cast<int>(n & 1) != iw) continue;
           const int acc = iw * 2 + (mine & 1);
           const uint32_t use = mine >> 1;
@@ -679,10 +748,10 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
     bool ok = true;
     unsigned long long base = 0;
     float acc[BN];
-    FD_PROF_DECL(wf); FD_PROF_DECL(ld); FD_PROF_DECL(fm); FD_PROF_DECL(seg);
+    FD_PROF_DECL(wf); FD_PROF_DECL(ld); FD_PROF_DECL(fm); FD_PROF_DECL(xc); FD_PROF_DECL(pr); FD_PROF_DECL(fn);
 
     for (int pi = 0; pi < p.n_phases; ++pi) {
-      const SllmFdPhase& ph = p.ph[pi];
+      const SllmFdPhase& ph = sh->ph[pi];
       const FdPhaseGeom g = fd_geom(ph, cta, G);
       float norm_part = 0.f;
       bool norm_ready = ph.norm_tiles == 0;
@@ -690,6 +759,13 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
         if (pi == 0) {
           pdl_wait();
           base = fd_ld_acquire_u64(p.sync) / kFdSyncQuantum * kFdSyncQuantum;
+          if (sh->rope.positions && et < T) {
+            // page lookups of the KV append, long before the q/k/v phase needs them
+            const int pos = sh->rope.positions[et];
+            sh->rope_pos[et] = pos;
+            sh->rope_page[et] = sh->rope.block_table[static_cast<size_t>(sh->rope.seq_index[et]) * sh->rope.max_blocks +
+                                                     pos / sh->rope.page_size];
+          }
         } else if (ok) {
           if (et == 0) fd_grid_wait(p.sync, base + static_cast<unsigned long long>(pi) * G, abort_flag, p.status, limit);
           fd_epi_any(false);                 // the group resumes together; a failed wait shows at the next segment end
@@ -708,6 +784,8 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       }
       bool first_unit = true;
       const size_t part_floats = static_cast<size_t>(1 + g.dual) * BN * 128;
+      int pend[2];          // split tiles this CTA arrived last for (a CTA's range touches at most two)
+      int npend = 0;
       // Weight scales (one fp32 per weight row and K block) come straight from L2, where the producer's prefetch
       // cursor has put them: each thread keeps the scales of its next two K blocks in registers.
       const uint32_t nkb_u = static_cast<uint32_t>(g.nkb);
@@ -725,10 +803,10 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
       float sa_q0 = load_sa(s_next), sa_q1 = load_sa(s_next + s_stride);
       s_next += 2 * s_stride;
 
-      long long u = g.u0;
+      uint32_t u = g.u0;
       while (u < g.u1 && ok) {
         const int tile = static_cast<int>(u / g.nkb);
-        const int kb0 = static_cast<int>(u - static_cast<long long>(tile) * g.nkb);
+        const int kb0 = static_cast<int>(u - static_cast<uint32_t>(tile) * static_cast<uint32_t>(g.nkb));
         int kbe = g.nkb;
         if (g.u1 - u < g.nkb - kb0) kbe = kb0 + static_cast<int>(g.u1 - u);
         const bool split = !(kb0 == 0 && kbe == g.nkb);
@@ -785,6 +863,7 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
         // both halves go to the workspace
         const bool both_to_ws = split && g.dual;
         float* my_part = p.ws + (static_cast<size_t>(2 * cta) + (seg_first ? 0 : 1)) * part_floats;
+        { FD_PROF_T0();
         if (both_to_ws) {
           float* dst = my_part + grp * (BN * 128);
 #pragma unroll
@@ -799,33 +878,40 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
           break;
         }
         if (grp == 0 && et == 0) fd_stamp(p.trace, cta, pi, 3);         // segment promoted
-        float up[BN];
-        if (grp == 0 && !both_to_ws) {
-          if (g.dual) {
+        if (!split) {
+          // ---- a whole tile: group 0's sums go to the staging buffer (group 1's are in xchg), then both groups
+          // run the tile epilogue
+          if (grp == 0) {
 #pragma unroll
-            for (int c = 0; c < BN; ++c) up[c] = xchg[c * 128 + row];
-          } else {
-#pragma unroll
-            for (int c = 0; c < BN; ++c) acc[c] += xchg[c * 128 + row];
+            for (int c = 0; c < BN; ++c) stage[c * 128 + row] = acc[c];
           }
-        }
-        // ---- a tile shared with other CTAs: publish the partial; the last arriver sums all parts in order
-        const long long tu0 = static_cast<long long>(tile) * g.nkb;
-        int first_c = 0, last_c = 0;
-        if (split) {
-          first_c = fd_cta_of_unit(tu0, g.U, G);
-          last_c = fd_cta_of_unit(tu0 + g.nkb - 1, g.U, G);
+          FD_PROF_ADD(xc);
+          {
+            FD_PROF_T0();
+            if (grp == 0 && et == 0) fd_stamp(p.trace, cta, pi, 4);
+            if (!fd_finish_tile<BN>(p.status, ph, sh, stage, xchg, tile, grp, ew, lane, et, T, g.dual, g.dual ? 0 : 1,
+                                    norm_part, norm_ready, abort_flag, limit))
+              *abort_flag = 1;
+            FD_PROF_ADD(fn);
+          }
+        } else {
+          // ---- a tile shared with other CTAs: publish the partial now; whoever arrives last finishes the tile
+          // after its own segments, so that no CTA delays the parts it still owes to other tiles
           if (grp == 0) {
             if (!g.dual) {
 #pragma unroll
-              for (int c = 0; c < BN; ++c) my_part[c * 128 + row] = acc[c];
+              for (int c = 0; c < BN; ++c) my_part[c * 128 + row] = acc[c] + xchg[c * 128 + row];
               __threadfence();
               asm volatile("bar.sync 1, 128;" ::: "memory");
             }
             if (et == 0) {
+              const uint32_t tu0 = static_cast<uint32_t>(tile) * static_cast<uint32_t>(g.nkb);
+              const int first_c = fd_cta_of_unit(tu0, g.U, G);
+              const int last_c = fd_cta_of_unit(tu0 + g.nkb - 1, g.U, G);
               // CTAs with an empty unit range (fewer units than CTAs) contribute no part
               int nparts = 0;
-              for (int j = first_c; j <= last_c; ++j) nparts += ((j + 1) * g.U / G > j * g.U / G) ? 1 : 0;
+              for (int j = first_c; j <= last_c; ++j)
+                nparts += (static_cast<uint32_t>(j + 1) * g.U / G > static_cast<uint32_t>(j) * g.U / G) ? 1 : 0;
               const int old = atomicAdd(&p.counters[tile], 1);
               const int last = old == nparts - 1;
               if (last) p.counters[tile] = 0;
@@ -833,99 +919,67 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
               __threadfence();
             }
           }
+          asm volatile("bar.sync 3, 256;" ::: "memory");     // xchg consumed, is_last visible
+          if (sh->is_last != 0) pend[npend++] = tile;
+          FD_PROF_ADD(xc);
         }
-        asm volatile("bar.sync 3, 256;" ::: "memory");     // xchg consumed, is_last visible
-        if (split) {
-          if (sh->is_last == 0) continue;
-          // ---- last arriver: sum the parts in CTA order.  With up to 8 parts the loads of all parts of 8 token
-          // columns are in flight together (one L2 round trip per 8 columns); in a plain phase the two groups
-          // share the columns, in a gate/up phase each sums its own half of the accumulators.
-          const int np = last_c - first_c + 1;
-          const bool fast = np <= kFdFastParts && g.U >= G;   // every CTA of the range holds a part
-          const float* base0 = p.ws + (g.dual ? grp * (BN * 128) : 0) + row;
-          if (fast) {
-            uint32_t offs[kFdFastParts];
-#pragma unroll
-            for (int jj = 0; jj < kFdFastParts; ++jj) {
-              const long long j = first_c + jj;
-              const long long sj = j * g.U / G;
-              offs[jj] = static_cast<uint32_t>((static_cast<size_t>(2 * j) + (sj >= tu0 ? 0 : 1)) * part_floats);
-            }
-            // sums land in shared memory: plain phase -> stage (each group half of the columns); gate/up phase ->
-            // gate in stage (group 0), up in xchg (group 1)
-            float* dst = ((g.dual && grp == 1) ? xchg : stage) + row;
-            const int col0 = g.dual ? 0 : grp * (BN / 2);
-            const int ncol = g.dual ? BN : BN / 2;
-#pragma unroll 1
-            for (int cc = 0; cc < ncol; cc += 8) fd_sum_parts(base0, offs, np, col0 + cc, dst);
-          } else if (grp == 0 || g.dual) {
-#pragma unroll
-            for (int c = 0; c < BN; ++c) acc[c] = 0.f;
-            for (int j = first_c; j <= last_c; ++j) {
-              const long long sj = j * g.U / G;
-              if ((j + 1) * g.U / G == sj) continue;
-              const float* src = base0 + (static_cast<size_t>(2 * j) + (sj >= tu0 ? 0 : 1)) * part_floats;
-#pragma unroll
-              for (int c = 0; c < BN; ++c) acc[c] += __ldcg(src + c * 128);
-            }
-          }
-          if (fast) {
-            asm volatile("bar.sync 2, 256;" ::: "memory");
-            if (grp == 0) {
-#pragma unroll
-              for (int c = 0; c < BN; ++c) acc[c] = stage[c * 128 + row];
-              if (g.dual) {
-#pragma unroll
-                for (int c = 0; c < BN; ++c) up[c] = xchg[c * 128 + row];
-              }
-            }
-            asm volatile("bar.sync 3, 256;" ::: "memory");
-          } else if (g.dual) {
-            if (grp == 1) {
-#pragma unroll
-              for (int c = 0; c < BN; ++c) xchg[c * 128 + row] = acc[c];
-            }
-            asm volatile("bar.sync 2, 256;" ::: "memory");
-            if (grp == 0) {
-#pragma unroll
-              for (int c = 0; c < BN; ++c) up[c] = xchg[c * 128 + row];
-            }
-            asm volatile("bar.sync 3, 256;" ::: "memory");
-          }
         }
-        if (grp == 1) continue;              // group 1 goes on with the next segment
-        if (et == 0) fd_stamp(p.trace, cta, pi, 4);         // tile complete in registers
+      }
 
-        // ---- tile epilogue (group 0): norm factor / activation, then staged as stage[token][row of the tile]
-        const bool has_norm = ph.norm_tiles > 0;
-        if (!norm_ready) {
-          constexpr int kParts = 128 / BN;
-          stage[et] = norm_part;                 // [part][token]
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (et < BN) {
-            float ss = 0.f;
+      // ---- tiles this CTA arrived last for: sum the parts in CTA order, then the tile epilogue.  With up to
+      // kFdFastParts parts the loads of all parts of 8 token columns are in flight together; in a plain phase the
+      // two groups share the columns, in a gate/up phase each sums its own half of the accumulators.
+      if (npend > 0 && ok) asm volatile("bar.sync 3, 256;" ::: "memory");   // group 0 is done with the staging buffer
+      for (int pd = 0; pd < npend && ok; ++pd) {
+        const int tile = pend[pd];
+        FD_PROF_T0();
+        const uint32_t tu0 = static_cast<uint32_t>(tile) * static_cast<uint32_t>(g.nkb);
+        const int first_c = fd_cta_of_unit(tu0, g.U, G);
+        const int last_c = fd_cta_of_unit(tu0 + g.nkb - 1, g.U, G);
+        const int np = last_c - first_c + 1;
+        const bool fast = np <= kFdFastParts && g.U >= G;   // every CTA of the range holds a part
+        const float* base0 = p.ws + (g.dual ? grp * (BN * 128) : 0) + row;
+        float* dst = ((g.dual && grp == 1) ? xchg : stage) + row;
+        if (fast) {
+          uint32_t offs[kFdFastParts];
 #pragma unroll
-            for (int q = 0; q < kParts; ++q) ss += stage[q * BN + et];
-            sh->rnorm[et] = rsqrtf(ss / static_cast<float>(ph.norm_dim) + ph.eps);
+          for (int jj = 0; jj < kFdFastParts; ++jj) {
+            const uint32_t j = static_cast<uint32_t>(first_c + jj);
+            const uint32_t sj = j * g.U / static_cast<uint32_t>(G);
+            offs[jj] = static_cast<uint32_t>((static_cast<size_t>(2 * j) + (sj >= tu0 ? 0 : 1)) * part_floats);
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          norm_ready = true;
-        }
+          const int col0 = g.dual ? 0 : grp * (BN / 2);
+          const int ncol = g.dual ? BN : BN / 2;
+          if (np <= 3 && ncol >= 16) {
+#pragma unroll 1
+            for (int cc = 0; cc < ncol; cc += 16) fd_sum_parts<3, 16>(base0, offs, np, col0 + cc, dst);
+          } else {
+#pragma unroll 1
+            for (int cc = 0; cc < ncol; cc += 8) fd_sum_parts<kFdFastParts, 8>(base0, offs, np, col0 + cc, dst);
+          }
+        } else if (grp == 0 || g.dual) {
 #pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          float v = acc[c];
-          const float rn = has_norm ? sh->rnorm[c] : 1.f;
-          v *= rn;
-          if (g.dual) {
-            const float a = ph.act == 0 ? fd_silu(v) : fd_gelu_tanh(v);
-            v = fd_bf16r(a) * (up[c] * rn);
+          for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+          for (int j = first_c; j <= last_c; ++j) {
+            const uint32_t sj = static_cast<uint32_t>(j) * g.U / static_cast<uint32_t>(G);
+            if (static_cast<uint32_t>(j + 1) * g.U / static_cast<uint32_t>(G) == sj) continue;
+            const float* src = base0 + (static_cast<size_t>(2 * j) + (sj >= tu0 ? 0 : 1)) * part_floats;
+#pragma unroll
+            for (int c = 0; c < BN; ++c) acc[c] += __ldcg(src + c * 128);
           }
-          stage[c * 128 + row] = v;
+#pragma unroll
+          for (int c = 0; c < BN; ++c) dst[c * 128] = acc[c];
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (!fd_finish_columns<BN>(p, ph, sh, stage, tile, ew, lane, et, T, abort_flag, limit)) ok = false;
-        // the staging buffer is reused by the next tile
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        FD_PROF_ADD(pr);
+        {
+          FD_PROF_T0();
+          if (grp == 0 && et == 0) fd_stamp(p.trace, cta, pi, 4);
+          if (!fd_finish_tile<BN>(p.status, ph, sh, stage, xchg, tile, grp, ew, lane, et, T, g.dual, 0, norm_part,
+                                  norm_ready, abort_flag, limit))
+            *abort_flag = 1;
+          FD_PROF_ADD(fn);
+        }
+        if (fd_all_any(*abort_flag != 0)) ok = false;
       }
 
       if (grp == 0) {
@@ -945,7 +999,10 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
         }
       }
     }
-    if (et == 0) { FD_PROF_OUT(8 + grp * 4 + 0, wf); FD_PROF_OUT(8 + grp * 4 + 1, ld); FD_PROF_OUT(8 + grp * 4 + 2, fm); }
+    if (et == 0) {
+      FD_PROF_OUT(8 + grp * 4 + 0, wf); FD_PROF_OUT(8 + grp * 4 + 1, ld); FD_PROF_OUT(8 + grp * 4 + 2, fm);
+      FD_PROF_OUT(20 + grp * 3 + 0, xc); FD_PROF_OUT(20 + grp * 3 + 1, pr); FD_PROF_OUT(20 + grp * 3 + 2, fn);
+    }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -1093,6 +1150,7 @@ SLLM_EXPORT int sllm_fused_decode(const SllmFdDesc* d, void* stream) {
       return SLLM_ERR_INVALID_ARGUMENT;
     const int tiles = (ph.n + 127) / 128;
     if (tiles > d->n_counters) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+    if (static_cast<long long>(tiles) * (ph.k / 128) * (grid + 1) >= (1LL << 31)) return SLLM_ERR_UNSUPPORTED_SHAPE;
     if (ph.ld_sb < bn || (ph.ld_sb & 3) || (ph.ld_sa & 3) || ph.ld_sa < ph.dual_off + ph.n) return SLLM_ERR_INVALID_ARGUMENT;
     if ((reinterpret_cast<uintptr_t>(ph.w_scale) & 15) || (reinterpret_cast<uintptr_t>(ph.x_scale) & 15))
       return SLLM_ERR_ALIGNMENT;
@@ -1116,6 +1174,7 @@ SLLM_EXPORT int sllm_fused_decode(const SllmFdDesc* d, void* stream) {
             !r.v_pages || r.hq <= 0 || r.hkv <= 0 || ph.n != (r.hq + 2 * r.hkv) * 128 || r.page_size <= 0)
           return SLLM_ERR_INVALID_ARGUMENT;
         if (r.rotary_dim != 32 && r.rotary_dim != 64 && r.rotary_dim != 128) return SLLM_ERR_UNSUPPORTED_SHAPE;
+        if (!r.inv_freq) return SLLM_ERR_INVALID_ARGUMENT;     // [rotary_dim / 2] frequencies, computed by the caller
         if (r.kv_fp8 && (r.k_static <= 0.f || r.v_static <= 0.f) && (!r.k_scale || !r.v_scale))
           return SLLM_ERR_INVALID_ARGUMENT;
         break;

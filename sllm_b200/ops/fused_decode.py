@@ -146,9 +146,25 @@ def phase(epilogue: int, w, w_scale, x, x_scale, *, n: int, k: int, dual_off: in
     return ph
 
 
+_inv_freq_cache: dict = {}
+
+
+def inv_freq_table(theta: float, rotary_dim: int, device) -> torch.Tensor:
+    """theta^(-2 i / rotary_dim), i < rotary_dim / 2, evaluated in float64 and rounded once to fp32."""
+    key = (float(theta), int(rotary_dim), str(device))
+    t = _inv_freq_cache.get(key)
+    if t is None:
+        i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+        t = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rotary_dim).to(torch.float32).to(device)
+        _inv_freq_cache[key] = t
+    return t
+
+
 def rope_desc(positions, seq_index, block_table, kv, hq: int, hkv: int, rotary_dim: int, theta: float,
               inv_freq=None) -> FdRope:
     r = FdRope()
+    if inv_freq is None:
+        inv_freq = inv_freq_table(theta, rotary_dim, positions.device)
     r.positions, r.seq_index, r.block_table = positions.data_ptr(), seq_index.data_ptr(), block_table.data_ptr()
     r.max_blocks, r.hq, r.hkv, r.rotary_dim = block_table.stride(0), hq, hkv, rotary_dim
     r.page_size, r.kv_fp8, r.theta = kv.page_size, int(kv.fp8), theta
@@ -156,7 +172,7 @@ def rope_desc(positions, seq_index, block_table, kv, hq: int, hkv: int, rotary_d
     r.k_pages, r.v_pages = kv.k.data_ptr(), kv.v.data_ptr()
     r.k_scale = None if kv.k_scale is None else kv.k_scale.data_ptr()
     r.v_scale = None if kv.v_scale is None else kv.v_scale.data_ptr()
-    r.inv_freq = None if inv_freq is None else inv_freq.data_ptr()
+    r.inv_freq = inv_freq.data_ptr()
     return r
 
 
