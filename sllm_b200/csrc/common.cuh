@@ -52,8 +52,8 @@ inline bool pdl_enabled() {
   return v == 1;
 }
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                 unsigned cluster_z, Args&&... args) {
+inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                         unsigned cluster_x, unsigned cluster_z, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -66,16 +66,21 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
   }
-  if (cluster_z > 1) {
+  if (cluster_z > 1 || cluster_x > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
-    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.x = cluster_x > 1 ? cluster_x : 1;
     attr[n].val.clusterDim.y = 1;
-    attr[n].val.clusterDim.z = cluster_z;
+    attr[n].val.clusterDim.z = cluster_z > 1 ? cluster_z : 1;
     ++n;
   }
   cfg.attrs = attr;
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 unsigned cluster_z, Args&&... args) {
+  return launch_kernel_cluster(kernel, grid, block, smem, stream, 1u, cluster_z, static_cast<Args&&>(args)...);
 }
 
 // ~2 s at 2 GHz; a healthy wait finishes in microseconds.

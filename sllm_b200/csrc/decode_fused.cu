@@ -30,6 +30,7 @@
 #include "common.cuh"
 #include "api.h"
 #include "decode_fused.h"
+#include "epilogue_columns.cuh"
 #include <cstddef>
 #include <cstring>
 
@@ -368,110 +369,18 @@ __device__ __noinline__ bool fd_finish_tile(int* status, const SllmFdPhase& ph, 
     if (grp == 0) comm_ok = fd_comm_sum_tile<BN>(status, sh, stage, tile, ew, lane, et, T, abort_flag, limit);
     if (fd_all_any(!comm_ok)) return false;
   }
-  const int n0 = tile * 128 + lane * 4;     // first of this lane's four outputs of a token row
-  const bool resid = ph.epilogue == SLLM_FD_RESID_QUANT;    // the residual is already part of the staged values
-  const __nv_bfloat16* res_base = static_cast<const __nv_bfloat16*>(ph.residual);     // PLAIN: optional residual
+  ColEpilogue e;
+  e.mode = ph.epilogue; e.n = ph.n; e.ldy = ph.ldy; e.ld_s = ph.ld_s_out; e.softcap = ph.softcap;
+  e.y = static_cast<__nv_bfloat16*>(ph.y);
+  // the residual of a RESID_QUANT tile is already part of the staged values
+  e.residual = ph.epilogue == SLLM_FD_PLAIN ? static_cast<const __nv_bfloat16*>(ph.residual) : nullptr;
+  e.q_out = static_cast<uint8_t*>(ph.q_out); e.s_out = ph.s_out; e.ssq_out = ph.ssq_out;
+  e.rope = &sh->rope; e.inv_freq = sh->inv_freq;
 #pragma unroll 1
   for (int c = grp * 4 + ew; c < T; c += 8) {
     const float4 x = *reinterpret_cast<const float4*>(stage + c * 128 + lane * 4);
     float v[4] = {x.x, x.y, x.z, x.w};
-    if (ph.epilogue == SLLM_FD_PLAIN) {
-      __nv_bfloat16* y = static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0;
-      const __nv_bfloat16* res = res_base ? res_base + static_cast<size_t>(c) * ph.ldy + n0 : nullptr;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (n0 + j < ph.n) {
-          float o = v[j];
-          if (res) o += __bfloat162float(res[j]);
-          if (ph.softcap > 0.f) o = ph.softcap * tanhf(o / ph.softcap);
-          y[j] = __float2bfloat16_rn(o);
-        }
-      }
-    } else if (ph.epilogue == SLLM_FD_RESID_QUANT || ph.epilogue == SLLM_FD_SILU_QUANT) {
-      if (resid) {
-        uint2 hw;
-        *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
-        *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
-        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
-      }
-      float amax = 0.f, ss = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        v[j] = fd_bf16r(v[j]);
-        ss += v[j] * v[j];
-        const float a = fabsf(v[j]);
-        if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
-      }
-      amax = warp_max(amax);
-      const float scale = amax > 0.f ? amax / kFdE4M3Max : 1.f;
-      uint32_t q = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
-      *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ph.q_out) + static_cast<size_t>(c) * ph.n + n0) = q;
-      if (lane == 0) ph.s_out[static_cast<size_t>(tile) * ph.ld_s_out + c] = scale;
-      if (ph.ssq_out) {
-        ss = warp_sum(ss);
-        if (lane == 0) ph.ssq_out[static_cast<size_t>(tile) * ph.ld_s_out + c] = ss;
-      }
-    } else {
-      // ROPE_KV: tile = head index (q heads, then k heads, then v heads), lane holds dims 4 lane .. 4 lane + 3
-      const SllmFdRope& rp = sh->rope;
-      const int head = tile;
-      const bool is_q = head < rp.hq;
-      const bool is_v = head >= rp.hq + rp.hkv;
-      const int pos = sh->rope_pos[c];
-      if (!is_v) {
-        const int half = rp.rotary_dim >> 1;
-        const int lane_off = half >> 2;          // partner lane distance (half / 4), a power of two
-        float pv[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) pv[j] = __shfl_xor_sync(0xffffffffu, v[j], lane_off);
-        const int i0 = lane * 4;
-        if (i0 < rp.rotary_dim) {
-          const bool lo = i0 < half;
-          const int f0 = lo ? i0 : i0 - half;
-#pragma unroll 1
-          for (int j = 0; j < 4; ++j) {
-            float sn, cs;
-            sincosf(static_cast<float>(pos) * sh->inv_freq[f0 + j], &sn, &cs);
-            const float a = lo ? v[j] : pv[j], b = lo ? pv[j] : v[j];
-            v[j] = lo ? a * cs - b * sn : b * cs + a * sn;
-          }
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = fd_bf16r(v[j]);
-      uint2 hw;
-      *reinterpret_cast<__nv_bfloat162*>(&hw.x) = __floats2bfloat162_rn(v[0], v[1]);
-      *reinterpret_cast<__nv_bfloat162*>(&hw.y) = __floats2bfloat162_rn(v[2], v[3]);
-      if (is_q) {
-        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(ph.y) + static_cast<size_t>(c) * ph.ldy + n0) = hw;
-      } else {
-        const int kvh = is_v ? head - rp.hq - rp.hkv : head - rp.hq;
-        const int blk = sh->rope_page[c];
-        const size_t slot = (static_cast<size_t>(blk) * rp.hkv + kvh) * rp.page_size + pos % rp.page_size;
-        if (!rp.kv_fp8) {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
-          *reinterpret_cast<uint2*>(dst) = hw;
-        } else {
-          float amax = 0.f;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float a = fabsf(v[j]);
-            if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
-          }
-          amax = warp_max(amax);
-          const float st = is_v ? rp.v_static : rp.k_static;
-          const float scale = st > 0.f ? st : (amax > 0.f ? amax / kFdE4M3Max : 1.f);
-          uint32_t q = 0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
-          uint8_t* dst = static_cast<uint8_t*>(is_v ? rp.v_pages : rp.k_pages) + slot * 128 + lane * 4;
-          *reinterpret_cast<uint32_t*>(dst) = q;
-          if (lane == 0 && st <= 0.f) (is_v ? rp.v_scale : rp.k_scale)[slot] = scale;
-        }
-      }
-    }
+    col_epilogue(e, tile, c, lane, v, sh->rope_pos[c], sh->rope_page[c]);
   }
   asm volatile("bar.sync 2, 256;" ::: "memory");          // the staging buffers are free again
   return true;

@@ -37,6 +37,7 @@
 // (native/hip/src/matmul_kernel.hip.cpp:586-830, native/hip/src/matmul_runtime.inc:690).
 #include "common.cuh"
 #include "api.h"
+#include "epilogue_columns.cuh"
 #include <cudaTypedefs.h>
 #include <cstring>
 #include <map>
@@ -81,6 +82,25 @@ struct GatherParams {
   const uint32_t* epoch;     // local: the epoch this call consumes
 };
 
+// Fused row epilogue of a decode GEMM (swap-AB, block-scaled FP8, cluster split-K or no split): the work of the
+// kernels that used to follow the projection happens on the fp32 sums of each token row (epilogue_columns.cuh).
+// SILU_QUANT expects the gate / up weight rows interleaved per tile (rows 0..63 gate, 64..127 up of the same 64
+// features) and a cluster of two tiles along x: the two CTAs exchange the row maxima of their 64 features so that
+// the 128 features they cover share one E4M3 scale.
+struct FusedEpi {
+  int mode;            // 0 = off, else SllmFdEpilogue + 1
+  int n;               // logical outputs per row (SILU_QUANT: the gated width)
+  int norm_tiles, norm_dim;
+  float eps, softcap;
+  int act, ld_s;
+  const float* ssq_in;
+  uint8_t* q_out;
+  float* s_out;
+  float* ssq_out;
+  const float* inv_freq;
+  SllmFdRope rope;
+};
+
 struct GemmParams {
   int a_rows, b_rows;
   int num_kb;          // K blocks (of kBoxBytes) over the whole K range
@@ -101,6 +121,7 @@ struct GemmParams {
   int* status;         // device status word (0 = ok)
   CommParams comm;     // used by the kComm instantiation only
   GatherParams gather; // world > 1: B operand gathered from the peers (unscaled GEMM only)
+  FusedEpi fe;         // mode != 0: fused row epilogue (scaled, swap-AB launches)
 };
 
 #ifdef SLLM_TRACE
@@ -130,6 +151,7 @@ struct __align__(16) GemmBarriers {
   int abort_flag;
   int is_last;
   uint32_t epoch;
+  float famax[128];    // fused SiLU epilogue: row maxima exchanged between the two tiles of a scale block
 };
 
 template <int BN>
@@ -492,10 +514,93 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   }
 
   if (threadIdx.x == 64) TRACE(7);
-  if (cluster_split) cluster_sync_all();  // partials visible cluster-wide
+  constexpr bool kFusable = kScaled && !kComm && BN <= 32;      // instantiations that carry the fused row epilogue
+  const bool pair_x = kFusable && p.fe.mode == SLLM_FD_SILU_QUANT + 1;     // cluster of two tiles along x (no K split)
+  if (cluster_split || pair_x) cluster_sync_all();  // partials visible cluster-wide
   if (threadIdx.x == 64) TRACE(8);
 
-  if (warp >= 2 && warp < 6 && active && ok) {
+  if (kFusable && p.fe.mode != 0) {
+    // ------------------------------------------------------------ fused row epilogue
+    // Each CTA finishes the token rows [c0, c0 + cw) of its tile (all of them without a K split): a warp sums the
+    // cluster's partials of one row over DSMEM (lane l: outputs 4 l .. 4 l + 3), applies the norm factor and runs
+    // the row epilogue.
+    const FusedEpi& fe = p.fe;
+    const int nslice = cluster_split ? static_cast<int>(gridDim.z) : 1;
+    const int cw = BN / nslice;
+    const int c0 = (cluster_split ? split : 0) * cw;
+    const int T = p.b_rows;
+    const int ew = warp - 2;
+    const bool epi_warp = warp >= 2 && warp < 6 && active && ok;
+    int my_pos = 0, my_page = 0;
+    if (epi_warp) {
+      if (fe.mode == SLLM_FD_ROPE_KV + 1 && lane < cw && c0 + lane < T) {
+        my_pos = fe.rope.positions[c0 + lane];
+        my_page = fe.rope.block_table[static_cast<size_t>(fe.rope.seq_index[c0 + lane]) * fe.rope.max_blocks +
+                                      my_pos / fe.rope.page_size];
+      }
+      ColEpilogue e;
+      e.mode = fe.mode - 1; e.n = fe.n; e.ldy = p.ldy; e.ld_s = fe.ld_s; e.softcap = fe.softcap;
+      e.y = p.y; e.residual = p.residual;
+      e.q_out = fe.q_out; e.s_out = fe.s_out; e.ssq_out = fe.ssq_out;
+      e.rope = &fe.rope; e.inv_freq = fe.inv_freq;
+      for (int cl = ew; cl < cw; cl += 4) {
+        const int col = c0 + cl;
+        if (col >= T) break;
+        float rn = 1.f;
+        if (fe.norm_tiles > 0) {
+          float ss = 0.f;
+          for (int i = lane; i < fe.norm_tiles; i += 32) ss += __ldcg(fe.ssq_in + static_cast<size_t>(i) * fe.ld_s + col);
+          rn = rsqrtf(warp_sum(ss) / static_cast<float>(fe.norm_dim) + fe.eps);
+        }
+        const float* src = red + col * kTileA + lane * 4;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < nslice; ++s) {
+          const float4 x = nslice == 1 ? *reinterpret_cast<const float4*>(src) : ld_dsmem_f32x4(src, s);
+          sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
+        }
+        float v[4] = {sum.x * rn, sum.y * rn, sum.z * rn, sum.w * rn};
+        if (pair_x) {
+          // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 64 features
+          float up[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) up[j] = __shfl_xor_sync(0xffffffffu, v[j], 16);
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = fe.act == 0 ? v[j] / (1.f + __expf(-v[j]))
+                                        : 0.5f * v[j] * (1.f + tanhf(0.7978845608028654f * (v[j] + 0.044715f * v[j] * v[j] * v[j])));
+            v[j] = col_bf16r(col_bf16r(a) * up[j]);
+            const float x = fabsf(v[j]);
+            if (lane < 16 && x == x && x <= 3.0e38f) amax = fmaxf(amax, x);
+          }
+          amax = warp_max(amax);
+          if (lane < 16) *reinterpret_cast<float4*>(red + col * kTileA + lane * 4) = make_float4(v[0], v[1], v[2], v[3]);
+          if (lane == 0) bars->famax[col] = amax;
+        } else {
+          col_epilogue(e, a_tile, col, lane, v, __shfl_sync(0xffffffffu, my_pos, cl), __shfl_sync(0xffffffffu, my_page, cl));
+        }
+      }
+    }
+    if (pair_x) {
+      cluster_sync_all();     // both tiles' row maxima are written (all threads of both CTAs take part)
+      if (epi_warp) {
+        const uint32_t partner = (blockIdx.x & 1u) ^ 1u;
+        for (int col = ew; col < T; col += 4) {
+          const float amax = fmaxf(bars->famax[col], ld_dsmem_f32(&bars->famax[col], partner));
+          const float scale = amax > 0.f ? amax / 448.f : 1.f;
+          if (lane < 16) {
+            const float4 x = *reinterpret_cast<const float4*>(red + col * kTileA + lane * 4);
+            const float v[4] = {x.x, x.y, x.z, x.w};
+            uint32_t q = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
+            *reinterpret_cast<uint32_t*>(fe.q_out + static_cast<size_t>(col) * fe.n + a_tile * 64 + lane * 4) = q;
+          }
+          if (lane == 0 && (blockIdx.x & 1u) == 0) fe.s_out[static_cast<size_t>(a_tile >> 1) * fe.ld_s + col] = scale;
+        }
+      }
+    }
+  } else if (warp >= 2 && warp < 6 && active && ok) {
     const int nslice = cluster_split ? static_cast<int>(gridDim.z) : 1;
     const int cw = BN / nslice;            // columns of the tile this CTA finishes
     const int c0 = (cluster_split ? split : 0) * cw;
@@ -672,7 +777,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (threadIdx.x == 64) TRACE(10);
   // Non-leader CTAs must stay resident until the leader has read their shared memory.
-  if (cluster_split) cluster_sync_all();
+  if (cluster_split || pair_x) cluster_sync_all();
   if (threadIdx.x == 64) TRACE(11);
 
   // ------------------------------------------------------------ teardown
@@ -784,12 +889,14 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       cluster_smem[z] = smem;
     }
     if (cluster_ok[z] < 0) {
+      if (pp.fe.mode != 0) return SLLM_ERR_UNSUPPORTED_SHAPE;   // the fused row epilogue needs the DSMEM reduction
       pp.cluster_split = 0;
       if (!pp.ws || !pp.counters) return SLLM_ERR_WORKSPACE_TOO_SMALL;
     }
   }
-  if (launch_kernel(gemm_tcgen05_kernel<BN, kScaled, kComm>, grid, dim3(gemm_threads(BN)), smem, stream,
-                    pp.cluster_split ? grid.z : 1u, ta, tb, pp) != cudaSuccess) {
+  const unsigned cluster_x = pp.fe.mode == SLLM_FD_SILU_QUANT + 1 ? 2u : 1u;
+  if (launch_kernel_cluster(gemm_tcgen05_kernel<BN, kScaled, kComm>, grid, dim3(gemm_threads(BN)), smem, stream, cluster_x,
+                            pp.cluster_split ? grid.z : 1u, ta, tb, pp) != cudaSuccess) {
     cudaGetLastError();
     return SLLM_ERR_CUDA;
   }
@@ -829,7 +936,7 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
                      const void* residual, int a_rows, int b_rows, int k, int scaled, int transpose_out, int ldy,
                      int ld_sa, int ld_sb, int bn, int splits, int stages, float* ws, long long ws_floats,
                      int* counters, int n_counters, int* status, void* stream, const SllmCommDesc* comm,
-                     const SllmGatherDesc* gather = nullptr) {
+                     const SllmGatherDesc* gather = nullptr, const FusedEpi* fused = nullptr) {
   if (gather) b = a;    // the B operand comes from the peers' buffers; keep the argument checks below simple
   if (!a || !b || !y || a_rows <= 0 || b_rows <= 0 || k <= 0 || splits < 1) return SLLM_ERR_INVALID_ARGUMENT;
   if (bn != 16 && bn != 32 && bn != 64 && bn != 128) return SLLM_ERR_UNSUPPORTED_SHAPE;
@@ -894,6 +1001,13 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
   p.y = static_cast<__nv_bfloat16*>(y);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ws = ws; p.counters = counters; p.status = status;
+  if (fused) {
+    // the row epilogue works on whole token rows of a tile: no K split, or a cluster split reduced over DSMEM
+    if (!scaled || !transpose_out || comm || gather || (splits > 1 && !p.cluster_split) || bn > 32)
+      return SLLM_ERR_UNSUPPORTED_SHAPE;
+    if (fused->mode == SLLM_FD_SILU_QUANT + 1 && (splits != 1 || (a_tiles & 1))) return SLLM_ERR_UNSUPPORTED_SHAPE;
+    p.fe = *fused;
+  }
   if (gather) {
     if (scaled || !transpose_out || comm || gather->world < 2 || gather->world > kMaxWorld || gather->rank < 0 ||
         gather->rank >= gather->world || !gather->maps || !gather->flags || !gather->epoch || num_kb % gather->world)
@@ -1024,4 +1138,51 @@ SLLM_EXPORT int sllm_gemm_allgather(const void* w, void* y, const void* residual
   if (!gather) return SLLM_ERR_INVALID_ARGUMENT;
   return gemm_impl(w, nullptr, y, nullptr, nullptr, residual, n, rows, k, 0, 1, ldy, 0, 0, bn, splits, stages, ws,
                    ws_floats, counters, n_counters, status, stream, nullptr, static_cast<const SllmGatherDesc*>(gather));
+}
+
+// One decode GEMM with a fused row epilogue, described by a phase record of the fused decode path (decode_fused.h):
+// Y[t, n] = X[t, :] . W[n, :] (block-scaled FP8, weights as the 128-row operand), K split over a thread-block cluster
+// and reduced over DSMEM, then the PLAIN / RESID_QUANT / SILU_QUANT / ROPE_KV row epilogue.  For SILU_QUANT `ph->w`
+// is the gate / up matrix with rows interleaved per 128-row tile (64 gate rows, then the 64 up rows of the same
+// features) and `ph->w_scale` its scales in the same row order; dual_off is ignored.
+SLLM_EXPORT int sllm_gemm_fused(const SllmFdPhase* ph, const SllmFdRope* rope, int rows, int bn, int splits, int stages,
+                                float* ws, long long ws_floats, int* counters, int n_counters, int* status, void* stream) {
+  if (!ph || rows < 1 || rows > 32 || !ph->w || !ph->w_scale || !ph->x || !ph->x_scale || ph->n <= 0 || ph->k <= 0 ||
+      (ph->k & 127))
+    return SLLM_ERR_INVALID_ARGUMENT;
+  FusedEpi fe;
+  memset(&fe, 0, sizeof(fe));
+  fe.mode = ph->epilogue + 1;
+  fe.n = ph->n; fe.norm_tiles = ph->norm_tiles; fe.norm_dim = ph->norm_dim; fe.eps = ph->eps; fe.softcap = ph->softcap;
+  fe.act = ph->act; fe.ld_s = ph->ld_s_out; fe.ssq_in = ph->ssq_in;
+  fe.q_out = static_cast<uint8_t*>(ph->q_out); fe.s_out = ph->s_out; fe.ssq_out = ph->ssq_out;
+  int w_rows = ph->n;
+  void* y = ph->y;
+  switch (ph->epilogue) {
+    case SLLM_FD_PLAIN:
+      if (!ph->y || (ph->ldy & 3)) return SLLM_ERR_INVALID_ARGUMENT;
+      break;
+    case SLLM_FD_RESID_QUANT:
+      if (!ph->y || !ph->residual || !ph->q_out || !ph->s_out || (ph->n & 127) || (ph->ldy & 3)) return SLLM_ERR_INVALID_ARGUMENT;
+      break;
+    case SLLM_FD_SILU_QUANT:
+      if (!ph->q_out || !ph->s_out || (ph->n & 127)) return SLLM_ERR_INVALID_ARGUMENT;
+      w_rows = 2 * ph->n;
+      y = ph->q_out;      // no bf16 output; the GEMM launcher only needs a non-null, aligned pointer
+      break;
+    case SLLM_FD_ROPE_KV:
+      if (!rope || !ph->y || (ph->ldy & 3) || !rope->positions || !rope->seq_index || !rope->block_table || !rope->k_pages ||
+          !rope->v_pages || !rope->inv_freq || ph->n != (rope->hq + 2 * rope->hkv) * 128 ||
+          (rope->rotary_dim != 32 && rope->rotary_dim != 64 && rope->rotary_dim != 128))
+        return SLLM_ERR_INVALID_ARGUMENT;
+      fe.rope = *rope;
+      fe.inv_freq = rope->inv_freq;
+      break;
+    default:
+      return SLLM_ERR_INVALID_ARGUMENT;
+  }
+  if (ph->norm_tiles > 0 && (!ph->ssq_in || ph->norm_dim <= 0)) return SLLM_ERR_INVALID_ARGUMENT;
+  return gemm_impl(ph->w, ph->x, y, ph->w_scale, ph->x_scale, ph->epilogue == SLLM_FD_SILU_QUANT ? nullptr : ph->residual,
+                   w_rows, rows, ph->k, 1, 1, ph->ldy > 0 ? ph->ldy : ph->n, ph->ld_sa, ph->ld_sb, bn, splits, stages, ws,
+                   ws_floats, counters, n_counters, status, stream, nullptr, nullptr, &fe);
 }

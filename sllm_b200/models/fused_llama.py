@@ -106,6 +106,11 @@ class FusedLlamaDecoder:
         self.vocab_local = model.w.lm_head.out_features
         self.logits = z((rows, self.vocab_local), torch.bfloat16)
         fold_norms(cfg, model.w)
+        self.impl = fd.backend() if model.tp.size == 1 else "persistent"
+        # the cluster GEMM's SiLU epilogue reads gate and up rows of the same features from one 128-row tile
+        if self.impl == "cluster" and getattr(model.w, "gate_up_interleaved", None) is None:
+            model.w.gate_up_interleaved = [fd.interleave_gate_up(lw.gate_up.w, lw.gate_up.scale_t, self.ffn_local)
+                                           for lw in model.w.layers]
 
     # ---- phases
     def _qkv(self, lw, kv, b):
@@ -147,7 +152,7 @@ class FusedLlamaDecoder:
         comm = m.tp.desc if m.tp.size > 1 else None
         fd.embed_quant(w.embed, b.tokens, self.h, self.hq, self.hs, self.ssq, cfg.embedding_scale)
         ph, rope = self._qkv(w.layers[0], cache.layer(0), b)
-        fd.launch([ph], rows, dev, rope)
+        fd.launch([ph], rows, dev, rope, impl=self.impl)
         out = QTensor(self.aq, self.a_s)
         n_layers = len(w.layers)
         for li, lw in enumerate(w.layers):
@@ -160,5 +165,6 @@ class FusedLlamaDecoder:
                 phases.append(ph)
             else:
                 phases.append(self._head())
-            fd.launch(phases, rows, dev, rope, comm=comm)
+            il = [None, w.gate_up_interleaved[li], None, None] if self.impl == "cluster" else None
+            fd.launch(phases, rows, dev, rope, comm=comm, impl=self.impl, interleaved=il)
         return self.logits

@@ -55,6 +55,8 @@ _lib.EXTRA_KERNEL_SIGNATURES.update({
     "sllm_fused_decode_abi": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "sllm_fused_decode_set_trace": (None, [C.c_void_p]),
     "sllm_fused_decode_set_lookahead": (None, [C.c_int]),
+    "sllm_gemm_fused": (C.c_int, [C.POINTER(FdPhase), C.POINTER(FdRope), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                  C.c_longlong, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
 })
 
 _abi_checked = False
@@ -176,12 +178,63 @@ def rope_desc(positions, seq_index, block_table, kv, hq: int, hkv: int, rotary_d
     return r
 
 
+_il_cache: dict = {}
+
+
+def interleave_gate_up(w: torch.Tensor, scale_t: torch.Tensor, ffn: int):
+    """Row order of the gate / up matrix for the cluster-GEMM SiLU epilogue: per 128-row tile, the 64 gate rows of 64
+    features followed by the 64 up rows of the same features.  Returns (weight, scales) in that order."""
+    if ffn % 128:
+        raise ValueError("the gated width must be a multiple of 128")
+    j = torch.arange(ffn // 64, device=w.device).repeat_interleave(64) * 64 + torch.arange(64, device=w.device).repeat(ffn // 64)
+    idx = torch.stack([j.view(-1, 64), (j + ffn).view(-1, 64)], dim=1).reshape(-1)
+    return w[idx].contiguous(), scale_t[:, idx].contiguous()
+
+
+def backend() -> str:
+    """'cluster': one cluster split-K GEMM launch per phase (gemm_tcgen05.cu); 'persistent': all phases of a launch in
+    one persistent kernel (decode_fused.cu).  Chosen by SLLM_FD_BACKEND (default cluster)."""
+    import os
+    return os.environ.get("SLLM_FD_BACKEND", "cluster")
+
+
+def _launch_cluster(phases: list, rows: int, device: torch.device, rope: Optional[FdRope], il: Optional[list]) -> None:
+    from .core import _gemm_plan
+    wsp = workspace(device)
+    lib = _lib.kernels()
+    for i, ph in enumerate(phases):
+        one = FdPhase.from_buffer_copy(ph)
+        w_rows = ph.n
+        if ph.epilogue == SILU_QUANT:
+            pair = il[i] if il is not None and il[i] is not None else None
+            if pair is None:
+                key = (ph.w, ph.w_scale, ph.n)
+                pair = _il_cache.get(key)
+                if pair is None:
+                    raise ValueError("the cluster backend needs the interleaved gate / up weight (interleave_gate_up)")
+            one.w, one.w_scale = pair[0].data_ptr(), pair[1].data_ptr()
+            one.ld_sa = _ld(pair[1])
+            w_rows = 2 * ph.n
+        _, bn, splits, stages = _gemm_plan(rows, w_rows, ph.k // 128)
+        if ph.epilogue == SILU_QUANT:
+            splits = 1
+        rc = lib.sllm_gemm_fused(C.byref(one), C.byref(rope) if rope is not None else None, rows, bn, splits, stages,
+                                 _p(wsp.ws), wsp.ws.numel(), _p(wsp.counters), wsp.counters.numel(), _p(wsp.status),
+                                 _stream())
+        _lib.check(rc, "gemm_fused")
+
+
 def launch(phases: list, rows: int, device: torch.device, rope: Optional[FdRope] = None, comm=None, grid: int = 0,
-           wait_limit_cycles: int = 0) -> None:
-    """Runs the phases (1..4) as one kernel on the current stream."""
+           wait_limit_cycles: int = 0, impl: Optional[str] = None, interleaved: Optional[list] = None) -> None:
+    """Runs the phases (1..4) on the current stream: as one persistent kernel, or as one cluster GEMM per phase
+    (``impl`` / SLLM_FD_BACKEND).  ``interleaved[i]``: (weight, scales) of a SILU_QUANT phase in the row order of
+    ``interleave_gate_up`` (cluster backend)."""
     check_abi()
     if not 1 <= len(phases) <= MAX_PHASES or not 1 <= rows <= MAX_ROWS:
         raise ValueError("a fused decode launch takes 1..4 phases and 1..32 rows")
+    impl = impl or backend()
+    if impl == "cluster" and comm is None:
+        return _launch_cluster(phases, rows, device, rope, interleaved)
     st = state(device)
     d = FdDesc()
     d.n_phases, d.rows, d.n_counters, d.grid = len(phases), rows, st.counters.numel(), grid

@@ -12,6 +12,7 @@ from sllm_b200.ops.core import KVLayer, LinearWeight
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+IMPLS = ["persistent", "cluster"]      # one persistent kernel for all phases / one cluster split-K GEMM per phase
 
 
 def _status_ok():
@@ -48,7 +49,8 @@ def _acts(rows, k, bn, seed):
 @pytest.mark.parametrize("rows,n,k,grid", [(1, 128, 128, 1), (5, 384, 512, 3), (16, 1000, 256, 7), (17, 640, 1024, 148),
                                            (32, 4096, 4096, 148), (32, 128, 2048, 148), (31, 2052, 384, 0),
                                            (8, 256, 14336, 148)])
-def test_plain_phase(rows, n, k, grid):
+@pytest.mark.parametrize("impl", IMPLS)
+def test_plain_phase(impl, rows, n, k, grid):
     bn = 16 if rows <= 16 else 32
     lw = _weights(n, k, n + k)
     xq, xs = _acts(rows, k, bn, rows)
@@ -57,14 +59,15 @@ def test_plain_phase(rows, n, k, grid):
     ph = fd.phase(fd.PLAIN, lw.w, lw.scale_t, xq, xs, n=n, k=k, y=y, ldy=n, residual=res)
     for _ in range(2):      # the second call runs on the counters and the barrier word the first one left
         y.zero_()
-        fd.launch([ph], rows, torch.device(DEV), grid=grid)
+        fd.launch([ph], rows, torch.device(DEV), grid=grid, impl=impl)
     want = fd.ref_plain(lw.w, lw.scale_t, xq, xs, rows, residual=res)
     close(y, want, name="plain")
     _status_ok()
 
 
 @pytest.mark.parametrize("rows,d,k,grid", [(1, 256, 512, 5), (16, 512, 256, 148), (32, 4096, 4096, 148), (20, 1024, 1792, 37)])
-def test_resid_quant_phase(rows, d, k, grid):
+@pytest.mark.parametrize("impl", IMPLS)
+def test_resid_quant_phase(impl, rows, d, k, grid):
     bn = 16 if rows <= 16 else 32
     lw = _weights(d, k, d * 3 + k)
     xq, xs = _acts(rows, k, bn, rows + 1)
@@ -75,7 +78,7 @@ def test_resid_quant_phase(rows, d, k, grid):
     ssq = torch.zeros((d // 128, bn), dtype=torch.float32, device=DEV)
     ph = fd.phase(fd.RESID_QUANT, lw.w, lw.scale_t, xq, xs, n=d, k=k, y=h, ldy=d, residual=h, q_out=q, s_out=s,
                   ssq_out=ssq, ld_s_out=bn)
-    fd.launch([ph], rows, torch.device(DEV), grid=grid)
+    fd.launch([ph], rows, torch.device(DEV), grid=grid, impl=impl)
     want = fd.ref_plain(lw.w, lw.scale_t, xq, xs, rows, residual=h0)
     close(h, want, name="residual stream")
     # the quantised form and the statistics describe the bf16 values the kernel itself wrote
@@ -88,7 +91,8 @@ def test_resid_quant_phase(rows, d, k, grid):
 
 @pytest.mark.parametrize("rows,ffn,k,grid,act", [(3, 256, 256, 4, 0), (16, 1792, 512, 148, 0), (32, 14336, 4096, 148, 0),
                                                  (32, 384, 1024, 9, 1)])
-def test_silu_quant_phase(rows, ffn, k, grid, act):
+@pytest.mark.parametrize("impl", IMPLS)
+def test_silu_quant_phase(impl, rows, ffn, k, grid, act):
     bn = 16 if rows <= 16 else 32
     lw = _weights(2 * ffn, k, ffn + k)
     xq, xs = _acts(rows, k, bn, rows + 2)
@@ -97,7 +101,8 @@ def test_silu_quant_phase(rows, ffn, k, grid, act):
     s = torch.zeros((ffn // 128, bn), dtype=torch.float32, device=DEV)
     ph = fd.phase(fd.SILU_QUANT, lw.w, lw.scale_t, xq, xs, n=ffn, k=k, dual_off=ffn, ssq_in=ssq_in, norm_dim=k, eps=1e-5,
                   act=act, q_out=q, s_out=s, ld_s_out=bn)
-    fd.launch([ph], rows, torch.device(DEV), grid=grid)
+    il = [fd.interleave_gate_up(lw.w, lw.scale_t, ffn)]
+    fd.launch([ph], rows, torch.device(DEV), grid=grid, impl=impl, interleaved=il)
     norm = fd.ref_norm_factor(ssq_in, rows, k, 1e-5)
     want = fd.ref_silu(lw.w, lw.scale_t, xq, xs, rows, ffn, ffn, norm, act)
     got = ref.dequant_fp8_1x128(q.cpu(), s.cpu()[:, :rows].contiguous())
@@ -110,7 +115,8 @@ def test_silu_quant_phase(rows, ffn, k, grid, act):
 
 @pytest.mark.parametrize("rows,hq,hkv,rd,fp8,grid", [(1, 4, 2, 128, True, 6), (16, 8, 2, 128, True, 148), (32, 32, 8, 128, True, 148),
                                                      (7, 4, 4, 64, False, 11), (9, 2, 1, 128, True, 1)])
-def test_rope_kv_phase(rows, hq, hkv, rd, fp8, grid):
+@pytest.mark.parametrize("impl", IMPLS)
+def test_rope_kv_phase(impl, rows, hq, hkv, rd, fp8, grid):
     hd, d, page = 128, 512, 16
     bn = 16 if rows <= 16 else 32
     n = (hq + 2 * hkv) * hd
@@ -139,7 +145,7 @@ def test_rope_kv_phase(rows, hq, hkv, rd, fp8, grid):
     ph = fd.phase(fd.ROPE_KV, lw.w, lw.scale_t, xq, xs, n=n, k=d, ssq_in=ssq_in, norm_dim=d, eps=1e-6, y=qout, ldy=hq * hd,
                   ld_s_out=bn)
     rope = fd.rope_desc(positions.to(DEV), seq_index.to(DEV), block_table.to(DEV), kv, hq, hkv, rd, theta)
-    fd.launch([ph], rows, torch.device(DEV), rope, grid=grid)
+    fd.launch([ph], rows, torch.device(DEV), rope, grid=grid, impl=impl)
     # reference: projection (fp32), norm factor, then the per-op rotary + append on CPU tensors
     norm = fd.ref_norm_factor(ssq_in, rows, d, 1e-6)
     qkv = fd.ref_plain(lw.w, lw.scale_t, xq, xs, rows, norm=norm)
@@ -167,7 +173,8 @@ def test_rope_kv_phase(rows, hq, hkv, rd, fp8, grid):
 
 
 @pytest.mark.parametrize("rows,grid", [(4, 148), (32, 148), (32, 5)])
-def test_four_phase_chain_matches_sequential_reference(rows, grid):
+@pytest.mark.parametrize("impl", IMPLS)
+def test_four_phase_chain_matches_sequential_reference(impl, rows, grid):
     """o-proj -> gate/up -> down -> head as one launch: outputs of each phase feed the next through the grid barrier."""
     d, qs, ffn, vocab = 512, 256, 768, 1000
     bn = 16 if rows <= 16 else 32
@@ -187,7 +194,8 @@ def test_four_phase_chain_matches_sequential_reference(rows, grid):
         fd.phase(fd.RESID_QUANT, wd.w, wd.scale_t, actq, acts, n=d, k=ffn, y=h, ldy=d, residual=h, q_out=hq, s_out=hs, ssq_out=ssq, ld_s_out=bn),
         fd.phase(fd.PLAIN, wh.w, wh.scale_t, hq, hs, n=vocab, k=d, ssq_in=ssq, norm_dim=d, eps=eps, y=logits, ldy=vocab, ld_s_out=bn),
     ]
-    fd.launch(phases, rows, dev, grid=grid)
+    il = [None, fd.interleave_gate_up(wgu.w, wgu.scale_t, ffn), None, None]
+    fd.launch(phases, rows, dev, grid=grid, impl=impl, interleaved=il)
     got_logits = logits.clone()
     # sequential reference with the kernel's rounding points
     h1 = ref.round_bf16(fd.ref_plain(wo.w, wo.scale_t, aq, a_s, rows, residual=h0))
@@ -204,7 +212,7 @@ def test_four_phase_chain_matches_sequential_reference(rows, grid):
     assert ((got - wantf).norm() / wantf.norm()).item() < 3e-2
     # replays are bit-identical (fixed summation order of split tiles)
     h.copy_(h0)
-    fd.launch(phases, rows, dev, grid=grid)
+    fd.launch(phases, rows, dev, grid=grid, impl=impl, interleaved=il)
     assert torch.equal(logits, got_logits)
     _status_ok()
 
@@ -226,8 +234,9 @@ def test_embed_quant():
     assert torch.allclose(ssq.cpu()[:, :rows], ssq_ref, rtol=1e-5)
 
 
+@pytest.mark.parametrize("impl", IMPLS)
 @pytest.mark.parametrize("batch", [1, 3, 16, 32])
-def test_engine_decode_fused_matches_per_op_path(batch, monkeypatch):
+def test_engine_decode_fused_matches_per_op_path(batch, impl, monkeypatch):
     """Whole decode steps: the fused chain and the per-op path produce the same greedy tokens and close logits."""
     from sllm_b200.engine.engine import build_engine
     from sllm_b200.models.config import ModelConfig
@@ -238,6 +247,7 @@ def test_engine_decode_fused_matches_per_op_path(batch, monkeypatch):
 
     def run(fused: bool):
         monkeypatch.setenv("SLLM_FUSED_DECODE", "1" if fused else "0")
+        monkeypatch.setenv("SLLM_FD_BACKEND", impl)
         eng = build_engine(cfg, DEV, seed=3, max_batch=32, use_cuda_graphs=False)
         seqs = [eng.new_sequence(p) for p in prompts]
         for s, t in zip(seqs, eng.prefill(seqs)):
