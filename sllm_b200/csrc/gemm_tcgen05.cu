@@ -112,6 +112,7 @@ struct GemmParams {
   int epilogue;        // 0 = store, 1 = add residual
   int cluster_split;   // 1: gridDim.z CTAs form one cluster and reduce split-K partials over DSMEM
   int const_operand;   // operand that no kernel writes (weights): 0 none, 1 A, 2 B; loaded before the PDL wait
+  int early_trigger;   // 1: dependents may become resident as soon as this CTA holds its resources
   const float* scale_a;  // [num_kb, ld_sa]
   const float* scale_b;  // [num_kb, ld_sb]
   __nv_bfloat16* y;
@@ -247,6 +248,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
   if (threadIdx.x == 0) TRACE(1);
+  // With the early trigger the next kernel's CTAs become resident while this one runs (where shared memory and
+  // TMEM allow): their set-up and the first ring of weight tiles then overlap this kernel instead of following it.
+  if (p.early_trigger && threadIdx.x == 0) pdl_trigger();
 
   // Epilogue-thread coordinates (meaningful for warps 2..5 only).
   const int q = warp & 3;              // TMEM lane quarter this warp may read
@@ -256,6 +260,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   float acc[BN];
   bool ok = true;
   bool active = true;   // this CTA takes part in the output phase (false for non-final global split-K CTAs)
+  float rn_lane = 1.f;  // fused row epilogue: RMSNorm factor of token row `lane`
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -394,6 +399,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     // ------------------------------------------------------------ epilogue main loop (128 threads)
     pdl_wait();
+    if constexpr (kScaled && BN <= 32) {
+      // norm factor of every token row from the sums of squares its producer wrote: requested now, used after the
+      // last K block, so the L2 round trip hides under the main loop
+      if (p.fe.mode != 0 && p.fe.norm_tiles > 0 && lane < p.b_rows) {
+        float ss = 0.f;
+        for (int i = 0; i < p.fe.norm_tiles; ++i) ss += __ldcg(p.fe.ssq_in + static_cast<size_t>(i) * p.fe.ld_s + lane);
+        rn_lane = rsqrtf(ss / static_cast<float>(p.fe.norm_dim) + p.fe.eps);
+      }
+    }
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
     for (int c = 0; c < BN; ++c) acc[c] = 0.f;
@@ -514,7 +528,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   }
 
   if (threadIdx.x == 64) TRACE(7);
-  constexpr bool kFusable = kScaled && !kComm && BN <= 32;      // instantiations that carry the fused row epilogue
+  constexpr bool kFusable = kScaled && BN <= 32;      // instantiations that carry the fused row epilogue
   const bool pair_x = kFusable && p.fe.mode == SLLM_FD_SILU_QUANT + 1;     // cluster of two tiles along x (no K split)
   if (cluster_split || pair_x) cluster_sync_all();  // partials visible cluster-wide
   if (threadIdx.x == 64) TRACE(8);
@@ -543,20 +557,83 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       e.y = p.y; e.residual = p.residual;
       e.q_out = fe.q_out; e.s_out = fe.s_out; e.ssq_out = fe.ssq_out;
       e.rope = &fe.rope; e.inv_freq = fe.inv_freq;
-      for (int cl = ew; cl < cw; cl += 4) {
+      [[maybe_unused]] uint32_t comm_epoch = 0;
+      [[maybe_unused]] long long comm_region = 0, comm_toff = 0;
+      [[maybe_unused]] bool comm_ok = true;
+      if constexpr (kComm) {
+        // ---- tensor parallelism: this rank's partial of every row of the slice goes (bf16) to all ranks, then
+        // flags, a bounded wait for the peers' flags, and below the rows are summed in rank order
+        const CommParams& cm = p.comm;
+        const int tile_id = a_tile * gridDim.y + b_tile;
+        const int slot = tile_id * kMaxSlices + (cluster_split ? split : 0);
+        if (et == 0) {
+          const uint32_t e1 = cm.epoch[slot] + 1;
+          cm.epoch[slot] = e1;
+          bars->epoch = e1;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        comm_epoch = bars->epoch;
+        comm_region = static_cast<long long>(comm_epoch & 1) * cm.world;
+        comm_toff = static_cast<long long>(tile_id) * (kTileA * BN);
+        for (int cl = ew; cl < cw; cl += 4) {
+          const int col = c0 + cl;
+          if (col >= T) break;
+          const float* src = red + col * kTileA + lane * 4;
+          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s = 0; s < nslice; ++s) {
+            const float4 x = nslice == 1 ? *reinterpret_cast<const float4*>(src) : ld_dsmem_f32x4(src, s);
+            sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
+          }
+          uint2 w;
+          *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(sum.x, sum.y);
+          *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(sum.z, sum.w);
+          const long long off = (comm_region + cm.rank) * cm.cap_elems + comm_toff + col * kTileA + lane * 4;
+          for (int peer = 0; peer < cm.world; ++peer) *reinterpret_cast<uint2*>(cm.recv[peer] + off) = w;
+        }
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et < cm.world && et != cm.rank) {
+          st_release_sys(cm.flags[et] + static_cast<size_t>(slot) * cm.world + cm.rank, comm_epoch);
+          const uint32_t* f = cm.flags[cm.rank] + static_cast<size_t>(slot) * cm.world + et;
+          uint32_t spins = 0;
+          long long t0 = 0;
+          while (static_cast<int32_t>(ld_acquire_sys(f) - comm_epoch) < 0) {
+            ++spins;
+            if (spins == 1024) t0 = clock64();
+            if (spins > 1024 && (spins & 63) == 0) {
+              if (*abort_flag) break;
+              if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                if (p.status) atomicCAS(p.status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
+                break;
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*abort_flag) comm_ok = false;
+      }
+      for (int cl = ew; cl < cw && comm_ok; cl += 4) {
         const int col = c0 + cl;
         if (col >= T) break;
-        float rn = 1.f;
-        if (fe.norm_tiles > 0) {
-          float ss = 0.f;
-          for (int i = lane; i < fe.norm_tiles; i += 32) ss += __ldcg(fe.ssq_in + static_cast<size_t>(i) * fe.ld_s + col);
-          rn = rsqrtf(warp_sum(ss) / static_cast<float>(fe.norm_dim) + fe.eps);
-        }
-        const float* src = red + col * kTileA + lane * 4;
+        const float rn = __shfl_sync(0xffffffffu, rn_lane, col);
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s = 0; s < nslice; ++s) {
-          const float4 x = nslice == 1 ? *reinterpret_cast<const float4*>(src) : ld_dsmem_f32x4(src, s);
-          sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
+        if constexpr (kComm) {
+          const CommParams& cm = p.comm;
+          for (int src = 0; src < cm.world; ++src) {
+            const uint2 w = __ldcg(reinterpret_cast<const uint2*>(cm.recv[cm.rank] + (comm_region + src) * cm.cap_elems +
+                                                                  comm_toff + col * kTileA + lane * 4));
+            const __nv_bfloat162 h0 = *reinterpret_cast<const __nv_bfloat162*>(&w.x);
+            const __nv_bfloat162 h1 = *reinterpret_cast<const __nv_bfloat162*>(&w.y);
+            sum.x += __bfloat162float(h0.x); sum.y += __bfloat162float(h0.y);
+            sum.z += __bfloat162float(h1.x); sum.w += __bfloat162float(h1.y);
+          }
+        } else {
+          const float* src = red + col * kTileA + lane * 4;
+          for (int s = 0; s < nslice; ++s) {
+            const float4 x = nslice == 1 ? *reinterpret_cast<const float4*>(src) : ld_dsmem_f32x4(src, s);
+            sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
+          }
         }
         float v[4] = {sum.x * rn, sum.y * rn, sum.z * rn, sum.w * rn};
         if (pair_x) {
@@ -585,8 +662,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       cluster_sync_all();     // both tiles' row maxima are written (all threads of both CTAs take part)
       if (epi_warp) {
         const uint32_t partner = (blockIdx.x & 1u) ^ 1u;
+        const float amax_lane = lane < T ? fmaxf(bars->famax[lane], ld_dsmem_f32(&bars->famax[lane], partner)) : 0.f;
         for (int col = ew; col < T; col += 4) {
-          const float amax = fmaxf(bars->famax[col], ld_dsmem_f32(&bars->famax[col], partner));
+          const float amax = __shfl_sync(0xffffffffu, amax_lane, col);
           const float scale = amax > 0.f ? amax / 448.f : 1.f;
           if (lane < 16) {
             const float4 x = *reinterpret_cast<const float4*>(red + col * kTileA + lane * 4);
@@ -915,6 +993,17 @@ SLLM_EXPORT long long sllm_gemm_workspace_floats(int a_rows, int b_rows, int bn,
 
 static int g_disable_cluster_split = 0;
 
+// SLLM_GEMM_EARLY_TRIGGER=0/1 (default 0) or sllm_gemm_set_early_trigger: see GemmParams::early_trigger.
+static int g_gemm_early = -1;
+static int gemm_early_trigger() {
+  if (g_gemm_early < 0) {
+    const char* e = getenv("SLLM_GEMM_EARLY_TRIGGER");
+    g_gemm_early = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_gemm_early;
+}
+SLLM_EXPORT void sllm_gemm_set_early_trigger(int enabled) { g_gemm_early = enabled ? 1 : 0; }
+
 struct SllmCommDesc {   // host-side mirror passed by the Python layer (ctypes.Structure)
   int world, rank;
   long long cap_elems;
@@ -997,14 +1086,16 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
   const bool pow2 = splits == 2 || splits == 4 || splits == 8;
   p.cluster_split = (pow2 && bn % splits == 0 && (transpose_out || bn / splits >= 8) && !g_disable_cluster_split) ? 1 : 0;
   p.const_operand = transpose_out ? 1 : 2;   // swap-AB: A is the weight matrix, else B is
+  p.early_trigger = gemm_early_trigger();
   p.scale_a = scale_a; p.scale_b = scale_b;
   p.y = static_cast<__nv_bfloat16*>(y);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ws = ws; p.counters = counters; p.status = status;
   if (fused) {
     // the row epilogue works on whole token rows of a tile: no K split, or a cluster split reduced over DSMEM
-    if (!scaled || !transpose_out || comm || gather || (splits > 1 && !p.cluster_split) || bn > 32)
+    if (!scaled || !transpose_out || gather || (splits > 1 && !p.cluster_split) || bn > 32)
       return SLLM_ERR_UNSUPPORTED_SHAPE;
+    if (comm && fused->mode != SLLM_FD_RESID_QUANT + 1) return SLLM_ERR_UNSUPPORTED_SHAPE;   // only row-parallel phases sum
     if (fused->mode == SLLM_FD_SILU_QUANT + 1 && (splits != 1 || (a_tiles & 1))) return SLLM_ERR_UNSUPPORTED_SHAPE;
     p.fe = *fused;
   }
@@ -1144,9 +1235,11 @@ SLLM_EXPORT int sllm_gemm_allgather(const void* w, void* y, const void* residual
 // Y[t, n] = X[t, :] . W[n, :] (block-scaled FP8, weights as the 128-row operand), K split over a thread-block cluster
 // and reduced over DSMEM, then the PLAIN / RESID_QUANT / SILU_QUANT / ROPE_KV row epilogue.  For SILU_QUANT `ph->w`
 // is the gate / up matrix with rows interleaved per 128-row tile (64 gate rows, then the 64 up rows of the same
-// features) and `ph->w_scale` its scales in the same row order; dual_off is ignored.
+// features) and `ph->w_scale` its scales in the same row order; dual_off is ignored.  `comm` (a host SllmCommDesc, or
+// null) makes RESID_QUANT phases sum their rows across the tensor-parallel ranks before the residual joins.
 SLLM_EXPORT int sllm_gemm_fused(const SllmFdPhase* ph, const SllmFdRope* rope, int rows, int bn, int splits, int stages,
-                                float* ws, long long ws_floats, int* counters, int n_counters, int* status, void* stream) {
+                                float* ws, long long ws_floats, int* counters, int n_counters, int* status, void* stream,
+                                const void* comm) {
   if (!ph || rows < 1 || rows > 32 || !ph->w || !ph->w_scale || !ph->x || !ph->x_scale || ph->n <= 0 || ph->k <= 0 ||
       (ph->k & 127))
     return SLLM_ERR_INVALID_ARGUMENT;
@@ -1184,5 +1277,6 @@ SLLM_EXPORT int sllm_gemm_fused(const SllmFdPhase* ph, const SllmFdRope* rope, i
   if (ph->norm_tiles > 0 && (!ph->ssq_in || ph->norm_dim <= 0)) return SLLM_ERR_INVALID_ARGUMENT;
   return gemm_impl(ph->w, ph->x, y, ph->w_scale, ph->x_scale, ph->epilogue == SLLM_FD_SILU_QUANT ? nullptr : ph->residual,
                    w_rows, rows, ph->k, 1, 1, ph->ldy > 0 ? ph->ldy : ph->n, ph->ld_sa, ph->ld_sb, bn, splits, stages, ws,
-                   ws_floats, counters, n_counters, status, stream, nullptr, nullptr, &fe);
+                   ws_floats, counters, n_counters, status, stream,
+                   ph->epilogue == SLLM_FD_RESID_QUANT ? static_cast<const SllmCommDesc*>(comm) : nullptr, nullptr, &fe);
 }

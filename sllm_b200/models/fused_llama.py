@@ -106,7 +106,7 @@ class FusedLlamaDecoder:
         self.vocab_local = model.w.lm_head.out_features
         self.logits = z((rows, self.vocab_local), torch.bfloat16)
         fold_norms(cfg, model.w)
-        self.impl = fd.backend() if model.tp.size == 1 else "persistent"
+        self.impl = fd.backend()
         # the cluster GEMM's SiLU epilogue reads gate and up rows of the same features from one 128-row tile
         if self.impl == "cluster" and getattr(model.w, "gate_up_interleaved", None) is None:
             model.w.gate_up_interleaved = [fd.interleave_gate_up(lw.gate_up.w, lw.gate_up.scale_t, self.ffn_local)
@@ -149,7 +149,8 @@ class FusedLlamaDecoder:
         """Local logits [rows, vocab shard] (bf16); the final residual stream stays in ``self.h``."""
         m, cfg = self.model, self.model.cfg
         w, rows, dev = m.w, self.rows, self.device
-        comm = m.tp.desc if m.tp.size > 1 else None
+        # the persistent kernel numbers its exchange slots per tile, the cluster GEMM per (tile, K slice): two regions
+        comm = None if m.tp.size == 1 else (m.tp.desc if self.impl == "cluster" else m.tp.desc_fd)
         fd.embed_quant(w.embed, b.tokens, self.h, self.hq, self.hs, self.ssq, cfg.embedding_scale)
         ph, rope = self._qkv(w.layers[0], cache.layer(0), b)
         fd.launch([ph], rows, dev, rope, impl=self.impl)

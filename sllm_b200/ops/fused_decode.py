@@ -56,7 +56,7 @@ _lib.EXTRA_KERNEL_SIGNATURES.update({
     "sllm_fused_decode_set_trace": (None, [C.c_void_p]),
     "sllm_fused_decode_set_lookahead": (None, [C.c_int]),
     "sllm_gemm_fused": (C.c_int, [C.POINTER(FdPhase), C.POINTER(FdRope), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
-                                  C.c_longlong, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+                                  C.c_longlong, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
 })
 
 _abi_checked = False
@@ -198,7 +198,8 @@ def backend() -> str:
     return os.environ.get("SLLM_FD_BACKEND", "cluster")
 
 
-def _launch_cluster(phases: list, rows: int, device: torch.device, rope: Optional[FdRope], il: Optional[list]) -> None:
+def _launch_cluster(phases: list, rows: int, device: torch.device, rope: Optional[FdRope], il: Optional[list],
+                    comm=None) -> None:
     from .core import _gemm_plan
     wsp = workspace(device)
     lib = _lib.kernels()
@@ -220,7 +221,7 @@ def _launch_cluster(phases: list, rows: int, device: torch.device, rope: Optiona
             splits = 1
         rc = lib.sllm_gemm_fused(C.byref(one), C.byref(rope) if rope is not None else None, rows, bn, splits, stages,
                                  _p(wsp.ws), wsp.ws.numel(), _p(wsp.counters), wsp.counters.numel(), _p(wsp.status),
-                                 _stream())
+                                 _stream(), None if comm is None else C.cast(C.pointer(comm), C.c_void_p))
         _lib.check(rc, "gemm_fused")
 
 
@@ -233,8 +234,8 @@ def launch(phases: list, rows: int, device: torch.device, rope: Optional[FdRope]
     if not 1 <= len(phases) <= MAX_PHASES or not 1 <= rows <= MAX_ROWS:
         raise ValueError("a fused decode launch takes 1..4 phases and 1..32 rows")
     impl = impl or backend()
-    if impl == "cluster" and comm is None:
-        return _launch_cluster(phases, rows, device, rope, interleaved)
+    if impl == "cluster":
+        return _launch_cluster(phases, rows, device, rope, interleaved, comm)
     st = state(device)
     d = FdDesc()
     d.n_phases, d.rows, d.n_counters, d.grid = len(phases), rows, st.counters.numel(), grid

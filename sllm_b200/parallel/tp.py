@@ -98,7 +98,13 @@ class FusedTP(NcclTP):
         flag_bytes = self.max_tiles * 8 * size * 4   # 8 cluster slices per tile
         small_slot = max_rows_small * 8
         small_bytes = 2 * size * small_slot
-        total = recv_bytes + flag_bytes + small_bytes + 4096
+        # the fused decode path sums whole 128-row tiles of up to 32 token rows: its own receive buffers, flags and
+        # epochs (one slot per tile), so that its slot numbering never meets the per-GEMM kernel's in one region
+        self.fd_cap_elems = 32 * n_pad
+        self.fd_max_tiles = n_pad // 128
+        fd_recv_bytes = 2 * size * self.fd_cap_elems * 2
+        fd_flag_bytes = self.fd_max_tiles * size * 4
+        total = recv_bytes + flag_bytes + small_bytes + fd_recv_bytes + fd_flag_bytes + 8192
         self.region = SymmetricRegion(total, size, rank, group)
         self.off_recv = self.region.carve(recv_bytes)
         self.off_flags = self.region.carve(flag_bytes)
@@ -116,6 +122,17 @@ class FusedTP(NcclTP):
             self.desc.recv[r] = recv[r]
             self.desc.flags[r] = flags[r]
         self.desc.epoch = self.epoch.data_ptr()
+        off_fd_recv = self.region.carve(fd_recv_bytes)
+        off_fd_flags = self.region.carve(fd_flag_bytes)
+        self.fd_epoch = torch.zeros(self.fd_max_tiles + 8, dtype=torch.int32, device=device)
+        self.desc_fd = CommDesc()
+        self.desc_fd.world, self.desc_fd.rank = size, rank
+        self.desc_fd.cap_elems, self.desc_fd.max_tiles = self.fd_cap_elems, self.fd_max_tiles
+        fd_recv, fd_flags = self.region.peer_array(off_fd_recv), self.region.peer_array(off_fd_flags)
+        for r in range(size):
+            self.desc_fd.recv[r] = fd_recv[r]
+            self.desc_fd.flags[r] = fd_flags[r]
+        self.desc_fd.epoch = self.fd_epoch.data_ptr()
         self._small_bases = self.region.peer_array(0)
         self._small_src = torch.zeros(small_slot, dtype=torch.uint8, device=device)
         self._small_dst = torch.zeros(size * small_slot, dtype=torch.uint8, device=device)

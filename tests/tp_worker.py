@@ -92,6 +92,10 @@ def main():
     ref_eng = build_engine(cfg, dev, seed=1, max_batch=4)
     ref_seqs = [ref_eng.new_sequence(p) for p in prompts]
     want_logits = ref_eng.prefill(ref_seqs, sample=False).float()
+    first = want_logits.argmax(-1).tolist()
+    for s, t in zip(ref_seqs, first):
+        s.tokens.append(t)
+    want_decode = ref_eng.decode(ref_seqs, sample=False).float().clone()      # one decode step (the fused decode path)
     for tp in (fused, nccl):
         mark(f"building {tp.impl} engine")
         eng = build_engine(cfg, dev, seed=1, max_batch=4, tp=tp)
@@ -99,6 +103,14 @@ def main():
         got_logits = eng.prefill(seqs, sample=False).float()
         assert got_logits.shape == want_logits.shape
         assert rel(got_logits, want_logits) < 0.12, (tp.impl, rel(got_logits, want_logits))  # fp8 model, bf16 partial sums
+        # decode step of the same sequences: with the fused communicator this is the fused decode chain, whose
+        # row-parallel phases sum their tiles across ranks inside the kernel
+        for s, t in zip(seqs, first):
+            s.tokens.append(t)
+        got_decode = eng.decode(seqs, sample=False).float()
+        assert rel(got_decode, want_decode) < 0.12, (tp.impl, "decode", rel(got_decode, want_decode))
+        if tp.impl == "fused":
+            assert bool(eng.model._fused), "the tensor-parallel decode step did not take the fused chain"
         for s in seqs:
             eng.free_sequence(s)
         mark(f"{tp.impl} prefill logits ok")
