@@ -1,7 +1,7 @@
 """Session checkpoints: a little-endian, digest-protected envelope and a quota-bound store.
 
 File layout (all integers little endian):
-    0   8  magic "SLLMCKP1"
+    0   8  magic "SB2CKPT1"
     8   2  schema version (1)         10  2  section count
     12  4  header bytes               16  8  total file bytes
     24  4  reserved (0)               28 32  SHA-256 of the whole file with this field zeroed
@@ -15,8 +15,11 @@ planes (opaque native KV pages, one section per plane), 5 sampler state (JSON), 
 Decoding checks magic, version, bounds, table/payload overlap, every section digest, the file digest and
 (optionally) that the identity matches the running model before any state is imported.  The store writes
 to a temporary file in the same directory, fsyncs and renames (atomic replace), enforces a byte quota and
-validates ids (reference: crates/sllm-core/src/session_checkpoint.rs:22-44 constants, :530-779 codec,
-:1332-1540 store).
+validates ids.  The envelope plays the role of the reference's `SLLMCKP1` container
+(crates/sllm-core/src/session_checkpoint.rs:22-44 constants, :530-779 codec, :1332-1540 store) and protects the same
+things, but it is NOT wire-compatible with it: the state planes are this engine's head-major KV pages, sections are
+32-byte aligned and one per plane, and the identity block differs.  It therefore carries its own magic and schema id,
+so that a file of either engine is rejected by the other as "not a session checkpoint" instead of as a malformed one.
 """
 from __future__ import annotations
 
@@ -30,9 +33,9 @@ from typing import Optional
 
 import numpy as np
 
-MAGIC = b"SLLMCKP1"
+MAGIC = b"SB2CKPT1"
 SCHEMA_VERSION = 1
-SCHEMA_ID = "sllm-session-checkpoint-v1"
+SCHEMA_ID = "sllm-b200-session-checkpoint-v1"
 MAX_HEADER_BYTES = 4096 + 56 * 4096
 MAX_SECTIONS = 4096
 MAX_CHECKPOINT_BYTES = 64 << 30

@@ -105,7 +105,7 @@ def main(argv=None) -> int:
         p.add_argument("--output", required=True)
         p.add_argument("--derived-lock", required=True)
         p.add_argument("--converter-commit", default="unknown")
-        p.add_argument("--weight-format", choices=("fp32", "bf16", "fp8"), default="bf16")
+        p.add_argument("--weight-format", choices=("fp32", "bf16", "fp8", "nvfp4", "mxfp4"), default="bf16")
         p.add_argument("--seed", type=int, default=0)
         p.add_argument("--layers", type=int, default=None)
         p.add_argument("--synthetic-tokenizer", action="store_true",

@@ -594,7 +594,7 @@ SLLM_EXPORT int sllm_argmax_noalloc_max_rows(void) { return kNoAllocMaxRows; }
 
 SLLM_EXPORT int sllm_argmax_noalloc(const void* logits, int* out_idx, float* out_val, int rows, int n, int ld,
                                     int index_offset, void* stream) {
-  if (!logits || !out_idx || rows <= 0 || n <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  if (!logits || !out_idx || rows <= 0 || n <= 0 || ld < n) return SLLM_ERR_INVALID_ARGUMENT;   // rows may not overlap
   if (rows > kNoAllocMaxRows) return SLLM_ERR_LIMIT;   // larger batches must use sllm_argmax with a workspace
   // The array's name is only a host-side handle; the kernel needs its device address, which is looked
   // up once per device (with that device current) and remembered.
@@ -613,10 +613,8 @@ SLLM_EXPORT int sllm_argmax_noalloc(const void* logits, int* out_idx, float* out
         cudaGetLastError();
         return SLLM_ERR_CUDA;
       }
-      // counters must start at zero; the kernel leaves them zero after every launch
-      if (cudaMemsetAsync(static_cast<unsigned char*>(p) + kNoAllocPartialBytes, 0, kNoAllocMaxRows * sizeof(int), st) !=
-          cudaSuccess)
-        return SLLM_ERR_CUDA;
+      // the counters need no clearing here: a __device__ array is zero when the library image is loaded, and
+      // the kernel returns every counter to zero before it ends
       scratch_ptr[dev] = p;
     }
     base = scratch_ptr[dev];

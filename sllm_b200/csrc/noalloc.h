@@ -17,8 +17,9 @@
  *     status 7 (limit exceeded) and nothing is launched;
  *   - the scratch (about 257 KiB: partial records plus one counter per row) is a fixed array in the
  *     library image, so every GPU that loads the library carries it until the process ends;
- *   - the first call on each device looks up the array's device address and zeroes its counters.
- *     Make that first call outside of any stream capture; later calls only launch the kernel;
+ *   - the first call on each device looks up the array's device address (the array itself starts zeroed when
+ *     the library is loaded).  Make that first call before any stream capture; later calls only launch the kernel;
+ *   - ld (the row stride) must be at least n: overlapping rows are refused with status 1;
  *   - all calls share the one array.  It keeps whatever the previous call left there; the counters
  *     are returned to zero by every launch, the records are overwritten before they are read.  Two
  *     calls whose kernels may overlap on the GPU (different streams, no ordering) would race on it:

@@ -145,6 +145,10 @@ class Engine:
         if self.has_state and length < s.num_computed:
             raise ValueError("a recurrent-state model cannot rewind computed tokens without a state snapshot")
         self.cache.pool.truncate(s.seq_id, length)
+        # the new tail may sit inside a page that a forked sibling or a prefix-cache entry still references: the next
+        # append must not write into it (copy-on-write of the tail page)
+        if hasattr(self.cache, "ensure_private_tail"):
+            self.cache.ensure_private_tail(s.seq_id)
         s.num_computed = min(s.num_computed, length)
         del s.tokens[length:]
         log = self._hidden_log.get(s.seq_id)

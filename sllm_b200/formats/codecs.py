@@ -202,6 +202,53 @@ def dequantize_nvfp4(packed: np.ndarray, block_scales: np.ndarray, tensor_scale,
     return decode_e2m1(codes) * s
 
 
+# ---------------------------------------------------------------------------------------------- GGML super-blocks
+# GGUF stores 4-bit tensors as standard GGML blocks (reference: crates/sllm-core/src/gguf_convert.rs:33-143, lossless
+# regrouping of its adjacent-pair nibble planes):
+#   MXFP4 (type 39): per 32 elements 17 bytes = E8M0 scale, then 16 bytes with byte i = code[i] | code[i + 16] << 4
+#   NVFP4 (type 40): per 64 elements 36 bytes = four E4M3 block-16 scales, then per sub-block of 16 elements 8 bytes
+#                    with byte i = code[i] | code[i + 8] << 4; the FP32 tensor scale travels as its own tensor
+def _to_ggml_halves(codes: np.ndarray, span: int) -> np.ndarray:
+    """[..., K] codes -> bytes grouped per `span` elements as (element i | element i + span / 2 << 4)."""
+    c = codes.reshape(codes.shape[:-1] + (codes.shape[-1] // span, 2, span // 2))
+    return (c[..., 0, :] | (c[..., 1, :] << 4)).astype(np.uint8)          # [..., K / span, span / 2]
+
+
+def _from_ggml_halves(b: np.ndarray, span: int) -> np.ndarray:
+    lo, hi = b & 0xF, b >> 4                                              # [..., blocks, span / 2]
+    return np.concatenate([lo, hi], axis=-1).reshape(b.shape[:-2] + (b.shape[-2] * span,)).astype(np.uint8)
+
+
+def to_ggml_mxfp4(packed: np.ndarray, scales: np.ndarray, k: int) -> bytes:
+    """Adjacent-pair codes [N, K/2] + E8M0 scales [N, K/32] -> GGML MXFP4 blocks (K a multiple of 32)."""
+    if k % 32:
+        raise ValueError("MXFP4 rows must be a multiple of 32 elements")
+    q = _to_ggml_halves(unpack_nibbles(packed, k), 32)                    # [N, K/32, 16]
+    out = np.concatenate([np.asarray(scales, dtype=np.uint8)[..., None], q], axis=-1)
+    return np.ascontiguousarray(out).tobytes()
+
+
+def from_ggml_mxfp4(raw, n: int, k: int):
+    b = np.frombuffer(raw, dtype=np.uint8).reshape(n, k // 32, 17)
+    return pack_nibbles(_from_ggml_halves(b[..., 1:], 32)), np.ascontiguousarray(b[..., 0])
+
+
+def to_ggml_nvfp4(packed: np.ndarray, block_scales: np.ndarray, k: int) -> bytes:
+    """Adjacent-pair codes [N, K/2] + E4M3 block-16 scales [N, K/16] -> GGML NVFP4 blocks (K a multiple of 64)."""
+    if k % 64:
+        raise ValueError("NVFP4 rows must be a multiple of 64 elements")
+    n = packed.shape[0]
+    q = _to_ggml_halves(unpack_nibbles(packed, k), 16).reshape(n, k // 64, 32)
+    sc = np.asarray(block_scales, dtype=np.uint8).reshape(n, k // 64, 4)
+    return np.ascontiguousarray(np.concatenate([sc, q], axis=-1)).tobytes()
+
+
+def from_ggml_nvfp4(raw, n: int, k: int):
+    b = np.frombuffer(raw, dtype=np.uint8).reshape(n, k // 64, 36)
+    codes = _from_ggml_halves(b[..., 4:].reshape(n, k // 16, 8), 16)
+    return pack_nibbles(codes), np.ascontiguousarray(b[..., :4].reshape(n, k // 16))
+
+
 def decode_e8m0(code: np.ndarray) -> np.ndarray:
     c = np.asarray(code, dtype=np.uint8)
     if np.any(c == 255):

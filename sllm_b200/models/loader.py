@@ -23,6 +23,9 @@ from .llama import LayerWeights, LlamaWeights
 
 CONVERTER_ID = "sllm-b200-convert-gguf-v1"
 FP8_ENCODING = "fp8-e4m3fn-kblock128-f32-scale"
+FP8_CHANNEL_ENCODINGS = ("fp8-e4m3fn-channel-f32-scale", "fp8-e4m3fn-channel-bf16-scale")
+NVFP4_ENCODING = "nvfp4-e2m1-block16-e4m3fn-f32-outer"
+MXFP4_ENCODING = "mxfp4-e2m1-block32-e8m0"
 
 
 def _bf16_bytes(t: torch.Tensor) -> bytes:
@@ -39,9 +42,11 @@ def _u8_bytes(t: torch.Tensor) -> bytes:
 
 def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_json: Optional[str] = None,
                       chat_template: Optional[str] = None, source_fingerprints: tuple = (),
-                      converter_args: Optional[dict] = None, mtp=None, vision=None) -> dict:
+                      converter_args: Optional[dict] = None, mtp=None, vision=None, fp8_channel_scales: bool = False) -> dict:
     """Writes unsharded (tensor-parallel size 1) weights; returns the derived lock document.  ``mtp``
-    (models.mtp.MtpWeights, dense) adds the multi-token-prediction component as `mtp.*` tensors."""
+    (models.mtp.MtpWeights, dense) adds the multi-token-prediction component as `mtp.*` tensors.
+    ``fp8_channel_scales`` writes FP8 projections with one FP32 scale per output row (the reference's "outer vector"
+    form, re-quantised from the resident values) instead of 1x128 block scales."""
     tensors, bindings = [], []
     dense_t = G.T_F32 if cfg.weight_format == "fp32" else G.T_BF16
     dense_b = _f32_bytes if cfg.weight_format == "fp32" else _bf16_bytes
@@ -50,7 +55,15 @@ def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_js
         tensors.append((name, tuple(t.shape), dense_t, dense_b(t)))
 
     def add_linear(name, lw: LinearWeight, r0: int, r1: int):
-        if lw.kind == "fp8":
+        if lw.kind == "fp8" and fp8_channel_scales:
+            from ..formats import codecs
+            codes, sc = codecs.quantize_fp8_outer_rows(lw.dequantized()[r0:r1].cpu().numpy())
+            tensors.append((name, tuple(codes.shape), G.T_I8, np.ascontiguousarray(codes).tobytes()))
+            tensors.append((name + ".scale", (codes.shape[0],), G.T_F32, np.asarray(sc, dtype="<f4").tobytes()))
+            bindings.append({"logical_tensor": name, "value_tensor": name, "encoding": FP8_CHANNEL_ENCODINGS[0],
+                             "role": "weight", "logical_shape": list(codes.shape), "scope": "consumed",
+                             "scales": [{"role": "channel", "tensor": name + ".scale"}]})
+        elif lw.kind == "fp8":
             val = lw.w[r0:r1]
             sc = lw.scale_t[:, r0:r1].t().contiguous()          # file layout [N, ceil(K/128)]
             tensors.append((name, tuple(val.shape), G.T_I8, _u8_bytes(val)))
@@ -58,6 +71,24 @@ def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_js
             bindings.append({"logical_tensor": name, "value_tensor": name, "encoding": FP8_ENCODING, "role": "weight",
                              "logical_shape": list(val.shape), "scope": "consumed",
                              "scales": [{"role": "block", "tensor": name + ".scale"}]})
+        elif lw.kind == "w4":
+            # 4-bit weights travel as standard GGML blocks (MXFP4 type 39, NVFP4 type 40); an NVFP4 tensor also binds
+            # its FP32 tensor ("outer") scale (reference: gguf_convert.rs:33-96, recipe encodings gguf.rs:175-180)
+            from ..formats import codecs
+            w4 = lw.w4
+            packed, scales = w4.to_file_layout(0)
+            packed, scales = packed[r0:r1], scales[r0:r1]
+            shape = (r1 - r0, w4.k)
+            if w4.fmt == "mxfp4":
+                tensors.append((name, shape, G.T_MXFP4, codecs.to_ggml_mxfp4(packed, scales, w4.k)))
+                bindings.append({"logical_tensor": name, "value_tensor": name, "encoding": MXFP4_ENCODING, "role": "weight",
+                                 "logical_shape": list(shape), "scope": "consumed", "scales": []})
+            else:
+                tensors.append((name, shape, G.T_NVFP4, codecs.to_ggml_nvfp4(packed, scales, w4.k)))
+                tensors.append((name + ".outer_scale", (1,), G.T_F32, _f32_bytes(w4.tensor_scale[:1])))
+                bindings.append({"logical_tensor": name, "value_tensor": name, "encoding": NVFP4_ENCODING, "role": "weight",
+                                 "logical_shape": list(shape), "scope": "consumed",
+                                 "scales": [{"role": "outer", "tensor": name + ".outer_scale"}]})
         else:
             add_dense(name, lw.w[r0:r1])
 
@@ -142,18 +173,82 @@ def load_llama_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, k
             v = dense(name)
             v = v[lo:hi] if cols is None else v[lo:hi, cols[0]:cols[1]]
             return v, None
-        if b["encoding"] != FP8_ENCODING or t.ttype != G.T_I8:
-            raise G.GgufError(f"{name}: unsupported encoding {b['encoding']}")
-        v = g.upload(name, device, torch.uint8).view(t.shape)
-        sname = b["scales"][0]["tensor"]
-        s = g.upload(sname, device, torch.float32).view(g.tensors[sname].shape)
+        enc = b["encoding"]
+        if enc in (NVFP4_ENCODING, MXFP4_ENCODING):
+            return w4_rows(name, t, b, lo, hi, cols)
+        if enc in FP8_CHANNEL_ENCODINGS and t.ttype == G.T_I8:
+            # one scale per output row ("outer vector", the form the reference executes: fp8.rs:201): the same scale
+            # for every 128-wide K block is the block-scaled form of it, exactly
+            v = g.upload(name, device, torch.uint8).view(t.shape)
+            sname = b["scales"][0]["tensor"]
+            st = g.tensors[sname]
+            if st.ttype == G.T_BF16:
+                sv = g.upload(sname, device, torch.bfloat16).float()
+            elif st.ttype == G.T_F32:
+                sv = g.upload(sname, device, torch.float32)
+            else:
+                raise G.GgufError(f"{sname}: unexpected scale tensor type {st.ttype}")
+            if sv.numel() != t.shape[0]:
+                raise G.GgufError(f"{sname}: expected one scale per output row")
+            s = sv.view(-1, 1).expand(t.shape[0], (t.shape[1] + 127) // 128).contiguous()
+        elif enc == FP8_ENCODING and t.ttype == G.T_I8:
+            v = g.upload(name, device, torch.uint8).view(t.shape)
+            sname = b["scales"][0]["tensor"]
+            s = g.upload(sname, device, torch.float32).view(g.tensors[sname].shape)
+        else:
+            raise G.GgufError(f"{name}: unsupported encoding {enc}")
         if cols is None:
             return v[lo:hi], s[lo:hi]
         if cols[0] % 128 or cols[1] % 128:
             raise G.GgufError("tensor-parallel column shards of FP8 weights must align to 128")
         return v[lo:hi, cols[0]:cols[1]], s[lo:hi, cols[0] // 128:cols[1] // 128]
 
+    def w4_rows(name, t, b, lo, hi, cols):
+        """A row / column range of a 4-bit tensor as ("w4", fmt, packed, scales, tensor_scale, k)."""
+        from ..formats import codecs
+        n, k = t.shape
+        raw = g.upload(name, "cpu", torch.uint8).numpy().tobytes()
+        if b["encoding"] == MXFP4_ENCODING:
+            if t.ttype != G.T_MXFP4:
+                raise G.GgufError(f"{name}: MXFP4 binding on tensor type {t.ttype}")
+            fmt, blk, ts = "mxfp4", 32, None
+            packed, scales = codecs.from_ggml_mxfp4(raw, n, k)
+        else:
+            if t.ttype != G.T_NVFP4:
+                raise G.GgufError(f"{name}: NVFP4 binding on tensor type {t.ttype}")
+            outer = [x for x in b.get("scales", []) if x.get("role") == "outer"]
+            if len(outer) != 1:
+                raise G.GgufError(f"{name}: an NVFP4 binding needs exactly one outer scale")
+            fmt, blk = "nvfp4", 16
+            ts = float(g.upload(outer[0]["tensor"], "cpu", torch.float32)[0])
+            packed, scales = codecs.from_ggml_nvfp4(raw, n, k)
+        packed, scales = packed[lo:hi], scales[lo:hi]
+        if cols is not None:
+            if cols[0] % 128 or cols[1] % 128:
+                raise G.GgufError("tensor-parallel column shards of 4-bit weights must align to 128")
+            packed, scales, k = packed[:, cols[0] // 2:cols[1] // 2], scales[:, cols[0] // blk:cols[1] // blk], cols[1] - cols[0]
+        return ("w4", fmt, np.ascontiguousarray(packed), np.ascontiguousarray(scales), ts, k)
+
+    def lin_w4(parts) -> LinearWeight:
+        from ..formats import codecs
+        from ..ops.w4 import W4Weight
+        fmt, k = parts[0][1], parts[0][5]
+        scales_equal = all(p[4] == parts[0][4] for p in parts)
+        if scales_equal:          # one tensor scale (or none): the file bytes are used as they are
+            packed = np.concatenate([p[2] for p in parts], axis=0)
+            sc = np.concatenate([p[3] for p in parts], axis=0)
+            return LinearWeight("w4", None, None, W4Weight.from_file_layout(fmt, packed, sc, k, parts[0][4], device))
+        # q | k | v (or gate | up) quantised with different NVFP4 tensor scales share one matrix here: the values are
+        # exact in fp32, so the fused matrix is re-quantised once with a common tensor scale
+        full = np.concatenate([codecs.dequantize_nvfp4(p[2], p[3], p[4], k) for p in parts], axis=0)
+        wt = torch.from_numpy(full)
+        if device.type == "cuda":
+            return LinearWeight("w4", None, None, W4Weight.quantize_device(fmt, wt.to(device)))
+        return LinearWeight("w4", None, None, W4Weight.quantize(fmt, wt, device))
+
     def lin(parts) -> LinearWeight:
+        if isinstance(parts[0], tuple) and len(parts[0]) == 6 and parts[0][0] == "w4":
+            return lin_w4(parts)
         vals = torch.cat([p[0] for p in parts], dim=0).contiguous()
         if parts[0][1] is None:
             return LinearWeight("dense", vals)

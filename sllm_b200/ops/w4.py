@@ -168,6 +168,22 @@ class W4Weight:
         out = vals * np.repeat(s, self.block, axis=1)
         return torch.from_numpy(out[:self.n, :self.k].astype(np.float32))
 
+    def to_file_layout(self, group: int = 0):
+        """(packed [n, k / 2] adjacent-pair nibbles, scales [n, k / block]) of one group: the inverse of
+        ``from_file_layout`` (exact), used when a resident weight is written back to a model file."""
+        rt, kc = self.n_rows // 128, self.k_pad // 128
+        t = self.tiles.cpu().numpy()[group]
+        pk = np.ascontiguousarray(t[:, :, :8192].reshape(rt, kc, 128, 64).transpose(0, 2, 1, 3)).reshape(self.n_rows, self.k_pad // 2)
+        words = pk.view(np.uint32).reshape(self.n_rows, self.k_pad // 8)
+        order = [0, 2, 4, 6, 1, 3, 5, 7]
+        codes = np.zeros((self.n_rows, self.k_pad // 8, 8), dtype=np.uint8)
+        for pos in range(8):
+            codes[..., order[pos]] = (words >> (4 * pos)) & 0xF
+        codes = codes.reshape(self.n_rows, self.k_pad)[:self.n, :self.k]
+        sb = 128 // self.block
+        sc = t[:, :, 8192:].reshape(rt, kc, 128, sb).transpose(0, 2, 1, 3).reshape(self.n_rows, self.k_pad // self.block)
+        return codecs.pack_nibbles(codes), np.ascontiguousarray(sc[:self.n, :(self.k + self.block - 1) // self.block])
+
     def nbytes(self) -> int:
         return self.tiles.numel()
 

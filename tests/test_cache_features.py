@@ -204,3 +204,36 @@ def test_paged_kv_offset_matches_tensor_layout():
         off = paged_kv_offset(page_list, tok, head, ch, page, hkv, hd, elem_bytes=1)
         want = plane[page_list[tok // page], head, tok % page, ch].data_ptr() - plane.data_ptr()
         assert off * plane.element_size() == want
+
+
+def test_rollback_into_a_shared_page_copies_the_tail_before_the_next_append():
+    """A fork at a page boundary shares whole pages by reference count; rolling the child back into such a page and
+    appending again must leave the parent's page bytes and reference counts untouched (copy-on-write of the tail)."""
+    cfg = MC.tiny_llama()
+    eng = build_engine(cfg, "cpu", seed=0, max_batch=4, use_cuda_graphs=False)
+    page = cfg.page_size
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (2 * page + 1,), generator=g).tolist()
+    parent = eng.new_sequence(prompt)
+    eng.prefill([parent])                                   # 2 * page + 1 tokens computed
+    child = eng.fork_sequence(parent, prompt[:2 * page] + [7])      # shares the two full pages
+    assert child.num_computed == 2 * page
+    pool = eng.cache.pool
+    shared = pool.pages(parent.seq_id)[1]
+    assert pool.pages(child.seq_id)[1] == shared and pool.refcount(shared) == 2
+    before = eng.cache.values[:, :, shared].clone()
+    eng.rollback(child, 2 * page - 4)                       # the child's tail now lies inside the shared page
+    assert pool.refcount(shared) == 1                       # the child got a private copy
+    private = pool.pages(child.seq_id)[1]
+    assert private != shared
+    assert torch.equal(eng.cache.values[:, :, private], before)
+    child.tokens += [3, 9, 11, 2]
+    eng.prefill([child])                                    # appends into the private page
+    assert torch.equal(eng.cache.values[:, :, shared], before)
+    assert not torch.equal(eng.cache.values[:, :, private], before)
+    # the parent still decodes as if nothing happened
+    ref = build_engine(cfg, "cpu", seed=0, max_batch=4, use_cuda_graphs=False)
+    rs = ref.new_sequence(prompt)
+    first = ref.prefill([rs])
+    parent.tokens.append(first[0]); rs.tokens.append(first[0])
+    assert eng.decode([parent]) == ref.decode([rs])

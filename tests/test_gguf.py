@@ -220,3 +220,51 @@ def test_llama_export_load_roundtrip(tmp_path, wf):
         assert ws.vocab_offset == wr.vocab_offset and ws.lm_head.w.shape == wr.lm_head.w.shape
     assert type(loader.tokenizer_from_gguf(g)).__name__ == "ByteTokenizer"
     g.close()
+
+
+@pytest.mark.parametrize("wf", ["mxfp4", "nvfp4"])
+def test_llama_4bit_export_load_roundtrip(tmp_path, wf):
+    """4-bit weights travel as standard GGML blocks (types 39 / 40) and come back bit-identical in the resident layout."""
+    cfg = MC.tiny_llama()
+    cfg.weight_format, cfg.kv_format, cfg.ffn = wf, "bf16", 512
+    w = init_random_weights(cfg, "cpu", seed=4)
+    p = str(tmp_path / "tiny4.gguf")
+    lock = loader.export_llama_gguf(cfg, w, p)
+    g = G.verify_gguf(p, lock)
+    want_type = G.T_MXFP4 if wf == "mxfp4" else G.T_NVFP4
+    assert g.tensors["blk.0.attn_q.weight"].ttype == want_type
+    enc = {b["logical_tensor"]: b for b in g.recipe()["bindings"]}["blk.0.ffn_down.weight"]
+    assert enc["encoding"] == (loader.MXFP4_ENCODING if wf == "mxfp4" else loader.NVFP4_ENCODING)
+    cfg2, w2 = loader.load_llama_gguf(g, "cpu")
+    assert cfg2 == cfg
+    for a, b in zip(w.layers, w2.layers):
+        for n in ("qkv", "o", "gate_up", "down"):
+            la, lb = getattr(a, n), getattr(b, n)
+            assert lb.kind == "w4" and torch.equal(la.w4.tiles, lb.w4.tiles)
+            if wf == "nvfp4":
+                assert torch.equal(la.w4.tensor_scale, lb.w4.tensor_scale)
+    # a tensor-parallel shard decodes to the same values as the matching slice of the full matrix
+    _, ws = loader.load_llama_gguf(g, "cpu", tp_size=2, tp_rank=1)
+    full = w.layers[0].down.w4.dequantized(0)
+    assert torch.equal(ws.layers[0].down.w4.dequantized(0), full[:, full.shape[1] // 2:])
+    g.close()
+
+
+def test_fp8_channel_scale_weights_load_as_block_scaled(tmp_path):
+    """One scale per output row is the 1x128 form with the scale repeated along K: the loader accepts it exactly."""
+    from sllm_b200.formats import codecs
+    cfg = MC.tiny_llama()
+    cfg.weight_format, cfg.kv_format, cfg.ffn = "fp8", "fp8", 512
+    w = init_random_weights(cfg, "cpu", seed=6)
+    p = str(tmp_path / "chan.gguf")
+    lock = loader.export_llama_gguf(cfg, w, p, fp8_channel_scales=True)
+    g = G.verify_gguf(p, lock)
+    b = {x["logical_tensor"]: x for x in g.recipe()["bindings"]}["blk.1.attn_output.weight"]
+    assert b["encoding"] == "fp8-e4m3fn-channel-f32-scale"
+    _, w2 = loader.load_llama_gguf(g, "cpu")
+    lw = w2.layers[1].o
+    codes, sc = codecs.quantize_fp8_outer_rows(w.layers[1].o.dequantized().numpy())
+    assert lw.kind == "fp8" and np.array_equal(lw.w.numpy(), codes)
+    assert lw.scale_t.shape == (cfg.q_size // 128, cfg.d_model)
+    np.testing.assert_array_equal(lw.dequantized().numpy(), codecs.dequantize_fp8_outer_rows(codes, sc))
+    g.close()

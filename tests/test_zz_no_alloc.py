@@ -45,8 +45,14 @@ def test_noalloc_argmax_matches_regular_entry_point_twice():
         both = ~torch.isnan(want_val)
         assert torch.equal(out_val[both], want_val[both])
         assert out_idx[1].item() == 17 + 1000 * call
+        # and, independently of this library's own kernel: rows without a tie or a NaN agree with torch.argmax
+        plain = [r for r in range(rows) if r not in (1, 2)]
+        assert torch.equal(out_idx[plain].long() - 1000 * call, logits[plain].float().argmax(dim=-1))
     too_many = lib.sllm_argmax_noalloc_max_rows() + 1
     big = torch.zeros(too_many, 16, device=dev, dtype=torch.bfloat16)
     out = torch.zeros(too_many, dtype=torch.int32, device=dev)
     rc = lib.sllm_argmax_noalloc(big.data_ptr(), out.data_ptr(), None, too_many, 16, 16, 0, None)
     assert rc == 7      # limit exceeded, nothing launched
+    ok_rows = torch.zeros(4, 16, device=dev, dtype=torch.bfloat16)
+    rc = lib.sllm_argmax_noalloc(ok_rows.data_ptr(), out.data_ptr(), None, 4, 16, 8, 0, None)
+    assert rc == 1      # a row stride below the row length would make rows overlap
