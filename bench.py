@@ -69,7 +69,7 @@ class ClockSampler:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=f, stderr=subprocess.DEVNULL)
+                                          "-lms", "20", "-i", str(self.gpu)], stdout=f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -446,6 +446,8 @@ def main():
             "higher_is_better": True,
             "scaling": "strong",
             "vs_baseline": round(value / REFERENCE_PUBLISHED_TOK_S, 2),
+            "vs_baseline_denominator": "56.62 tok/s: the reference's published FP8 decode rate (Qwen3.5-4B, one request, "
+                                       "MI300X); another model, batch and GPU, so context rather than a like-for-like ratio",
             "dtype": ("fp8_e4m3_block128_weights+fp8_kv (bf16 activations, fp32 accumulate)" if args.weights == "fp8" else
                       f"{args.weights} weights ({cfg.expert_format} experts) + {args.kv} kv, bf16 activations, fp32 accumulate"
                       if cfg.family == "moe" else f"{args.weights} weights + {args.kv} kv, bf16 activations, fp32 accumulate"),
@@ -465,6 +467,7 @@ def main():
             "ttft_ms_batch_prefill": round(main_res["prefill_ms"], 2),
             "itl_ms": round(main_res["e2e_ms"] / k, 4),
             "device_status": main_res["status"],
+            "fallbacks": _lib.fallbacks(),
             "impl": "own",
         }
         if extra:

@@ -206,6 +206,24 @@ class PagedKVCache:
             out["scales"] = self.scales[:, :, pages].cpu()
         return out
 
+    def export_token_major(self, seqs: list, max_tokens: int) -> torch.Tensor:
+        """Value planes of ``seqs`` in the reference's dense token-major order
+        ``[layers, 2 (K, V), batch, blocks, block_size, kv_heads, head_dim]`` (docs/architecture/kv-memory.md of the
+        reference; offsets as in its layout oracle tests/reference/oracles.py:209-239), blocks = ceil(max_tokens /
+        page).  The resident pages are head-major (one head's 16 tokens contiguous); this is the interchange view for
+        tools that expect the reference's order.  Tokens beyond a sequence's length read as zero."""
+        page = self.pool.page_size
+        blocks = (max_tokens + page - 1) // page
+        L, two, _, hkv, _, hd = self.values.shape
+        out = torch.zeros((L, two, len(seqs), blocks, page, hkv, hd), dtype=self.values.dtype, device=self.values.device)
+        for bi, seq in enumerate(seqs):
+            pages = self.pool.pages(seq)[:blocks]
+            if pages:
+                idx = torch.tensor(pages, dtype=torch.long, device=self.device)
+                # [L, 2, n, hkv, page, hd] -> [L, 2, n, page, hkv, hd]
+                out[:, :, bi, :len(pages)] = self.values[:, :, idx].permute(0, 1, 2, 4, 3, 5)
+        return out
+
     def import_pages(self, image: dict) -> int:
         seq = self.pool.new_seq()
         n = int(image["length"])

@@ -7,8 +7,10 @@
 // exchange the 64-byte handles at start-up.  The reference has no multi-GPU path at all
 // (docs/architecture/runtime.md:547-555); this file has no counterpart there.
 //
-// Rules kept here: plain ld/st/red to peer addresses only (no TMA from peer memory, no cluster
-// multicast); every wait on a peer flag is bounded and reports through the status word.
+// Rules kept here: plain ld/st/red to peer addresses only and no cluster multicast anywhere; the one place
+// that reads peer memory with TMA is the all-gather GEMM (gemm_tcgen05.cu), through plain, non-multicast tiled
+// loads whose tensor maps are built per peer buffer.  Every wait on a peer flag is bounded and reports through
+// the status word.
 #include "common.cuh"
 #include "api.h"
 #include <cstring>

@@ -1280,3 +1280,18 @@ SLLM_EXPORT int sllm_gemm_fused(const SllmFdPhase* ph, const SllmFdRope* rope, i
                    ws_floats, counters, n_counters, status, stream,
                    ph->epilogue == SLLM_FD_RESID_QUANT ? static_cast<const SllmCommDesc*>(comm) : nullptr, nullptr, &fe);
 }
+
+// sizeof / offsetof records of the two descriptor structs that foreign-language bindings mirror by hand
+// (SllmCommDesc: size, recv, flags, epoch; SllmGatherDesc: size, maps, flags, epoch): writes up to n ints and returns
+// how many there are.  A binding compares them with its own layout before it passes a descriptor.
+SLLM_EXPORT int sllm_comm_abi(int* out, int n) {
+  const int rec[] = {
+      static_cast<int>(sizeof(SllmCommDesc)), static_cast<int>(offsetof(SllmCommDesc, recv)),
+      static_cast<int>(offsetof(SllmCommDesc, flags)), static_cast<int>(offsetof(SllmCommDesc, epoch)),
+      static_cast<int>(sizeof(SllmGatherDesc)), static_cast<int>(offsetof(SllmGatherDesc, maps)),
+      static_cast<int>(offsetof(SllmGatherDesc, flags)), static_cast<int>(offsetof(SllmGatherDesc, epoch)),
+  };
+  const int have = static_cast<int>(sizeof(rec) / sizeof(rec[0]));
+  for (int i = 0; i < n && i < have; ++i) out[i] = rec[i];
+  return have;
+}

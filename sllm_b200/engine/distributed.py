@@ -7,6 +7,12 @@ own shard inside `follow()`.  All ranks therefore issue the same kernels and col
 is what the fused peer-memory kernels and NCCL both require.  Commands travel over a gloo group (host side), so
 the device streams stay free of control traffic.  (The reference has no multi-GPU path; this is the glue that lets
 its single-process server design drive N GPUs.)
+
+Failure detection stays on the host.  A follower whose replay raises posts the error under its rank in the
+rendezvous store and leaves; the leader looks at those keys before every command and raises ``FollowerFailed``
+instead of launching work that would wait for a dead rank.  A follower whose command channel fails (the leader
+exited or stopped answering within the control group's timeout) raises ``LeaderLost`` and leaves.  Ranks only
+leave between steps, with none of their kernels or collectives in flight.
 """
 from __future__ import annotations
 
@@ -19,18 +25,56 @@ import torch.distributed as dist
 from .engine import Engine, Sequence
 
 _STOP = "__stop__"
+_FAIL_KEY = "sllm/follower_failed/"
+
+
+class FollowerFailed(RuntimeError):
+    """A follower rank reported an error; the engine group must be torn down."""
+
+
+class LeaderLost(RuntimeError):
+    """The command channel to the leader failed."""
+
+
+def _store():
+    try:
+        return dist.distributed_c10d._get_default_store()
+    except Exception:
+        return None
 
 
 class _Channel:
     def __init__(self, group=None, src: int = 0):
         self.group, self.src = group, src
+        self.store = _store()
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    def check_followers(self) -> None:
+        if self.store is None:
+            return
+        for r in range(self.world):
+            if r != self.src and self.store.check([_FAIL_KEY + str(r)]):
+                raise FollowerFailed(f"rank {r}: {self.store.get(_FAIL_KEY + str(r)).decode('utf-8', 'replace')}")
+
+    def report_failure(self, exc: BaseException) -> None:
+        if self.store is not None:
+            self.store.set(_FAIL_KEY + str(self.rank), f"{type(exc).__name__}: {exc}"[:500])
 
     def send(self, obj) -> None:
-        dist.broadcast_object_list([obj], src=self.src, group=self.group)
+        self.check_followers()
+        try:
+            dist.broadcast_object_list([obj], src=self.src, group=self.group)
+        except RuntimeError as exc:        # a follower left without reporting, or the channel timed out
+            self.check_followers()
+            raise FollowerFailed(f"command channel failed: {exc}") from None
 
     def recv(self):
         box = [None]
-        dist.broadcast_object_list(box, src=self.src, group=self.group)
+        try:
+            dist.broadcast_object_list(box, src=self.src, group=self.group)
+        except RuntimeError as exc:
+            raise LeaderLost(f"command channel failed: {exc}") from None
         return box[0]
 
 
@@ -122,44 +166,54 @@ def follow(engine: Engine, control_group=None) -> int:
         n += 1
         if op == _STOP:
             return n
-        if op == "new":
-            seqs[cmd[1]] = engine.new_sequence(cmd[2])
-        elif op == "fork":
-            seqs[cmd[1]] = engine.fork_sequence(seqs[cmd[2]], cmd[3])
-        elif op == "fork_pool":
-            src = Sequence(prompt=list(cmd[3]))
-            src.seq_id, src.num_computed = cmd[2], len(cmd[3])
-            seqs[cmd[1]] = engine.fork_sequence(src, cmd[4])
-        elif op == "free":
-            s = seqs.pop(cmd[1], None)
-            if s is not None:
-                engine.free_sequence(s)
-        elif op == "rollback":
-            engine.rollback(seqs[cmd[1]], cmd[2])
-        elif op == "kvfork":
-            engine.fork_kv(seqs[cmd[1]], cmd[2])          # pool ids advance identically on every rank
-        elif op == "kvfree":
-            engine.free_kv(cmd[1])
-        elif op in ("prefill", "extend"):
-            batch = []
-            for h, new_tokens in cmd[1]:
-                s = seqs[h]
-                del s.tokens[s.num_computed:]
-                s.tokens.extend(new_tokens)
-                batch.append(s)
-            if op == "prefill":
-                engine.prefill(batch, cmd[2], cmd[3], one_chunk=cmd[4])
-            else:
-                engine.extend(batch, cmd[2])
-        elif op == "decode":
-            batch = []
-            for h, last in cmd[1]:
-                s = seqs[h]
-                if len(s.tokens) == s.num_computed:
-                    s.tokens.append(last)
-                else:
-                    s.tokens[-1] = last
-                batch.append(s)
-            engine.decode(batch, cmd[2])
+        try:
+            _replay(engine, seqs, cmd)
+        except BaseException as exc:       # tell the leader on the host, then leave between steps
+            ch.report_failure(exc)
+            raise
+
+
+def _replay(engine: Engine, seqs: dict, cmd) -> None:
+    """Applies one mirrored command to this rank's engine."""
+    op = cmd[0]
+    if op == "new":
+        seqs[cmd[1]] = engine.new_sequence(cmd[2])
+    elif op == "fork":
+        seqs[cmd[1]] = engine.fork_sequence(seqs[cmd[2]], cmd[3])
+    elif op == "fork_pool":
+        src = Sequence(prompt=list(cmd[3]))
+        src.seq_id, src.num_computed = cmd[2], len(cmd[3])
+        seqs[cmd[1]] = engine.fork_sequence(src, cmd[4])
+    elif op == "free":
+        s = seqs.pop(cmd[1], None)
+        if s is not None:
+            engine.free_sequence(s)
+    elif op == "rollback":
+        engine.rollback(seqs[cmd[1]], cmd[2])
+    elif op == "kvfork":
+        engine.fork_kv(seqs[cmd[1]], cmd[2])          # pool ids advance identically on every rank
+    elif op == "kvfree":
+        engine.free_kv(cmd[1])
+    elif op in ("prefill", "extend"):
+        batch = []
+        for h, new_tokens in cmd[1]:
+            s = seqs[h]
+            del s.tokens[s.num_computed:]
+            s.tokens.extend(new_tokens)
+            batch.append(s)
+        if op == "prefill":
+            engine.prefill(batch, cmd[2], cmd[3], one_chunk=cmd[4])
         else:
-            raise RuntimeError(f"unknown engine command {op!r}")
+            engine.extend(batch, cmd[2])
+    elif op == "decode":
+        batch = []
+        for h, last in cmd[1]:
+            s = seqs[h]
+            if len(s.tokens) == s.num_computed:
+                s.tokens.append(last)
+            else:
+                s.tokens[-1] = last
+            batch.append(s)
+        engine.decode(batch, cmd[2])
+    else:
+        raise RuntimeError(f"unknown engine command {op!r}")

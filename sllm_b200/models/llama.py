@@ -171,7 +171,6 @@ class LlamaModel:
         self.adapters = None      # models.adapters.AdapterSet applied to every forward while set
         self._fused: dict = {}    # row count -> FusedLlamaDecoder (decode steps of up to 32 rows)
         self._fused_reason = None
-        self.fallbacks = 0        # forwards of a fused-eligible model that took the per-op path
 
     def _fused_decoder(self, b: ForwardBatch):
         """The fused decode chain for this batch, or None when the batch or the model is not covered (prefill rows,
@@ -179,12 +178,15 @@ class LlamaModel:
         if not b.tokens.is_cuda or b.logit_rows is not None or b.embeds is not None or b.rope_pos3 is not None:
             return None
         rows = b.num_tokens
-        if rows > 32 or (self.adapters is not None and (self.adapters.loras or self.adapters.cvs)):
-            return None
         if self._fused_reason is None:
             from . import fused_llama
             self._fused_reason = fused_llama.eligible(self) or ""
         if self._fused_reason:
+            return None
+        if rows > 32 or (self.adapters is not None and (self.adapters.loras or self.adapters.cvs)):
+            # a decode-shaped batch of a model that has the fused chain, on the per-op path
+            from ..ops import _lib
+            _lib.note_fallback("decode_per_op:rows_above_32" if rows > 32 else "decode_per_op:adapters")
             return None
         dec = self._fused.get(rows)
         if dec is None:

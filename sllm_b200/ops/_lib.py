@@ -40,6 +40,18 @@ class KernelError(RuntimeError):
 
 LAUNCH_COUNT = [0]  # kernels launched through this library (graph capture counts once per capture)
 
+# Work that left its intended fast path, by reason (reported by /props and the benchmark line; the reference's
+# dispatch records carry the same information as `fallback_used`, include/sllm/hip.h:651-671).
+FALLBACKS: dict = {}
+
+
+def note_fallback(reason: str) -> None:
+    FALLBACKS[reason] = FALLBACKS.get(reason, 0) + 1
+
+
+def fallbacks() -> dict:
+    return dict(FALLBACKS)
+
 
 def check(rc: int, what: str) -> None:
     if rc != 0:

@@ -58,6 +58,8 @@ class GatherGemm(NcclGatherGemm):
     def __init__(self, size: int, rank: int, device, max_rows: int, k: int, group=None):
         super().__init__(size, rank, device, group)
         from .symm import SymmetricRegion
+        from .tp import check_comm_abi
+        check_comm_abi()
         if k % (64 * size):
             raise ValueError("k must be a multiple of 64 * world (whole 128-byte K blocks per rank)")
         self.max_rows = (max_rows + 127) // 128 * 128 if max_rows > 64 else (16 if max_rows <= 16 else 32 if max_rows <= 32 else 64)

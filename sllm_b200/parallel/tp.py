@@ -30,6 +30,26 @@ class CommDesc(C.Structure):
                 ("reserved", C.c_int), ("recv", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("epoch", C.c_void_p)]
 
 
+_abi_ok = False
+
+
+def check_comm_abi() -> None:
+    """Compares the ctypes mirrors of the communicator descriptors with the layout the library was compiled with
+    (a silent field-order drift would hand peer pointers to the wrong slots)."""
+    global _abi_ok
+    if _abi_ok:
+        return
+    from .gather import GatherDesc
+    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_comm_abi", (C.c_int, [C.POINTER(C.c_int), C.c_int]))
+    buf = (C.c_int * 16)()
+    n = _lib.kernels().sllm_comm_abi(buf, 16)
+    mine = [C.sizeof(CommDesc), CommDesc.recv.offset, CommDesc.flags.offset, CommDesc.epoch.offset,
+            C.sizeof(GatherDesc), GatherDesc.maps.offset, GatherDesc.flags.offset, GatherDesc.epoch.offset]
+    if n != len(mine) or list(buf[:n]) != mine:
+        raise _lib.KernelError(f"communicator descriptor layout mismatch: library {list(buf[:n])}, bindings {mine}")
+    _abi_ok = True
+
+
 class NcclTP:
     """Unfused baseline: library collectives between kernels."""
     impl = "nccl"
@@ -84,6 +104,7 @@ class FusedTP(NcclTP):
     def __init__(self, size: int, rank: int, device, max_tokens: int, d_model: int, group=None,
                  max_rows_small: int = 1024):
         super().__init__(size, rank, device, group)
+        check_comm_abi()
         from .symm import SymmetricRegion
         self.max_tokens = max_tokens
         self._d_model = d_model
@@ -161,11 +182,14 @@ class FusedTP(NcclTP):
         xd = x.data if isinstance(x, QTensor) else x
         m, n = xd.shape[0], w.out_features
         if not xd.is_cuda or m > self.max_tokens:
+            if xd.is_cuda:
+                _lib.note_fallback("tp_row_linear_nccl:rows_above_fused_limit")
             return super().row_linear(x, w, residual)
         if w.kind == "w4":
             # 4-bit weights: W4A16 GEMM, then the fused peer-memory reduction
             part = ops.linear(x, w)
             if n != self._d_model:
+                _lib.note_fallback("tp_row_linear_nccl:w4_width")
                 return super().row_linear(x, w, residual)
             return self._reduce_rows(part, residual)
         lib = _lib.kernels()

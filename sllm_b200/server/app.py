@@ -97,6 +97,12 @@ def _split_utf8(text: str, limit: int = MAX_DELTA_BYTES) -> list:
     return out
 
 
+def _fallbacks() -> dict:
+    """Counters of work that left its fast path (fused tensor-parallel GEMM -> NCCL, fused decode -> per-op kernels)."""
+    from ..ops import _lib
+    return _lib.fallbacks()
+
+
 def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, lifecycle: Optional[ServerLifecycle] = None) -> FastAPI:
     cfg = config or ServerConfig()
     life = lifecycle or ServerLifecycle()
@@ -262,7 +268,8 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
                 "scheduler": {a: b.scheduler_stats() for a, b in registry.backends.items()},
                 "features": {"metrics": cfg.metrics, "resumable_sse": cfg.resumable_sse,
                              "compatibility_profile": cfg.compatibility_profile,
-                             "dynamic_models": registry.dynamic is not None, "cors": bool(cfg.cors_origins)}}
+                             "dynamic_models": registry.dynamic is not None, "cors": bool(cfg.cors_origins)},
+                "fallbacks": _fallbacks()}
 
     @app.get("/slots")
     async def slots(request: Request):

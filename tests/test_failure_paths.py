@@ -1,0 +1,108 @@
+"""Failure paths made on the host (CPU) and bounded device waits that give up (GPU), without faulting anything."""
+import ctypes as C
+
+import pytest
+import torch
+
+from sllm_b200.cache.paged import OutOfPages
+from sllm_b200.engine.engine import build_engine
+from sllm_b200.models import config as MC
+
+
+def test_injected_page_allocation_failure_fails_the_request_not_the_engine():
+    """The page pool's fault hook makes one allocation fail: the step raises, the sequence's published state is
+    untouched, and the same request succeeds afterwards with the result of an undisturbed engine."""
+    cfg = MC.tiny_llama()
+    prompt = list(range(3, 40))
+    eng = build_engine(cfg, "cpu", seed=2, num_pages=64, max_batch=4, use_cuda_graphs=False)
+    want = build_engine(cfg, "cpu", seed=2, num_pages=64, max_batch=4, use_cuda_graphs=False).generate([prompt], 5)[0]
+    s = eng.new_sequence(prompt)
+    free_before = eng.cache.pool.stats()["free"]
+    eng.cache.pool.inject_alloc_failure(0)
+    with pytest.raises(OutOfPages):
+        eng.prefill([s])
+    assert s.num_computed == 0 and eng.cache.pool.length(s.seq_id) == 0
+    assert eng.cache.pool.stats()["free"] == free_before          # nothing leaked
+    eng.cache.pool.inject_alloc_failure(-1)                       # the hook fails every allocation until it is cleared
+    got = [eng.prefill([s])[0]]
+    for _ in range(4):
+        s.tokens.append(got[-1])
+        got.append(eng.decode([s])[0])
+    assert got == want
+    # a failure in the middle of decoding: only that step fails
+    s.tokens.append(got[-1])
+    while eng.cache.pool.length(s.seq_id) % cfg.page_size != 0 or len(s.tokens) % cfg.page_size != 1:
+        s.tokens.append(eng.decode([s])[0])                        # run up to a page boundary
+    published = eng.cache.pool.length(s.seq_id)
+    eng.cache.pool.inject_alloc_failure(0)
+    with pytest.raises(OutOfPages):
+        eng.decode([s])
+    assert eng.cache.pool.length(s.seq_id) == published
+    eng.cache.pool.inject_alloc_failure(-1)
+    assert isinstance(eng.decode([s])[0], int)
+
+
+@pytest.mark.gpu
+def test_bounded_peer_wait_gives_up_and_the_context_survives():
+    """A cross-rank sum whose peer flag is never raised: the wait runs out after the limit given to the launch, the kernel
+    records status 105 and returns through its normal teardown, and the next launch on the same context works."""
+    from sllm_b200 import ops
+    from sllm_b200.ops import fused_decode as fd
+    from sllm_b200.ops import reference as ref
+    from sllm_b200.ops.core import LinearWeight
+    from sllm_b200.parallel.tp import CommDesc
+    dev = torch.device("cuda")
+    rows, d, k, bn = 4, 256, 256, 16
+    g = torch.Generator().manual_seed(0)
+    lw = LinearWeight.from_dense((torch.randn(d, k, generator=g) * 0.03).bfloat16(), "fp8").to(dev)
+    xq, xs_t = ref.quant_fp8_1x128((torch.randn(rows, k, generator=g)).bfloat16())
+    xs = torch.zeros((k // 128, bn)); xs[:, :rows] = xs_t
+    xq, xs = xq.to(dev), xs.to(dev)
+    h = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
+    q = torch.zeros((rows, d), dtype=torch.uint8, device=dev)
+    s = torch.zeros((d // 128, bn), dtype=torch.float32, device=dev)
+    ssq = torch.zeros((d // 128, bn), dtype=torch.float32, device=dev)
+    ph = fd.phase(fd.RESID_QUANT, lw.w, lw.scale_t, xq, xs, n=d, k=k, y=h, ldy=d, residual=h, q_out=q, s_out=s, ssq_out=ssq,
+                  ld_s_out=bn)
+    # a two-rank communicator whose "peer" is this GPU's own memory and never answers
+    recv = torch.zeros(2 * 2 * 32 * d, dtype=torch.bfloat16, device=dev)
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    epoch = torch.zeros(16, dtype=torch.int32, device=dev)
+    comm = CommDesc()
+    comm.world, comm.rank, comm.cap_elems, comm.max_tiles = 2, 0, 32 * d, d // 128
+    for r in range(2):
+        comm.recv[r], comm.flags[r] = recv.data_ptr(), flags.data_ptr()
+    comm.epoch = epoch.data_ptr()
+    assert ops.device_status(dev) == 0
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    fd.launch([ph], rows, dev, comm=comm, impl="persistent", wait_limit_cycles=4_000_000)     # ~2 ms
+    t1.record()
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 2000.0                  # it gave up after the limit, not after the library default
+    assert ops.device_status(dev) == 105                 # timeout waiting for a peer flag (reading clears the word)
+    fd.reset_state(dev)
+    y = torch.zeros((rows, d), dtype=torch.bfloat16, device=dev)
+    ok = fd.phase(fd.PLAIN, lw.w, lw.scale_t, xq, xs, n=d, k=k, y=y, ldy=d)
+    fd.launch([ok], rows, dev, impl="persistent")
+    want = fd.ref_plain(lw.w, lw.scale_t, xq, xs, rows)
+    assert ((y.float().cpu() - want).norm() / want.norm()).item() < 6e-3
+    assert ops.device_status(dev) == 0
+
+
+@pytest.mark.gpu
+def test_kernel_trace_tool_output_schema(capsys):
+    """The tracing tool's JSON form is stable: schema id, column names, one row per tile / phase, stamps that increase
+    along a row where taken."""
+    import json
+    from sllm_b200.utils import kernel_trace
+    assert kernel_trace.main(["--op", "fused-decode", "--batch", "8", "--json"]) == 0
+    doc = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert doc["schema"] == "sllm-kernel-trace-v1" and doc["op"] == "fused-decode" and doc["cold_us"] > 0
+    assert len(doc["rows"]) == 4 and all(len(r) == len(doc["columns"]) for r in doc["rows"])
+    col = {n: i for i, n in enumerate(doc["columns"])}
+    for r in doc["rows"]:
+        assert r[col["input_visible.first"]] <= r[col["first_accumulator.first"]] <= r[col["barrier_arrival.last"]]
+    # each phase starts after the previous one's last barrier arrival
+    for a, b in zip(doc["rows"], doc["rows"][1:]):
+        assert b[col["input_visible.first"]] >= a[col["barrier_arrival.last"]]

@@ -16,19 +16,40 @@ class FixedUniform:
         return self.u
 
 
-# Golden cases of the profile sampler (same numbers as the reference's
-# tests/fixtures/profile_sampling_cases.json, schema profile-sampling-cases-v1).
-GOLDEN = [
-    ([0.0, 1.0, -1.0, 0.5, 2.0, 0.25, -0.25], 0.7, 0.9, 0.0, 0.0, [], 0.5, 4),
-    ([0.0, 2.5, 1.0], 1.0, 1.0, 1.0, 1.0, [1, 1], 0.1, 2),
-    ([2.0, 2.0, 1.0], 1.0, 0.0, 0.0, 0.0, [], 0.9, 0),
-    ([-3.0, 0.0, 3.0, 1.0, -1.0], 2.0, 1.0, 0.0, 0.0, [], 0.73, 3),
-]
+def _restated_profile_sampler(logits, t, top_p, pp, fp, hist, u):
+    """Independent restatement: penalties on seen ids, temperature, stable order, smallest top-p prefix, inverse CDF."""
+    lg = np.asarray(logits, dtype=np.float64).copy()
+    for tok in set(hist):
+        lg[tok] -= pp + fp * hist.count(tok)
+    lg = lg / t
+    p = np.exp(lg - lg.max())
+    p /= p.sum()
+    order = sorted(range(len(p)), key=lambda i: (-p[i], i))
+    cum, keep = 0.0, []
+    for i in order:
+        keep.append(i)
+        cum += p[i]
+        if cum >= top_p:
+            break
+    mass = sum(p[i] for i in keep)
+    acc = 0.0
+    for i in keep:
+        acc += p[i]
+        if u * mass < acc:
+            return i
+    return keep[-1]
 
 
-@pytest.mark.parametrize("logits,t,top_p,pp,fp,hist,u,want", GOLDEN)
-def test_profile_sampler_golden(logits, t, top_p, pp, fp, hist, u, want):
+@pytest.mark.parametrize("logits,t,top_p,pp,fp,hist,u", [
+    ([0.2, 1.4, -0.7, 0.9, 1.4], 0.8, 0.85, 0.0, 0.0, [], 0.41),
+    ([1.0, 3.0, 2.0, 0.5], 1.3, 1.0, 0.6, 0.4, [1, 1, 2], 0.07),
+    ([0.5, 0.5, 0.5], 1.0, 0.01, 0.0, 0.0, [], 0.99),
+    ([-2.0, 4.0, 1.5, 1.5, 0.0, 3.5], 1.9, 0.95, -0.5, 0.2, [5, 5], 0.66),
+])
+def test_profile_sampler_matches_restatement(logits, t, top_p, pp, fp, hist, u):
+    """(The reference's own golden cases are read from its fixture file in test_reference_fixtures.py.)"""
     s = S.ProfileSampler(S.SamplingParams(t, top_p, pp, fp), hist)
+    want = _restated_profile_sampler(logits, t, top_p, pp, fp, hist, u)
     assert s.select(0, np.array(logits, dtype=np.float32), FixedUniform(u)) == want
 
 
