@@ -49,6 +49,12 @@ int sllm_rope_kv_append_mrope(void* qkv, const int* positions, const int* seq_in
                               int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8, float theta,
                               float k_static_scale, float v_static_scale, const float* inv_freq,
                               const int* rope_pos3, int sec_t, int sec_h, void* stream);
+/* pair_offset > 0: channel i < rotary_dim / 2 pairs with i + pair_offset and frequencies are theta^(-2 i / hd). */
+int sllm_rope_kv_append_paired(void* qkv, const int* positions, const int* seq_index, const int* block_table,
+                               int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale, int tokens,
+                               int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8, float theta,
+                               float k_static_scale, float v_static_scale, const float* inv_freq, int pair_offset,
+                               void* stream);
 int sllm_elementwise(const void* a, const void* b, void* y, long long n, int d, int op, float s, void* stream);
 int sllm_argmax(const void* logits, int* out_idx, float* out_val, int rows, int n, int ld, int index_offset,
                 void* ws, long long ws_bytes, int* counters, int n_counters, void* stream);

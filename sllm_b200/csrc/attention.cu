@@ -271,7 +271,7 @@ SLLM_EXPORT int sllm_paged_attention(const void* q, int q_ld, const void* k_page
   if (kv_fp8 && !k_scale && !(k_static_scale > 0.f && v_static_scale > 0.f)) return SLLM_ERR_INVALID_ARGUMENT;
   if (splits < 1 || splits > 65535 || hkv > 65535) return SLLM_ERR_INVALID_ARGUMENT;
   const int g = hq / hkv;
-  PagedAttnParams p;
+  PagedAttnParams p = {};
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_ld = q_ld;
   p.k_pages = k_pages; p.v_pages = v_pages; p.k_scale = k_scale; p.v_scale = v_scale;
   p.k_static_scale = k_static_scale; p.v_static_scale = v_static_scale;

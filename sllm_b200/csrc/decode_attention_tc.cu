@@ -95,7 +95,6 @@ template <int G>
 __global__ void __launch_bounds__(kDaThreads, 2)
 decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            const PagedAttnParams p) {
-  pdl_wait();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // layout: stages x {K tile, V tile} | Q (16 x 128 B) | 2 x P^T (16 x 128 B) | barriers | tail scratch
@@ -154,6 +153,9 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // Everything above reads only launch inputs no kernel writes (row -> sequence map, lengths); q and the newest
+  // K / V slots come from the kernel before this one.
+  pdl_wait();
   // Dependents may start once this CTA holds its tensor memory: the next GEMM then requests its first weight
   // tiles while this grid drains.
   if (p.early_trigger) pdl_trigger();
@@ -547,7 +549,7 @@ SLLM_EXPORT int sllm_decode_attention_tc(const void* q, int q_ld, const void* k_
   if (k_scale && ((reinterpret_cast<uintptr_t>(k_scale) | reinterpret_cast<uintptr_t>(v_scale)) & 15)) return SLLM_ERR_ALIGNMENT;
   if (k_scale && !v_scale) return SLLM_ERR_INVALID_ARGUMENT;
   const int g = hq / hkv;
-  PagedAttnParams p;
+  PagedAttnParams p = {};
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_ld = q_ld;
   p.k_pages = k_pages; p.v_pages = v_pages; p.k_scale = k_scale; p.v_scale = v_scale;
   p.k_static_scale = k_static_scale; p.v_static_scale = v_static_scale;

@@ -136,9 +136,6 @@ __device__ __forceinline__ void fd_tma_prefetch_l2(const CUtensorMap* m, int x, 
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
                : "memory");
 }
-__device__ __forceinline__ void fd_prefetch_l2(const void* gsrc, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
-}
 // 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread, no wait.
 __device__ __forceinline__ void fd_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -491,7 +488,7 @@ fused_decode_kernel(const __grid_constant__ FdMaps maps, const __grid_constant__
         fd_tma_prefetch_l2(&maps.a[f_pi], fk * 128, frow);
         int fs = fp.dual_off + fp.n - frow;      // the row scales the epilogue will read from L2
         if (fs > 128) fs = 128;
-        fd_prefetch_l2(fp.w_scale + static_cast<size_t>(fk) * fp.ld_sa + frow, fs * 4);
+        prefetch_l2_bulk(fp.w_scale + static_cast<size_t>(fk) * fp.ld_sa + frow, fs * 4);
         if (f_half < fg.dual) ++f_half; else { f_half = 0; ++f_u; }
       };
       for (int i = 0; i < p.lookahead; ++i) prefetch_next();

@@ -69,7 +69,8 @@ typedef struct SllmFdRope {
   void* v_pages;
   float* k_scale;          /* [pages, hkv, page] (dynamic FP8 only) */
   float* v_scale;
-  const float* inv_freq;   /* [rotary_dim / 2] rotary frequencies theta^(-2 i / rotary_dim) (or a scaled variant) */
+  const float* inv_freq;   /* [rotary_dim / 2] rotary frequencies theta^(-2 i / rotary_dim) (or a scaled variant);
+                              read in the kernel preamble: written before the launch is enqueued, by no kernel */
 } SllmFdRope;
 
 typedef struct SllmFdDesc {

@@ -225,6 +225,10 @@ struct RopeKvParams {
   // Null: every pair turns with positions[t].  The page slot always comes from positions[t].
   const int* rope_pos3;
   int tokens, sec_t, sec_h;
+  // 0: channel i pairs with i + rotary_dim / 2, frequencies theta^(-2 i / rotary_dim).  > 0 ("proportional" layout of
+  // partially rotated wide heads): channel i < rotary_dim / 2 pairs with i + pair_offset (= head_dim / 2) and the
+  // frequencies are theta^(-2 i / head_dim); the channels between stay as they are.
+  int pair_offset;
 };
 
 __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams p) {
@@ -241,14 +245,16 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
   const bool is_v = h >= p.hq + p.hkv;
   const bool is_q = h < p.hq;
   const int half = p.rotary_dim >> 1;
+  const int poff = p.pair_offset > 0 ? p.pair_offset : half;      // distance between the two channels of a pair
+  const int fdim = p.pair_offset > 0 ? hd : p.rotary_dim;         // denominator of the frequency exponent
   for (int i = threadIdx.x; i < hd; i += blockDim.x) vals[i] = __bfloat162float(src[i]);
   __syncthreads();
   float amax = 0.f;
   for (int i = threadIdx.x; i < hd; i += blockDim.x) {
     float o = vals[i];
-    if (!is_v && i < p.rotary_dim) {
-      const int fi = i < half ? i : i - half;
-      const float freq = p.inv_freq ? p.inv_freq[fi] : powf(p.theta, -2.f * fi / p.rotary_dim);
+    if (!is_v && (i < half || (i >= poff && i < poff + half))) {
+      const int fi = i < half ? i : i - poff;
+      const float freq = p.inv_freq ? p.inv_freq[fi] : powf(p.theta, -2.f * fi / fdim);
       int rp = pos;
       if (p.rope_pos3) {
         const int axis = fi < p.sec_t ? 0 : (fi < p.sec_t + p.sec_h ? 1 : 2);
@@ -256,7 +262,7 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
       }
       float sn, cs;
       sincosf(rp * freq, &sn, &cs);
-      const float a = vals[fi], b = vals[fi + half];
+      const float a = vals[fi], b = vals[fi + poff];
       o = i < half ? a * cs - b * sn : b * cs + a * sn;
     }
     o = __bfloat162float(__float2bfloat16_rn(o));
@@ -503,8 +509,10 @@ static int rope_kv_append_impl(void* qkv, const int* positions, const int* seq_i
                                int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale,
                                int tokens, int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8,
                                float theta, float k_static_scale, float v_static_scale, const float* inv_freq,
-                               const int* rope_pos3, int sec_t, int sec_h, void* stream) {
+                               const int* rope_pos3, int sec_t, int sec_h, void* stream, int pair_offset = 0) {
   if (!qkv || !positions || !seq_index || !block_table || !k_pages || !v_pages || tokens <= 0)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  if (pair_offset < 0 || (pair_offset > 0 && (pair_offset < rotary_dim / 2 || pair_offset + rotary_dim / 2 > hd)))
     return SLLM_ERR_INVALID_ARGUMENT;
   if (hd > 512 || (rotary_dim & 1) || rotary_dim > hd || page_size <= 0) return SLLM_ERR_UNSUPPORTED_SHAPE;
   if (kv_fp8 && k_static_scale <= 0.f && (!k_scale || !v_scale)) return SLLM_ERR_INVALID_ARGUMENT;
@@ -515,7 +523,7 @@ static int rope_kv_append_impl(void* qkv, const int* positions, const int* seq_i
   p.k_pages = k_pages; p.v_pages = v_pages; p.k_scale = k_scale; p.v_scale = v_scale;
   p.hq = hq; p.hkv = hkv; p.hd = hd; p.rotary_dim = rotary_dim; p.page_size = page_size; p.kv_fp8 = kv_fp8;
   p.theta = theta; p.k_static_scale = k_static_scale; p.v_static_scale = v_static_scale; p.inv_freq = inv_freq;
-  p.rope_pos3 = rope_pos3; p.tokens = tokens; p.sec_t = sec_t; p.sec_h = sec_h;
+  p.rope_pos3 = rope_pos3; p.tokens = tokens; p.sec_t = sec_t; p.sec_h = sec_h; p.pair_offset = pair_offset;
   dim3 grid(tokens, hq + 2 * hkv);
   launch_kernel(rope_kv_append_kernel, dim3(grid), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u, p);
   return check_launch();
@@ -529,6 +537,18 @@ SLLM_EXPORT int sllm_rope_kv_append(void* qkv, const int* positions, const int* 
   return rope_kv_append_impl(qkv, positions, seq_index, block_table, max_blocks, k_pages, v_pages, k_scale, v_scale,
                              tokens, hq, hkv, hd, rotary_dim, page_size, kv_fp8, theta, k_static_scale, v_static_scale,
                              inv_freq, nullptr, 0, 0, stream);
+}
+
+// The same with the "proportional" pair layout of partially rotated wide heads (see RopeKvParams::pair_offset;
+// reference: SplitHalfRotaryContract, crates/sllm-core/src/op.rs:805-811).
+SLLM_EXPORT int sllm_rope_kv_append_paired(void* qkv, const int* positions, const int* seq_index, const int* block_table,
+                                           int max_blocks, void* k_pages, void* v_pages, float* k_scale, float* v_scale,
+                                           int tokens, int hq, int hkv, int hd, int rotary_dim, int page_size, int kv_fp8,
+                                           float theta, float k_static_scale, float v_static_scale, const float* inv_freq,
+                                           int pair_offset, void* stream) {
+  return rope_kv_append_impl(qkv, positions, seq_index, block_table, max_blocks, k_pages, v_pages, k_scale, v_scale,
+                             tokens, hq, hkv, hd, rotary_dim, page_size, kv_fp8, theta, k_static_scale, v_static_scale,
+                             inv_freq, nullptr, 0, 0, stream, pair_offset);
 }
 
 // The same with 3-axis rotary positions rope_pos3 [3, tokens] (see RopeKvParams).

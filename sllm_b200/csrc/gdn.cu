@@ -130,15 +130,16 @@ gdn_recurrent_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16*
 
 // In place per-head RMSNorm of the q and k heads inside a fused qkv activation (query/key normalisation of
 // the Qwen3 / Gemma families): x [T, ld], heads 0 .. hq + hkv - 1 of width hd each; weight_q / weight_k fp32-exact
-// bf16 [hd]; offset_one: scale = 1 + w.  grid (T, hq + hkv), 128 threads.
+// bf16 [hd] (null: ones); offset_one: scale = 1 + w.  grid (T, heads), 128 threads; head0 = first head to touch;
+// heads from hq + hkv on are value heads and take no weight.
 __global__ void qk_headnorm_kernel(__nv_bfloat16* __restrict__ x, int ld, int hq, int hkv, int hd,
                                    const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk, float eps,
-                                   int offset_one) {
+                                   int offset_one, int head0) {
   pdl_wait();
   pdl_trigger();
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int t = blockIdx.x, h = head0 + blockIdx.y;
   __nv_bfloat16* p = x + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * hd;
-  const __nv_bfloat16* w = h < hq ? wq : wk;
+  const __nv_bfloat16* w = h < hq ? wq : (h < hq + hkv ? wk : nullptr);
   __shared__ float red[4];
   float ss = 0.f;
   for (int i = threadIdx.x; i < hd; i += blockDim.x) {
@@ -151,7 +152,7 @@ __global__ void qk_headnorm_kernel(__nv_bfloat16* __restrict__ x, int ld, int hq
   ss = red[0] + red[1] + red[2] + red[3];
   const float inv = rsqrtf(ss / static_cast<float>(hd) + eps);
   for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-    const float g = __bfloat162float(w[i]) + (offset_one ? 1.f : 0.f);
+    const float g = w ? __bfloat162float(w[i]) + (offset_one ? 1.f : 0.f) : 1.f;
     p[i] = __float2bfloat16_rn(__bfloat162float(p[i]) * inv * g);
   }
 }
@@ -191,6 +192,21 @@ SLLM_EXPORT int sllm_qk_headnorm(void* x, int ld, int tokens, int hq, int hkv, i
   if (!x || !wq || !wk || tokens <= 0 || hq <= 0 || hkv <= 0 || hd <= 0) return SLLM_ERR_INVALID_ARGUMENT;
   cudaError_t e = launch_kernel(qk_headnorm_kernel, dim3(tokens, hq + hkv), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u,
                                 static_cast<__nv_bfloat16*>(x), ld, hq, hkv, hd, static_cast<const __nv_bfloat16*>(wq),
-                                static_cast<const __nv_bfloat16*>(wk), eps, offset_one);
+                                static_cast<const __nv_bfloat16*>(wk), eps, offset_one, 0);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+// The same over a chosen span of heads: skip_qk leaves the q / k heads alone, norm_v adds the value heads (unweighted:
+// reference crates/sllm-core/src/gemma4_graph.rs:740).  Null weights mean ones.
+SLLM_EXPORT int sllm_qkv_headnorm(void* x, int ld, int tokens, int hq, int hkv, int hd, const void* wq, const void* wk,
+                                  float eps, int offset_one, int skip_qk, int norm_v, void* stream) {
+  if (!x || tokens <= 0 || hq <= 0 || hkv <= 0 || hd <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  const int head0 = skip_qk ? hq + hkv : 0;
+  const int heads = (skip_qk ? 0 : hq + hkv) + (norm_v ? hkv : 0);
+  if (heads == 0) return SLLM_OK;
+  // a q / k span followed by the value span is contiguous in head index; a lone value span starts at hq + hkv
+  cudaError_t e = launch_kernel(qk_headnorm_kernel, dim3(tokens, heads), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u,
+                                static_cast<__nv_bfloat16*>(x), ld, hq, hkv, hd, static_cast<const __nv_bfloat16*>(wq),
+                                static_cast<const __nv_bfloat16*>(wk), eps, offset_one, head0);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }

@@ -52,6 +52,14 @@ class ModelConfig:
     gdn_conv_kernel: int = 4
     attn_output_gate: bool = False
     post_norms: bool = False         # Gemma-style norms after attention and after the MLP (before the residual add)
+    # Gemma-4 attention details (reference: crates/sllm-core/src/gemma4_graph.rs:690-915)
+    rope_theta_local: float = 0.0    # rotary base of the sliding-window layers (0: rope_theta)
+    rope_proportional: bool = False  # full-attention layers: channel i < rotary_dim_full / 2 pairs with i + head_dim / 2,
+    rotary_dim_full: Optional[int] = None  # frequencies theta^(-2 i / head_dim); the channels between are not rotated
+    v_norm: bool = False             # unweighted RMS norm of every value head
+    attn_scale: Optional[float] = None     # softmax scale (None: 1 / sqrt(head_dim)); 1.0 where q / k norms set the scale
+    layer_scalar: bool = False       # the residual stream is multiplied by a learned scalar at the end of every layer
+    k_equals_v_full: bool = False    # full-attention layers have no value projection: v = the (un-normed) key projection
     # vision-language models: rotary pairs [0, t) follow the temporal index, [t, t + h) the height index and the rest
     # the width index of a token's 3-axis position (text tokens carry the same value on all three)
     mrope_sections: Optional[list] = None
@@ -67,6 +75,15 @@ class ModelConfig:
         if self.window_layers is None:
             return self.sliding_window
         return self.sliding_window if self.window_layers[layer] else 0
+
+    def layer_rope(self, layer: int) -> tuple:
+        """(theta, rotary_dim, pair_offset) of a layer; pair_offset 0 is the plain split-half layout."""
+        windowed = self.layer_window(layer) > 0
+        if windowed:
+            return (self.rope_theta_local or self.rope_theta), (self.rotary_dim or self.head_dim), 0
+        if self.rope_proportional:
+            return self.rope_theta, (self.rotary_dim_full or self.rotary_dim or self.head_dim), self.head_dim // 2
+        return self.rope_theta, (self.rotary_dim or self.head_dim), 0
 
     @property
     def q_size(self) -> int:
@@ -121,8 +138,13 @@ def qwen35_hybrid_shape(layers: int = 32) -> ModelConfig:
 
 def gemma4_shape(layers: int = 48) -> ModelConfig:
     """Gemma-4-class dense decoder: five 1024-token sliding-window layers per full layer, q/k norm, sandwich norms,
-    gelu-tanh gated MLP, embeddings scaled by sqrt(d), final logit soft-cap 30, tied embeddings."""
-    return ModelConfig(name="gemma4", family="gemma4", n_layers=layers, d_model=3840, n_heads=16, n_kv_heads=8, head_dim=256,
+    gelu-tanh gated MLP, embeddings scaled by sqrt(d), final logit soft-cap 30, tied embeddings; value heads get an
+    unweighted RMS norm, the softmax scale is 1, every layer ends in a learned scalar, sliding layers rotate with base
+    1e4, full layers with base 1e6 in the proportional layout (a quarter of the head) and reuse the key projection as
+    value.  One head geometry (256 wide, 8 kv heads) serves every layer here; the reference's full layers are 512 wide
+    with one kv head (gemma4_graph.rs:754-775)."""
+    return ModelConfig(rope_theta_local=1e4, rope_proportional=True, rotary_dim_full=64, v_norm=True, attn_scale=1.0,
+                       layer_scalar=True, k_equals_v_full=True, name="gemma4", family="gemma4", n_layers=layers, d_model=3840, n_heads=16, n_kv_heads=8, head_dim=256,
                        ffn=15360, vocab=262144, rope_theta=1e6, rms_eps=1e-6, act="gelu_tanh", tie_embeddings=True,
                        embedding_scale=3840 ** 0.5, logit_softcap=30.0, weight_format="bf16", kv_format="bf16",
                        sliding_window=1024, window_layers=[(i + 1) % 6 != 0 for i in range(layers)], qk_norm=True,

@@ -71,6 +71,8 @@ def eligible(model) -> Optional[str]:
         return "weights are not block-scaled FP8"
     if cfg.head_dim != 128 or cfg.qk_norm or cfg.post_norms or cfg.mrope_sections:
         return "head_dim / q-k norm / sandwich norms / multi-axis rotary not covered"
+    if cfg.v_norm or cfg.layer_scalar or cfg.attn_scale is not None or cfg.rope_proportional or cfg.rope_theta_local:
+        return "Gemma-4 attention options not covered"
     if (cfg.rotary_dim or cfg.head_dim) not in (32, 64, 128) or cfg.act not in ("silu", "gelu_tanh"):
         return "rotary width or activation not covered"
     hq, hkv = model.hq, model.hkv
@@ -157,9 +159,9 @@ class FusedLlamaDecoder:
         out = QTensor(self.aq, self.a_s)
         n_layers = len(w.layers)
         for li, lw in enumerate(w.layers):
+            phases = [self._o(lw), self._gate_up(lw), self._down(lw)]
             ops.paged_attention(self.q, cache.layer(li), b.block_table, b.seq_index, b.kv_lens, m.hq, m.hkv,
                                 cfg.head_dim, window=cfg.layer_window(li), max_kv=b.max_kv, quant_out=True, out=out)
-            phases = [self._o(lw), self._gate_up(lw), self._down(lw)]
             rope = None
             if li + 1 < n_layers:
                 ph, rope = self._qkv(w.layers[li + 1], cache.layer(li + 1), b)

@@ -51,6 +51,13 @@ class LayerWeights:
     k_norm: Optional[torch.Tensor] = None
     post_attn_norm: Optional[torch.Tensor] = None     # Gemma-style norms applied to the block output before the add
     post_mlp_norm: Optional[torch.Tensor] = None
+    layer_scalar: Optional[torch.Tensor] = None       # [1]: multiplies the residual stream at the end of the layer
+    _scalar: Optional[float] = None
+
+    def layer_scalar_value(self) -> float:
+        if self._scalar is None:        # read once: the value is a launch argument of the scaling kernel
+            self._scalar = float(self.layer_scalar.float().item())
+        return self._scalar
 
 
 @dataclass
@@ -132,7 +139,10 @@ def init_random_weights(cfg: ModelConfig, device, seed: int = 0, tp_size: int = 
             wo = wo[:, tp_rank * qs:(tp_rank + 1) * qs]
             wg, wu = wg[tp_rank * fs:(tp_rank + 1) * fs], wu[tp_rank * fs:(tp_rank + 1) * fs]
             wd = wd[:, tp_rank * fs:(tp_rank + 1) * fs]
+        if cfg.k_equals_v_full and cfg.layer_window(len(layers)) == 0:
+            wv = wk            # no value projection: the value rows of the fused matrix repeat the key rows
         layers.append(LayerWeights(
+            layer_scalar=torch.ones(1, device=device, dtype=dense_dtype) if cfg.layer_scalar else None,
             attn_norm=torch.ones(d, device=device, dtype=dense_dtype),
             qkv=lin(torch.cat([wq, wk, wv], dim=0)),
             o=lin(wo),
@@ -217,14 +227,16 @@ class LlamaModel:
                 continue
             x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
             qkv = ops.linear(x, lw.qkv)
-            if cfg.qk_norm:
+            if cfg.qk_norm or cfg.v_norm:
                 from ..ops import gdn as _g
-                qkv = _g.qk_headnorm(qkv, self.hq, self.hkv, hd, lw.q_norm, lw.k_norm, cfg.rms_eps, cfg.norm_offset_one)
+                qkv = _g.qk_headnorm(qkv, self.hq, self.hkv, hd, lw.q_norm, lw.k_norm, cfg.rms_eps, cfg.norm_offset_one,
+                                     norm_v=cfg.v_norm)
+            theta, rdim, poff = cfg.layer_rope(li)
             q = ops.rope_kv_append(qkv, b.positions, b.seq_index, b.block_table, kv, self.hq, self.hkv, hd,
-                                   cfg.rope_theta, cfg.rotary_dim, rope_pos3=b.rope_pos3,
-                                   mrope_sections=cfg.mrope_sections)
+                                   theta, rdim, rope_pos3=b.rope_pos3, mrope_sections=cfg.mrope_sections,
+                                   pair_offset=poff)
             a = ops.attention(q, kv, b, self.hq, self.hkv, hd, window=cfg.layer_window(li), quant_out=qo,
-                              qkv=qkv)
+                              qkv=qkv, sm_scale=cfg.attn_scale)
             if self.quant and not qo:
                 a = ops.quant_fp8(a)
             if cfg.post_norms:
@@ -241,6 +253,8 @@ class LlamaModel:
                 h = ops.elementwise("add", h, o)
             else:
                 h = self.tp.row_linear(act, lw.down, h)
+            if lw.layer_scalar is not None:
+                h = ops.elementwise("scalar_mul", h, s=lw.layer_scalar_value())
         return h
 
     def _adapter_layer(self, li, lw, h, b, kv, ad):

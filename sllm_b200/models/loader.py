@@ -28,6 +28,12 @@ NVFP4_ENCODING = "nvfp4-e2m1-block16-e4m3fn-f32-outer"
 MXFP4_ENCODING = "mxfp4-e2m1-block32-e8m0"
 
 
+# per-layer vectors only some families carry: (tensor name after `blk.N.`, LayerWeights field)
+_OPTIONAL_LAYER_VECTORS = (("attn_q_norm.weight", "q_norm"), ("attn_k_norm.weight", "k_norm"),
+                           ("post_attention_norm.weight", "post_attn_norm"), ("post_ffw_norm.weight", "post_mlp_norm"),
+                           ("layer_output_scale.weight", "layer_scalar"))
+
+
 def _bf16_bytes(t: torch.Tensor) -> bytes:
     return t.detach().to(torch.bfloat16).contiguous().cpu().view(torch.int16).numpy().tobytes()
 
@@ -105,6 +111,9 @@ def export_llama_gguf(cfg: ModelConfig, w: LlamaWeights, path: str, tokenizer_js
         add_linear(p + "ffn_gate.weight", l.gate_up, 0, f)
         add_linear(p + "ffn_up.weight", l.gate_up, f, 2 * f)
         add_linear(p + "ffn_down.weight", l.down, 0, cfg.d_model)
+        for name, t in _OPTIONAL_LAYER_VECTORS:
+            if getattr(l, t) is not None:
+                add_dense(p + name, getattr(l, t))
     add_dense("output_norm.weight", w.final_norm)
     if not cfg.tie_embeddings:
         add_linear("output.weight", w.lm_head, 0, cfg.vocab)
@@ -274,7 +283,8 @@ def load_llama_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, k
             mlp_norm=dense(p + "ffn_norm.weight"),
             gate_up=lin([rows(p + "ffn_gate.weight", tp_rank * fs, (tp_rank + 1) * fs),
                          rows(p + "ffn_up.weight", tp_rank * fs, (tp_rank + 1) * fs)]),
-            down=lin([rows(p + "ffn_down.weight", 0, cfg.d_model, (tp_rank * fs, (tp_rank + 1) * fs))])))
+            down=lin([rows(p + "ffn_down.weight", 0, cfg.d_model, (tp_rank * fs, (tp_rank + 1) * fs))]),
+            **{f: dense(p + n) for n, f in _OPTIONAL_LAYER_VECTORS if p + n in g.tensors}))
     final_norm = dense("output_norm.weight")
     vs = (cfg.vocab + tp_size - 1) // tp_size
     vo = tp_rank * vs if tp_size > 1 else 0

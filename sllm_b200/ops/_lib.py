@@ -67,6 +67,7 @@ _KERNEL_SIGNATURES = {
     "sllm_gated_act": (I, [P, P, P, P, I, I, I, I, P]),
     "sllm_quant_fp8_1x128": (I, [P, P, P, I, I, I, P]),
     "sllm_rope_kv_append": (I, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, F, F, P, P]),
+    "sllm_rope_kv_append_paired": (I, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, F, F, P, I, P]),
     "sllm_rope_kv_append_mrope": (I, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, F, F, P, P, I, I, P]),
     "sllm_elementwise": (I, [P, P, P, L, I, I, F, P]),
     "sllm_argmax": (I, [P, P, P, I, I, I, I, P, L, P, I, P]),

@@ -325,7 +325,7 @@ class KVLayer:
 def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.Tensor, block_table: torch.Tensor,
                    kv: KVLayer, hq: int, hkv: int, hd: int, theta: float, rotary_dim: Optional[int] = None,
                    inv_freq: Optional[torch.Tensor] = None, rope_pos3: Optional[torch.Tensor] = None,
-                   mrope_sections: Optional[tuple] = None) -> torch.Tensor:
+                   mrope_sections: Optional[tuple] = None, pair_offset: int = 0) -> torch.Tensor:
     """Rotates q and k in ``qkv`` [T, (hq + 2 hkv) hd], appends k / v to the pages; returns q [T, hq*hd]
     (a view of qkv, rotated in place on CUDA).  ``rope_pos3`` (int32 [3, T]) with ``mrope_sections`` (temporal and
     height pair counts) gives 3-axis rotary positions; the page slot still follows ``positions``."""
@@ -337,8 +337,8 @@ def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.
         rope_pos3 = rope_pos3.contiguous()
     if not qkv.is_cuda:
         x = qkv.view(t, hq + 2 * hkv, hd)
-        q = ref.rope_split_half(x[:, :hq], positions, theta, rd, inv_freq, rope_pos3, mrope_sections)
-        k = ref.rope_split_half(x[:, hq:hq + hkv], positions, theta, rd, inv_freq, rope_pos3, mrope_sections)
+        q = ref.rope_split_half(x[:, :hq], positions, theta, rd, inv_freq, rope_pos3, mrope_sections, pair_offset)
+        k = ref.rope_split_half(x[:, hq:hq + hkv], positions, theta, rd, inv_freq, rope_pos3, mrope_sections, pair_offset)
         v = x[:, hq + hkv:].to(torch.float32)
         if qkv.dtype != torch.float32:
             q, k = ref.round_bf16(q), ref.round_bf16(k)
@@ -363,6 +363,13 @@ def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.
             _p(kv.k_scale), _p(kv.v_scale), t, hq, hkv, hd, rd, kv.page_size, int(kv.fp8), theta, kv.k_static,
             kv.v_static, _p(inv_freq), _p(rope_pos3), int(mrope_sections[0]), int(mrope_sections[1]), _stream())
         _lib.check(rc, "rope_kv_append_mrope")
+        return qkv[:, :hq * hd]
+    if pair_offset > 0:
+        rc = _lib.kernels().sllm_rope_kv_append_paired(
+            _p(qkv), _p(positions), _p(seq_index), _p(block_table), block_table.stride(0), _p(kv.k), _p(kv.v),
+            _p(kv.k_scale), _p(kv.v_scale), t, hq, hkv, hd, rd, kv.page_size, int(kv.fp8), theta, kv.k_static,
+            kv.v_static, _p(inv_freq), pair_offset, _stream())
+        _lib.check(rc, "rope_kv_append_paired")
         return qkv[:, :hq * hd]
     rc = _lib.kernels().sllm_rope_kv_append(
         _p(qkv), _p(positions), _p(seq_index), _p(block_table), block_table.stride(0), _p(kv.k), _p(kv.v),

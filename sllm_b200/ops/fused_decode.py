@@ -158,6 +158,10 @@ def inv_freq_table(theta: float, rotary_dim: int, device) -> torch.Tensor:
     if t is None:
         i = torch.arange(rotary_dim // 2, dtype=torch.float64)
         t = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rotary_dim).to(torch.float32).to(device)
+        if t.is_cuda:
+            # the kernels stage this table in their preamble, which may run before the work queued ahead of them has
+            # finished: the upload must have landed before the first launch that names it
+            torch.cuda.current_stream(t.device).synchronize()
         _inv_freq_cache[key] = t
     return t
 
@@ -198,27 +202,33 @@ def backend() -> str:
     return os.environ.get("SLLM_FD_BACKEND", "cluster")
 
 
+def _resolve_cluster_phase(ph: FdPhase, i: int, rows: int, il: Optional[list]):
+    """(descriptor with the weight the cluster GEMM reads, weight rows, bn, splits, stages) of a phase."""
+    from .core import _gemm_plan
+    one = FdPhase.from_buffer_copy(ph)
+    w_rows = ph.n
+    if ph.epilogue == SILU_QUANT:
+        pair = il[i] if il is not None and il[i] is not None else None
+        if pair is None:
+            key = (ph.w, ph.w_scale, ph.n)
+            pair = _il_cache.get(key)
+            if pair is None:
+                raise ValueError("the cluster backend needs the interleaved gate / up weight (interleave_gate_up)")
+        one.w, one.w_scale = pair[0].data_ptr(), pair[1].data_ptr()
+        one.ld_sa = _ld(pair[1])
+        w_rows = 2 * ph.n
+    _, bn, splits, stages = _gemm_plan(rows, w_rows, ph.k // 128)
+    if ph.epilogue == SILU_QUANT:
+        splits = 1
+    return one, w_rows, bn, splits, stages
+
+
 def _launch_cluster(phases: list, rows: int, device: torch.device, rope: Optional[FdRope], il: Optional[list],
                     comm=None) -> None:
-    from .core import _gemm_plan
     wsp = workspace(device)
     lib = _lib.kernels()
-    for i, ph in enumerate(phases):
-        one = FdPhase.from_buffer_copy(ph)
-        w_rows = ph.n
-        if ph.epilogue == SILU_QUANT:
-            pair = il[i] if il is not None and il[i] is not None else None
-            if pair is None:
-                key = (ph.w, ph.w_scale, ph.n)
-                pair = _il_cache.get(key)
-                if pair is None:
-                    raise ValueError("the cluster backend needs the interleaved gate / up weight (interleave_gate_up)")
-            one.w, one.w_scale = pair[0].data_ptr(), pair[1].data_ptr()
-            one.ld_sa = _ld(pair[1])
-            w_rows = 2 * ph.n
-        _, bn, splits, stages = _gemm_plan(rows, w_rows, ph.k // 128)
-        if ph.epilogue == SILU_QUANT:
-            splits = 1
+    plans = [_resolve_cluster_phase(ph, i, rows, il) for i, ph in enumerate(phases)]
+    for one, w_rows, bn, splits, stages in plans:
         rc = lib.sllm_gemm_fused(C.byref(one), C.byref(rope) if rope is not None else None, rows, bn, splits, stages,
                                  _p(wsp.ws), wsp.ws.numel(), _p(wsp.counters), wsp.counters.numel(), _p(wsp.status),
                                  _stream(), None if comm is None else C.cast(C.pointer(comm), C.c_void_p))

@@ -7,6 +7,8 @@ from __future__ import annotations
 import ctypes as C
 import math
 
+from typing import Optional
+
 import torch
 
 from . import _lib
@@ -16,6 +18,7 @@ _SIGS = {
     "sllm_gdn_conv_silu": (I, [P, P, P, P, P, P, I, I, I, P]),
     "sllm_gdn_recurrent": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]),
     "sllm_qk_headnorm": (I, [P, I, I, I, I, I, P, P, F, I, P]),
+    "sllm_qkv_headnorm": (I, [P, I, I, I, I, I, P, P, F, I, I, I, P]),
 }
 
 
@@ -92,18 +95,25 @@ def recurrent(qkv, z, b, a, a_log, dt_bias, norm_w, state, row_off, slots, qk_he
     return out
 
 
-def qk_headnorm(qkv: torch.Tensor, hq: int, hkv: int, hd: int, wq: torch.Tensor, wk: torch.Tensor, eps: float,
-                offset_one: bool = False) -> torch.Tensor:
-    """RMS-normalises every q and k head of a fused [T, (hq + 2 hkv) * hd] activation in place; returns it."""
+def qk_headnorm(qkv: torch.Tensor, hq: int, hkv: int, hd: int, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+                eps: float, offset_one: bool = False, norm_v: bool = False) -> torch.Tensor:
+    """RMS-normalises every q and k head of a fused [T, (hq + 2 hkv) * hd] activation in place; returns it.
+    A missing weight vector means "all ones" (with wq and wk both None the q / k heads are left alone);
+    ``norm_v`` also normalises the value heads, without a weight (Gemma-4's v_norm)."""
     t = qkv.shape[0]
     if not qkv.is_cuda:
         x = qkv.view(t, hq + 2 * hkv, hd)
-        for lo, hi, w in ((0, hq, wq), (hq, hq + hkv, wk)):
+        spans = [] if (wq is None and wk is None) else [(0, hq, wq), (hq, hq + hkv, wk)]
+        if norm_v:
+            spans.append((hq + hkv, hq + 2 * hkv, None))
+        for lo, hi, w in spans:
             v = x[:, lo:hi].float()
-            g = w.float() + (1.0 if offset_one else 0.0)
+            g = 1.0 if w is None else w.float() + (1.0 if offset_one else 0.0)
             x[:, lo:hi] = (v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * g).to(qkv.dtype)
         return qkv
     from .core import _p, _stream
-    rc = _k().sllm_qk_headnorm(_p(qkv), qkv.stride(0), t, hq, hkv, hd, _p(wq), _p(wk), eps, int(offset_one), _stream())
-    _lib.check(rc, "qk_headnorm")
+    skip_qk = wq is None and wk is None
+    rc = _k().sllm_qkv_headnorm(_p(qkv), qkv.stride(0), t, hq, hkv, hd, _p(wq), _p(wk), eps, int(offset_one),
+                                int(skip_qk), int(norm_v), _stream())
+    _lib.check(rc, "qkv_headnorm")
     return qkv

@@ -84,16 +84,18 @@ def gated_act(x: torch.Tensor, act: str = "silu", round_intermediate: bool = Tru
 
 def rope_split_half(x: torch.Tensor, positions: torch.Tensor, theta: float, rotary_dim: Optional[int] = None,
                     inv_freq: Optional[torch.Tensor] = None, rope_pos3: Optional[torch.Tensor] = None,
-                    sections: Optional[tuple] = None) -> torch.Tensor:
+                    sections: Optional[tuple] = None, pair_offset: int = 0) -> torch.Tensor:
     """x: [T, H, D]; rotates the first rotary_dim channels, pairing channel i with i + rotary_dim/2.  With
     rope_pos3 [3, T] and sections (sec_t, sec_h), rotary pair j turns with the temporal index for j < sec_t, the
-    height index for j < sec_t + sec_h and the width index otherwise."""
+    height index for j < sec_t + sec_h and the width index otherwise.  ``pair_offset`` > 0 is the "proportional"
+    layout: channel i < rotary_dim / 2 pairs with i + pair_offset (= D / 2), frequencies theta^(-2 i / D)."""
     t, h, d = x.shape
     r = rotary_dim or d
     half = r // 2
+    poff = pair_offset if pair_offset > 0 else half
     xf = x.to(torch.float32)
     if inv_freq is None:
-        inv_freq = theta ** (-2.0 * torch.arange(half, dtype=torch.float32, device=x.device) / r)
+        inv_freq = theta ** (-2.0 * torch.arange(half, dtype=torch.float32, device=x.device) / (d if pair_offset > 0 else r))
     if rope_pos3 is not None:
         st, sh = sections
         axis = torch.tensor([0 if j < st else (1 if j < st + sh else 2) for j in range(half)], device=x.device)
@@ -102,10 +104,10 @@ def rope_split_half(x: torch.Tensor, positions: torch.Tensor, theta: float, rota
     else:
         ang = positions.to(torch.float32).unsqueeze(-1) * inv_freq.to(torch.float32).unsqueeze(0)  # [T, half]
     cs, sn = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
-    a, b = xf[..., :half], xf[..., half:r]
+    a, b = xf[..., :half], xf[..., poff:poff + half]
     out = xf.clone()
     out[..., :half] = a * cs - b * sn
-    out[..., half:r] = b * cs + a * sn
+    out[..., poff:poff + half] = b * cs + a * sn
     return out
 
 

@@ -144,7 +144,9 @@ def test_rope_kv_phase(impl, rows, hq, hkv, rd, fp8, grid):
     qout = torch.zeros((rows, hq * hd), dtype=torch.bfloat16, device=DEV)
     ph = fd.phase(fd.ROPE_KV, lw.w, lw.scale_t, xq, xs, n=n, k=d, ssq_in=ssq_in, norm_dim=d, eps=1e-6, y=qout, ldy=hq * hd,
                   ld_s_out=bn)
-    rope = fd.rope_desc(positions.to(DEV), seq_index.to(DEV), block_table.to(DEV), kv, hq, hkv, rd, theta)
+    # the descriptor holds raw addresses: the device copies must outlive the launch
+    d_pos, d_seq, d_table = positions.to(DEV), seq_index.to(DEV), block_table.to(DEV)
+    rope = fd.rope_desc(d_pos, d_seq, d_table, kv, hq, hkv, rd, theta)
     fd.launch([ph], rows, torch.device(DEV), rope, grid=grid, impl=impl)
     # reference: projection (fp32), norm factor, then the per-op rotary + append on CPU tensors
     norm = fd.ref_norm_factor(ssq_in, rows, d, 1e-6)
@@ -176,6 +178,10 @@ def test_rope_kv_phase(impl, rows, hq, hkv, rd, fp8, grid):
 @pytest.mark.parametrize("impl", IMPLS)
 def test_four_phase_chain_matches_sequential_reference(impl, rows, grid):
     """o-proj -> gate/up -> down -> head as one launch: outputs of each phase feed the next through the grid barrier."""
+    _chain(impl, rows, grid)
+
+
+def _chain(impl, rows, grid):
     d, qs, ffn, vocab = 512, 256, 768, 1000
     bn = 16 if rows <= 16 else 32
     wo, wgu, wd, wh = _weights(d, qs, 1), _weights(2 * ffn, d, 2), _weights(d, ffn, 3), _weights(vocab, d, 4)

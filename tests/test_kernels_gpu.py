@@ -174,6 +174,51 @@ def test_rope_kv_append(fp8, hq, hkv, hd, rd):
 
 
 @pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("hq,hkv,hd,rd", [(16, 8, 256, 64), (8, 1, 512, 128), (4, 2, 128, 128)])
+def test_rope_kv_append_proportional_pairs(fp8, hq, hkv, hd, rd):
+    """Channel i < rd / 2 pairs with i + hd / 2, frequencies over hd; the channels between pass through."""
+    torch.manual_seed(hd)
+    t, page, pages = 29, 16, 12
+    qkv = torch.randn(t, (hq + 2 * hkv) * hd, device=DEV).bfloat16()
+    seq = (torch.arange(t, device=DEV) % 3).int()
+    pos = (torch.arange(t, device=DEV) // 3 + 11).int()
+    table = torch.randperm(pages, device=DEV).int().view(3, 4)
+    kv = _make_kv(pages, page, hkv, hd, fp8)
+    kvc = _cpu_kv(kv)
+    q_ref = ops.rope_kv_append(qkv.cpu().clone(), pos.cpu(), seq.cpu(), table.cpu(), kvc, hq, hkv, hd, 1e6, rd,
+                               pair_offset=hd // 2)
+    q = ops.rope_kv_append(qkv.clone(), pos, seq, table, kv, hq, hkv, hd, 1e6, rd, pair_offset=hd // 2)
+    assert rel_err(q.cpu(), q_ref) < 5e-3
+    untouched = q.view(t, hq, hd)[:, :, rd // 2:hd // 2]
+    assert torch.equal(untouched, qkv[:, :hq * hd].view(t, hq, hd)[:, :, rd // 2:hd // 2])
+    if fp8:
+        kd = ref.from_e4m3(kv.k.cpu()) * kv.k_scale.cpu().unsqueeze(-1)
+        kr = ref.from_e4m3(kvc.k) * kvc.k_scale.unsqueeze(-1)
+        assert rel_err(kd, kr) < 3e-2
+    else:
+        assert rel_err(kv.k.cpu(), kvc.k) < 5e-3
+    assert torch.equal(kv.v.cpu(), kvc.v)
+
+
+@pytest.mark.parametrize("qk,norm_v", [(True, True), (False, True), (True, False)])
+def test_qkv_headnorm_value_heads(qk, norm_v):
+    from sllm_b200.ops import gdn
+    torch.manual_seed(3)
+    t, hq, hkv, hd = 19, 8, 2, 256
+    qkv = torch.randn(t, (hq + 2 * hkv) * hd, device=DEV).bfloat16() * 3
+    wq = (torch.randn(hd, device=DEV) * 0.1).bfloat16() if qk else None
+    wk = (torch.randn(hd, device=DEV) * 0.1).bfloat16() if qk else None
+    c = lambda x: None if x is None else x.cpu()
+    want = gdn.qk_headnorm(qkv.cpu().clone(), hq, hkv, hd, c(wq), c(wk), 1e-6, True, norm_v=norm_v)
+    got = gdn.qk_headnorm(qkv.clone(), hq, hkv, hd, wq, wk, 1e-6, True, norm_v=norm_v)
+    assert rel_err(got.cpu(), want) < 6e-3
+    if not qk:
+        assert torch.equal(got[:, :(hq + hkv) * hd], qkv[:, :(hq + hkv) * hd])
+    if not norm_v:
+        assert torch.equal(got[:, (hq + hkv) * hd:], qkv[:, (hq + hkv) * hd:])
+
+
+@pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 64), (32, 8, 128), (64, 8, 64), (8, 8, 128), (16, 4, 256)])
 @pytest.mark.parametrize("window", [0, 40])
 def test_paged_attention(fp8, hq, hkv, hd, window):
