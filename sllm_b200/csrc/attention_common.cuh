@@ -30,6 +30,7 @@ struct PagedAttnParams {
   const float* sinks;       // optional [hq] attention-sink logits (added to the softmax denominator)
   int* status_word;         // device status word for bounded waits (tensor-core kernel)
   int early_trigger;        // tensor-core kernel: let dependent launches start once the CTA holds its TMEM
+  STEP_TRACE_FIELD
 };
 
 

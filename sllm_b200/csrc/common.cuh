@@ -243,6 +243,40 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---------------------------------------------------------------- step timeline (trace builds only)
+// Under -DSLLM_TRACE every launch of the pipelined kernels gets the next 4-word record of a device buffer set with
+// sllm_step_trace_set: [0] earliest CTA start, [1] CTA 0 past its dependency wait, [2] latest CTA end (globaltimer
+// ns), [3] kernel kind.  Records are assigned on the host when the launch is enqueued (or captured), so a replayed
+// graph fills the same records again; clear the buffer to ~0 / 0 between replays.  Never compiled into the product.
+#ifdef SLLM_TRACE
+unsigned long long* step_trace_next(int kind);      // host: record for the launch being enqueued, or null
+__device__ __forceinline__ unsigned long long step_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void step_trace_start(unsigned long long* rec) {
+  if (rec && threadIdx.x == 0) atomicMin(rec, step_now());
+}
+__device__ __forceinline__ void step_trace_waited(unsigned long long* rec) {
+  if (rec && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) rec[1] = step_now();
+}
+__device__ __forceinline__ void step_trace_end(unsigned long long* rec) {
+  if (rec && threadIdx.x == 0) atomicMax(rec + 2, step_now());
+}
+#define STEP_TRACE_FIELD unsigned long long* step_rec;
+#define STEP_TRACE_START(p) step_trace_start((p).step_rec)
+#define STEP_TRACE_WAITED(p) step_trace_waited((p).step_rec)
+#define STEP_TRACE_END(p) step_trace_end((p).step_rec)
+#define STEP_TRACE_ASSIGN(p, kind) (p).step_rec = step_trace_next(kind)
+#else
+#define STEP_TRACE_FIELD
+#define STEP_TRACE_START(p)
+#define STEP_TRACE_WAITED(p)
+#define STEP_TRACE_END(p)
+#define STEP_TRACE_ASSIGN(p, kind)
+#endif
+
 // ---------------------------------------------------------------- L2 prefetch
 // Requests bytes into L2 with no destination in shared memory and nothing to wait for (16-byte aligned, multiple of 16).
 __device__ __forceinline__ void prefetch_l2_bulk(const void* gsrc, uint32_t bytes) {

@@ -18,6 +18,7 @@
 //
 // The CUDA-core kernel in attention.cu stays the path for bf16 pages and other head sizes.  Counterpart
 // in the reference: causal_attention_decode_wave_split_kernel (causal_attention_kernel.hip.cpp:264).
+#include <cstdio>
 #include "common.cuh"
 #include "api.h"
 #include "attention_common.cuh"
@@ -95,6 +96,7 @@ template <int G>
 __global__ void __launch_bounds__(kDaThreads, 2)
 decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                            const PagedAttnParams p) {
+  STEP_TRACE_START(p);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // layout: stages x {K tile, V tile} | Q (16 x 128 B) | 2 x P^T (16 x 128 B) | barriers | tail scratch
@@ -156,6 +158,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
   // Everything above reads only launch inputs no kernel writes (row -> sequence map, lengths); q and the newest
   // K / V slots come from the kernel before this one.
   pdl_wait();
+  if (threadIdx.x == 64) STEP_TRACE_WAITED(p);
   // Dependents may start once this CTA holds its tensor memory: the next GEMM then requests its first weight
   // tiles while this grid drains.
   if (p.early_trigger) pdl_trigger();
@@ -441,6 +444,7 @@ decode_attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  STEP_TRACE_END(p);
 }
 
 // [pages*kv_heads, page_size tokens, 128] E4M3 plane (head-major pages); box = {128 channels, page_size tokens, 1}.
@@ -497,6 +501,13 @@ static int launch_da(const CUtensorMap& tk, const CUtensorMap& tv, const PagedAt
                              static_cast<int>(smem)) != cudaSuccess)
       return SLLM_ERR_CUDA;
     cfg = true;
+#ifdef SLLM_TRACE
+    int per_sm = -1;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_attention_tc_kernel<G>, kDaThreads, smem);
+    cudaFuncAttributes fa;
+    cudaFuncGetAttributes(&fa, decode_attention_tc_kernel<G>);
+    fprintf(stderr, "[trace] decode attention G=%d smem=%zu regs %d: %d CTAs/SM\n", G, smem, fa.numRegs, per_sm);
+#endif
   }
   dim3 grid(rows, p.hkv, splits);
   launch_kernel(decode_attention_tc_kernel<G>, dim3(grid), dim3(kDaThreads), smem, st, 1u, tk, tv, p);
@@ -559,6 +570,7 @@ SLLM_EXPORT int sllm_decode_attention_tc(const void* q, int q_ld, const void* k_
   p.out_scale = out_scale; p.ld_scale = ld_scale; p.sinks = sinks;
   p.ws_o = nullptr; p.ws_ml = nullptr; p.counters = counters; p.status_word = status;
   p.early_trigger = attn_early_trigger();
+  STEP_TRACE_ASSIGN(p, 2);
   if (splits > 1) {
     const long long units = static_cast<long long>(rows) * hkv;
     const long long need = units * splits * (static_cast<long long>(g) * 128 + g * 2);

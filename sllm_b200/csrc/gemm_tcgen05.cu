@@ -35,6 +35,7 @@
 //
 // Replaces the reference's scalar-FMA matmul family and its library GEMM calls
 // (native/hip/src/matmul_kernel.hip.cpp:586-830, native/hip/src/matmul_runtime.inc:690).
+#include <cstdio>
 #include "common.cuh"
 #include "api.h"
 #include "epilogue_columns.cuh"
@@ -123,6 +124,7 @@ struct GemmParams {
   CommParams comm;     // used by the kComm instantiation only
   GatherParams gather; // world > 1: B operand gathered from the peers (unscaled GEMM only)
   FusedEpi fe;         // mode != 0: fused row epilogue (scaled, swap-AB launches)
+  STEP_TRACE_FIELD
 };
 
 #ifdef SLLM_TRACE
@@ -152,7 +154,9 @@ struct __align__(16) GemmBarriers {
   int abort_flag;
   int is_last;
   uint32_t epoch;
-  float famax[128];    // fused SiLU epilogue: row maxima exchanged between the two tiles of a scale block
+  float famax[128];       // fused SiLU epilogue: row maxima of this tile ...
+  float famax_peer[128];  // ... and of the other tile of the scale block, written by that tile's CTA over DSMEM
+  float inv_freq[64];     // fused rotary epilogue: the frequency table, staged while the main loop runs
 };
 
 template <int BN>
@@ -178,26 +182,21 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float4 ld_dsmem_f32x4(const float* local_ptr, uint32_t cta_rank) {
+// Store into the shared memory of CTA `cta_rank` of the cluster, at the address `local_ptr` has in this CTA.
+// Partials travel by stores (fire and forget, made visible by the cluster barrier that follows) rather than by
+// loads, whose round trips over the cluster network would sit on the critical path one after another.
+__device__ __forceinline__ void st_dsmem_f32(float* local_ptr, uint32_t cta_rank, float v) {
   uint32_t ra;
-  float4 v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local_ptr)), "r"(cta_rank));
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(ra)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_dsmem_f32(const float* local_ptr, uint32_t cta_rank) {
-  uint32_t ra;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local_ptr)), "r"(cta_rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-  return v;
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
 }
 
 template <int BN, bool kScaled, bool kComm>
-__global__ void __launch_bounds__(gemm_threads(BN), (BN <= 64 ? 2 : 1))
+// Two CTAs per SM for the decode tiles (BN <= 64): 128 registers a thread and at most ~110 KB of shared memory each.
+// Measured: with the pipeline deepened to fill one CTA's 227 KB the same grids run a third slower (the second CTA of
+// an SM hides the first one's start-up, reduction and exit), although the occupancy query reports one CTA per SM for
+// every kernel that allocates tensor memory.
+__global__ void __launch_bounds__((BN <= 64 ? 256 : gemm_threads(BN)), (BN <= 64 ? 2 : 1))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -211,7 +210,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   constexpr int kElemsPerBox = kScaled ? 128 : 64;
   GemmBarriers<BN>* bars = reinterpret_cast<GemmBarriers<BN>*>(smem + p.stages * kStageBytes);
   GemmScales<BN>* sc = reinterpret_cast<GemmScales<BN>*>(bars + 1);
-  float* red = reinterpret_cast<float*>(smem);  // [BN][128] cluster split-K partial (pipeline memory, reused)
+  // Output staging in the drained pipeline memory: red[(s * cw + cl) * 128 + row] = the partial of K slice s for
+  // column c0 + cl of this CTA's column slice [c0, c0 + cw) (one slice s = 0 holding all BN columns without a
+  // cluster split).
+  float* red = reinterpret_cast<float*>(smem);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -223,6 +225,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   volatile int* abort_flag = &bars->abort_flag;
   const bool cluster_split = p.cluster_split != 0;
   if (threadIdx.x == 0) TRACE(0);
+  STEP_TRACE_START(p);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -261,6 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   bool ok = true;
   bool active = true;   // this CTA takes part in the output phase (false for non-final global split-K CTAs)
   float rn_lane = 1.f;  // fused row epilogue: RMSNorm factor of token row `lane`
+  int my_pos = 0, my_page = 0;  // fused rotary epilogue: position and KV page of token row c0 + lane of this CTA's slice
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -399,6 +403,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     // ------------------------------------------------------------ epilogue main loop (128 threads)
     pdl_wait();
+    if (threadIdx.x == 64) STEP_TRACE_WAITED(p);
     if constexpr (kScaled && BN <= 32) {
       // norm factor of every token row from the sums of squares its producer wrote: requested now, used after the
       // last K block, so the L2 round trip hides under the main loop
@@ -406,6 +411,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         float ss = 0.f;
         for (int i = 0; i < p.fe.norm_tiles; ++i) ss += __ldcg(p.fe.ssq_in + static_cast<size_t>(i) * p.fe.ld_s + lane);
         rn_lane = rsqrtf(ss / static_cast<float>(p.fe.norm_dim) + p.fe.eps);
+      }
+      if (p.fe.mode == SLLM_FD_ROPE_KV + 1) {
+        // position -> page walk (three dependent loads) and the frequency table: also requested now
+        const int cwp = cluster_split ? BN / static_cast<int>(gridDim.z) : BN;
+        const int c0p = cluster_split ? split * cwp : 0;
+        if (lane < cwp && c0p + lane < p.b_rows) {
+          my_pos = p.fe.rope.positions[c0p + lane];
+          my_page = p.fe.rope.block_table[static_cast<size_t>(p.fe.rope.seq_index[c0p + lane]) * p.fe.rope.max_blocks +
+                                          my_pos / p.fe.rope.page_size];
+        }
+        if (et < 64) bars->inv_freq[et] = et < (p.fe.rope.rotary_dim >> 1) ? p.fe.inv_freq[et] : 0.f;
       }
     }
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -517,20 +533,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       }
     }
-    // Park the fp32 tile in shared memory as red[column][row] (the pipeline stages are drained by
-    // now).  The output phase below works on 16-byte units out of this buffer, and with a cluster
-    // split every CTA reduces and writes its own column slice of the tile over DSMEM.
-    if (active) {
+    // Without a cluster split the fp32 tile is parked in this CTA's shared memory as red[column][row] (the
+    // pipeline stages are drained by now); the output phase below works on 16-byte units out of this buffer.
+    if (!cluster_split) {
+      if (active) {
 #pragma unroll
-      for (int c = 0; c < BN; ++c) red[c * kTileA + row] = acc[c];
+        for (int c = 0; c < BN; ++c) red[c * kTileA + row] = acc[c];
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
-    if (!cluster_split) asm volatile("bar.sync 1, 128;" ::: "memory");
   }
 
   if (threadIdx.x == 64) TRACE(7);
   constexpr bool kFusable = kScaled && BN <= 32;      // instantiations that carry the fused row epilogue
   const bool pair_x = kFusable && p.fe.mode == SLLM_FD_SILU_QUANT + 1;     // cluster of two tiles along x (no K split)
-  if (cluster_split || pair_x) cluster_sync_all();  // partials visible cluster-wide
+  if (cluster_split) {
+    // Cluster split-K: CTA j of the cluster finishes the columns [j cw, (j + 1) cw) of the tile.  Once every CTA's
+    // pipeline memory is drained (first barrier), each CTA stores its partial of those columns straight into CTA j's
+    // staging buffer, slot = its own K slice; after the second barrier every CTA sums its slots out of its OWN
+    // shared memory and nothing reads another CTA's memory again, so CTAs leave without a closing barrier.
+    cluster_sync_all();
+    if (warp >= 2 && warp < 6) {
+      const int cwp = BN / static_cast<int>(gridDim.z);       // a power of two
+      const int sh = 31 - __clz(cwp);
+#pragma unroll
+      for (int c = 0; c < BN; ++c)
+        st_dsmem_f32(red + (split * cwp + (c & (cwp - 1))) * kTileA + row, static_cast<uint32_t>(c >> sh), acc[c]);
+    }
+    cluster_sync_all();
+  }
   if (threadIdx.x == 64) TRACE(8);
 
   if (kFusable && p.fe.mode != 0) {
@@ -545,18 +576,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int T = p.b_rows;
     const int ew = warp - 2;
     const bool epi_warp = warp >= 2 && warp < 6 && active && ok;
-    int my_pos = 0, my_page = 0;
     if (epi_warp) {
-      if (fe.mode == SLLM_FD_ROPE_KV + 1 && lane < cw && c0 + lane < T) {
-        my_pos = fe.rope.positions[c0 + lane];
-        my_page = fe.rope.block_table[static_cast<size_t>(fe.rope.seq_index[c0 + lane]) * fe.rope.max_blocks +
-                                      my_pos / fe.rope.page_size];
-      }
       ColEpilogue e;
       e.mode = fe.mode - 1; e.n = fe.n; e.ldy = p.ldy; e.ld_s = fe.ld_s; e.softcap = fe.softcap;
       e.y = p.y; e.residual = p.residual;
       e.q_out = fe.q_out; e.s_out = fe.s_out; e.ssq_out = fe.ssq_out;
-      e.rope = &fe.rope; e.inv_freq = fe.inv_freq;
+      e.rope = &fe.rope; e.inv_freq = bars->inv_freq;
       [[maybe_unused]] uint32_t comm_epoch = 0;
       [[maybe_unused]] long long comm_region = 0, comm_toff = 0;
       [[maybe_unused]] bool comm_ok = true;
@@ -578,10 +603,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         for (int cl = ew; cl < cw; cl += 4) {
           const int col = c0 + cl;
           if (col >= T) break;
-          const float* src = red + col * kTileA + lane * 4;
+          const float* src = red + cl * kTileA + lane * 4;
           float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int s = 0; s < nslice; ++s) {
-            const float4 x = nslice == 1 ? *reinterpret_cast<const float4*>(src) : ld_dsmem_f32x4(src, s);
+            const float4 x = *reinterpret_cast<const float4*>(src + s * cw * kTileA);
             sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
           }
           uint2 w;
@@ -613,7 +638,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*abort_flag) comm_ok = false;
       }
-      for (int cl = ew; cl < cw && comm_ok; cl += 4) {
+      if (pair_x) {
+        // ---- SiLU(gate) * up of 64 features: a half warp per token row (lane l: features 4 l .. 4 l + 3, gate
+        // rows 0..63 and up rows 64..127 of the tile), two rows per warp step; the result goes back over the gate
+        // half of the staging buffer, the row maximum to both CTAs of the scale block
+        const int l16 = lane & 15;
+        for (int base = 2 * ew; base < T; base += 8) {
+          const int col = base + (lane >> 4);
+          const bool live = col < T;
+          const int cc = live ? col : base;
+          const float rn = __shfl_sync(0xffffffffu, rn_lane, cc);
+          float* slot = red + cc * kTileA + l16 * 4;
+          const float4 g = *reinterpret_cast<const float4*>(slot);
+          const float4 u = *reinterpret_cast<const float4*>(slot + 64);
+          float v[4] = {g.x * rn, g.y * rn, g.z * rn, g.w * rn};
+          const float up[4] = {u.x * rn, u.y * rn, u.z * rn, u.w * rn};
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = fe.act == 0 ? v[j] / (1.f + __expf(-v[j]))
+                                        : 0.5f * v[j] * (1.f + tanhf(0.7978845608028654f * (v[j] + 0.044715f * v[j] * v[j] * v[j])));
+            v[j] = col_bf16r(col_bf16r(a) * up[j]);
+            const float x = fabsf(v[j]);
+            if (x == x && x <= 3.0e38f) amax = fmaxf(amax, x);
+          }
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // within the half warp
+          if (live) {
+            *reinterpret_cast<float4*>(slot) = make_float4(v[0], v[1], v[2], v[3]);
+            if (l16 == 0) {
+              bars->famax[col] = amax;
+              st_dsmem_f32(&bars->famax_peer[col], (blockIdx.x & 1u) ^ 1u, amax);   // the other tile of the scale block
+            }
+          }
+        }
+      }
+      for (int cl = ew; cl < cw && comm_ok && !pair_x; cl += 4) {
         const int col = c0 + cl;
         if (col >= T) break;
         const float rn = __shfl_sync(0xffffffffu, rn_lane, col);
@@ -629,52 +689,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             sum.z += __bfloat162float(h1.x); sum.w += __bfloat162float(h1.y);
           }
         } else {
-          const float* src = red + col * kTileA + lane * 4;
+          const float* src = red + cl * kTileA + lane * 4;
           for (int s = 0; s < nslice; ++s) {
-            const float4 x = nslice == 1 ? *reinterpret_cast<const float4*>(src) : ld_dsmem_f32x4(src, s);
+            const float4 x = *reinterpret_cast<const float4*>(src + s * cw * kTileA);
             sum.x += x.x; sum.y += x.y; sum.z += x.z; sum.w += x.w;
           }
         }
         float v[4] = {sum.x * rn, sum.y * rn, sum.z * rn, sum.w * rn};
-        if (pair_x) {
-          // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 64 features
-          float up[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) up[j] = __shfl_xor_sync(0xffffffffu, v[j], 16);
-          float amax = 0.f;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float a = fe.act == 0 ? v[j] / (1.f + __expf(-v[j]))
-                                        : 0.5f * v[j] * (1.f + tanhf(0.7978845608028654f * (v[j] + 0.044715f * v[j] * v[j] * v[j])));
-            v[j] = col_bf16r(col_bf16r(a) * up[j]);
-            const float x = fabsf(v[j]);
-            if (lane < 16 && x == x && x <= 3.0e38f) amax = fmaxf(amax, x);
-          }
-          amax = warp_max(amax);
-          if (lane < 16) *reinterpret_cast<float4*>(red + col * kTileA + lane * 4) = make_float4(v[0], v[1], v[2], v[3]);
-          if (lane == 0) bars->famax[col] = amax;
-        } else {
-          col_epilogue(e, a_tile, col, lane, v, __shfl_sync(0xffffffffu, my_pos, cl), __shfl_sync(0xffffffffu, my_page, cl));
-        }
+        col_epilogue(e, a_tile, col, lane, v, __shfl_sync(0xffffffffu, my_pos, cl), __shfl_sync(0xffffffffu, my_page, cl));
       }
     }
     if (pair_x) {
-      cluster_sync_all();     // both tiles' row maxima are written (all threads of both CTAs take part)
+      // both tiles' row maxima are written, each into both CTAs (all threads of both CTAs take part); nothing
+      // reads the other CTA's memory afterwards
+      cluster_sync_all();
       if (epi_warp) {
-        const uint32_t partner = (blockIdx.x & 1u) ^ 1u;
-        const float amax_lane = lane < T ? fmaxf(bars->famax[lane], ld_dsmem_f32(&bars->famax[lane], partner)) : 0.f;
-        for (int col = ew; col < T; col += 4) {
-          const float amax = __shfl_sync(0xffffffffu, amax_lane, col);
-          const float scale = amax > 0.f ? amax / 448.f : 1.f;
-          if (lane < 16) {
-            const float4 x = *reinterpret_cast<const float4*>(red + col * kTileA + lane * 4);
+        const int l16 = lane & 15;
+        for (int base = 2 * ew; base < T; base += 8) {
+          const int col = base + (lane >> 4);
+          if (col < T) {
+            const float amax = fmaxf(bars->famax[col], bars->famax_peer[col]);
+            const float scale = amax > 0.f ? amax / 448.f : 1.f;
+            const float4 x = *reinterpret_cast<const float4*>(red + col * kTileA + l16 * 4);
             const float v[4] = {x.x, x.y, x.z, x.w};
             uint32_t q = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) q |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
-            *reinterpret_cast<uint32_t*>(fe.q_out + static_cast<size_t>(col) * fe.n + a_tile * 64 + lane * 4) = q;
+            *reinterpret_cast<uint32_t*>(fe.q_out + static_cast<size_t>(col) * fe.n + a_tile * 64 + l16 * 4) = q;
+            if (l16 == 0 && (blockIdx.x & 1u) == 0) fe.s_out[static_cast<size_t>(a_tile >> 1) * fe.ld_s + col] = scale;
           }
-          if (lane == 0 && (blockIdx.x & 1u) == 0) fe.s_out[static_cast<size_t>(a_tile >> 1) * fe.ld_s + col] = scale;
         }
       }
     }
@@ -694,24 +737,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = 0.f;
       for (int s = 0; s < nslice; ++s) {
+        const float* slot = red + (s * cw + col - c0) * kTileA + r0;     // this CTA's own shared memory
         if (tr) {
-          const float* src = red + col * kTileA + r0;
-          float4 x0, x1;
-          if (nslice == 1) {
-            x0 = *reinterpret_cast<const float4*>(src);
-            x1 = *reinterpret_cast<const float4*>(src + 4);
-          } else {
-            x0 = ld_dsmem_f32x4(src, s);
-            x1 = ld_dsmem_f32x4(src + 4, s);
-          }
+          const float4 x0 = *reinterpret_cast<const float4*>(slot);
+          const float4 x1 = *reinterpret_cast<const float4*>(slot + 4);
           v[0] += x0.x; v[1] += x0.y; v[2] += x0.z; v[3] += x0.w;
           v[4] += x1.x; v[5] += x1.y; v[6] += x1.z; v[7] += x1.w;
         } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float* src = red + (col + j) * kTileA + r0;
-            v[j] += (nslice == 1) ? *src : ld_dsmem_f32(src, s);
-          }
+          for (int j = 0; j < 8; ++j) v[j] += slot[j * kTileA];
         }
       }
     };
@@ -854,8 +888,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   }
 
   if (threadIdx.x == 64) TRACE(10);
-  // Non-leader CTAs must stay resident until the leader has read their shared memory.
-  if (cluster_split || pair_x) cluster_sync_all();
   if (threadIdx.x == 64) TRACE(11);
 
   // ------------------------------------------------------------ teardown
@@ -865,6 +897,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  STEP_TRACE_END(p);
 }
 
 // ---------------------------------------------------------------- host side
@@ -973,6 +1006,48 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     }
   }
   const unsigned cluster_x = pp.fe.mode == SLLM_FD_SILU_QUANT + 1 ? 2u : 1u;
+#ifdef SLLM_TRACE
+  {
+    // development aid: how many clusters of this shape the device holds at once, printed once per shape
+    static unsigned seen[64];
+    static int n_seen = 0;
+    const unsigned key = (BN << 16) | (cluster_x << 8) | (pp.cluster_split ? grid.z : 1u) | (kComm ? 1u << 30 : 0u);
+    bool have = false;
+    for (int i = 0; i < n_seen; ++i) have = have || seen[i] == key;
+    if (!have && n_seen < 64) {
+      seen[n_seen++] = key;
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = grid;
+      probe.blockDim = dim3(gemm_threads(BN));
+      probe.dynamicSmemBytes = smem;
+      cudaLaunchAttribute pa[1];
+      pa[0].id = cudaLaunchAttributeClusterDimension;
+      pa[0].val.clusterDim.x = cluster_x;
+      pa[0].val.clusterDim.y = 1;
+      pa[0].val.clusterDim.z = pp.cluster_split ? grid.z : 1u;
+      probe.attrs = pa;
+      probe.numAttrs = 1;
+      int n_clusters = -1, per_sm = -1;
+      if (cudaOccupancyMaxActiveClusters(&n_clusters, gemm_tcgen05_kernel<BN, kScaled, kComm>, &probe) != cudaSuccess) cudaGetLastError();
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tcgen05_kernel<BN, kScaled, kComm>, gemm_threads(BN), smem);
+      fprintf(stderr, "[trace] gemm BN=%d cluster=(%u,1,%u) smem=%zu grid=(%u,%u,%u): max active clusters %d, CTAs per SM %d\n", BN,
+              cluster_x, pp.cluster_split ? grid.z : 1u, smem, grid.x, grid.y, grid.z, n_clusters, per_sm);
+      cudaFuncAttributes fa;
+      cudaFuncGetAttributes(&fa, gemm_tcgen05_kernel<BN, kScaled, kComm>);
+      cudaDeviceProp dp;
+      cudaGetDeviceProperties(&dp, 0);
+      fprintf(stderr, "[trace]   regs %d static smem %zu max dyn %d max threads %d | SM: regs %d smem %zu reserved/block %zu max blocks %d\n",
+              fa.numRegs, fa.sharedSizeBytes, fa.maxDynamicSharedSizeBytes, fa.maxThreadsPerBlock, dp.regsPerMultiprocessor,
+              dp.sharedMemPerMultiprocessor, dp.reservedSharedMemPerBlock, dp.maxBlocksPerMultiProcessor);
+      for (int th : {192, 224, 256})
+        for (size_t sm : {size_t(0), size_t(65536), size_t(104912), size_t(112000), size_t(115000)}) {
+          int n = -1;
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_tcgen05_kernel<BN, kScaled, kComm>, th, sm);
+          fprintf(stderr, "[trace]   threads %d smem %zu -> %d CTAs/SM\n", th, sm, n);
+        }
+    }
+  }
+#endif
   if (launch_kernel_cluster(gemm_tcgen05_kernel<BN, kScaled, kComm>, grid, dim3(gemm_threads(BN)), smem, stream, cluster_x,
                             pp.cluster_split ? grid.z : 1u, ta, tb, pp) != cudaSuccess) {
     cudaGetLastError();
@@ -1087,6 +1162,7 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
   p.cluster_split = (pow2 && bn % splits == 0 && (transpose_out || bn / splits >= 8) && !g_disable_cluster_split) ? 1 : 0;
   p.const_operand = transpose_out ? 1 : 2;   // swap-AB: A is the weight matrix, else B is
   p.early_trigger = gemm_early_trigger();
+  STEP_TRACE_ASSIGN(p, 1);
   p.scale_a = scale_a; p.scale_b = scale_b;
   p.y = static_cast<__nv_bfloat16*>(y);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
@@ -1129,6 +1205,24 @@ static int gemm_impl(const void* a, const void* b, void* y, const float* scale_a
 }
 
 #ifdef SLLM_TRACE
+static unsigned long long* g_step_buf = nullptr;
+static int g_step_cap = 0, g_step_next = 0;
+namespace sllm {
+unsigned long long* step_trace_next(int kind) {
+  if (!g_step_buf || g_step_next >= g_step_cap) return nullptr;
+  unsigned long long* rec = g_step_buf + 4 * static_cast<size_t>(g_step_next++);
+  const unsigned long long k = static_cast<unsigned long long>(kind);
+  cudaMemcpy(rec + 3, &k, sizeof(k), cudaMemcpyHostToDevice);
+  return rec;
+}
+}  // namespace sllm
+// dev_buf: records * 4 64-bit words on the device (null switches the timeline off); numbering restarts at 0.
+SLLM_EXPORT void sllm_step_trace_set(void* dev_buf, int records) {
+  g_step_buf = static_cast<unsigned long long*>(dev_buf);
+  g_step_cap = records;
+  g_step_next = 0;
+}
+SLLM_EXPORT int sllm_step_trace_count() { return g_step_next; }
 SLLM_EXPORT int sllm_gemm_read_trace(unsigned long long* out32) {
   return cudaMemcpyFromSymbol(out32, g_trace, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : 5;
 }

@@ -94,51 +94,105 @@ __global__ void moe_route_kernel(const __nv_bfloat16* __restrict__ logits, int l
   }
 }
 
-// Single CTA.  Counts per local expert in shared memory, exclusive scan, then placement; assignments keep token
-// order inside an expert (two passes over the assignments in index order, the second with a running cursor per
-// expert owned by one thread), so the layout is deterministic.
-__global__ void moe_permute_kernel(const int* __restrict__ idx, const float* __restrict__ w, int tokens, int top_k,
-                                   int e_lo, int e_hi, int* __restrict__ tok_off, int* __restrict__ perm_src,
-                                   int* __restrict__ perm_dst, float* __restrict__ perm_w) {
+// Single CTA of kPermuteThreads threads.  Counts per local expert in shared memory, exclusive scan, then a stable
+// placement chunk by chunk: inside a chunk of one assignment per thread, lanes that share an expert find each
+// other with match.any and rank themselves by lane, each warp's count per expert is scanned over the warps in
+// order, and the running cursor of the expert advances by the chunk's total.  Assignments therefore keep their
+// index order inside an expert (the layout is deterministic) at O(assignments / threads) steps instead of one
+// serial walk per expert.
+constexpr int kPermuteThreads = 1024;
+constexpr int kPermuteWarps = kPermuteThreads / 32;
+
+__global__ void __launch_bounds__(kPermuteThreads)
+moe_permute_kernel(const int* __restrict__ idx, const float* __restrict__ w, int tokens, int top_k, int e_lo, int e_hi,
+                   int* __restrict__ tok_off, int* __restrict__ perm_src, int* __restrict__ perm_dst,
+                   float* __restrict__ perm_w) {
   pdl_wait();
   pdl_trigger();
-  __shared__ int counts[kMaxExperts + 1];
+  __shared__ int cursor[kMaxExperts + 1];
+  __shared__ int wcount[kPermuteWarps * kMaxExperts];   // [warp][local expert] counts, then start offsets, of a chunk
   const int n_local = e_hi - e_lo;
   const int total = tokens * top_k;
-  for (int i = threadIdx.x; i <= n_local; i += blockDim.x) counts[i] = 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i <= n_local; i += blockDim.x) cursor[i] = 0;
   __syncthreads();
   for (int a = threadIdx.x; a < total; a += blockDim.x) {
     const int e = idx[a];
-    if (e >= e_lo && e < e_hi) atomicAdd(&counts[e - e_lo], 1);
+    if (e >= e_lo && e < e_hi) atomicAdd(&cursor[e - e_lo], 1);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
     for (int e = 0; e < n_local; ++e) {
-      const int c = counts[e];
-      counts[e] = run;
+      const int c = cursor[e];
+      cursor[e] = run;
       tok_off[e] = run;
       run += c;
     }
-    counts[n_local] = run;
+    cursor[n_local] = run;
     tok_off[n_local] = run;
   }
-  __syncthreads();
-  // thread e walks all assignments in order and places those of its expert: stable and race free
-  for (int e = threadIdx.x; e < n_local; e += blockDim.x) {
-    int cur = counts[e];
-    for (int a = 0; a < total; ++a) {
-      if (idx[a] == e + e_lo) {
-        perm_src[cur] = a / top_k;
-        perm_w[cur] = w[a];
-        perm_dst[a] = cur;
-        ++cur;
-      }
+  for (int base = 0; base < total; base += kPermuteThreads) {
+    for (int i = threadIdx.x; i < kPermuteWarps * n_local; i += blockDim.x) wcount[i] = 0;
+    __syncthreads();                                   // also orders the scan above / the previous chunk's reads
+    const int a = base + threadIdx.x;
+    int e = -1;
+    if (a < total) {
+      e = idx[a] - e_lo;
+      if (e < 0 || e >= n_local) e = -1;
     }
+    // lanes without a local expert get a key of their own, so they match nobody
+    const unsigned peers = __match_any_sync(0xffffffffu, e >= 0 ? e : (0x40000000 | lane));
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) wcount[warp * n_local + e] = __popc(peers);
+    __syncthreads();
+    for (int x = threadIdx.x; x < n_local; x += blockDim.x) {
+      int run = cursor[x];
+      for (int wv = 0; wv < kPermuteWarps; ++wv) {
+        const int c = wcount[wv * n_local + x];
+        wcount[wv * n_local + x] = run;
+        run += c;
+      }
+      cursor[x] = run;
+    }
+    __syncthreads();
+    if (e >= 0) {
+      const int pos = wcount[warp * n_local + e] + rank;
+      perm_src[pos] = a / top_k;
+      perm_w[pos] = w[a];
+      perm_dst[a] = pos;
+    } else if (a < total) {
+      perm_dst[a] = -1;
+    }
+    __syncthreads();
   }
-  for (int a = threadIdx.x; a < total; a += blockDim.x) {
-    const int e = idx[a];
-    if (e < e_lo || e >= e_hi) perm_dst[a] = -1;
+}
+
+// Shared expert of the Qwen3.5 MoE layer: y[t, :] = a[t, :] + sigmoid(gate[t * ld_gate]) * b[t, :] (the always-on
+// expert's output joins the routed sum under a per-token sigmoid gate; reference:
+// native/hip/src/moe_expert_kernel.hip.cpp:134-174 computes the gate, :176 applies it in the combine).
+__global__ void moe_shared_add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                      const __nv_bfloat16* __restrict__ gate, int ld_gate, __nv_bfloat16* __restrict__ y,
+                                      int d) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const float g = 1.f / (1.f + __expf(-__bfloat162float(gate[static_cast<size_t>(t) * ld_gate])));
+  const uint4* pa = reinterpret_cast<const uint4*>(a + static_cast<size_t>(t) * d);
+  const uint4* pb = reinterpret_cast<const uint4*>(b + static_cast<size_t>(t) * d);
+  uint4* py = reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * d);
+  for (int i = threadIdx.x; i < d / 8; i += blockDim.x) {
+    const uint4 va = pa[i], vb = pb[i];
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&va);
+    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&vb);
+    uint4 o;
+    __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 fa = __bfloat1622float2(ha[j]), fb = __bfloat1622float2(hb[j]);
+      ho[j] = __floats2bfloat162_rn(fa.x + g * fb.x, fa.y + g * fb.y);
+    }
+    py[i] = o;
   }
 }
 
@@ -288,8 +342,21 @@ SLLM_EXPORT int sllm_moe_permute(const int* idx, const float* w, int tokens, int
   if (!idx || !w || !tok_off || !perm_src || !perm_dst || !perm_w || tokens <= 0 || top_k <= 0 || e_lo < 0 ||
       e_hi <= e_lo || e_hi - e_lo > kMaxExperts)
     return SLLM_ERR_INVALID_ARGUMENT;
-  cudaError_t e = launch_kernel(moe_permute_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), 1u, idx, w,
-                                tokens, top_k, e_lo, e_hi, tok_off, perm_src, perm_dst, perm_w);
+  if (static_cast<long long>(tokens) * top_k > (1LL << 30)) return SLLM_ERR_UNSUPPORTED_SHAPE;
+  cudaError_t e = launch_kernel(moe_permute_kernel, dim3(1), dim3(kPermuteThreads), 0, static_cast<cudaStream_t>(stream), 1u,
+                                idx, w, tokens, top_k, e_lo, e_hi, tok_off, perm_src, perm_dst, perm_w);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+// y = a + sigmoid(gate[t * ld_gate]) * b over [tokens, d] bf16 rows (y may alias a); d a multiple of 8.
+SLLM_EXPORT int sllm_moe_shared_add(const void* a, const void* b, const void* gate, int ld_gate, void* y, int tokens, int d,
+                                    void* stream) {
+  if (!a || !b || !gate || !y || tokens <= 0 || d <= 0 || (d % 8) || ld_gate <= 0) return SLLM_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(y)) & 15)
+    return SLLM_ERR_ALIGNMENT;
+  cudaError_t e = launch_kernel(moe_shared_add_kernel, dim3(tokens), dim3(128), 0, static_cast<cudaStream_t>(stream), 1u,
+                                static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
+                                static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__nv_bfloat16*>(y), d);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 

@@ -151,7 +151,13 @@ def gemma4_shape(layers: int = 48) -> ModelConfig:
                        post_norms=True, max_context=8192)
 
 
+def _qwen35_moe():
+    from .moe import qwen35_moe_shape
+    return qwen35_moe_shape()
+
+
 NAMED = {
+    "qwen35-moe": _qwen35_moe,
     "tiny-llama": tiny_llama,
     "llama3-8b": llama3_8b,
     "llama3-70b": llama3_70b,

@@ -33,6 +33,10 @@ class MoeLayerWeights:
     router: LinearWeight               # [E, d] bf16
     gate_up: W4Weight                  # local experts, [2 * expert_ffn, d] each
     down: W4Weight                     # local experts, [d, expert_ffn] each
+    # always-on shared expert (Qwen3.5 MoE): dense gated MLP whose output joins the routed sum under a per-token
+    # sigmoid gate; the gate vector rides as row n_experts of `router` (rows above it are zero padding)
+    shared_gate_up: Optional[LinearWeight] = None     # [2 * shared_expert_ffn, d]
+    shared_down: Optional[LinearWeight] = None        # [d, shared_expert_ffn]
 
 
 @dataclass
@@ -86,7 +90,14 @@ def init_random_moe_weights(cfg: ModelConfig, device, seed: int = 0, tp_size: in
             if e_lo <= e < e_hi:
                 gu_local.append(gu)
                 dn_local.append(dn)
-        layers.append(MoeLayerWeights(
+        shared = {}
+        if cfg.shared_expert_ffn > 0:
+            fs = cfg.shared_expert_ffn
+            sgu, sdn, sg = rnd((2 * fs, d)), rnd((d, fs)), rnd((1, d))
+            router = torch.cat([router, sg, torch.zeros((7, d), dtype=router.dtype, device=router.device)], dim=0)
+            shared = dict(shared_gate_up=LinearWeight("dense", sgu.to(dt).contiguous().to(device)),
+                          shared_down=LinearWeight("dense", sdn.to(dt).contiguous().to(device)))
+        layers.append(MoeLayerWeights(**shared, 
             attn_norm=torch.ones(d, dtype=dt, device=device),
             qkv=LinearWeight("dense", qkv.to(dt).contiguous().to(device)),
             o=LinearWeight("dense", wo[:, tp_rank * qs:(tp_rank + 1) * qs].to(dt).contiguous().to(device)),
@@ -135,9 +146,13 @@ class MoeModel:
             h = self.tp.row_linear(a, lw.o, h)
             x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
             logits = ops.linear(x, lw.router)
-            idx, rw = M.route(logits, cfg.top_k)
+            idx, rw = M.route(logits[:, :cfg.n_experts], cfg.top_k)
             yp, perm_dst = M.experts_forward(x, idx, rw, lw.gate_up, lw.down, cfg.act, self.e_lo, self.e_hi)
             h = self.ep.combine(yp, perm_dst, h)
+            if lw.shared_gate_up is not None:
+                # replicated on every rank: the shared expert is a few percent of a layer's bytes
+                sh = ops.linear(ops.gated_act(ops.linear(x, lw.shared_gate_up), cfg.act), lw.shared_down)
+                h = M.shared_add(h, sh, logits[:, cfg.n_experts])
         return h
 
     def _keep(self, h: torch.Tensor) -> torch.Tensor:
@@ -158,6 +173,23 @@ class MoeModel:
 
     def greedy(self, b: ForwardBatch, cache) -> torch.Tensor:
         return self.tp.argmax(self.logits(self._keep(self.hidden(b, cache)), b), self.w.vocab_offset)
+
+
+def qwen35_moe_shape(layers: int = 40) -> ModelConfig:
+    """Qwen3.5-MoE-class layer geometry as the reference's expert kernels fix it (hidden 2048, 256 experts top-8,
+    expert and shared-expert width 512: native/hip/src/moe_expert_kernel_internal.hpp:10-13), with plain GQA
+    attention in every layer."""
+    return ModelConfig(name="qwen35-moe", family="moe", n_layers=layers, d_model=2048, n_heads=16, n_kv_heads=2, head_dim=128,
+                       ffn=512, vocab=151936, rope_theta=1e7, rms_eps=1e-6, weight_format="bf16", kv_format="bf16",
+                       n_experts=256, top_k=8, expert_ffn=512, shared_expert_ffn=512, expert_format="mxfp4",
+                       max_context=8192)
+
+
+def tiny_shared_moe() -> ModelConfig:
+    """CPU-checkable Qwen3.5-MoE-style layer: 256 experts top-8 plus the gated shared expert, small widths."""
+    return ModelConfig(name="tiny-shared-moe", family="moe", n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64,
+                       ffn=128, vocab=1024, weight_format="bf16", kv_format="bf16", n_experts=256, top_k=8, expert_ffn=128,
+                       shared_expert_ffn=128, expert_format="mxfp4", max_context=256)
 
 
 def tiny_moe() -> ModelConfig:

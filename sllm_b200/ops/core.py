@@ -120,7 +120,8 @@ _SM_COUNT = 148
 # GEMM
 # ------------------------------------------------------------------------------------------------
 def _gemm_plan(m: int, n: int, k_blocks: int):
-    """(swap_ab, bn, splits, stages) for Y[m, n]."""
+    """(swap_ab, bn, splits, stages) for Y[m, n].  Stage counts keep a CTA near 105 KB of shared memory so that two
+    CTAs share an SM (deeper pipelines that fill the SM with one CTA measured a third slower on the decode shapes)."""
     if m <= 128:
         bn = 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128
         tiles = (n + 127) // 128

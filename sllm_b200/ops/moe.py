@@ -19,6 +19,7 @@ _SIGS = {
     "sllm_moe_permute": (I, [P, P, I, I, I, I, P, P, P, P, P]),
     "sllm_moe_gather": (I, [P, I, P, P, I, P, I, I, P]),
     "sllm_moe_combine": (I, [P, P, I, P, P, I, I, P]),
+    "sllm_moe_shared_add": (I, [P, P, P, I, P, I, I, P]),
     "sllm_moe_combine_allreduce": (I, [P, P, I, I, P, P, I, P, P, I, I, I, L, I, P, P, P]),
 }
 
@@ -108,6 +109,19 @@ def combine(yp: torch.Tensor, perm_dst: torch.Tensor, residual: Optional[torch.T
     y = torch.empty((t, d), dtype=torch.bfloat16, device=yp.device)
     rc = _k().sllm_moe_combine(_p(yp), _p(perm_dst), k, _p(residual), _p(y), t, d, _stream())
     _lib.check(rc, "moe_combine")
+    return y
+
+
+def shared_add(a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """a + sigmoid(gate) * b with one gate logit per row: a, b [T, d]; gate [T] (any stride, e.g. a column of the
+    router logits)."""
+    if not a.is_cuda:
+        out = a.float() + torch.sigmoid(gate.float()).unsqueeze(1) * b.float()
+        return out if a.dtype == torch.float32 else out.to(torch.bfloat16)
+    from .core import _p, _stream
+    y = torch.empty_like(a)
+    rc = _k().sllm_moe_shared_add(_p(a), _p(b), _p(gate), gate.stride(0), _p(y), a.shape[0], a.shape[1], _stream())
+    _lib.check(rc, "moe_shared_add")
     return y
 
 

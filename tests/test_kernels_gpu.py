@@ -414,7 +414,7 @@ def test_gemm_w4_grouped(fmt):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("t,e,k", [(1, 8, 2), (37, 128, 4), (64, 32, 8), (200, 128, 4)])
+@pytest.mark.parametrize("t,e,k", [(1, 8, 2), (37, 128, 4), (64, 32, 8), (200, 128, 4), (129, 256, 8), (700, 256, 8)])
 def test_moe_route_permute_gather_combine(t, e, k):
     from sllm_b200.ops import moe as M
     torch.manual_seed(t)
@@ -438,6 +438,56 @@ def test_moe_route_permute_gather_combine(t, e, k):
     y = M.combine(xp, got[2], res)
     yc = M.combine(xp.cpu().float(), want[2], res.cpu().float())
     assert rel_err(y.float().cpu(), yc) < 5e-3
+
+
+@pytest.mark.gpu
+def test_moe_permute_all_local_many_chunks():
+    """Every expert local, several thousand assignments (many 1024-wide chunks): stable order inside each expert."""
+    from sllm_b200.ops import moe as M
+    torch.manual_seed(5)
+    t, e, k = 1500, 256, 8
+    idx = torch.stack([torch.randperm(e)[:k] for _ in range(t)]).int()
+    idx[:, 0] = 7                                           # one crowded expert
+    w = torch.rand(t, k)
+    tok_off, src, dst, pw = M.permute(idx.to(DEV), w.to(DEV), 0, e)
+    flat = idx.reshape(-1)
+    order = torch.sort(flat.long(), stable=True).indices    # assignments grouped by expert, index order inside
+    assert torch.equal(src.cpu().long(), order // k)
+    assert torch.equal(pw.cpu(), w.reshape(-1)[order])
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel())
+    assert torch.equal(dst.cpu().reshape(-1).long(), inv)
+    counts = torch.bincount(flat.long(), minlength=e)
+    assert torch.equal(tok_off.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]))
+
+
+@pytest.mark.gpu
+def test_shared_expert_moe_gpu_matches_cpu():
+    """256-way routing with top-8 and the sigmoid-gated shared expert (Qwen3.5 MoE layer), small widths."""
+    from sllm_b200.cache.paged import PagedKVCache
+    from sllm_b200.engine.engine import Engine
+    from sllm_b200.models import moe as MOE
+    from sllm_b200.ops import moe as M
+    a = torch.randn(11, 264, device=DEV).bfloat16()
+    b = torch.randn(11, 264, device=DEV).bfloat16()
+    gate = torch.randn(11, 40, device=DEV).bfloat16()
+    got = M.shared_add(a, b, gate[:, 33])
+    want = M.shared_add(a.cpu().float(), b.cpu().float(), gate[:, 33].cpu().float())
+    assert rel_err(got.float().cpu(), want) < 5e-3
+    cfg = MOE.tiny_shared_moe()
+
+    def engine(dev):
+        w = MOE.init_random_moe_weights(cfg, dev, seed=4)
+        m = MOE.MoeModel(cfg, w)
+        return Engine(cfg, m, PagedKVCache(cfg, 64, torch.device(dev), kv_heads=m.local_kv_heads), dev, max_batch=4)
+
+    prompts = [list(range(3, 40)), [9, 8, 7, 6]]
+    g, c = engine(DEV), engine("cpu")
+    lg = g.prefill([g.new_sequence(p) for p in prompts], sample=False).float().cpu()
+    lc = c.prefill([c.new_sequence(p) for p in prompts], sample=False).float()
+    assert rel_err(lg, lc) < 3e-2
+    assert all(len(o) == 6 for o in g.generate(prompts, 6))
+    assert ops.device_status(torch.device(DEV)) == 0
 
 
 @pytest.mark.gpu

@@ -92,3 +92,33 @@ def test_expert_parallel_partials_add_up():
         yp_r, dst_r = M.experts_forward(x, idx, rw, parts[r].gate_up, parts[r].down, cfg.act, r * 4, r * 4 + 4)
         acc += M.combine(yp_r, dst_r, None)
     assert torch.allclose(acc, want, rtol=1e-5, atol=1e-6)
+
+
+def test_shared_expert_and_256_way_routing():
+    """Qwen3.5-MoE layer: top-8 of 256 experts plus a dense shared expert under a per-token sigmoid gate
+    (reference: native/hip/src/moe_expert_kernel.hip.cpp:134-174)."""
+    cfg = MOE.tiny_shared_moe()
+    cfg.weight_format, cfg.kv_format = "fp32", "fp32"
+    eng = _engine(cfg)
+    lw = eng.model.w.layers[0]
+    assert lw.router.w.shape[0] == cfg.n_experts + 8 and lw.shared_gate_up.w.shape == (2 * cfg.shared_expert_ffn, cfg.d_model)
+    prompts = [list(range(5, 30)), [7, 8, 9]]
+    out = eng.generate(prompts, 5)
+    assert eng.generate([prompts[0] + out[0][:2]], 3)[0] == out[0][2:5]
+    # one block against a direct restatement
+    torch.manual_seed(1)
+    x = torch.randn(4, cfg.d_model)
+    logits = x @ lw.router.w.float().t()
+    idx, rw = M.route(logits[:, :cfg.n_experts], cfg.top_k)
+    assert idx.shape == (4, 8) and int(idx.max()) < 256
+    yp, dst = M.experts_forward(x, idx, rw, lw.gate_up, lw.down, cfg.act, 0, cfg.n_experts)
+    routed = M.combine(yp, dst, None)
+    gu = x @ lw.shared_gate_up.w.float().t()
+    fs = cfg.shared_expert_ffn
+    sh = (torch.nn.functional.silu(gu[:, :fs]) * gu[:, fs:]) @ lw.shared_down.w.float().t()
+    want = routed + torch.sigmoid(x @ lw.router.w.float()[cfg.n_experts]).unsqueeze(1) * sh
+    got = M.shared_add(routed, sh, logits[:, cfg.n_experts])
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-5)
+    from sllm_b200.models import config as MC
+    big = MC.NAMED["qwen35-moe"]()
+    assert (big.n_experts, big.top_k, big.shared_expert_ffn) == (256, 8, 512)
