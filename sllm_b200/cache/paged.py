@@ -148,7 +148,10 @@ class PagedKVCache:
     """Device pages for every layer + the pool.  ``layer(i)`` gives the tensors an op needs."""
 
     def __init__(self, cfg: ModelConfig, num_pages: int, device: torch.device, kv_heads: Optional[int] = None,
-                 k_static: float = 0.0, v_static: float = 0.0):
+                 k_static: float = 0.0, v_static: float = 0.0, static_scales: Optional[list] = None):
+        """``static_scales``: [(k, v)] decode scales per layer for the `fp8-static` format (a quantised checkpoint
+        binds one pair per layer: reference crates/sllm-core/src/quantized_model.rs:80-95); otherwise k_static /
+        v_static apply to every layer."""
         hkv = kv_heads if kv_heads is not None else cfg.n_kv_heads
         self.spec = KVSpec(cfg.n_layers, hkv, cfg.head_dim, cfg.page_size, cfg.kv_format)
         self.device = device
@@ -163,11 +166,17 @@ class PagedKVCache:
             self.scales = torch.ones((cfg.n_layers, 2, num_pages, hkv, cfg.page_size), dtype=torch.float32,
                                      device=device)
         self.k_static, self.v_static = (k_static or 1.0, v_static or 1.0) if fmt == "fp8-static" else (0.0, 0.0)
+        if static_scales is None and fmt == "fp8-static" and cfg.kv_static_scales:
+            static_scales = [tuple(x) for x in cfg.kv_static_scales]     # the binding a converted checkpoint carries
+        if static_scales is not None:
+            if fmt != "fp8-static" or len(static_scales) != cfg.n_layers or any(k <= 0 or v <= 0 for k, v in static_scales):
+                raise ValueError("static_scales needs the fp8-static format and one positive (k, v) pair per layer")
+        per_layer = static_scales or [(self.k_static, self.v_static)] * cfg.n_layers
         self._layers = [
             KVLayer(self.values[l, 0], self.values[l, 1],
                     None if self.scales is None else self.scales[l, 0],
                     None if self.scales is None else self.scales[l, 1],
-                    self.fp8, cfg.page_size, self.k_static, self.v_static)
+                    self.fp8, cfg.page_size, float(per_layer[l][0]), float(per_layer[l][1]))
             for l in range(cfg.n_layers)
         ]
 

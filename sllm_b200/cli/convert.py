@@ -4,6 +4,10 @@ Kinds:
   random-llama   seeded random-init weights of a named shape (`--artifact llama3-8b`), for benchmarks and tests
   hf-llama       a Llama-style Hugging Face checkpoint (config.json + safetensors) from a directory that is first
                  verified against its model lock (`--lock lock.json --cache DIR`)
+  mixed-precision  a compressed-tensors checkpoint with FP8 channel-scaled attention projections, NVFP4 MLP
+                 projections and per-layer static FP8 KV scales (formats/quantized_model.py); same lock verification.
+                 The file keeps the FP8 matrices block-scaled, the NVFP4 matrices as GGML type-40 blocks with their
+                 outer scales, and the KV scales in the model configuration
 `--weight-format bf16|fp8` selects the resident encoding (fp8 = E4M3FN with FP32 scales per 1x128 block).
 `--dry-run` validates inputs and prints the plan without writing.  (Reference: crates/sllm-server/src/bin/
 sllm-convert-gguf.rs flags --kind --lock --cache --artifact --manifest --output --derived-lock
@@ -17,7 +21,7 @@ import sys
 
 from .common import CliError, StrictParser, emit, run_main
 
-KINDS = ("random-llama", "hf-llama")
+KINDS = ("random-llama", "hf-llama", "mixed-precision")
 
 
 def _hf_config(raw: dict, weight_format: str):
@@ -148,7 +152,16 @@ def main(argv=None) -> int:
             except (OSError, ML.ModelLockError) as exc:
                 raise CliError(f"source verification failed: {exc}", 3) from None
             fps = [lock.fingerprint]
-            cfg = _hf_config(json.loads(cache.read("config.json", 1 << 20)), a.weight_format)
+            raw_cfg = json.loads(cache.read("config.json", 1 << 20))
+            if a.kind == "mixed-precision":
+                text = dict(raw_cfg.get("text_config") or raw_cfg)
+                text.setdefault("model_type", "llama")
+                if text["model_type"] not in ("llama", "mistral", "qwen2", "qwen3"):
+                    text["model_type"] = "llama"          # the decoder stack of a multimodal wrapper
+                cfg = _hf_config(text, "mixed-fp8-nvfp4")
+                cfg.kv_format, cfg.tie_embeddings = "fp8-static", True
+            else:
+                cfg = _hf_config(raw_cfg, a.weight_format)
             if "tokenizer.json" in cache.fds:
                 tokenizer_json = cache.read("tokenizer.json").decode("utf-8")
             if "chat_template.jinja" in cache.fds:
@@ -167,6 +180,20 @@ def main(argv=None) -> int:
         if a.kind == "random-llama":
             dev = "cuda" if torch.cuda.is_available() else "cpu"
             w = init_random_weights(cfg, dev, seed=a.seed)
+        elif a.kind == "mixed-precision":
+            from ..formats import quantized_model as QM
+            try:
+                header, _ = QM.read_safetensors_header(os.path.join(cache.root, "model.safetensors"))
+                prefix = "model.language_model" if any(n.startswith("model.language_model.") for n in header) else "model"
+                geo = QM.ModelGeometry(cfg.n_layers, cfg.d_model, cfg.q_size, cfg.kv_size, cfg.ffn, cfg.vocab, prefix)
+                qm = QM.open_mixed_precision_checkpoint(cache.root, geo)
+                w, kv_scales = QM.load_resident(qm, cfg, "cpu")
+            except (OSError, QM.QuantizedModelError) as exc:
+                raise CliError(f"quantised checkpoint rejected: {exc}", 3) from None
+            cfg.kv_static_scales = [[float(k), float(v)] for k, v in kv_scales]
+            plan["recipe"] = qm.recipe.to_dict()
+            plan["recipe_digest"] = qm.digest
+            cache.close()
         else:
             w = _load_hf(cache, cfg)
             cache.close()

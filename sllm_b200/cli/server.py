@@ -29,6 +29,9 @@ def build_parser() -> StrictParser:
     p.add_argument("--models", default=None, help="model manifest for dynamic multi-model serving")
     p.add_argument("--max-resident-models", type=int, default=4)
     p.add_argument("--cpu", action="store_true")
+    p.add_argument("--allow-cpu-fallback", action="store_true",
+                   help="GPU serving only: let an op that is handed a CPU tensor compute its PyTorch oracle (recorded as a "
+                        "fallback) instead of failing the request")
     # listener / security
     p.add_argument("--listen", default="127.0.0.1:8080")
     p.add_argument("--api-key-env")
@@ -127,6 +130,9 @@ def make_backend(a, gguf: str, derived_lock: str, alias: str, overrides=None):
                              context_length=o.get("context_length") or a.context_length, cpu=a.cpu)
     tp, ctrl = getattr(a, "_tp", None), getattr(a, "_ctrl", None)
     eng, tok, g, lock = open_model(src, max_batch=o.get("max_batch") or a.max_batch, tp=tp)
+    if not a.cpu and not a.allow_cpu_fallback:
+        from ..ops import _lib
+        _lib.set_fail_closed(True)             # serving from a GPU: a tensor that strays to the CPU is an error
     if tp is None and not a.cpu:
         eng.warm_up(greedy_modes=(False,))     # capture the decode graphs before the first request, not during it
     if tp is not None:
@@ -250,6 +256,9 @@ def serve(a) -> int:
     audit = {"event": "shutdown_audit", "cancelled_at_shutdown": 0, "models": {}}
     for alias, b in backends.items():
         r = b.shutdown(a.shutdown_timeout_seconds)
+        eng = getattr(b, "engine", None)
+        if eng is not None and hasattr(eng, "shutdown_report"):
+            r["engine"] = eng.shutdown_report()       # memory by category, high-water mark, launches, fallbacks, quarantine
         audit["models"][alias] = r
         audit["cancelled_at_shutdown"] += r.get("cancelled_at_shutdown", 0)
     if dyn is not None:

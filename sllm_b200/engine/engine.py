@@ -44,6 +44,16 @@ class Sequence:
         return len(self.tokens) - len(self.prompt)
 
 
+class EngineQuarantined(RuntimeError):
+    """The engine gave up on the device (a bounded device wait ran out): it computes nothing further."""
+
+
+# Buffers of quarantined engines whose device work could not be proven complete: kept referenced for the life of the
+# process so that their memory is never handed to anyone else (reference: the "unowned cleanup state" of
+# native/hip/src/runtime_impl.hpp, where memory of a failed stream is parked instead of freed).
+_PARKED: list = []
+
+
 class Engine:
     GRAPH_BATCHES = (1, 2, 4, 8, 16, 32, 64, 128)
 
@@ -93,9 +103,91 @@ class Engine:
         # sequence (consumed by a multi-token-prediction head through take_hidden)
         self.keep_hidden = False
         self._hidden_log: dict = {}
+        self.quarantine: Optional[dict] = None     # set once by _enter_quarantine; the engine then refuses all work
+        self._mem_mark = torch.cuda.memory_allocated(self.device) if self.is_cuda else 0
+
+    # ------------------------------------------------------------------ failure containment and accounting
+    def _guard(self) -> None:
+        if self.quarantine is not None:
+            raise EngineQuarantined(f"engine is quarantined: {self.quarantine['reason']}")
+
+    def _enter_quarantine(self, reason: str, device_status: int = 0) -> None:
+        """Stops the engine for good.  Captured graphs are dropped; the device is given one synchronize to prove that
+        nothing of this engine is still running: only then may `release` free its memory, otherwise the buffers are
+        parked for the life of the process."""
+        if self.quarantine is not None:
+            return
+        completed = True
+        if self.is_cuda:
+            try:
+                torch.cuda.synchronize(self.device)
+            except RuntimeError:
+                completed = False
+        self._graphs.clear()
+        self.quarantine = {"reason": reason, "device_status": int(device_status), "work_completed": completed,
+                           "steps": self._steps}
+
+    def release(self) -> dict:
+        """Drops the engine's device memory (KV pages, staging) when that is safe; returns what happened to it."""
+        cache_bytes = self.cache.values.numel() * self.cache.values.element_size() if hasattr(self.cache, "values") else 0
+        if self.quarantine is not None and not self.quarantine["work_completed"]:
+            _PARKED.append((self.cache, self.model, self._graphs))
+            return {"freed_bytes": 0, "parked_bytes": cache_bytes}
+        self._graphs.clear()
+        if hasattr(self.cache, "values"):
+            self.cache.values = self.cache.values.new_empty(0)
+            if getattr(self.cache, "scales", None) is not None:
+                self.cache.scales = self.cache.scales.new_empty(0)
+            self.cache._layers = []
+        if self.quarantine is None:
+            self.quarantine = {"reason": "released", "device_status": 0, "work_completed": True, "steps": self._steps}
+        return {"freed_bytes": cache_bytes, "parked_bytes": 0}
+
+    def accounting(self) -> dict:
+        """Bytes by category, and the allocator's high-water mark since the engine was built (reference: the session
+        allocation categories and high-water of crates/sllm-core/src/execution.rs)."""
+        def nbytes(t):
+            return 0 if t is None else t.numel() * t.element_size()
+
+        def weight_bytes(obj, seen, depth=0):
+            total = 0
+            if isinstance(obj, torch.Tensor):
+                if obj.data_ptr() not in seen:
+                    seen.add(obj.data_ptr())
+                    total += nbytes(obj)
+            elif isinstance(obj, (list, tuple)):
+                total += sum(weight_bytes(x, seen, depth + 1) for x in obj)
+            elif hasattr(obj, "__dict__") and depth < 6:
+                total += sum(weight_bytes(v, seen, depth + 1) for v in vars(obj).values())
+            return total
+
+        cache = self.cache
+        staging = sum(nbytes(getattr(self, n)) for n in ("d_tokens", "d_positions", "d_kv_lens", "d_seq_index", "d_table", "d_out",
+                                                        "d_slots", "d_row_off", "d_rope_delta", "d_rope3", "d_logits"))
+        pinned = sum(nbytes(getattr(self, n)) for n in ("h_tokens", "h_positions", "h_table", "h_out", "h_slots", "h_rope_delta"))
+        out = {"weights": weight_bytes(self.model.w, set()),
+               "kv_pages": nbytes(getattr(cache, "values", None)), "kv_scales": nbytes(getattr(cache, "scales", None)),
+               "device_staging": staging, "pinned_host": pinned, "captured_graphs": len(self._graphs)}
+        if self.is_cuda:
+            ws = ops.workspace(self.device)
+            out["kernel_workspace"] = sum(nbytes(getattr(ws, n, None)) for n in ("ws", "counters", "status"))
+            out["allocator_now"] = torch.cuda.memory_allocated(self.device)
+            out["allocator_high_water"] = torch.cuda.max_memory_allocated(self.device)
+            out["allocator_at_build"] = self._mem_mark
+        return out
+
+    def shutdown_report(self) -> dict:
+        """What a supervisor logs when the engine goes away: memory by category, launch and copy counters, fallbacks
+        and the quarantine record."""
+        from ..ops import _lib
+        return {"accounting": self.accounting(), "steps": self._steps, "kernel_launches": self.kernel_launches,
+                "h2d_bytes": self.h2d_bytes, "d2h_bytes": self.d2h_bytes, "fallbacks": _lib.fallbacks(),
+                "quarantine": self.quarantine,
+                "kv_pool": self.cache.pool.stats() if hasattr(self.cache, "pool") else None}
 
     # ------------------------------------------------------------------ sequences
     def new_sequence(self, prompt: list, user=None) -> Sequence:
+        self._guard()
         s = Sequence(prompt=list(prompt), user=user)
         s.seq_id = self.cache.pool.new_seq()
         if self.has_state:
@@ -203,6 +295,7 @@ class Engine:
         With ``one_chunk`` only the first ``chunk_tokens`` uncomputed tokens of every sequence run; a sequence is done
         when ``num_computed == len(tokens)`` afterwards, and only then is its row of the result meaningful (a
         scheduler interleaves the chunks of a long prompt with decode steps of the running requests)."""
+        self._guard()
         if embeds is not None or rope_pos3 is not None:
             if chunk_tokens:
                 raise ValueError("a multimodal prefill runs as one chunk")
@@ -451,6 +544,7 @@ class Engine:
     def decode(self, seqs: list, sample: bool = True):
         """One token for every sequence (the last token of each is the input).  Returns greedy next
         tokens, or logits [len(seqs), vocab] with sample=False."""
+        self._guard()
         n = len(seqs)
         if n > self.max_batch:
             raise ValueError("decode batch larger than max_batch")
@@ -512,7 +606,8 @@ class Engine:
             ws = ops.workspace(self.device)
             if int(ws.status[0].item()):
                 code = ops.device_status(self.device)
-                raise RuntimeError(f"device wait gave up (status {code}); engine must be drained")
+                self._enter_quarantine(f"a bounded device wait gave up (status {code})", code)
+                raise EngineQuarantined(f"device wait gave up (status {code}); the engine is quarantined")
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: list, max_new_tokens: int, eos: Optional[int] = None,

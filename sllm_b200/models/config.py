@@ -31,6 +31,7 @@ class ModelConfig:
     logit_softcap: float = 0.0
     weight_format: str = "bf16"       # fp32 | bf16 | fp8 | nvfp4 | mxfp4
     kv_format: str = "bf16"           # fp32 | bf16 | fp8 | fp8-static
+    kv_static_scales: Optional[list] = None   # fp8-static: [[k, v]] decode scales per layer (from a quantised checkpoint)
     page_size: int = 16
     max_context: int = 8192
     # sliding-window attention: window size and per-layer flags (True = windowed layer)

@@ -218,14 +218,17 @@ class LlamaModel:
         cfg, w = self.cfg, self.w
         hd = cfg.head_dim
         h = b.embeds if b.embeds is not None else ops.embedding(w.embed, b.tokens, cfg.embedding_scale)
-        qo = self.quant and hd == 128 and h.is_cuda
         for li, lw in enumerate(w.layers):
+            # activations are quantised for the projections that hold FP8 weights (a mixed-precision model has FP8
+            # attention and 4-bit MLP matrices)
+            q_attn, q_o, q_mlp, q_down = (x.kind == "fp8" for x in (lw.qkv, lw.o, lw.gate_up, lw.down))
+            qo = q_o and hd == 128 and h.is_cuda
             kv = cache.layer(li)
             ad = self.adapters
             if ad is not None and (ad.loras or ad.cvs):
                 h = self._adapter_layer(li, lw, h, b, kv, ad)
                 continue
-            x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
+            x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one, quant=q_attn)
             qkv = ops.linear(x, lw.qkv)
             if cfg.qk_norm or cfg.v_norm:
                 from ..ops import gdn as _g
@@ -237,7 +240,7 @@ class LlamaModel:
                                    pair_offset=poff)
             a = ops.attention(q, kv, b, self.hq, self.hkv, hd, window=cfg.layer_window(li), quant_out=qo,
                               qkv=qkv, sm_scale=cfg.attn_scale)
-            if self.quant and not qo:
+            if q_o and not qo:
                 a = ops.quant_fp8(a)
             if cfg.post_norms:
                 # sandwich norms: the block output is normalised before it joins the residual stream
@@ -245,9 +248,9 @@ class LlamaModel:
                 h = ops.elementwise("add", h, o)
             else:
                 h = self.tp.row_linear(a, lw.o, h)
-            x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
+            x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one, quant=q_mlp)
             gu = ops.linear(x, lw.gate_up)
-            act = ops.gated_act(gu, cfg.act, quant=self.quant)
+            act = ops.gated_act(gu, cfg.act, quant=q_down)
             if cfg.post_norms:
                 o = ops.rmsnorm(self.tp.row_linear(act, lw.down, None), lw.post_mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
                 h = ops.elementwise("add", h, o)
@@ -287,7 +290,7 @@ class LlamaModel:
         cfg, w = self.cfg, self.w
         if b.logit_rows is not None:
             h = h.index_select(0, b.logit_rows)
-        x = ops.rmsnorm(h, w.final_norm, cfg.rms_eps, cfg.norm_offset_one, quant=self.quant)
+        x = ops.rmsnorm(h, w.final_norm, cfg.rms_eps, cfg.norm_offset_one, quant=w.lm_head.kind == "fp8")
         lg = ops.linear(x, w.lm_head)
         if cfg.logit_softcap > 0:
             lg = ops.elementwise("tanh_softcap", lg, s=cfg.logit_softcap)

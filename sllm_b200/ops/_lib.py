@@ -53,6 +53,42 @@ def fallbacks() -> dict:
     return dict(FALLBACKS)
 
 
+# Fail-closed mode: with it on, an op that is handed a CPU tensor raises instead of computing the PyTorch oracle of
+# the op (the reference's host build of its native layer reports "unavailable" and never computes:
+# native/hip/src/host_stub.cpp).  On by SLLM_FAIL_CLOSED=1 or set_fail_closed(True); the server switches it on when it
+# serves from a GPU, so a tensor that strays to the CPU is an error there and not a silent slow path.
+_fail_closed = [None]
+
+
+def set_fail_closed(on: bool) -> None:
+    _fail_closed[0] = bool(on)
+
+
+def fail_closed() -> bool:
+    if _fail_closed[0] is None:
+        import os
+        _fail_closed[0] = os.environ.get("SLLM_FAIL_CLOSED", "0") == "1"
+    return _fail_closed[0]
+
+
+_cuda_present = [None]
+
+
+def on_cpu(t) -> bool:
+    """True when the op should take its CPU oracle branch for tensor ``t``.  Raises in fail-closed mode; on a machine
+    that has a GPU the detour is recorded as a fallback."""
+    if t.is_cuda:
+        return False
+    if fail_closed():
+        raise KernelError("CUDA kernels are required (fail-closed mode): the op was handed a CPU tensor")
+    if _cuda_present[0] is None:
+        import torch
+        _cuda_present[0] = torch.cuda.is_available()
+    if _cuda_present[0]:
+        note_fallback("cpu_oracle_on_gpu_host")
+    return True
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise KernelError(f"{what}: launch rejected ({STATUS_NAMES.get(rc, rc)})")

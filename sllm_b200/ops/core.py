@@ -153,7 +153,7 @@ def linear(x, w: LinearWeight, residual: Optional[torch.Tensor] = None) -> torch
     if w.kind == "w4":
         from .w4 import linear_w4
         return linear_w4(xd, w.w4, residual=residual)
-    if not xd.is_cuda:
+    if _lib.on_cpu(xd):
         if isinstance(x, QTensor):
             xf = ref.dequant_fp8_1x128(x.data, x.scale)
         else:
@@ -198,7 +198,7 @@ def _alloc_q(m: int, k: int, device) -> QTensor:
 
 
 def quant_fp8(x: torch.Tensor) -> QTensor:
-    if not x.is_cuda:
+    if _lib.on_cpu(x):
         return QTensor(*ref.quant_fp8_1x128(x))
     m, k = x.shape
     q = _alloc_q(m, k, x.device)
@@ -209,7 +209,7 @@ def quant_fp8(x: torch.Tensor) -> QTensor:
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, offset_one: bool = False, quant: bool = False):
     """RMSNorm over the last dim of [M, d]; quant=True returns a QTensor for a following FP8 GEMM."""
-    if not x.is_cuda:
+    if _lib.on_cpu(x):
         y = ref.rmsnorm(x, w, eps, offset_one)
         if x.dtype == torch.float32 and not quant:
             return y
@@ -230,7 +230,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, offset_one: bool = Fal
 
 def gated_act(x: torch.Tensor, act: str = "silu", quant: bool = False):
     """[M, 2I] (gate | up) -> act(gate) * up, optionally FP8-quantised for the down projection."""
-    if not x.is_cuda:
+    if _lib.on_cpu(x):
         y = ref.gated_act(x, act, round_intermediate=x.dtype != torch.float32)
         if x.dtype == torch.float32 and not quant:
             return y
@@ -252,7 +252,7 @@ def gated_act(x: torch.Tensor, act: str = "silu", quant: bool = False):
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-    if not table.is_cuda:
+    if _lib.on_cpu(table):
         y = table[ids.long()]
         return y * scale if scale != 1.0 else y
     t = ids.numel()
@@ -266,7 +266,7 @@ _EW_OPS = {"add": 0, "scalar_mul": 1, "sigmoid_mul": 2, "tanh_softcap": 3, "broa
 
 
 def elementwise(op: str, a: torch.Tensor, b: Optional[torch.Tensor] = None, s: float = 0.0) -> torch.Tensor:
-    if not a.is_cuda:
+    if _lib.on_cpu(a):
         af = a.to(torch.float32)
         if op == "add" or op == "broadcast_add":
             r = af + b.to(torch.float32)
@@ -288,7 +288,7 @@ def elementwise(op: str, a: torch.Tensor, b: Optional[torch.Tensor] = None, s: f
 
 def argmax(logits: torch.Tensor, index_offset: int = 0, with_values: bool = False):
     """Row argmax: NaN in a row -> -1, ties -> lowest index."""
-    if not logits.is_cuda:
+    if _lib.on_cpu(logits):
         lf = logits.to(torch.float32)
         idx = lf.argmax(dim=-1).to(torch.int32)
         # torch.argmax returns the first maximal index on CPU, matching the tie rule
@@ -336,7 +336,7 @@ def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.
         if mrope_sections is None or tuple(rope_pos3.shape) != (3, t):
             raise ValueError("rope_pos3 must be [3, tokens] and needs mrope_sections")
         rope_pos3 = rope_pos3.contiguous()
-    if not qkv.is_cuda:
+    if _lib.on_cpu(qkv):
         x = qkv.view(t, hq + 2 * hkv, hd)
         q = ref.rope_split_half(x[:, :hq], positions, theta, rd, inv_freq, rope_pos3, mrope_sections, pair_offset)
         k = ref.rope_split_half(x[:, hq:hq + hkv], positions, theta, rd, inv_freq, rope_pos3, mrope_sections, pair_offset)
@@ -399,7 +399,7 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
     (its scale plane may have a leading dimension larger than R)."""
     scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(hd)
     r = q.shape[0]
-    if not q.is_cuda:
+    if _lib.on_cpu(q):
         out = torch.empty((r, hq, hd), dtype=torch.float32)
         for i in range(r):
             s = int(seq_index[i])

@@ -36,7 +36,7 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, row_off: to
     """x [T, width]; w [width, taps]; state [slots, taps - 1, width] updated in place; returns silu(conv) [T, width]."""
     t, width = x.shape
     taps = w.shape[1]
-    if not x.is_cuda:
+    if _lib.on_cpu(x):
         y = torch.empty((t, width), dtype=torch.float32)
         xf, wf = x.float(), w.float()
         offs = row_off.tolist()
@@ -60,7 +60,7 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, row_off: to
 def recurrent(qkv, z, b, a, a_log, dt_bias, norm_w, state, row_off, slots, qk_heads: int, v_heads: int, hd: int = 128):
     """Gated delta rule over a flat batch; state [slots, v_heads, hd, hd] fp32 updated in place; returns [T, v_heads*hd]."""
     t = qkv.shape[0]
-    if not qkv.is_cuda:
+    if _lib.on_cpu(qkv):
         out = torch.empty((t, v_heads * hd), dtype=torch.float32)
         rep = v_heads // qk_heads
         offs = row_off.tolist()
@@ -101,7 +101,7 @@ def qk_headnorm(qkv: torch.Tensor, hq: int, hkv: int, hd: int, wq: Optional[torc
     A missing weight vector means "all ones" (with wq and wk both None the q / k heads are left alone);
     ``norm_v`` also normalises the value heads, without a weight (Gemma-4's v_norm)."""
     t = qkv.shape[0]
-    if not qkv.is_cuda:
+    if _lib.on_cpu(qkv):
         x = qkv.view(t, hq + 2 * hkv, hd)
         spans = [] if (wq is None and wk is None) else [(0, hq, wq), (hq, hq + hkv, wk)]
         if norm_v:

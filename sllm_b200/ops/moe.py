@@ -33,7 +33,7 @@ def _k():
 def route(logits: torch.Tensor, top_k: int, softmax_all: bool = False):
     """[T, E] -> (idx int32 [T, k], weights fp32 [T, k])."""
     t, e = logits.shape
-    if not logits.is_cuda:
+    if _lib.on_cpu(logits):
         lf = torch.nan_to_num(logits.float(), nan=float("-inf"))
         # stable ordering: larger logit first, ties to the lower index
         order = torch.sort(-lf, dim=1, stable=True).indices[:, :top_k]
@@ -61,7 +61,7 @@ def permute(idx: torch.Tensor, w: torch.Tensor, e_lo: int, e_hi: int):
     perm_src = torch.zeros(t * k, dtype=torch.int32, device=dev)
     perm_dst = torch.full((t, k), -1, dtype=torch.int32, device=dev)
     perm_w = torch.zeros(t * k, dtype=torch.float32, device=dev)
-    if not idx.is_cuda:
+    if _lib.on_cpu(idx):
         flat = idx.reshape(-1).tolist()
         wf = w.reshape(-1).tolist()
         cur = 0
@@ -83,7 +83,7 @@ def permute(idx: torch.Tensor, w: torch.Tensor, e_lo: int, e_hi: int):
 
 def gather(x: torch.Tensor, perm_src: torch.Tensor, tok_off: torch.Tensor) -> torch.Tensor:
     rows = perm_src.numel()
-    if not x.is_cuda:
+    if _lib.on_cpu(x):
         return x[perm_src.long()]
     from .core import _p, _stream
     xp = torch.empty((rows, x.shape[1]), dtype=torch.bfloat16, device=x.device)
@@ -96,7 +96,7 @@ def gather(x: torch.Tensor, perm_src: torch.Tensor, tok_off: torch.Tensor) -> to
 def combine(yp: torch.Tensor, perm_dst: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
     t, k = perm_dst.shape
     d = yp.shape[1]
-    if not yp.is_cuda:
+    if _lib.on_cpu(yp):
         out = torch.zeros((t, d), dtype=torch.float32)
         for j in range(k):
             p = perm_dst[:, j].long()
@@ -115,7 +115,7 @@ def combine(yp: torch.Tensor, perm_dst: torch.Tensor, residual: Optional[torch.T
 def shared_add(a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     """a + sigmoid(gate) * b with one gate logit per row: a, b [T, d]; gate [T] (any stride, e.g. a column of the
     router logits)."""
-    if not a.is_cuda:
+    if _lib.on_cpu(a):
         out = a.float() + torch.sigmoid(gate.float()).unsqueeze(1) * b.float()
         return out if a.dtype == torch.float32 else out.to(torch.bfloat16)
     from .core import _p, _stream

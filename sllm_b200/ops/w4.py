@@ -199,7 +199,7 @@ def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = N
     t, k = x.shape
     if k != w.k:
         raise ValueError("input width does not match the weight")
-    if not x.is_cuda:
+    if _lib.on_cpu(x):
         out = torch.zeros((t, w.n), dtype=torch.float32)
         offs = [0, t] if tok_off is None else tok_off.tolist()
         xf = x.float()

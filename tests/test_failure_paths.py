@@ -106,3 +106,57 @@ def test_kernel_trace_tool_output_schema(capsys):
     # each phase starts after the previous one's last barrier arrival
     for a, b in zip(doc["rows"], doc["rows"][1:]):
         assert b[col["input_visible.first"]] >= a[col["barrier_arrival.last"]]
+
+
+def test_fail_closed_mode_never_computes_on_cpu():
+    """With fail-closed mode on, an op handed a CPU tensor raises instead of computing its PyTorch oracle."""
+    import torch
+    from sllm_b200 import ops
+    from sllm_b200.ops import _lib
+    x = torch.randn(2, 128)
+    w = torch.ones(128)
+    assert ops.rmsnorm(x, w, 1e-5).shape == (2, 128)            # the CPU oracle path, as the CPU tests use it
+    _lib.set_fail_closed(True)
+    try:
+        for call in (lambda: ops.rmsnorm(x, w, 1e-5), lambda: ops.argmax(torch.randn(2, 16)),
+                     lambda: ops.embedding(torch.randn(4, 8), torch.tensor([1, 2], dtype=torch.int32))):
+            try:
+                call()
+            except _lib.KernelError as exc:
+                assert "fail-closed" in str(exc)
+            else:
+                raise AssertionError("a CPU tensor was computed in fail-closed mode")
+    finally:
+        _lib.set_fail_closed(False)
+    assert ops.rmsnorm(x, w, 1e-5).shape == (2, 128)
+
+
+def test_quarantine_accounting_and_release():
+    """A device failure quarantines the engine: every entry point refuses, the backend stops accepting, the report
+    says why; memory is freed only when the device work is known to be complete, otherwise it is parked."""
+    import pytest
+    import torch
+    from sllm_b200.engine import engine as E
+    from sllm_b200.models import config as MC
+    eng = E.build_engine(MC.tiny_llama(), "cpu", seed=1, num_pages=16, max_batch=2, use_cuda_graphs=False)
+    acc = eng.accounting()
+    assert acc["weights"] > 0 and acc["kv_pages"] == eng.cache.values.numel() * eng.cache.values.element_size()
+    assert acc["captured_graphs"] == 0 and acc["pinned_host"] > 0
+    out = eng.generate([[1, 2, 3]], 3)
+    eng._enter_quarantine("a bounded device wait gave up (status 105)", 105)
+    for call in (lambda: eng.new_sequence([1, 2]), lambda: eng.generate([[1, 2, 3]], 2)):
+        with pytest.raises(E.EngineQuarantined):
+            call()
+    rep = eng.shutdown_report()
+    assert rep["quarantine"]["device_status"] == 105 and rep["quarantine"]["work_completed"] and rep["steps"] >= 2
+    assert rep["kv_pool"] is not None and "fallbacks" in rep
+    freed = eng.release()
+    assert freed["freed_bytes"] == acc["kv_pages"] and freed["parked_bytes"] == 0 and eng.cache.values.numel() == 0
+    # work that cannot be proven complete: nothing is freed, the buffers stay referenced
+    e2 = E.build_engine(MC.tiny_llama(), "cpu", seed=1, num_pages=16, max_batch=2, use_cuda_graphs=False)
+    e2._enter_quarantine("synchronize failed", 0)
+    e2.quarantine["work_completed"] = False
+    n = len(E._PARKED)
+    r2 = e2.release()
+    assert r2["freed_bytes"] == 0 and r2["parked_bytes"] > 0 and len(E._PARKED) == n + 1 and e2.cache.values.numel() > 0
+    assert out and len(out[0]) == 3

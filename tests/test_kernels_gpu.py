@@ -58,6 +58,67 @@ def test_gemm_fp8_blockscaled(m, n, k):
     _status_ok()
 
 
+def elementwise_close(got, want, rtol, atol_frac, what=""):
+    """Every element: |got - want| <= rtol |want| + atol_frac max|want| (a wrong 16x8 unit or a mis-scaled tile edge
+    fails here even when the norm of the whole output barely moves)."""
+    got, want = got.float().cpu(), want.float().cpu()
+    tol = rtol * want.abs() + atol_frac * want.abs().max()
+    bad = (got - want).abs() > tol
+    if bad.any():
+        idx = bad.nonzero()[0].tolist()
+        raise AssertionError(f"{what}: {int(bad.sum())} elements off, first at {idx}: got {got[tuple(idx)].item():.5g} "
+                             f"want {want[tuple(idx)].item():.5g}")
+
+
+@pytest.mark.parametrize("scaled", [False, True])
+@pytest.mark.parametrize("bn,m", [(16, 1), (16, 15), (16, 16), (32, 17), (32, 31), (32, 32), (64, 33), (64, 63), (64, 64),
+                                  (128, 65), (128, 127), (128, 128)])
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_gemm_swap_ab_tile_edges_per_element(scaled, bn, m, splits):
+    """Small-M (swap-AB) tiles at every token-tile width, rows at the edges of the tile, weight rows at 127 / 128 / 129
+    boundaries, every cluster split count: checked element by element against fp32."""
+    torch.manual_seed(bn * 131 + m * 7 + splits)
+    k = 1024
+    for n in (128, 136, 264):                    # one full weight tile; one full + 8 rows; two full + 8 rows
+        n_rows = n
+        x = (torch.randn(m, k, device=DEV) * 0.7).bfloat16()
+        w = (torch.randn(n_rows, k, device=DEV) * 0.05).bfloat16()
+        w[-1] *= 8                                     # the last weight row carries a large, easy to misplace value
+        x[-1] *= 4
+        y = torch.full((m, n_rows), float("nan"), device=DEV, dtype=torch.bfloat16)
+        if scaled:
+            xq = ops.quant_fp8(x)
+            lw = LinearWeight.from_dense(w.cpu(), "fp8").to(DEV)
+            ops.gemm_raw(lw.w, xq.data, y, scale_a=lw.scale_t, scale_b=xq.scale, transpose_out=True, bn=bn, splits=splits,
+                         stages=4 if bn <= 32 else 3)
+            want = ref.linear_fp8(xq.data.cpu(), xq.scale.cpu(), lw.w.cpu(), lw.scale_t.cpu())
+        else:
+            ops.gemm_raw(w, x, y, transpose_out=True, bn=bn, splits=splits, stages=4 if bn <= 32 else 3)
+            want = x.float() @ w.float().t()
+        assert not torch.isnan(y.float()).any(), "an output element was never written"
+        elementwise_close(y, want, 1.2e-2, 2e-3, f"n={n_rows}")
+    _status_ok()
+
+
+@pytest.mark.parametrize("m", [127, 128, 129, 255, 257])
+@pytest.mark.parametrize("n", [128, 136, 264])
+def test_gemm_large_m_row_edges_per_element(m, n):
+    """The 128 x 128-tile path at 127 / 128 / 129 rows and ragged column counts (multiples of 8)."""
+    torch.manual_seed(m + n)
+    k = 512
+    x = (torch.randn(m, k, device=DEV) * 0.7).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.05).bfloat16()
+    x[-1] *= 4
+    w[-1] *= 8
+    y = ops.linear(x, LinearWeight("dense", w))
+    elementwise_close(y, x.float() @ w.float().t(), 1.2e-2, 2e-3, "bf16")
+    lw = LinearWeight.from_dense(w.cpu(), "fp8").to(DEV)
+    xq = ops.quant_fp8(x)
+    yq = ops.linear(xq, lw)
+    elementwise_close(yq, ref.linear_fp8(xq.data.cpu(), xq.scale.cpu(), lw.w.cpu(), lw.scale_t.cpu()), 1.2e-2, 2e-3, "fp8")
+    _status_ok()
+
+
 @pytest.mark.parametrize("cluster", [True, False])
 @pytest.mark.parametrize("splits", [1, 2, 4, 7, 8, 12])
 def test_gemm_split_k_deterministic(splits, cluster):
