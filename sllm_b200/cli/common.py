@@ -76,7 +76,12 @@ def open_model(args, max_batch: int = 8, tp=None):
             raise CliError("kv-cache-encoding nvfp4 is not available in this build", 2)
         kvf = _KV_MAP[args.kv_cache_encoding]
     tp_size, tp_rank = (tp.size, tp.rank) if tp is not None else (1, 0)
-    cfg, weights = loader.load_llama_gguf(g, device, tp_size, tp_rank, kv_format=kvf)
+    ep = getattr(args, "_ep", None)           # expert-parallel context of a mixture-of-experts run (same ranks as tp)
+    ep_size, ep_rank = (ep.size, ep.rank) if ep is not None else (1, 0)
+    try:
+        cfg, weights, family = loader.load_model_gguf(g, device, tp_size, tp_rank, ep_size, ep_rank, kv_format=kvf)
+    except G.GgufError as exc:
+        raise CliError(f"model load failed: {exc}", 3) from None
     if use_cpu and cfg.kv_format not in ("fp32", "bf16"):
         cfg.kv_format = "fp32"
     if args.context_length:
@@ -84,12 +89,24 @@ def open_model(args, max_batch: int = 8, tp=None):
             emit({"event": "warning", "code": "context_length_exceeds_recommended",
                   "requested": args.context_length, "recommended": cfg.max_context})
         cfg.max_context = args.context_length
-    model = LlamaModel(cfg, weights, tp)
     blocks = (cfg.max_context + cfg.page_size - 1) // cfg.page_size
-    cache = PagedKVCache(cfg, max_batch * blocks + 8, device, kv_heads=model.local_kv_heads)
+    if family == "moe":
+        from ..models.moe import MoeModel
+        model = MoeModel(cfg, weights, tp, ep)
+        cache = PagedKVCache(cfg, max_batch * blocks + 8, device, kv_heads=model.local_kv_heads)
+    elif family == "qwen35":
+        from ..cache.hybrid import HybridCache
+        from ..models.qwen35 import Qwen35Model
+        model = Qwen35Model(cfg, weights, tp)
+        cache = HybridCache(cfg, max_batch * blocks + 8, device, max_seqs=2 * max_batch + 2, kv_heads=model.local_kv_heads,
+                            tp_size=tp_size)
+    else:
+        model = LlamaModel(cfg, weights, tp)
+        cache = PagedKVCache(cfg, max_batch * blocks + 8, device, kv_heads=model.local_kv_heads)
     eng = Engine(cfg, model, cache, device, max_batch=max_batch, use_cuda_graphs=not use_cpu, tp=tp)
-    eng.mtp_weights = loader.load_mtp_gguf(g, cfg, device) if tp_size == 1 else None
-    vis = loader.load_vision_gguf(g, cfg, device)
+    dense_family = family not in ("moe", "qwen35")
+    eng.mtp_weights = loader.load_mtp_gguf(g, cfg, device) if tp_size == 1 and dense_family else None
+    vis = loader.load_vision_gguf(g, cfg, device) if dense_family else None
     if vis is not None:
         from ..models.vision_tower import VisionTower
         eng.vision = VisionTower(*vis)

@@ -1,7 +1,9 @@
 """`sllm-convert-gguf`: writes a GGUF file plus its derived lock.
 
 Kinds:
-  random-llama   seeded random-init weights of a named shape (`--artifact llama3-8b`), for benchmarks and tests
+  random-llama   seeded random-init weights of a named shape (`--artifact llama3-8b`), for benchmarks and tests; the
+                 mixture-of-experts (`moe-120b`, `qwen35-moe`, `tiny-moe`, `tiny-shared-moe`) and hybrid
+                 (`qwen35-hybrid`, `tiny-qwen35`) shapes are written through models/family_io.py with MXFP4 experts
   hf-llama       a Llama-style Hugging Face checkpoint (config.json + safetensors) from a directory that is first
                  verified against its model lock (`--lock lock.json --cache DIR`)
   mixed-precision  a compressed-tensors checkpoint with FP8 channel-scaled attention projections, NVFP4 MLP
@@ -98,6 +100,15 @@ def _load_hf(cache, cfg):
     return LlamaWeights(embed, layers, get("model.norm.weight"), lin(head), 0)
 
 
+def _write_lock(path: str, doc: dict) -> None:
+    tmp = path + ".tmp"
+    with open(tmp, "w", encoding="utf-8") as f:
+        json.dump(doc, f, sort_keys=True, indent=1)
+        f.flush()
+        os.fsync(f.fileno())
+    os.replace(tmp, path)
+
+
 def main(argv=None) -> int:
     def go():
         p = StrictParser(prog="sllm-convert-gguf")
@@ -134,10 +145,19 @@ def main(argv=None) -> int:
             if not isinstance(overrides, dict):
                 raise CliError("--manifest must hold a JSON object")
         fps, tokenizer_json, chat_template = [], None, None
+        named = dict(MC.NAMED)
+        from ..models import moe as _moe
+        from ..models import qwen35 as _q35
+        named.update({"tiny-moe": _moe.tiny_moe, "tiny-shared-moe": _moe.tiny_shared_moe, "tiny-qwen35": _q35.tiny_qwen35})
         if a.kind == "random-llama":
-            if a.artifact not in MC.NAMED:
-                raise CliError(f"--artifact must be one of {sorted(MC.NAMED)}")
-            cfg = MC.NAMED[a.artifact]()
+            if a.artifact not in named:
+                raise CliError(f"--artifact must be one of {sorted(named)}")
+            cfg = named[a.artifact]()
+            if cfg.family in ("moe", "qwen35"):
+                if a.weight_format not in ("bf16", "fp32"):
+                    raise CliError("the mixture-of-experts and hybrid families keep bf16 attention (experts are MXFP4)")
+                if a.with_vision or a.with_mtp:
+                    raise CliError("--with-vision / --with-mtp apply to the dense decoder family")
             cfg.weight_format = a.weight_format
             if a.weight_format != "fp8" and cfg.kv_format == "fp8":
                 cfg.kv_format = "bf16"
@@ -176,6 +196,22 @@ def main(argv=None) -> int:
                 "output": a.output, "derived_lock": a.derived_lock, "source_lock_fingerprints": fps}
         if a.dry_run:
             emit({"dry_run": True, **plan})
+            return 0
+        if a.kind == "random-llama" and cfg.family in ("moe", "qwen35"):
+            from ..models import family_io
+            dev = "cuda" if torch.cuda.is_available() else "cpu"
+            if cfg.family == "moe":
+                w = _moe.init_random_moe_weights(cfg, dev, seed=a.seed)
+            else:
+                w = _q35.init_random_qwen35_weights(cfg, dev, seed=a.seed)
+            if a.synthetic_tokenizer:
+                tokenizer_json = _synthetic_tokenizer(cfg.vocab)
+            dl = family_io.export_family_gguf(cfg, w, a.output, tokenizer_json=tokenizer_json, chat_template=chat_template,
+                                              converter_args={"kind": a.kind, "commit": a.converter_commit, "seed": a.seed,
+                                                              "weight_format": a.weight_format})
+            _write_lock(a.derived_lock, dl)
+            emit({"written": True, **plan, "size_bytes": dl["output"]["size_bytes"], "sha256": dl["output"]["sha256"],
+                  "fingerprint": dl["fingerprint"]})
             return 0
         if a.kind == "random-llama":
             dev = "cuda" if torch.cuda.is_available() else "cpu"
@@ -225,12 +261,7 @@ def main(argv=None) -> int:
                                       source_fingerprints=tuple(fps), mtp=mtp, vision=vision,
                                       converter_args={"kind": a.kind, "commit": a.converter_commit, "seed": a.seed,
                                                       "weight_format": a.weight_format})
-        tmp = a.derived_lock + ".tmp"
-        with open(tmp, "w", encoding="utf-8") as f:
-            json.dump(dl, f, sort_keys=True, indent=1)
-            f.flush()
-            os.fsync(f.fileno())
-        os.replace(tmp, a.derived_lock)
+        _write_lock(a.derived_lock, dl)
         emit({"written": True, **plan, "size_bytes": dl["output"]["size_bytes"], "sha256": dl["output"]["sha256"],
               "fingerprint": dl["fingerprint"]})
         return 0

@@ -127,7 +127,8 @@ def make_backend(a, gguf: str, derived_lock: str, alias: str, overrides=None):
     o = overrides or {}
     src = argparse.Namespace(gguf=gguf, derived_lock=derived_lock, device_index=o.get("device_index", a.device_index),
                              target=a.target, kv_cache_encoding=o.get("kv_cache_encoding") or a.kv_cache_encoding,
-                             context_length=o.get("context_length") or a.context_length, cpu=a.cpu)
+                             context_length=o.get("context_length") or a.context_length, cpu=a.cpu,
+                             _ep=getattr(a, "_ep", None))
     tp, ctrl = getattr(a, "_tp", None), getattr(a, "_ctrl", None)
     eng, tok, g, lock = open_model(src, max_batch=o.get("max_batch") or a.max_batch, tp=tp)
     if not a.cpu and not a.allow_cpu_fallback:
@@ -188,9 +189,15 @@ def serve(a) -> int:
         from ..formats import gguf as G
         from ..models import loader
         gfile = G.GgufFile(a.gguf)
-        d_model = loader.config_from_gguf(gfile).d_model
+        file_cfg = loader.config_from_gguf(gfile)
+        d_model = file_cfg.d_model
         gfile.close()
         a._tp = make_tp(world, rank, torch.device("cuda", local), impl="fused", max_tokens=max(a.max_batch, 128), d_model=d_model)
+        a._ep = None
+        if file_cfg.family == "moe":
+            # the ranks that shard the attention also hold the experts: n_experts / world each
+            from ..parallel.ep import FusedEP
+            a._ep = FusedEP(world, rank, torch.device("cuda", local), max_tokens=max(a.max_batch, 128), d_model=d_model)
         if rank != 0:
             make_backend(a, a.gguf, a.derived_lock, a.model or "model")     # follows until the leader stops
             a._tp.close()

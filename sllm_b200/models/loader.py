@@ -296,6 +296,21 @@ def load_llama_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, k
     return cfg, LlamaWeights(embed, layers, final_norm, head, vo)
 
 
+def load_model_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, ep_size: int = 1, ep_rank: int = 0,
+                    kv_format: Optional[str] = None):
+    """(cfg, weights, family) of this rank for any model family a file can carry: the dense decoder (`llama`,
+    `gemma4`) through load_llama_gguf, `moe` and `qwen35` through models.family_io."""
+    cfg = config_from_gguf(g)
+    if cfg.family in ("moe", "qwen35"):
+        from . import family_io
+        cfg, w = family_io.load_family_gguf(g, device, tp_size, tp_rank, ep_size, ep_rank, kv_format=kv_format)
+        return cfg, w, cfg.family
+    if ep_size != 1:
+        raise G.GgufError("expert parallelism applies to the mixture-of-experts family")
+    cfg, w = load_llama_gguf(g, device, tp_size, tp_rank, kv_format=kv_format)
+    return cfg, w, cfg.family
+
+
 def vision_tensor_list(w) -> list:
     """(name, tensor) of every tensor of a vision tower, in file order."""
     out = [("v.patch_embd.weight", w.patch_w.w), ("v.patch_embd.bias", w.patch_b), ("v.position_embd.weight", w.pos_table)]

@@ -319,3 +319,20 @@ def test_serve_bench_against_live_server(model):
             proc.communicate(timeout=60)
         except Exception:
             proc.kill()
+
+
+@pytest.mark.parametrize("artifact", ["tiny-moe", "tiny-shared-moe", "tiny-qwen35"])
+def test_other_families_convert_and_generate(capsys, tmp_path, artifact):
+    """The mixture-of-experts and hybrid families go through the same converter, verification and CLI commands."""
+    g, l = str(tmp_path / "m.gguf"), str(tmp_path / "m.lock.json")
+    assert convert.main(["--kind", "random-llama", "--artifact", artifact, "--weight-format", "fp32", "--output", g,
+                         "--derived-lock", l, "--synthetic-tokenizer"]) == 0
+    capsys.readouterr()
+    rc, out = run(capsys, ["verify-model", "--gguf", g, "--derived-lock", l])
+    assert rc == 0 and out[0]["verified"]
+    rc, out = run(capsys, ["decode", "--gguf", g, "--derived-lock", l, "--cpu", "--input-token-ids", "5 6 7 8 9", "--max-new-tokens", "5"])
+    assert rc == 0 and len(out[0]["output_tokens"]) == 5
+    rc, again = run(capsys, ["decode", "--gguf", g, "--derived-lock", l, "--cpu", "--input-token-ids", "5 6 7 8 9", "--max-new-tokens", "5"])
+    assert again[0]["output_tokens"] == out[0]["output_tokens"]
+    rc = convert.main(["--kind", "random-llama", "--artifact", artifact, "--weight-format", "fp8", "--output", g, "--derived-lock", l])
+    assert rc == 2

@@ -174,3 +174,27 @@ def test_engine_served_over_http_greedy_json_and_concurrency(engine_client):
     assert len(e[0]["embedding"]) == 256 and abs(np.linalg.norm(e[0]["embedding"]) - 1) < 1e-4
     assert "sllm_tokens_total" in c.get("/metrics").text
     assert c.post("/v1/chat/completions", json={**req, "max_completion_tokens": 4096}).status_code == 400   # context bound
+
+
+@pytest.mark.parametrize("artifact", ["tiny-shared-moe", "tiny-qwen35"])
+def test_other_model_families_served_from_converted_files(tmp_path, artifact):
+    """A mixture-of-experts file and a hybrid (gated delta net) file go convert -> verify -> open_model -> HTTP."""
+    import argparse
+    from sllm_b200.cli import convert
+    from sllm_b200.cli.common import open_model
+    g, l = str(tmp_path / "m.gguf"), str(tmp_path / "m.lock.json")
+    assert convert.main(["--kind", "random-llama", "--artifact", artifact, "--weight-format", "fp32", "--output", g,
+                         "--derived-lock", l, "--synthetic-tokenizer"]) == 0
+    args = argparse.Namespace(gguf=g, derived_lock=l, device_index=0, target="sm_100a", kv_cache_encoding=None,
+                              context_length=None, cpu=True)
+    eng, tok, _, _ = open_model(args, max_batch=2)
+    backend = EngineBackend(eng, tok, aliases=(M,), queue_capacity=4)
+    try:
+        c = TestClient(build_app(ModelRegistry({M: backend}), ServerConfig()))
+        req = {"model": M, "prompt": "alpha beta gamma", "max_tokens": 6, "temperature": 0}
+        a, b = c.post("/v1/completions", json=req).json(), c.post("/v1/completions", json=req).json()
+        assert a["choices"][0]["text"] == b["choices"][0]["text"] and a["usage"]["completion_tokens"] == 6
+        props = c.get("/props").json()["models"][0]
+        assert props["model_family"] == eng.cfg.family and props["quarantine"] is None
+    finally:
+        backend.shutdown(1.0)
