@@ -89,6 +89,42 @@ def on_cpu(t) -> bool:
     return True
 
 
+# Dispatch audit: when switched on, every planned launch of the main ops leaves a record (op, kernel path, shape,
+# tile / split plan, whether the fast path was left) in a bounded ring that /props, the evidence runners and tests
+# read (reference: the dispatch-info records of include/sllm/hip.h:651-671 - kernel id, grid, fallback_used).
+_AUDIT_CAP = 256
+_audit_on = [None]
+_audit_ring: list = []
+_audit_total = [0]
+
+
+def audit(on: bool) -> None:
+    _audit_on[0] = bool(on)
+
+
+def audit_enabled() -> bool:
+    if _audit_on[0] is None:
+        import os
+        _audit_on[0] = os.environ.get("SLLM_DISPATCH_AUDIT", "0") == "1"
+    return _audit_on[0]
+
+
+def record_dispatch(op: str, kernel: str, fallback_used: bool = False, **info) -> None:
+    if not audit_enabled():
+        return
+    _audit_total[0] += 1
+    _audit_ring.append({"seq": _audit_total[0], "op": op, "kernel": kernel, "fallback_used": bool(fallback_used), **info})
+    if len(_audit_ring) > _AUDIT_CAP:
+        del _audit_ring[:len(_audit_ring) - _AUDIT_CAP]
+
+
+def dispatch_records(clear: bool = False) -> list:
+    out = list(_audit_ring)
+    if clear:
+        _audit_ring.clear()
+    return out
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise KernelError(f"{what}: launch rejected ({STATUS_NAMES.get(rc, rc)})")

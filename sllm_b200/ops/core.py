@@ -174,6 +174,10 @@ def linear(x, w: LinearWeight, residual: Optional[torch.Tensor] = None) -> torch
         k_blocks = (w.in_features + 63) // 64
     y = torch.empty((m, n), dtype=torch.bfloat16, device=xd.device)
     swap, bn, splits, stages = _gemm_plan(m, n, k_blocks)
+    if _lib.audit_enabled():
+        _lib.record_dispatch("linear", "gemm_tcgen05_kernel", m=m, n=n, k=w.in_features, kind=w.kind, swap_ab=swap, bn=bn,
+                             splits=splits, stages=stages, grid=[(n + 127) // 128 if swap else (m + 127) // 128,
+                                                                 (m + bn - 1) // bn if swap else (n + bn - 1) // bn, splits])
     if w.kind == "fp8":
         if swap:
             gemm_raw(w.w, x.data, y, scale_a=w.scale_t, scale_b=x.scale, residual=residual, transpose_out=True,
@@ -443,6 +447,9 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
         ctas = r * hkv
         # one wave of 2 CTAs per SM; a split keeps at least one 128-key tile
         splits = max(1, min((2 * _SM_COUNT) // ctas, (mk + 127) // 128, 64)) if ctas < 2 * _SM_COUNT else 1
+        if _lib.audit_enabled():
+            _lib.record_dispatch("paged_attention", "decode_attention_tc_kernel", rows=r, hq=hq, hkv=hkv, hd=hd, window=window,
+                                 splits=splits, grid=[r, hkv, splits])
         rc = lib.sllm_decode_attention_tc(
             _p(q), q.stride(0), _p(kv.k), _p(kv.v), _p(kv.k_scale), _p(kv.v_scale), kv.k_static, kv.v_static,
             _p(block_table), block_table.stride(0), _p(seq_index), _p(kv_lens), r, hq, hkv, kv.k.shape[0],
@@ -450,6 +457,11 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
             wsp.ws.numel(), _p(wsp.counters), wsp.counters.numel(), _p(wsp.status), _stream())
         _lib.check(rc, "decode_attention_tc")
         return oq if quant_out else ob
+    if _lib.audit_enabled():
+        # the CUDA-core kernel serves what the tensor-core kernel does not cover; for FP8 pages of 128-wide heads
+        # that is a detour worth seeing
+        _lib.record_dispatch("paged_attention", "paged_attention_kernel", fallback_used=bool(kv.fp8 and hd == 128),
+                             rows=r, hq=hq, hkv=hkv, hd=hd, window=window, splits=splits)
     rc = lib.sllm_paged_attention(
         _p(q), q.stride(0), _p(kv.k), _p(kv.v), _p(kv.k_scale), _p(kv.v_scale), kv.k_static, kv.v_static,
         _p(block_table), block_table.stride(0), _p(seq_index), _p(kv_lens), r, hq, hkv, hd, kv.page_size, window,

@@ -229,6 +229,10 @@ def _launch_cluster(phases: list, rows: int, device: torch.device, rope: Optiona
     lib = _lib.kernels()
     plans = [_resolve_cluster_phase(ph, i, rows, il) for i, ph in enumerate(phases)]
     for one, w_rows, bn, splits, stages in plans:
+        if _lib.audit_enabled():
+            _lib.record_dispatch("fused_decode_phase", "gemm_tcgen05_kernel", epilogue=int(one.epilogue), rows=rows, n=w_rows,
+                                 k=int(one.k), bn=bn, splits=splits, stages=stages, tensor_parallel=comm is not None,
+                                 grid=[(w_rows + 127) // 128, 1, splits])
         rc = lib.sllm_gemm_fused(C.byref(one), C.byref(rope) if rope is not None else None, rows, bn, splits, stages,
                                  _p(wsp.ws), wsp.ws.numel(), _p(wsp.counters), wsp.counters.numel(), _p(wsp.status),
                                  _stream(), None if comm is None else C.cast(C.pointer(comm), C.c_void_p))

@@ -229,6 +229,9 @@ def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = N
         while ctas * splits < 148 and splits * 2 <= max(1, k_chunks // 4) and splits < 16:
             splits *= 2
     wsp = workspace(x.device)
+    if _lib.audit_enabled():
+        _lib.record_dispatch("linear_w4", "gemm_w4_kernel", fmt=w.fmt, tokens=t, n=w.n, k=w.k, groups=w.groups,
+                             grouped=tok_off is not None, bn=bn, splits=splits)
     rc = _lib.kernels().sllm_gemm_w4(_p(w.tiles), _p(w.tensor_scale), _p(x), _p(y), _p(residual), _p(tok_off),
                                      _p(tok_scale), 0 if w.fmt == "mxfp4" else 1, w.groups, w.n_rows, w.n, w.k_pad, w.k,
                                      x.stride(0), t, mgt, y.stride(0), bn, splits, 0, _p(wsp.ws), wsp.ws.numel(),

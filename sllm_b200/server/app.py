@@ -97,6 +97,12 @@ def _split_utf8(text: str, limit: int = MAX_DELTA_BYTES) -> list:
     return out
 
 
+def _dispatch_tail(n: int = 16) -> list:
+    """The last dispatch records (empty unless SLLM_DISPATCH_AUDIT=1 switched the audit on)."""
+    from ..ops import _lib
+    return _lib.dispatch_records()[-n:]
+
+
 def _fallbacks() -> dict:
     """Counters of work that left its fast path (fused tensor-parallel GEMM -> NCCL, fused decode -> per-op kernels)."""
     from ..ops import _lib
@@ -269,7 +275,7 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
                 "features": {"metrics": cfg.metrics, "resumable_sse": cfg.resumable_sse,
                              "compatibility_profile": cfg.compatibility_profile,
                              "dynamic_models": registry.dynamic is not None, "cors": bool(cfg.cors_origins)},
-                "fallbacks": _fallbacks()}
+                "fallbacks": _fallbacks(), "dispatch_audit": _dispatch_tail()}
 
     @app.get("/slots")
     async def slots(request: Request):
