@@ -157,12 +157,20 @@ class PagedKVCache:
         self.device = device
         self.pool = PagePool(num_pages, cfg.page_size)
         fmt = cfg.kv_format
+        if fmt not in ("fp32", "bf16", "fp16", "fp8", "fp8-static", "nvfp4"):
+            raise ValueError(f"unknown KV-cache format {fmt!r}")
         self.fp8 = fmt in ("fp8", "fp8-static")
+        self.nvfp4 = fmt == "nvfp4"
+        if self.nvfp4 and cfg.head_dim % 64:
+            raise ValueError("NVFP4 KV rows need a head width that is a multiple of 64")
         vdtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}.get(fmt, torch.uint8)
-        shape = (cfg.n_layers, 2, num_pages, hkv, cfg.page_size, cfg.head_dim)
+        # an NVFP4 row holds head_dim / 2 code bytes and head_dim / 16 block-scale bytes (9 bits per value with the
+        # fp32 outer scale of the row in the scale plane)
+        row = cfg.head_dim // 2 + cfg.head_dim // 16 if self.nvfp4 else cfg.head_dim
+        shape = (cfg.n_layers, 2, num_pages, hkv, cfg.page_size, row)
         self.values = torch.zeros(shape, dtype=vdtype, device=device)
         self.scales = None
-        if fmt == "fp8":
+        if fmt in ("fp8", "nvfp4"):
             self.scales = torch.ones((cfg.n_layers, 2, num_pages, hkv, cfg.page_size), dtype=torch.float32,
                                      device=device)
         self.k_static, self.v_static = (k_static or 1.0, v_static or 1.0) if fmt == "fp8-static" else (0.0, 0.0)
@@ -176,7 +184,7 @@ class PagedKVCache:
             KVLayer(self.values[l, 0], self.values[l, 1],
                     None if self.scales is None else self.scales[l, 0],
                     None if self.scales is None else self.scales[l, 1],
-                    self.fp8, cfg.page_size, float(per_layer[l][0]), float(per_layer[l][1]))
+                    self.fp8, cfg.page_size, float(per_layer[l][0]), float(per_layer[l][1]), self.nvfp4)
             for l in range(cfg.n_layers)
         ]
 
@@ -185,7 +193,7 @@ class PagedKVCache:
 
     def bytes_per_token(self) -> int:
         s = self.spec
-        b = 2 * s.n_layers * s.kv_heads * s.head_dim * self.values.element_size()
+        b = 2 * s.n_layers * s.kv_heads * self.values.shape[-1] * self.values.element_size()
         if self.scales is not None:
             b += 2 * s.n_layers * s.kv_heads * 4
         return b

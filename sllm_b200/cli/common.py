@@ -48,7 +48,7 @@ def emit(obj) -> None:
     sys.stdout.flush()
 
 
-_KV_MAP = {"fp16": "bf16", "bf16": "bf16", "fp8": "fp8", "fp8-static": "fp8-static"}
+_KV_MAP = {"fp16": "bf16", "bf16": "bf16", "fp8": "fp8", "fp8-static": "fp8-static", "nvfp4": "nvfp4"}
 
 
 def open_model(args, max_batch: int = 8, tp=None):
@@ -72,8 +72,6 @@ def open_model(args, max_batch: int = 8, tp=None):
     device = torch.device("cpu") if use_cpu else torch.device("cuda", args.device_index)
     kvf = None
     if args.kv_cache_encoding:
-        if args.kv_cache_encoding == "nvfp4":
-            raise CliError("kv-cache-encoding nvfp4 is not available in this build", 2)
         kvf = _KV_MAP[args.kv_cache_encoding]
     tp_size, tp_rank = (tp.size, tp.rank) if tp is not None else (1, 0)
     ep = getattr(args, "_ep", None)           # expert-parallel context of a mixture-of-experts run (same ranks as tp)
@@ -82,7 +80,7 @@ def open_model(args, max_batch: int = 8, tp=None):
         cfg, weights, family = loader.load_model_gguf(g, device, tp_size, tp_rank, ep_size, ep_rank, kv_format=kvf)
     except G.GgufError as exc:
         raise CliError(f"model load failed: {exc}", 3) from None
-    if use_cpu and cfg.kv_format not in ("fp32", "bf16"):
+    if use_cpu and cfg.kv_format not in ("fp32", "bf16", "nvfp4"):
         cfg.kv_format = "fp32"
     if args.context_length:
         if args.context_length > cfg.max_context:

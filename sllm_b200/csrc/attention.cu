@@ -22,10 +22,14 @@
 
 namespace sllm {
 
-template <int HD, int G, bool kFp8>
+// kFmt: 0 bf16 pages, 1 E4M3 pages (scale per token and head, or static), 2 NVFP4 rows (E2M1 codes, E4M3 scale per 16
+// channels inside the row, fp32 outer scale per token and head in the scale plane; see nvfp4_row_bytes).
+template <int HD, int G, int kFmt>
 __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnParams p) {
   pdl_wait();
   pdl_trigger();
+  constexpr bool kFp8 = kFmt == 1;
+  constexpr bool kNv4 = kFmt == 2;
   constexpr int EPL = HD / 32;  // channels per lane in the P.V phase
   extern __shared__ float smem[];
   float* q_s = smem;                       // [G][HD]
@@ -80,6 +84,41 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
     if (valid) {
       const int blk = bt[tok / p.page_size];
       slot = (static_cast<size_t>(blk) * p.hkv + kvh) * p.page_size + tok % p.page_size;   // head-major pages
+    }
+    if (kNv4 && valid) {
+      // the whole row (code words, then the block-scale words) is requested before any of it is used
+      constexpr int kCodeWords = HD / 8, kScaleWords = (HD / 16 + 3) / 4;
+      const uint8_t* rowp = static_cast<const uint8_t*>(p.k_pages) + slot * nvfp4_row_bytes(HD);
+      uint32_t cw[kCodeWords], sw[kScaleWords];
+#pragma unroll
+      for (int i = 0; i < kCodeWords; ++i) cw[i] = reinterpret_cast<const uint32_t*>(rowp)[i];
+#pragma unroll
+      for (int i = 0; i < kScaleWords; ++i) {
+        sw[i] = 0u;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (4 * i + b < HD / 16) sw[i] |= static_cast<uint32_t>(rowp[HD / 2 + 4 * i + b]) << (8 * b);
+      }
+#pragma unroll
+      for (int b = 0; b < HD / 16; ++b) {
+        const float bs = e4m3_to_f32(static_cast<uint8_t>((sw[b >> 2] >> (8 * (b & 3))) & 0xffu));
+        float kf[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) kf[j] = e2m1_to_f32((cw[2 * b + (j >> 3)] >> (4 * (j & 7))) & 0xfu);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float a = 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) a = fmaf(q_s[g * HD + 16 * b + j], kf[j], a);
+          s[g] = fmaf(a, bs, s[g]);
+        }
+      }
+      const float ksc = p.k_scale[slot];
+      vsc = p.v_scale[slot];
+#pragma unroll
+      for (int g = 0; g < G; ++g) s[g] *= ksc;
+    }
+    if (!kNv4 && valid) {
       // All 16-byte pieces of (up to) 128 bytes of the key row are requested before any is used, so one
       // memory round trip covers the whole row.
       constexpr int kVecs = HD * (kFp8 ? 1 : 2) / 16;
@@ -154,7 +193,19 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
       for (int u = 0; u < 8; ++u) {
         const size_t vslot = __shfl_sync(0xffffffffu, slot, (j0 + u) & 31);
         const bool live = j0 + u < cnt;
-        if (kFp8) {
+        if (kNv4) {
+          // this lane's EPL channels: EPL / 2 code bytes and the scale of the 16-channel block they lie in
+          const uint8_t* rowp = static_cast<const uint8_t*>(p.v_pages) + vslot * nvfp4_row_bytes(HD);
+          uint32_t codes = 0u;
+          float bs = 0.f;
+          if (live) {
+#pragma unroll
+            for (int b = 0; b < EPL / 2; ++b) codes |= static_cast<uint32_t>(rowp[lane * (EPL / 2) + b]) << (8 * b);
+            bs = e4m3_to_f32(rowp[HD / 2 + (lane * EPL) / 16]);
+          }
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) vf[u][e] = e2m1_to_f32((codes >> (4 * e)) & 0xfu) * bs;
+        } else if (kFp8) {
           const uint8_t* vp = static_cast<const uint8_t*>(p.v_pages) + vslot * HD + lane * EPL;
           float f4[4];
           if (EPL == 4) {
@@ -221,7 +272,7 @@ __global__ void __launch_bounds__(128) paged_attention_kernel(const PagedAttnPar
   attention_tail<HD, G, 4, SyncCta>(p, r, kvh, split, splits, threadIdx.x, m_s, l_s, o_s, &s_is_last, s_red);
 }
 
-template <int HD, int G, bool kFp8>
+template <int HD, int G, int kFp8>
 static int launch_paged(const PagedAttnParams& p, int rows, int splits, cudaStream_t st) {
   const size_t smem = sizeof(float) * (G * HD + 4 * 32 * G + 8 * G + 4 * G * HD);
   static bool cfg = false;
@@ -236,7 +287,7 @@ static int launch_paged(const PagedAttnParams& p, int rows, int splits, cudaStre
   return cudaGetLastError() == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 
-template <int HD, bool kFp8>
+template <int HD, int kFp8>
 static int dispatch_g(const PagedAttnParams& p, int rows, int g, int splits, cudaStream_t st) {
   switch (g) {
     case 1: return launch_paged<HD, 1, kFp8>(p, rows, splits, st);
@@ -289,17 +340,26 @@ SLLM_EXPORT int sllm_paged_attention(const void* q, int q_ld, const void* k_page
     p.ws_ml = ws + units * splits * g * hd;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kv_fp8 == 2) {
+    if (!k_scale || !v_scale) return SLLM_ERR_INVALID_ARGUMENT;       // the outer scales of the NVFP4 rows
+    switch (hd) {
+      case 64: return dispatch_g<64, 2>(p, rows, g, splits, st);
+      case 128: return dispatch_g<128, 2>(p, rows, g, splits, st);
+      case 256: return dispatch_g<256, 2>(p, rows, g, splits, st);
+      default: return SLLM_ERR_UNSUPPORTED_SHAPE;
+    }
+  }
   if (kv_fp8) {
     switch (hd) {
-      case 64: return dispatch_g<64, true>(p, rows, g, splits, st);
-      case 128: return dispatch_g<128, true>(p, rows, g, splits, st);
-      case 256: return dispatch_g<256, true>(p, rows, g, splits, st);
+      case 64: return dispatch_g<64, 1>(p, rows, g, splits, st);
+      case 128: return dispatch_g<128, 1>(p, rows, g, splits, st);
+      case 256: return dispatch_g<256, 1>(p, rows, g, splits, st);
     }
   } else {
     switch (hd) {
-      case 64: return dispatch_g<64, false>(p, rows, g, splits, st);
-      case 128: return dispatch_g<128, false>(p, rows, g, splits, st);
-      case 256: return dispatch_g<256, false>(p, rows, g, splits, st);
+      case 64: return dispatch_g<64, 0>(p, rows, g, splits, st);
+      case 128: return dispatch_g<128, 0>(p, rows, g, splits, st);
+      case 256: return dispatch_g<256, 0>(p, rows, g, splits, st);
     }
   }
   return SLLM_ERR_UNSUPPORTED_SHAPE;

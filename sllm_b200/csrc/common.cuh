@@ -277,6 +277,25 @@ __device__ __forceinline__ void step_trace_end(unsigned long long* rec) {
 #define STEP_TRACE_ASSIGN(p, kind)
 #endif
 
+// ---------------------------------------------------------------- E2M1 (4-bit float: sign | 2-bit exponent | 1-bit mantissa)
+// Values 0, 0.5, 1, 1.5, 2, 3, 4, 6.  Encoding rounds to the nearest value, ties to the even index, saturates at 6
+// and maps NaN to +0, like the host codec.
+__device__ __forceinline__ uint32_t f32_to_e2m1(float v) {
+  if (v != v) return 0u;
+  const float a = fabsf(v);
+  const uint32_t idx = a <= 0.25f ? 0u : a < 0.75f ? 1u : a <= 1.25f ? 2u : a < 1.75f ? 3u : a <= 2.5f ? 4u : a < 3.5f ? 5u
+                                                                                                 : a <= 5.0f ? 6u : 7u;
+  return idx | ((v < 0.f && idx != 0u) ? 8u : 0u);
+}
+__device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
+  const uint32_t e = (code >> 1) & 3u, m = code & 1u;
+  const float mag = e ? __uint_as_float(((126u + e) << 23) | (m << 22)) : 0.5f * static_cast<float>(m);
+  return (code & 8u) ? -mag : mag;
+}
+// Bytes of one NVFP4 KV row of `hd` channels: hd / 2 code bytes (element 2 i in the low nibble of byte i) followed
+// by hd / 16 E4M3 block scales; the fp32 outer scale of the row lives in the scale plane.
+__host__ __device__ constexpr int nvfp4_row_bytes(int hd) { return hd / 2 + hd / 16; }
+
 // ---------------------------------------------------------------- L2 prefetch
 // Requests bytes into L2 with no destination in shared memory and nothing to wait for (16-byte aligned, multiple of 16).
 __device__ __forceinline__ void prefetch_l2_bulk(const void* gsrc, uint32_t bytes) {

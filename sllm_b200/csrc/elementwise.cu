@@ -284,6 +284,35 @@ __global__ void __launch_bounds__(128) rope_kv_append_kernel(const RopeKvParams 
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
   __syncthreads();
   amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  if (p.kv_fp8 == 2) {
+    // ---- NVFP4 row: outer = amax / (448 * 6) (1 for an all-zero row), an E4M3 scale per 16 channels relative to it,
+    // E2M1 codes relative to the decoded block scale (reference: kv_state_kernel.hip.cpp:240-290)
+    const float outer = amax > 0.f ? amax / (kE4M3Max * 6.f) : 1.f;
+    uint8_t* dst = static_cast<uint8_t*>(is_v ? p.v_pages : p.k_pages) + slot * nvfp4_row_bytes(hd);
+    for (int b = threadIdx.x; b < hd / 16; b += blockDim.x) {
+      float bmax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float a = fabsf(rot[16 * b + j]);
+        if (a == a && a <= 3.0e38f) bmax = fmaxf(bmax, a);
+        else if (a > 3.0e38f) bmax = 3.0e38f;               // an infinity saturates the block
+      }
+      const uint8_t sb = f32_to_e4m3(__fdiv_rn(bmax / 6.f, outer));
+      const float bs = e4m3_to_f32(sb) * outer;
+      dst[hd / 2 + b] = sb;
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        uint32_t lo = 0u, hi = 0u;
+        if (bs > 0.f) {
+          lo = f32_to_e2m1(__fdiv_rn(fminf(fmaxf(rot[16 * b + j], -3.0e38f), 3.0e38f), bs));
+          hi = f32_to_e2m1(__fdiv_rn(fminf(fmaxf(rot[16 * b + j + 1], -3.0e38f), 3.0e38f), bs));
+        }
+        dst[8 * b + j / 2] = static_cast<uint8_t>(lo | (hi << 4));
+      }
+    }
+    if (threadIdx.x == 0) (is_v ? p.v_scale : p.k_scale)[slot] = outer;
+    return;
+  }
   const float st = is_v ? p.v_static_scale : p.k_static_scale;
   const float scale = st > 0.f ? st : (amax > 0.f ? amax / kE4M3Max : 1.f);
   uint8_t* dst = static_cast<uint8_t*>(is_v ? p.v_pages : p.k_pages) + slot * hd;
@@ -516,6 +545,8 @@ static int rope_kv_append_impl(void* qkv, const int* positions, const int* seq_i
     return SLLM_ERR_INVALID_ARGUMENT;
   if (hd > 512 || (rotary_dim & 1) || rotary_dim > hd || page_size <= 0) return SLLM_ERR_UNSUPPORTED_SHAPE;
   if (kv_fp8 && k_static_scale <= 0.f && (!k_scale || !v_scale)) return SLLM_ERR_INVALID_ARGUMENT;
+  if (kv_fp8 == 2 && ((hd & 15) || !k_scale || !v_scale)) return SLLM_ERR_INVALID_ARGUMENT;   // NVFP4 rows: outer scale planes
+  if (kv_fp8 < 0 || kv_fp8 > 2) return SLLM_ERR_INVALID_ARGUMENT;
   if (rope_pos3 && (sec_t < 0 || sec_h < 0 || sec_t + sec_h > rotary_dim / 2)) return SLLM_ERR_INVALID_ARGUMENT;
   RopeKvParams p;
   p.qkv = static_cast<__nv_bfloat16*>(qkv);

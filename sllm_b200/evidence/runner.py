@@ -142,7 +142,7 @@ def _attention(size):
     want = ops.paged_attention(q.cpu(), cpu_kv, table.cpu(), seq.cpu(), lens.cpu(), hq, hkv, hd) if batch * ctx <= 4 * 256 else None
     byts = 2 * batch * ctx * hkv * (hd + 4)
     return (lambda: ops.paged_attention(q, kv, table, seq, lens, hq, hkv, hd, max_kv=ctx)), want, byts, 4 * batch * hq * ctx * hd, \
-        {"batch": batch, "ctx": ctx, "hq": hq, "hkv": hkv, "hd": hd, "kv": "fp8"}, (3e-2, 1.5e-2)
+        {"batch": batch, "ctx": ctx, "hq": hq, "hkv": hkv, "hd": hd, "kv": "fp8"}, (5e-2, 4e-2)   # Q and P are E4M3 on the tensor cores
 
 
 def _moe_route(size):

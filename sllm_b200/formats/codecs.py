@@ -320,14 +320,20 @@ def quantize_kv_nvfp4(x: np.ndarray):
     outer = amax / (448 * 6) per (token, head); NaN -> 0, Inf saturates."""
     x = np.nan_to_num(np.asarray(x, dtype=np.float32), nan=0.0, posinf=np.float32(3.0e38), neginf=np.float32(-3.0e38))
     t, h, d = x.shape
+    nb = (d + 15) // 16
     flat = x.reshape(t * h, d)
-    packed = np.zeros((t * h, (d + 1) // 2), dtype=np.uint8)
-    bsc = np.zeros((t * h, (d + 15) // 16), dtype=np.uint8)
-    outer = np.zeros(t * h, dtype=np.float32)
-    for i in range(t * h):
-        p, b, ts = quantize_nvfp4(flat[i:i + 1])
-        packed[i], bsc[i], outer[i] = p[0], b[0], ts
-    return packed.reshape(t, h, -1), bsc.reshape(t, h, -1), outer.reshape(t, h)
+    if nb * 16 != d:
+        flat = np.pad(flat, ((0, 0), (0, nb * 16 - d)))
+    blk = flat.reshape(t * h, nb, 16)
+    mag = np.abs(blk)
+    amax = mag.max(axis=(1, 2))
+    outer = np.where(amax > 0, amax / np.float32(E4M3_MAX * 6.0), np.float32(1.0)).astype(np.float32)
+    bs_codes = encode_e4m3fn((mag.max(axis=2) / np.float32(6.0)) / outer[:, None])
+    bs = decode_e4m3fn(bs_codes) * outer[:, None]
+    safe = np.where(bs > 0, bs, np.float32(1.0))
+    codes = encode_e2m1(blk / safe[:, :, None])
+    codes = np.where((bs > 0)[:, :, None], codes, np.uint8(0)).reshape(t * h, nb * 16)[:, :d]
+    return (pack_nibbles(codes).reshape(t, h, -1), bs_codes.astype(np.uint8).reshape(t, h, -1), outer.reshape(t, h))
 
 
 def round_bf16(x: np.ndarray) -> np.ndarray:

@@ -69,6 +69,8 @@ def eligible(model) -> Optional[str]:
         return "disabled by SLLM_FUSED_DECODE=0"
     if cfg.weight_format != "fp8":
         return "weights are not block-scaled FP8"
+    if cfg.kv_format not in ("bf16", "fp8", "fp8-static"):
+        return "KV-cache format not covered by the fused rotary epilogue"
     if cfg.head_dim != 128 or cfg.qk_norm or cfg.post_norms or cfg.mrope_sections:
         return "head_dim / q-k norm / sandwich norms / multi-axis rotary not covered"
     if cfg.v_norm or cfg.layer_scalar or cfg.attn_scale is not None or cfg.rope_proportional or cfg.rope_theta_local:

