@@ -71,6 +71,9 @@ struct W4Params {
   const float* tok_scale;       // [total_tokens] routing weight per permuted token, or null
   const __nv_bfloat16* residual;  // [total_tokens, ldy] or null
   __nv_bfloat16* y;             // [total_tokens, ldy]
+  // scatter epilogue: when non-null, permuted token row t is stored at address row_ptr[t] (+ feature) instead of
+  // y + t * ldy; the addresses may lie in another GPU's memory (expert-parallel combine: the row goes to its owner)
+  const long long* row_ptr;
   float* ws;                    // split-K partials [splits][total_tokens][n_valid]
   int* counters;                // one per (group, row tile, token tile)
   int* status;
@@ -348,7 +351,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Params p) {
       float v = a * ts;
       if (p.tok_scale) v *= p.tok_scale[tok];
       if (p.residual) v += __bfloat162float(p.residual[static_cast<size_t>(tok) * p.ldy + out_row]);
-      p.y[static_cast<size_t>(tok) * p.ldy + out_row] = __float2bfloat16_rn(v);
+      __nv_bfloat16* dst = p.row_ptr ? reinterpret_cast<__nv_bfloat16*>(p.row_ptr[tok]) + out_row
+                                     : p.y + static_cast<size_t>(tok) * p.ldy + out_row;
+      *dst = __float2bfloat16_rn(v);
     };
 #pragma unroll 1
     for (int cb = 0; cb < BN / 16; ++cb) {
@@ -452,13 +457,13 @@ SLLM_EXPORT int sllm_gemm_w4_read_trace(long long* out1024) {
 // x: bf16 [total_tokens, k] with row stride ldx elements (columns k .. k_pad read as zero); y: bf16 [total_tokens, ldy].
 // fmt 0 = MXFP4, 1 = NVFP4.  bn in {16, 32, 64, 128}.  max_group_tokens bounds the tokens of any group
 // (dense: total_tokens).  Workspace: splits * total_tokens * n_valid floats and one counter per tile when splits > 1.
-SLLM_EXPORT int sllm_gemm_w4(const void* wtiles, const float* tensor_scale, const void* x, void* y,
-                             const void* residual, const int* tok_off, const float* tok_scale, int fmt, int groups,
-                             int n_rows, int n_valid, int k_pad, int k, int ldx, int total_tokens, int max_group_tokens,
-                             int ldy, int bn,
-                             int splits, int stages, float* ws, long long ws_floats, int* counters, int n_counters,
-                             int* status, void* stream) {
-  if (!wtiles || !x || !y || groups <= 0 || n_rows <= 0 || (n_rows % kW4Rows) || n_valid <= 0 ||
+static int gemm_w4_impl(const void* wtiles, const float* tensor_scale, const void* x, void* y,
+                        const void* residual, const int* tok_off, const float* tok_scale, int fmt, int groups,
+                        int n_rows, int n_valid, int k_pad, int k, int ldx, int total_tokens, int max_group_tokens,
+                        int ldy, int bn,
+                        int splits, int stages, float* ws, long long ws_floats, int* counters, int n_counters,
+                        int* status, void* stream, const long long* row_ptr) {
+  if (!wtiles || !x || (!y && !row_ptr) || groups <= 0 || n_rows <= 0 || (n_rows % kW4Rows) || n_valid <= 0 ||
       n_valid > n_rows || k_pad <= 0 || (k_pad % kW4Chunk) || k <= 0 || k > k_pad || ldx < k || (ldx % 8) ||
       total_tokens <= 0 || max_group_tokens <= 0)
     return SLLM_ERR_INVALID_ARGUMENT;
@@ -488,6 +493,7 @@ SLLM_EXPORT int sllm_gemm_w4(const void* wtiles, const float* tensor_scale, cons
   p.wtiles = static_cast<const uint8_t*>(wtiles); p.tensor_scale = tensor_scale; p.tok_off = tok_off;
   p.tok_scale = tok_scale; p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.y = static_cast<__nv_bfloat16*>(y); p.ws = ws; p.counters = counters; p.status = status;
+  p.row_ptr = row_ptr;
   dim3 grid(row_tiles, groups, tok_tiles * splits);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define SLLM_W4_CASE(BNV)                                                                      \
@@ -501,4 +507,28 @@ SLLM_EXPORT int sllm_gemm_w4(const void* wtiles, const float* tensor_scale, cons
   }
 #undef SLLM_W4_CASE
   return SLLM_ERR_UNSUPPORTED_SHAPE;
+}
+
+SLLM_EXPORT int sllm_gemm_w4(const void* wtiles, const float* tensor_scale, const void* x, void* y,
+                             const void* residual, const int* tok_off, const float* tok_scale, int fmt, int groups,
+                             int n_rows, int n_valid, int k_pad, int k, int ldx, int total_tokens, int max_group_tokens,
+                             int ldy, int bn,
+                             int splits, int stages, float* ws, long long ws_floats, int* counters, int n_counters,
+                             int* status, void* stream) {
+  return gemm_w4_impl(wtiles, tensor_scale, x, y, residual, tok_off, tok_scale, fmt, groups, n_rows, n_valid, k_pad, k, ldx,
+                      total_tokens, max_group_tokens, ldy, bn, splits, stages, ws, ws_floats, counters, n_counters, status,
+                      stream, nullptr);
+}
+
+// The same with a scatter epilogue: row t of the result is stored at row_ptr[t] (a device array of bf16 row addresses,
+// 2-byte aligned, possibly in peer memory) instead of y + t * ldy; no residual.
+SLLM_EXPORT int sllm_gemm_w4_scatter(const void* wtiles, const float* tensor_scale, const void* x, const long long* row_ptr,
+                                     const int* tok_off, const float* tok_scale, int fmt, int groups, int n_rows,
+                                     int n_valid, int k_pad, int k, int ldx, int total_tokens, int max_group_tokens, int bn,
+                                     int splits, int stages, float* ws, long long ws_floats, int* counters, int n_counters,
+                                     int* status, void* stream) {
+  if (!row_ptr) return SLLM_ERR_INVALID_ARGUMENT;
+  return gemm_w4_impl(wtiles, tensor_scale, x, nullptr, nullptr, tok_off, tok_scale, fmt, groups, n_rows, n_valid, k_pad, k,
+                      ldx, total_tokens, max_group_tokens, n_valid, bn, splits, stages, ws, ws_floats, counters, n_counters,
+                      status, stream, row_ptr);
 }

@@ -322,9 +322,194 @@ __global__ void moe_combine_allreduce_kernel(EpPeers pe, const __nv_bfloat16* __
   }
 }
 
+// ------------------------------------------------------------------------------------------------ owner combine
+// Expert parallelism with token owners.  Rank r owns the tokens [r tpr, (r + 1) tpr).  The down-projection GEMM of
+// every rank stores each routed row (route weight applied) straight into the OWNER's receive slot (token, j) over
+// NVLink - slot j of a token belongs to the j-th expert of its top-k list, written by the one rank that holds that
+// expert - so a rank sends only the rows its experts produced, once, to one peer.  Then:
+//   signal  (1 CTA)  after the GEMM: system fence, "my rows have landed" flag at every peer
+//   reduce  owners wait for all ranks' flags (bounded), sum their tokens' k slots in slot order (+ residual) and
+//           store the finished row into every rank's gather buffer; the last CTA raises "my tokens are out"
+//   finish  waits for all ranks' gather flags (bounded) and copies the gathered rows out
+// Per step a rank sends (rows its experts produced) + (world - 1) tpr rows, instead of (world - 1) T rows when every
+// rank pushed a full partial to every peer.  Slots and gather rows alternate between two parities per call.
+// No counterpart in the reference, which has no multi-GPU path (its fused single-GPU pair is
+// native/hip/src/moe_expert_kernel.hip.cpp:88 gate/up + SiLU and :176 down + route weight + combine).
+struct EpOwner {
+  int world, rank;
+  __nv_bfloat16* recv[8];     // recv[p]: rank p's slots [2][tpr_cap * top_k_cap * d]
+  __nv_bfloat16* gath[8];     // gath[p]: rank p's gather buffer [2][max_tokens * d]
+  uint32_t* flags[8];         // flags[p]: rank p's flags [2][world]: rows landed / tokens out, per source rank
+  long long recv_cap, gath_cap;   // elements per parity
+};
+
+__global__ void moe_owner_plan_kernel(EpOwner pe, const int* __restrict__ perm_dst, int tokens, int top_k, int d, int tpr,
+                                      const uint32_t* __restrict__ epoch, long long* __restrict__ row_ptr) {
+  pdl_wait();
+  pdl_trigger();
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= tokens * top_k) return;
+  const int p = perm_dst[a];
+  if (p < 0) return;                       // another rank holds that expert
+  const int t = a / top_k, j = a - t * top_k;
+  const int owner = t / tpr, tl = t - owner * tpr;
+  const uint32_t e = epoch[0] + 1;         // the call in progress; the signal kernel publishes it
+  row_ptr[p] = reinterpret_cast<long long>(pe.recv[owner] + static_cast<long long>(e & 1) * pe.recv_cap +
+                                           (static_cast<long long>(tl) * top_k + j) * d);
+}
+
+__global__ void moe_owner_signal_kernel(EpOwner pe, uint32_t* epoch) {
+  pdl_wait();
+  pdl_trigger();
+  const uint32_t e = epoch[0] + 1;
+  __threadfence_system();
+  if (threadIdx.x < pe.world) st_release_sys(pe.flags[threadIdx.x] + pe.rank, e);
+  __syncthreads();
+  if (threadIdx.x == 0) epoch[0] = e;
+}
+
+// Bounded wait of thread `src` (< world) for flag word `kind * world + src` of this rank; false when it gave up.
+__device__ __forceinline__ bool owner_wait(const EpOwner& pe, int kind, int src, uint32_t e, int* status) {
+  const uint32_t* f = pe.flags[pe.rank] + kind * pe.world + src;
+  uint32_t spins = 0;
+  long long tstart = 0;
+  while (static_cast<int32_t>(ld_acquire_sys_(f) - e) < 0) {
+    ++spins;
+    if (spins == 1024) tstart = clock64();
+    if (spins > 1024 && (spins & 63) == 0 && clock64() - tstart > kWaitLimitCycles) {
+      if (status) atomicCAS(status, 0, SLLM_DEV_TIMEOUT_PEER_FLAG);
+      return false;
+    }
+  }
+  return true;
+}
+
+__global__ void moe_owner_reduce_kernel(EpOwner pe, int top_k, const __nv_bfloat16* __restrict__ residual, int tokens,
+                                        int d, int tpr, int rows_per_block, const uint32_t* __restrict__ epoch,
+                                        int* counter, int* status) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int s_ok;
+  const uint32_t e = epoch[0];
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < pe.world && !owner_wait(pe, 0, threadIdx.x, e, status)) s_ok = 0;
+  __syncthreads();
+  const int t_lo = pe.rank * tpr;
+  const int t_hi = min(tokens, t_lo + tpr);
+  const int t0 = t_lo + blockIdx.x * rows_per_block;
+  const int t1 = min(t_hi, t0 + rows_per_block);
+  const int vec = d / 8;
+  if (s_ok && t0 < t1) {
+    const __nv_bfloat16* slots = pe.recv[pe.rank] + static_cast<long long>(e & 1) * pe.recv_cap;
+    const long long goff = static_cast<long long>(e & 1) * pe.gath_cap;
+    for (int i = threadIdx.x; i < (t1 - t0) * vec; i += blockDim.x) {
+      const int t = t0 + i / vec, c = i % vec;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      const __nv_bfloat16* row = slots + static_cast<long long>(t - t_lo) * top_k * d;
+      for (int j = 0; j < top_k; ++j) add8(acc, __ldcg(reinterpret_cast<const uint4*>(row + static_cast<long long>(j) * d) + c));
+      if (residual) add8(acc, reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * d)[c]);
+      const uint4 o = pack8(acc);
+      for (int p = 0; p < pe.world; ++p)
+        *reinterpret_cast<uint4*>(pe.gath[p] + goff + static_cast<long long>(t) * d + c * 8) = o;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(counter, 1);
+    s_ok = (prev == static_cast<int>(gridDim.x) - 1) ? 2 : 0;
+    if (s_ok == 2) *counter = 0;
+  }
+  __syncthreads();
+  // the last CTA of this rank: every row of its tokens is on its way to every peer
+  if (s_ok == 2) {
+    __threadfence_system();
+    if (threadIdx.x < pe.world) st_release_sys(pe.flags[threadIdx.x] + pe.world + pe.rank, e);
+  }
+}
+
+__global__ void moe_owner_finish_kernel(EpOwner pe, __nv_bfloat16* __restrict__ y, int tokens, int d, int rows_per_block,
+                                        const uint32_t* __restrict__ epoch, int* status) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int s_ok;
+  const uint32_t e = epoch[0];
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < pe.world && !owner_wait(pe, 1, threadIdx.x, e, status)) s_ok = 0;
+  __syncthreads();
+  if (!s_ok) return;
+  const int t0 = blockIdx.x * rows_per_block, t1 = min(tokens, t0 + rows_per_block);
+  const int vec = d / 8;
+  const uint4* src = reinterpret_cast<const uint4*>(pe.gath[pe.rank] + static_cast<long long>(e & 1) * pe.gath_cap);
+  for (int i = threadIdx.x; i < (t1 - t0) * vec; i += blockDim.x)
+    reinterpret_cast<uint4*>(y)[static_cast<size_t>(t0) * vec + i] = __ldcg(src + static_cast<size_t>(t0) * vec + i);
+}
+
 }  // namespace sllm
 
 using namespace sllm;
+
+static int owner_desc(EpOwner* pe, void* const* recv, void* const* gath, void* const* flags, int world, int rank,
+                      long long recv_cap, long long gath_cap) {
+  if (!recv || !gath || !flags || world < 1 || world > 8 || rank < 0 || rank >= world || recv_cap <= 0 || gath_cap <= 0)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  pe->world = world; pe->rank = rank; pe->recv_cap = recv_cap; pe->gath_cap = gath_cap;
+  for (int i = 0; i < world; ++i) {
+    if (!recv[i] || !gath[i] || !flags[i]) return SLLM_ERR_INVALID_ARGUMENT;
+    pe->recv[i] = static_cast<__nv_bfloat16*>(recv[i]);
+    pe->gath[i] = static_cast<__nv_bfloat16*>(gath[i]);
+    pe->flags[i] = static_cast<uint32_t*>(flags[i]);
+  }
+  return SLLM_OK;
+}
+
+// Step 1 of the owner combine: destination address of every local permuted row (perm_dst from sllm_moe_permute) in
+// its token owner's receive slots, for the scatter epilogue of the down-projection GEMM (sllm_gemm_w4_scatter).
+// tpr = tokens per rank (ceil(tokens / world)); epoch: one device word, zero before the first call.
+SLLM_EXPORT int sllm_moe_owner_plan(void* const* recv, void* const* gath, void* const* flags, int world, int rank,
+                                    long long recv_cap, long long gath_cap, const int* perm_dst, int tokens, int top_k, int d,
+                                    int tpr, const void* epoch, long long* row_ptr, void* stream) {
+  EpOwner pe;
+  const int rc = owner_desc(&pe, recv, gath, flags, world, rank, recv_cap, gath_cap);
+  if (rc != SLLM_OK) return rc;
+  if (!perm_dst || !epoch || !row_ptr || tokens <= 0 || top_k <= 0 || d <= 0 || (d % 8) || tpr <= 0 ||
+      static_cast<long long>(tpr) * world < tokens || static_cast<long long>(tpr) * top_k * d > recv_cap ||
+      static_cast<long long>(tokens) * d > gath_cap)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  const int n = tokens * top_k;
+  cudaError_t e = launch_kernel(moe_owner_plan_kernel, dim3((n + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), 1u,
+                                pe, perm_dst, tokens, top_k, d, tpr, static_cast<const uint32_t*>(epoch), row_ptr);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+// Steps 2-4, launched after the scatter GEMM on the same stream: signal, reduce + gather, finish (see above).
+// y: bf16 [tokens, d] result on this rank; counter: one zeroed device int.
+SLLM_EXPORT int sllm_moe_owner_combine(void* const* recv, void* const* gath, void* const* flags, int world, int rank,
+                                       long long recv_cap, long long gath_cap, int top_k, const void* residual, void* y,
+                                       int tokens, int d, int tpr, int rows_per_block, void* epoch, int* counter, int* status,
+                                       void* stream) {
+  EpOwner pe;
+  const int rc = owner_desc(&pe, recv, gath, flags, world, rank, recv_cap, gath_cap);
+  if (rc != SLLM_OK) return rc;
+  if (!y || !epoch || !counter || tokens <= 0 || top_k <= 0 || d <= 0 || (d % 8) || tpr <= 0 || rows_per_block <= 0 ||
+      static_cast<long long>(tpr) * world < tokens)
+    return SLLM_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (launch_kernel(moe_owner_signal_kernel, dim3(1), dim3(32), 0, st, 1u, pe, static_cast<uint32_t*>(epoch)) != cudaSuccess)
+    return SLLM_ERR_CUDA;
+  const int own_blocks = (tpr + rows_per_block - 1) / rows_per_block;
+  if (launch_kernel(moe_owner_reduce_kernel, dim3(own_blocks), dim3(256), 0, st, 1u, pe, top_k,
+                    static_cast<const __nv_bfloat16*>(residual), tokens, d, tpr, rows_per_block,
+                    static_cast<const uint32_t*>(epoch), counter, status) != cudaSuccess)
+    return SLLM_ERR_CUDA;
+  const int blocks = (tokens + rows_per_block - 1) / rows_per_block;
+  if (launch_kernel(moe_owner_finish_kernel, dim3(blocks), dim3(256), 0, st, 1u, pe, static_cast<__nv_bfloat16*>(y), tokens, d,
+                    rows_per_block, static_cast<const uint32_t*>(epoch), status) != cudaSuccess)
+    return SLLM_ERR_CUDA;
+  return SLLM_OK;
+}
 
 SLLM_EXPORT int sllm_moe_route(const void* logits, int ld, int tokens, int experts, int top_k, int softmax_all,
                                int* out_idx, float* out_w, void* stream) {

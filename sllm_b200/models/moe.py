@@ -147,8 +147,7 @@ class MoeModel:
             x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
             logits = ops.linear(x, lw.router)
             idx, rw = M.route(logits[:, :cfg.n_experts], cfg.top_k)
-            yp, perm_dst = M.experts_forward(x, idx, rw, lw.gate_up, lw.down, cfg.act, self.e_lo, self.e_hi)
-            h = self.ep.combine(yp, perm_dst, h)
+            h = self.ep.experts_combine(x, idx, rw, lw.gate_up, lw.down, cfg.act, self.e_lo, self.e_hi, h)
             if lw.shared_gate_up is not None:
                 # replicated on every rank: the shared expert is a few percent of a layer's bytes
                 sh = ops.linear(ops.gated_act(ops.linear(x, lw.shared_gate_up), cfg.act), lw.shared_down)

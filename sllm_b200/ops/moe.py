@@ -20,6 +20,8 @@ _SIGS = {
     "sllm_moe_gather": (I, [P, I, P, P, I, P, I, I, P]),
     "sllm_moe_combine": (I, [P, P, I, P, P, I, I, P]),
     "sllm_moe_shared_add": (I, [P, P, P, I, P, I, I, P]),
+    "sllm_moe_owner_plan": (I, [P, P, P, I, I, L, L, P, I, I, I, I, P, P, P]),
+    "sllm_moe_owner_combine": (I, [P, P, P, I, I, L, L, I, P, P, I, I, I, I, P, P, P, P]),
     "sllm_moe_combine_allreduce": (I, [P, P, I, I, P, P, I, P, P, I, I, I, L, I, P, P, P]),
 }
 

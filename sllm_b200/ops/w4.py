@@ -193,7 +193,8 @@ def _bn_for(tokens: int) -> int:
 
 
 def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = None, tok_off: Optional[torch.Tensor] = None,
-              tok_scale: Optional[torch.Tensor] = None, max_group_tokens: Optional[int] = None, splits: int = 0) -> torch.Tensor:
+              tok_scale: Optional[torch.Tensor] = None, max_group_tokens: Optional[int] = None, splits: int = 0,
+              row_ptr: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """y[t, :] = x[t, :] @ W_g(t)^T (* tok_scale[t]) (+ residual).  Dense when tok_off is None (groups must be 1);
     grouped otherwise: tokens of group g are rows tok_off[g] .. tok_off[g + 1] of x."""
     t, k = x.shape
@@ -232,6 +233,18 @@ def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = N
     if _lib.audit_enabled():
         _lib.record_dispatch("linear_w4", "gemm_w4_kernel", fmt=w.fmt, tokens=t, n=w.n, k=w.k, groups=w.groups,
                              grouped=tok_off is not None, bn=bn, splits=splits)
+    if row_ptr is not None:
+        # scatter epilogue: result row t goes to the bf16 row at address row_ptr[t] (int64, may be peer memory)
+        if residual is not None or row_ptr.dtype != torch.int64 or row_ptr.numel() < t:
+            raise ValueError("row_ptr: int64 addresses, one per token row, and no residual")
+        _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_gemm_w4_scatter", (I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I,
+                                                                           I, P, L, P, I, P, P]))
+        rc = _lib.kernels().sllm_gemm_w4_scatter(_p(w.tiles), _p(w.tensor_scale), _p(x), _p(row_ptr), _p(tok_off),
+                                                 _p(tok_scale), 0 if w.fmt == "mxfp4" else 1, w.groups, w.n_rows, w.n, w.k_pad,
+                                                 w.k, x.stride(0), t, mgt, bn, splits, 0, _p(wsp.ws), wsp.ws.numel(),
+                                                 _p(wsp.counters), wsp.counters.numel(), _p(wsp.status), _stream())
+        _lib.check(rc, "gemm_w4_scatter")
+        return None
     rc = _lib.kernels().sllm_gemm_w4(_p(w.tiles), _p(w.tensor_scale), _p(x), _p(y), _p(residual), _p(tok_off),
                                      _p(tok_scale), 0 if w.fmt == "mxfp4" else 1, w.groups, w.n_rows, w.n, w.k_pad, w.k,
                                      x.stride(0), t, mgt, y.stride(0), bn, splits, 0, _p(wsp.ws), wsp.ws.numel(),

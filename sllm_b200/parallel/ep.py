@@ -1,10 +1,14 @@
 """Expert parallelism: which experts a rank owns and how the expert outputs are combined across ranks.
 
 Activations are replicated across the expert-parallel ranks (they leave the attention all-reduce that way), so
-"dispatch" is a local gather of the tokens routed to this rank's experts; "combine" adds the ranks' partial
-outputs.  `FusedEP` does the combine in ONE kernel that stores each partial token block into every peer's
-receive slot over NVLink and sums in rank order (csrc/moe.cu: moe_combine_allreduce); `NcclEP` is the unfused
-baseline (local combine kernel + NCCL all-reduce).  The reference has no expert parallelism
+"dispatch" needs no transfer: a rank gathers the tokens routed to its experts locally.  "Combine" is where bytes
+move.  `FusedEP.experts_combine` runs the token-owner path (csrc/moe.cu, "owner combine"): the down-projection GEMM
+of every rank stores each routed row, route weight applied, straight into the receive slot of the token's OWNER over
+NVLink (scatter epilogue of the grouped W4 GEMM); owners sum their tokens' top-k slots in slot order, add the
+residual and store the finished rows into every rank's gather buffer.  A rank sends the rows its experts produced
+plus its own tokens' results, instead of a full partial of every token to every peer (`FusedEP.combine`, the earlier
+all-reduce form, kept for callers that hold permuted expert outputs already).  `NcclEP` is the unfused baseline
+(local combine kernel + NCCL all-reduce).  The reference has no expert parallelism
 (docs/architecture/runtime.md:554 "no multi-GPU path").
 """
 from __future__ import annotations
@@ -26,6 +30,11 @@ class NoEP:
 
     def combine(self, yp, perm_dst, residual):
         return M.combine(yp, perm_dst, residual)
+
+    def experts_combine(self, x, idx, rw, gate_up, down, act: str, e_lo: int, e_hi: int, residual):
+        """Routed experts of this rank on `x` and the sum over all ranks (+ residual): the MoE block after routing."""
+        yp, perm_dst = M.experts_forward(x, idx, rw, gate_up, down, act, e_lo, e_hi)
+        return self.combine(yp, perm_dst, residual)
 
 
 class NcclEP(NoEP):
@@ -72,6 +81,18 @@ class FusedEP(NcclEP):
         self._recv = self.region.peer_array(self.off_recv)
         self._flags = self.region.peer_array(self.off_flags)
         self.epoch = torch.zeros(self.max_blocks, dtype=torch.int32, device=device)
+        # token-owner path: receive slots [2][tokens per rank x top-k x d], gather buffer [2][tokens x d], two flag rows
+        self.top_k_cap = 8
+        self.tpr_cap = (max_tokens + size - 1) // size
+        self.slot_cap = self.tpr_cap * self.top_k_cap * d_model
+        slot_bytes, gath_bytes, oflag_bytes = 2 * self.slot_cap * 2, 2 * self.cap * 2, 2 * size * 4
+        self.owner_region = SymmetricRegion(slot_bytes + gath_bytes + oflag_bytes + 4096, size, rank, group)
+        self._oslots = self.owner_region.peer_array(self.owner_region.carve(slot_bytes))
+        self._ogath = self.owner_region.peer_array(self.owner_region.carve(gath_bytes))
+        self._oflags = self.owner_region.peer_array(self.owner_region.carve(oflag_bytes))
+        self.owner_epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.owner_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.owner_path = True
 
     def combine(self, yp, perm_dst, residual):
         t, k = perm_dst.shape
@@ -86,9 +107,38 @@ class FusedEP(NcclEP):
         _lib.check(rc, "moe_combine_allreduce")
         return y
 
+    def experts_combine(self, x, idx, rw, gate_up, down, act: str, e_lo: int, e_hi: int, residual):
+        t, k = idx.shape
+        if not (self.owner_path and x.is_cuda and t <= self.max_tokens and k <= self.top_k_cap and down.n == self.d):
+            if x.is_cuda:
+                _lib.note_fallback("ep_owner_combine:outside_limits")
+            return super().experts_combine(x, idx, rw, gate_up, down, act, e_lo, e_hi, residual)
+        from ..ops import core
+        from ..ops.core import _p, _stream, workspace
+        from ..ops.w4 import linear_w4
+        lib = M._k()
+        P, I, L = C.c_void_p, C.c_int, C.c_longlong
+        tok_off, perm_src, perm_dst, perm_w = M.permute(idx, rw, e_lo, e_hi)
+        xp = M.gather(x, perm_src, tok_off)
+        a = core.gated_act(linear_w4(xp, gate_up, tok_off=tok_off, max_group_tokens=t), act)
+        tpr = (t + self.size - 1) // self.size
+        row_ptr = torch.empty(t * k, dtype=torch.int64, device=x.device)
+        peers = (C.cast(self._oslots, P), C.cast(self._ogath, P), C.cast(self._oflags, P), self.size, self.rank,
+                 self.slot_cap, self.cap)
+        rc = lib.sllm_moe_owner_plan(*peers, _p(perm_dst), t, k, self.d, tpr, _p(self.owner_epoch), _p(row_ptr), _stream())
+        _lib.check(rc, "moe_owner_plan")
+        # the down projection stores every routed row (route weight applied) into its owner's slot, on whatever GPU
+        linear_w4(a, down, tok_off=tok_off, tok_scale=perm_w, max_group_tokens=t, row_ptr=row_ptr)
+        y = torch.empty((t, self.d), dtype=torch.bfloat16, device=x.device)
+        rc = lib.sllm_moe_owner_combine(*peers, k, _p(residual), _p(y), t, self.d, tpr, self.rows_per_block,
+                                        _p(self.owner_epoch), _p(self.owner_counter), _p(workspace(x.device).status), _stream())
+        _lib.check(rc, "moe_owner_combine")
+        return y
+
     def close(self):
         if self.region is not None:
             torch.cuda.synchronize()
             dist.barrier(group=self.group)
             self.region.close()
+            self.owner_region.close()
             self.region = None

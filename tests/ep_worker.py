@@ -57,6 +57,12 @@ def main():
             dist.all_gather(parts, got_f)
             for p in parts:
                 assert torch.equal(p, parts[0]), "ranks disagree"
+            # token-owner path: rows leave the down-projection epilogue for their owner, owners sum and gather
+            got_o = fused.experts_combine(x, idx, rw, mine.gate_up, mine.down, cfg.act, e_lo, e_hi, res)
+            assert rel(got_o, want) < 1.5e-2, ("owner", t, rep, rel(got_o, want))
+            dist.all_gather(parts, got_o)
+            for p in parts:
+                assert torch.equal(p, parts[0]), "ranks disagree (owner path)"
     assert ops.device_status(dev) == 0
     # end to end: EP + TP MoE engine reproduces the single-GPU greedy tokens on every rank
     g = torch.Generator().manual_seed(5)
