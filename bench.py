@@ -48,6 +48,11 @@ def parse_args():
                     help="speculative decoding: draft tokens per step from a llama-draft model (acceptance forced by a "
                          "seeded Bernoulli(0.7) mask so that the full verify compute always runs)")
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "tp", "dp"],
+                    help="N > 1: tp = one model sharded over the GPUs (fused GEMM + all-reduce), dp = one replica per GPU, "
+                         "each decoding batch / N of the sequences (no communication inside a step); auto = dp when the "
+                         "weights are small enough that a replica per GPU streams less per token than the sharded "
+                         "model's per-kernel floor costs (dense models under 16 GiB of weights), else tp")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: override the layer count")
     ap.add_argument("--no-batch1", action="store_true", help="skip the extra batch-1 measurement")
     return ap.parse_args()
@@ -287,6 +292,14 @@ def model_forward_rows(model, tokens, row0: int, start: int):
         model.k, model.v = k_full, v_full
 
 
+def _estimate_weight_bytes(cfg) -> float:
+    """Resident weight bytes of a dense decoder of this shape in its weight format (embedding and head included)."""
+    per = {"fp32": 4.0, "bf16": 2.0, "fp8": 1.0 + 4.0 / 128, "nvfp4": 0.5 + 1.0 / 16, "mxfp4": 0.5 + 1.0 / 32}.get(cfg.weight_format, 2.0)
+    d = cfg.d_model
+    layer = (cfg.q_size + 2 * cfg.kv_size) * d + d * cfg.q_size + 3 * cfg.ffn * d
+    return cfg.n_layers * layer * per + (1 if cfg.tie_embeddings else 2) * cfg.vocab * d * per
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -325,12 +338,20 @@ def main():
         cfg.name += f"-{args.layers}layers-PROFILING-ONLY"
     total_ctx = args.prompt + args.warmup + 2 * args.steps + 64
     cfg.max_context = ((total_ctx + 255) // 256) * 256
+    weight_gib = _estimate_weight_bytes(cfg) / 2 ** 30
+    layout = args.parallelism
+    if layout == "auto":
+        layout = "dp" if (world > 1 and cfg.family != "moe" and weight_gib < 16 and args.batch % world == 0
+                          and args.spec_width == 0) else "tp"
+    if layout == "dp" and (world == 1 or args.batch % world or cfg.family == "moe"):
+        layout = "tp"
+    replicas = world if layout == "dp" else 1
     tp = None
-    if world > 1:
+    if world > 1 and layout == "tp":
         from sllm_b200.parallel.tp import make_tp
         tp = make_tp(world, rank, device, impl=args.tp_impl, max_tokens=max(args.batch, 128), d_model=cfg.d_model)
     ep = None
-    if world > 1 and cfg.family == "moe":
+    if world > 1 and layout == "tp" and cfg.family == "moe":
         from sllm_b200.parallel.ep import FusedEP, NcclEP
         ep = FusedEP(world, rank, device, max(args.batch, 128), cfg.d_model) if args.tp_impl == "fused" \
             else NcclEP(world, rank, device)
@@ -426,7 +447,8 @@ def main():
 
     if args.spec_width > 0:
         return run_speculative(args, cfg, device, tp, world, rank, barrier, max_over_ranks, ClockSampler(local_rank))
-    main_res = measure(args.batch, args.steps, args.warmup, True)
+    # data parallel: every rank is a replica decoding its share of the sequences; the step time is the slowest rank's
+    main_res = measure(args.batch // replicas, args.steps, args.warmup, True)
     extra = None
     if not args.no_batch1 and args.batch != 1:
         extra = measure(1, min(args.steps, 64), max(3, min(args.warmup, 4)), False)
@@ -456,14 +478,18 @@ def main():
                      if args.synthetic_kv else ""),
             "config": {"model": f"{cfg.name}-{args.weights}", "global_batch": args.batch,
                        "seq_len": args.prompt, "output_tokens": k, "kv_cache": f"{args.kv}-paged-16",
-                       "parallelism": (f"tp{args.gpus}+ep{args.gpus}" if cfg.family == "moe" else f"tp{args.gpus}") +
-                                      (f"-{args.tp_impl}" if args.gpus > 1 else ""),
+                       "parallelism": (f"dp{args.gpus}" if layout == "dp" else
+                                       (f"tp{args.gpus}+ep{args.gpus}" if cfg.family == "moe" else f"tp{args.gpus}") +
+                                       (f"-{args.tp_impl}" if args.gpus > 1 else "")),
+                       "parallelism_note": ("one replica per GPU, each decoding global_batch / N sequences; launches and "
+                                            "copied bytes are job totals" if layout == "dp" else
+                                            "one model sharded over the GPUs"),
                        "l2": "each step streams the full weight set (>> 126 MB L2); no flush needed"},
             "clocks": main_res["clocks"],
             "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "ms_per_step": round(main_res["e2e_ms"] / k, 4),
-                    "h2d_bytes_per_step": int(main_res["h2d"]), "d2h_bytes_per_step": int(main_res["d2h"]),
+                    "h2d_bytes_per_step": int(main_res["h2d"]) * replicas, "d2h_bytes_per_step": int(main_res["d2h"]) * replicas,
                     "api": "sllm_b200.engine.Engine.decode"},
-            "gpu_launches": int(main_res["launches_per_step"] * k),
+            "gpu_launches": int(main_res["launches_per_step"] * k) * replicas,
             "ttft_ms_batch_prefill": round(main_res["prefill_ms"], 2),
             "itl_ms": round(main_res["e2e_ms"] / k, 4),
             "device_status": main_res["status"],
