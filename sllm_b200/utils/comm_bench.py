@@ -10,7 +10,12 @@ Three pairs, Llama-3-8B decode shapes by default, bf16, one line of JSON per pai
                   producer pulls the peers' shards) vs ncclAllGather + GEMM
   ep_combine      expert-parallel combine of rows x top-4 expert outputs (fused: weighted sum + cross-rank sum in one
                   kernel over peer memory) vs local combine + ncclAllReduce
-Times are CUDA events around `iters` back-to-back calls after warm-up, max over ranks.  The roofline of a pair is the
+  ep_experts      the whole MoE block after routing at the 120B-class expert shape (permute, gather, grouped MXFP4
+                  gate_up, SiLU*up, grouped down projection, combine): token-owner path (rows leave the down-projection
+                  epilogue for their owner's slots, owners sum and gather) vs the all-reduce form (every rank pushes a
+                  full partial to every peer) vs local combine + ncclAllReduce
+Times are CUDA events around one replay of a CUDA graph that holds `iters` back-to-back calls (`--eager` times eager
+calls instead), after warm-up, max over ranks.  The roofline of a pair is the
 slower of (weight bytes / measured copy bandwidth) and (bytes that must cross NVLink per GPU / 770 GB/s).
 """
 from __future__ import annotations
@@ -35,6 +40,9 @@ def _hbm_gbs():
         return HBM_GBS_FALLBACK, "of fallback"
 
 
+_EAGER = [False]
+
+
 def _time(fn, iters: int, warmup: int = 5) -> float:
     for _ in range(warmup):
         fn()
@@ -42,10 +50,26 @@ def _time(fn, iters: int, warmup: int = 5) -> float:
     dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        fn()
-    e1.record()
+    if _EAGER[0]:
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+    else:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(iters):
+                    fn()
+            g.replay()                      # first replay: uploads the graph
+            side.synchronize()
+            dist.barrier()
+            e0.record(side)
+            g.replay()
+            e1.record(side)
+            side.synchronize()
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1) * 1000.0 / iters], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -58,7 +82,10 @@ def main(argv=None) -> int:
     ap.add_argument("--d", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA graph replay")
+    ap.add_argument("--moe-rows", type=int, default=64)
     a = ap.parse_args(argv)
+    _EAGER[0] = a.eager
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
@@ -115,16 +142,48 @@ def main(argv=None) -> int:
     link_bytes = m * d * 2 * (world - 1)
     out.append({"op": "ep_combine", "fused_us": t_f, "nccl_us": t_n, "roofline_us": link_bytes / NVLINK_GBS / 1e3,
                 "nvlink_bytes_per_gpu": link_bytes})
+    # ---- the MoE block after routing, 120B-class expert shape (d 2880, expert ffn 2880, 128 experts, top-4, MXFP4)
+    from ..ops import moe as M
+    from ..ops.w4 import W4Weight
+    md, mf, n_exp, mk, rows = 2880, 2880, 128, 4, a.moe_rows
+    per = n_exp // world
+    e_lo, e_hi = rank * per, (rank + 1) * per
+    g2 = torch.Generator(device=dev).manual_seed(100 + rank)
+    gate_up = W4Weight.quantize_device("mxfp4", (torch.randn(per, 2 * mf, md, device=dev, generator=g2) * 0.02).bfloat16())
+    down = W4Weight.quantize_device("mxfp4", (torch.randn(per, md, mf, device=dev, generator=g2) * 0.02).bfloat16())
+    gx = torch.Generator(device=dev).manual_seed(7)          # the same tokens and routing on every rank
+    xm = (torch.randn(rows, md, device=dev, generator=gx)).bfloat16()
+    resm = (torch.randn(rows, md, device=dev, generator=gx)).bfloat16()
+    idx_m, rw_m = M.route((torch.randn(rows, n_exp, device=dev, generator=gx)).bfloat16(), mk)
+    fo = FusedEP(world, rank, dev, max(rows, 128), md)
+    t_o = _time(lambda: fo.experts_combine(xm, idx_m, rw_m, gate_up, down, "silu", e_lo, e_hi, resm), a.iters)
+    fo.owner_path = False
+    t_a = _time(lambda: fo.experts_combine(xm, idx_m, rw_m, gate_up, down, "silu", e_lo, e_hi, resm), a.iters)
+    t_n = _time(lambda: ne.experts_combine(xm, idx_m, rw_m, gate_up, down, "silu", e_lo, e_hi, resm), a.iters)
+    mine_rows = int(((idx_m >= e_lo) & (idx_m < e_hi)).sum().item())
+    tpr = (rows + world - 1) // world
+    owner_bytes = (mine_rows + tpr * (world - 1)) * md * 2       # routed rows to their owners (upper bound: all remote) + own tokens to every peer
+    w_bytes = (gate_up.nbytes() + down.nbytes())
+    out.append({"op": "ep_experts", "fused_us": t_o, "allreduce_form_us": t_a, "nccl_us": t_n,
+                "roofline_us": max(w_bytes / hbm / 1e3, owner_bytes / NVLINK_GBS / 1e3), "weight_mb": w_bytes / 1e6,
+                "nvlink_bytes_per_gpu": owner_bytes, "nvlink_bytes_per_gpu_allreduce_form": rows * md * 2 * (world - 1),
+                "rows": rows, "top_k": mk, "experts_per_rank": per})
     status = ops.device_status(dev)
     torch.cuda.synchronize()
+    fo.close()
     gg.close()
     fe.close()
     fused_tp.close()
     if rank == 0:
         for o in out:
-            o.update({"world": world, "rows": m, "d": d, "speedup_vs_nccl": round(o["nccl_us"] / o["fused_us"], 3),
+            o.setdefault("rows", m)
+            o.setdefault("d", d)
+            o.update({"world": world, "timed": "eager" if a.eager else "graph replay",
+                      "speedup_vs_nccl": round(o["nccl_us"] / o["fused_us"], 3),
                       "fraction_of_roofline": round(o["roofline_us"] / o["fused_us"], 3), "fraction_basis": basis,
                       "device_status": status})
+            if "allreduce_form_us" in o:
+                o["allreduce_form_us"] = round(o["allreduce_form_us"], 2)
             o["fused_us"], o["nccl_us"], o["roofline_us"] = (round(o[k], 2) for k in ("fused_us", "nccl_us", "roofline_us"))
             print(json.dumps(o), flush=True)
     dist.barrier()
