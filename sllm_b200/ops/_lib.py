@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
+from typing import Optional
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent.parent
@@ -77,7 +78,7 @@ _cuda_present = [None]
 def on_cpu(t) -> bool:
     """True when the op should take its CPU oracle branch for tensor ``t``.  Raises in fail-closed mode; on a machine
     that has a GPU the detour is recorded as a fallback."""
-    if t.is_cuda:
+    if t.is_cuda or _fake[0] is not None:
         return False
     if fail_closed():
         raise KernelError("CUDA kernels are required (fail-closed mode): the op was handed a CPU tensor")
@@ -160,9 +161,54 @@ def kernels_available() -> bool:
     return _KERNEL_PATH.exists()
 
 
+# ---------------------------------------------------------------------------------------------- fake device layer
+class FakeKernelLibrary:
+    """Programmable stand-in for the kernel library (reference: native/hip/tests/fake_hip/fake_hip_runtime.cpp).
+
+    Every entry point of the signature tables exists; a call is recorded as (name, args) and returns the next status
+    scripted for that name (`script = {"sllm_gemm": [0, 0, 9]}`: the third GEMM launch is rejected with status 9;
+    an exhausted or missing script means 0).  Nothing is computed and no pointer is dereferenced, so it runs on a
+    machine without a GPU: while a fake is installed the ops take their device branch for CPU tensors too (outputs are
+    allocated but not written).  Used to test what the layers above do with launch failures."""
+
+    def __init__(self, script: Optional[dict] = None):
+        self.script = {k: list(v) for k, v in (script or {}).items()}
+        self.calls: list = []
+
+    def __getattr__(self, name: str):
+        if name.startswith("__") or (name not in _KERNEL_SIGNATURES and name not in EXTRA_KERNEL_SIGNATURES):
+            raise AttributeError(name)
+        restype = (_KERNEL_SIGNATURES.get(name) or EXTRA_KERNEL_SIGNATURES.get(name))[0]
+
+        def call(*args):
+            self.calls.append((name, args))
+            if restype is None:
+                return None
+            pending = self.script.get(name)
+            return pending.pop(0) if pending else 0
+        return call
+
+    def count(self, name: str) -> int:
+        return sum(1 for n, _ in self.calls if n == name)
+
+
+_fake = [None]
+
+
+def install_fake(fake: Optional[FakeKernelLibrary]) -> None:
+    """Routes every kernel call to `fake` (None restores the real library)."""
+    _fake[0] = fake
+
+
+def fake_active() -> bool:
+    return _fake[0] is not None
+
+
 def kernels():
     """The CUDA kernel library.  Raises when it has not been built."""
     global _kernels
+    if _fake[0] is not None:
+        return _fake[0]
     if _kernels is None:
         with _lock:
             if _kernels is None:

@@ -88,6 +88,11 @@ _workspaces: dict = {}
 
 
 def workspace(device: torch.device) -> Workspace:
+    if device.type != "cuda":            # only reached under a fake kernel library: a small host stand-in
+        w = _workspaces.get(("cpu", 0))
+        if w is None:
+            w = _workspaces[("cpu", 0)] = Workspace(device, floats=1 << 16, counters=1 << 10)
+        return w
     key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
     w = _workspaces.get(key)
     if w is None:
@@ -110,6 +115,8 @@ def _p(t: Optional[torch.Tensor]):
 
 
 def _stream() -> C.c_void_p:
+    if _lib.fake_active():
+        return C.c_void_p(0)
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -139,6 +146,8 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, *, scale_a=None,
     scaled = scale_a is not None
     a_rows, k = a.shape
     b_rows = b.shape[0]
+    from ..core.types import reject_aliasing
+    reject_aliasing(y, {"a": a, "b": b, "scale_a": scale_a, "scale_b": scale_b, "residual": residual}, may_equal=("residual",))
     wsp = workspace(a.device)
     rc = lib.sllm_gemm(_p(a), _p(b), _p(y), _p(scale_a), _p(scale_b), _p(residual), a_rows, b_rows, k,
                        1 if scaled else 0, 1 if transpose_out else 0, y.stride(0),

@@ -51,3 +51,45 @@ def test_every_runner_passes_on_the_gpu(op):
     assert rep["timing"]["median_us"] > 0 and rep["device"]["device_status"] == 0
     if op.startswith("gemm-") or op == "paged-attention-fp8":
         assert rep["dispatch"] and not any(d["fallback_used"] for d in rep["dispatch"])
+
+
+def test_roundtrip_reaper_and_circuit_breaker(tmp_path):
+    """The model-free round trip: a child that overstays is reaped by pid, consecutive failures open the breaker, an
+    open breaker attempts nothing, the cooldown lets one trial through and a success closes it."""
+    import sys
+    from sllm_b200.evidence import roundtrip as RT
+    now = [1000.0]
+    kw = dict(state_dir=str(tmp_path), threshold=2, cooldown=60.0, clock=lambda: now[0])
+    ok_cmd = [sys.executable, "-c", 'print(\'{"ok": true, "checks": {}}\')']
+    bad_cmd = [sys.executable, "-c", 'import sys; print(\'{"ok": false}\'); sys.exit(1)']
+    hang_cmd = [sys.executable, "-c", "import time; time.sleep(60)"]
+    r = RT.roundtrip(cmd=ok_cmd, **kw)
+    assert r["ok"] and r["circuit"] == "closed" and r["attempted"] and not r["reaped"]
+    r = RT.roundtrip(cmd=hang_cmd, timeout=0.5, **kw)
+    assert not r["ok"] and r["reaped"] and r["consecutive_failures"] == 1 and r["circuit"] == "closed"
+    r = RT.roundtrip(cmd=bad_cmd, **kw)
+    assert not r["ok"] and r["consecutive_failures"] == 2 and r["circuit"] == "open"
+    r = RT.roundtrip(cmd=ok_cmd, **kw)                                   # open: not even attempted
+    assert r["circuit"] == "open" and not r["attempted"]
+    now[0] += 61
+    r = RT.roundtrip(cmd=bad_cmd, **kw)                                  # half-open trial fails: open again, clock restarts
+    assert r["attempted"] and r["circuit"] == "open"
+    assert not RT.roundtrip(cmd=ok_cmd, **kw)["attempted"]
+    now[0] += 61
+    r = RT.roundtrip(cmd=ok_cmd, **kw)
+    assert r["ok"] and r["circuit"] == "closed" and r["consecutive_failures"] == 0
+    # "no GPU" neither trips nor resets the breaker
+    none_cmd = [sys.executable, "-c", 'print(\'{"ok": false, "unavailable": "no CUDA device"}\')']
+    RT.roundtrip(cmd=bad_cmd, **kw)
+    r = RT.roundtrip(cmd=none_cmd, **kw)
+    assert r["consecutive_failures"] == 1 and r["attempted"]
+    if not torch.cuda.is_available():
+        assert RT.main(["--state-dir", str(tmp_path / "real")]) == 0      # the real child: unavailable here, exit 0
+
+
+@pytest.mark.gpu
+def test_roundtrip_on_the_gpu(tmp_path):
+    from sllm_b200.evidence import roundtrip as RT
+    r = RT.roundtrip(state_dir=str(tmp_path), timeout=240.0)
+    assert r["ok"] and r["device_status"] == 0 and r["circuit"] == "closed", r
+    assert set(r["checks"]) == {"gemm_bf16", "gemm_fp8", "rmsnorm", "gated_act", "argmax", "paged_attention"}

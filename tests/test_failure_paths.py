@@ -160,3 +160,53 @@ def test_quarantine_accounting_and_release():
     r2 = e2.release()
     assert r2["freed_bytes"] == 0 and r2["parked_bytes"] > 0 and len(E._PARKED) == n + 1 and e2.cache.values.numel() > 0
     assert out and len(out[0]) == 3
+
+
+def test_fake_kernel_library_scripts_launch_failures():
+    """The programmable fake of the kernel library: calls are recorded, scripted status codes come back as KernelError
+    naming the status, successful launches are counted, and an engine step that hits a rejected launch fails without
+    committing anything, so the same sequence decodes again afterwards."""
+    import pytest
+    import torch
+    from sllm_b200 import ops
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.models import config as MC
+    from sllm_b200.ops import _lib
+    x, w = torch.randn(3, 256), torch.ones(256)
+    want = ops.rmsnorm(x, w, 1e-5)
+    fake = _lib.FakeKernelLibrary({"sllm_rmsnorm": [0, 3]})
+    _lib.install_fake(fake)
+    try:
+        n0 = _lib.LAUNCH_COUNT[0]
+        y = ops.rmsnorm(x, w, 1e-5)                                   # "launched": allocated, not computed
+        assert y.shape == want.shape and fake.count("sllm_rmsnorm") == 1 and _lib.LAUNCH_COUNT[0] == n0 + 1
+        name, args = fake.calls[0]
+        assert name == "sllm_rmsnorm" and args[0].value == x.data_ptr()
+        with pytest.raises(_lib.KernelError) as ei:
+            ops.rmsnorm(x, w, 1e-5)
+        assert _lib.STATUS_NAMES.get(3, "3") in str(ei.value) and _lib.LAUNCH_COUNT[0] == n0 + 1
+        with pytest.raises(AttributeError):
+            fake.sllm_no_such_entry_point
+    finally:
+        _lib.install_fake(None)
+    assert torch.equal(ops.rmsnorm(x, w, 1e-5), want)                  # the real (CPU oracle) path is back
+    # an engine step under a fake that rejects the 5th GEMM launch
+    eng = build_engine(MC.tiny_llama(), "cpu", seed=1, num_pages=16, max_batch=2, use_cuda_graphs=False)
+    s = eng.new_sequence([3, 4, 5, 6])
+    first = eng.prefill([s])[0]
+    s.tokens.append(first)
+    computed = s.num_computed
+    fake = _lib.FakeKernelLibrary({"sllm_gemm": [0, 0, 0, 0, 9]})
+    _lib.install_fake(fake)
+    try:
+        with pytest.raises(_lib.KernelError):
+            eng.decode([s])
+        assert fake.count("sllm_gemm") == 5
+    finally:
+        _lib.install_fake(None)
+    assert s.num_computed == computed and eng.cache.pool.length(s.seq_id) == computed      # nothing was committed
+    tok = eng.decode([s])[0]
+    ref_eng = build_engine(MC.tiny_llama(), "cpu", seed=1, num_pages=16, max_batch=2, use_cuda_graphs=False)
+    r = ref_eng.new_sequence([3, 4, 5, 6])
+    r.tokens.append(ref_eng.prefill([r])[0])
+    assert tok == ref_eng.decode([r])[0]
