@@ -168,6 +168,9 @@ def serve(a) -> int:
     from ..server.model_lifecycle import ManifestError, ModelLifecycleRegistry, read_manifest
     life = ServerLifecycle()
     t0 = time.time()
+    # The engine thread releases the interpreter lock while the GPU works and needs it back the moment a step ends; with
+    # the default 5 ms switch interval a busy HTTP thread keeps it that long, which is longer than a whole decode step.
+    sys.setswitchinterval(float(os.environ.get("SLLM_SWITCH_INTERVAL", "2e-4")))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         # one process per GPU: rank 0 serves HTTP and drives the others through the leader/follower protocol

@@ -236,17 +236,30 @@ def view_of(t, encoding: Optional[Encoding] = None) -> TensorView:
                       t.data_ptr())
 
 
+def _byte_span(t) -> tuple:
+    """[begin, end) of the bytes a torch tensor addresses (no object construction: this runs on every GEMM launch)."""
+    n = t.numel()
+    if n == 0:
+        return 0, 0
+    b = t.data_ptr()
+    if t.is_contiguous():
+        return b, b + n * t.element_size()
+    last = 0
+    for s_, st in zip(t.shape, t.stride()):
+        last += (s_ - 1) * st
+    return b, b + (last + 1) * t.element_size()
+
+
 def reject_aliasing(out, inputs: dict, may_equal: tuple = ()) -> None:
     """Raises TensorError when `out` overlaps one of `inputs` (name -> tensor or None).  Inputs named in `may_equal`
     may BE the output (the same region: an in-place residual), but may not overlap it partially."""
-    ov = view_of(out)
+    ob, oe = _byte_span(out)
     for name, t in inputs.items():
         if t is None:
             continue
-        iv = view_of(t)
-        if not ov.overlaps(iv):
+        ib, ie = _byte_span(t)
+        if ib >= oe or ob >= ie or ib == ie or ob == oe:
             continue
-        if name in may_equal and ov.same_region(iv):
+        if name in may_equal and ib == ob and t.shape == out.shape and t.stride() == out.stride() and t.dtype == out.dtype:
             continue
-        raise TensorError(f"the output overlaps input {name!r} (bytes [{iv.begin:#x}, {iv.end:#x}) vs "
-                          f"[{ov.begin:#x}, {ov.end:#x}))")
+        raise TensorError(f"the output overlaps input {name!r} (bytes [{ib:#x}, {ie:#x}) vs [{ob:#x}, {oe:#x}))")

@@ -176,6 +176,33 @@ class Engine:
             out["allocator_at_build"] = self._mem_mark
         return out
 
+    def kernel_timing(self, seqs: list) -> dict:
+        """Runs ONE eager decode step of `seqs` with a CUDA event after every launch and returns the device time by
+        launch kind: {"step_us", "launches", "by_kernel": {name: {"launches", "us"}}}.  The step is a real one (the
+        sequences advance by a token); graphs are bypassed for it."""
+        from ..ops import _lib
+        self._guard()
+        saved, self.use_graphs = self.use_graphs, False
+        try:
+            if self.is_cuda:
+                torch.cuda.synchronize(self.device)
+            _lib.timing(True)
+            toks = self.decode(seqs)
+            rep = _lib.timing_report()
+        finally:
+            _lib.timing(False)
+            self.use_graphs = saved
+        by: dict = {}
+        for name, us in rep:
+            e = by.setdefault(name, {"launches": 0, "us": 0.0})
+            e["launches"] += 1
+            e["us"] += us
+        for e in by.values():
+            e["us"] = round(e["us"], 2)
+        for s_, t in zip(seqs, toks):
+            s_.tokens.append(t)
+        return {"step_us": round(sum(us for _, us in rep), 2), "launches": len(rep), "by_kernel": by}
+
     def shutdown_report(self) -> dict:
         """What a supervisor logs when the engine goes away: memory by category, launch and copy counters, fallbacks
         and the quarantine record."""

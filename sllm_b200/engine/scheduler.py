@@ -274,6 +274,28 @@ class EngineLoop:
             self._wake.notify_all()
             return True
 
+    # Request audit: one record per finished request in a bounded ring (what was asked, what it cost, how it ended),
+    # served by `/props`; the reference keeps the same per-request submission counts (include/sllm/hip.h:651-671).
+    AUDIT_CAP = 128
+
+    def _audit(self, req: GenRequest, reason: str) -> None:
+        now = time.monotonic()
+        rec = {"rid": req.rid, "prompt_tokens": len(req.prompt), "prefix_hit_tokens": req.prefix_hit_tokens,
+               "generated": req.generated, "finish_reason": reason, "sampled": req.chain is not None,
+               "constrained": req.mask_fn is not None, "multimodal": req.mm is not None,
+               "context_shifts": req.shift_count, "shifted_tokens": req.shifted_tokens,
+               "queue_to_first_token_ms": None if req.first_token_at is None
+               else round((req.first_token_at - req.submitted_at) * 1e3, 3),
+               "total_ms": round((now - req.submitted_at) * 1e3, 3),
+               "decode_rounds_at_finish": self.rounds.get("decode", 0), "prefill_rounds_at_finish": self.rounds.get("prefill", 0)}
+        ring = self.__dict__.setdefault("_audit_ring", [])
+        ring.append(rec)
+        if len(ring) > self.AUDIT_CAP:
+            del ring[:len(ring) - self.AUDIT_CAP]
+
+    def request_audit(self, n: int = 16) -> list:
+        return list(self.__dict__.get("_audit_ring", []))[-n:]
+
     def slots(self) -> list:
         with self._lock:
             return [{"id": r.rid, "state": r.state, "phase": self.planner.entries[r.rid].phase
@@ -318,6 +340,7 @@ class EngineLoop:
             return
         req.state = "done"
         req.finish_reason = reason
+        self._audit(req, reason)
         if req.prefix_seq is not None:
             self._release_prefix(req)
         if req.seq is not None:

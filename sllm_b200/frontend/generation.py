@@ -11,6 +11,7 @@ The queue is bounded: a slow consumer back-pressures only its own request (runti
 """
 from __future__ import annotations
 
+import collections
 import queue
 import threading
 import time
@@ -41,9 +42,142 @@ class GenerationConfig:
     echo_tokens: bool = False
 
 
+class _LoopNotifier:
+    """One wake-up of an asyncio loop for any number of channels that became readable: producers (the engine thread)
+    post a channel; the first post since the last flush schedules ONE `call_soon_threadsafe`, the flush wakes every
+    posted channel's waiter.  An engine round that publishes a token for each of 32 streams thus costs one self-pipe
+    write instead of 32 thread hand-offs."""
+
+    _by_loop: dict = {}
+    _guard = threading.Lock()
+
+    def __init__(self, loop):
+        self.loop = loop
+        self._lock = threading.Lock()
+        self._ready: list = []
+        self._scheduled = False
+
+    @classmethod
+    def of(cls, loop) -> "_LoopNotifier":
+        with cls._guard:
+            n = cls._by_loop.get(id(loop))
+            if n is None or n.loop is not loop:
+                if len(cls._by_loop) > 64:
+                    cls._by_loop.clear()
+                n = cls._by_loop[id(loop)] = _LoopNotifier(loop)
+            return n
+
+    def post(self, channel: "EventChannel") -> None:
+        with self._lock:
+            self._ready.append(channel)
+            if self._scheduled:
+                return
+            self._scheduled = True
+        try:
+            self.loop.call_soon_threadsafe(self._flush)
+        except RuntimeError:                 # the loop is closed: nobody is waiting any more
+            with self._lock:
+                self._scheduled = False
+                self._ready.clear()
+
+    def _flush(self) -> None:
+        with self._lock:
+            ready, self._ready = self._ready, []
+            self._scheduled = False
+        for ch in ready:
+            ch._wake_async()
+
+
+class EventChannel:
+    """Bounded event queue between the engine thread (producer) and one consumer that is either a thread (`get`,
+    iteration) or a coroutine (`aget`, `aget_batch`).  The coroutine side needs no helper thread: it parks a future,
+    and the producer wakes the loop through the loop's notifier only while such a future is parked.  Same exceptions
+    as queue.Queue (queue.Full / queue.Empty)."""
+
+    def __init__(self, capacity: int):
+        self.capacity = capacity
+        self._items: collections.deque = collections.deque()
+        self._cv = threading.Condition(threading.Lock())
+        self._waiter = None              # asyncio.Future of the coroutine consumer, owned by its loop
+        self._notifier: Optional[_LoopNotifier] = None
+
+    # ---- producer
+    def put(self, item, timeout: Optional[float] = None) -> None:
+        with self._cv:
+            if len(self._items) >= self.capacity:
+                if not self._cv.wait_for(lambda: len(self._items) < self.capacity, timeout):
+                    raise queue.Full
+            self._items.append(item)
+            self._cv.notify()
+            notifier = self._notifier if self._waiter is not None else None
+        if notifier is not None:
+            notifier.post(self)
+
+    def put_nowait(self, item) -> None:
+        with self._cv:
+            if len(self._items) >= self.capacity:
+                raise queue.Full
+            self._items.append(item)
+            self._cv.notify()
+            notifier = self._notifier if self._waiter is not None else None
+        if notifier is not None:
+            notifier.post(self)
+
+    # ---- thread consumer
+    def get(self, timeout: Optional[float] = None):
+        with self._cv:
+            if not self._cv.wait_for(lambda: self._items, timeout):
+                raise queue.Empty
+            item = self._items.popleft()
+            self._cv.notify()
+            return item
+
+    def get_nowait(self):
+        with self._cv:
+            if not self._items:
+                raise queue.Empty
+            item = self._items.popleft()
+            self._cv.notify()
+            return item
+
+    def qsize(self) -> int:
+        return len(self._items)
+
+    # ---- coroutine consumer (one at a time)
+    def _wake_async(self) -> None:
+        with self._cv:
+            w, self._waiter = self._waiter, None
+        if w is not None and not w.done():
+            w.set_result(None)
+
+    async def aget_batch(self, limit: int = 64) -> list:
+        """Waits for one event, then takes what else is queued (up to `limit`, stopping after a terminal event)."""
+        import asyncio
+        loop = asyncio.get_running_loop()
+        while True:
+            with self._cv:
+                if self._items:
+                    out = [self._items.popleft()]
+                    while len(out) < limit and out[-1][0] == "delta" and self._items:
+                        out.append(self._items.popleft())
+                    self._cv.notify_all()
+                    return out
+                self._notifier = _LoopNotifier.of(loop)
+                self._waiter = fut = loop.create_future()
+            try:
+                await fut
+            finally:
+                with self._cv:
+                    if self._waiter is fut:
+                        self._waiter = None
+
+    async def aget(self):
+        return (await self.aget_batch(1))[0]
+
+
 class GenerationHandle:
     def __init__(self, service: "GenerationService", capacity: int):
-        self.events: "queue.Queue" = queue.Queue(maxsize=capacity)
+        self.events: EventChannel = EventChannel(capacity)
         self.service = service
         self.rid = 0
         self.prompt_tokens = 0

@@ -77,6 +77,7 @@ class HFTokenizer:
         self.identity = "hf:" + hashlib.sha256(self.tk.to_str().encode()).hexdigest()[:16]
         self._special = {i for t, i in self.tk.get_vocab(with_added_tokens=True).items()
                          if t.startswith("<|") and t.endswith("|>")}
+        self._token_bytes: dict = {}
 
     def encode(self, text: str, allow_special: bool = True) -> list:
         return self.tk.encode(text, add_special_tokens=False).ids
@@ -88,6 +89,12 @@ class HFTokenizer:
         return tid in self._special
 
     def token_bytes(self, tid: int) -> bytes:
+        cached = self._token_bytes.get(tid)
+        if cached is None:
+            cached = self._token_bytes[tid] = self._token_bytes_uncached(tid)      # called once per generated token
+        return cached
+
+    def _token_bytes_uncached(self, tid: int) -> bytes:
         tok = self.tk.id_to_token(tid)
         if tok is None:
             return b""

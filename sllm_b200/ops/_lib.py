@@ -126,10 +126,41 @@ def dispatch_records(clear: bool = False) -> list:
     return out
 
 
+# Per-launch device timing (eager launches only): with timing on, every successful launch is followed by a CUDA event
+# on the current stream; the report gives, per launch, the device time since the previous event.
+_timing: list = []
+_timing_on = [False]
+
+
+def timing(on: bool) -> None:
+    """Starts (records the base event) or stops per-launch timing.  Not usable during stream capture."""
+    import torch
+    _timing_on[0] = bool(on) and torch.cuda.is_available() and not fake_active()
+    _timing.clear()
+    if _timing_on[0]:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        _timing.append(("<start>", ev))
+
+
+def timing_report() -> list:
+    """[(launch name, microseconds since the previous launch finished)] since `timing(True)`; synchronises."""
+    import torch
+    if len(_timing) < 2:
+        return []
+    torch.cuda.synchronize()
+    return [(name, _timing[i - 1][1].elapsed_time(ev) * 1e3) for i, (name, ev) in enumerate(_timing) if i > 0]
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise KernelError(f"{what}: launch rejected ({STATUS_NAMES.get(rc, rc)})")
     LAUNCH_COUNT[0] += 1
+    if _timing_on[0]:
+        import torch
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        _timing.append((what, ev))
 
 
 _KERNEL_SIGNATURES = {

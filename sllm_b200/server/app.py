@@ -200,23 +200,13 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
             raise E.invalid_value(str(exc)) from None
 
     async def next_event(handle):
-        return await asyncio.to_thread(handle.events.get)
-
-    def _drain_events(handle, limit: int = 64) -> list:
-        """Blocks for one event, then takes whatever else is already queued (up to `limit`, stopping after a
-        terminal event).  A stream whose consumer lags behind the engine then pays one thread hop, one JSON
-        document and one socket write for the whole backlog instead of one per token."""
-        import queue as _q
-        out = [handle.events.get()]
-        try:
-            while len(out) < limit and out[-1][0] == "delta":
-                out.append(handle.events.get_nowait())
-        except _q.Empty:
-            pass
-        return out
+        return await handle.events.aget()
 
     async def next_events(handle):
-        return await asyncio.to_thread(_drain_events, handle)
+        """One event, plus whatever else is already queued (a stream whose consumer lags behind the engine pays one
+        JSON document and one socket write for the whole backlog).  No helper thread: the engine thread wakes this
+        loop once per round for all streams (frontend.generation.EventChannel)."""
+        return await handle.events.aget_batch(64)
 
     def grammar_for(response_format: dict) -> Optional[str]:
         t = response_format.get("type")
@@ -275,7 +265,8 @@ def build_app(registry: ModelRegistry, config: Optional[ServerConfig] = None, li
                 "features": {"metrics": cfg.metrics, "resumable_sse": cfg.resumable_sse,
                              "compatibility_profile": cfg.compatibility_profile,
                              "dynamic_models": registry.dynamic is not None, "cors": bool(cfg.cors_origins)},
-                "fallbacks": _fallbacks(), "dispatch_audit": _dispatch_tail()}
+                "fallbacks": _fallbacks(), "dispatch_audit": _dispatch_tail(),
+                "request_audit": {a: b.request_audit() for a, b in registry.backends.items() if hasattr(b, "request_audit")}}
 
     @app.get("/slots")
     async def slots(request: Request):

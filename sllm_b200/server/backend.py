@@ -16,13 +16,13 @@ from typing import Optional
 import numpy as np
 
 from ..engine.scheduler import QueueFull
-from ..frontend.generation import GenerationConfig, GenerationHandle, GenerationService
+from ..frontend.generation import EventChannel, GenerationConfig, GenerationHandle, GenerationService
 from ..frontend.text import ByteTokenizer
 
 
 class ScriptHandle:
     def __init__(self, prompt_tokens: int):
-        self.events: "queue.Queue" = queue.Queue()
+        self.events = EventChannel(1 << 20)
         self.prompt_tokens = prompt_tokens
         self.completion_tokens = 0
         self.cancelled = threading.Event()
@@ -229,6 +229,9 @@ class EngineBackend:
 
     def scheduler_stats(self) -> dict:
         return self.loop.stats()
+
+    def request_audit(self, n: int = 16) -> list:
+        return self.loop.request_audit(n)
 
     def slots(self) -> list:
         return self.loop.slots()

@@ -28,8 +28,10 @@ def _pct(xs, p):
     return xs[min(len(xs) - 1, int(round(p / 100.0 * (len(xs) - 1))))]
 
 
-async def _one(session, url, model, prompt, max_tokens, headers, out):
+async def _one(session, url, model, prompt, max_tokens, headers, out, temperature=None):
     body = {"model": model, "messages": [{"role": "user", "content": prompt}], "max_completion_tokens": max_tokens, "stream": True}
+    if temperature is not None:
+        body["temperature"] = temperature
     t0 = time.perf_counter()
     first, last, gaps, usage, err = None, None, [], None, None
     try:
@@ -75,7 +77,7 @@ async def run(a) -> dict:
     async with aiohttp.ClientSession(timeout=timeout) as session:
         async def guarded(prompt, n):
             async with sem:
-                await _one(session, a.url, a.model, prompt, n, headers, results)
+                await _one(session, a.url, a.model, prompt, n, headers, results, getattr(a, "temperature", None))
 
         t_start = time.perf_counter()
         for _ in range(a.requests):
@@ -122,6 +124,7 @@ def main(argv=None) -> int:
     ap.add_argument("--api-key-env")
     ap.add_argument("--timeout", type=float, default=600.0)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--temperature", type=float, default=None, help="sampling temperature sent with every request (0 = greedy)")
     a = ap.parse_args(argv)
     print(json.dumps(asyncio.run(run(a))))
     return 0

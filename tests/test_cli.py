@@ -312,7 +312,7 @@ def test_serve_bench_against_live_server(model):
                                timeout=120.0, seed=1)
         rep = asyncio.run(serve_bench.run(a))
         assert rep["completed"] == 6 and rep["failed"] == 0 and rep["output_tokens"] >= 20
-        assert rep["ttft_ms"]["p50"] > 0 and rep["itl_ms"]["p50"] is not None
+        assert rep["ttft_ms"]["p50"] > 0 and "p50" in rep["itl_ms"]      # (no interval when a backlog arrived as one chunk)
     finally:
         proc.send_signal(signal.SIGTERM)
         try:

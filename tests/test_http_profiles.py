@@ -173,6 +173,11 @@ def test_engine_served_over_http_greedy_json_and_concurrency(engine_client):
     e = c.post("/v1/embeddings", json={"model": M, "input": ["abc", "abd"]}).json()["data"]
     assert len(e[0]["embedding"]) == 256 and abs(np.linalg.norm(e[0]["embedding"]) - 1) < 1e-4
     assert "sllm_tokens_total" in c.get("/metrics").text
+    # every finished request left an audit record: what it asked for, what it cost, how it ended
+    audit = c.get("/props").json()["request_audit"][M]
+    assert audit and audit[-1]["finish_reason"] in ("stop", "length") and audit[-1]["prompt_tokens"] > 0
+    assert audit[-1]["total_ms"] >= (audit[-1]["queue_to_first_token_ms"] or 0) and "generated" in audit[-1]
+    assert any(r["sampled"] for r in audit) and any(r["constrained"] for r in audit)
     assert c.post("/v1/chat/completions", json={**req, "max_completion_tokens": 4096}).status_code == 400   # context bound
 
 

