@@ -48,11 +48,13 @@ def parse_args():
                     help="speculative decoding: draft tokens per step from a llama-draft model (acceptance forced by a "
                          "seeded Bernoulli(0.7) mask so that the full verify compute always runs)")
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--parallelism", default="auto", choices=["auto", "tp", "dp"],
-                    help="N > 1: tp = one model sharded over the GPUs (fused GEMM + all-reduce), dp = one replica per GPU, "
-                         "each decoding batch / N of the sequences (no communication inside a step); auto = dp when the "
-                         "weights are small enough that a replica per GPU streams less per token than the sharded "
-                         "model's per-kernel floor costs (dense models under 16 GiB of weights), else tp")
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
+                    help="N > 1: tp = one model sharded over the GPUs (fused GEMM + all-reduce; the layout the benchmark "
+                         "configuration names), dp = one replica per GPU, each decoding batch / N of the sequences (no "
+                         "communication inside a step)")
+    ap.add_argument("--no-replica-run", action="store_true",
+                    help="N > 1, dense models under 16 GiB of weights: skip the second measurement of the same global batch "
+                         "as one replica per GPU (reported under `replica_layout`)")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: override the layer count")
     ap.add_argument("--no-batch1", action="store_true", help="skip the extra batch-1 measurement")
     return ap.parse_args()
@@ -340,11 +342,10 @@ def main():
     cfg.max_context = ((total_ctx + 255) // 256) * 256
     weight_gib = _estimate_weight_bytes(cfg) / 2 ** 30
     layout = args.parallelism
-    if layout == "auto":
-        layout = "dp" if (world > 1 and cfg.family != "moe" and weight_gib < 16 and args.batch % world == 0
-                          and args.spec_width == 0) else "tp"
     if layout == "dp" and (world == 1 or args.batch % world or cfg.family == "moe"):
         layout = "tp"
+    also_replicas = (layout == "tp" and world > 1 and cfg.family != "moe" and weight_gib < 16 and args.batch % world == 0
+                     and args.spec_width == 0 and not args.no_replica_run)
     replicas = world if layout == "dp" else 1
     tp = None
     if world > 1 and layout == "tp":
@@ -368,8 +369,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def measure(batch: int, steps: int, warmup: int, sample_clocks: bool):
-        eng = build_engine(cfg, device, seed=0, max_batch=batch, tp=tp, ep=ep)
+    def measure(batch: int, steps: int, warmup: int, sample_clocks: bool, sharded: bool = True):
+        eng = build_engine(cfg, device, seed=0, max_batch=batch, tp=tp if sharded else None, ep=ep if sharded else None)
         g = torch.Generator().manual_seed(1234)
         prompts = torch.randint(0, cfg.vocab, (batch, args.prompt), generator=g).tolist()
         seqs = [eng.new_sequence(p) for p in prompts]
@@ -449,6 +450,7 @@ def main():
         return run_speculative(args, cfg, device, tp, world, rank, barrier, max_over_ranks, ClockSampler(local_rank))
     # data parallel: every rank is a replica decoding its share of the sequences; the step time is the slowest rank's
     main_res = measure(args.batch // replicas, args.steps, args.warmup, True)
+    replica_res = measure(args.batch // world, args.steps, args.warmup, False, sharded=False) if also_replicas else None
     extra = None
     if not args.no_batch1 and args.batch != 1:
         extra = measure(1, min(args.steps, 64), max(3, min(args.warmup, 4)), False)
@@ -496,6 +498,17 @@ def main():
             "fallbacks": _lib.fallbacks(),
             "impl": "own",
         }
+        if replica_res is not None:
+            kk = args.steps
+            out["replica_layout"] = {
+                "parallelism": f"dp{args.gpus}",
+                "note": "the same global batch as one replica per GPU, each decoding global_batch / N sequences; no "
+                        "communication inside a step; launches and copied bytes are job totals",
+                "value": round(args.batch * kk / (replica_res["dev_ms"] / 1e3), 2), "unit": "tok/s",
+                "ms_per_step": round(replica_res["dev_ms"] / kk, 4),
+                "e2e": {"value": round(args.batch * kk / (replica_res["e2e_ms"] / 1e3), 2), "unit": "tok/s",
+                        "h2d_bytes_per_step": int(replica_res["h2d"]) * world, "d2h_bytes_per_step": int(replica_res["d2h"]) * world},
+                "gpu_launches": int(replica_res["launches_per_step"] * kk) * world, "device_status": replica_res["status"]}
         if extra:
             ks = min(args.steps, 64)
             out["batch1"] = {"tok_s_device": round(ks / (extra["dev_ms"] / 1e3), 2),
