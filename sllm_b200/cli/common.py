@@ -95,7 +95,7 @@ def open_model(args, max_batch: int = 8, tp=None):
     elif family == "qwen35":
         from ..cache.hybrid import HybridCache
         from ..models.qwen35 import Qwen35Model
-        model = Qwen35Model(cfg, weights, tp)
+        model = Qwen35Model(cfg, weights, tp, ep)
         cache = HybridCache(cfg, max_batch * blocks + 8, device, max_seqs=2 * max_batch + 2, kv_heads=model.local_kv_heads,
                             tp_size=tp_size)
     else:

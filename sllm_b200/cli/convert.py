@@ -3,13 +3,17 @@
 Kinds:
   random-llama   seeded random-init weights of a named shape (`--artifact llama3-8b`), for benchmarks and tests; the
                  mixture-of-experts (`moe-120b`, `qwen35-moe`, `tiny-moe`, `tiny-shared-moe`) and hybrid
-                 (`qwen35-hybrid`, `tiny-qwen35`) shapes are written through models/family_io.py with MXFP4 experts
+                 (`qwen35-hybrid`, `qwen35-moe-hybrid`, `tiny-qwen35`, `tiny-qwen35-moe`) shapes are written through models/family_io.py with MXFP4 experts
   hf-llama       a Llama-style Hugging Face checkpoint (config.json + safetensors) from a directory that is first
                  verified against its model lock (`--lock lock.json --cache DIR`)
   mixed-precision  a compressed-tensors checkpoint with FP8 channel-scaled attention projections, NVFP4 MLP
                  projections and per-layer static FP8 KV scales (formats/quantized_model.py); same lock verification.
                  The file keeps the FP8 matrices block-scaled, the NVFP4 matrices as GGML type-40 blocks with their
                  outer scales, and the KV scales in the model configuration
+  hf-qwen35      a Qwen3.5 checkpoint (gated-delta-net / full-attention hybrid; `qwen3_5_text` with a dense MLP or
+                 `qwen3_5_moe_text` with routed MXFP4 experts stored as packed U8 values plus E8M0 `weight_scale`
+                 planes and a gated shared expert); the decoder tensors under `model.language_model.` are consumed,
+                 `model.visual.*` and `mtp.*` are recorded as known-unconsumed; same lock verification
 `--weight-format bf16|fp8` selects the resident encoding (fp8 = E4M3FN with FP32 scales per 1x128 block).
 `--dry-run` validates inputs and prints the plan without writing.  (Reference: crates/sllm-server/src/bin/
 sllm-convert-gguf.rs flags --kind --lock --cache --artifact --manifest --output --derived-lock
@@ -23,7 +27,7 @@ import sys
 
 from .common import CliError, StrictParser, emit, run_main
 
-KINDS = ("random-llama", "hf-llama", "mixed-precision")
+KINDS = ("random-llama", "hf-llama", "hf-qwen35", "mixed-precision")
 
 
 def _hf_config(raw: dict, weight_format: str):
@@ -100,6 +104,141 @@ def _load_hf(cache, cfg):
     return LlamaWeights(embed, layers, get("model.norm.weight"), lin(head), 0)
 
 
+def _hf_qwen35_config(raw: dict):
+    """Model configuration of a Qwen3.5 text decoder (fields as crates/sllm-core/src/model.rs:1138-1260 and
+    qwen35_moe.rs:1177-1189 read them)."""
+    from ..models.config import ModelConfig
+    text = dict(raw.get("text_config") or raw)
+    mt = text.get("model_type")
+    if mt not in ("qwen3_5_text", "qwen3_5_moe_text"):
+        raise CliError(f"unsupported model_type {mt!r} for kind hf-qwen35")
+    rp = text.get("rope_parameters") or {}
+    hd = int(text["head_dim"])
+    ghd = int(text["linear_key_head_dim"])
+    if int(text["linear_value_head_dim"]) != ghd:
+        raise CliError("gated-delta-net key and value head widths differ")
+    sparse = mt == "qwen3_5_moe_text"
+    return ModelConfig(
+        name=raw.get("_name_or_path") or mt, family="qwen35", n_layers=int(text["num_hidden_layers"]),
+        d_model=int(text["hidden_size"]), n_heads=int(text["num_attention_heads"]),
+        n_kv_heads=int(text["num_key_value_heads"]), head_dim=hd,
+        ffn=int(text["moe_intermediate_size"] if sparse else text["intermediate_size"]), vocab=int(text["vocab_size"]),
+        rope_theta=float(rp.get("rope_theta", text.get("rope_theta", 1e7))),
+        rotary_dim=int(round(hd * float(rp.get("partial_rotary_factor", text.get("partial_rotary_factor", 0.25))))),
+        rms_eps=float(text.get("rms_norm_eps", 1e-6)), norm_offset_one=True, weight_format="bf16", kv_format="bf16",
+        qk_norm=True, full_attention_interval=int(text.get("full_attention_interval", 4)),
+        gdn_heads=int(text["linear_num_value_heads"]), gdn_qk_heads=int(text["linear_num_key_heads"]), gdn_head_dim=ghd,
+        gdn_conv_kernel=int(text["linear_conv_kernel_dim"]), attn_output_gate=bool(text.get("attn_output_gate", True)),
+        tie_embeddings=bool(raw.get("tie_word_embeddings", text.get("tie_word_embeddings", False))),
+        n_experts=int(text["num_experts"]) if sparse else 0, top_k=int(text["num_experts_per_tok"]) if sparse else 0,
+        expert_ffn=int(text["moe_intermediate_size"]) if sparse else 0,
+        shared_expert_ffn=int(text.get("shared_expert_intermediate_size", 0)) if sparse else 0,
+        expert_format="mxfp4", max_context=min(int(text.get("max_position_embeddings", 8192)), 131072))
+
+
+def _load_hf_qwen35(cache, cfg):
+    """Qwen35Weights on the CPU from the verified safetensors shards, and the names left unconsumed on purpose.
+
+    Source layout (crates/sllm-core/src/model.rs:1406-1540): per layer `input_layernorm`, `post_attention_layernorm`,
+    the MLP, and either `linear_attn.{in_proj_qkv,in_proj_z,in_proj_b,in_proj_a,conv1d,A_log,dt_bias,norm,out_proj}` or
+    `self_attn.{q_proj,k_proj,v_proj,o_proj,q_norm,k_norm}`, where q_proj holds [query | output gate] per head
+    (native/hip/src/attention_preprocess_kernel.hip.cpp:131-135).  Sparse MLP (qwen35_moe.rs:1576-1624): `mlp.gate`
+    (router), `mlp.shared_expert_gate`, `mlp.shared_expert.*`, and per expert three packed U8 matrices with U8 E8M0
+    scales per 32 inputs."""
+    import numpy as np
+    import torch
+    from safetensors import safe_open
+    from ..models.qwen35 import Qwen35Layer, Qwen35Weights
+    from ..ops.core import LinearWeight
+    from ..ops.w4 import W4Weight
+    tensors = {}
+    for n in sorted(p for p in cache.fds if p.endswith(".safetensors")):
+        with safe_open(os.path.join(cache.root, n), framework="pt") as f:
+            for k in f.keys():
+                tensors[k] = f.get_tensor(k)
+    root = "model.language_model." if any(k.startswith("model.language_model.") for k in tensors) else "model."
+    bf = torch.bfloat16
+
+    def get(name, dtype=bf, shape=None):
+        if name not in tensors:
+            raise CliError(f"checkpoint lacks tensor {name}")
+        t = tensors.pop(name)
+        if shape is not None and tuple(t.shape) != tuple(shape):
+            raise CliError(f"{name}: shape {tuple(t.shape)} differs from the expected {tuple(shape)}")
+        return t.to(dtype) if dtype is not None else t
+
+    lin = lambda w: LinearWeight("dense", w.contiguous())
+    d, hd, hq, hkv = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+    ghd, vh, qh = cfg.gdn_head_dim, cfg.gdn_heads, cfg.gdn_qk_heads
+    width = (2 * qh + vh) * ghd
+    E, F, fs = cfg.n_experts, cfg.expert_ffn, cfg.shared_expert_ffn
+
+    def experts(p, stems, n, k):
+        """[E, len(stems) * n, k] routed matrices from packed values [n, k / 2] and scales [n, k / 32]."""
+        vals = np.empty((E, len(stems) * n, k // 2), dtype=np.uint8)
+        scs = np.empty((E, len(stems) * n, k // 32), dtype=np.uint8)
+        for e in range(E):
+            for j, stem in enumerate(stems):
+                base = f"{p}mlp.experts.{e}.{stem}"
+                vals[e, j * n:(j + 1) * n] = get(base + ".weight", None, (n, k // 2)).numpy()
+                scs[e, j * n:(j + 1) * n] = get(base + ".weight_scale", None, (n, k // 32)).numpy()
+        return W4Weight.from_file_layout("mxfp4", vals, scs, k, None, "cpu")
+
+    layers = []
+    for i in range(cfg.n_layers):
+        p = f"{root}layers.{i}."
+        common = dict(in_norm=get(p + "input_layernorm.weight", shape=(d,)),
+                      mlp_norm=get(p + "post_attention_layernorm.weight", shape=(d,)))
+        if E:
+            router = get(p + "mlp.gate.weight", shape=(E, d))
+            if fs:
+                router = torch.cat([router, get(p + "mlp.shared_expert_gate.weight", shape=(1, d)),
+                                    torch.zeros((7, d), dtype=bf)], dim=0)
+                common.update(
+                    shared_gate_up=lin(torch.cat([get(p + "mlp.shared_expert.gate_proj.weight", shape=(fs, d)),
+                                                  get(p + "mlp.shared_expert.up_proj.weight", shape=(fs, d))], dim=0)),
+                    shared_down=lin(get(p + "mlp.shared_expert.down_proj.weight", shape=(d, fs))))
+            common.update(router=lin(router), exp_gate_up=experts(p, ("gate_proj", "up_proj"), F, d),
+                          exp_down=experts(p, ("down_proj",), d, F))
+        else:
+            f = cfg.ffn
+            common.update(gate_up=lin(torch.cat([get(p + "mlp.gate_proj.weight", shape=(f, d)),
+                                                 get(p + "mlp.up_proj.weight", shape=(f, d))], dim=0)),
+                          down=lin(get(p + "mlp.down_proj.weight", shape=(d, f))))
+        if (i + 1) % cfg.full_attention_interval == 0:
+            a = p + "self_attn."
+            gate = None
+            if cfg.attn_output_gate:
+                packed = get(a + "q_proj.weight", shape=(2 * hq * hd, d)).view(hq, 2, hd, d)
+                wq, gate = packed[:, 0].reshape(hq * hd, d), lin(packed[:, 1].reshape(hq * hd, d))
+            else:
+                wq = get(a + "q_proj.weight", shape=(hq * hd, d))
+            qkv = torch.cat([wq, get(a + "k_proj.weight", shape=(hkv * hd, d)), get(a + "v_proj.weight", shape=(hkv * hd, d))])
+            layers.append(Qwen35Layer("full", qkv=lin(qkv), gate=gate, o=lin(get(a + "o_proj.weight", shape=(d, hq * hd))),
+                                      q_norm=get(a + "q_norm.weight", shape=(hd,)), k_norm=get(a + "k_norm.weight", shape=(hd,)),
+                                      **common))
+        else:
+            a = p + "linear_attn."
+            w_loc = torch.cat([get(a + "in_proj_qkv.weight", shape=(width, d)), get(a + "in_proj_z.weight", shape=(vh * ghd, d)),
+                               get(a + "in_proj_b.weight", shape=(vh, d)), get(a + "in_proj_a.weight", shape=(vh, d))], dim=0)
+            w_in = torch.zeros(((w_loc.shape[0] + 7) // 8 * 8, d), dtype=bf)
+            w_in[:w_loc.shape[0]] = w_loc
+            layers.append(Qwen35Layer(
+                "gdn", in_proj=lin(w_in),
+                conv_w=get(a + "conv1d.weight", shape=(width, 1, cfg.gdn_conv_kernel)).reshape(width, cfg.gdn_conv_kernel).contiguous(),
+                a_log=get(a + "A_log", torch.float32, (vh,)), dt_bias=get(a + "dt_bias", shape=(vh,)),
+                out_norm=get(a + "norm.weight", torch.float32, (ghd,)), out_proj=lin(get(a + "out_proj.weight", shape=(d, vh * ghd))),
+                **common))
+    embed = get(root + "embed_tokens.weight", shape=(cfg.vocab, d))
+    head = embed if cfg.tie_embeddings else get("lm_head.weight", shape=(cfg.vocab, d))
+    final = get(root + "norm.weight", shape=(d,))
+    unconsumed = sorted(k for k in tensors if k.startswith(("model.visual.", "mtp.")))
+    leftover = [k for k in tensors if k not in unconsumed and not k.endswith("rotary_emb.inv_freq")]
+    if leftover:
+        raise CliError(f"unconsumed tensors in the checkpoint (unknown policy is reject): {leftover[:4]}")
+    return Qwen35Weights(embed, layers, final, LinearWeight("dense", head), 0), unconsumed
+
+
 def _write_lock(path: str, doc: dict) -> None:
     tmp = path + ".tmp"
     with open(tmp, "w", encoding="utf-8") as f:
@@ -148,7 +287,8 @@ def main(argv=None) -> int:
         named = dict(MC.NAMED)
         from ..models import moe as _moe
         from ..models import qwen35 as _q35
-        named.update({"tiny-moe": _moe.tiny_moe, "tiny-shared-moe": _moe.tiny_shared_moe, "tiny-qwen35": _q35.tiny_qwen35})
+        named.update({"tiny-moe": _moe.tiny_moe, "tiny-shared-moe": _moe.tiny_shared_moe, "tiny-qwen35": _q35.tiny_qwen35,
+                      "tiny-qwen35-moe": _q35.tiny_qwen35_moe})
         if a.kind == "random-llama":
             if a.artifact not in named:
                 raise CliError(f"--artifact must be one of {sorted(named)}")
@@ -165,7 +305,7 @@ def main(argv=None) -> int:
                 cfg.kv_format = "fp32"
         else:
             if not (a.lock and a.cache):
-                raise CliError("kind hf-llama needs --lock and --cache")
+                raise CliError(f"kind {a.kind} needs --lock and --cache")
             try:
                 lock = ML.read_model_lock(a.lock)
                 cache = lock.verify_cache(a.cache)
@@ -180,6 +320,10 @@ def main(argv=None) -> int:
                     text["model_type"] = "llama"          # the decoder stack of a multimodal wrapper
                 cfg = _hf_config(text, "mixed-fp8-nvfp4")
                 cfg.kv_format, cfg.tie_embeddings = "fp8-static", True
+            elif a.kind == "hf-qwen35":
+                if a.weight_format != "bf16":
+                    raise CliError("kind hf-qwen35 keeps the checkpoint's encodings (bf16 matrices, MXFP4 experts)")
+                cfg = _hf_qwen35_config(raw_cfg)
             else:
                 cfg = _hf_config(raw_cfg, a.weight_format)
             if "tokenizer.json" in cache.fds:
@@ -197,18 +341,26 @@ def main(argv=None) -> int:
         if a.dry_run:
             emit({"dry_run": True, **plan})
             return 0
-        if a.kind == "random-llama" and cfg.family in ("moe", "qwen35"):
+        if a.kind == "hf-qwen35" or (a.kind == "random-llama" and cfg.family in ("moe", "qwen35")):
             from ..models import family_io
             dev = "cuda" if torch.cuda.is_available() else "cpu"
-            if cfg.family == "moe":
+            extra = {}
+            if a.kind == "hf-qwen35":
+                w, unconsumed = _load_hf_qwen35(cache, cfg)
+                cache.close()
+                plan["known_unconsumed_tensors"] = len(unconsumed)
+                extra = {"known_unconsumed": unconsumed, "source_fingerprints": tuple(fps)}
+            elif cfg.family == "moe":
                 w = _moe.init_random_moe_weights(cfg, dev, seed=a.seed)
             else:
                 w = _q35.init_random_qwen35_weights(cfg, dev, seed=a.seed)
             if a.synthetic_tokenizer:
+                if a.kind != "random-llama":
+                    raise CliError("--synthetic-tokenizer applies to kind random-llama")
                 tokenizer_json = _synthetic_tokenizer(cfg.vocab)
             dl = family_io.export_family_gguf(cfg, w, a.output, tokenizer_json=tokenizer_json, chat_template=chat_template,
                                               converter_args={"kind": a.kind, "commit": a.converter_commit, "seed": a.seed,
-                                                              "weight_format": a.weight_format})
+                                                              "weight_format": a.weight_format}, **extra)
             _write_lock(a.derived_lock, dl)
             emit({"written": True, **plan, "size_bytes": dl["output"]["size_bytes"], "sha256": dl["output"]["sha256"],
                   "fingerprint": dl["fingerprint"]})

@@ -674,13 +674,15 @@ class Engine:
 def build_engine(cfg: ModelConfig, device="cuda", seed: int = 0, num_pages: Optional[int] = None,
                  max_batch: int = 64, use_cuda_graphs: bool = True, tp=None, ep=None) -> Engine:
     """Random-init engine for a named shape (benchmarks, tests, smoke).  `ep` (expert-parallel context) applies to
-    the mixture-of-experts family."""
+    the mixture-of-experts family and to hybrid models with a sparse MLP."""
     device = torch.device(device)
     tp_size, tp_rank = (tp.size, tp.rank) if tp is not None else (1, 0)
     if cfg.family == "qwen35":
         from ..cache.hybrid import HybridCache
         from ..models.qwen35 import Qwen35Model, init_random_qwen35_weights
-        model = Qwen35Model(cfg, init_random_qwen35_weights(cfg, device, seed, tp_size=tp_size, tp_rank=tp_rank), tp)
+        ep_size, ep_rank = (ep.size, ep.rank) if ep is not None else (1, 0)
+        model = Qwen35Model(cfg, init_random_qwen35_weights(cfg, device, seed, tp_size=tp_size, tp_rank=tp_rank,
+                                                            ep_size=ep_size, ep_rank=ep_rank), tp, ep)
         if num_pages is None:
             num_pages = max_batch * ((cfg.max_context + cfg.page_size - 1) // cfg.page_size) + 8
         cache = HybridCache(cfg, num_pages, device, max_seqs=2 * max_batch + 2, kv_heads=model.local_kv_heads,

@@ -417,9 +417,11 @@ class GgufFile:
         return rec
 
 
-def recipe_metadata(bindings: list, static_fp8_kv: Optional[list] = None) -> dict:
+def recipe_metadata(bindings: list, static_fp8_kv: Optional[list] = None, known_unconsumed: Optional[list] = None) -> dict:
     rec = {"schema_version": "sllm-tensor-recipe-v1", "bindings": bindings, "logical_shapes": [],
            "static_fp8_kv": static_fp8_kv or []}
+    if known_unconsumed:
+        rec["known_unconsumed_tensors"] = sorted(known_unconsumed)
     raw = json.dumps(rec, sort_keys=True, separators=(",", ":"))
     return {EXT_VERSION_KEY: 1, RECIPE_KEY: raw, RECIPE_SHA_KEY: hashlib.sha256(raw.encode()).hexdigest()}
 

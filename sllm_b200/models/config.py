@@ -157,8 +157,14 @@ def _qwen35_moe():
     return qwen35_moe_shape()
 
 
+def _qwen35_moe_hybrid():
+    from .qwen35 import qwen35_moe_hybrid_shape
+    return qwen35_moe_hybrid_shape()
+
+
 NAMED = {
     "qwen35-moe": _qwen35_moe,
+    "qwen35-moe-hybrid": _qwen35_moe_hybrid,
     "tiny-llama": tiny_llama,
     "llama3-8b": llama3_8b,
     "llama3-70b": llama3_70b,

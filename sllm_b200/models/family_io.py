@@ -8,7 +8,8 @@ whose rows are expert-major.
 
 Tensor names, MoE layer i:  blk.i.attn_norm | attn_q | attn_k | attn_v | attn_output | attn_sinks | ffn_norm |
 ffn_gate_inp (router; rows past n_experts: the shared-expert gate and zero padding) | ffn_gate_up_exps | ffn_down_exps |
-ffn_gate_up_shexp | ffn_down_shexp.  Hybrid layer i: blk.i.attn_norm | ffn_norm | ffn_gate | ffn_up | ffn_down and either
+ffn_gate_up_shexp | ffn_down_shexp.  Hybrid layer i: blk.i.attn_norm | ffn_norm | ffn_gate | ffn_up | ffn_down (or, with
+a sparse MLP, the ffn_gate_inp / ffn_*_exps / ffn_*_shexp tensors of the MoE layer) and either
 attn_q | attn_k | attn_v | attn_gate | attn_output | attn_q_norm | attn_k_norm (full attention) or ssm_in | ssm_conv1d |
 ssm_a | ssm_dt | ssm_norm | ssm_out (gated delta net).
 
@@ -79,8 +80,11 @@ class _Sink:
 
 
 def export_family_gguf(cfg: ModelConfig, w, path: str, tokenizer_json: Optional[str] = None,
-                       chat_template: Optional[str] = None, converter_args: Optional[dict] = None) -> dict:
-    """Writes unsharded weights of a `moe` or `qwen35` model; returns the derived lock document."""
+                       chat_template: Optional[str] = None, converter_args: Optional[dict] = None,
+                       known_unconsumed: Optional[list] = None, source_fingerprints: tuple = ()) -> dict:
+    """Writes unsharded weights of a `moe` or `qwen35` model; returns the derived lock document.  `known_unconsumed`
+    names source tensors the converter left out on purpose (vision tower, multi-token-prediction head); they are
+    recorded in the tensor recipe."""
     if cfg.family not in FAMILIES:
         raise G.GgufError(f"family {cfg.family!r} is written by models.loader.export_llama_gguf")
     s = _Sink()
@@ -104,9 +108,16 @@ def export_family_gguf(cfg: ModelConfig, w, path: str, tokenizer_json: Optional[
         else:
             s.dense(p + "attn_norm.weight", l.in_norm)
             s.dense(p + "ffn_norm.weight", l.mlp_norm)
-            s.linear(p + "ffn_gate.weight", l.gate_up, 0, f)
-            s.linear(p + "ffn_up.weight", l.gate_up, f, 2 * f)
-            s.linear(p + "ffn_down.weight", l.down)
+            if l.router is not None:
+                s.linear(p + "ffn_gate_inp.weight", l.router)
+                s.experts(p + "ffn_gate_up_exps.weight", l.exp_gate_up)
+                s.experts(p + "ffn_down_exps.weight", l.exp_down)
+                s.linear(p + "ffn_gate_up_shexp.weight", l.shared_gate_up)
+                s.linear(p + "ffn_down_shexp.weight", l.shared_down)
+            else:
+                s.linear(p + "ffn_gate.weight", l.gate_up, 0, f)
+                s.linear(p + "ffn_up.weight", l.gate_up, f, 2 * f)
+                s.linear(p + "ffn_down.weight", l.down)
             if l.kind == "full":
                 s.linear(p + "attn_q.weight", l.qkv, 0, q)
                 s.linear(p + "attn_k.weight", l.qkv, q, q + kv)
@@ -132,9 +143,9 @@ def export_family_gguf(cfg: ModelConfig, w, path: str, tokenizer_json: Optional[
         md[G.FRONTEND_TOKENIZER_KEY] = tokenizer_json
     if chat_template is not None:
         md["tokenizer.chat_template"] = chat_template
-    md.update(G.recipe_metadata(s.bindings))
+    md.update(G.recipe_metadata(s.bindings, known_unconsumed=known_unconsumed))
     digests = G.write_gguf(path, md, s.tensors)
-    return G.make_derived_lock(path, digests, f"{cfg.name}:{cfg.family}", [], {"id": CONVERTER_ID, "args": converter_args or {}})
+    return G.make_derived_lock(path, digests, f"{cfg.name}:{cfg.family}", list(source_fingerprints), {"id": CONVERTER_ID, "args": converter_args or {}})
 
 
 def _gdn_in_rows(cfg: ModelConfig) -> int:
@@ -260,17 +271,30 @@ def load_family_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, 
     else:
         from .qwen35 import Qwen35Layer, Qwen35Weights
         ghd, vh, qh = cfg.gdn_head_dim, cfg.gdn_heads, cfg.gdn_qk_heads
-        for name, v in (("gdn_heads", vh), ("gdn_qk_heads", qh), ("ffn", f)):
+        sparse = cfg.n_experts > 0
+        for name, v in (("gdn_heads", vh), ("gdn_qk_heads", qh), ("ffn", tp_size if sparse else f)):
             if v % tp_size:
                 raise G.GgufError(f"{name} = {v} does not divide over {tp_size} tensor-parallel ranks")
+        if sparse and cfg.n_experts % ep_size:
+            raise G.GgufError("experts do not divide over the expert-parallel ranks")
+        per = cfg.n_experts // ep_size if sparse else 0
+        e_lo, e_hi = ep_rank * per, (ep_rank + 1) * per
         norm_dt = torch.bfloat16 if src.dt != torch.float32 else torch.float32
         for i in range(cfg.n_layers):
             p = f"blk.{i}."
-            gate_up = torch.cat([src.head_rows(p + "ffn_gate.weight", [(f, 1)], tp_size, tp_rank),
-                                 src.head_rows(p + "ffn_up.weight", [(f, 1)], tp_size, tp_rank)], dim=0)
-            common = dict(in_norm=src.dense(p + "attn_norm.weight"), mlp_norm=src.dense(p + "ffn_norm.weight"),
-                          gate_up=lin(gate_up),
-                          down=lin(src.head_rows(p + "ffn_down.weight", [(f, 1)], tp_size, tp_rank, transpose=True)))
+            common = dict(in_norm=src.dense(p + "attn_norm.weight"), mlp_norm=src.dense(p + "ffn_norm.weight"))
+            if sparse:
+                common.update(router=lin(src.dense(p + "ffn_gate_inp.weight")),
+                              exp_gate_up=src.experts(p + "ffn_gate_up_exps.weight", cfg.n_experts, e_lo, e_hi),
+                              exp_down=src.experts(p + "ffn_down_exps.weight", cfg.n_experts, e_lo, e_hi))
+                if src.has(p + "ffn_gate_up_shexp.weight"):
+                    common.update(shared_gate_up=lin(src.dense(p + "ffn_gate_up_shexp.weight")),
+                                  shared_down=lin(src.dense(p + "ffn_down_shexp.weight")))
+            else:
+                gate_up = torch.cat([src.head_rows(p + "ffn_gate.weight", [(f, 1)], tp_size, tp_rank),
+                                     src.head_rows(p + "ffn_up.weight", [(f, 1)], tp_size, tp_rank)], dim=0)
+                common.update(gate_up=lin(gate_up),
+                              down=lin(src.head_rows(p + "ffn_down.weight", [(f, 1)], tp_size, tp_rank, transpose=True)))
             if (i + 1) % cfg.full_attention_interval == 0:
                 gate = None
                 if src.has(p + "attn_gate.weight"):

@@ -27,8 +27,8 @@ class Qwen35Layer:
     kind: str                       # full | gdn
     in_norm: torch.Tensor
     mlp_norm: torch.Tensor
-    gate_up: LinearWeight
-    down: LinearWeight
+    gate_up: Optional[LinearWeight] = None
+    down: Optional[LinearWeight] = None
     # full attention
     qkv: Optional[LinearWeight] = None
     gate: Optional[LinearWeight] = None
@@ -42,6 +42,13 @@ class Qwen35Layer:
     dt_bias: Optional[torch.Tensor] = None      # bf16 [v_heads]
     out_norm: Optional[torch.Tensor] = None     # fp32 [hd]
     out_proj: Optional[LinearWeight] = None
+    # sparse MLP (Qwen3.5-MoE): replaces gate_up / down when the configuration has experts.  `router` holds the
+    # expert rows, then the shared-expert gate vector, then zero padding to a multiple of 8
+    router: Optional[LinearWeight] = None
+    exp_gate_up: Optional[object] = None        # W4Weight, local experts, [2 * expert_ffn, d] each
+    exp_down: Optional[object] = None           # W4Weight, local experts, [d, expert_ffn] each
+    shared_gate_up: Optional[LinearWeight] = None
+    shared_down: Optional[LinearWeight] = None
 
 
 @dataclass
@@ -69,9 +76,10 @@ def _head_rows(w: torch.Tensor, segments: list, tp_size: int, tp_rank: int) -> t
 
 
 def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: float = 0.02, tp_size: int = 1,
-                               tp_rank: int = 0) -> Qwen35Weights:
+                               tp_rank: int = 0, ep_size: int = 1, ep_rank: int = 0) -> Qwen35Weights:
     """Every rank draws the full tensors from the same generator and keeps its shard: attention and gated-delta-net
-    layers are sharded by head, the MLP by intermediate channel; norms, embedding and output matrix are replicated."""
+    layers are sharded by head, the dense MLP by intermediate channel, routed experts by expert range; norms,
+    embedding, output matrix, router and shared expert are replicated."""
     device = torch.device(device)
     gen = torch.Generator(device="cpu")
     gen.manual_seed(seed)
@@ -96,10 +104,38 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
         return _head_rows(w.t(), segments, tp_size, tp_rank).t()
 
     f = cfg.ffn
+    E = cfg.n_experts
+    if E % ep_size:
+        raise ValueError(f"{E} experts do not divide over {ep_size} expert-parallel ranks")
+    e_lo, e_hi = ep_rank * (E // ep_size), (ep_rank + 1) * (E // ep_size)
+
+    def sparse_mlp():
+        from ..ops.w4 import W4Weight
+        F, fs = cfg.expert_ffn, cfg.shared_expert_ffn
+        router = rnd((E, d))
+        gu_local, dn_local = [], []
+        for e in range(E):                       # every rank advances the generator past every expert
+            gu, dn = rnd((2 * F, d)), rnd((d, F))
+            if e_lo <= e < e_hi:
+                gu_local.append(gu)
+                dn_local.append(dn)
+        out = {}
+        if fs > 0:
+            sgu, sdn, sg = rnd((2 * fs, d)), rnd((d, fs)), rnd((1, d))
+            router = torch.cat([router, sg, torch.zeros((7, d))], dim=0)
+            out.update(shared_gate_up=lin(sgu), shared_down=lin(sdn))
+        out.update(router=lin(router),
+                   exp_gate_up=W4Weight.quantize(cfg.expert_format, torch.stack(gu_local), device, keep_file=False),
+                   exp_down=W4Weight.quantize(cfg.expert_format, torch.stack(dn_local), device, keep_file=False))
+        return out
+
     layers = []
     for i in range(cfg.n_layers):
-        common = dict(in_norm=vec(rnd((d,), 0.05)), mlp_norm=vec(rnd((d,), 0.05)),
-                      gate_up=lin(rows(rnd((2 * f, d)), [(f, 1), (f, 1)])), down=lin(cols(rnd((d, f)), [(f, 1)])))
+        common = dict(in_norm=vec(rnd((d,), 0.05)), mlp_norm=vec(rnd((d,), 0.05)))
+        if E > 0:
+            common.update(sparse_mlp())
+        else:
+            common.update(gate_up=lin(rows(rnd((2 * f, d)), [(f, 1), (f, 1)])), down=lin(cols(rnd((d, f)), [(f, 1)])))
         if (i + 1) % cfg.full_attention_interval == 0:
             hq, hkv = cfg.n_heads, cfg.n_kv_heads
             qkv = rows(rnd((cfg.q_size + 2 * cfg.kv_size, d)), [(hq, hd), (hkv, hd), (hkv, hd)])
@@ -126,12 +162,15 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
 
 
 class Qwen35Model:
-    def __init__(self, cfg: ModelConfig, weights: Qwen35Weights, tp=None):
+    def __init__(self, cfg: ModelConfig, weights: Qwen35Weights, tp=None, ep=None):
+        from ..parallel.ep import NoEP
         self.cfg, self.w = cfg, weights
         self.tp = tp or NoTP()
+        self.ep = ep or NoEP()
+        self.e_lo, self.e_hi = self.ep.expert_range(cfg.n_experts) if cfg.n_experts else (0, 0)
         n = self.tp.size
         for name, v in (("n_heads", cfg.n_heads), ("n_kv_heads", cfg.n_kv_heads), ("gdn_heads", cfg.gdn_heads),
-                        ("gdn_qk_heads", cfg.gdn_qk_heads), ("ffn", cfg.ffn)):
+                        ("gdn_qk_heads", cfg.gdn_qk_heads), ("ffn", cfg.ffn if not cfg.n_experts else n)):
             if v % n:
                 raise ValueError(f"{name} = {v} does not divide over {n} tensor-parallel ranks")
         # heads of this rank (attention and gated-delta-net layers are sharded by head)
@@ -145,7 +184,18 @@ class Qwen35Model:
     def _mlp(self, h, lw):
         cfg = self.cfg
         x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
-        return self.tp.row_linear(ops.gated_act(ops.linear(x, lw.gate_up), cfg.act), lw.down, h)
+        if lw.router is None:
+            return self.tp.row_linear(ops.gated_act(ops.linear(x, lw.gate_up), cfg.act), lw.down, h)
+        # routed experts (softmax over the selected logits = softmax over all, renormalised over the selection) plus
+        # the always-on shared expert under its sigmoid gate (crates/sllm-core/src/qwen35_moe.rs:1576-1600)
+        from ..ops import moe as M
+        logits = ops.linear(x, lw.router)
+        idx, rw = M.route(logits[:, :cfg.n_experts], cfg.top_k)
+        h = self.ep.experts_combine(x, idx, rw, lw.exp_gate_up, lw.exp_down, cfg.act, self.e_lo, self.e_hi, h)
+        if lw.shared_gate_up is not None:
+            sh = ops.linear(ops.gated_act(ops.linear(x, lw.shared_gate_up), cfg.act), lw.shared_down)
+            h = M.shared_add(h, sh, logits[:, cfg.n_experts])
+        return h
 
     def hidden(self, b: ForwardBatch, cache) -> torch.Tensor:
         cfg, w = self.cfg, self.w
@@ -197,6 +247,26 @@ class Qwen35Model:
 
     def greedy(self, b, cache):
         return ops.argmax(self.logits(self._keep(self.hidden(b, cache)), b))
+
+
+def qwen35_moe_hybrid_shape(layers: int = 40) -> ModelConfig:
+    """Qwen3.5-MoE as the reference pins it (crates/sllm-core/src/qwen35_moe.rs:1177-1189): 40 layers of width 2048,
+    every fourth one full attention (16 heads, 2 kv heads, 256 wide), the others gated delta nets; every MLP is 256
+    MXFP4 experts of width 512 with 8 selected per token plus a gated shared expert of width 512; vocabulary 248 320."""
+    return ModelConfig(name="qwen35-moe-hybrid", family="qwen35", n_layers=layers, d_model=2048, n_heads=16, n_kv_heads=2,
+                       head_dim=256, ffn=512, vocab=248320, rope_theta=1e7, rotary_dim=64, rms_eps=1e-6, norm_offset_one=True,
+                       weight_format="bf16", kv_format="bf16", qk_norm=True, full_attention_interval=4, gdn_heads=32,
+                       gdn_qk_heads=16, gdn_head_dim=128, gdn_conv_kernel=4, attn_output_gate=True, n_experts=256, top_k=8,
+                       expert_ffn=512, shared_expert_ffn=512, expert_format="mxfp4", max_context=8192)
+
+
+def tiny_qwen35_moe() -> ModelConfig:
+    """CPU-checkable hybrid with a sparse MLP: the tiny hybrid's layers, 8 experts of width 128 with 2 selected, and
+    the gated shared expert."""
+    c = tiny_qwen35()
+    c.name, c.n_experts, c.top_k, c.expert_ffn, c.shared_expert_ffn, c.expert_format = "tiny-qwen35-moe", 8, 2, 128, 128, "mxfp4"
+    c.d_model = 128
+    return c
 
 
 def tiny_qwen35() -> ModelConfig:

@@ -321,7 +321,7 @@ def test_serve_bench_against_live_server(model):
             proc.kill()
 
 
-@pytest.mark.parametrize("artifact", ["tiny-moe", "tiny-shared-moe", "tiny-qwen35"])
+@pytest.mark.parametrize("artifact", ["tiny-moe", "tiny-shared-moe", "tiny-qwen35", "tiny-qwen35-moe"])
 def test_other_families_convert_and_generate(capsys, tmp_path, artifact):
     """The mixture-of-experts and hybrid families go through the same converter, verification and CLI commands."""
     g, l = str(tmp_path / "m.gguf"), str(tmp_path / "m.lock.json")

@@ -181,7 +181,7 @@ def test_engine_served_over_http_greedy_json_and_concurrency(engine_client):
     assert c.post("/v1/chat/completions", json={**req, "max_completion_tokens": 4096}).status_code == 400   # context bound
 
 
-@pytest.mark.parametrize("artifact", ["tiny-shared-moe", "tiny-qwen35"])
+@pytest.mark.parametrize("artifact", ["tiny-shared-moe", "tiny-qwen35", "tiny-qwen35-moe"])
 def test_other_model_families_served_from_converted_files(tmp_path, artifact):
     """A mixture-of-experts file and a hybrid (gated delta net) file go convert -> verify -> open_model -> HTTP."""
     import argparse

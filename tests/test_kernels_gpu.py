@@ -762,12 +762,12 @@ def test_gdn_kernels_match_oracle():
 def test_hybrid_and_gemma_models_gpu_match_cpu():
     from sllm_b200.engine.engine import build_engine
     from sllm_b200.models import config as MC
-    from sllm_b200.models.qwen35 import tiny_qwen35
+    from sllm_b200.models.qwen35 import tiny_qwen35, tiny_qwen35_moe
     gem = MC.ModelConfig(name="tiny-gemma", family="gemma4", n_layers=3, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512,
                          vocab=1024, act="gelu_tanh", tie_embeddings=True, embedding_scale=16.0, logit_softcap=30.0,
                          weight_format="bf16", kv_format="bf16", sliding_window=16, window_layers=[True, True, False], qk_norm=True,
                          post_norms=True, max_context=128)
-    for cfg in (tiny_qwen35(), gem):
+    for cfg in (tiny_qwen35(), tiny_qwen35_moe(), gem):       # dense hybrid, hybrid with routed experts, Gemma options
         g = build_engine(cfg, DEV, seed=1, num_pages=32, max_batch=2)
         c = build_engine(cfg, "cpu", seed=1, num_pages=32, max_batch=2, use_cuda_graphs=False) if cfg.family == "qwen35" \
             else _cpu_twin(g, cfg)
