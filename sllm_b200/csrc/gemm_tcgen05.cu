@@ -958,6 +958,33 @@ int cached_kmajor_tmap(CUtensorMap* out, const void* ptr, int elem_bytes, long l
   return rc;
 }
 
+int cached_plain_tmap(CUtensorMap* out, const void* ptr, long long rows, long long row_bytes, long long row_stride_bytes,
+                      int box_bytes, int box_rows) {
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (row_stride_bytes & 15) || (box_bytes & 15) || box_bytes <= 0 ||
+      box_rows <= 0 || box_rows > 256)
+    return SLLM_ERR_ALIGNMENT;
+  TmapKey key{ptr, rows, row_bytes, row_stride_bytes, -box_bytes, box_rows};   // negative element size: plain maps
+  std::lock_guard<std::mutex> g(g_tmap_mutex);
+  auto it = g_tmap_cache.find(key);
+  if (it != g_tmap_cache.end()) {
+    *out = it->second;
+    return SLLM_OK;
+  }
+  auto fn = get_encode_fn();
+  if (!fn) return SLLM_ERR_DRIVER_ENTRY;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(row_stride_bytes)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return SLLM_ERR_CUDA;
+  if (g_tmap_cache.size() > 65536) g_tmap_cache.clear();
+  g_tmap_cache[key] = *out;
+  return SLLM_OK;
+}
+
 template <int BN, bool kScaled>
 constexpr size_t gemm_fixed_smem() {
   return sizeof(GemmBarriers<BN>) + (kScaled ? sizeof(GemmScales<BN>) : 0) + 1024;

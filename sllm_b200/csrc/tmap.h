@@ -10,4 +10,9 @@ namespace sllm {
 int cached_kmajor_tmap(CUtensorMap* out, const void* ptr, int elem_bytes, long long rows, long long k_elems,
                        long long row_stride_bytes, int box_rows);
 
+// Tensor map over a row-major byte matrix [rows, row_bytes] with a box of {box_bytes, box_rows} and no swizzle
+// (box_bytes, the row stride and the base address are multiples of 16).  Cached like the one above.
+int cached_plain_tmap(CUtensorMap* out, const void* ptr, long long rows, long long row_bytes, long long row_stride_bytes,
+                      int box_bytes, int box_rows);
+
 }  // namespace sllm

@@ -81,7 +81,10 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
     layers are sharded by head, the dense MLP by intermediate channel, routed experts by expert range; norms,
     embedding, output matrix, router and shared expert are replicated."""
     device = torch.device(device)
-    gen = torch.Generator(device="cpu")
+    # benchmark shapes with routed experts (~10^10 parameters) draw and quantise on the target device; everything
+    # else draws on the CPU so that every device sees identical weights
+    big = cfg.n_layers * cfg.n_experts * cfg.expert_ffn * cfg.d_model * 3 > 2e9 and device.type == "cuda"
+    gen = torch.Generator(device=device if big else "cpu")
     gen.manual_seed(seed)
     dt = torch.float32 if cfg.weight_format == "fp32" else torch.bfloat16
     d, hd = cfg.d_model, cfg.head_dim
@@ -89,7 +92,7 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
     width = (2 * qh + vh) * ghd
 
     def rnd(shape, s=std):
-        return (torch.randn(shape, generator=gen, dtype=torch.float32) * s)
+        return (torch.randn(shape, generator=gen, dtype=torch.float32, device=device if big else "cpu") * s)
 
     def lin(w):
         return LinearWeight("dense", w.to(dt).contiguous().to(device))
@@ -122,11 +125,11 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
         out = {}
         if fs > 0:
             sgu, sdn, sg = rnd((2 * fs, d)), rnd((d, fs)), rnd((1, d))
-            router = torch.cat([router, sg, torch.zeros((7, d))], dim=0)
+            router = torch.cat([router, sg, torch.zeros((7, d), device=router.device)], dim=0)
             out.update(shared_gate_up=lin(sgu), shared_down=lin(sdn))
-        out.update(router=lin(router),
-                   exp_gate_up=W4Weight.quantize(cfg.expert_format, torch.stack(gu_local), device, keep_file=False),
-                   exp_down=W4Weight.quantize(cfg.expert_format, torch.stack(dn_local), device, keep_file=False))
+        quant = W4Weight.quantize_device if big else (lambda f, w: W4Weight.quantize(f, w, device, keep_file=False))
+        out.update(router=lin(router), exp_gate_up=quant(cfg.expert_format, torch.stack(gu_local)),
+                   exp_down=quant(cfg.expert_format, torch.stack(dn_local)))
         return out
 
     layers = []
@@ -148,7 +151,7 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
             n_in = width + vh * ghd + 2 * vh
             segs = [(qh, ghd), (qh, ghd), (vh, ghd), (vh, ghd), (vh, 1), (vh, 1)]
             w_loc = rows(rnd((n_in, d)), segs)
-            w_in = torch.zeros(((w_loc.shape[0] + 7) // 8 * 8, d))
+            w_in = torch.zeros(((w_loc.shape[0] + 7) // 8 * 8, d), device=w_loc.device)
             w_in[:w_loc.shape[0]] = w_loc
             conv = rows(rnd((width, cfg.gdn_conv_kernel), 0.3), segs[:3])
             layers.append(Qwen35Layer("gdn", in_proj=lin(w_in), conv_w=vec(conv),

@@ -171,3 +171,65 @@ def dequant_kv_nvfp4_rows(rows: torch.Tensor, outer: torch.Tensor, d: int) -> to
     bs = codecs.decode_e4m3fn(flat[:, d // 2:]) * outer.cpu().numpy().reshape(-1, 1).astype(np.float32)
     vals = codecs.decode_e2m1(codes) * np.repeat(bs, 16, axis=1)[:, :d]
     return torch.from_numpy(vals.astype(np.float32).reshape(*lead, d)).to(rows.device)
+
+
+# ------------------------------------------------------------------------------------------ 4-bit activations
+_E2M1_VALUES = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+
+
+def _e2m1_codes(a: torch.Tensor) -> torch.Tensor:
+    """Nearest E2M1 magnitude index (ties to the even index, saturating at 6) of non-negative fp32 values."""
+    a = a.clamp(max=6.0)
+    hi = torch.bucketize(a, _E2M1_VALUES).clamp(max=7)
+    lo = (hi - 1).clamp(min=0)
+    dlo, dhi = (a - _E2M1_VALUES[lo]).abs(), (_E2M1_VALUES[hi] - a).abs()
+    return torch.where((dhi < dlo) | ((dhi == dlo) & ((hi & 1) == 0)), hi, lo)
+
+
+def quant_act_fp4(x: torch.Tensor, fmt: str):
+    """Oracle of the activation quantiser of the W4A4 path (csrc/gemm_fp4.cu): x [T, K] -> (codes uint8 [T, K_pad / 2]
+    with element 2 i in the low nibble, block scales uint8 [T, K_pad / block], row scales fp32 [T]); K padded to 256."""
+    t, k = x.shape
+    block = 32 if fmt == "mxfp4" else 16
+    k_pad = (k + 255) // 256 * 256
+    xf = torch.zeros((t, k_pad), dtype=torch.float32)
+    xf[:, :k] = x.float()
+    blk = xf.view(t, k_pad // block, block)
+    finite = torch.where(torch.isfinite(blk), blk.abs(), torch.zeros_like(blk))
+    bamax = finite.amax(dim=2)
+    if fmt == "mxfp4":
+        outer = torch.ones(t, dtype=torch.float32)
+        bits = bamax.contiguous().view(torch.int32).to(torch.int64) + 0x00200000
+        code = (((bits >> 23) & 0xFF) - 2).clamp(0, 254)
+        code = torch.where(bamax > 0, code, torch.zeros_like(code))
+        scale = torch.where(bamax > 0, torch.ldexp(torch.ones_like(bamax), (code - 127).to(torch.int32)), torch.zeros_like(bamax))
+        sf = code.to(torch.uint8)
+    else:
+        amax = finite.view(t, -1).amax(dim=1)
+        outer = torch.where(amax > 0, amax / 2688.0, torch.ones_like(amax)).float()
+        want = ((bamax / 6.0) / outer[:, None]).clamp(max=448.0)
+        sf = want.to(torch.float8_e4m3fn).view(torch.uint8)
+        scale = sf.view(torch.float8_e4m3fn).float() * outer[:, None]
+    safe = torch.where(scale > 0, scale, torch.ones_like(scale))
+    q = blk / safe.unsqueeze(-1)
+    idx = _e2m1_codes(torch.nan_to_num(q.abs(), nan=0.0))
+    codes = idx | (((q < 0) & (idx != 0)).to(torch.int64) << 3)
+    codes = torch.where((scale > 0).unsqueeze(-1), codes, torch.zeros_like(codes)).view(t, k_pad // 2, 2)
+    packed = (codes[..., 0] | (codes[..., 1] << 4)).to(torch.uint8)
+    return packed, sf, outer
+
+
+def dequant_act_fp4(xq: torch.Tensor, xsf: torch.Tensor, outer: torch.Tensor, fmt: str) -> torch.Tensor:
+    """fp32 [T, K_pad] of what `quant_act_fp4` (or the kernel) wrote."""
+    xq, xsf, outer = xq.cpu(), xsf.cpu(), outer.cpu().float()
+    t = xq.shape[0]
+    block = 32 if fmt == "mxfp4" else 16
+    codes = torch.stack([xq & 0xF, xq >> 4], dim=-1).view(t, -1).long()
+    mag = _E2M1_VALUES[codes & 7]
+    vals = torch.where((codes & 8) != 0, -mag, mag)
+    if fmt == "mxfp4":
+        s = torch.ldexp(torch.ones(xsf.shape), xsf.to(torch.int32) - 127)
+    else:
+        s = xsf.view(torch.float8_e4m3fn).float()
+    s = s[:, :vals.shape[1] // block]
+    return vals * s.repeat_interleave(block, dim=1) * outer[:, None]

@@ -35,6 +35,7 @@ class W4Weight:
     tensor_scale: Optional[torch.Tensor]   # fp32 [groups] (nvfp4)
     file_packed: Optional[np.ndarray] = None    # kept on CPU weights for the oracle
     file_scales: Optional[np.ndarray] = None
+    native: Optional[torch.Tensor] = None       # tiles of the block-scaled tensor-core path (see `native_tiles`)
 
     @property
     def block(self) -> int:
@@ -185,7 +186,41 @@ class W4Weight:
         return codecs.pack_nibbles(codes), np.ascontiguousarray(sc[:self.n, :(self.k + self.block - 1) // self.block])
 
     def nbytes(self) -> int:
-        return self.tiles.numel()
+        return self.tiles.numel() + (self.native.numel() if self.native is not None else 0)
+
+    def native_tiles(self) -> torch.Tensor:
+        """Tiles for the W4A4 kernel (csrc/gemm_fp4.cu), built once from the resident ones on their device:
+        uint8 [groups, row tiles, K blocks of 256, 16384 + 512 * atoms].  A tile is the 128-byte-swizzled shared-memory
+        image of 128 rows x 128 B of codes in the standard nibble order (element 2 i in the low nibble of byte i),
+        followed by the block's scale atoms (4 for block 16, 2 for block 32): 512 bytes = [32 r][4 j][4 s] holding scale s
+        of row r + 32 j, the form tcgen05.cp moves to TMEM."""
+        if self.native is not None:
+            return self.native
+        t = self.tiles
+        g, rt, kc, _ = t.shape
+        sb = 128 // self.block
+        kb = (kc + 1) // 2
+        dev = t.device
+        rr = (torch.arange(128, device=dev) & 7).view(128, 1)
+        src = (torch.arange(8, device=dev).view(1, 8) ^ rr).view(1, 1, 1, 128, 8, 1)
+        out = torch.empty((g, rt, kb, 16384 + 128 * 2 * sb), dtype=torch.uint8, device=dev)
+        step = max(1, (1 << 24) // max(1, rt * kc * 128 * 16))
+        for g0 in range(0, g, step):
+            tt = t[g0:g0 + step]
+            gg = tt.shape[0]
+            if kc % 2:
+                tt = torch.cat([tt, torch.zeros((gg, rt, 1, tt.shape[3]), dtype=torch.uint8, device=dev)], dim=2)
+            words = tt[..., :8192].contiguous().view(torch.int32).view(gg, rt, 2 * kb, 128, 16).to(torch.int64) & 0xFFFFFFFF
+            # resident nibble order (e0,e2,e4,e6,e1,e3,e5,e7) -> bytes (e1 e0), (e3 e2), (e5 e4), (e7 e6)
+            by = torch.stack([((words >> (4 * b)) & 0xF) | (((words >> (16 + 4 * b)) & 0xF) << 4) for b in range(4)],
+                             dim=-1).to(torch.uint8)
+            rows = by.view(gg, rt, kb, 2, 128, 64).permute(0, 1, 2, 4, 3, 5).reshape(gg, rt, kb, 128, 8, 16)
+            img = torch.gather(rows, 4, src.expand(gg, rt, kb, 128, 8, 16)).reshape(gg, rt, kb, 16384)
+            sc = tt[..., 8192:].reshape(gg, rt, kb, 2, 128, sb).permute(0, 1, 2, 4, 3, 5).reshape(gg, rt, kb, 4, 32, 2 * sb // 4, 4)
+            atoms = sc.permute(0, 1, 2, 5, 4, 3, 6).reshape(gg, rt, kb, 128 * 2 * sb)
+            out[g0:g0 + gg] = torch.cat([img, atoms], dim=3)
+        self.native = out
+        return out
 
 
 def _bn_for(tokens: int) -> int:
@@ -250,4 +285,121 @@ def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = N
                                      x.stride(0), t, mgt, y.stride(0), bn, splits, 0, _p(wsp.ws), wsp.ws.numel(),
                                      _p(wsp.counters), wsp.counters.numel(), _p(wsp.status), _stream())
     _lib.check(rc, "gemm_w4")
+    return y
+
+
+# ------------------------------------------------------------------------------------------ W4A4 (block-scaled MMA)
+_W4A4 = {"on": None}
+
+
+def w4a4_enabled() -> bool:
+    """Whether 4-bit GEMMs quantise their activations to the weights' own 4-bit format and run on the block-scaled
+    tensor-core path (SLLM_W4A4=1 or `set_w4a4(True)`); off by default: W4A16 is the accuracy baseline."""
+    if _W4A4["on"] is None:
+        import os
+        _W4A4["on"] = os.environ.get("SLLM_W4A4", "0") == "1"
+    return _W4A4["on"]
+
+
+def set_w4a4(on: bool) -> None:
+    _W4A4["on"] = bool(on)
+
+
+def act_quant_fp4(x: torch.Tensor, fmt: str, src_row: Optional[torch.Tensor] = None, tokens: Optional[int] = None):
+    """bf16 [T, K] -> (codes uint8 [T, K_pad / 2], block scales uint8 [T, 2 K_pad / block], row scales fp32 [T]) with K
+    padded to 256.  The scale matrix is the kernel's operand: four scale bytes, then four unused ones (`sf_compact`
+    drops them).  nvfp4: row scale amax / 2688, UE4M3 block scales; mxfp4: UE8M0 block scales, row scale 1.  With
+    `src_row` (int32 [T]) token t reads row src_row[t] of x."""
+    from . import reference
+    t = tokens if tokens is not None else (x.shape[0] if src_row is None else src_row.numel())
+    k = x.shape[1]
+    block = 32 if fmt == "mxfp4" else 16
+    k_pad = (k + 255) // 256 * 256
+    if _lib.on_cpu(x):
+        xs = x if src_row is None else x.index_select(0, src_row.long()[:t])
+        codes, sf, outer = reference.quant_act_fp4(xs[:t], fmt)
+        return codes, sf_padded(sf), outer
+    from .core import _p, _stream
+    P, I = C.c_void_p, C.c_int
+    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_act_quant_fp4", (I, [P, I, I, I, I, P, I, P, P, I, P, P]))
+    if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or k % 8:
+        raise ValueError("act_quant_fp4: bf16 rows with a stride and width that are multiples of 8")
+    xq = torch.empty((t, k_pad // 2), dtype=torch.uint8, device=x.device)
+    xsf = torch.empty((t, 2 * k_pad // block), dtype=torch.uint8, device=x.device)      # a multiple of 16 bytes
+    outer = torch.empty((t,), dtype=torch.float32, device=x.device)
+    rc = _lib.kernels().sllm_act_quant_fp4(_p(x), x.stride(0), t, k, k_pad, _p(src_row), 0 if fmt == "mxfp4" else 1, _p(xq),
+                                           _p(xsf), xsf.stride(0), _p(outer), _stream())
+    _lib.check(rc, "act_quant_fp4")
+    return xq, xsf, outer
+
+
+def sf_padded(sf: torch.Tensor) -> torch.Tensor:
+    """Compact block scales [T, n] -> the kernel's operand [T, 2 n]: every four scale bytes followed by four zeros."""
+    t, n = sf.shape
+    out = torch.zeros((t, n // 4, 8), dtype=torch.uint8, device=sf.device)
+    out[:, :, :4] = sf.view(t, n // 4, 4)
+    return out.view(t, 2 * n)
+
+
+def sf_compact(xsf: torch.Tensor) -> torch.Tensor:
+    t, n = xsf.shape
+    return xsf.view(t, n // 8, 8)[:, :, :4].reshape(t, n // 2)
+
+
+def linear_w4a4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = None, tok_off: Optional[torch.Tensor] = None,
+                tok_scale: Optional[torch.Tensor] = None, max_group_tokens: Optional[int] = None, splits: int = 0,
+                row_ptr: Optional[torch.Tensor] = None, quantized=None) -> Optional[torch.Tensor]:
+    """`linear_w4` with the activations quantised to the weights' 4-bit format first (or passed as `quantized` =
+    (codes, block scales, row scales) from `act_quant_fp4`).  The tensor core multiplies E2M1 by E2M1 and applies both
+    block scales; the row and tensor scales are applied to the fp32 sums."""
+    t, k = x.shape if quantized is None else (quantized[0].shape[0], w.k)
+    if k != w.k:
+        raise ValueError("input width does not match the weight")
+    q = quantized if quantized is not None else act_quant_fp4(x, w.fmt)
+    xq, xsf, outer = q
+    if _lib.on_cpu(xq):
+        from . import reference
+        xf = reference.dequant_act_fp4(xq, sf_compact(xsf), outer, w.fmt)[:, :k]
+        out = torch.zeros((t, w.n), dtype=torch.float32)
+        offs = [0, t] if tok_off is None else tok_off.tolist()
+        for g in range(w.groups):
+            a, b = offs[g], offs[g + 1]
+            if b > a:
+                out[a:b] = xf[a:b] @ w.dequantized(g).t()
+        if tok_scale is not None:
+            out = out * tok_scale.float()[:, None]
+        if residual is not None:
+            out = out + residual.float()
+        return out.to(torch.bfloat16)
+    from .core import _p, _stream, workspace
+    P, I, L = C.c_void_p, C.c_int, C.c_longlong
+    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_gemm_fp4", (I, [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I,
+                                                                P, L, P, I, P, P]))
+    if w.groups > 1 and tok_off is None:
+        raise ValueError("grouped weights need token offsets")
+    tiles = w.native_tiles()
+    kb = tiles.shape[2]
+    mgt = max_group_tokens or t
+    bn = _bn_for(mgt if tok_off is None else min(mgt, 32))
+    min_splits = (kb + 7) // 8 if bn > 32 else 1
+    if splits <= 0:
+        ctas = (w.n_rows // 128) * (w.groups if tok_off is None else max(1, min(w.groups, t))) * ((min(mgt, t) + bn - 1) // bn)
+        splits = min_splits
+        while ctas * splits < 296 and splits * 2 <= max(1, kb // 2) and splits < 16:
+            splits *= 2
+    splits = max(splits, min_splits)
+    wsp = workspace(xq.device)
+    if _lib.audit_enabled():
+        _lib.record_dispatch("linear_w4a4", "gemm_fp4_kernel", fmt=w.fmt, tokens=t, n=w.n, k=w.k, groups=w.groups,
+                             grouped=tok_off is not None, bn=bn, splits=splits)
+    y = None
+    if row_ptr is None:
+        y = torch.empty((t, w.n), dtype=torch.bfloat16, device=xq.device)
+    elif residual is not None or row_ptr.dtype != torch.int64 or row_ptr.numel() < t:
+        raise ValueError("row_ptr: int64 addresses, one per token row, and no residual")
+    rc = _lib.kernels().sllm_gemm_fp4(_p(tiles), _p(w.tensor_scale), _p(xq), _p(xsf), xsf.stride(0), _p(outer), _p(y),
+                                      _p(residual), _p(tok_off), _p(tok_scale), _p(row_ptr), 0 if w.fmt == "mxfp4" else 1,
+                                      w.groups, w.n_rows, w.n, kb * 256, t, mgt, w.n, bn, splits, _p(wsp.ws), wsp.ws.numel(),
+                                      _p(wsp.counters), wsp.counters.numel(), _p(wsp.status), _stream())
+    _lib.check(rc, "gemm_fp4")
     return y

@@ -117,9 +117,11 @@ def bench_gemm(m, n, k, fp8, reps, graph=False):
             "TFLOPs": flops / t / 1e12, "roofline_us": roof * 1e6, "fraction": roof / t, "fraction_basis": tag}
 
 
-def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False):
-    """Dense (groups = 1) or grouped W4A16 GEMM; grouped: m tokens spread evenly over the groups."""
-    from ..ops.w4 import W4Weight, linear_w4
+def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False, a4=False, active=0):
+    """Dense (groups = 1) or grouped 4-bit-weight GEMM; grouped: m tokens spread evenly over the first `active` groups
+    (all of them when 0).  a4: activations quantised to the weights' format and the block-scaled tensor-core kernel
+    (the quantiser's launch is inside the timed call); otherwise the W4A16 kernel."""
+    from ..ops.w4 import W4Weight, linear_w4, linear_w4a4
     dev = "cuda"
     g = max(1, groups)
     import numpy as np
@@ -131,13 +133,22 @@ def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False):
     w = W4Weight.from_file_layout(fmt, packed, scales, k, None, dev)
     x = torch.randn(m, k, device=dev).bfloat16()
     off = None
+    act = g if active <= 0 else min(active, g)
+    mgt = m
     if g > 1:
-        per = [m // g + (1 if i < m % g else 0) for i in range(g)]
+        per = [m // act + (1 if i < m % act else 0) if i < act else 0 for i in range(g)]
         off = torch.tensor([0] + list(np.cumsum(per)), dtype=torch.int32, device=dev)
-    call = lambda w_: linear_w4(x, w_, tok_off=off, max_group_tokens=m)
-    wbytes = w.nbytes()
+        mgt = max(per)
+    if a4:
+        w.native_tiles()
+        call = lambda w_: linear_w4a4(x, w_, tok_off=off, max_group_tokens=mgt)
+        wbytes = w.native.numel() * act // g
+    else:
+        call = lambda w_: linear_w4(x, w_, tok_off=off, max_group_tokens=mgt)
+        wbytes = w.tiles.numel() * act // g
     if graph:
-        ws = [w] + [W4Weight(w.fmt, w.groups, w.n, w.k, w.n_rows, w.k_pad, w.tiles.clone(), w.tensor_scale)
+        ws = [w] + [W4Weight(w.fmt, w.groups, w.n, w.k, w.n_rows, w.k_pad, w.tiles if a4 else w.tiles.clone(), w.tensor_scale,
+                             native=w.native.clone() if a4 else None)
                     for _ in range(_copies(wbytes) - 1)]
         t = timed_graph([(lambda w_=w_: call(w_)) for w_ in ws], reps)
     else:
@@ -146,7 +157,8 @@ def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False):
     bytes_ = wbytes + 2 * m * k + 2 * m * n
     flops = 2.0 * m * n * k
     roof = max(bytes_ / bw, flops / fl)
-    return {"op": "gemm_w4", "fmt": fmt, "m": m, "n": n, "k": k, "groups": g, "us": t * 1e6, "GBps": bytes_ / t / 1e9,
+    return {"op": "gemm_w4a4" if a4 else "gemm_w4", "fmt": fmt, "m": m, "n": n, "k": k, "groups": g, "active_groups": act,
+            "us": t * 1e6, "GBps": bytes_ / t / 1e9,
             "TFLOPs": flops / t / 1e12, "roofline_us": roof * 1e6, "fraction": roof / t, "fraction_basis": tag}
 
 
@@ -206,6 +218,8 @@ def main():
     ap.add_argument("--op", required=True, choices=["gemm", "gemm-w4", "attention", "prefill", "decode-gemms"])
     ap.add_argument("--fmt", default="nvfp4", choices=["nvfp4", "mxfp4"])
     ap.add_argument("--groups", type=int, default=1)
+    ap.add_argument("--active", type=int, default=0, help="gemm-w4, grouped: groups that receive tokens (0 = all)")
+    ap.add_argument("--a4", action="store_true", help="gemm-w4: 4-bit activations on the block-scaled tensor-core kernel")
     ap.add_argument("--m", type=int, default=32)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -224,7 +238,7 @@ def main():
     if a.op == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.fp8, a.reps, a.graph)))
     elif a.op == "gemm-w4":
-        print(json.dumps(bench_gemm_w4(a.m, a.n, a.k, a.fmt, a.groups, a.reps, a.graph)))
+        print(json.dumps(bench_gemm_w4(a.m, a.n, a.k, a.fmt, a.groups, a.reps, a.graph, a.a4, a.active)))
     elif a.op == "attention":
         print(json.dumps(bench_attention(a.batch, a.ctx, a.hq, a.hkv, a.hd, a.fp8, a.reps, a.graph)))
     elif a.op == "prefill":

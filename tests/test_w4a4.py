@@ -1,0 +1,166 @@
+"""W4A4 path: 4-bit activations (NVFP4 / MXFP4) times 4-bit weights on the block-scaled tensor-core kinds.
+
+CPU: the activation quantiser's oracle, the native tile layout (swizzled code image + scale atoms) against the file
+layout, and the CPU form of the GEMM.  GPU: the quantiser kernel bit for bit against the oracle, structured probes that
+isolate each scale mapping (weight row, weight K block, token row, activation K block), and random dense / grouped /
+split-K cases against an fp32 evaluation of the same quantised operands.
+(Reference: native/hip/src/matmul_kernel.hip.cpp:343,396,457,562 - activation quantisers and W4A4 dots.)"""
+import numpy as np
+import pytest
+import torch
+
+from sllm_b200 import ops
+from sllm_b200.ops import reference as R
+from sllm_b200.ops.w4 import W4Weight, act_quant_fp4, linear_w4, linear_w4a4, sf_compact, sf_padded
+
+DEV = "cuda"
+
+
+def rel(a, b):
+    return ((a - b).norm() / (b.norm() + 1e-9)).item()
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_activation_quantiser_oracle(fmt):
+    torch.manual_seed(0)
+    x = (torch.randn(6, 200) * torch.logspace(-3, 2, 6).view(6, 1)).to(torch.bfloat16)
+    x[2] = 0
+    x[4, 7] = float("nan")
+    codes, sf, outer = R.quant_act_fp4(x, fmt)
+    block = 32 if fmt == "mxfp4" else 16
+    assert codes.shape == (6, 128) and sf.shape == (6, 256 // block) and outer.shape == (6,)
+    back = R.dequant_act_fp4(codes, sf, outer, fmt)
+    assert torch.equal(back[2], torch.zeros(256)) and torch.equal(back[:, 200:], torch.zeros(6, 56))
+    for r in (0, 1, 3, 5):                       # every magnitude range keeps the 4-bit relative error
+        assert rel(back[r, :200], x[r].float()) < 0.16
+    assert torch.isfinite(back).all()            # the NaN element became a zero code
+    if fmt == "nvfp4":
+        assert torch.allclose(outer[0], x[0].float().abs().max() / 2688.0) and outer[2] == 1.0
+    else:
+        assert torch.equal(outer, torch.ones(6))
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_native_tiles_hold_the_file_layout(fmt):
+    torch.manual_seed(1)
+    w = W4Weight.quantize(fmt, torch.randn(2, 130, 200) * 0.1)
+    nt = w.native_tiles()
+    g, rt, kb, width = nt.shape
+    atoms = 4 if fmt == "nvfp4" else 2
+    assert (g, rt, kb, width) == (2, 2, 1, 16384 + 512 * atoms) and w.native_tiles() is nt
+    img = nt[..., :16384].view(g, rt, kb, 128, 8, 16)
+    rr = (torch.arange(128) & 7).view(128, 1)
+    src = (torch.arange(8).view(1, 8) ^ rr).view(1, 1, 1, 128, 8, 1)
+    rows = torch.gather(img, 4, src.expand(g, rt, kb, 128, 8, 16)).reshape(g, rt, kb, 128, 128)
+    rows = rows.permute(0, 1, 3, 2, 4).reshape(g, rt * 128, kb * 128)
+    for gi in range(g):
+        packed, scales = w.to_file_layout(gi)
+        assert np.array_equal(rows[gi, :130, :100].numpy(), packed)
+        at = nt[gi, ..., 16384:].view(rt, kb, atoms, 32, 4, 4)                 # [atom][r][j][s]: scale s of row r + 32 j
+        sc = at.permute(0, 4, 3, 1, 2, 5).reshape(rt * 128, kb * atoms * 4)
+        assert np.array_equal(sc[:130, :scales.shape[1]].numpy(), scales)
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_cpu_form_tracks_the_w4a16_result(fmt):
+    torch.manual_seed(2)
+    w = W4Weight.quantize(fmt, torch.randn(96, 320) * 0.1)
+    x = torch.randn(5, 320).to(torch.bfloat16)
+    a16 = linear_w4(x, w).float()
+    a4 = linear_w4a4(x, w).float()
+    assert 0.02 < rel(a4, a16) < 0.16            # 4-bit activations cost about a tenth, and are not a no-op
+    q = act_quant_fp4(x, fmt)
+    assert torch.equal(sf_compact(q[1]), R.quant_act_fp4(x, fmt)[1]) and torch.equal(sf_padded(sf_compact(q[1])), q[1])
+    assert torch.equal(linear_w4a4(x, w, quantized=q), linear_w4a4(x, w))
+
+
+# ---------------------------------------------------------------------------------------------------- GPU
+def _oracle(q, w, t, tok_off=None, tok_scale=None, residual=None):
+    xf = R.dequant_act_fp4(q[0], sf_compact(q[1].cpu()), q[2], w.fmt)[:, :w.k]
+    out = torch.zeros((t, w.n))
+    offs = [0, t] if tok_off is None else tok_off.cpu().tolist()
+    for g in range(w.groups):
+        a, b = offs[g], offs[g + 1]
+        if b > a:
+            out[a:b] = xf[a:b] @ w.dequantized(g).t()
+    if tok_scale is not None:
+        out = out * tok_scale.cpu().float()[:, None]
+    if residual is not None:
+        out = out + residual.float().cpu()
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_quantiser_kernel_is_bit_exact(fmt):
+    torch.manual_seed(3)
+    x = (torch.randn(9, 2880) * torch.logspace(-2, 1, 9).view(9, 1)).to(torch.bfloat16)
+    x[3] = 0
+    def same(got, want):
+        assert torch.equal(got[0].cpu(), want[0]) and torch.equal(got[2].cpu(), want[2])
+        assert torch.equal(sf_compact(got[1].cpu()), want[1])          # four scale bytes, then four the kernel ignores
+
+    same(act_quant_fp4(x.to(DEV), fmt), R.quant_act_fp4(x, fmt))
+    # gathered rows: token t reads source row src_row[t]
+    src = torch.tensor([8, 0, 0, 5], dtype=torch.int32, device=DEV)
+    same(act_quant_fp4(x.to(DEV), fmt, src_row=src), R.quant_act_fp4(x[[8, 0, 0, 5]], fmt))
+    assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("kind", ["ones", "w_row", "w_k", "x_row", "x_k"])
+def test_scale_mappings_one_at_a_time(fmt, kind):
+    """All codes are 1.0; one family of scales varies, so a wrong lane, column or byte of the scale layout in tensor
+    memory changes the (exactly representable) result."""
+    block = 32 if fmt == "mxfp4" else 16
+    n, k, t = 128, 512, 32
+    sc = (lambda e: 127 + e) if fmt == "mxfp4" else (lambda e: 0x38 + 8 * e)
+    wp, ws = np.full((n, k // 2), 0x22, dtype=np.uint8), np.full((n, k // block), sc(0), dtype=np.uint8)
+    xp, xs = torch.full((t, k // 2), 0x22, dtype=torch.uint8), torch.full((t, k // block), sc(0), dtype=torch.uint8)
+    if kind == "w_row":
+        for m in range(n):
+            ws[m, :] = sc(m % 4)
+    elif kind == "w_k":
+        for b in range(k // block):
+            ws[:, b] = sc(b % 5)
+    elif kind == "x_row":
+        for m in range(t):
+            xs[m, :] = sc(m % 3)
+    elif kind == "x_k":
+        for b in range(k // block):
+            xs[:, b] = sc(b % 5)
+    w = W4Weight.from_file_layout(fmt, wp, ws, k, None, DEV)
+    q = (xp.to(DEV), sf_padded(xs).to(DEV), torch.ones(t, device=DEV))
+    y = linear_w4a4(None, w, quantized=q).float().cpu()
+    assert torch.equal(y, _oracle(q, w, t))
+    assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("t,n,k,groups,splits", [(1, 256, 512, 1, 0), (7, 300, 2880, 1, 0), (32, 1024, 4096, 1, 2),
+                                                  (32, 512, 8192, 1, 0), (100, 384, 1024, 1, 0), (40, 256, 2048, 8, 0),
+                                                  (130, 256, 1024, 3, 0)])
+def test_gemm_fp4_against_fp32_of_the_same_operands(fmt, t, n, k, groups, splits):
+    torch.manual_seed(t + n)
+    w = W4Weight.quantize(fmt, torch.randn(groups, n, k) * 0.1, DEV, keep_file=False)
+    x = torch.randn(t, k).to(torch.bfloat16).to(DEV)
+    tok_off = ts = mg = res = None
+    if groups > 1:
+        cuts = sorted(torch.randint(0, t + 1, (groups - 1,)).tolist())
+        offs = [0] + cuts + [t]
+        tok_off = torch.tensor(offs, dtype=torch.int32, device=DEV)
+        mg = max(b - a for a, b in zip(offs, offs[1:]))
+        ts = torch.rand(t, device=DEV)
+    else:
+        res = torch.randn(t, n).to(torch.bfloat16).to(DEV)
+    q = act_quant_fp4(x, fmt)
+    y = linear_w4a4(x, w, residual=res, tok_off=tok_off, tok_scale=ts, max_group_tokens=mg, splits=splits, quantized=q)
+    want = _oracle(q, w, t, tok_off, ts, res)
+    assert rel(y.float().cpu(), want) < 4e-3
+    # the whole path (quantise + multiply) stays within the 4-bit activation error of the bf16-activation kernel
+    if groups == 1:
+        a16 = linear_w4(x, w, residual=res).float().cpu()
+        assert rel(y.float().cpu(), a16) < 0.16
+    assert ops.device_status(torch.device(DEV)) == 0
