@@ -55,6 +55,9 @@ def parse_args():
     ap.add_argument("--no-replica-run", action="store_true",
                     help="N > 1, dense models under 16 GiB of weights: skip the second measurement of the same global batch "
                          "as one replica per GPU (reported under `replica_layout`)")
+    ap.add_argument("--act4", action="store_true",
+                    help="4-bit-weight models: quantise activations to the weights' 4-bit format and run the GEMMs on the "
+                         "block-scaled tensor-core kernel (W4A4) instead of W4A16")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: override the layer count")
     ap.add_argument("--no-batch1", action="store_true", help="skip the extra batch-1 measurement")
     return ap.parse_args()
@@ -329,6 +332,9 @@ def main():
     from sllm_b200.models import config as mc
     from sllm_b200.ops import _lib
 
+    if args.act4:
+        from sllm_b200.ops import w4 as _w4
+        _w4.set_w4a4(True)
     cfg = mc.NAMED[args.model]()
     if cfg.family != "moe":
         cfg.weight_format, cfg.kv_format = args.weights or "fp8", args.kv or "fp8"
@@ -474,7 +480,8 @@ def main():
                                        "MI300X); another model, batch and GPU, so context rather than a like-for-like ratio",
             "dtype": ("fp8_e4m3_block128_weights+fp8_kv (bf16 activations, fp32 accumulate)" if args.weights == "fp8" else
                       f"{args.weights} weights ({cfg.expert_format} experts) + {args.kv} kv, bf16 activations, fp32 accumulate"
-                      if cfg.family == "moe" else f"{args.weights} weights + {args.kv} kv, bf16 activations, fp32 accumulate"),
+                      if cfg.family == "moe" else f"{args.weights} weights + {args.kv} kv, bf16 activations, fp32 accumulate") +
+                     ("; 4-bit GEMMs take 4-bit block-scaled activations (W4A4)" if args.act4 else ""),
             "data": "synthetic: seeded uniform-random prompts, seeded N(0,0.02) random-init weights" +
                     ("; KV pages of the prompt marked computed without a prefill (decode-only measurement)"
                      if args.synthetic_kv else ""),

@@ -12,7 +12,12 @@
 //   warp 0      producer: per 256-element K block ONE bulk copy of the weight tile - the 128-byte-swizzled image of
 //               128 rows x 128 B of codes followed by its scale "atoms" - and one TMA box of the activations' codes
 //               (BN tokens x 128 B, 128-byte swizzle);
-//   warp 1      MMA issuer: tcgen05.cp of the block's scale atoms into TMEM, then four MMAs;
+//   warps 1-3, 8  MMA issuers (K blocks round robin, each into its own accumulator and its own scale columns):
+//               tcgen05.cp of the block's scale atoms into TMEM, then four MMAs.  One thread needs about 150 ns per
+//               tcgen05 instruction and a block-16 K block takes eleven of them: one issuer moves ~11 GB/s of weights, two
+//               ~22 GB/s, and an SM's share of the HBM bandwidth is ~44 GB/s (measured: 80 CTAs alone on their SMs
+//               streamed 22 GB/s each with two issuers).  tcgen05.cp and tcgen05.mma of one thread execute in issue
+//               order, so an issuer reuses its scale columns for its next K block without a barrier;
 //   warps 4..7  (tiles of more than 32 tokens only: first stage the activations' scales of the CTA's K range into
 //               shared memory in atom order), then the epilogue: TMEM -> registers, times weight-tensor scale x activation-row scale (x routing weight),
 //               (+ residual), bf16 store Y[token, row]; split-K partials go through an fp32 workspace.
@@ -44,8 +49,9 @@ constexpr int kF4ABytes = kF4Rows * 128;        // 16 KB of codes per weight til
 constexpr int kF4AtomBytes = 512;
 constexpr int kF4MaxAtoms = 4;                  // scale atoms per K block: 4 (block 16) or 2 (block 32)
 constexpr int kF4MaxKb = 8;                     // K blocks per CTA; split-K keeps a CTA's share within it
-constexpr int kF4Threads = 256;
-constexpr int kF4MaxStages = 6;
+constexpr int kF4Threads = 288;                 // warp 0 producer, warps 1-3 and 8 issuers, warps 4-7 epilogue
+constexpr int kF4MaxStages = 8;
+__host__ __device__ constexpr int f4_issuers(int bn) { return bn <= 64 ? 4 : 2; }   // bounded by the 512 TMEM columns
 
 struct F4Params {
   int n_rows, n_valid, k_blocks, groups;
@@ -137,9 +143,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   constexpr int kStageBytes = kOffSfb + kSfbStage;
   static_assert(kStageBytes % 1024 == 0, "stage alignment");
   constexpr int kSfbBytes = kTmaSfb ? 0 : kF4MaxKb * kAtoms * kF4AtomBytes;
-  // TMEM: accumulator, then two buffers of (weight scales | activation scales), four columns per atom
+  // TMEM: one accumulator per issuer, then per issuer (weight scales | activation scales), four columns per atom
+  constexpr int kIss = f4_issuers(BN);
   constexpr uint32_t kSfCols = 4 * kAtoms;
-  constexpr uint32_t kNeed = BN + 4 * kSfCols;
+  constexpr uint32_t kNeed = kIss * (BN + 2 * kSfCols);
   constexpr uint32_t kTmemCols = kNeed <= 32 ? 32 : kNeed <= 64 ? 64 : kNeed <= 128 ? 128 : kNeed <= 256 ? 256 : 512;
   uint8_t* sfb_region = smem;
   uint8_t* stages = smem + ((kSfbBytes + 1023) & ~1023);
@@ -164,7 +171,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       mbar_init(&bars->empty[s], 1);
     }
     mbar_init(&bars->sfb_ready, 128);
-    mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->acc_full, kIss);
     bars->abort_flag = 0;
     bars->is_last = 0;
     mbar_fence_init();
@@ -226,19 +233,23 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+  } else if (warp < 4 || warp == 8) {
+    // ------------------------------------------------------------ MMA issuers
+    // (the number of stages is a multiple of the number of issuers, so a stage always carries K blocks of one issuer:
+    // a parity wait is only sound for a waiter that has itself seen the barrier's previous phase complete)
+    const int iw = warp < 4 ? warp - 1 : 3;
+    if (lane == 0 && iw < kIss) {
       constexpr uint32_t idesc = make_idesc_f4(BN, kBlock == 32 ? 1u : 0u);
-      bool ok = nk > 0 && (kTmaSfb || mbar_wait(&bars->sfb_ready, 0, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL));
-      for (int i = 0; ok && i < nk; ++i) {
+      const uint32_t d_tmem = tmem_base + iw * BN;
+      const uint32_t sfa_t = tmem_base + kIss * BN + iw * 2 * kSfCols;
+      const uint32_t sfb_t = sfa_t + kSfCols;
+      bool ok = kTmaSfb || nk <= iw || mbar_wait(&bars->sfb_ready, 0, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL);
+      for (int i = iw; ok && i < nk; i += kIss) {
         const int s = i % p.stages;
         ok = mbar_wait(&bars->full[s], (i / p.stages) & 1, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMA_FULL);
         if (!ok) break;
         tc_fence_after();
         const uint32_t st = smem_u32(stages + s * kStageBytes);
-        const uint32_t sfa_t = tmem_base + BN + (i & 1) * 2 * kSfCols;
-        const uint32_t sfb_t = sfa_t + kSfCols;
 #pragma unroll
         for (int a = 0; a < kAtoms; ++a) {
           tmem_cp_atom(sfa_t + 4 * a, make_smem_desc_atom(st + kF4ABytes + a * kF4AtomBytes));
@@ -260,11 +271,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
           // decode tiles: the four scale bytes MMA j starts in are the j-th (block 32: (j / 2)-th) 8-byte unit of the
           // token's K block, i.e. column 2 j (2 (j / 2)) of its boxes - always an even column
           const uint32_t colb = kTmaSfb ? (kBlock == 16 ? 2u * j : 2u * (j >> 1)) : col;
-          umma_f4<kBlock>(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc | (id << 29) | (id << 4),
-                          (sfa_t + col) | (id << 30), (sfb_t + colb) | (id << 30), (i > 0) || (j > 0));
+          umma_f4<kBlock>(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc | (id << 29) | (id << 4),
+                          (sfa_t + col) | (id << 30), (sfb_t + colb) | (id << 30), (i > iw) || (j > 0));
         }
         tc_commit(&bars->empty[s]);
       }
+      // an issuer without K blocks has nothing in flight: its commit arrives at once
       if (ok) tc_commit(&bars->acc_full);
     }
   } else if (warp >= 4) {
@@ -313,11 +325,15 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 #pragma unroll
       for (int j = 0; j < 16; ++j) v[j] = 0.f;
       if (ok && nk > 0) {
-        uint32_t t[16];
-        tmem_ld16(lane_addr + cb * 16, t);
-        tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(t[j]);
+        for (int a = 0; a < kIss; ++a) {
+          if (a >= nk) continue;                 // that issuer had no K block: its accumulator was never written
+          uint32_t t[16];
+          tmem_ld16(lane_addr + a * BN + cb * 16, t);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] += __uint_as_float(t[j]);
+        }
       }
       if (row_ok) {
 #pragma unroll
@@ -383,6 +399,7 @@ static int launch_f4(const CUtensorMap& tx, const CUtensorMap& tsf, F4Params& p,
   const int budget = BN <= 32 ? 113 * 1024 : 227 * 1024;
   int stages = (budget - fixed) / kStageBytes;
   if (stages > kF4MaxStages) stages = kF4MaxStages;
+  stages -= stages % f4_issuers(BN);             // a stage stays with one issuer
   if (stages < 2) return SLLM_ERR_UNSUPPORTED_SHAPE;
   p.stages = stages;
   const size_t smem = static_cast<size_t>(fixed) + static_cast<size_t>(stages) * kStageBytes;
@@ -403,24 +420,52 @@ static int launch_f4(const CUtensorMap& tx, const CUtensorMap& tsf, F4Params& p,
 // (block amax / 6) / row scale; fmt 0 (MXFP4): block scale UE8M0 with the same exponent rule as the weight
 // quantiser, row scale 1.  (Reference: native/hip/src/matmul_kernel.hip.cpp:343,457 - a calibrated global scale
 // there, the row's own maximum here.)
+__device__ __forceinline__ float f4_silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float f4_gelu_tanh(float x) {
+  const float c = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tanhf(c * (x + 0.044715f * x * x * x)));
+}
+
+// Eight consecutive values of the row to quantise.  gated (1 SiLU, 2 GELU-tanh): the row is [gate (k) | up (k)] and the
+// value is act(gate) * up with the bf16 roundings of the stand-alone gated-activation kernel (elementwise.cu).
+__device__ __forceinline__ void f4_load8(const __nv_bfloat16* row, int i, int k, int gated, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+  const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+  if (!gated) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(h[j]);
+  } else {
+    const uint4 rawu = *reinterpret_cast<const uint4*>(row + k + i);
+    const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&rawu);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g = __bfloat162float(h[j]);
+      const float a = gated == 1 ? f4_silu(g) : f4_gelu_tanh(g);
+      v[j] = __bfloat162float(__float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(a)) * __bfloat162float(u[j])));
+    }
+  }
+}
+
 template <int kBlock>
 __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int k, int k_pad,
-                                                            const int* __restrict__ src_row, uint8_t* __restrict__ xq,
-                                                            uint8_t* __restrict__ xsf, int sf_ld, float* __restrict__ outer) {
+                                                            const int* __restrict__ src_row, const int* __restrict__ n_rows_ptr,
+                                                            int gated, uint8_t* __restrict__ xq, uint8_t* __restrict__ xsf,
+                                                            int sf_ld, float* __restrict__ outer) {
   __shared__ float red[8];
   pdl_wait();
   const int t = blockIdx.x;
+  if (n_rows_ptr && t >= *n_rows_ptr) return;        // rows past the routed ones: their source index is not defined
   const __nv_bfloat16* row = x + static_cast<size_t>(src_row ? src_row[t] : t) * ldx;
   float outer_s = 1.f;
   if (kBlock == 16) {
     float amax = 0.f;
     for (int i = threadIdx.x * 8; i < k; i += 256 * 8) {
-      const uint4 v = *reinterpret_cast<const uint4*>(row + i);
-      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&v);
+      float v[8];
+      f4_load8(row, i, k, gated, v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float a = fabsf(__bfloat162float(h[j]));
-        if (i + j < k && a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
+        const float a = fabsf(v[j]);
+        if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
       }
     }
     amax = warp_max(amax);
@@ -431,7 +476,7 @@ __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16*
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
     outer_s = amax > 0.f ? __fdiv_rn(amax, 2688.f) : 1.f;
     if (threadIdx.x == 0) outer[t] = outer_s;
-  } else if (threadIdx.x == 0 && outer) {
+  } else if (threadIdx.x == 0) {
     outer[t] = 1.f;
   }
   pdl_trigger();
@@ -442,14 +487,12 @@ __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16*
 #pragma unroll
     for (int c = 0; c < kBlock / 8; ++c) {
       const int i = b * kBlock + c * 8;
-      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-      if (i < k) raw = *reinterpret_cast<const uint4*>(row + i);       // k is a multiple of 8
-      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (i < k) f4_load8(row, i, k, gated, f);                          // k is a multiple of 8
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float f = __bfloat162float(h[j]);
-        v[c * 8 + j] = f;
-        const float a = fabsf(f);
+        v[c * 8 + j] = f[j];
+        const float a = fabsf(f[j]);
         if (a == a && a <= 3.0e38f) bamax = fmaxf(bamax, a);
       }
     }
@@ -489,22 +532,25 @@ __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16*
 using namespace sllm;
 
 // x: bf16 [rows of the source, k] (row stride ldx elements, k a multiple of 8); token t reads source row src_row[t]
-// (or t when src_row is null: gathering the rows of a routed batch costs nothing extra).  xq: [tokens, k_pad / 2];
-// xsf: [tokens, sf_ld] with sf_ld >= 2 k_pad / block (8 bytes per four scales), a multiple of 16; outer: [tokens] fp32.  fmt 0 = MXFP4 (block 32), 1 = NVFP4 (16).
-SLLM_EXPORT int sllm_act_quant_fp4(const void* x, int ldx, int tokens, int k, int k_pad, const int* src_row, int fmt,
-                                   void* xq, void* xsf, int sf_ld, float* outer, void* stream) {
+// (or t when src_row is null: gathering the rows of a routed batch costs nothing extra); with n_rows_ptr (device int)
+// tokens >= *n_rows_ptr are skipped.  gated (0 none, 1 SiLU, 2 GELU-tanh): x rows are [gate (k) | up (k)] and the
+// quantised value is act(gate) * up.  xq: [tokens, k_pad / 2]; xsf: [tokens, sf_ld] with sf_ld >= 2 k_pad / block
+// (8 bytes per four scales), a multiple of 16; outer: [tokens] fp32.  fmt 0 = MXFP4 (block 32), 1 = NVFP4 (16).
+SLLM_EXPORT int sllm_act_quant_fp4(const void* x, int ldx, int tokens, int k, int k_pad, const int* src_row,
+                                   const int* n_rows_ptr, int gated, int fmt, void* xq, void* xsf, int sf_ld, float* outer,
+                                   void* stream) {
   if (!x || !xq || !xsf || !outer || tokens <= 0 || k <= 0 || (k % 8) || k_pad < k || (k_pad % kF4KBlock) || (ldx % 8) ||
-      (fmt != 0 && fmt != 1))
+      (fmt != 0 && fmt != 1) || gated < 0 || gated > 2 || ldx < (gated ? 2 * k : k))
     return SLLM_ERR_INVALID_ARGUMENT;
   if (sf_ld < 2 * k_pad / (fmt ? 16 : 32) || (sf_ld % 16)) return SLLM_ERR_INVALID_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (fmt)
     e = launch_kernel(act_quant_fp4_kernel<16>, dim3(tokens), dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
-                      k, k_pad, src_row, static_cast<uint8_t*>(xq), static_cast<uint8_t*>(xsf), sf_ld, outer);
+                      k, k_pad, src_row, n_rows_ptr, gated, static_cast<uint8_t*>(xq), static_cast<uint8_t*>(xsf), sf_ld, outer);
   else
     e = launch_kernel(act_quant_fp4_kernel<32>, dim3(tokens), dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
-                      k, k_pad, src_row, static_cast<uint8_t*>(xq), static_cast<uint8_t*>(xsf), sf_ld, outer);
+                      k, k_pad, src_row, n_rows_ptr, gated, static_cast<uint8_t*>(xq), static_cast<uint8_t*>(xsf), sf_ld, outer);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 

@@ -127,15 +127,39 @@ def shared_add(a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor) -> torch.Te
     return y
 
 
+def expert_mlp(x: torch.Tensor, tok_off: torch.Tensor, perm_src: torch.Tensor, perm_w: torch.Tensor, gate_up: W4Weight,
+               down: W4Weight, act: str, row_ptr: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The gated MLP of the local experts over the routed rows (grouped by expert: `tok_off`), routing weights applied:
+    y_perm [T*k, d], or None when `row_ptr` scatters the rows (see `linear_w4`).
+
+    W4A16 (default): gather rows -> grouped gate_up GEMM -> SiLU*up -> grouped down GEMM, bf16 activations.
+    W4A4 (`ops.w4.set_w4a4`): the quantiser reads the routed rows in place (no gather), both GEMMs run on the
+    block-scaled 4-bit tensor-core kernel, and SiLU*up is computed inside the quantiser of the down projection
+    (reference: the fused expert kernels, native/hip/src/moe_expert_kernel.hip.cpp:88,176)."""
+    from . import core
+    from . import w4 as W
+    t = x.shape[0]
+    if W.w4a4_enabled() and x.dtype == torch.bfloat16:
+        rows = perm_src.numel()
+        n_rows = tok_off[-1:] if x.is_cuda else None
+        if not x.is_cuda:
+            rows = int(tok_off[-1])
+        q = W.act_quant_fp4(x, gate_up.fmt, src_row=perm_src, tokens=rows, n_rows=n_rows)
+        gu = W.linear_w4a4(None, gate_up, tok_off=tok_off, max_group_tokens=t, quantized=q)
+        q2 = W.act_quant_fp4(gu, down.fmt, n_rows=n_rows, gated=act)
+        y = W.linear_w4a4(None, down, tok_off=tok_off, tok_scale=perm_w[:rows], max_group_tokens=t, quantized=q2,
+                          row_ptr=row_ptr)
+        if y is not None and y.shape[0] < perm_src.numel():
+            y = torch.cat([y, y.new_zeros((perm_src.numel() - y.shape[0], y.shape[1]))])
+        return y
+    xp = gather(x, perm_src, tok_off)
+    a = core.gated_act(linear_w4(xp, gate_up, tok_off=tok_off, max_group_tokens=t), act)
+    return linear_w4(a, down, tok_off=tok_off, tok_scale=perm_w, max_group_tokens=t, row_ptr=row_ptr)
+
+
 def experts_forward(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, gate_up: W4Weight, down: W4Weight, act: str,
                     e_lo: int, e_hi: int):
     """Runs the local experts [e_lo, e_hi) on the tokens routed to them.  Returns (y_perm [T*k, d] with the routing
     weights applied, perm_dst [T, k])."""
-    from . import core
     tok_off, perm_src, perm_dst, perm_w = permute(idx, w, e_lo, e_hi)
-    xp = gather(x, perm_src, tok_off)
-    t = x.shape[0]
-    gu = linear_w4(xp, gate_up, tok_off=tok_off, max_group_tokens=t)
-    a = core.gated_act(gu, act)
-    yp = linear_w4(a, down, tok_off=tok_off, tok_scale=perm_w, max_group_tokens=t)
-    return yp, perm_dst
+    return expert_mlp(x, tok_off, perm_src, perm_w, gate_up, down, act), perm_dst

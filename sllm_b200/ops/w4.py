@@ -248,6 +248,8 @@ def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = N
         if residual is not None:
             out = out + residual.float()
         return out if x.dtype == torch.float32 else out.to(torch.bfloat16)
+    if w4a4_enabled() and x.dtype == torch.bfloat16 and k % 8 == 0:
+        return linear_w4a4(x, w, residual, tok_off, tok_scale, max_group_tokens, 0, row_ptr)
     from .core import _p, _stream, workspace
     P, I, L, F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
     _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_gemm_w4", (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I,
@@ -305,30 +307,37 @@ def set_w4a4(on: bool) -> None:
     _W4A4["on"] = bool(on)
 
 
-def act_quant_fp4(x: torch.Tensor, fmt: str, src_row: Optional[torch.Tensor] = None, tokens: Optional[int] = None):
+def act_quant_fp4(x: torch.Tensor, fmt: str, src_row: Optional[torch.Tensor] = None, tokens: Optional[int] = None,
+                  n_rows: Optional[torch.Tensor] = None, gated: Optional[str] = None):
     """bf16 [T, K] -> (codes uint8 [T, K_pad / 2], block scales uint8 [T, 2 K_pad / block], row scales fp32 [T]) with K
     padded to 256.  The scale matrix is the kernel's operand: four scale bytes, then four unused ones (`sf_compact`
-    drops them).  nvfp4: row scale amax / 2688, UE4M3 block scales; mxfp4: UE8M0 block scales, row scale 1.  With
-    `src_row` (int32 [T]) token t reads row src_row[t] of x."""
+    drops them).  nvfp4: row scale amax / 2688, UE4M3 block scales; mxfp4: UE8M0 block scales, row scale 1.
+    `src_row` (int32 [T]): token t reads row src_row[t] of x; `n_rows` (int32 device scalar): tokens from *n_rows on are
+    skipped (their outputs stay undefined); `gated` ("silu" | "gelu_tanh"): x is [T, 2 K] = [gate | up] and
+    act(gate) * up is what gets quantised."""
     from . import reference
     t = tokens if tokens is not None else (x.shape[0] if src_row is None else src_row.numel())
-    k = x.shape[1]
+    k = x.shape[1] // 2 if gated else x.shape[1]
     block = 32 if fmt == "mxfp4" else 16
     k_pad = (k + 255) // 256 * 256
     if _lib.on_cpu(x):
-        xs = x if src_row is None else x.index_select(0, src_row.long()[:t])
-        codes, sf, outer = reference.quant_act_fp4(xs[:t], fmt)
+        xs = x if src_row is None else x.index_select(0, src_row.long()[:t].clamp(0, x.shape[0] - 1))
+        xs = xs[:t]
+        if gated:
+            xs = reference.round_bf16(reference.gated_act(xs, gated))
+        codes, sf, outer = reference.quant_act_fp4(xs, fmt)
         return codes, sf_padded(sf), outer
     from .core import _p, _stream
     P, I = C.c_void_p, C.c_int
-    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_act_quant_fp4", (I, [P, I, I, I, I, P, I, P, P, I, P, P]))
+    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_act_quant_fp4", (I, [P, I, I, I, I, P, P, I, I, P, P, I, P, P]))
     if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or k % 8:
         raise ValueError("act_quant_fp4: bf16 rows with a stride and width that are multiples of 8")
     xq = torch.empty((t, k_pad // 2), dtype=torch.uint8, device=x.device)
     xsf = torch.empty((t, 2 * k_pad // block), dtype=torch.uint8, device=x.device)      # a multiple of 16 bytes
     outer = torch.empty((t,), dtype=torch.float32, device=x.device)
-    rc = _lib.kernels().sllm_act_quant_fp4(_p(x), x.stride(0), t, k, k_pad, _p(src_row), 0 if fmt == "mxfp4" else 1, _p(xq),
-                                           _p(xsf), xsf.stride(0), _p(outer), _stream())
+    g = 0 if not gated else 1 if gated == "silu" else 2
+    rc = _lib.kernels().sllm_act_quant_fp4(_p(x), x.stride(0), t, k, k_pad, _p(src_row), _p(n_rows), g,
+                                           0 if fmt == "mxfp4" else 1, _p(xq), _p(xsf), xsf.stride(0), _p(outer), _stream())
     _lib.check(rc, "act_quant_fp4")
     return xq, xsf, outer
 

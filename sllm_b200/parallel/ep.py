@@ -119,8 +119,6 @@ class FusedEP(NcclEP):
         lib = M._k()
         P, I, L = C.c_void_p, C.c_int, C.c_longlong
         tok_off, perm_src, perm_dst, perm_w = M.permute(idx, rw, e_lo, e_hi)
-        xp = M.gather(x, perm_src, tok_off)
-        a = core.gated_act(linear_w4(xp, gate_up, tok_off=tok_off, max_group_tokens=t), act)
         tpr = (t + self.size - 1) // self.size
         row_ptr = torch.empty(t * k, dtype=torch.int64, device=x.device)
         peers = (C.cast(self._oslots, P), C.cast(self._ogath, P), C.cast(self._oflags, P), self.size, self.rank,
@@ -128,7 +126,7 @@ class FusedEP(NcclEP):
         rc = lib.sllm_moe_owner_plan(*peers, _p(perm_dst), t, k, self.d, tpr, _p(self.owner_epoch), _p(row_ptr), _stream())
         _lib.check(rc, "moe_owner_plan")
         # the down projection stores every routed row (route weight applied) into its owner's slot, on whatever GPU
-        linear_w4(a, down, tok_off=tok_off, tok_scale=perm_w, max_group_tokens=t, row_ptr=row_ptr)
+        M.expert_mlp(x, tok_off, perm_src, perm_w, gate_up, down, act, row_ptr=row_ptr)
         y = torch.empty((t, self.d), dtype=torch.bfloat16, device=x.device)
         rc = lib.sllm_moe_owner_combine(*peers, k, _p(residual), _p(y), t, self.d, tpr, self.rows_per_block,
                                         _p(self.owner_epoch), _p(self.owner_counter), _p(workspace(x.device).status), _stream())

@@ -117,7 +117,7 @@ def bench_gemm(m, n, k, fp8, reps, graph=False):
             "TFLOPs": flops / t / 1e12, "roofline_us": roof * 1e6, "fraction": roof / t, "fraction_basis": tag}
 
 
-def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False, a4=False, active=0):
+def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False, a4=False, active=0, splits=0):
     """Dense (groups = 1) or grouped 4-bit-weight GEMM; grouped: m tokens spread evenly over the first `active` groups
     (all of them when 0).  a4: activations quantised to the weights' format and the block-scaled tensor-core kernel
     (the quantiser's launch is inside the timed call); otherwise the W4A16 kernel."""
@@ -141,10 +141,10 @@ def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False, a4=False, active=0):
         mgt = max(per)
     if a4:
         w.native_tiles()
-        call = lambda w_: linear_w4a4(x, w_, tok_off=off, max_group_tokens=mgt)
+        call = lambda w_: linear_w4a4(x, w_, tok_off=off, max_group_tokens=mgt, splits=splits)
         wbytes = w.native.numel() * act // g
     else:
-        call = lambda w_: linear_w4(x, w_, tok_off=off, max_group_tokens=mgt)
+        call = lambda w_: linear_w4(x, w_, tok_off=off, max_group_tokens=mgt, splits=splits)
         wbytes = w.tiles.numel() * act // g
     if graph:
         ws = [w] + [W4Weight(w.fmt, w.groups, w.n, w.k, w.n_rows, w.k_pad, w.tiles if a4 else w.tiles.clone(), w.tensor_scale,
@@ -158,7 +158,7 @@ def bench_gemm_w4(m, n, k, fmt, groups, reps, graph=False, a4=False, active=0):
     flops = 2.0 * m * n * k
     roof = max(bytes_ / bw, flops / fl)
     return {"op": "gemm_w4a4" if a4 else "gemm_w4", "fmt": fmt, "m": m, "n": n, "k": k, "groups": g, "active_groups": act,
-            "us": t * 1e6, "GBps": bytes_ / t / 1e9,
+            "splits": splits, "us": t * 1e6, "GBps": bytes_ / t / 1e9,
             "TFLOPs": flops / t / 1e12, "roofline_us": roof * 1e6, "fraction": roof / t, "fraction_basis": tag}
 
 
@@ -219,6 +219,7 @@ def main():
     ap.add_argument("--fmt", default="nvfp4", choices=["nvfp4", "mxfp4"])
     ap.add_argument("--groups", type=int, default=1)
     ap.add_argument("--active", type=int, default=0, help="gemm-w4, grouped: groups that receive tokens (0 = all)")
+    ap.add_argument("--splits", type=int, default=0, help="gemm-w4: K splits (0 = the wrapper's choice)")
     ap.add_argument("--a4", action="store_true", help="gemm-w4: 4-bit activations on the block-scaled tensor-core kernel")
     ap.add_argument("--m", type=int, default=32)
     ap.add_argument("--n", type=int, default=4096)
@@ -238,7 +239,7 @@ def main():
     if a.op == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.fp8, a.reps, a.graph)))
     elif a.op == "gemm-w4":
-        print(json.dumps(bench_gemm_w4(a.m, a.n, a.k, a.fmt, a.groups, a.reps, a.graph, a.a4, a.active)))
+        print(json.dumps(bench_gemm_w4(a.m, a.n, a.k, a.fmt, a.groups, a.reps, a.graph, a.a4, a.active, a.splits)))
     elif a.op == "attention":
         print(json.dumps(bench_attention(a.batch, a.ctx, a.hq, a.hkv, a.hd, a.fp8, a.reps, a.graph)))
     elif a.op == "prefill":

@@ -164,3 +164,61 @@ def test_gemm_fp4_against_fp32_of_the_same_operands(fmt, t, n, k, groups, splits
         a16 = linear_w4(x, w, residual=res).float().cpu()
         assert rel(y.float().cpu(), a16) < 0.16
     assert ops.device_status(torch.device(DEV)) == 0
+
+
+def test_expert_mlp_with_4bit_activations_cpu():
+    """The routed expert MLP in its W4A4 form (quantiser reads the routed rows, SiLU*up inside the second quantiser)
+    tracks the bf16-activation form within the 4-bit error, and the switch really changes the path."""
+    from sllm_b200.ops import moe as M
+    from sllm_b200.ops import w4 as W
+    torch.manual_seed(5)
+    E, d, F, t, k = 8, 256, 128, 6, 2
+    gate_up = W4Weight.quantize("mxfp4", torch.randn(E, 2 * F, d) * 0.1)
+    down = W4Weight.quantize("mxfp4", torch.randn(E, d, F) * 0.1)
+    x = torch.randn(t, d).to(torch.bfloat16)
+    idx, rw = M.route(torch.randn(t, E), k)
+    base, perm = M.experts_forward(x, idx, rw, gate_up, down, "silu", 0, E)
+    W.set_w4a4(True)
+    try:
+        a4, perm4 = M.experts_forward(x, idx, rw, gate_up, down, "silu", 0, E)
+    finally:
+        W.set_w4a4(False)
+    assert torch.equal(perm, perm4) and a4.shape == base.shape
+    assert 0.02 < rel(a4.float(), base.float()) < 0.25
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_gated_quantiser_and_expert_mlp_gpu(fmt):
+    from sllm_b200.ops import moe as M
+    from sllm_b200.ops import w4 as W
+    torch.manual_seed(6)
+    # SiLU*up inside the quantiser: within the 4-bit step of quantising the stand-alone kernel's output
+    gu = torch.randn(5, 2 * 384).to(torch.bfloat16)
+    q = act_quant_fp4(gu.to(DEV), fmt, gated="silu")
+    want = R.round_bf16(R.gated_act(gu, "silu"))
+    got = R.dequant_act_fp4(q[0], sf_compact(q[1].cpu()), q[2], fmt)[:, :384]
+    assert rel(got, want) < 0.16
+    ref = R.dequant_act_fp4(*[a if i != 1 else a for i, a in enumerate(R.quant_act_fp4(want, fmt))], fmt)[:, :384]
+    assert rel(got, ref) < 0.03                       # the same quantiser up to the device's exp()
+    # the routed expert MLP, GPU against the CPU form of the same W4A4 arithmetic
+    E, d, F, t, k = 8, 256, 256, 40, 2
+    wgu, wdn = torch.randn(E, 2 * F, d) * 0.1, torch.randn(E, d, F) * 0.1
+    x = torch.randn(t, d).to(torch.bfloat16)
+    idx, rw = M.route(torch.randn(t, E), k)
+    W.set_w4a4(True)
+    try:
+        want, _ = M.experts_forward(x, idx, rw, W4Weight.quantize(fmt, wgu), W4Weight.quantize(fmt, wdn), "silu", 0, E)
+        got, _ = M.experts_forward(x.to(DEV), idx.to(DEV), rw.to(DEV), W4Weight.quantize(fmt, wgu, DEV, keep_file=False),
+                                   W4Weight.quantize(fmt, wdn, DEV, keep_file=False), "silu", 0, E)
+        # a scatter-free combine of both gives the layer output; rows past the routed ones are not compared
+        n = t * k
+        assert rel(got[:n].float().cpu(), want[:n].float()) < 0.05
+        # dense form through the switch
+        w = W4Weight.quantize(fmt, torch.randn(192, d) * 0.1, DEV, keep_file=False)
+        y4 = linear_w4(x.to(DEV), w)
+    finally:
+        W.set_w4a4(False)
+    y16 = linear_w4(x.to(DEV), w)
+    assert 0.02 < rel(y4.float(), y16.float()) < 0.16
+    assert ops.device_status(torch.device(DEV)) == 0
