@@ -14,10 +14,9 @@
 //               (BN tokens x 128 B, 128-byte swizzle);
 //   warps 1-3, 8  MMA issuers (K blocks round robin, each into its own accumulator and its own scale columns):
 //               tcgen05.cp of the block's scale atoms into TMEM, then four MMAs.  One thread needs about 150 ns per
-//               tcgen05 instruction and a block-16 K block takes eleven of them: one issuer moves ~11 GB/s of weights, two
-//               ~22 GB/s, and an SM's share of the HBM bandwidth is ~44 GB/s (measured: 80 CTAs alone on their SMs
-//               streamed 22 GB/s each with two issuers).  tcgen05.cp and tcgen05.mma of one thread execute in issue
-//               order, so an issuer reuses its scale columns for its next K block without a barrier;
+//               tcgen05 instruction and a block-16 K block takes eleven of them, so the issue work is spread over four
+//               threads.  tcgen05.cp and tcgen05.mma of one thread execute in issue order, so an issuer reuses its scale
+//               columns for its next K block without a barrier;
 //   warps 4..7  (tiles of more than 32 tokens only: first stage the activations' scales of the CTA's K range into
 //               shared memory in atom order), then the epilogue: TMEM -> registers, times weight-tensor scale x activation-row scale (x routing weight),
 //               (+ residual), bf16 store Y[token, row]; split-K partials go through an fp32 workspace.
@@ -395,8 +394,18 @@ static int launch_f4(const CUtensorMap& tx, const CUtensorMap& tsf, F4Params& p,
   constexpr int kStageBytes = kF4ABytes + kF4MaxAtoms * kF4AtomBytes + BN * 128 + (BN <= 32 ? 1024 : 0);
   constexpr int kSfb = BN <= 32 ? 0 : ((kF4MaxKb * kAtoms * kF4AtomBytes + 1023) & ~1023);
   const int fixed = kSfb + static_cast<int>(sizeof(F4Barriers)) + 1024;
-  // two CTAs per SM at the decode tile sizes: their pipelines fill each other's bubbles
-  const int budget = BN <= 32 ? 113 * 1024 : 227 * 1024;
+  // An SM's share of the HBM bandwidth (~44 GB/s) needs ~190 KB of copies in flight at the loaded memory latency:
+  // two CTAs per SM with four stages each at the decode tile sizes, or, when the launch has no more CTAs than the
+  // device has SMs, one CTA with eight stages (a four-stage CTA alone on its SM streamed 22 GB/s, an eight-stage
+  // one 40 GB/s).
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      sms = 148;
+  }
+  const long long ctas = static_cast<long long>(grid.x) * grid.y * grid.z;
+  const int budget = (BN <= 32 && ctas > sms) ? 113 * 1024 : 227 * 1024;
   int stages = (budget - fixed) / kStageBytes;
   if (stages > kF4MaxStages) stages = kF4MaxStages;
   stages -= stages % f4_issuers(BN);             // a stage stays with one issuer

@@ -394,8 +394,13 @@ def linear_w4a4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] =
     if splits <= 0:
         ctas = (w.n_rows // 128) * (w.groups if tok_off is None else max(1, min(w.groups, t))) * ((min(mgt, t) + bn - 1) // bn)
         splits = min_splits
-        while ctas * splits < 296 and splits * 2 <= max(1, kb // 2) and splits < 16:
-            splits *= 2
+        if bn > 32:
+            while ctas * splits < 148 and splits * 2 <= max(1, kb // 2) and splits < 16:
+                splits *= 2
+        elif ctas < 100 and kb >= 64:
+            # decode tiles: a K split costs more than it balances (measured: one split wins down to 80 row tiles);
+            # only a long K over few row tiles is worth two
+            splits = 2
     splits = max(splits, min_splits)
     wsp = workspace(xq.device)
     if _lib.audit_enabled():

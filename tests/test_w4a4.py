@@ -141,7 +141,10 @@ def test_scale_mappings_one_at_a_time(fmt, kind):
 @pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
 @pytest.mark.parametrize("t,n,k,groups,splits", [(1, 256, 512, 1, 0), (7, 300, 2880, 1, 0), (32, 1024, 4096, 1, 2),
                                                   (32, 512, 8192, 1, 0), (100, 384, 1024, 1, 0), (40, 256, 2048, 8, 0),
-                                                  (130, 256, 1024, 3, 0)])
+                                                  (130, 256, 1024, 3, 0),
+                                                  # dense decode schedule: runs of K blocks that cross row tiles unevenly
+                                                  (3, 640, 3328, 1, 0), (32, 2944, 4096, 1, 0), (16, 8192, 8192, 1, 0),
+                                                  (16, 8192, 8192, 1, 1)])
 def test_gemm_fp4_against_fp32_of_the_same_operands(fmt, t, n, k, groups, splits):
     torch.manual_seed(t + n)
     w = W4Weight.quantize(fmt, torch.randn(groups, n, k) * 0.1, DEV, keep_file=False)
