@@ -20,6 +20,7 @@ import torch
 
 from .. import ops
 from ..engine.batch import ForwardBatch
+from ..ops import w4 as _w4
 from ..ops.core import LinearWeight, QTensor
 from .config import ModelConfig
 
@@ -250,7 +251,12 @@ class LlamaModel:
                 h = self.tp.row_linear(a, lw.o, h)
             x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one, quant=q_mlp)
             gu = ops.linear(x, lw.gate_up)
-            act = ops.gated_act(gu, cfg.act, quant=q_down)
+            if lw.down.kind == "w4" and _w4.w4a4_enabled() and gu.dtype == torch.bfloat16:
+                # 4-bit activations: SiLU*up runs inside the quantiser of the down projection
+                wd = lw.down.w4
+                act = _w4.Fp4Act(*_w4.act_quant_fp4(gu, wd.fmt, gated=cfg.act), k=gu.shape[1] // 2, fmt=wd.fmt)
+            else:
+                act = ops.gated_act(gu, cfg.act, quant=q_down)
             if cfg.post_norms:
                 o = ops.rmsnorm(self.tp.row_linear(act, lw.down, None), lw.post_mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
                 h = ops.elementwise("add", h, o)

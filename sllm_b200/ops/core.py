@@ -161,7 +161,7 @@ def linear(x, w: LinearWeight, residual: Optional[torch.Tensor] = None) -> torch
     xd = x.data if isinstance(x, QTensor) else x
     if w.kind == "w4":
         from .w4 import linear_w4
-        return linear_w4(xd, w.w4, residual=residual)
+        return linear_w4(xd, w.w4, residual=residual)       # xd: a matrix, or activations quantised to 4 bits (Fp4Act)
     if _lib.on_cpu(xd):
         if isinstance(x, QTensor):
             xf = ref.dequant_fp8_1x128(x.data, x.scale)

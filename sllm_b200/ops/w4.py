@@ -223,6 +223,21 @@ class W4Weight:
         return out
 
 
+@dataclass
+class Fp4Act:
+    """Activations already quantised for the W4A4 kernel (what `act_quant_fp4` returns), passed where a bf16 matrix
+    would be: `ops.linear` / `linear_w4` / the tensor-parallel row-parallel projection accept it for 4-bit weights."""
+    data: torch.Tensor          # codes uint8 [T, K_pad / 2]
+    sf: torch.Tensor            # block scales, 8 bytes per four
+    outer: torch.Tensor         # fp32 [T]
+    k: int
+    fmt: str
+
+    @property
+    def shape(self):
+        return (self.data.shape[0], self.k)
+
+
 def _bn_for(tokens: int) -> int:
     return 16 if tokens <= 16 else 32 if tokens <= 32 else 64 if tokens <= 64 else 128
 
@@ -232,10 +247,17 @@ def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = N
               row_ptr: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """y[t, :] = x[t, :] @ W_g(t)^T (* tok_scale[t]) (+ residual).  Dense when tok_off is None (groups must be 1);
     grouped otherwise: tokens of group g are rows tok_off[g] .. tok_off[g + 1] of x."""
+    if isinstance(x, Fp4Act):
+        if x.k != w.k or x.fmt != w.fmt:
+            raise ValueError("quantised activations do not match the weight's width or format")
+        return linear_w4a4(None, w, residual, tok_off, tok_scale, max_group_tokens, 0, row_ptr,
+                           quantized=(x.data, x.sf, x.outer))
     t, k = x.shape
     if k != w.k:
         raise ValueError("input width does not match the weight")
     if _lib.on_cpu(x):
+        if w4a4_enabled() and x.dtype == torch.bfloat16 and k % 8 == 0:
+            return linear_w4a4(x, w, residual, tok_off, tok_scale, max_group_tokens, 0, row_ptr)
         out = torch.zeros((t, w.n), dtype=torch.float32)
         offs = [0, t] if tok_off is None else tok_off.tolist()
         xf = x.float()

@@ -179,7 +179,7 @@ class FusedTP(NcclTP):
         return self._row_reduce.combine(part, self._ident[:part.shape[0]], residual)
 
     def row_linear(self, x, w: LinearWeight, residual):
-        xd = x.data if isinstance(x, QTensor) else x
+        xd = x.data if isinstance(x, QTensor) or hasattr(x, "sf") else x      # QTensor, 4-bit activations, or a matrix
         m, n = xd.shape[0], w.out_features
         if not xd.is_cuda or m > self.max_tokens:
             if xd.is_cuda:

@@ -722,6 +722,34 @@ def test_w4_llama_gpu_matches_cpu(fmt):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_w4a4_llama_gpu_matches_cpu(fmt):
+    """The dense 4-bit model with 4-bit activations (block-scaled tensor-core GEMMs, SiLU*up inside the quantiser of the
+    down projection) against the CPU evaluation of the same quantised arithmetic, and against its own W4A16 logits."""
+    from sllm_b200.engine.engine import build_engine
+    from sllm_b200.models import config as MC
+    from sllm_b200.ops import w4 as W
+    cfg = MC.ModelConfig(name="w4a4-test", n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, vocab=2048,
+                         weight_format=fmt, kv_format="bf16", max_context=256)
+    g = build_engine(cfg, DEV, seed=3, num_pages=64, max_batch=4)
+    c = _cpu_twin(g, cfg)
+    prompts = [list(range(3, 40)), [9, 8, 7, 6]]
+    base = g.prefill([g.new_sequence(p) for p in prompts], sample=False).float().cpu()
+    W.set_w4a4(True)
+    try:
+        g2 = build_engine(cfg, DEV, seed=3, num_pages=64, max_batch=4)
+        lg = g2.prefill([g2.new_sequence(p) for p in prompts], sample=False).float().cpu()
+        lc = c.prefill([c.new_sequence(p) for p in prompts], sample=False).float()
+        out = g2.generate(prompts, 8)                      # graph-captured decode on the 4-bit path
+        assert out == g2.generate(prompts, 8) and all(len(o) == 8 for o in out)
+    finally:
+        W.set_w4a4(False)
+    assert rel_err(lg, lc) < 6e-2                          # quantisation decisions flip on bf16-level differences
+    assert 0.02 < rel_err(lg, base) < 0.5                  # 4-bit activations change the logits, within reason
+    assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
 def test_gdn_kernels_match_oracle():
     from sllm_b200.ops import gdn
     torch.manual_seed(3)

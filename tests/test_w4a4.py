@@ -225,3 +225,24 @@ def test_gated_quantiser_and_expert_mlp_gpu(fmt):
     y16 = linear_w4(x.to(DEV), w)
     assert 0.02 < rel(y4.float(), y16.float()) < 0.16
     assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
+def test_scatter_epilogue_places_rows_by_address():
+    """row_ptr: result row t is stored at the bf16 row whose address is row_ptr[t] (the expert-parallel combine hands
+    addresses in the token owner's memory); here the addresses permute the rows of a local buffer."""
+    torch.manual_seed(8)
+    t, n, k, groups = 24, 256, 512, 4
+    w = W4Weight.quantize("mxfp4", torch.randn(groups, n, k) * 0.1, DEV, keep_file=False)
+    x = torch.randn(t, k).to(torch.bfloat16).to(DEV)
+    tok_off = torch.tensor([0, 5, 5, 17, 24], dtype=torch.int32, device=DEV)
+    ts = torch.rand(t, device=DEV)
+    q = act_quant_fp4(x, "mxfp4")
+    plain = linear_w4a4(None, w, tok_off=tok_off, tok_scale=ts, max_group_tokens=12, quantized=q)
+    buf = torch.zeros((t, n), dtype=torch.bfloat16, device=DEV)
+    perm = torch.randperm(t)
+    row_ptr = torch.tensor([buf.data_ptr() + int(p) * n * 2 for p in perm], dtype=torch.int64, device=DEV)
+    assert linear_w4a4(None, w, tok_off=tok_off, tok_scale=ts, max_group_tokens=12, quantized=q, row_ptr=row_ptr) is None
+    torch.cuda.synchronize()
+    assert torch.equal(buf[perm.to(DEV)], plain)
+    assert ops.device_status(torch.device(DEV)) == 0
