@@ -437,10 +437,21 @@ __device__ __forceinline__ float f4_gelu_tanh(float x) {
 
 // Eight consecutive values of the row to quantise.  gated (1 SiLU, 2 GELU-tanh): the row is [gate (k) | up (k)] and the
 // value is act(gate) * up with the bf16 roundings of the stand-alone gated-activation kernel (elementwise.cu).
-__device__ __forceinline__ void f4_load8(const __nv_bfloat16* row, int i, int k, int gated, float (&v)[8]) {
+// norm_w: the value is the RMS-normalised element x * inv * weight (weight + 1 with offset_one), rounded to bf16 as the
+// stand-alone norm kernel writes it.
+__device__ __forceinline__ void f4_load8(const __nv_bfloat16* row, int i, int k, int gated, const __nv_bfloat16* norm_w,
+                                         float inv, int offset_one, float (&v)[8]) {
   const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
   const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
-  if (!gated) {
+  if (norm_w) {
+    const uint4 raww = *reinterpret_cast<const uint4*>(norm_w + i);
+    const __nv_bfloat16* wv = reinterpret_cast<const __nv_bfloat16*>(&raww);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g = offset_one ? 1.f + __bfloat162float(wv[j]) : __bfloat162float(wv[j]);
+      v[j] = __bfloat162float(__float2bfloat16_rn(__bfloat162float(h[j]) * inv * g));
+    }
+  } else if (!gated) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(h[j]);
   } else {
@@ -458,19 +469,41 @@ __device__ __forceinline__ void f4_load8(const __nv_bfloat16* row, int i, int k,
 template <int kBlock>
 __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int k, int k_pad,
                                                             const int* __restrict__ src_row, const int* __restrict__ n_rows_ptr,
-                                                            int gated, uint8_t* __restrict__ xq, uint8_t* __restrict__ xsf,
-                                                            int sf_ld, float* __restrict__ outer) {
+                                                            int gated, const __nv_bfloat16* __restrict__ norm_w, float eps,
+                                                            int offset_one, uint8_t* __restrict__ xq,
+                                                            uint8_t* __restrict__ xsf, int sf_ld, float* __restrict__ outer) {
   __shared__ float red[8];
   pdl_wait();
   const int t = blockIdx.x;
   if (n_rows_ptr && t >= *n_rows_ptr) return;        // rows past the routed ones: their source index is not defined
   const __nv_bfloat16* row = x + static_cast<size_t>(src_row ? src_row[t] : t) * ldx;
+  float inv = 1.f;
+  if (norm_w) {
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < k; i += 256 * 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = __bfloat162float(h[j]);
+        ss += f * f;
+      }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    inv = rsqrtf(tot / k + eps);
+    __syncthreads();                                   // red is reused below
+  }
   float outer_s = 1.f;
   if (kBlock == 16) {
     float amax = 0.f;
     for (int i = threadIdx.x * 8; i < k; i += 256 * 8) {
       float v[8];
-      f4_load8(row, i, k, gated, v);
+      f4_load8(row, i, k, gated, norm_w, inv, offset_one, v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float a = fabsf(v[j]);
@@ -497,7 +530,7 @@ __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16*
     for (int c = 0; c < kBlock / 8; ++c) {
       const int i = b * kBlock + c * 8;
       float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (i < k) f4_load8(row, i, k, gated, f);                          // k is a multiple of 8
+      if (i < k) f4_load8(row, i, k, gated, norm_w, inv, offset_one, f);   // k is a multiple of 8
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         v[c * 8 + j] = f[j];
@@ -543,23 +576,28 @@ using namespace sllm;
 // x: bf16 [rows of the source, k] (row stride ldx elements, k a multiple of 8); token t reads source row src_row[t]
 // (or t when src_row is null: gathering the rows of a routed batch costs nothing extra); with n_rows_ptr (device int)
 // tokens >= *n_rows_ptr are skipped.  gated (0 none, 1 SiLU, 2 GELU-tanh): x rows are [gate (k) | up (k)] and the
-// quantised value is act(gate) * up.  xq: [tokens, k_pad / 2]; xsf: [tokens, sf_ld] with sf_ld >= 2 k_pad / block
+// quantised value is act(gate) * up.  norm_w (bf16 [k], optional, not with gated): the row is RMS-normalised first
+// (eps; weight + 1 with offset_one).  xq: [tokens, k_pad / 2]; xsf: [tokens, sf_ld] with sf_ld >= 2 k_pad / block
 // (8 bytes per four scales), a multiple of 16; outer: [tokens] fp32.  fmt 0 = MXFP4 (block 32), 1 = NVFP4 (16).
 SLLM_EXPORT int sllm_act_quant_fp4(const void* x, int ldx, int tokens, int k, int k_pad, const int* src_row,
-                                   const int* n_rows_ptr, int gated, int fmt, void* xq, void* xsf, int sf_ld, float* outer,
-                                   void* stream) {
+                                   const int* n_rows_ptr, int gated, const void* norm_w, float eps, int offset_one, int fmt,
+                                   void* xq, void* xsf, int sf_ld, float* outer, void* stream) {
   if (!x || !xq || !xsf || !outer || tokens <= 0 || k <= 0 || (k % 8) || k_pad < k || (k_pad % kF4KBlock) || (ldx % 8) ||
-      (fmt != 0 && fmt != 1) || gated < 0 || gated > 2 || ldx < (gated ? 2 * k : k))
+      (fmt != 0 && fmt != 1) || gated < 0 || gated > 2 || ldx < (gated ? 2 * k : k) || (norm_w && gated) ||
+      (reinterpret_cast<uintptr_t>(norm_w) & 15))
     return SLLM_ERR_INVALID_ARGUMENT;
+  const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(norm_w);
   if (sf_ld < 2 * k_pad / (fmt ? 16 : 32) || (sf_ld % 16)) return SLLM_ERR_INVALID_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (fmt)
     e = launch_kernel(act_quant_fp4_kernel<16>, dim3(tokens), dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
-                      k, k_pad, src_row, n_rows_ptr, gated, static_cast<uint8_t*>(xq), static_cast<uint8_t*>(xsf), sf_ld, outer);
+                      k, k_pad, src_row, n_rows_ptr, gated, nw, eps, offset_one, static_cast<uint8_t*>(xq),
+                      static_cast<uint8_t*>(xsf), sf_ld, outer);
   else
     e = launch_kernel(act_quant_fp4_kernel<32>, dim3(tokens), dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
-                      k, k_pad, src_row, n_rows_ptr, gated, static_cast<uint8_t*>(xq), static_cast<uint8_t*>(xsf), sf_ld, outer);
+                      k, k_pad, src_row, n_rows_ptr, gated, nw, eps, offset_one, static_cast<uint8_t*>(xq),
+                      static_cast<uint8_t*>(xsf), sf_ld, outer);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 

@@ -215,6 +215,16 @@ class LlamaModel:
     def local_kv_heads(self) -> int:
         return self.hkv
 
+    def _norm_in(self, h, norm_w, consumer: LinearWeight, quant_fp8: bool):
+        """The RMS-normalised residual stream in the form its consumer takes: FP8 + scales, bf16, or - for a 4-bit
+        matrix on the W4A4 path - 4-bit codes, the norm computed inside the quantiser."""
+        cfg = self.cfg
+        if (consumer.kind == "w4" and _w4.w4a4_enabled() and h.dtype == torch.bfloat16 and norm_w.dtype == torch.bfloat16
+                and h.shape[1] % 8 == 0):
+            q = _w4.act_quant_fp4(h, consumer.w4.fmt, norm=(norm_w, cfg.rms_eps, cfg.norm_offset_one))
+            return _w4.Fp4Act(*q, k=h.shape[1], fmt=consumer.w4.fmt)
+        return ops.rmsnorm(h, norm_w, cfg.rms_eps, cfg.norm_offset_one, quant=quant_fp8)
+
     def hidden(self, b: ForwardBatch, cache) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         hd = cfg.head_dim
@@ -229,7 +239,7 @@ class LlamaModel:
             if ad is not None and (ad.loras or ad.cvs):
                 h = self._adapter_layer(li, lw, h, b, kv, ad)
                 continue
-            x = ops.rmsnorm(h, lw.attn_norm, cfg.rms_eps, cfg.norm_offset_one, quant=q_attn)
+            x = self._norm_in(h, lw.attn_norm, lw.qkv, q_attn)
             qkv = ops.linear(x, lw.qkv)
             if cfg.qk_norm or cfg.v_norm:
                 from ..ops import gdn as _g
@@ -249,7 +259,7 @@ class LlamaModel:
                 h = ops.elementwise("add", h, o)
             else:
                 h = self.tp.row_linear(a, lw.o, h)
-            x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one, quant=q_mlp)
+            x = self._norm_in(h, lw.mlp_norm, lw.gate_up, q_mlp)
             gu = ops.linear(x, lw.gate_up)
             if lw.down.kind == "w4" and _w4.w4a4_enabled() and gu.dtype == torch.bfloat16:
                 # 4-bit activations: SiLU*up runs inside the quantiser of the down projection

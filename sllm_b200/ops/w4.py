@@ -330,13 +330,14 @@ def set_w4a4(on: bool) -> None:
 
 
 def act_quant_fp4(x: torch.Tensor, fmt: str, src_row: Optional[torch.Tensor] = None, tokens: Optional[int] = None,
-                  n_rows: Optional[torch.Tensor] = None, gated: Optional[str] = None):
+                  n_rows: Optional[torch.Tensor] = None, gated: Optional[str] = None, norm: Optional[tuple] = None):
     """bf16 [T, K] -> (codes uint8 [T, K_pad / 2], block scales uint8 [T, 2 K_pad / block], row scales fp32 [T]) with K
     padded to 256.  The scale matrix is the kernel's operand: four scale bytes, then four unused ones (`sf_compact`
     drops them).  nvfp4: row scale amax / 2688, UE4M3 block scales; mxfp4: UE8M0 block scales, row scale 1.
     `src_row` (int32 [T]): token t reads row src_row[t] of x; `n_rows` (int32 device scalar): tokens from *n_rows on are
     skipped (their outputs stay undefined); `gated` ("silu" | "gelu_tanh"): x is [T, 2 K] = [gate | up] and
-    act(gate) * up is what gets quantised."""
+    act(gate) * up is what gets quantised; `norm` = (weight bf16 [K], eps, offset_one): the RMS-normalised row is what
+    gets quantised (not together with `gated`)."""
     from . import reference
     t = tokens if tokens is not None else (x.shape[0] if src_row is None else src_row.numel())
     k = x.shape[1] // 2 if gated else x.shape[1]
@@ -347,18 +348,23 @@ def act_quant_fp4(x: torch.Tensor, fmt: str, src_row: Optional[torch.Tensor] = N
         xs = xs[:t]
         if gated:
             xs = reference.round_bf16(reference.gated_act(xs, gated))
+        if norm is not None:
+            xs = reference.round_bf16(reference.rmsnorm(xs, norm[0], norm[1], norm[2]))
         codes, sf, outer = reference.quant_act_fp4(xs, fmt)
         return codes, sf_padded(sf), outer
     from .core import _p, _stream
     P, I = C.c_void_p, C.c_int
-    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_act_quant_fp4", (I, [P, I, I, I, I, P, P, I, I, P, P, I, P, P]))
+    _lib.EXTRA_KERNEL_SIGNATURES.setdefault("sllm_act_quant_fp4", (I, [P, I, I, I, I, P, P, I, P, C.c_float, I, I, P, P, I, P, P]))
+    if norm is not None and (gated or norm[0].dtype != torch.bfloat16 or norm[0].numel() != k):
+        raise ValueError("act_quant_fp4: norm takes a bf16 weight of the row width and excludes gated")
     if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or k % 8:
         raise ValueError("act_quant_fp4: bf16 rows with a stride and width that are multiples of 8")
     xq = torch.empty((t, k_pad // 2), dtype=torch.uint8, device=x.device)
     xsf = torch.empty((t, 2 * k_pad // block), dtype=torch.uint8, device=x.device)      # a multiple of 16 bytes
     outer = torch.empty((t,), dtype=torch.float32, device=x.device)
     g = 0 if not gated else 1 if gated == "silu" else 2
-    rc = _lib.kernels().sllm_act_quant_fp4(_p(x), x.stride(0), t, k, k_pad, _p(src_row), _p(n_rows), g,
+    nw, eps, off1 = (norm[0], float(norm[1]), int(bool(norm[2]))) if norm is not None else (None, 0.0, 0)
+    rc = _lib.kernels().sllm_act_quant_fp4(_p(x), x.stride(0), t, k, k_pad, _p(src_row), _p(n_rows), g, _p(nw), eps, off1,
                                            0 if fmt == "mxfp4" else 1, _p(xq), _p(xsf), xsf.stride(0), _p(outer), _stream())
     _lib.check(rc, "act_quant_fp4")
     return xq, xsf, outer

@@ -204,6 +204,15 @@ def test_gated_quantiser_and_expert_mlp_gpu(fmt):
     assert rel(got, want) < 0.16
     ref = R.dequant_act_fp4(*[a if i != 1 else a for i, a in enumerate(R.quant_act_fp4(want, fmt))], fmt)[:, :384]
     assert rel(got, ref) < 0.03                       # the same quantiser up to the device's exp()
+    # RMSNorm inside the quantiser
+    h = torch.randn(7, 640).to(torch.bfloat16)
+    nw = (torch.randn(640) * 0.1).to(torch.bfloat16)
+    for off1 in (False, True):
+        qn = act_quant_fp4(h.to(DEV), fmt, norm=(nw.to(DEV), 1e-5, off1))
+        wantn = R.round_bf16(R.rmsnorm(h, nw, 1e-5, off1))
+        gotn = R.dequant_act_fp4(qn[0], sf_compact(qn[1].cpu()), qn[2], fmt)[:, :640]
+        refn = R.dequant_act_fp4(*R.quant_act_fp4(wantn, fmt), fmt)[:, :640]
+        assert rel(gotn, wantn) < 0.16 and rel(gotn, refn) < 0.03
     # the routed expert MLP, GPU against the CPU form of the same W4A4 arithmetic
     E, d, F, t, k = 8, 256, 256, 40, 2
     wgu, wdn = torch.randn(E, 2 * F, d) * 0.1, torch.randn(E, d, F) * 0.1
