@@ -40,12 +40,25 @@ def add_model_source(p: argparse.ArgumentParser, required: bool = True) -> None:
     p.add_argument("--target", default=TARGET)
     p.add_argument("--kv-cache-encoding", choices=KV_ENCODINGS, default=None)
     p.add_argument("--context-length", type=int, default=None)
+    p.add_argument("--activation-encoding", choices=ACT_ENCODINGS, default=None,
+                   help="4-bit-weight models: bf16 (W4A16, default) or fp4 (activations quantised to the weights' 4-bit "
+                        "format, GEMMs on the block-scaled tensor-core kernel)")
     p.add_argument("--cpu", action="store_true", help="run the CPU oracle path (small models only)")
 
 
 def emit(obj) -> None:
     sys.stdout.write(json.dumps(obj, ensure_ascii=False, separators=(",", ":")) + "\n")
     sys.stdout.flush()
+
+
+ACT_ENCODINGS = ("bf16", "fp4")
+
+
+def apply_activation_encoding(args) -> None:
+    enc = getattr(args, "activation_encoding", None)
+    if enc is not None:
+        from ..ops import w4
+        w4.set_w4a4(enc == "fp4")
 
 
 _KV_MAP = {"fp16": "bf16", "bf16": "bf16", "fp8": "fp8", "fp8-static": "fp8-static", "nvfp4": "nvfp4"}
@@ -66,6 +79,7 @@ def open_model(args, max_batch: int = 8, tp=None):
         g = G.verify_gguf(args.gguf, lock)
     except (OSError, G.GgufError) as exc:
         raise CliError(f"model verification failed: {exc}", 3) from None
+    apply_activation_encoding(args)
     use_cpu = getattr(args, "cpu", False)
     if not use_cpu and not torch.cuda.is_available():
         raise CliError("no CUDA device is available (pass --cpu for the CPU oracle path)", 4)

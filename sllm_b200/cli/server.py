@@ -15,7 +15,7 @@ import sys
 import threading
 import time
 
-from .common import KV_ENCODINGS, TARGET, CliError, StrictParser, emit, open_model, run_main
+from .common import ACT_ENCODINGS, KV_ENCODINGS, TARGET, CliError, StrictParser, emit, open_model, run_main
 
 
 def build_parser() -> StrictParser:
@@ -55,6 +55,8 @@ def build_parser() -> StrictParser:
     # context / KV
     p.add_argument("--context-length", type=int, default=None)
     p.add_argument("--kv-cache-encoding", choices=KV_ENCODINGS, default=None)
+    p.add_argument("--activation-encoding", choices=ACT_ENCODINGS, default=None,
+                   help="4-bit-weight models: bf16 (W4A16, default) or fp4 (W4A4 on the block-scaled tensor-core kernel)")
     p.add_argument("--prefix-cache", action="store_true")
     p.add_argument("--prefix-cache-max-entries", type=int, default=256)
     p.add_argument("--prefix-cache-max-tokens", type=int, default=1 << 20)

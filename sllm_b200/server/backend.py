@@ -210,7 +210,9 @@ class EngineBackend:
 
     def props(self) -> dict:
         c = self.engine.cfg
-        return {"backend": "sllm-b200", "quarantine": getattr(self.engine, "quarantine", None), "model_family": c.family, "context_length": c.max_context, "vocab_size": c.vocab,
+        from ..ops import w4 as _w4
+        return {"backend": "sllm-b200", "quarantine": getattr(self.engine, "quarantine", None), "model_family": c.family,
+                "activation_encoding": "fp4" if _w4.w4a4_enabled() else "bf16", "context_length": c.max_context, "vocab_size": c.vocab,
                 "kv_cache_encoding": c.kv_format, "weight_format": c.weight_format, "page_size": c.page_size,
                 "tensor_parallel": getattr(self.engine.tp, "size", 1) if self.engine.tp else 1,
                 "prefix_cache": self.prefix_cache is not None, "vision": getattr(self.engine, "vision", None) is not None}

@@ -203,3 +203,31 @@ def test_other_model_families_served_from_converted_files(tmp_path, artifact):
         assert props["model_family"] == eng.cfg.family and props["quarantine"] is None
     finally:
         backend.shutdown(1.0)
+
+
+def test_activation_encoding_flag_serves_the_w4a4_path(tmp_path):
+    """`--activation-encoding fp4`: a mixture-of-experts file served with 4-bit activations (CPU form of the W4A4
+    arithmetic); /props reports it and greedy completions are reproducible."""
+    import argparse
+    from sllm_b200.cli import convert
+    from sllm_b200.cli.common import open_model
+    from sllm_b200.ops import w4
+    g, l = str(tmp_path / "m.gguf"), str(tmp_path / "m.lock.json")
+    assert convert.main(["--kind", "random-llama", "--artifact", "tiny-shared-moe", "--weight-format", "bf16", "--output", g,
+                         "--derived-lock", l, "--synthetic-tokenizer"]) == 0
+    args = argparse.Namespace(gguf=g, derived_lock=l, device_index=0, target="sm_100a", kv_cache_encoding=None,
+                              context_length=None, cpu=True, activation_encoding="fp4")
+    try:
+        eng, tok, _, _ = open_model(args, max_batch=2)
+        assert w4.w4a4_enabled()
+        backend = EngineBackend(eng, tok, aliases=(M,), queue_capacity=4)
+        try:
+            c = TestClient(build_app(ModelRegistry({M: backend}), ServerConfig()))
+            req = {"model": M, "prompt": "alpha beta gamma", "max_tokens": 5, "temperature": 0}
+            a, b = c.post("/v1/completions", json=req).json(), c.post("/v1/completions", json=req).json()
+            assert a["choices"][0]["text"] == b["choices"][0]["text"] and a["usage"]["completion_tokens"] == 5
+            assert c.get("/props").json()["models"][0]["activation_encoding"] == "fp4"
+        finally:
+            backend.shutdown(1.0)
+    finally:
+        w4.set_w4a4(False)
