@@ -15,6 +15,8 @@ enum SllmHostStatus {
   SLLM_HOST_LIMIT = 4,
   SLLM_HOST_PARSE_ERROR = 5,
   SLLM_HOST_BUSY = 6,
+  SLLM_SAMPLE_NAN = 7,     /* a logit is NaN: *token holds its index */
+  SLLM_SAMPLE_EMPTY = 8,   /* no token is left to choose from */
 };
 
 /* page_pool.cpp */
@@ -46,3 +48,38 @@ SLLM_HOST_EXPORT int sllm_grammar_accept(int s, int token);
 SLLM_HOST_EXPORT int sllm_grammar_accept_bytes(int s, const unsigned char* bytes, int n);
 SLLM_HOST_EXPORT int sllm_grammar_is_complete(int s);
 SLLM_HOST_EXPORT int sllm_grammar_stats(int h, long long* out3);
+
+/* sampler.cpp: the host sampler chain over one row of logits (stage order and arithmetic: see the file). */
+typedef struct SllmSamplerConfig {
+  double temperature, top_p, min_p, typical_p;   /* temperature <= 0: greedy over the processed logits */
+  double presence_penalty, frequency_penalty, repeat_penalty;
+  double dyn_range, dyn_exponent;                /* used when dynamic_temperature != 0 */
+  double dry_multiplier, dry_base;
+  double xtc_probability, xtc_threshold;
+  double mirostat_tau, mirostat_eta;
+  const int* bias_tokens;                        /* n_bias (token, value) pairs */
+  const float* bias_values;
+  const int* dry_breakers;                       /* single-token sequence breakers */
+  int n_bias, n_dry_breakers;
+  int top_k;                                     /* 0: off */
+  int repeat_last_n;
+  int dynamic_temperature;
+  int ignore_eos_token;                          /* < 0: off */
+  int dry, dry_allowed_length, dry_last_n;
+  int xtc, xtc_min_keep;
+  int mirostat;                                  /* 0 off, 1, 2 */
+  int return_logprobs, top_logprobs;
+} SllmSamplerConfig;
+
+typedef struct SllmSamplerState {
+  uint64_t rng_state;                            /* SplitMix64: the state after k draws is seed + k * gamma */
+  long long draws;
+  double mu;                                     /* Mirostat */
+} SllmSamplerState;
+
+/* history: accepted tokens, oldest first; count_tokens / count_values: occurrences per distinct token.
+ * top_ids / top_logprobs: room for cfg->top_logprobs entries (may be null when that is 0). */
+SLLM_HOST_EXPORT int sllm_host_sample(const float* logits, int vocab, const unsigned char* valid_mask,
+                                      const SllmSamplerConfig* cfg, SllmSamplerState* state, const int* history,
+                                      int n_history, const int* count_tokens, const int* count_values, int n_counts,
+                                      int* token, double* logprob, int* top_ids, double* top_logprobs, int* n_top);

@@ -15,6 +15,7 @@ Behavioural contract (reference: crates/sllm-core/src/sampling.rs):
 """
 from __future__ import annotations
 
+import ctypes as C
 import json
 import math
 import os
@@ -261,6 +262,47 @@ class Selection:
     top_logprobs: list = field(default_factory=list)  # [(token, logprob)]
 
 
+class _NativeConfig(C.Structure):
+    """struct SllmSamplerConfig of csrc/host/host_api.h."""
+    _fields_ = ([(n, C.c_double) for n in ("temperature", "top_p", "min_p", "typical_p", "presence_penalty", "frequency_penalty",
+                                           "repeat_penalty", "dyn_range", "dyn_exponent", "dry_multiplier", "dry_base",
+                                           "xtc_probability", "xtc_threshold", "mirostat_tau", "mirostat_eta")]
+                + [("bias_tokens", C.POINTER(C.c_int)), ("bias_values", C.POINTER(C.c_float)), ("dry_breakers", C.POINTER(C.c_int))]
+                + [(n, C.c_int) for n in ("n_bias", "n_dry_breakers", "top_k", "repeat_last_n", "dynamic_temperature",
+                                          "ignore_eos_token", "dry", "dry_allowed_length", "dry_last_n", "xtc", "xtc_min_keep",
+                                          "mirostat", "return_logprobs", "top_logprobs")])
+
+
+class _NativeState(C.Structure):
+    _fields_ = [("rng_state", C.c_uint64), ("draws", C.c_longlong), ("mu", C.c_double)]
+
+
+_native = {"lib": None, "on": None}
+
+
+def _native_lib():
+    if _native["lib"] is None:
+        from ..ops import _lib
+        lib = _lib.host()
+        lib.sllm_host_sample.restype = C.c_int
+        lib.sllm_host_sample.argtypes = [C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_ubyte), C.POINTER(_NativeConfig),
+                                         C.POINTER(_NativeState), C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int),
+                                         C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_double),
+                                         C.POINTER(C.c_int), C.POINTER(C.c_double), C.POINTER(C.c_int)]
+        _native["lib"] = lib
+    return _native["lib"]
+
+
+def native_sampler_enabled() -> bool:
+    if _native["on"] is None:
+        _native["on"] = os.environ.get("SLLM_HOST_SAMPLER", "native") != "python"
+    return _native["on"]
+
+
+def use_native_sampler(on: bool) -> None:
+    _native["on"] = bool(on)
+
+
 class SamplerChain:
     """The ordered chain.  `select` consumes one row of logits (float32) and an optional validity mask."""
 
@@ -387,7 +429,10 @@ class SamplerChain:
     # -------------------------------------------------------------- host selection
     def select(self, logits: Optional[np.ndarray], device_argmax: Optional[int] = None,
                valid_mask: Optional[np.ndarray] = None) -> Selection:
-        c, p = self.cfg, self.cfg.params
+        """One token from one row of logits.  The chain runs in the native host library (csrc/host/sampler.cpp);
+        `SLLM_HOST_SAMPLER=python` (or `use_native_sampler(False)`) selects the NumPy form of the same chain, which is
+        the oracle of the native one."""
+        c = self.cfg
         if not c.requires_logits and not c.extended and valid_mask is None and c.ignore_eos_token is None:
             if device_argmax is None:
                 if logits is None:
@@ -396,6 +441,79 @@ class SamplerChain:
             return Selection(int(device_argmax))
         if logits is None:
             raise SamplingError("logits are required by the configured sampler chain")
+        if native_sampler_enabled():
+            return self._select_native(logits, valid_mask)
+        return self._select_python(logits, valid_mask)
+
+    def _native_config(self):
+        if getattr(self, "_ncfg", None) is not None:
+            return self._ncfg
+        c, p = self.cfg, self.cfg.params
+        keep = []
+        k = _NativeConfig()
+        k.temperature, k.top_p, k.min_p, k.typical_p = float(p.temperature), float(p.top_p), float(c.min_p), float(c.typical_p)
+        k.presence_penalty, k.frequency_penalty = float(p.presence_penalty), float(p.frequency_penalty)
+        k.repeat_penalty = float(c.repeat_penalty)
+        if c.dynamic_temperature is not None:
+            k.dynamic_temperature, k.dyn_range, k.dyn_exponent = 1, float(c.dynamic_temperature[0]), float(c.dynamic_temperature[1])
+        if c.logit_bias:
+            bt = (C.c_int * len(c.logit_bias))(*[int(t) for t, _ in c.logit_bias])
+            bv = (C.c_float * len(c.logit_bias))(*[float(np.float32(b)) for _, b in c.logit_bias])
+            keep += [bt, bv]
+            k.bias_tokens, k.bias_values, k.n_bias = C.cast(bt, C.POINTER(C.c_int)), C.cast(bv, C.POINTER(C.c_float)), len(c.logit_bias)
+        if c.dry is not None:
+            single = [int(b[0]) for b in c.dry.sequence_breakers if len(b) == 1]
+            br = (C.c_int * max(1, len(single)))(*single)
+            keep.append(br)
+            k.dry, k.dry_multiplier, k.dry_base = 1, float(c.dry.multiplier), float(c.dry.base)
+            k.dry_allowed_length, k.dry_last_n = int(c.dry.allowed_length), int(c.dry.penalty_last_n)
+            k.dry_breakers, k.n_dry_breakers = C.cast(br, C.POINTER(C.c_int)), len(single)
+        k.top_k = int(c.top_k or 0)
+        k.repeat_last_n = int(c.repeat_last_n)
+        k.ignore_eos_token = -1 if c.ignore_eos_token is None else int(c.ignore_eos_token)
+        if c.xtc is not None:
+            k.xtc, k.xtc_probability, k.xtc_threshold, k.xtc_min_keep = 1, float(c.xtc.probability), float(c.xtc.threshold), int(c.xtc.min_keep)
+        if c.mirostat is not None:
+            k.mirostat, k.mirostat_tau, k.mirostat_eta = int(c.mirostat.mode), float(c.mirostat.tau), float(c.mirostat.eta)
+        k.return_logprobs, k.top_logprobs = int(bool(c.return_logprobs)), int(c.top_logprobs)
+        self._ncfg, self._ncfg_keep = k, keep
+        return k
+
+    def _select_native(self, logits, valid_mask) -> Selection:
+        lib = _native_lib()
+        raw = np.ascontiguousarray(np.asarray(logits, dtype=np.float32).reshape(-1))
+        cfg = self._native_config()
+        st = _NativeState(self.rng.state, self.draws, float(self.mu))
+        hist = np.asarray(self.history, dtype=np.int32)
+        ct = np.fromiter(self.counts.keys(), dtype=np.int32, count=len(self.counts))
+        cv = np.fromiter(self.counts.values(), dtype=np.int32, count=len(self.counts))
+        mask = None
+        if valid_mask is not None:
+            mask = np.ascontiguousarray(np.asarray(valid_mask).reshape(-1) != 0).view(np.uint8)
+            if mask.size != raw.size:
+                raise SamplingError("validity mask and logits differ in length")
+        tok, lp, ntop = C.c_int(0), C.c_double(0.0), C.c_int(0)
+        nt = max(1, self.cfg.top_logprobs)
+        top_ids, top_lp = (C.c_int * nt)(), (C.c_double * nt)()
+        ptr = lambda a, t: a.ctypes.data_as(C.POINTER(t)) if a is not None and a.size else None
+        rc = lib.sllm_host_sample(ptr(raw, C.c_float), raw.size, ptr(mask, C.c_ubyte), C.byref(cfg), C.byref(st),
+                                  ptr(hist, C.c_int), hist.size, ptr(ct, C.c_int), ptr(cv, C.c_int), ct.size, C.byref(tok),
+                                  C.byref(lp), top_ids, top_lp, C.byref(ntop))
+        if rc == 7:
+            raise SamplingError(f"NaN logit at token {tok.value}")
+        if rc == 8:
+            raise SamplingError("empty distribution")
+        if rc != 0:
+            raise SamplingError(f"host sampler failed with status {rc}")
+        self.rng.state, self.draws, self.mu = int(st.rng_state), int(st.draws), float(st.mu)
+        sel = Selection(int(tok.value))
+        if self.cfg.return_logprobs or self.cfg.top_logprobs:
+            sel.logprob = float(lp.value)
+            sel.top_logprobs = [(int(top_ids[i]), float(top_lp[i])) for i in range(ntop.value)]
+        return sel
+
+    def _select_python(self, logits, valid_mask=None) -> Selection:
+        c, p = self.cfg, self.cfg.params
         raw = np.asarray(logits, dtype=np.float32)
         if np.isnan(raw).any():
             raise SamplingError(f"NaN logit at token {int(np.argmax(np.isnan(raw)))}")

@@ -158,3 +158,101 @@ def test_reference_selector_matches_profile_sampler_order():
         assert tok == want
     assert S.reference_select(np.array([np.nan, 1.0], dtype=np.float32), (1.0, 1.0, 0.0, 0, 1, 0))[1] == 1
     assert S.reference_select(np.zeros(4, dtype=np.float32), (1.0, 1.0, 0.0, 0, 1, 0), mask=np.zeros(4))[1] == 2
+
+
+# ---------------------------------------------------------------------------------------------- native host sampler
+def _random_chain_config(rng):
+    from sllm_b200.engine import sampling as S
+    pick = lambda p: rng.random() < p
+    params = S.SamplingParams(temperature=float(rng.choice([0.0, 0.3, 0.8, 1.5])), top_p=float(rng.choice([1.0, 0.95, 0.7])),
+                              presence_penalty=float(rng.choice([0.0, 0.5])), frequency_penalty=float(rng.choice([0.0, 0.3])))
+    cfg = S.SamplerChainConfig(params=params)
+    if pick(0.4):
+        cfg.top_k = int(rng.integers(1, 60))
+    if pick(0.4):
+        cfg.min_p = float(rng.choice([0.01, 0.1]))
+    if pick(0.3):
+        cfg.typical_p = float(rng.choice([0.5, 0.9]))
+    if pick(0.4):
+        cfg.repeat_penalty, cfg.repeat_last_n = float(rng.choice([0.8, 1.2])), int(rng.integers(1, 40))
+    if pick(0.3) and params.temperature > 0:
+        cfg.dynamic_temperature = (0.3, 1.5)
+    if pick(0.3):
+        cfg.ignore_eos_token = 7
+    if pick(0.4):
+        toks = rng.choice(400, size=5, replace=False)
+        cfg.logit_bias = [(int(t), float(b)) for t, b in zip(toks, rng.uniform(-5, 5, 5))]
+    if pick(0.3):
+        cfg.dry = S.DryConfig(multiplier=0.8, base=1.75, allowed_length=2, sequence_breakers=[[3], [4, 5]], penalty_last_n=int(rng.choice([0, 30])))
+    if pick(0.3) and params.temperature > 0:
+        cfg.xtc = S.XtcConfig(probability=0.6, threshold=0.05, min_keep=1)
+    if pick(0.25):
+        cfg.mirostat = S.MirostatConfig(mode=int(rng.choice([1, 2])), tau=4.0, eta=0.2, mu=8.0)
+    if pick(0.5):
+        cfg.return_logprobs, cfg.top_logprobs = True, int(rng.integers(0, 5))
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_native_host_sampler_matches_the_python_chain(seed):
+    """The C++ chain (csrc/host/sampler.cpp) against the NumPy chain it restates: same tokens, same random-stream and
+    Mirostat state after every step, log-probabilities to rounding, for random stage combinations, histories with
+    repetitions (DRY / repeat penalty), grammar masks and +inf / -inf logits."""
+    from sllm_b200.engine import sampling as S
+    rng = np.random.default_rng(seed)
+    cfg = _random_chain_config(rng)
+    vocab = int(rng.integers(400, 3000))
+    prior = [int(t) for t in rng.integers(0, 40, size=int(rng.integers(0, 60)))]
+    chains = []
+    for native in (True, False):
+        S.use_native_sampler(native)
+        chains.append(S.SamplerChain(cfg, prior_tokens=prior, seed=1234 + seed))
+    try:
+        for step in range(6):
+            lg = (rng.standard_normal(vocab) * 3).astype(np.float32)
+            if step == 2:
+                lg[rng.integers(0, vocab, 3)] = -np.inf
+            if step == 4 and cfg.params.temperature > 0 and cfg.mirostat is None:
+                lg[[11, 12]] = np.inf
+            mask = (rng.random(vocab) < 0.7) if step % 3 == 1 else None
+            if mask is not None:
+                mask[int(np.argmax(lg))] = True
+            out = []
+            for native, ch in zip((True, False), chains):
+                S.use_native_sampler(native)
+                out.append(ch.select(lg, valid_mask=mask))
+            a, b = out
+            assert a.token == b.token, (seed, step)
+            assert (chains[0].rng.state, chains[0].draws) == (chains[1].rng.state, chains[1].draws)
+            assert chains[0].mu == pytest.approx(chains[1].mu, rel=1e-12, abs=1e-12)
+            if cfg.return_logprobs or cfg.top_logprobs:
+                # (+inf logits make the log-probabilities NaN in both forms)
+                assert np.allclose(a.logprob, b.logprob, rtol=1e-9, atol=1e-9, equal_nan=True)
+                if not np.isnan(b.logprob):
+                    assert [t for t, _ in a.top_logprobs] == [t for t, _ in b.top_logprobs]
+                    assert np.allclose([v for _, v in a.top_logprobs], [v for _, v in b.top_logprobs], rtol=1e-9, atol=1e-9)
+            for ch in chains:
+                ch.accept(a.token)
+    finally:
+        S.use_native_sampler(True)
+
+
+def test_native_host_sampler_errors_and_snapshot():
+    from sllm_b200.engine import sampling as S
+    S.use_native_sampler(True)
+    cfg = S.SamplerChainConfig(params=S.SamplingParams(temperature=0.7, top_p=0.9), typical_p=0.8)
+    ch = S.SamplerChain(cfg, seed=5)
+    lg = np.zeros(64, dtype=np.float32)
+    lg[9] = np.nan
+    with pytest.raises(S.SamplingError, match="NaN logit at token 9"):
+        ch.select(lg)
+    with pytest.raises(S.SamplingError, match="empty distribution"):
+        ch.select(np.zeros(64, dtype=np.float32), valid_mask=np.zeros(64, dtype=bool))
+    # a restored snapshot continues the same stream through the native path
+    lg = np.random.default_rng(0).standard_normal(64).astype(np.float32)
+    first = [ch.select(lg).token for _ in range(3)]
+    blob = ch.snapshot()
+    nxt = [ch.select(lg).token for _ in range(4)]
+    ch2 = S.SamplerChain(cfg, seed=99)
+    ch2.restore(blob)
+    assert [ch2.select(lg).token for _ in range(4)] == nxt and len(first) == 3
