@@ -128,6 +128,135 @@ gdn_recurrent_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16*
   for (int i = 0; i < HD; i += 4) *reinterpret_cast<float4*>(srow + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
 }
 
+// ---------------------------------------------------------------- prompt form of the recurrence: three stages
+// The fused kernel above pays two block reductions and three barriers per token; on a prompt that is most of the
+// ~1.7 us a token costs.  Everything that does not depend on the state is the same for all tokens and runs in
+// parallel over them:
+//   gdn_pre_kernel    per (token, head): normalised q and k (fp32, already rounded and scaled), beta, decay
+//   gdn_scan_kernel   per (value head, sequence): the state update alone - thread d keeps row d of S in registers and
+//                     reads a chunk of tokens' q / k from shared memory; no reduction, one barrier per 16 tokens
+//   gdn_post_kernel   per (token, value head): RMSNorm over dv and the SiLU(z) gate
+// (the reference's column pipeline: native/hip/src/linear_attention_kernel.hip.cpp, pre / recurrent / post process).
+// Same arithmetic as the fused kernel except that the two dot products over dk are summed in four interleaved partial
+// sums instead of one chain.
+constexpr int kGdnChunk = 16;
+
+// grid (T, qk_heads + ceil(v_heads / 128)), 128 threads.  qn / kn: [T, qk_heads, 128] fp32; gates: [T, v_heads, 2].
+__global__ void __launch_bounds__(kGdnHeadDim)
+gdn_pre_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ b_in,
+               const __nv_bfloat16* __restrict__ a_in, const float* __restrict__ a_log,
+               const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ qn, float* __restrict__ kn,
+               float* __restrict__ gates, int qk_heads, int v_heads) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int HD = kGdnHeadDim;
+  const int r = blockIdx.x, d = threadIdx.x;
+  if (static_cast<int>(blockIdx.y) >= qk_heads) {
+    const int vh = (blockIdx.y - qk_heads) * HD + d;
+    if (vh < v_heads) {
+      const float bq = __bfloat162float(b_in[static_cast<size_t>(r) * v_heads + vh]);
+      const float av = __bfloat162float(a_in[static_cast<size_t>(r) * v_heads + vh]) + __bfloat162float(dt_bias[vh]);
+      gates[(static_cast<size_t>(r) * v_heads + vh) * 2] = bf16_round(1.f / (1.f + expf(-bq)));
+      gates[(static_cast<size_t>(r) * v_heads + vh) * 2 + 1] = expf(-expf(a_log[vh]) * softplus_f(av));
+    }
+    return;
+  }
+  const int qh = blockIdx.y;
+  const int width = (2 * qk_heads + v_heads) * HD;
+  __shared__ float red[2][4];
+  const size_t row = static_cast<size_t>(r) * width;
+  const float qv = __bfloat162float(qkv[row + qh * HD + d]);
+  const float kv = __bfloat162float(qkv[row + (qk_heads + qh) * HD + d]);
+  float qq = warp_sum(qv * qv), kk = warp_sum(kv * kv);
+  if ((d & 31) == 0) { red[0][d >> 5] = qq; red[1][d >> 5] = kk; }
+  __syncthreads();
+  qq = red[0][0] + red[0][1] + red[0][2] + red[0][3];
+  kk = red[1][0] + red[1][1] + red[1][2] + red[1][3];
+  const size_t o = (static_cast<size_t>(r) * qk_heads + qh) * HD + d;
+  qn[o] = bf16_round(qv * (1.f / sqrtf(qq + 1e-6f))) * (1.f / sqrtf(static_cast<float>(HD)));
+  kn[o] = bf16_round(kv * (1.f / sqrtf(kk + 1e-6f)));
+}
+
+// grid (v_heads, sequences), 128 threads.  o_raw: [T, v_heads * 128] fp32 = bf16-rounded S q.
+__global__ void __launch_bounds__(kGdnHeadDim)
+gdn_scan_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ qn, const float* __restrict__ kn,
+                const float* __restrict__ gates, float* __restrict__ state, float* __restrict__ o_raw,
+                const int* __restrict__ row_off, const int* __restrict__ slots, int qk_heads, int v_heads) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int HD = kGdnHeadDim;
+  const int vh = blockIdx.x, s = blockIdx.y, d = threadIdx.x;
+  const int qh = vh / (v_heads / qk_heads);
+  const int width = (2 * qk_heads + v_heads) * HD, ow = v_heads * HD;
+  const int r0 = row_off[s], r1 = row_off[s + 1];
+  if (r1 <= r0) return;
+  __shared__ __align__(16) float q_s[kGdnChunk][HD];
+  __shared__ __align__(16) float k_s[kGdnChunk][HD];
+  __shared__ float g_s[kGdnChunk][2];
+  float* srow = state + ((static_cast<size_t>(slots[s]) * v_heads + vh) * HD + d) * HD;
+  float S[HD];
+#pragma unroll
+  for (int i = 0; i < HD; i += 4) {
+    const float4 v4 = *reinterpret_cast<const float4*>(srow + i);
+    S[i] = v4.x; S[i + 1] = v4.y; S[i + 2] = v4.z; S[i + 3] = v4.w;
+  }
+  for (int c0 = r0; c0 < r1; c0 += kGdnChunk) {
+    const int cn = min(kGdnChunk, r1 - c0);
+    __syncthreads();                                       // the previous chunk has been consumed
+    for (int t = 0; t < cn; ++t) {
+      const size_t o = (static_cast<size_t>(c0 + t) * qk_heads + qh) * HD + d;
+      q_s[t][d] = qn[o];
+      k_s[t][d] = kn[o];
+    }
+    if (d < 2 * cn) g_s[d >> 1][d & 1] = gates[(static_cast<size_t>(c0 + (d >> 1)) * v_heads + vh) * 2 + (d & 1)];
+    __syncthreads();
+    for (int t = 0; t < cn; ++t) {
+      const int r = c0 + t;
+      const float vv = __bfloat162float(qkv[static_cast<size_t>(r) * width + (2 * qk_heads + vh) * HD + d]);
+      const float beta = g_s[t][0], decay = g_s[t][1];
+      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < HD; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&k_s[t][i]);
+        S[i] *= decay; S[i + 1] *= decay; S[i + 2] *= decay; S[i + 3] *= decay;
+        p0 += S[i] * k4.x; p1 += S[i + 1] * k4.y; p2 += S[i + 2] * k4.z; p3 += S[i + 3] * k4.w;
+      }
+      const float resid = beta * (vv - ((p0 + p1) + (p2 + p3)));
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < HD; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&k_s[t][i]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&q_s[t][i]);
+        S[i] += resid * k4.x; S[i + 1] += resid * k4.y; S[i + 2] += resid * k4.z; S[i + 3] += resid * k4.w;
+        o0 += S[i] * q4.x; o1 += S[i + 1] * q4.y; o2 += S[i + 2] * q4.z; o3 += S[i + 3] * q4.w;
+      }
+      o_raw[static_cast<size_t>(r) * ow + vh * HD + d] = bf16_round((o0 + o1) + (o2 + o3));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < HD; i += 4) *reinterpret_cast<float4*>(srow + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+}
+
+// grid (T, v_heads), 128 threads.
+__global__ void __launch_bounds__(kGdnHeadDim)
+gdn_post_kernel(const float* __restrict__ o_raw, const __nv_bfloat16* __restrict__ z, const float* __restrict__ norm_w,
+                __nv_bfloat16* __restrict__ out, int v_heads) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int HD = kGdnHeadDim;
+  const int r = blockIdx.x, vh = blockIdx.y, d = threadIdx.x;
+  __shared__ float red[4];
+  const size_t idx = static_cast<size_t>(r) * v_heads * HD + vh * HD + d;
+  const float o = o_raw[idx];
+  float oo = warp_sum(o * o);
+  if ((d & 31) == 0) red[d >> 5] = oo;
+  __syncthreads();
+  oo = red[0] + red[1] + red[2] + red[3];
+  const float inv = 1.f / sqrtf(oo / static_cast<float>(HD) + 1e-6f);
+  const float zv = __bfloat162float(z[idx]);
+  out[idx] = __float2bfloat16_rn(bf16_round(o * inv) * norm_w[d] * (zv / (1.f + expf(-zv))));
+}
+
 // In place per-head RMSNorm of the q and k heads inside a fused qkv activation (query/key normalisation of
 // the Qwen3 / Gemma families): x [T, ld], heads 0 .. hq + hkv - 1 of width hd each; weight_q / weight_k fp32-exact
 // bf16 [hd] (null: ones); offset_one: scale = 1 + w.  grid (T, heads), 128 threads; head0 = first head to touch;
@@ -184,6 +313,40 @@ SLLM_EXPORT int sllm_gdn_recurrent(const void* qkv, const void* z, const void* b
                                 static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(b),
                                 static_cast<const __nv_bfloat16*>(a), a_log, static_cast<const __nv_bfloat16*>(dt_bias), norm_w,
                                 state, static_cast<__nv_bfloat16*>(out), row_off, slots, qk_heads, v_heads);
+  return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
+}
+
+// The prompt form (three launches).  tokens = rows of qkv; scratch: fp32, at least
+// tokens * (2 * qk_heads * 128 + 2 * v_heads + v_heads * 128) elements.
+SLLM_EXPORT int sllm_gdn_recurrent_prompt(const void* qkv, const void* z, const void* b, const void* a, const float* a_log,
+                                          const void* dt_bias, const float* norm_w, float* state, void* out,
+                                          const int* row_off, const int* slots, int sequences, int tokens, int qk_heads,
+                                          int v_heads, int head_dim, float* scratch, long long scratch_floats, void* stream) {
+  if (!qkv || !z || !b || !a || !a_log || !dt_bias || !norm_w || !state || !out || !row_off || !slots || !scratch ||
+      sequences <= 0 || tokens <= 0 || qk_heads <= 0 || v_heads <= 0 || (v_heads % qk_heads))
+    return SLLM_ERR_INVALID_ARGUMENT;
+  if (head_dim != kGdnHeadDim) return SLLM_ERR_UNSUPPORTED_SHAPE;
+  const long long nq = static_cast<long long>(tokens) * qk_heads * kGdnHeadDim;
+  const long long ng = static_cast<long long>(tokens) * v_heads * 2;
+  const long long no = static_cast<long long>(tokens) * v_heads * kGdnHeadDim;
+  if (scratch_floats < 2 * nq + ng + no) return SLLM_ERR_WORKSPACE_TOO_SMALL;
+  float* qn = scratch;
+  float* kn = qn + nq;
+  float* gates = kn + nq;
+  float* o_raw = gates + ng;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int gate_blocks = (v_heads + kGdnHeadDim - 1) / kGdnHeadDim;
+  cudaError_t e = launch_kernel(gdn_pre_kernel, dim3(tokens, qk_heads + gate_blocks), dim3(kGdnHeadDim), 0, st, 1u,
+                                static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(b),
+                                static_cast<const __nv_bfloat16*>(a), a_log, static_cast<const __nv_bfloat16*>(dt_bias), qn, kn,
+                                gates, qk_heads, v_heads);
+  if (e != cudaSuccess) return SLLM_ERR_CUDA;
+  e = launch_kernel(gdn_scan_kernel, dim3(v_heads, sequences), dim3(kGdnHeadDim), 0, st, 1u,
+                    static_cast<const __nv_bfloat16*>(qkv), static_cast<const float*>(qn), static_cast<const float*>(kn),
+                    static_cast<const float*>(gates), state, o_raw, row_off, slots, qk_heads, v_heads);
+  if (e != cudaSuccess) return SLLM_ERR_CUDA;
+  e = launch_kernel(gdn_post_kernel, dim3(tokens, v_heads), dim3(kGdnHeadDim), 0, st, 1u, static_cast<const float*>(o_raw),
+                    static_cast<const __nv_bfloat16*>(z), norm_w, static_cast<__nv_bfloat16*>(out), v_heads);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 

@@ -17,6 +17,7 @@ P, I, F = C.c_void_p, C.c_int, C.c_float
 _SIGS = {
     "sllm_gdn_conv_silu": (I, [P, P, P, P, P, P, I, I, I, P]),
     "sllm_gdn_recurrent": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]),
+    "sllm_gdn_recurrent_prompt": (I, [P] * 11 + [I] * 5 + [P, C.c_longlong, P]),
     "sllm_qk_headnorm": (I, [P, I, I, I, I, I, P, P, F, I, P]),
     "sllm_qkv_headnorm": (I, [P, I, I, I, I, I, P, P, F, I, I, I, P]),
 }
@@ -57,6 +58,19 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, row_off: to
     return y
 
 
+PROMPT_FORM_MIN_ROWS_PER_SEQUENCE = 8
+_prompt_form = {"on": True}
+
+
+def prompt_form_enabled() -> bool:
+    return _prompt_form["on"]
+
+
+def set_prompt_form(on: bool) -> None:
+    """Whether flat batches that average 8 or more rows per sequence take the three-stage form of the recurrence."""
+    _prompt_form["on"] = bool(on)
+
+
 def recurrent(qkv, z, b, a, a_log, dt_bias, norm_w, state, row_off, slots, qk_heads: int, v_heads: int, hd: int = 128):
     """Gated delta rule over a flat batch; state [slots, v_heads, hd, hd] fp32 updated in place; returns [T, v_heads*hd]."""
     t = qkv.shape[0]
@@ -89,6 +103,16 @@ def recurrent(qkv, z, b, a, a_log, dt_bias, norm_w, state, row_off, slots, qk_he
         return out if qkv.dtype == torch.float32 else out.to(torch.bfloat16)
     from .core import _p, _stream
     out = torch.empty((t, v_heads * hd), dtype=torch.bfloat16, device=qkv.device)
+    if t >= PROMPT_FORM_MIN_ROWS_PER_SEQUENCE * slots.numel() and prompt_form_enabled():
+        # prompts: the state-independent work (q / k normalisation, gates, output norm) runs in parallel over the
+        # tokens, the scan itself carries no reduction (three launches; a decode step keeps the fused kernel)
+        n = t * (2 * qk_heads * hd + 2 * v_heads + v_heads * hd)
+        scratch = torch.empty((n,), dtype=torch.float32, device=qkv.device)
+        rc = _k().sllm_gdn_recurrent_prompt(_p(qkv), _p(z), _p(b), _p(a), _p(a_log), _p(dt_bias), _p(norm_w), _p(state), _p(out),
+                                            _p(row_off), _p(slots), slots.numel(), t, qk_heads, v_heads, hd, _p(scratch), n,
+                                            _stream())
+        _lib.check(rc, "gdn_recurrent_prompt")
+        return out
     rc = _k().sllm_gdn_recurrent(_p(qkv), _p(z), _p(b), _p(a), _p(a_log), _p(dt_bias), _p(norm_w), _p(state), _p(out),
                                  _p(row_off), _p(slots), slots.numel(), qk_heads, v_heads, hd, _stream())
     _lib.check(rc, "gdn_recurrent")

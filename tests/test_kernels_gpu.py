@@ -750,6 +750,45 @@ def test_w4a4_llama_gpu_matches_cpu(fmt):
 
 
 @pytest.mark.gpu
+def test_gdn_prompt_form_matches_the_fused_kernel_and_the_oracle():
+    """Flat batches that average 8 or more rows per sequence take the three-stage form of the recurrence (parallel
+    pre- and post-processing, a scan without reductions): same outputs and states as the fused kernel up to the order
+    of the dot-product sums, and as the CPU oracle."""
+    from sllm_b200.ops import gdn
+    torch.manual_seed(11)
+    qk_heads, v_heads, hd = 2, 4, 128
+    width = (2 * qk_heads + v_heads) * hd
+    for counts in ([40, 3, 17, 33], [20, 9]):
+        t = sum(counts)
+        offs = [0]
+        for c in counts:
+            offs.append(offs[-1] + c)
+        row_off = torch.tensor(offs, dtype=torch.int32)
+        slots = torch.tensor(list(range(len(counts)))[::-1], dtype=torch.int32)
+        qkv = (torch.randn(t, width) * 0.5).bfloat16()
+        z = torch.randn(t, v_heads * hd).bfloat16()
+        b, a = torch.randn(t, v_heads).bfloat16(), torch.randn(t, v_heads).bfloat16()
+        a_log, dt_bias = torch.randn(v_heads) * 0.5, (torch.randn(v_heads) * 0.5).bfloat16()
+        norm_w = 1.0 + torch.randn(hd) * 0.05
+        st0 = torch.randn(len(counts), v_heads, hd, hd) * 0.1
+        dev = lambda x: x.to(DEV)
+        outs, states = [], []
+        for prompt_form in (True, False):
+            gdn.set_prompt_form(prompt_form)
+            st = st0.clone().to(DEV)
+            outs.append(gdn.recurrent(dev(qkv), dev(z), dev(b), dev(a), dev(a_log), dev(dt_bias), dev(norm_w), st, dev(row_off),
+                                      dev(slots), qk_heads, v_heads, hd).float().cpu())
+            states.append(st.cpu())
+        gdn.set_prompt_form(True)
+        assert rel_err(outs[0], outs[1]) < 5e-3 and rel_err(states[0], states[1]) < 1e-4
+        if t < 40:
+            stc = st0.clone()
+            want = gdn.recurrent(qkv, z, b, a, a_log, dt_bias, norm_w, stc, row_off, slots, qk_heads, v_heads, hd).float()
+            assert rel_err(outs[0], want) < 2e-2 and rel_err(states[0], stc) < 1e-3
+    assert ops.device_status(torch.device(DEV)) == 0
+
+
+@pytest.mark.gpu
 def test_gdn_kernels_match_oracle():
     from sllm_b200.ops import gdn
     torch.manual_seed(3)
