@@ -220,7 +220,7 @@ class LlamaModel:
         matrix on the W4A4 path - 4-bit codes, the norm computed inside the quantiser."""
         cfg = self.cfg
         if (consumer.kind == "w4" and _w4.w4a4_enabled() and h.dtype == torch.bfloat16 and norm_w.dtype == torch.bfloat16
-                and h.shape[1] % 8 == 0):
+                and h.shape[1] % 8 == 0 and h.shape[0] <= _w4.W4A4_MAX_DENSE_ROWS):
             q = _w4.act_quant_fp4(h, consumer.w4.fmt, norm=(norm_w, cfg.rms_eps, cfg.norm_offset_one))
             return _w4.Fp4Act(*q, k=h.shape[1], fmt=consumer.w4.fmt)
         return ops.rmsnorm(h, norm_w, cfg.rms_eps, cfg.norm_offset_one, quant=quant_fp8)
@@ -261,7 +261,8 @@ class LlamaModel:
                 h = self.tp.row_linear(a, lw.o, h)
             x = self._norm_in(h, lw.mlp_norm, lw.gate_up, q_mlp)
             gu = ops.linear(x, lw.gate_up)
-            if lw.down.kind == "w4" and _w4.w4a4_enabled() and gu.dtype == torch.bfloat16:
+            if (lw.down.kind == "w4" and _w4.w4a4_enabled() and gu.dtype == torch.bfloat16
+                    and gu.shape[0] <= _w4.W4A4_MAX_DENSE_ROWS):
                 # 4-bit activations: SiLU*up runs inside the quantiser of the down projection
                 wd = lw.down.w4
                 act = _w4.Fp4Act(*_w4.act_quant_fp4(gu, wd.fmt, gated=cfg.act), k=gu.shape[1] // 2, fmt=wd.fmt)

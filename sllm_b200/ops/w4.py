@@ -256,7 +256,7 @@ def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = N
     if k != w.k:
         raise ValueError("input width does not match the weight")
     if _lib.on_cpu(x):
-        if w4a4_enabled() and x.dtype == torch.bfloat16 and k % 8 == 0:
+        if w4a4_enabled() and x.dtype == torch.bfloat16 and k % 8 == 0 and (tok_off is not None or t <= W4A4_MAX_DENSE_ROWS):
             return linear_w4a4(x, w, residual, tok_off, tok_scale, max_group_tokens, 0, row_ptr)
         out = torch.zeros((t, w.n), dtype=torch.float32)
         offs = [0, t] if tok_off is None else tok_off.tolist()
@@ -270,7 +270,9 @@ def linear_w4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = N
         if residual is not None:
             out = out + residual.float()
         return out if x.dtype == torch.float32 else out.to(torch.bfloat16)
-    if w4a4_enabled() and x.dtype == torch.bfloat16 and k % 8 == 0:
+    # 4-bit activations serve the decode regime (few rows per weight tile); a prompt's rows are compute bound and keep
+    # bf16 activations on the W4A16 kernel
+    if w4a4_enabled() and x.dtype == torch.bfloat16 and k % 8 == 0 and (tok_off is not None or t <= W4A4_MAX_DENSE_ROWS):
         return linear_w4a4(x, w, residual, tok_off, tok_scale, max_group_tokens, 0, row_ptr)
     from .core import _p, _stream, workspace
     P, I, L, F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
@@ -383,12 +385,17 @@ def sf_compact(xsf: torch.Tensor) -> torch.Tensor:
     return xsf.view(t, n // 8, 8)[:, :, :4].reshape(t, n // 2)
 
 
+W4A4_MAX_DENSE_ROWS = 32
+
+
 def linear_w4a4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] = None, tok_off: Optional[torch.Tensor] = None,
                 tok_scale: Optional[torch.Tensor] = None, max_group_tokens: Optional[int] = None, splits: int = 0,
-                row_ptr: Optional[torch.Tensor] = None, quantized=None) -> Optional[torch.Tensor]:
+                row_ptr: Optional[torch.Tensor] = None, quantized=None, bn: Optional[int] = None) -> Optional[torch.Tensor]:
     """`linear_w4` with the activations quantised to the weights' 4-bit format first (or passed as `quantized` =
     (codes, block scales, row scales) from `act_quant_fp4`).  The tensor core multiplies E2M1 by E2M1 and applies both
-    block scales; the row and tensor scales are applied to the fp32 sums."""
+    block scales; the row and tensor scales are applied to the fp32 sums.  Token tiles are 16 or 32 rows wide (the
+    weights of a row tile are streamed once per token tile: the decode and routed-expert regime); `bn` = 64 / 128
+    selects the wide tiles, whose K range per CTA is bounded (split-K through the workspace)."""
     t, k = x.shape if quantized is None else (quantized[0].shape[0], w.k)
     if k != w.k:
         raise ValueError("input width does not match the weight")
@@ -417,7 +424,8 @@ def linear_w4a4(x: torch.Tensor, w: W4Weight, residual: Optional[torch.Tensor] =
     tiles = w.native_tiles()
     kb = tiles.shape[2]
     mgt = max_group_tokens or t
-    bn = _bn_for(mgt if tok_off is None else min(mgt, 32))
+    if bn is None:
+        bn = _bn_for(min(mgt, 32))
     min_splits = (kb + 7) // 8 if bn > 32 else 1
     if splits <= 0:
         ctas = (w.n_rows // 128) * (w.groups if tok_off is None else max(1, min(w.groups, t))) * ((min(mgt, t) + bn - 1) // bn)

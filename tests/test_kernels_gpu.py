@@ -733,7 +733,7 @@ def test_w4a4_llama_gpu_matches_cpu(fmt):
                          weight_format=fmt, kv_format="bf16", max_context=256)
     g = build_engine(cfg, DEV, seed=3, num_pages=64, max_batch=4)
     c = _cpu_twin(g, cfg)
-    prompts = [list(range(3, 40)), [9, 8, 7, 6]]
+    prompts = [list(range(3, 20)), [9, 8, 7, 6]]           # 21 rows: a decode-size batch, which takes the 4-bit path
     base = g.prefill([g.new_sequence(p) for p in prompts], sample=False).float().cpu()
     W.set_w4a4(True)
     try:
@@ -742,6 +742,16 @@ def test_w4a4_llama_gpu_matches_cpu(fmt):
         lc = c.prefill([c.new_sequence(p) for p in prompts], sample=False).float()
         out = g2.generate(prompts, 8)                      # graph-captured decode on the 4-bit path
         assert out == g2.generate(prompts, 8) and all(len(o) == 8 for o in out)
+        # the rows of a prompt of more than 32 tokens keep bf16 activations (W4A16 kernel); only the single logit row
+        # of the output matrix is a decode-size batch
+        from sllm_b200.ops import _lib
+        _lib.audit(True)
+        _lib.dispatch_records(clear=True)
+        g2.prefill([g2.new_sequence(list(range(3, 60)))], sample=False)
+        recs = _lib.dispatch_records(clear=True)
+        _lib.audit(False)
+        assert {r["tokens"] for r in recs if r["op"] == "linear_w4a4"} == {1}
+        assert {r["tokens"] for r in recs if r["op"] == "linear_w4"} == {57}
     finally:
         W.set_w4a4(False)
     assert rel_err(lg, lc) < 6e-2                          # quantisation decisions flip on bf16-level differences

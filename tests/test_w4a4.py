@@ -162,6 +162,11 @@ def test_gemm_fp4_against_fp32_of_the_same_operands(fmt, t, n, k, groups, splits
     y = linear_w4a4(x, w, residual=res, tok_off=tok_off, tok_scale=ts, max_group_tokens=mg, splits=splits, quantized=q)
     want = _oracle(q, w, t, tok_off, ts, res)
     assert rel(y.float().cpu(), want) < 4e-3
+    if t > 32:
+        # the wide token tiles (scales staged through shared memory, K split through the workspace)
+        for bn in (64, 128):
+            yw = linear_w4a4(x, w, residual=res, tok_off=tok_off, tok_scale=ts, max_group_tokens=mg, quantized=q, bn=bn)
+            assert rel(yw.float().cpu(), want) < 4e-3
     # the whole path (quantise + multiply) stays within the 4-bit activation error of the bf16-activation kernel
     if groups == 1:
         a16 = linear_w4(x, w, residual=res).float().cpu()
@@ -226,13 +231,15 @@ def test_gated_quantiser_and_expert_mlp_gpu(fmt):
         # a scatter-free combine of both gives the layer output; rows past the routed ones are not compared
         n = t * k
         assert rel(got[:n].float().cpu(), want[:n].float()) < 0.05
-        # dense form through the switch
+        # dense form through the switch: decode-size batches take the 4-bit path, prompt-size ones keep bf16 activations
         w = W4Weight.quantize(fmt, torch.randn(192, d) * 0.1, DEV, keep_file=False)
-        y4 = linear_w4(x.to(DEV), w)
+        y4 = linear_w4(x[:32].to(DEV), w)
+        y4_prompt = linear_w4(x.to(DEV), w)
     finally:
         W.set_w4a4(False)
     y16 = linear_w4(x.to(DEV), w)
-    assert 0.02 < rel(y4.float(), y16.float()) < 0.16
+    assert 0.02 < rel(y4.float(), y16[:32].float()) < 0.16
+    assert torch.equal(y4_prompt, y16)
     assert ops.device_status(torch.device(DEV)) == 0
 
 
