@@ -517,13 +517,17 @@ __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16*
 #pragma unroll
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
     outer_s = amax > 0.f ? __fdiv_rn(amax, 2688.f) : 1.f;
-    if (threadIdx.x == 0) outer[t] = outer_s;
-  } else if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) outer[t] = outer_s;
+  } else if (threadIdx.x == 0 && blockIdx.y == 0) {
     outer[t] = 1.f;
   }
   pdl_trigger();
+  // the row's blocks are shared out over gridDim.y CTAs (each of them has computed the row's statistics itself: the
+  // row sits in L2, and a launch of a few token rows would otherwise occupy a few SMs for tens of microseconds)
   const int blocks = k_pad / kBlock;
-  for (int b = threadIdx.x; b < blocks; b += 256) {
+  const int per_cta = (blocks + gridDim.y - 1) / gridDim.y;
+  const int b_end = min(blocks, static_cast<int>(blockIdx.y + 1) * per_cta);
+  for (int b = blockIdx.y * per_cta + threadIdx.x; b < b_end; b += 256) {
     float v[kBlock];
     float bamax = 0.f;
 #pragma unroll
@@ -590,12 +594,18 @@ SLLM_EXPORT int sllm_act_quant_fp4(const void* x, int ldx, int tokens, int k, in
   if (sf_ld < 2 * k_pad / (fmt ? 16 : 32) || (sf_ld % 16)) return SLLM_ERR_INVALID_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
+  // enough CTAs for two per SM, at least 256 blocks (one per thread) each
+  const int blocks = k_pad / (fmt ? 16 : 32);
+  int chunks = (296 + tokens - 1) / tokens;
+  if (chunks > (blocks + 255) / 256) chunks = (blocks + 255) / 256;
+  if (chunks < 1) chunks = 1;
+  const dim3 qgrid(tokens, chunks);
   if (fmt)
-    e = launch_kernel(act_quant_fp4_kernel<16>, dim3(tokens), dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
+    e = launch_kernel(act_quant_fp4_kernel<16>, qgrid, dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
                       k, k_pad, src_row, n_rows_ptr, gated, nw, eps, offset_one, static_cast<uint8_t*>(xq),
                       static_cast<uint8_t*>(xsf), sf_ld, outer);
   else
-    e = launch_kernel(act_quant_fp4_kernel<32>, dim3(tokens), dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
+    e = launch_kernel(act_quant_fp4_kernel<32>, qgrid, dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
                       k, k_pad, src_row, n_rows_ptr, gated, nw, eps, offset_one, static_cast<uint8_t*>(xq),
                       static_cast<uint8_t*>(xsf), sf_ld, outer);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
