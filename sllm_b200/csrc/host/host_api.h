@@ -83,3 +83,4 @@ SLLM_HOST_EXPORT int sllm_host_sample(const float* logits, int vocab, const unsi
                                       const SllmSamplerConfig* cfg, SllmSamplerState* state, const int* history,
                                       int n_history, const int* count_tokens, const int* count_values, int n_counts,
                                       int* token, double* logprob, int* top_ids, double* top_logprobs, int* n_top);
+SLLM_HOST_EXPORT int sllm_host_sampler_abi(int* out, int cap);

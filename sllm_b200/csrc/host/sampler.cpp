@@ -13,6 +13,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstddef>
 #include <cstdint>
 #include <limits>
 #include <unordered_map>
@@ -388,4 +389,24 @@ SLLM_HOST_EXPORT int sllm_host_sample(const float* logits, int vocab, const unsi
   int i = search_cumsum(prob, thr, true);
   i = std::min<int>(i, static_cast<int>(cid.size()) - 1);
   return finish(cid[i]);
+}
+
+// Layout of the two structs the Python bindings mirror by hand: sizes and the offsets of fields spread over the struct.
+SLLM_HOST_EXPORT int sllm_host_sampler_abi(int* out, int cap) {
+  const int v[] = {static_cast<int>(sizeof(SllmSamplerConfig)),
+                   static_cast<int>(offsetof(SllmSamplerConfig, repeat_penalty)),
+                   static_cast<int>(offsetof(SllmSamplerConfig, mirostat_eta)),
+                   static_cast<int>(offsetof(SllmSamplerConfig, bias_tokens)),
+                   static_cast<int>(offsetof(SllmSamplerConfig, dry_breakers)),
+                   static_cast<int>(offsetof(SllmSamplerConfig, n_bias)),
+                   static_cast<int>(offsetof(SllmSamplerConfig, ignore_eos_token)),
+                   static_cast<int>(offsetof(SllmSamplerConfig, mirostat)),
+                   static_cast<int>(offsetof(SllmSamplerConfig, top_logprobs)),
+                   static_cast<int>(sizeof(SllmSamplerState)),
+                   static_cast<int>(offsetof(SllmSamplerState, draws)),
+                   static_cast<int>(offsetof(SllmSamplerState, mu))};
+  const int n = static_cast<int>(sizeof(v) / sizeof(v[0]));
+  if (!out || cap < n) return -SLLM_HOST_INVALID;
+  for (int i = 0; i < n; ++i) out[i] = v[i];
+  return n;
 }

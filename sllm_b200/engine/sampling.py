@@ -289,6 +289,17 @@ def _native_lib():
                                          C.POINTER(_NativeState), C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int),
                                          C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_double),
                                          C.POINTER(C.c_int), C.POINTER(C.c_double), C.POINTER(C.c_int)]
+        # the hand-written mirrors above must have the layout the library was compiled with
+        lib.sllm_host_sampler_abi.restype = C.c_int
+        lib.sllm_host_sampler_abi.argtypes = [C.POINTER(C.c_int), C.c_int]
+        buf = (C.c_int * 16)()
+        n = lib.sllm_host_sampler_abi(buf, 16)
+        k, s_ = _NativeConfig, _NativeState
+        mine = [C.sizeof(k), k.repeat_penalty.offset, k.mirostat_eta.offset, k.bias_tokens.offset, k.dry_breakers.offset,
+                k.n_bias.offset, k.ignore_eos_token.offset, k.mirostat.offset, k.top_logprobs.offset, C.sizeof(s_),
+                s_.draws.offset, s_.mu.offset]
+        if n != len(mine) or list(buf[:n]) != mine:
+            raise SamplingError(f"host sampler struct layout mismatch: library {list(buf[:max(n, 0)])}, bindings {mine}")
         _native["lib"] = lib
     return _native["lib"]
 

@@ -29,3 +29,23 @@ def test_a_drifted_mirror_is_refused(monkeypatch):
     with pytest.raises(_lib.KernelError):
         tp.check_comm_abi()
     tp._abi_ok = False
+
+
+def test_host_sampler_struct_layouts(monkeypatch):
+    """The sampler configuration / state mirrors are checked against the host library when it is first bound; a mirror
+    with two fields swapped is refused."""
+    import ctypes as C
+    from sllm_b200.engine import sampling as S
+    S._native["lib"] = None
+    assert S._native_lib() is not None
+
+    class Drifted(C.Structure):
+        _fields_ = [("draws", C.c_longlong), ("rng_state", C.c_uint64), ("mu", C.c_double)]
+
+    monkeypatch.setattr(S, "_NativeState", Drifted)
+    S._native["lib"] = None
+    with pytest.raises(S.SamplingError, match="layout mismatch"):
+        S._native_lib()
+    monkeypatch.undo()
+    S._native["lib"] = None
+    assert S._native_lib() is not None
