@@ -79,6 +79,8 @@ struct __align__(16) F4Barriers {
   uint32_t tmem_base;
   int abort_flag;
   int is_last;
+  float tok_mult[128];        // per token of the tile: weight-tensor scale x activation-row scale x routing weight
+  long long tok_ptr[128];     // per token: destination row address of the scatter epilogue
 };
 
 __device__ __forceinline__ void f4_bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -300,24 +302,47 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
 
     bool ok = true;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const int out_row = row_tile * kF4Rows + r;
+    const bool row_ok = out_row < p.n_valid;
+    // Everything the epilogue reads from memory is fetched while the main loop runs: a load per token inside the
+    // store loop costs a memory latency per token (32 dependent residual loads were a third of the o-projection).
+    if (e < BN) {
+      float m = 0.f;
+      long long ptr = 0;
+      if (e < count) {
+        const int tok = t_begin + e;
+        m = p.tensor_scale ? p.tensor_scale[g] : 1.f;
+        if (p.x_outer) m *= p.x_outer[tok];
+        if (p.tok_scale) m *= p.tok_scale[tok];
+        if (p.row_ptr) ptr = p.row_ptr[tok];
+      }
+      bars->tok_mult[e] = m;
+      bars->tok_ptr[e] = ptr;
+    }
+    constexpr int kResRegs = BN <= 32 ? BN : 1;
+    float res[kResRegs];
+    const bool res_ready = BN <= 32 && p.residual != nullptr && p.splits == 1;
+    if (res_ready) {
+#pragma unroll
+      for (int c = 0; c < kResRegs; ++c)
+        res[c] = (row_ok && c < count) ? __bfloat162float(p.residual[static_cast<size_t>(t_begin + c) * p.ldy + out_row]) : 0.f;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
     if (nk > 0) {
       ok = mbar_wait(&bars->acc_full, 0, abort_flag, p.status, SLLM_DEV_TIMEOUT_TMEM_FULL);
       if (ok) tc_fence_after();
     }
-    const int out_row = row_tile * kF4Rows + r;
-    const bool row_ok = out_row < p.n_valid;
-    const float ts = p.tensor_scale ? p.tensor_scale[g] : 1.f;
-    auto finalize = [&](int c, float a) {
+    auto finalize = [&](int c, float a, float resid) {
       const int tok = t_begin + c;
-      float v = a * ts;
-      if (p.x_outer) v *= p.x_outer[tok];
-      if (p.tok_scale) v *= p.tok_scale[tok];
-      if (p.residual) v += __bfloat162float(p.residual[static_cast<size_t>(tok) * p.ldy + out_row]);
-      __nv_bfloat16* dst = p.row_ptr ? reinterpret_cast<__nv_bfloat16*>(p.row_ptr[tok]) + out_row
+      const float v = a * bars->tok_mult[c] + resid;
+      __nv_bfloat16* dst = p.row_ptr ? reinterpret_cast<__nv_bfloat16*>(bars->tok_ptr[c]) + out_row
                                      : p.y + static_cast<size_t>(tok) * p.ldy + out_row;
       *dst = __float2bfloat16_rn(v);
     };
-#pragma unroll 1
+    auto resid_at = [&](int c) {
+      return p.residual ? __bfloat162float(p.residual[static_cast<size_t>(t_begin + c) * p.ldy + out_row]) : 0.f;
+    };
+#pragma unroll
     for (int cb = 0; cb < BN / 16; ++cb) {
       if (cb * 16 >= count) break;
       float v[16];
@@ -342,7 +367,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             if (p.splits > 1)
               p.ws[(static_cast<size_t>(split) * p.total_tokens + t_begin + c) * p.n_valid + out_row] = v[j];
             else
-              finalize(c, v[j]);
+              finalize(c, v[j], res_ready ? res[c < kResRegs ? c : 0] : resid_at(c));
           }
         }
       }
@@ -373,7 +398,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-              if (cq + u < count) finalize(cq + u, sum[u]);
+              if (cq + u < count) finalize(cq + u, sum[u], resid_at(cq + u));
           }
         }
       }
@@ -466,6 +491,38 @@ __device__ __forceinline__ void f4_load8(const __nv_bfloat16* row, int i, int k,
   }
 }
 
+__device__ __forceinline__ void f4_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void f4_st_peer(float* local_ptr, uint32_t cta_rank, float v) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local_ptr)), "r"(cta_rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
+}
+
+// Block reduction (sum or max) of `v`, then the same over the CTAs of the row's cluster: every CTA stores its partial
+// into slot `rank` of every peer's exchange array and reads all slots after the cluster barrier (in rank order, so
+// the result is the same in every CTA and from run to run).
+template <bool kMax>
+__device__ __forceinline__ float f4_row_reduce(float v, float* red, float* xch, int rank, int nctas) {
+  v = kMax ? warp_max(v) : warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) t = kMax ? fmaxf(t, red[w]) : t + red[w];
+  __syncthreads();                                     // red is reused by the next reduction
+  if (nctas == 1) return t;
+  if (threadIdx.x < nctas) f4_st_peer(&xch[rank], threadIdx.x, t);
+  f4_cluster_sync();
+  float r = xch[0];
+  for (int c = 1; c < nctas; ++c) r = kMax ? fmaxf(r, xch[c]) : r + xch[c];
+  return r;
+}
+
+// grid (tokens, 1, chunks) with the chunks of a row forming one thread-block cluster: every CTA quantises its share of
+// the row's blocks, and the row's statistics (sum of squares for the norm, maximum for the NVFP4 row scale) are reduced
+// over the cluster instead of being recomputed by every CTA.
 template <int kBlock>
 __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int k, int k_pad,
                                                             const int* __restrict__ src_row, const int* __restrict__ n_rows_ptr,
@@ -473,14 +530,22 @@ __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16*
                                                             int offset_one, uint8_t* __restrict__ xq,
                                                             uint8_t* __restrict__ xsf, int sf_ld, float* __restrict__ outer) {
   __shared__ float red[8];
+  __shared__ float xch[2][8];
   pdl_wait();
   const int t = blockIdx.x;
-  if (n_rows_ptr && t >= *n_rows_ptr) return;        // rows past the routed ones: their source index is not defined
+  const int rank = blockIdx.z, nctas = gridDim.z;
+  // rows past the routed ones: their source index is not defined.  (Uniform over the row's cluster: no CTA is left
+  // waiting at a cluster barrier.)
+  if (n_rows_ptr && t >= *n_rows_ptr) return;
   const __nv_bfloat16* row = x + static_cast<size_t>(src_row ? src_row[t] : t) * ldx;
+  const int blocks = k_pad / kBlock;
+  const int per_cta = (blocks + nctas - 1) / nctas;
+  const int b_begin = rank * per_cta, b_end = min(blocks, (rank + 1) * per_cta);
+  const int e_begin = b_begin * kBlock, e_end = min(k, b_end * kBlock);     // this CTA's share of the row's elements
   float inv = 1.f;
   if (norm_w) {
     float ss = 0.f;
-    for (int i = threadIdx.x * 8; i < k; i += 256 * 8) {
+    for (int i = e_begin + threadIdx.x * 8; i < e_end; i += 256 * 8) {
       const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
       const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll
@@ -489,19 +554,12 @@ __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16*
         ss += f * f;
       }
     }
-    ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) tot += red[w];
-    inv = rsqrtf(tot / k + eps);
-    __syncthreads();                                   // red is reused below
+    inv = rsqrtf(f4_row_reduce<false>(ss, red, xch[0], rank, nctas) / k + eps);
   }
   float outer_s = 1.f;
   if (kBlock == 16) {
     float amax = 0.f;
-    for (int i = threadIdx.x * 8; i < k; i += 256 * 8) {
+    for (int i = e_begin + threadIdx.x * 8; i < e_end; i += 256 * 8) {
       float v[8];
       f4_load8(row, i, k, gated, norm_w, inv, offset_one, v);
 #pragma unroll
@@ -510,24 +568,14 @@ __global__ void __launch_bounds__(256) act_quant_fp4_kernel(const __nv_bfloat16*
         if (a == a && a <= 3.0e38f) amax = fmaxf(amax, a);
       }
     }
-    amax = warp_max(amax);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    amax = red[0];
-#pragma unroll
-    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+    amax = f4_row_reduce<true>(amax, red, xch[1], rank, nctas);
     outer_s = amax > 0.f ? __fdiv_rn(amax, 2688.f) : 1.f;
-    if (threadIdx.x == 0 && blockIdx.y == 0) outer[t] = outer_s;
-  } else if (threadIdx.x == 0 && blockIdx.y == 0) {
+    if (threadIdx.x == 0 && rank == 0) outer[t] = outer_s;
+  } else if (threadIdx.x == 0 && rank == 0) {
     outer[t] = 1.f;
   }
   pdl_trigger();
-  // the row's blocks are shared out over gridDim.y CTAs (each of them has computed the row's statistics itself: the
-  // row sits in L2, and a launch of a few token rows would otherwise occupy a few SMs for tens of microseconds)
-  const int blocks = k_pad / kBlock;
-  const int per_cta = (blocks + gridDim.y - 1) / gridDim.y;
-  const int b_end = min(blocks, static_cast<int>(blockIdx.y + 1) * per_cta);
-  for (int b = blockIdx.y * per_cta + threadIdx.x; b < b_end; b += 256) {
+  for (int b = b_begin + threadIdx.x; b < b_end; b += 256) {
     float v[kBlock];
     float bamax = 0.f;
 #pragma unroll
@@ -594,18 +642,20 @@ SLLM_EXPORT int sllm_act_quant_fp4(const void* x, int ldx, int tokens, int k, in
   if (sf_ld < 2 * k_pad / (fmt ? 16 : 32) || (sf_ld % 16)) return SLLM_ERR_INVALID_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  // enough CTAs for two per SM, at least 256 blocks (one per thread) each
+  // a row's blocks are shared out over a cluster of 1, 2, 4 or 8 CTAs: enough CTAs for two per SM, at least 256
+  // blocks (one per thread) each (a launch of a few token rows would otherwise keep a few SMs busy for tens of
+  // microseconds)
   const int blocks = k_pad / (fmt ? 16 : 32);
-  int chunks = (296 + tokens - 1) / tokens;
-  if (chunks > (blocks + 255) / 256) chunks = (blocks + 255) / 256;
-  if (chunks < 1) chunks = 1;
-  const dim3 qgrid(tokens, chunks);
+  int chunks = 1;
+  while (chunks < 8 && tokens * chunks < 296 && blocks >= 256 * chunks * 2) chunks *= 2;
+  const dim3 qgrid(tokens, 1, chunks);
+  const unsigned cz = static_cast<unsigned>(chunks);
   if (fmt)
-    e = launch_kernel(act_quant_fp4_kernel<16>, qgrid, dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
+    e = launch_kernel(act_quant_fp4_kernel<16>, qgrid, dim3(256), 0, st, cz, static_cast<const __nv_bfloat16*>(x), ldx,
                       k, k_pad, src_row, n_rows_ptr, gated, nw, eps, offset_one, static_cast<uint8_t*>(xq),
                       static_cast<uint8_t*>(xsf), sf_ld, outer);
   else
-    e = launch_kernel(act_quant_fp4_kernel<32>, qgrid, dim3(256), 0, st, 1u, static_cast<const __nv_bfloat16*>(x), ldx,
+    e = launch_kernel(act_quant_fp4_kernel<32>, qgrid, dim3(256), 0, st, cz, static_cast<const __nv_bfloat16*>(x), ldx,
                       k, k_pad, src_row, n_rows_ptr, gated, nw, eps, offset_one, static_cast<uint8_t*>(xq),
                       static_cast<uint8_t*>(xsf), sf_ld, outer);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
