@@ -139,7 +139,9 @@ def expert_mlp(x: torch.Tensor, tok_off: torch.Tensor, perm_src: torch.Tensor, p
     from . import core
     from . import w4 as W
     t = x.shape[0]
-    if W.w4a4_enabled() and x.dtype == torch.bfloat16:
+    # 4-bit activations serve the decode regime; with more than 32 routed rows per expert on average (a prompt) the
+    # rows are compute bound and keep bf16 activations on the W4A16 kernel, whose token tiles are 128 wide
+    if W.w4a4_enabled() and x.dtype == torch.bfloat16 and perm_src.numel() <= W.W4A4_MAX_DENSE_ROWS * gate_up.groups:
         rows = perm_src.numel()
         n_rows = tok_off[-1:] if x.is_cuda else None
         if not x.is_cuda:
