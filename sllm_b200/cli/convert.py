@@ -167,7 +167,10 @@ def _load_hf_qwen35(cache, cfg):
             raise CliError(f"{name}: shape {tuple(t.shape)} differs from the expected {tuple(shape)}")
         return t.to(dtype) if dtype is not None else t
 
-    lin = lambda w: LinearWeight("dense", w.contiguous())
+    dense = lambda w: LinearWeight("dense", w.contiguous())
+    # --weight-format fp8: projections are quantised to E4M3 with one fp32 scale per 1 x 128 block (the reference's FP8
+    # plan takes them from a sidecar instead: gguf_convert.rs:253-329); the router stays bf16
+    lin = (lambda w: LinearWeight.from_dense(w.float().contiguous(), "fp8")) if cfg.weight_format == "fp8" else dense
     d, hd, hq, hkv = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
     ghd, vh, qh = cfg.gdn_head_dim, cfg.gdn_heads, cfg.gdn_qk_heads
     width = (2 * qh + vh) * ghd
@@ -198,7 +201,7 @@ def _load_hf_qwen35(cache, cfg):
                     shared_gate_up=lin(torch.cat([get(p + "mlp.shared_expert.gate_proj.weight", shape=(fs, d)),
                                                   get(p + "mlp.shared_expert.up_proj.weight", shape=(fs, d))], dim=0)),
                     shared_down=lin(get(p + "mlp.shared_expert.down_proj.weight", shape=(d, fs))))
-            common.update(router=lin(router), exp_gate_up=experts(p, ("gate_proj", "up_proj"), F, d),
+            common.update(router=dense(router), exp_gate_up=experts(p, ("gate_proj", "up_proj"), F, d),
                           exp_down=experts(p, ("down_proj",), d, F))
         else:
             f = cfg.ffn
@@ -236,7 +239,8 @@ def _load_hf_qwen35(cache, cfg):
     leftover = [k for k in tensors if k not in unconsumed and not k.endswith("rotary_emb.inv_freq")]
     if leftover:
         raise CliError(f"unconsumed tensors in the checkpoint (unknown policy is reject): {leftover[:4]}")
-    return Qwen35Weights(embed, layers, final, LinearWeight("dense", head), 0), unconsumed
+    head_w = LinearWeight("dense", head) if cfg.tie_embeddings else lin(head)
+    return Qwen35Weights(embed, layers, final, head_w, 0), unconsumed
 
 
 def _write_lock(path: str, doc: dict) -> None:
@@ -294,8 +298,10 @@ def main(argv=None) -> int:
                 raise CliError(f"--artifact must be one of {sorted(named)}")
             cfg = named[a.artifact]()
             if cfg.family in ("moe", "qwen35"):
-                if a.weight_format not in ("bf16", "fp32"):
-                    raise CliError("the mixture-of-experts and hybrid families keep bf16 attention (experts are MXFP4)")
+                ok = ("bf16", "fp32", "fp8") if cfg.family == "qwen35" else ("bf16", "fp32")
+                if a.weight_format not in ok:
+                    raise CliError("the mixture-of-experts family keeps bf16 attention (experts are MXFP4); the hybrid "
+                                   "family takes bf16, fp32 or fp8 projections")
                 if a.with_vision or a.with_mtp:
                     raise CliError("--with-vision / --with-mtp apply to the dense decoder family")
             cfg.weight_format = a.weight_format
@@ -321,9 +327,11 @@ def main(argv=None) -> int:
                 cfg = _hf_config(text, "mixed-fp8-nvfp4")
                 cfg.kv_format, cfg.tie_embeddings = "fp8-static", True
             elif a.kind == "hf-qwen35":
-                if a.weight_format != "bf16":
-                    raise CliError("kind hf-qwen35 keeps the checkpoint's encodings (bf16 matrices, MXFP4 experts)")
+                if a.weight_format not in ("bf16", "fp8"):
+                    raise CliError("kind hf-qwen35 writes bf16 projections or quantises them to block-scaled FP8 "
+                                   "(routed experts keep their MXFP4 encoding)")
                 cfg = _hf_qwen35_config(raw_cfg)
+                cfg.weight_format = a.weight_format
             else:
                 cfg = _hf_config(raw_cfg, a.weight_format)
             if "tokenizer.json" in cache.fds:

@@ -29,7 +29,7 @@ from ..formats import gguf as G
 from ..ops.core import LinearWeight
 from ..ops.w4 import W4Weight
 from .config import ModelConfig
-from .loader import CONVERTER_ID, MXFP4_ENCODING, NVFP4_ENCODING, config_from_gguf
+from .loader import CONVERTER_ID, FP8_ENCODING, MXFP4_ENCODING, NVFP4_ENCODING, config_from_gguf
 
 FAMILIES = ("moe", "qwen35")
 
@@ -55,9 +55,20 @@ class _Sink:
     def linear(self, name: str, lw: Optional[LinearWeight], r0: int = 0, r1: Optional[int] = None) -> None:
         if lw is None:
             return
+        r1 = r1 if r1 is not None else lw.w.shape[0]
+        if lw.kind == "fp8":
+            # E4M3 bytes + the file layout of the 1 x 128 block scales, [N, ceil(K / 128)] fp32
+            val = lw.w[r0:r1].detach().cpu().contiguous()
+            sc = lw.scale_t[:, r0:r1].t().detach().cpu().float().contiguous()
+            self.tensors.append((name, tuple(val.shape), G.T_I8, val.numpy().tobytes()))
+            self.tensors.append((name + ".scale", tuple(sc.shape), G.T_F32, sc.numpy().astype("<f4").tobytes()))
+            self.bindings.append({"logical_tensor": name, "value_tensor": name, "encoding": FP8_ENCODING, "role": "weight",
+                                  "logical_shape": list(val.shape), "scope": "consumed",
+                                  "scales": [{"role": "block", "tensor": name + ".scale"}]})
+            return
         if lw.kind != "dense":
-            raise G.GgufError(f"{name}: this family writes dense projections (found {lw.kind})")
-        self.dense(name, lw.w[r0:r1 if r1 is not None else lw.w.shape[0]])
+            raise G.GgufError(f"{name}: this family writes dense or FP8 projections (found {lw.kind})")
+        self.dense(name, lw.w[r0:r1])
 
     def experts(self, name: str, w4: W4Weight) -> None:
         """All groups of a 4-bit weight as one tensor [groups * n, k], expert-major rows."""
@@ -191,6 +202,71 @@ class _Source:
         w = torch.cat(out, dim=0)
         return (w.t() if transpose else w).contiguous()
 
+    # ---- projections: bf16 / fp32 values, or E4M3 bytes with [N, ceil(K / 128)] block scales
+    def matrix(self, name: str) -> tuple:
+        """(values [N, K], block scales [N, ceil(K / 128)] or None)."""
+        t = self.g.tensors[name]
+        if t.ttype == G.T_I8:
+            b = self.bound.get(name)
+            if b is None or b["encoding"] != FP8_ENCODING:
+                raise G.GgufError(f"{name}: 8-bit tensor without a block-scaled FP8 binding")
+            sc_name = [x["tensor"] for x in b.get("scales", []) if x.get("role") == "block"]
+            if len(sc_name) != 1:
+                raise G.GgufError(f"{name}: an FP8 binding needs exactly one block-scale tensor")
+            val = self.g.upload(name, self.device, torch.uint8).view(t.shape)
+            sc = self.g.upload(sc_name[0], self.device, torch.float32).view(self.g.tensors[sc_name[0]].shape)
+            if sc.shape != (t.shape[0], (t.shape[1] + 127) // 128):
+                raise G.GgufError(f"{name}: block-scale tensor shape {tuple(sc.shape)} does not match")
+            return val, sc
+        return self.dense(name), None
+
+    @staticmethod
+    def _segments(n: int, segments: list, tp_size: int, tp_rank: int, what: str) -> list:
+        """Index ranges of this rank's share of `n` rows that are consecutive (heads, rows per head) segments."""
+        out, r0 = [], 0
+        for heads, per in segments:
+            if heads % tp_size:
+                raise G.GgufError(f"{what}: {heads} heads do not divide over {tp_size} ranks")
+            loc = heads // tp_size
+            out.append((r0 + tp_rank * loc * per, r0 + (tp_rank + 1) * loc * per))
+            r0 += heads * per
+        return out
+
+    def shard(self, name: str, segments: list, tp_size: int, tp_rank: int, transpose: bool = False) -> tuple:
+        """This rank's rows (columns with `transpose`) of a projection, as `matrix` returns it."""
+        val, sc = self.matrix(name)
+        if tp_size == 1:
+            return val, sc
+        if not transpose:
+            rs = self._segments(val.shape[0], segments, tp_size, tp_rank, name)
+            val = torch.cat([val[a:b] for a, b in rs], dim=0)
+            sc = None if sc is None else torch.cat([sc[a:b] for a, b in rs], dim=0)
+            return val.contiguous(), sc
+        cs = self._segments(val.shape[1], segments, tp_size, tp_rank, name)
+        if sc is not None and any(a % 128 or b % 128 for a, b in cs):
+            raise G.GgufError(f"{name}: a column shard of a block-scaled FP8 matrix must fall on 128-column borders")
+        val = torch.cat([val[:, a:b] for a, b in cs], dim=1)
+        sc = None if sc is None else torch.cat([sc[:, a // 128:b // 128] for a, b in cs], dim=1)
+        return val.contiguous(), sc
+
+    @staticmethod
+    def cat_rows(parts: list, pad_to: int = 1) -> tuple:
+        val = torch.cat([p[0] for p in parts], dim=0)
+        sc = None if parts[0][1] is None else torch.cat([p[1] for p in parts], dim=0)
+        pad = (-val.shape[0]) % pad_to
+        if pad:
+            val = torch.cat([val, torch.zeros((pad, val.shape[1]), dtype=val.dtype, device=val.device)], dim=0)
+            if sc is not None:
+                sc = torch.cat([sc, torch.ones((pad, sc.shape[1]), dtype=sc.dtype, device=sc.device)], dim=0)
+        return val, sc
+
+    @staticmethod
+    def to_linear(m: tuple) -> LinearWeight:
+        val, sc = m
+        if sc is None:
+            return LinearWeight("dense", val.contiguous())
+        return LinearWeight("fp8", val.contiguous(), sc.t().contiguous())
+
     def experts(self, name: str, groups: int, g_lo: int, g_hi: int) -> W4Weight:
         t = self.g.tensors[name]
         b = self.bound.get(name)
@@ -227,7 +303,7 @@ def load_family_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, 
     if kv_format:
         cfg.kv_format = kv_format
     src = _Source(g, cfg, device)
-    lin = lambda t: LinearWeight("dense", t.contiguous())
+    L = src.to_linear
     d, hd, hq, hkv, f = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.ffn
     if hq % tp_size or (hkv % tp_size and tp_size % hkv):
         raise G.GgufError("attention heads do not divide over the tensor-parallel ranks")
@@ -235,13 +311,14 @@ def load_family_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, 
 
     def kv_rows(name):
         if kv_seg is not None:
-            return src.head_rows(name, kv_seg, tp_size, tp_rank)
+            return src.shard(name, kv_seg, tp_size, tp_rank)
         head = tp_rank * hkv // tp_size          # fewer kv heads than ranks: the head this rank's query group uses
-        return src.dense(name)[head * hd:(head + 1) * hd]
+        val, sc = src.matrix(name)
+        return val[head * hd:(head + 1) * hd], None if sc is None else sc[head * hd:(head + 1) * hd]
 
     def qkv(p):
-        return lin(torch.cat([src.head_rows(p + "attn_q.weight", [(hq, hd)], tp_size, tp_rank), kv_rows(p + "attn_k.weight"),
-                              kv_rows(p + "attn_v.weight")], dim=0))
+        return L(src.cat_rows([src.shard(p + "attn_q.weight", [(hq, hd)], tp_size, tp_rank), kv_rows(p + "attn_k.weight"),
+                               kv_rows(p + "attn_v.weight")]))
 
     embed = src.dense("token_embd.weight")
     layers = []
@@ -259,12 +336,12 @@ def load_family_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, 
                 sinks = sinks[tp_rank * (hq // tp_size):(tp_rank + 1) * (hq // tp_size)].contiguous()
             shared = {}
             if src.has(p + "ffn_gate_up_shexp.weight"):
-                shared = dict(shared_gate_up=lin(src.dense(p + "ffn_gate_up_shexp.weight")),
-                              shared_down=lin(src.dense(p + "ffn_down_shexp.weight")))
+                shared = dict(shared_gate_up=L(src.matrix(p + "ffn_gate_up_shexp.weight")),
+                              shared_down=L(src.matrix(p + "ffn_down_shexp.weight")))
             layers.append(MoeLayerWeights(
                 attn_norm=src.dense(p + "attn_norm.weight"), qkv=qkv(p),
-                o=lin(src.head_rows(p + "attn_output.weight", [(hq, hd)], tp_size, tp_rank, transpose=True)),
-                sinks=sinks, mlp_norm=src.dense(p + "ffn_norm.weight"), router=lin(src.dense(p + "ffn_gate_inp.weight")),
+                o=L(src.shard(p + "attn_output.weight", [(hq, hd)], tp_size, tp_rank, transpose=True)),
+                sinks=sinks, mlp_norm=src.dense(p + "ffn_norm.weight"), router=L(src.matrix(p + "ffn_gate_inp.weight")),
                 gate_up=src.experts(p + "ffn_gate_up_exps.weight", cfg.n_experts, e_lo, e_hi),
                 down=src.experts(p + "ffn_down_exps.weight", cfg.n_experts, e_lo, e_hi), **shared))
         make = MoeWeights
@@ -284,44 +361,44 @@ def load_family_gguf(g: G.GgufFile, device, tp_size: int = 1, tp_rank: int = 0, 
             p = f"blk.{i}."
             common = dict(in_norm=src.dense(p + "attn_norm.weight"), mlp_norm=src.dense(p + "ffn_norm.weight"))
             if sparse:
-                common.update(router=lin(src.dense(p + "ffn_gate_inp.weight")),
+                common.update(router=L(src.matrix(p + "ffn_gate_inp.weight")),
                               exp_gate_up=src.experts(p + "ffn_gate_up_exps.weight", cfg.n_experts, e_lo, e_hi),
                               exp_down=src.experts(p + "ffn_down_exps.weight", cfg.n_experts, e_lo, e_hi))
                 if src.has(p + "ffn_gate_up_shexp.weight"):
-                    common.update(shared_gate_up=lin(src.dense(p + "ffn_gate_up_shexp.weight")),
-                                  shared_down=lin(src.dense(p + "ffn_down_shexp.weight")))
+                    common.update(shared_gate_up=L(src.matrix(p + "ffn_gate_up_shexp.weight")),
+                                  shared_down=L(src.matrix(p + "ffn_down_shexp.weight")))
             else:
-                gate_up = torch.cat([src.head_rows(p + "ffn_gate.weight", [(f, 1)], tp_size, tp_rank),
-                                     src.head_rows(p + "ffn_up.weight", [(f, 1)], tp_size, tp_rank)], dim=0)
-                common.update(gate_up=lin(gate_up),
-                              down=lin(src.head_rows(p + "ffn_down.weight", [(f, 1)], tp_size, tp_rank, transpose=True)))
+                gate_up = src.cat_rows([src.shard(p + "ffn_gate.weight", [(f, 1)], tp_size, tp_rank),
+                                        src.shard(p + "ffn_up.weight", [(f, 1)], tp_size, tp_rank)])
+                common.update(gate_up=L(gate_up),
+                              down=L(src.shard(p + "ffn_down.weight", [(f, 1)], tp_size, tp_rank, transpose=True)))
             if (i + 1) % cfg.full_attention_interval == 0:
                 gate = None
                 if src.has(p + "attn_gate.weight"):
-                    gate = lin(src.head_rows(p + "attn_gate.weight", [(hq, hd)], tp_size, tp_rank))
+                    gate = L(src.shard(p + "attn_gate.weight", [(hq, hd)], tp_size, tp_rank))
                 layers.append(Qwen35Layer("full", qkv=qkv(p), gate=gate,
-                                          o=lin(src.head_rows(p + "attn_output.weight", [(hq, hd)], tp_size, tp_rank, transpose=True)),
+                                          o=L(src.shard(p + "attn_output.weight", [(hq, hd)], tp_size, tp_rank, transpose=True)),
                                           q_norm=src.dense(p + "attn_q_norm.weight").to(norm_dt),
                                           k_norm=src.dense(p + "attn_k_norm.weight").to(norm_dt), **common))
             else:
                 segs = [(qh, ghd), (qh, ghd), (vh, ghd), (vh, ghd), (vh, 1), (vh, 1)]
-                w_loc = src.head_rows(p + "ssm_in.weight", segs, tp_size, tp_rank)
-                w_in = torch.zeros(((w_loc.shape[0] + 7) // 8 * 8, d), dtype=w_loc.dtype, device=w_loc.device)
-                w_in[:w_loc.shape[0]] = w_loc
+                w_in = src.cat_rows([src.shard(p + "ssm_in.weight", segs, tp_size, tp_rank)], pad_to=8)
                 layers.append(Qwen35Layer(
-                    "gdn", in_proj=lin(w_in), conv_w=src.head_rows(p + "ssm_conv1d.weight", segs[:3], tp_size, tp_rank),
+                    "gdn", in_proj=L(w_in), conv_w=src.head_rows(p + "ssm_conv1d.weight", segs[:3], tp_size, tp_rank),
                     a_log=src.head_rows(p + "ssm_a", [(vh, 1)], tp_size, tp_rank, keep_f32=True).contiguous(),
                     dt_bias=src.head_rows(p + "ssm_dt.bias", [(vh, 1)], tp_size, tp_rank),
                     out_norm=src.dense(p + "ssm_norm.weight", keep_f32=True),
-                    out_proj=lin(src.head_rows(p + "ssm_out.weight", [(vh, ghd)], tp_size, tp_rank, transpose=True)), **common))
+                    out_proj=L(src.shard(p + "ssm_out.weight", [(vh, ghd)], tp_size, tp_rank, transpose=True)), **common))
         make = Qwen35Weights
     final_norm = src.dense("output_norm.weight")
     vs = (cfg.vocab + tp_size - 1) // tp_size
     vo = tp_rank * vs if tp_size > 1 else 0
     v_hi = min(cfg.vocab, vo + vs) if tp_size > 1 else cfg.vocab
-    head_src = embed if cfg.tie_embeddings else src.dense("output.weight")
     if tp_size == 1 and cfg.tie_embeddings:
         head = LinearWeight("dense", embed)
+    elif cfg.tie_embeddings:
+        head = LinearWeight("dense", embed[vo:v_hi].contiguous())
     else:
-        head = lin(head_src[vo:v_hi])
+        val, sc = src.matrix("output.weight")
+        head = L((val[vo:v_hi], None if sc is None else sc[vo:v_hi]))
     return cfg, make(embed, layers, final_norm, head, vo)

@@ -94,7 +94,20 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
     def rnd(shape, s=std):
         return (torch.randn(shape, generator=gen, dtype=torch.float32, device=device if big else "cpu") * s)
 
+    fp8 = cfg.weight_format == "fp8"
+
     def lin(w):
+        """Projection matrices: bf16, or block-scaled FP8 (E4M3 + one fp32 scale per 1 x 128 block) when the
+        configuration asks for FP8 weights; norms, convolution taps, gates' bias vectors and the router stay bf16."""
+        w = w.to(dt).contiguous().to(device)
+        if fp8:
+            if w.is_cuda:
+                q = ops.quant_fp8(w)
+                return LinearWeight("fp8", q.data, q.scale)
+            return LinearWeight.from_dense(w.float(), "fp8")
+        return LinearWeight("dense", w)
+
+    def lin_bf16(w):
         return LinearWeight("dense", w.to(dt).contiguous().to(device))
 
     def vec(v, dtype=None):
@@ -128,7 +141,7 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
             router = torch.cat([router, sg, torch.zeros((7, d), device=router.device)], dim=0)
             out.update(shared_gate_up=lin(sgu), shared_down=lin(sdn))
         quant = W4Weight.quantize_device if big else (lambda f, w: W4Weight.quantize(f, w, device, keep_file=False))
-        out.update(router=lin(router), exp_gate_up=quant(cfg.expert_format, torch.stack(gu_local)),
+        out.update(router=lin_bf16(router), exp_gate_up=quant(cfg.expert_format, torch.stack(gu_local)),
                    exp_down=quant(cfg.expert_format, torch.stack(dn_local)))
         return out
 
@@ -161,7 +174,10 @@ def init_random_qwen35_weights(cfg: ModelConfig, device, seed: int = 0, std: flo
                                       out_proj=lin(cols(rnd((d, vh * ghd)), [(vh, ghd)])), **common))
     embed = rnd((cfg.vocab, d)).to(dt).to(device)
     head = embed if cfg.tie_embeddings else rnd((cfg.vocab, d)).to(dt).contiguous().to(device)
-    return Qwen35Weights(embed, layers, vec(rnd((d,), 0.05)), LinearWeight("dense", head), 0)
+    head_w = LinearWeight("dense", head)
+    if fp8 and not cfg.tie_embeddings:
+        head_w = lin(head)
+    return Qwen35Weights(embed, layers, vec(rnd((d,), 0.05)), head_w, 0)
 
 
 class Qwen35Model:
@@ -186,9 +202,11 @@ class Qwen35Model:
 
     def _mlp(self, h, lw):
         cfg = self.cfg
-        x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
         if lw.router is None:
-            return self.tp.row_linear(ops.gated_act(ops.linear(x, lw.gate_up), cfg.act), lw.down, h)
+            x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one, quant=lw.gate_up.kind == "fp8")
+            act = ops.gated_act(ops.linear(x, lw.gate_up), cfg.act, quant=lw.down.kind == "fp8")
+            return self.tp.row_linear(act, lw.down, h)
+        x = ops.rmsnorm(h, lw.mlp_norm, cfg.rms_eps, cfg.norm_offset_one)
         # routed experts (softmax over the selected logits = softmax over all, renormalised over the selection) plus
         # the always-on shared expert under its sigmoid gate (crates/sllm-core/src/qwen35_moe.rs:1576-1600)
         from ..ops import moe as M
@@ -208,7 +226,9 @@ class Qwen35Model:
             raise ValueError("the hybrid family needs row offsets and state slots in the batch")
         h = ops.embedding(w.embed, b.tokens, cfg.embedding_scale)
         for li, lw in enumerate(w.layers):
-            x = ops.rmsnorm(h, lw.in_norm, cfg.rms_eps, cfg.norm_offset_one)
+            first = lw.qkv if lw.kind == "full" else lw.in_proj
+            # FP8 projections take the normalised row as E4M3 + block scales, written by the norm kernel itself
+            x = ops.rmsnorm(h, lw.in_norm, cfg.rms_eps, cfg.norm_offset_one, quant=first.kind == "fp8")
             if lw.kind == "full":
                 kv = cache.layer(li)
                 qkv = ops.linear(x, lw.qkv)

@@ -282,3 +282,70 @@ def test_hf_qwen35_importer(tmp_path, capsys, sparse):
     assert convert.main(["--kind", "hf-qwen35", "--lock", str(tmp_path / "lock.json"), "--cache", str(src), "--output", out,
                          "--derived-lock", dl]) != 0
     assert "unconsumed tensors" in capsys.readouterr().out
+
+
+def test_hybrid_family_with_fp8_projections(tmp_path):
+    """Block-scaled FP8 projections in the hybrid family: the model runs (logits near the bf16 model's), the GGUF round
+    trip is bit-exact, and tensor-parallel ranks read the shard the seeded initialiser keeps (row shards and 128-column
+    aligned column shards of values and block scales)."""
+    from sllm_b200.cache.hybrid import HybridCache
+    cfg = tiny_qwen35()
+    cfg.weight_format = "fp8"
+    w = init_random_qwen35_weights(cfg, "cpu", seed=5)
+    assert w.layers[0].in_proj.kind == "fp8" and w.layers[3].qkv.kind == "fp8" and w.layers[0].gate_up.kind == "fp8"
+    path = str(tmp_path / "hy8.gguf")
+    g = G.verify_gguf(path, FIO.export_family_gguf(cfg, w, path))
+    assert g.tensors["blk.0.ssm_in.weight"].ttype == G.T_I8 and "blk.0.ssm_in.weight.scale" in g.tensors
+    cfg2, w2 = FIO.load_family_gguf(g, "cpu")
+    assert cfg2 == cfg
+
+    def same_lin(a, b, path):
+        assert a.kind == b.kind == "fp8", path
+        assert torch.equal(a.w, b.w) and torch.equal(a.scale_t, b.scale_t), path
+
+    for i, (a, b) in enumerate(zip(w.layers, w2.layers)):
+        for name in ("gate_up", "down", "qkv", "gate", "o", "in_proj", "out_proj"):
+            if getattr(a, name) is not None:
+                same_lin(getattr(a, name), getattr(b, name), f"layer{i}.{name}")
+
+    def engine(c, ww):
+        m = Qwen35Model(c, ww)
+        cache = HybridCache(c, 32, torch.device("cpu"), max_seqs=6, kv_heads=m.local_kv_heads)
+        return Engine(c, m, cache, "cpu", max_batch=2, use_cuda_graphs=False)
+
+    prompt = list(range(3, 25))
+    e8 = engine(cfg, w)
+    assert e8.generate([prompt], 5) == engine(cfg2, w2).generate([prompt], 5)
+    cfg16 = tiny_qwen35()
+    e16 = engine(cfg16, init_random_qwen35_weights(cfg16, "cpu", seed=5))
+    l8 = e8.prefill([e8.new_sequence(prompt)], sample=False).float()
+    l16 = e16.prefill([e16.new_sequence(prompt)], sample=False).float()
+    assert ((l8 - l16).norm() / l16.norm()).item() < 0.15
+    # shards: a geometry that divides over two ranks with 128-aligned column shards
+    cfg.n_kv_heads, cfg.gdn_qk_heads, cfg.gdn_heads, cfg.head_dim, cfg.rotary_dim = 2, 2, 4, 128, 32
+    path2 = str(tmp_path / "hy8b.gguf")
+    g2 = G.verify_gguf(path2, FIO.export_family_gguf(cfg, init_random_qwen35_weights(cfg, "cpu", seed=5), path2))
+    for r in range(2):
+        want = init_random_qwen35_weights(cfg, "cpu", seed=5, tp_size=2, tp_rank=r)
+        _, got = FIO.load_family_gguf(g2, "cpu", tp_size=2, tp_rank=r)
+        for i, (a, b) in enumerate(zip(want.layers, got.layers)):
+            for name in ("gate_up", "qkv", "gate", "in_proj"):            # row shards: quantisation is per row block
+                if getattr(a, name) is not None:
+                    same_lin(getattr(a, name), getattr(b, name), f"rank{r}.layer{i}.{name}")
+            for name in ("down", "o", "out_proj"):                         # column shards: whole 128-column blocks
+                if getattr(a, name) is not None:
+                    same_lin(getattr(a, name), getattr(b, name), f"rank{r}.layer{i}.{name}")
+
+
+def test_converter_writes_fp8_hybrid_files(tmp_path, capsys):
+    from sllm_b200.cli import convert
+    from sllm_b200.models import loader
+    out, dl = str(tmp_path / "q8.gguf"), str(tmp_path / "q8.lock.json")
+    assert convert.main(["--kind", "random-llama", "--artifact", "tiny-qwen35", "--weight-format", "fp8", "--output", out,
+                         "--derived-lock", dl]) == 0
+    capsys.readouterr()
+    g = G.verify_gguf(out, G.read_derived_lock(dl))
+    cfg, w, family = loader.load_model_gguf(g, "cpu")
+    assert family == "qwen35" and cfg.weight_format == "fp8" and w.layers[0].in_proj.kind == "fp8"
+    assert convert.main(["--kind", "random-llama", "--artifact", "tiny-moe", "--weight-format", "fp8", "--output", out,
+                         "--derived-lock", dl]) != 0

@@ -844,7 +844,10 @@ def test_hybrid_and_gemma_models_gpu_match_cpu():
                          vocab=1024, act="gelu_tanh", tie_embeddings=True, embedding_scale=16.0, logit_softcap=30.0,
                          weight_format="bf16", kv_format="bf16", sliding_window=16, window_layers=[True, True, False], qk_norm=True,
                          post_norms=True, max_context=128)
-    for cfg in (tiny_qwen35(), tiny_qwen35_moe(), gem):       # dense hybrid, hybrid with routed experts, Gemma options
+    q8 = tiny_qwen35()
+    q8.weight_format, q8.name = "fp8", "tiny-qwen35-fp8"
+    # dense hybrid, the same with block-scaled FP8 projections, hybrid with routed experts, Gemma options
+    for cfg in (tiny_qwen35(), q8, tiny_qwen35_moe(), gem):
         g = build_engine(cfg, DEV, seed=1, num_pages=32, max_batch=2)
         c = build_engine(cfg, "cpu", seed=1, num_pages=32, max_batch=2, use_cuda_graphs=False) if cfg.family == "qwen35" \
             else _cpu_twin(g, cfg)
