@@ -26,7 +26,8 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // grid (ceil(width / 128), sequences).
 __global__ void gdn_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                      __nv_bfloat16* __restrict__ state, __nv_bfloat16* __restrict__ y,
-                                     const int* __restrict__ row_off, const int* __restrict__ slots, int width, int taps) {
+                                     const int* __restrict__ row_off, const int* __restrict__ slots, int width, int taps,
+                                     int ldx) {
   pdl_wait();
   pdl_trigger();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -40,7 +41,7 @@ __global__ void gdn_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, const 
   for (int t = 0; t < taps; ++t) wt[t] = __bfloat162float(w[static_cast<size_t>(c) * taps + t]);
   for (int t = 0; t < hist; ++t) win[t] = __bfloat162float(st[static_cast<size_t>(t) * width + c]);
   for (int r = r0; r < r1; ++r) {
-    win[hist] = __bfloat162float(x[static_cast<size_t>(r) * width + c]);
+    win[hist] = __bfloat162float(x[static_cast<size_t>(r) * ldx + c]);
     float sum = 0.f;
     for (int t = 0; t < taps; ++t) sum += win[t] * wt[t];
     y[static_cast<size_t>(r) * width + c] = __float2bfloat16_rn(sum / (1.f + expf(-sum)));
@@ -58,7 +59,8 @@ gdn_recurrent_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16*
                      const __nv_bfloat16* __restrict__ b_in, const __nv_bfloat16* __restrict__ a_in,
                      const float* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
                      const float* __restrict__ norm_w, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
-                     const int* __restrict__ row_off, const int* __restrict__ slots, int qk_heads, int v_heads) {
+                     const int* __restrict__ row_off, const int* __restrict__ slots, int qk_heads, int v_heads, int ldz,
+                     int ldg) {
   pdl_wait();
   pdl_trigger();
   constexpr int HD = kGdnHeadDim;
@@ -90,9 +92,9 @@ gdn_recurrent_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16*
     if (lane == 0) { red[0][warp] = qq; red[1][warp] = kk; }
     __syncthreads();
     if (d == 0) {
-      const float bq = __bfloat162float(b_in[static_cast<size_t>(r) * v_heads + vh]);
+      const float bq = __bfloat162float(b_in[static_cast<size_t>(r) * ldg + vh]);
       sc[0] = bf16_round(1.f / (1.f + expf(-bq)));
-      const float av = __bfloat162float(a_in[static_cast<size_t>(r) * v_heads + vh]) + dtb;
+      const float av = __bfloat162float(a_in[static_cast<size_t>(r) * ldg + vh]) + dtb;
       sc[1] = expf(a_neg * softplus_f(av));
     }
     qq = red[0][0] + red[0][1] + red[0][2] + red[0][3];
@@ -120,7 +122,7 @@ gdn_recurrent_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16*
     __syncthreads();
     oo = red[2][0] + red[2][1] + red[2][2] + red[2][3];
     const float inv = 1.f / sqrtf(oo / static_cast<float>(HD) + 1e-6f);
-    const float zv = __bfloat162float(z[static_cast<size_t>(r) * ow + vh * HD + d]);
+    const float zv = __bfloat162float(z[static_cast<size_t>(r) * ldz + vh * HD + d]);
     out[static_cast<size_t>(r) * ow + vh * HD + d] = __float2bfloat16_rn(bf16_round(o * inv) * nw * (zv / (1.f + expf(-zv))));
     __syncthreads();
   }
@@ -146,7 +148,7 @@ __global__ void __launch_bounds__(kGdnHeadDim)
 gdn_pre_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ b_in,
                const __nv_bfloat16* __restrict__ a_in, const float* __restrict__ a_log,
                const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ qn, float* __restrict__ kn,
-               float* __restrict__ gates, int qk_heads, int v_heads) {
+               float* __restrict__ gates, int qk_heads, int v_heads, int ldg) {
   pdl_wait();
   pdl_trigger();
   constexpr int HD = kGdnHeadDim;
@@ -154,8 +156,8 @@ gdn_pre_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __res
   if (static_cast<int>(blockIdx.y) >= qk_heads) {
     const int vh = (blockIdx.y - qk_heads) * HD + d;
     if (vh < v_heads) {
-      const float bq = __bfloat162float(b_in[static_cast<size_t>(r) * v_heads + vh]);
-      const float av = __bfloat162float(a_in[static_cast<size_t>(r) * v_heads + vh]) + __bfloat162float(dt_bias[vh]);
+      const float bq = __bfloat162float(b_in[static_cast<size_t>(r) * ldg + vh]);
+      const float av = __bfloat162float(a_in[static_cast<size_t>(r) * ldg + vh]) + __bfloat162float(dt_bias[vh]);
       gates[(static_cast<size_t>(r) * v_heads + vh) * 2] = bf16_round(1.f / (1.f + expf(-bq)));
       gates[(static_cast<size_t>(r) * v_heads + vh) * 2 + 1] = expf(-expf(a_log[vh]) * softplus_f(av));
     }
@@ -240,7 +242,7 @@ gdn_scan_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__
 // grid (T, v_heads), 128 threads.
 __global__ void __launch_bounds__(kGdnHeadDim)
 gdn_post_kernel(const float* __restrict__ o_raw, const __nv_bfloat16* __restrict__ z, const float* __restrict__ norm_w,
-                __nv_bfloat16* __restrict__ out, int v_heads) {
+                __nv_bfloat16* __restrict__ out, int v_heads, int ldz) {
   pdl_wait();
   pdl_trigger();
   constexpr int HD = kGdnHeadDim;
@@ -253,7 +255,7 @@ gdn_post_kernel(const float* __restrict__ o_raw, const __nv_bfloat16* __restrict
   __syncthreads();
   oo = red[0] + red[1] + red[2] + red[3];
   const float inv = 1.f / sqrtf(oo / static_cast<float>(HD) + 1e-6f);
-  const float zv = __bfloat162float(z[idx]);
+  const float zv = __bfloat162float(z[static_cast<size_t>(r) * ldz + vh * HD + d]);
   out[idx] = __float2bfloat16_rn(bf16_round(o * inv) * norm_w[d] * (zv / (1.f + expf(-zv))));
 }
 
@@ -290,20 +292,24 @@ __global__ void qk_headnorm_kernel(__nv_bfloat16* __restrict__ x, int ld, int hq
 
 using namespace sllm;
 
+// ldx: row stride of x in elements (0: width) - x may be a column slice of a wider projection output.
 SLLM_EXPORT int sllm_gdn_conv_silu(const void* x, const void* w, void* state, void* y, const int* row_off, const int* slots,
-                                   int sequences, int width, int taps, void* stream) {
+                                   int sequences, int width, int taps, int ldx, void* stream) {
   if (!x || !w || !state || !y || !row_off || !slots || sequences <= 0 || width <= 0 || taps < 2 || taps > 8)
     return SLLM_ERR_INVALID_ARGUMENT;
   cudaError_t e = launch_kernel(gdn_conv_silu_kernel, dim3((width + 127) / 128, sequences), dim3(128), 0,
                                 static_cast<cudaStream_t>(stream), 1u, static_cast<const __nv_bfloat16*>(x),
                                 static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(state),
-                                static_cast<__nv_bfloat16*>(y), row_off, slots, width, taps);
+                                static_cast<__nv_bfloat16*>(y), row_off, slots, width, taps, ldx > 0 ? ldx : width);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 
+// ldz / ldg: row strides in elements of z and of b / a (0: v_heads * 128 and v_heads) - they may be column slices of a
+// wider projection output.
 SLLM_EXPORT int sllm_gdn_recurrent(const void* qkv, const void* z, const void* b, const void* a, const float* a_log,
                                    const void* dt_bias, const float* norm_w, float* state, void* out, const int* row_off,
-                                   const int* slots, int sequences, int qk_heads, int v_heads, int head_dim, void* stream) {
+                                   const int* slots, int sequences, int qk_heads, int v_heads, int head_dim, int ldz, int ldg,
+                                   void* stream) {
   if (!qkv || !z || !b || !a || !a_log || !dt_bias || !norm_w || !state || !out || !row_off || !slots || sequences <= 0 ||
       qk_heads <= 0 || v_heads <= 0 || (v_heads % qk_heads))
     return SLLM_ERR_INVALID_ARGUMENT;
@@ -312,7 +318,8 @@ SLLM_EXPORT int sllm_gdn_recurrent(const void* qkv, const void* z, const void* b
                                 static_cast<cudaStream_t>(stream), 1u, static_cast<const __nv_bfloat16*>(qkv),
                                 static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(b),
                                 static_cast<const __nv_bfloat16*>(a), a_log, static_cast<const __nv_bfloat16*>(dt_bias), norm_w,
-                                state, static_cast<__nv_bfloat16*>(out), row_off, slots, qk_heads, v_heads);
+                                state, static_cast<__nv_bfloat16*>(out), row_off, slots, qk_heads, v_heads,
+                                ldz > 0 ? ldz : v_heads * kGdnHeadDim, ldg > 0 ? ldg : v_heads);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 
@@ -321,7 +328,8 @@ SLLM_EXPORT int sllm_gdn_recurrent(const void* qkv, const void* z, const void* b
 SLLM_EXPORT int sllm_gdn_recurrent_prompt(const void* qkv, const void* z, const void* b, const void* a, const float* a_log,
                                           const void* dt_bias, const float* norm_w, float* state, void* out,
                                           const int* row_off, const int* slots, int sequences, int tokens, int qk_heads,
-                                          int v_heads, int head_dim, float* scratch, long long scratch_floats, void* stream) {
+                                          int v_heads, int head_dim, int ldz, int ldg, float* scratch,
+                                          long long scratch_floats, void* stream) {
   if (!qkv || !z || !b || !a || !a_log || !dt_bias || !norm_w || !state || !out || !row_off || !slots || !scratch ||
       sequences <= 0 || tokens <= 0 || qk_heads <= 0 || v_heads <= 0 || (v_heads % qk_heads))
     return SLLM_ERR_INVALID_ARGUMENT;
@@ -339,14 +347,15 @@ SLLM_EXPORT int sllm_gdn_recurrent_prompt(const void* qkv, const void* z, const 
   cudaError_t e = launch_kernel(gdn_pre_kernel, dim3(tokens, qk_heads + gate_blocks), dim3(kGdnHeadDim), 0, st, 1u,
                                 static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(b),
                                 static_cast<const __nv_bfloat16*>(a), a_log, static_cast<const __nv_bfloat16*>(dt_bias), qn, kn,
-                                gates, qk_heads, v_heads);
+                                gates, qk_heads, v_heads, ldg > 0 ? ldg : v_heads);
   if (e != cudaSuccess) return SLLM_ERR_CUDA;
   e = launch_kernel(gdn_scan_kernel, dim3(v_heads, sequences), dim3(kGdnHeadDim), 0, st, 1u,
                     static_cast<const __nv_bfloat16*>(qkv), static_cast<const float*>(qn), static_cast<const float*>(kn),
                     static_cast<const float*>(gates), state, o_raw, row_off, slots, qk_heads, v_heads);
   if (e != cudaSuccess) return SLLM_ERR_CUDA;
   e = launch_kernel(gdn_post_kernel, dim3(tokens, v_heads), dim3(kGdnHeadDim), 0, st, 1u, static_cast<const float*>(o_raw),
-                    static_cast<const __nv_bfloat16*>(z), norm_w, static_cast<__nv_bfloat16*>(out), v_heads);
+                    static_cast<const __nv_bfloat16*>(z), norm_w, static_cast<__nv_bfloat16*>(out), v_heads,
+                    ldz > 0 ? ldz : v_heads * kGdnHeadDim);
   return e == cudaSuccess ? SLLM_OK : SLLM_ERR_CUDA;
 }
 

@@ -242,10 +242,11 @@ class Qwen35Model:
             else:
                 conv_state, rec_state = cache.gdn(li)
                 p = ops.linear(x, lw.in_proj)
-                qkv = p[:, :width].contiguous()
-                z = p[:, width:width + vh * ghd].contiguous()
-                bb = p[:, width + vh * ghd:width + vh * ghd + vh].contiguous()
-                aa = p[:, width + vh * ghd + vh:width + vh * ghd + 2 * vh].contiguous()
+                # column slices of the projection output: the kernels take the row stride (no copies)
+                qkv = p[:, :width]
+                z = p[:, width:width + vh * ghd]
+                bb = p[:, width + vh * ghd:width + vh * ghd + vh]
+                aa = p[:, width + vh * ghd + vh:width + vh * ghd + 2 * vh]
                 qkv = G.conv_silu(qkv, lw.conv_w, conv_state, b.row_off, b.slots)
                 o = G.recurrent(qkv, z, bb, aa, lw.a_log, lw.dt_bias, lw.out_norm, rec_state, b.row_off, b.slots, qh, vh, ghd)
                 h = self.tp.row_linear(o, lw.out_proj, h)

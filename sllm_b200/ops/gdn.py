@@ -15,9 +15,9 @@ from . import _lib
 
 P, I, F = C.c_void_p, C.c_int, C.c_float
 _SIGS = {
-    "sllm_gdn_conv_silu": (I, [P, P, P, P, P, P, I, I, I, P]),
-    "sllm_gdn_recurrent": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P]),
-    "sllm_gdn_recurrent_prompt": (I, [P] * 11 + [I] * 5 + [P, C.c_longlong, P]),
+    "sllm_gdn_conv_silu": (I, [P, P, P, P, P, P, I, I, I, I, P]),
+    "sllm_gdn_recurrent": (I, [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
+    "sllm_gdn_recurrent_prompt": (I, [P] * 11 + [I] * 7 + [P, C.c_longlong, P]),
     "sllm_qk_headnorm": (I, [P, I, I, I, I, I, P, P, F, I, P]),
     "sllm_qkv_headnorm": (I, [P, I, I, I, I, I, P, P, F, I, I, I, P]),
 }
@@ -52,8 +52,11 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, row_off: to
             state[slot] = seq[-(taps - 1):].to(state.dtype)
         return y if x.dtype == torch.float32 else y.to(torch.bfloat16)
     from .core import _p, _stream
-    y = torch.empty_like(x)
-    rc = _k().sllm_gdn_conv_silu(_p(x), _p(w), _p(state), _p(y), _p(row_off), _p(slots), slots.numel(), width, taps, _stream())
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    y = torch.empty((t, width), dtype=x.dtype, device=x.device)       # x may be a column slice of a wider matrix
+    rc = _k().sllm_gdn_conv_silu(_p(x), _p(w), _p(state), _p(y), _p(row_off), _p(slots), slots.numel(), width, taps,
+                                 x.stride(0), _stream())
     _lib.check(rc, "gdn_conv_silu")
     return y
 
@@ -103,18 +106,25 @@ def recurrent(qkv, z, b, a, a_log, dt_bias, norm_w, state, row_off, slots, qk_he
         return out if qkv.dtype == torch.float32 else out.to(torch.bfloat16)
     from .core import _p, _stream
     out = torch.empty((t, v_heads * hd), dtype=torch.bfloat16, device=qkv.device)
+    # z, b and a may be column slices of the input projection's output: the kernels take their row strides
+    if z.stride(1) != 1:
+        z = z.contiguous()
+    if b.stride(1) != 1 or a.stride(1) != 1 or a.stride(0) != b.stride(0):
+        b, a = b.contiguous(), a.contiguous()
+    qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
+    ldz, ldg = z.stride(0), b.stride(0)
     if t >= PROMPT_FORM_MIN_ROWS_PER_SEQUENCE * slots.numel() and prompt_form_enabled():
         # prompts: the state-independent work (q / k normalisation, gates, output norm) runs in parallel over the
         # tokens, the scan itself carries no reduction (three launches; a decode step keeps the fused kernel)
         n = t * (2 * qk_heads * hd + 2 * v_heads + v_heads * hd)
         scratch = torch.empty((n,), dtype=torch.float32, device=qkv.device)
         rc = _k().sllm_gdn_recurrent_prompt(_p(qkv), _p(z), _p(b), _p(a), _p(a_log), _p(dt_bias), _p(norm_w), _p(state), _p(out),
-                                            _p(row_off), _p(slots), slots.numel(), t, qk_heads, v_heads, hd, _p(scratch), n,
-                                            _stream())
+                                            _p(row_off), _p(slots), slots.numel(), t, qk_heads, v_heads, hd, ldz, ldg,
+                                            _p(scratch), n, _stream())
         _lib.check(rc, "gdn_recurrent_prompt")
         return out
     rc = _k().sllm_gdn_recurrent(_p(qkv), _p(z), _p(b), _p(a), _p(a_log), _p(dt_bias), _p(norm_w), _p(state), _p(out),
-                                 _p(row_off), _p(slots), slots.numel(), qk_heads, v_heads, hd, _stream())
+                                 _p(row_off), _p(slots), slots.numel(), qk_heads, v_heads, hd, ldz, ldg, _stream())
     _lib.check(rc, "gdn_recurrent")
     return out
 
