@@ -145,6 +145,67 @@ def _attention(size):
         {"batch": batch, "ctx": ctx, "hq": hq, "hkv": hkv, "hd": hd, "kv": "fp8"}, (5e-2, 4e-2)   # Q and P are E4M3 on the tensor cores
 
 
+def _gemm_w4a4(fmt: str):
+    """4-bit weights x 4-bit activations on the block-scaled tensor-core kernel, against an fp32 evaluation of the same
+    quantised operands (the quantiser's launch is part of the timed op)."""
+    def make(size):
+        import torch
+        from ..ops import reference as ref
+        from ..ops.w4 import W4Weight, act_quant_fp4, linear_w4a4, sf_compact
+        m, n, k = {"small": (32, 1024, 1024), "decode": (32, 4096, 4096), "large": (32, 28672, 8192)}[size]
+        torch.manual_seed(1)
+        x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+        w4 = W4Weight.quantize_device(fmt, (torch.randn(n, k, device="cuda") * 0.05))
+        q = act_quant_fp4(x, fmt)
+        want = None
+        if n * k <= 4096 * 4096:
+            xf = ref.dequant_act_fp4(q[0], sf_compact(q[1].cpu()), q[2], fmt)[:, :k]
+            want = xf @ w4.dequantized().t()
+        return (lambda: linear_w4a4(x, w4)), want, m * k * 2 + n * k * 9 // 16 + 2 * m * n, 2 * m * n * k, \
+            {"m": m, "n": n, "k": k, "activations": fmt}, (1.2e-2, 4e-3)
+    return make
+
+
+def _act_quant(size):
+    import torch
+    from ..ops import reference as ref
+    from ..ops.w4 import act_quant_fp4
+    rows, k = {"small": (32, 1024), "decode": (32, 8192), "large": (32, 28672)}[size]
+    torch.manual_seed(4)
+    x = torch.randn(rows, k, device="cuda").bfloat16()
+    want = ref.quant_act_fp4(x.cpu(), "nvfp4")[0]            # the packed codes, byte for byte
+    return (lambda: act_quant_fp4(x, "nvfp4")[0]), want, rows * k * (2 + 9 / 16), 0, {"rows": rows, "k": k, "format": "nvfp4"}, (0.0, 0.0)
+
+
+def _gdn(size):
+    import torch
+    from ..ops import gdn
+    seqs, length = {"small": (2, 24), "decode": (16, 1), "large": (1, 2048)}[size]
+    qk_heads, v_heads, hd = 4, 8, 128
+    t = seqs * length
+    torch.manual_seed(5)
+    width = (2 * qk_heads + v_heads) * hd
+    qkv = (torch.randn(t, width) * 0.5).bfloat16()
+    z = torch.randn(t, v_heads * hd).bfloat16()
+    b, a = torch.randn(t, v_heads).bfloat16(), torch.randn(t, v_heads).bfloat16()
+    a_log, dt_bias, norm_w = torch.randn(v_heads) * 0.5, (torch.randn(v_heads) * 0.5).bfloat16(), 1.0 + torch.randn(hd) * 0.05
+    row_off = torch.arange(0, t + 1, length, dtype=torch.int32)
+    slots = torch.arange(seqs, dtype=torch.int32)
+    st0 = torch.randn(seqs, v_heads, hd, hd) * 0.1
+    want = None
+    if t <= 64:
+        want = gdn.recurrent(qkv, z, b, a, a_log, dt_bias, norm_w, st0.clone(), row_off, slots, qk_heads, v_heads, hd)
+    d = lambda v: v.to("cuda")
+    args = [d(v) for v in (qkv, z, b, a, a_log, dt_bias, norm_w)]
+    st, ro, sl = st0.to("cuda"), d(row_off), d(slots)
+
+    def run():
+        st.copy_(st0)
+        return gdn.recurrent(*args, st, ro, sl, qk_heads, v_heads, hd)
+    byts = 2 * t * (width + 2 * v_heads * hd) + 8 * seqs * v_heads * hd * hd
+    return run, want, byts, 4 * t * v_heads * hd * hd, {"sequences": seqs, "tokens_each": length, "v_heads": v_heads}, (2e-2, 1e-2)
+
+
 def _moe_route(size):
     import torch
     from ..ops import moe as M
@@ -155,6 +216,8 @@ def _moe_route(size):
 
 
 OPS = {"gemm-bf16": _gemm("bf16"), "gemm-fp8": _gemm("fp8"), "gemm-nvfp4": _gemm("nvfp4"), "gemm-mxfp4": _gemm("mxfp4"),
+       "gemm-w4a4-nvfp4": _gemm_w4a4("nvfp4"), "gemm-w4a4-mxfp4": _gemm_w4a4("mxfp4"), "act-quant-fp4": _act_quant,
+       "gated-delta-net": _gdn,
        "rmsnorm": _rmsnorm, "gated-act": _gated, "argmax": _argmax, "paged-attention-fp8": _attention, "moe-route": _moe_route}
 
 
