@@ -136,7 +136,12 @@ class LeaderEngine:
 
     def prefill(self, seqs, chunk_tokens: int = 0, sample: bool = True, embeds=None, rope_pos3=None, one_chunk: bool = False):
         if embeds is not None or rope_pos3 is not None:
-            raise ValueError("multimodal prompts are not mirrored to follower ranks")
+            # a multimodal prompt: the spliced input rows (text embeddings with the visual rows in place) and the 3-axis
+            # rotary positions travel with the command; every rank then runs the same one-chunk prefill on its shard
+            e_cpu = None if embeds is None else embeds.detach().to("cpu").contiguous()
+            p_cpu = None if rope_pos3 is None else rope_pos3.detach().to("cpu", torch.int32).contiguous()
+            self._ch.send(("prefill_mm", self._sync_tokens(seqs), sample, e_cpu, p_cpu))
+            return self._e.prefill(seqs, chunk_tokens, sample, embeds=embeds, rope_pos3=rope_pos3, one_chunk=one_chunk)
         self._ch.send(("prefill", self._sync_tokens(seqs), chunk_tokens, sample, one_chunk))
         return self._e.prefill(seqs, chunk_tokens, sample, one_chunk=one_chunk)
 
@@ -194,6 +199,16 @@ def _replay(engine: Engine, seqs: dict, cmd) -> None:
         engine.fork_kv(seqs[cmd[1]], cmd[2])          # pool ids advance identically on every rank
     elif op == "kvfree":
         engine.free_kv(cmd[1])
+    elif op == "prefill_mm":
+        batch = []
+        for h, new_tokens in cmd[1]:
+            s = seqs[h]
+            del s.tokens[s.num_computed:]
+            s.tokens.extend(new_tokens)
+            batch.append(s)
+        dev = engine.device
+        embeds = None if cmd[3] is None else cmd[3].to(dev)
+        engine.prefill(batch, 0, cmd[2], embeds=embeds, rope_pos3=cmd[4], one_chunk=True)
     elif op in ("prefill", "extend"):
         batch = []
         for h, new_tokens in cmd[1]:

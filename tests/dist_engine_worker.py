@@ -18,6 +18,8 @@ def main():
     dist.init_process_group("gloo")
     cfg = MC.tiny_llama()
     cfg.max_context = 128
+    pairs = (cfg.rotary_dim or cfg.head_dim) // 2
+    cfg.mrope_sections = [pairs // 4, (pairs - pairs // 4) // 2]       # 3-axis rotary sections (multimodal prompts)
     eng = build_engine(cfg, "cpu", seed=1, num_pages=64, max_batch=4, use_cuda_graphs=False)
     if rank == 0:
         lead = LeaderEngine(eng)
@@ -34,10 +36,29 @@ def main():
             time.sleep(0.005)
         loop.shutdown(2.0)
         assert done == ["length"] and toks == want[0]
+        # a multimodal prompt: spliced input rows and 3-axis positions are mirrored with the command
+        mm_tokens, d = [5, 6, 7, 8, 9, 10], cfg.d_model
+        g = torch.Generator().manual_seed(7)
+        embeds = (torch.randn(len(mm_tokens), d, generator=g) * 0.05).to(eng.model.w.embed.dtype)
+        pos3 = torch.tensor([[0, 1, 1, 1, 2, 3], [0, 1, 1, 2, 2, 3], [0, 1, 2, 1, 2, 3]], dtype=torch.int32)
+        ref_eng = build_engine(cfg, "cpu", seed=1, num_pages=64, max_batch=4, use_cuda_graphs=False)
+        rs = ref_eng.new_sequence(mm_tokens)
+        want_first = ref_eng.prefill([rs], embeds=embeds, rope_pos3=pos3, one_chunk=True)
+        rs.tokens.append(want_first[0])
+        want_next = ref_eng.decode([rs])
+        s = lead.new_sequence(mm_tokens)
+        first = lead.prefill([s], embeds=embeds, rope_pos3=pos3, one_chunk=True)
+        s.tokens.append(first[0])
+        nxt = lead.decode([s])
+        assert (first, nxt) == (want_first, want_next), (first, nxt, want_first, want_next)
+        mm_delta = s.rope_delta
+        lead.free_sequence(s)
+        ref_eng.free_sequence(rs)
         lead.stop_followers()
     else:
         handled = follow(eng)
         assert handled > 10
+        mm_delta = None
     st = eng.cache.pool.stats()
     assert st["sequences"] == 0 and st["free"] == st["pages"], st
     gathered = [None, None]
