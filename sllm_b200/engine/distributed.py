@@ -153,6 +153,10 @@ class LeaderEngine:
         self._ch.send(("extend", self._sync_tokens(seqs), sample))
         return self._e.extend(seqs, sample)
 
+    def embed_hidden(self, ids):
+        self._ch.send(("embed", list(ids)))
+        return self._e.embed_hidden(ids)
+
     def generate(self, prompts, max_new_tokens, eos=None, on_token=None):
         return Engine.generate(self, prompts, max_new_tokens, eos, on_token)
 
@@ -199,6 +203,8 @@ def _replay(engine: Engine, seqs: dict, cmd) -> None:
         engine.fork_kv(seqs[cmd[1]], cmd[2])          # pool ids advance identically on every rank
     elif op == "kvfree":
         engine.free_kv(cmd[1])
+    elif op == "embed":
+        engine.embed_hidden(cmd[1])
     elif op == "prefill_mm":
         batch = []
         for h, new_tokens in cmd[1]:

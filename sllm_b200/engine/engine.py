@@ -203,6 +203,24 @@ class Engine:
             s_.tokens.append(t)
         return {"step_us": round(sum(us for _, us in rep), 2), "launches": len(rep), "by_kernel": by}
 
+    def embed_hidden(self, ids: list) -> torch.Tensor:
+        """Final-normed hidden rows [len(ids), d] of one token list, computed on scratch KV pages that are released
+        again (the embeddings / rerank endpoints pool these rows).  On a multi-rank engine the leader mirrors the call,
+        so every rank runs the same kernels and collectives."""
+        from .batch import make_prefill_batch
+        from .. import ops
+        self._guard()
+        seq = self.new_sequence(ids)
+        try:
+            self.cache.pool.reserve(seq.seq_id, len(ids))
+            table = torch.zeros((1, self.max_blocks), dtype=torch.int32)
+            self.cache.pool.fill_block_table([seq.seq_id], table)
+            b = make_prefill_batch([list(ids)], table.to(self.device), self.device, last_only=False)
+            h = self.model.hidden(b, self.cache)
+            return ops.rmsnorm(h, self.model.w.final_norm, self.cfg.rms_eps, self.cfg.norm_offset_one)
+        finally:
+            self.free_sequence(seq)
+
     def shutdown_report(self) -> dict:
         """What a supervisor logs when the engine goes away: memory by category, launch and copy counters, fallbacks
         and the quarantine record."""

@@ -242,11 +242,31 @@ class EngineLoop:
         self._wake = threading.Condition(self._lock)
         self._accepting = True
         self._stop = False
+        self._calls: list = []               # (callable, result box) pairs to run on the engine thread between rounds
         self._thread = threading.Thread(target=self._run, name="sllm-engine-loop", daemon=True)
         self._thread.start()
         self.rounds = {"prefill": 0, "decode": 0}
 
     # ---------------------------------------------------------------- public
+    def call(self, fn, timeout: float = 600.0):
+        """Runs ``fn()`` on the engine thread between two rounds and returns its result (or raises what it raised).
+        Device work and KV bookkeeping have one owner: a handler thread that needs the engine (embeddings, rerank) goes
+        through here instead of touching it beside a running round - on a multi-rank engine that also keeps the
+        mirrored commands in one order."""
+        if threading.current_thread() is self._thread:
+            return fn()
+        box = {"done": threading.Event(), "out": None, "err": None}
+        with self._wake:
+            if self._stop:
+                raise QueueFull("scheduler has stopped")
+            self._calls.append((fn, box))
+            self._wake.notify_all()
+        if not box["done"].wait(timeout):
+            raise TimeoutError("engine call timed out")
+        if box["err"] is not None:
+            raise box["err"]
+        return box["out"]
+
     def submit(self, req: GenRequest) -> int:
         with self._wake:
             if not self._accepting:
@@ -370,11 +390,23 @@ class EngineLoop:
     def _run_loop(self) -> None:
         while True:
             with self._wake:
-                while not self._stop and self.planner.idle():
+                while not self._stop and self.planner.idle() and not self._calls:
                     self._wake.wait(timeout=0.05)
                     self._expire_locked()
+                calls, self._calls = self._calls, []
                 if self._stop:
+                    for _, box in calls:
+                        box["err"] = QueueFull("scheduler has stopped")
+                        box["done"].set()
                     return
+            for fn, box in calls:                  # outside the lock: submitters are not held up by device work
+                try:
+                    box["out"] = fn()
+                except BaseException as exc:       # handed to the caller
+                    box["err"] = exc
+                finally:
+                    box["done"].set()
+            with self._wake:
                 self._expire_locked()
                 rnd = self.planner.next_round()
                 if rnd is None:

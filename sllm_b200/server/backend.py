@@ -268,30 +268,19 @@ class EngineBackend:
         """Mean of the final hidden rows in float64, L2-normalised, finite float32
         (reference: crates/sllm-core/src/inference_embedding.rs)."""
         import torch
-        from ..engine.batch import make_prefill_batch
-        if type(self.engine).__name__ == "LeaderEngine":
-            raise RuntimeError("embeddings are not available on a multi-rank engine")
-        out = []
+
+        def one(ids):
+            h = self.engine.embed_hidden(ids)
+            v = h.double().mean(dim=0)
+            n = torch.linalg.vector_norm(v)
+            v = (v / n if float(n) > 0 else v).float().cpu().numpy()
+            if not np.isfinite(v).all():
+                raise ValueError("embedding is not finite")
+            return v
+
+        # one list per engine call: generation rounds of other requests interleave with a long batch of inputs
         with self._embed_lock:
-            for ids in token_lists:
-                seq = self.engine.new_sequence(ids)
-                try:
-                    self.engine.cache.pool.reserve(seq.seq_id, len(ids))
-                    table = torch.zeros((1, self.engine.max_blocks), dtype=torch.int32)
-                    self.engine.cache.pool.fill_block_table([seq.seq_id], table)
-                    b = make_prefill_batch([ids], table.to(self.engine.device), self.engine.device, last_only=False)
-                    h = self.engine.model.hidden(b, self.engine.cache)
-                    from .. import ops
-                    h = ops.rmsnorm(h, self.engine.model.w.final_norm, self.engine.cfg.rms_eps, self.engine.cfg.norm_offset_one)
-                    v = h.double().mean(dim=0)
-                    n = torch.linalg.vector_norm(v)
-                    v = (v / n if float(n) > 0 else v).float().cpu().numpy()
-                    if not np.isfinite(v).all():
-                        raise ValueError("embedding is not finite")
-                    out.append(v)
-                finally:
-                    self.engine.free_sequence(seq)
-        return out
+            return [self.loop.call(lambda ids=ids: one(ids)) for ids in token_lists]
 
     def shutdown(self, timeout: float = 30.0) -> dict:
         return self.loop.shutdown(timeout)

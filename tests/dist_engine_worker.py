@@ -54,6 +54,8 @@ def main():
         mm_delta = s.rope_delta
         lead.free_sequence(s)
         ref_eng.free_sequence(rs)
+        # hidden rows for the embeddings endpoint: mirrored too
+        assert torch.equal(lead.embed_hidden([3, 4, 5, 6, 7]), ref_eng.embed_hidden([3, 4, 5, 6, 7]))
         lead.stop_followers()
     else:
         handled = follow(eng)
