@@ -87,6 +87,12 @@ def test_multi_rank_server_over_http(world, tmp_path):
         with urllib.request.urlopen(f"http://127.0.0.1:{port}/props", timeout=30) as r:
             props = json.loads(r.read())
         assert props["models"][0]["tensor_parallel"] == world and props["models"][0]["quarantine"] is None
+        # embeddings run on the engine thread and are mirrored to the follower rank
+        emb = json.loads(post("/v1/embeddings", {"model": props["models"][0]["id"] if "id" in props["models"][0] else body["model"],
+                                                 "input": ["alpha beta gamma", "delta"]}))
+        assert len(emb["data"]) == 2 and abs(sum(x * x for x in emb["data"][0]["embedding"]) - 1.0) < 1e-3
+        c = json.loads(post("/v1/completions", body))          # generation still works after the mirrored calls
+        assert c["choices"][0]["text"] == a["choices"][0]["text"]
         # (numerical agreement of the sharded model with the single-GPU one is the subject of tp_worker.py; greedy text
         # of a random-weight model is decided by near-ties and is not compared across layouts)
     finally:
