@@ -93,3 +93,26 @@ def test_roundtrip_on_the_gpu(tmp_path):
     r = RT.roundtrip(state_dir=str(tmp_path), timeout=240.0)
     assert r["ok"] and r["device_status"] == 0 and r["circuit"] == "closed", r
     assert set(r["checks"]) == {"gemm_bf16", "gemm_fp8", "rmsnorm", "gated_act", "argmax", "paged_attention"}
+
+
+def test_accuracy_runner_orders_the_formats_on_the_cpu():
+    """KL(bf16 || candidate) over shared seeded weights: identical configurations give zero, FP8 moves the distribution
+    less than 4-bit weights, and 4-bit activations add to the 4-bit weights' divergence."""
+    from sllm_b200.evidence import accuracy as ACC
+    same = ACC.compare("bf16", "bf16", device="cpu", prompts=3, prompt_len=12)
+    assert same["kl_mean"] == 0.0 and same["top1_agreement"] == 1.0
+    fp8 = ACC.compare("bf16", "fp8", device="cpu", prompts=3, prompt_len=12)
+    w4 = ACC.compare("bf16", "nvfp4", device="cpu", prompts=3, prompt_len=12)
+    w4a4 = ACC.compare("bf16", "nvfp4", act4=True, device="cpu", prompts=3, prompt_len=12)
+    assert 0.0 < fp8["kl_mean"] < w4["kl_mean"] < w4a4["kl_mean"] and w4a4["finite"]
+    assert w4a4["candidate"] == "nvfp4+act4" and w4a4["schema"] == "sllm-accuracy-v1"
+    with pytest.raises(ValueError):
+        ACC.compare("bf16", "fp8", act4=True, device="cpu")
+
+
+@pytest.mark.gpu
+def test_accuracy_runner_on_the_gpu():
+    from sllm_b200.evidence import accuracy as ACC
+    rep = ACC.compare("bf16", "nvfp4", act4=True, device="cuda", prompts=4, prompt_len=16)
+    cpu = ACC.compare("bf16", "nvfp4", act4=True, device="cpu", prompts=4, prompt_len=16)
+    assert rep["finite"] and 0.0 < rep["kl_mean"] < 4 * cpu["kl_mean"] + 1e-3
